@@ -1,0 +1,844 @@
+// Implementation of include/hc-c/Cuda.h: the MLIR-free launch layer that sits where the
+// reference keeps its C API (lib/CAPI/HC.cpp, lib/CAPI/HCFront.cpp). It validates the
+// caller's buffers, chooses a kernel variant, encodes TMA tensor maps, manages the
+// context's scratch memory and enqueues the sm_100a kernels of lib/Kernels.
+//
+// Nothing here computes a matrix product on the host: without a device the compute entry
+// points fail.
+#include "hc-c/Cuda.h"
+
+#include "../Kernels/gemm_launch.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <dlfcn.h>
+#include <nccl.h>  // types only; the library is opened at run time
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <new>
+#include <string>
+
+namespace {
+
+using hc::sm100::kDTypeBF16;
+
+constexpr int kDefaultSmCount = 148;
+constexpr int64_t kMaxDim = int64_t(1) << 30;
+constexpr int64_t kMaxPitch = int64_t(1) << 38;
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                   const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                   const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct NcclApi {
+  void *handle = nullptr;
+  ncclResult_t (*GetUniqueId)(ncclUniqueId *) = nullptr;
+  ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
+  ncclResult_t (*AllGather)(const void *, void *, size_t, ncclDataType_t, ncclComm_t,
+                            cudaStream_t) = nullptr;
+  ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+  const char *(*GetErrorString)(ncclResult_t) = nullptr;
+  bool ok = false;
+};
+
+NcclApi &nccl_api() {
+  static NcclApi api;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    const char *override_path = std::getenv("HC_CUDA_NCCL_LIB");
+    const char *names[] = {override_path, "libnccl.so.2", "libnccl.so"};
+    for (const char *name : names) {
+      if (name == nullptr || *name == '\0')
+        continue;
+      api.handle = dlopen(name, RTLD_NOW | RTLD_GLOBAL);
+      if (api.handle != nullptr)
+        break;
+    }
+    if (api.handle == nullptr)
+      return;
+    api.GetUniqueId =
+        reinterpret_cast<decltype(api.GetUniqueId)>(dlsym(api.handle, "ncclGetUniqueId"));
+    api.CommInitRank =
+        reinterpret_cast<decltype(api.CommInitRank)>(dlsym(api.handle, "ncclCommInitRank"));
+    api.AllGather = reinterpret_cast<decltype(api.AllGather)>(dlsym(api.handle, "ncclAllGather"));
+    api.CommDestroy =
+        reinterpret_cast<decltype(api.CommDestroy)>(dlsym(api.handle, "ncclCommDestroy"));
+    api.GetErrorString =
+        reinterpret_cast<decltype(api.GetErrorString)>(dlsym(api.handle, "ncclGetErrorString"));
+    api.ok = api.GetUniqueId && api.CommInitRank && api.AllGather && api.CommDestroy &&
+             api.GetErrorString;
+  });
+  return api;
+}
+
+thread_local std::string g_thread_error;
+
+} // namespace
+
+struct HcCudaEvent {
+  cudaEvent_t event = nullptr;
+};
+
+struct HcCudaContext {
+  int device = -1;
+  cudaStream_t stream = nullptr;
+  cudaDeviceProp prop{};
+  int *status_dev = nullptr;
+  int *status_host = nullptr;  // pinned
+  void *scratch = nullptr;
+  size_t scratch_bytes = 0;
+  unsigned *counters = nullptr;
+  size_t counters_bytes = 0;
+  void *stage[3] = {nullptr, nullptr, nullptr};  // device staging for host-buffer calls
+  size_t stage_bytes[3] = {0, 0, 0};
+  EncodeTiledFn encode = nullptr;
+  int group_n = 8;
+  ncclComm_t comm = nullptr;
+  int nranks = 0;
+  int rank = -1;
+  mutable std::mutex mu;
+  std::string last_error;
+};
+
+namespace {
+
+int fail(const HcCudaContext *ctx, int status, const char *fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  if (ctx != nullptr)
+    const_cast<HcCudaContext *>(ctx)->last_error = buf;
+  else
+    g_thread_error = buf;
+  return status;
+}
+
+int fail_cuda(const HcCudaContext *ctx, cudaError_t err, const char *what) {
+  const int status = err == cudaErrorMemoryAllocation ? HC_CUDA_ERR_OUT_OF_MEMORY : HC_CUDA_ERR_CUDA;
+  return fail(ctx, status, "%s: %s (%s)", what, cudaGetErrorName(err), cudaGetErrorString(err));
+}
+
+#define HC_TRY_CUDA(ctx, expr)                                                                     \
+  do {                                                                                             \
+    cudaError_t hc_err__ = (expr);                                                                 \
+    if (hc_err__ != cudaSuccess)                                                                   \
+      return fail_cuda((ctx), hc_err__, #expr);                                                    \
+  } while (0)
+
+int64_t round_up(int64_t v, int64_t to) { return (v + to - 1) / to * to; }
+
+bool ranges_overlap(const void *p, size_t pbytes, const void *q, size_t qbytes) {
+  const uintptr_t a = reinterpret_cast<uintptr_t>(p), b = reinterpret_cast<uintptr_t>(q);
+  return pbytes != 0 && qbytes != 0 && a < b + qbytes && b < a + pbytes;
+}
+
+// Validation + variant choice shared by hcCudaGemmPlan, hcCudaGemm and hcCudaGemmHost.
+// `host_buffers`: the pointers are host memory that will be staged with aligned pitches, so
+// no repack is ever needed.
+int plan_gemm(const HcCudaContext *ctx, const HcCudaGemmArgs *args, int sm_count, bool host_buffers,
+              HcCudaGemmPlanInfo *plan) {
+  if (args == nullptr || plan == nullptr)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "args and plan must not be null");
+  std::memset(plan, 0, sizeof(*plan));
+  plan->splits = 1;
+  const int64_t m = args->m, n = args->n, k = args->k;
+  if (m < 0 || n < 0 || k < 0)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "m, n, k must be non-negative (got %lld, %lld, %lld)",
+                (long long)m, (long long)n, (long long)k);
+  if (m > kMaxDim || n > kMaxDim || k > kMaxDim)
+    return fail(ctx, HC_CUDA_ERR_UNSUPPORTED, "m, n, k must each be at most 2^30");
+  if (args->dtype != HC_CUDA_F16 && args->dtype != HC_CUDA_BF16)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "dtype must be HC_CUDA_F16 or HC_CUDA_BF16 (got %d)",
+                args->dtype);
+  if (args->variant != HC_CUDA_GEMM_AUTO && args->variant != HC_CUDA_GEMM_DENSE &&
+      args->variant != HC_CUDA_GEMM_SKINNY)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "variant must be AUTO, DENSE or SKINNY (got %d)",
+                args->variant);
+  if (sm_count <= 0)
+    sm_count = kDefaultSmCount;
+
+  if (m == 0 || n == 0) {
+    plan->variant = HC_CUDA_GEMM_NOOP;
+    return HC_CUDA_OK;
+  }
+  if (args->c == nullptr)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "c must not be null");
+  if (args->ldc < n || args->ldc > kMaxPitch)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "ldc (%lld) must be at least n (%lld)",
+                (long long)args->ldc, (long long)n);
+  if ((reinterpret_cast<uintptr_t>(args->c) & 3) != 0)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "c must be 4-byte aligned");
+  if (k == 0) {
+    plan->variant = HC_CUDA_GEMM_ZERO_FILL;
+    return HC_CUDA_OK;
+  }
+  if (args->a == nullptr || args->b == nullptr)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "a and b must not be null");
+  if (args->lda < k || args->lda > kMaxPitch)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "lda (%lld) must be at least k (%lld)",
+                (long long)args->lda, (long long)k);
+  if (args->ldb < n || args->ldb > kMaxPitch)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "ldb (%lld) must be at least n (%lld)",
+                (long long)args->ldb, (long long)n);
+  if ((reinterpret_cast<uintptr_t>(args->a) & 1) != 0 || (reinterpret_cast<uintptr_t>(args->b) & 1) != 0)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "a and b must be 2-byte aligned");
+  const size_t a_bytes = (static_cast<size_t>(m - 1) * args->lda + k) * 2;
+  const size_t b_bytes = (static_cast<size_t>(k - 1) * args->ldb + n) * 2;
+  const size_t c_bytes = (static_cast<size_t>(m - 1) * args->ldc + n) * 4;
+  if (ranges_overlap(args->c, c_bytes, args->a, a_bytes) ||
+      ranges_overlap(args->c, c_bytes, args->b, b_bytes))
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "c must not overlap a or b");
+
+  int variant = args->variant;
+  const int skinny_max_m = hc::sm100::skinny_shape(1).max_m;
+  if (variant == HC_CUDA_GEMM_SKINNY && m > skinny_max_m)
+    return fail(ctx, HC_CUDA_ERR_UNSUPPORTED, "the skinny variant needs m <= %d (got %lld)",
+                skinny_max_m, (long long)m);
+  if (variant == HC_CUDA_GEMM_AUTO)
+    variant = m <= skinny_max_m ? HC_CUDA_GEMM_SKINNY : HC_CUDA_GEMM_DENSE;
+  plan->variant = variant;
+
+  if (!host_buffers) {
+    plan->repack_a = ((args->lda & 7) != 0 || (reinterpret_cast<uintptr_t>(args->a) & 15) != 0) ? 1 : 0;
+    plan->repack_b = ((args->ldb & 7) != 0 || (reinterpret_cast<uintptr_t>(args->b) & 15) != 0) ? 1 : 0;
+  }
+  int64_t scratch = 0;
+  if (plan->repack_a)
+    scratch += round_up(m * round_up(k, 8) * 2, 1024);
+  if (plan->repack_b)
+    scratch += round_up(k * round_up(n, 8) * 2, 1024);
+  plan->kernel_launches = 1 + plan->repack_a + plan->repack_b;
+
+  if (variant == HC_CUDA_GEMM_DENSE) {
+    const hc::sm100::DenseTileShape t = hc::sm100::dense_tile_shape();
+    plan->tiles_m = static_cast<int32_t>((m + t.block_m - 1) / t.block_m);
+    plan->tiles_n = static_cast<int32_t>((n + t.block_n - 1) / t.block_n);
+    const int64_t tiles = static_cast<int64_t>(plan->tiles_m) * plan->tiles_n;
+    if (tiles > 0x7fffffffLL)
+      return fail(ctx, HC_CUDA_ERR_UNSUPPORTED, "too many tiles");
+    plan->grid = static_cast<int32_t>(tiles < sm_count ? tiles : sm_count);
+  } else {
+    const hc::sm100::SkinnyShape s = hc::sm100::skinny_shape(static_cast<int>(m));
+    plan->tiles_m = 1;
+    plan->tiles_n = static_cast<int32_t>((n + s.block_n - 1) / s.block_n);
+    plan->splits = hc::sm100::skinny_choose_splits(static_cast<int>(n), static_cast<int>(k), sm_count);
+    const int64_t units = static_cast<int64_t>(plan->tiles_n) * plan->splits;
+    const int64_t slots = static_cast<int64_t>(sm_count) * 2;
+    plan->grid = static_cast<int32_t>(units < slots ? units : slots);
+    scratch += static_cast<int64_t>(
+        hc::sm100::skinny_partials_bytes(static_cast<int>(m), static_cast<int>(n), plan->splits));
+  }
+  plan->scratch_bytes = scratch;
+  return HC_CUDA_OK;
+}
+
+int ensure_scratch(HcCudaContext *ctx, size_t bytes) {
+  if (bytes <= ctx->scratch_bytes)
+    return HC_CUDA_OK;
+  if (ctx->scratch != nullptr) {
+    HC_TRY_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    HC_TRY_CUDA(ctx, cudaFree(ctx->scratch));
+    ctx->scratch = nullptr;
+    ctx->scratch_bytes = 0;
+  }
+  const size_t grown = static_cast<size_t>(round_up(static_cast<int64_t>(bytes), 1 << 20));
+  HC_TRY_CUDA(ctx, cudaMalloc(&ctx->scratch, grown));
+  ctx->scratch_bytes = grown;
+  return HC_CUDA_OK;
+}
+
+int ensure_counters(HcCudaContext *ctx, size_t bytes) {
+  if (bytes <= ctx->counters_bytes)
+    return HC_CUDA_OK;
+  if (ctx->counters != nullptr) {
+    HC_TRY_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    HC_TRY_CUDA(ctx, cudaFree(ctx->counters));
+    ctx->counters = nullptr;
+    ctx->counters_bytes = 0;
+  }
+  const size_t grown = static_cast<size_t>(round_up(static_cast<int64_t>(bytes), 4096));
+  HC_TRY_CUDA(ctx, cudaMalloc(reinterpret_cast<void **>(&ctx->counters), grown));
+  HC_TRY_CUDA(ctx, cudaMemsetAsync(ctx->counters, 0, grown, ctx->stream));
+  ctx->counters_bytes = grown;
+  return HC_CUDA_OK;
+}
+
+int ensure_stage(HcCudaContext *ctx, int which, size_t bytes) {
+  if (bytes <= ctx->stage_bytes[which])
+    return HC_CUDA_OK;
+  if (ctx->stage[which] != nullptr) {
+    HC_TRY_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    HC_TRY_CUDA(ctx, cudaFree(ctx->stage[which]));
+    ctx->stage[which] = nullptr;
+    ctx->stage_bytes[which] = 0;
+  }
+  const size_t grown = static_cast<size_t>(round_up(static_cast<int64_t>(bytes), 1 << 20));
+  HC_TRY_CUDA(ctx, cudaMalloc(&ctx->stage[which], grown));
+  ctx->stage_bytes[which] = grown;
+  return HC_CUDA_OK;
+}
+
+int encode_map(HcCudaContext *ctx, CUtensorMap *map, int dtype, const void *base, uint64_t inner,
+               uint64_t outer, uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_outer) {
+  const cuuint64_t dims[2] = {inner, outer};
+  const cuuint64_t strides[1] = {pitch_bytes};
+  const cuuint32_t box[2] = {box_inner, box_outer};
+  const cuuint32_t elem_strides[2] = {1, 1};
+  const CUtensorMapDataType type =
+      dtype == HC_CUDA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const CUresult res = ctx->encode(map, type, 2, const_cast<void *>(base), dims, strides, box,
+                                   elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (res != CUDA_SUCCESS)
+    return fail(ctx, HC_CUDA_ERR_CUDA,
+                "cuTensorMapEncodeTiled failed with CUresult %d (base %p, dims %llu x %llu, pitch %llu)",
+                static_cast<int>(res), base, (unsigned long long)inner, (unsigned long long)outer,
+                (unsigned long long)pitch_bytes);
+  return HC_CUDA_OK;
+}
+
+// Enqueues the GEMM on device-resident buffers. The caller holds ctx->mu and has made the
+// context's device current.
+int enqueue_gemm(HcCudaContext *ctx, const HcCudaGemmArgs *args, const HcCudaGemmPlanInfo &plan) {
+  if (plan.variant == HC_CUDA_GEMM_NOOP)
+    return HC_CUDA_OK;
+  const int m = static_cast<int>(args->m), n = static_cast<int>(args->n), k = static_cast<int>(args->k);
+  if (plan.variant == HC_CUDA_GEMM_ZERO_FILL) {
+    HC_TRY_CUDA(ctx, cudaMemset2DAsync(args->c, static_cast<size_t>(args->ldc) * 4, 0,
+                                       static_cast<size_t>(n) * 4, static_cast<size_t>(m), ctx->stream));
+    return HC_CUDA_OK;
+  }
+  if (int rc = ensure_scratch(ctx, static_cast<size_t>(plan.scratch_bytes)))
+    return rc;
+
+  const void *a = args->a;
+  const void *b = args->b;
+  int64_t lda = args->lda, ldb = args->ldb;
+  char *cursor = static_cast<char *>(ctx->scratch);
+  if (plan.repack_a) {
+    const int64_t ld = round_up(k, 8);
+    HC_TRY_CUDA(ctx, hc::sm100::launch_repack_pitch(a, lda, cursor, ld, m, k, ctx->stream));
+    a = cursor;
+    lda = ld;
+    cursor += round_up(static_cast<int64_t>(m) * ld * 2, 1024);
+  }
+  if (plan.repack_b) {
+    const int64_t ld = round_up(n, 8);
+    HC_TRY_CUDA(ctx, hc::sm100::launch_repack_pitch(b, ldb, cursor, ld, k, n, ctx->stream));
+    b = cursor;
+    ldb = ld;
+    cursor += round_up(static_cast<int64_t>(k) * ld * 2, 1024);
+  }
+
+  CUtensorMap tmap_a, tmap_b;
+  if (plan.variant == HC_CUDA_GEMM_DENSE) {
+    const hc::sm100::DenseTileShape t = hc::sm100::dense_tile_shape();
+    if (int rc = encode_map(ctx, &tmap_a, args->dtype, a, k, m, static_cast<uint64_t>(lda) * 2,
+                            t.block_k, t.block_m))
+      return rc;
+    if (int rc = encode_map(ctx, &tmap_b, args->dtype, b, n, k, static_cast<uint64_t>(ldb) * 2, 64,
+                            t.block_k))
+      return rc;
+    HC_TRY_CUDA(ctx, hc::sm100::launch_gemm_dense(tmap_a, tmap_b, args->c, m, n, k, args->ldc,
+                                                  args->dtype, ctx->group_n, plan.grid,
+                                                  ctx->status_dev, ctx->stream));
+    return HC_CUDA_OK;
+  }
+
+  const hc::sm100::SkinnyShape s = hc::sm100::skinny_shape(m);
+  const uint32_t padded_m = m <= 16 ? 16 : (m <= 32 ? 32 : 64);
+  if (int rc = encode_map(ctx, &tmap_a, args->dtype, a, k, m, static_cast<uint64_t>(lda) * 2,
+                          s.block_k, padded_m))
+    return rc;
+  if (int rc = encode_map(ctx, &tmap_b, args->dtype, b, n, k, static_cast<uint64_t>(ldb) * 2, 64,
+                          s.block_k))
+    return rc;
+  float *partials = nullptr;
+  if (plan.splits > 1) {
+    partials = reinterpret_cast<float *>(cursor);
+    if (int rc = ensure_counters(ctx, hc::sm100::skinny_counters_bytes(n)))
+      return rc;
+  }
+  HC_TRY_CUDA(ctx, hc::sm100::launch_gemm_skinny(tmap_a, tmap_b, args->c, m, n, k, args->ldc,
+                                                 args->dtype, plan.splits, partials, ctx->counters,
+                                                 plan.grid, ctx->status_dev, ctx->stream));
+  return HC_CUDA_OK;
+}
+
+int synchronize_locked(HcCudaContext *ctx) {
+  HC_TRY_CUDA(ctx, cudaMemcpyAsync(ctx->status_host, ctx->status_dev, sizeof(int),
+                                   cudaMemcpyDeviceToHost, ctx->stream));
+  HC_TRY_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  const int device_status = *ctx->status_host;
+  if (device_status != 0) {
+    HC_TRY_CUDA(ctx, cudaMemsetAsync(ctx->status_dev, 0, sizeof(int), ctx->stream));
+    // A kernel that gave up may have left split-k arrival counters half counted.
+    if (ctx->counters != nullptr)
+      HC_TRY_CUDA(ctx, cudaMemsetAsync(ctx->counters, 0, ctx->counters_bytes, ctx->stream));
+    HC_TRY_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return fail(ctx, HC_CUDA_ERR_DEVICE_TIMEOUT,
+                "a kernel reported status %d: a bounded device-side wait ran out; the output of "
+                "that launch is invalid",
+                device_status);
+  }
+  return HC_CUDA_OK;
+}
+
+} // namespace
+
+extern "C" {
+
+int hcCudaApiVersion(void) { return HC_CUDA_API_VERSION; }
+
+const char *hcCudaStatusString(int status) {
+  switch (status) {
+  case HC_CUDA_OK: return "HC_CUDA_OK";
+  case HC_CUDA_ERR_INVALID_ARGUMENT: return "HC_CUDA_ERR_INVALID_ARGUMENT";
+  case HC_CUDA_ERR_UNSUPPORTED: return "HC_CUDA_ERR_UNSUPPORTED";
+  case HC_CUDA_ERR_CUDA: return "HC_CUDA_ERR_CUDA";
+  case HC_CUDA_ERR_NO_DEVICE: return "HC_CUDA_ERR_NO_DEVICE";
+  case HC_CUDA_ERR_DEVICE_TIMEOUT: return "HC_CUDA_ERR_DEVICE_TIMEOUT";
+  case HC_CUDA_ERR_COMM: return "HC_CUDA_ERR_COMM";
+  case HC_CUDA_ERR_OUT_OF_MEMORY: return "HC_CUDA_ERR_OUT_OF_MEMORY";
+  default: return "HC_CUDA_ERR_UNKNOWN";
+  }
+}
+
+int hcCudaGetDeviceCount(int *count) {
+  if (count == nullptr)
+    return fail(nullptr, HC_CUDA_ERR_INVALID_ARGUMENT, "count must not be null");
+  int n = 0;
+  const cudaError_t err = cudaGetDeviceCount(&n);
+  if (err != cudaSuccess) {
+    cudaGetLastError();  // no driver / no device is an answer, not a failure
+    n = 0;
+  }
+  *count = n;
+  return HC_CUDA_OK;
+}
+
+int hcCudaContextCreate(int device, HcCudaContext **out) {
+  if (out == nullptr)
+    return fail(nullptr, HC_CUDA_ERR_INVALID_ARGUMENT, "out must not be null");
+  *out = nullptr;
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess) {
+    cudaGetLastError();
+    count = 0;
+  }
+  if (device < 0 || device >= count)
+    return fail(nullptr, HC_CUDA_ERR_NO_DEVICE, "device %d does not exist (%d CUDA device(s) visible)",
+                device, count);
+  HcCudaContext *ctx = new (std::nothrow) HcCudaContext();
+  if (ctx == nullptr)
+    return fail(nullptr, HC_CUDA_ERR_OUT_OF_MEMORY, "out of host memory");
+  ctx->device = device;
+  auto bail = [&](int status) {
+    g_thread_error = ctx->last_error;
+    hcCudaContextDestroy(ctx);
+    return status;
+  };
+  cudaError_t err = cudaSetDevice(device);
+  if (err == cudaSuccess)
+    err = cudaGetDeviceProperties(&ctx->prop, device);
+  if (err != cudaSuccess)
+    return bail(fail_cuda(ctx, err, "selecting the device"));
+  if (ctx->prop.major != 10)
+    return bail(fail(ctx, HC_CUDA_ERR_NO_DEVICE,
+                     "device %d (%s) has compute capability %d.%d; this backend needs sm_100 (10.x)",
+                     device, ctx->prop.name, ctx->prop.major, ctx->prop.minor));
+  err = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
+  if (err == cudaSuccess)
+    err = cudaMalloc(reinterpret_cast<void **>(&ctx->status_dev), sizeof(int));
+  if (err == cudaSuccess)
+    err = cudaMemset(ctx->status_dev, 0, sizeof(int));
+  if (err == cudaSuccess)
+    err = cudaHostAlloc(reinterpret_cast<void **>(&ctx->status_host), sizeof(int), cudaHostAllocDefault);
+  if (err != cudaSuccess)
+    return bail(fail_cuda(ctx, err, "creating the context's stream and status word"));
+  void *fn = nullptr;
+  cudaDriverEntryPointQueryResult query = cudaDriverEntryPointSymbolNotFound;
+  err = cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &fn, 12000, cudaEnableDefault, &query);
+  if (err != cudaSuccess || query != cudaDriverEntryPointSuccess || fn == nullptr) {
+    cudaGetLastError();
+    return bail(fail(ctx, HC_CUDA_ERR_CUDA, "the driver does not provide cuTensorMapEncodeTiled"));
+  }
+  ctx->encode = reinterpret_cast<EncodeTiledFn>(fn);
+  if (const char *g = std::getenv("HC_CUDA_GROUP_N")) {
+    const int v = std::atoi(g);
+    if (v >= 1)
+      ctx->group_n = v;
+  }
+  *out = ctx;
+  return HC_CUDA_OK;
+}
+
+int hcCudaContextDestroy(HcCudaContext *ctx) {
+  if (ctx == nullptr)
+    return HC_CUDA_OK;
+  if (ctx->device >= 0 && cudaSetDevice(ctx->device) == cudaSuccess) {
+    if (ctx->stream != nullptr)
+      cudaStreamSynchronize(ctx->stream);
+    if (ctx->comm != nullptr && nccl_api().ok)
+      nccl_api().CommDestroy(ctx->comm);
+    for (void *p : ctx->stage)
+      if (p != nullptr)
+        cudaFree(p);
+    if (ctx->scratch != nullptr)
+      cudaFree(ctx->scratch);
+    if (ctx->counters != nullptr)
+      cudaFree(ctx->counters);
+    if (ctx->status_dev != nullptr)
+      cudaFree(ctx->status_dev);
+    if (ctx->status_host != nullptr)
+      cudaFreeHost(ctx->status_host);
+    if (ctx->stream != nullptr)
+      cudaStreamDestroy(ctx->stream);
+    cudaGetLastError();
+  }
+  delete ctx;
+  return HC_CUDA_OK;
+}
+
+const char *hcCudaContextLastError(const HcCudaContext *ctx) {
+  if (ctx == nullptr)
+    return g_thread_error.c_str();
+  return ctx->last_error.c_str();
+}
+
+int hcCudaContextGetDeviceInfo(HcCudaContext *ctx, HcCudaDeviceInfo *out) {
+  if (ctx == nullptr || out == nullptr)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "ctx and out must not be null");
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  std::memset(out, 0, sizeof(*out));
+  std::snprintf(out->name, sizeof(out->name), "%.127s", ctx->prop.name);
+  out->device = ctx->device;
+  out->cc_major = ctx->prop.major;
+  out->cc_minor = ctx->prop.minor;
+  out->sm_count = ctx->prop.multiProcessorCount;
+  out->total_memory_bytes = static_cast<int64_t>(ctx->prop.totalGlobalMem);
+  out->l2_bytes = ctx->prop.l2CacheSize;
+  int khz = 0;
+  if (cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, ctx->device) != cudaSuccess)
+    cudaGetLastError();
+  out->sm_clock_khz = khz;
+  return HC_CUDA_OK;
+}
+
+int hcCudaContextSynchronize(HcCudaContext *ctx) {
+  if (ctx == nullptr)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "ctx must not be null");
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  HC_TRY_CUDA(ctx, cudaSetDevice(ctx->device));
+  return synchronize_locked(ctx);
+}
+
+int hcCudaMalloc(HcCudaContext *ctx, size_t bytes, void **device_ptr) {
+  if (ctx == nullptr || device_ptr == nullptr)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "ctx and device_ptr must not be null");
+  *device_ptr = nullptr;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  HC_TRY_CUDA(ctx, cudaSetDevice(ctx->device));
+  if (bytes == 0)
+    return HC_CUDA_OK;
+  HC_TRY_CUDA(ctx, cudaMalloc(device_ptr, bytes));
+  return HC_CUDA_OK;
+}
+
+int hcCudaFree(HcCudaContext *ctx, void *device_ptr) {
+  if (ctx == nullptr)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "ctx must not be null");
+  if (device_ptr == nullptr)
+    return HC_CUDA_OK;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  HC_TRY_CUDA(ctx, cudaSetDevice(ctx->device));
+  HC_TRY_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  HC_TRY_CUDA(ctx, cudaFree(device_ptr));
+  return HC_CUDA_OK;
+}
+
+int hcCudaHostAlloc(size_t bytes, void **host_ptr) {
+  if (host_ptr == nullptr)
+    return fail(nullptr, HC_CUDA_ERR_INVALID_ARGUMENT, "host_ptr must not be null");
+  *host_ptr = nullptr;
+  if (bytes == 0)
+    return HC_CUDA_OK;
+  HC_TRY_CUDA(nullptr, cudaHostAlloc(host_ptr, bytes, cudaHostAllocPortable));
+  return HC_CUDA_OK;
+}
+
+int hcCudaHostFree(void *host_ptr) {
+  if (host_ptr == nullptr)
+    return HC_CUDA_OK;
+  HC_TRY_CUDA(nullptr, cudaFreeHost(host_ptr));
+  return HC_CUDA_OK;
+}
+
+int hcCudaMemcpyHtoD(HcCudaContext *ctx, void *device_dst, const void *host_src, size_t bytes) {
+  if (ctx == nullptr)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "ctx must not be null");
+  if (bytes == 0)
+    return HC_CUDA_OK;
+  if (device_dst == nullptr || host_src == nullptr)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "copy pointers must not be null");
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  HC_TRY_CUDA(ctx, cudaSetDevice(ctx->device));
+  HC_TRY_CUDA(ctx, cudaMemcpyAsync(device_dst, host_src, bytes, cudaMemcpyHostToDevice, ctx->stream));
+  HC_TRY_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return HC_CUDA_OK;
+}
+
+int hcCudaMemcpyDtoH(HcCudaContext *ctx, void *host_dst, const void *device_src, size_t bytes) {
+  if (ctx == nullptr)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "ctx must not be null");
+  if (bytes == 0)
+    return HC_CUDA_OK;
+  if (host_dst == nullptr || device_src == nullptr)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "copy pointers must not be null");
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  HC_TRY_CUDA(ctx, cudaSetDevice(ctx->device));
+  HC_TRY_CUDA(ctx, cudaMemcpyAsync(host_dst, device_src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+  HC_TRY_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return HC_CUDA_OK;
+}
+
+int hcCudaMemcpy2DHtoD(HcCudaContext *ctx, void *device_dst, size_t dst_pitch, const void *host_src,
+                       size_t src_pitch, size_t width_bytes, size_t rows) {
+  if (ctx == nullptr)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "ctx must not be null");
+  if (width_bytes == 0 || rows == 0)
+    return HC_CUDA_OK;
+  if (device_dst == nullptr || host_src == nullptr || dst_pitch < width_bytes || src_pitch < width_bytes)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "bad 2-D copy arguments");
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  HC_TRY_CUDA(ctx, cudaSetDevice(ctx->device));
+  HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(device_dst, dst_pitch, host_src, src_pitch, width_bytes, rows,
+                                     cudaMemcpyHostToDevice, ctx->stream));
+  HC_TRY_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return HC_CUDA_OK;
+}
+
+int hcCudaMemcpy2DDtoH(HcCudaContext *ctx, void *host_dst, size_t dst_pitch, const void *device_src,
+                       size_t src_pitch, size_t width_bytes, size_t rows) {
+  if (ctx == nullptr)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "ctx must not be null");
+  if (width_bytes == 0 || rows == 0)
+    return HC_CUDA_OK;
+  if (host_dst == nullptr || device_src == nullptr || dst_pitch < width_bytes || src_pitch < width_bytes)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "bad 2-D copy arguments");
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  HC_TRY_CUDA(ctx, cudaSetDevice(ctx->device));
+  HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(host_dst, dst_pitch, device_src, src_pitch, width_bytes, rows,
+                                     cudaMemcpyDeviceToHost, ctx->stream));
+  HC_TRY_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return HC_CUDA_OK;
+}
+
+int hcCudaMemset(HcCudaContext *ctx, void *device_ptr, int byte_value, size_t bytes) {
+  if (ctx == nullptr)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "ctx must not be null");
+  if (bytes == 0)
+    return HC_CUDA_OK;
+  if (device_ptr == nullptr)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "device_ptr must not be null");
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  HC_TRY_CUDA(ctx, cudaSetDevice(ctx->device));
+  HC_TRY_CUDA(ctx, cudaMemsetAsync(device_ptr, byte_value, bytes, ctx->stream));
+  return HC_CUDA_OK;
+}
+
+int hcCudaGemmPlan(const HcCudaGemmArgs *args, int sm_count, HcCudaGemmPlanInfo *out) {
+  return plan_gemm(nullptr, args, sm_count, /*host_buffers=*/false, out);
+}
+
+int hcCudaGemm(HcCudaContext *ctx, const HcCudaGemmArgs *args) {
+  if (ctx == nullptr)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "ctx must not be null");
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  HcCudaGemmPlanInfo plan;
+  if (int rc = plan_gemm(ctx, args, ctx->prop.multiProcessorCount, false, &plan))
+    return rc;
+  HC_TRY_CUDA(ctx, cudaSetDevice(ctx->device));
+  return enqueue_gemm(ctx, args, plan);
+}
+
+int hcCudaGemmHost(HcCudaContext *ctx, const HcCudaGemmArgs *args) {
+  if (ctx == nullptr)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "ctx must not be null");
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  HcCudaGemmPlanInfo plan;
+  if (int rc = plan_gemm(ctx, args, ctx->prop.multiProcessorCount, true, &plan))
+    return rc;
+  if (plan.variant == HC_CUDA_GEMM_NOOP)
+    return HC_CUDA_OK;
+  const size_t m = static_cast<size_t>(args->m), n = static_cast<size_t>(args->n),
+               k = static_cast<size_t>(args->k);
+  if (plan.variant == HC_CUDA_GEMM_ZERO_FILL) {
+    for (size_t i = 0; i < m; ++i)
+      std::memset(args->c + i * static_cast<size_t>(args->ldc), 0, n * sizeof(float));
+    return HC_CUDA_OK;
+  }
+  HC_TRY_CUDA(ctx, cudaSetDevice(ctx->device));
+  // Device copies get pitches that satisfy TMA (16 bytes), so no repack pass is needed.
+  const size_t lda = static_cast<size_t>(round_up(args->k, 8));
+  const size_t ldb = static_cast<size_t>(round_up(args->n, 8));
+  const size_t ldc = static_cast<size_t>(round_up(args->n, 4));
+  if (int rc = ensure_stage(ctx, 0, m * lda * 2))
+    return rc;
+  if (int rc = ensure_stage(ctx, 1, k * ldb * 2))
+    return rc;
+  if (int rc = ensure_stage(ctx, 2, m * ldc * 4))
+    return rc;
+  HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(ctx->stage[0], lda * 2, args->a, static_cast<size_t>(args->lda) * 2,
+                                     k * 2, m, cudaMemcpyHostToDevice, ctx->stream));
+  HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(ctx->stage[1], ldb * 2, args->b, static_cast<size_t>(args->ldb) * 2,
+                                     n * 2, k, cudaMemcpyHostToDevice, ctx->stream));
+  HcCudaGemmArgs dev = *args;
+  dev.a = ctx->stage[0];
+  dev.lda = static_cast<int64_t>(lda);
+  dev.b = ctx->stage[1];
+  dev.ldb = static_cast<int64_t>(ldb);
+  dev.c = static_cast<float *>(ctx->stage[2]);
+  dev.ldc = static_cast<int64_t>(ldc);
+  if (int rc = plan_gemm(ctx, &dev, ctx->prop.multiProcessorCount, false, &plan))
+    return rc;
+  if (int rc = enqueue_gemm(ctx, &dev, plan))
+    return rc;
+  HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(args->c, static_cast<size_t>(args->ldc) * 4, ctx->stage[2], ldc * 4,
+                                     n * 4, m, cudaMemcpyDeviceToHost, ctx->stream));
+  return synchronize_locked(ctx);
+}
+
+int hcCudaEventCreate(HcCudaContext *ctx, HcCudaEvent **out) {
+  if (ctx == nullptr || out == nullptr)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "ctx and out must not be null");
+  *out = nullptr;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  HC_TRY_CUDA(ctx, cudaSetDevice(ctx->device));
+  HcCudaEvent *ev = new (std::nothrow) HcCudaEvent();
+  if (ev == nullptr)
+    return fail(ctx, HC_CUDA_ERR_OUT_OF_MEMORY, "out of host memory");
+  const cudaError_t err = cudaEventCreate(&ev->event);
+  if (err != cudaSuccess) {
+    delete ev;
+    return fail_cuda(ctx, err, "cudaEventCreate");
+  }
+  *out = ev;
+  return HC_CUDA_OK;
+}
+
+int hcCudaEventDestroy(HcCudaContext *ctx, HcCudaEvent *event) {
+  if (event == nullptr)
+    return HC_CUDA_OK;
+  if (ctx != nullptr)
+    cudaSetDevice(ctx->device);
+  if (event->event != nullptr)
+    cudaEventDestroy(event->event);
+  delete event;
+  return HC_CUDA_OK;
+}
+
+int hcCudaEventRecord(HcCudaContext *ctx, HcCudaEvent *event) {
+  if (ctx == nullptr || event == nullptr)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "ctx and event must not be null");
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  HC_TRY_CUDA(ctx, cudaSetDevice(ctx->device));
+  HC_TRY_CUDA(ctx, cudaEventRecord(event->event, ctx->stream));
+  return HC_CUDA_OK;
+}
+
+int hcCudaEventElapsedMs(HcCudaContext *ctx, HcCudaEvent *start, HcCudaEvent *stop, float *milliseconds) {
+  if (ctx == nullptr || start == nullptr || stop == nullptr || milliseconds == nullptr)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "ctx, events and milliseconds must not be null");
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  HC_TRY_CUDA(ctx, cudaSetDevice(ctx->device));
+  HC_TRY_CUDA(ctx, cudaEventSynchronize(stop->event));
+  HC_TRY_CUDA(ctx, cudaEventElapsedTime(milliseconds, start->event, stop->event));
+  return HC_CUDA_OK;
+}
+
+int hcCudaCommGetUniqueId(void *id, size_t id_bytes) {
+  static_assert(sizeof(ncclUniqueId) <= HC_CUDA_COMM_ID_BYTES, "id buffer too small");
+  if (id == nullptr || id_bytes < sizeof(ncclUniqueId))
+    return fail(nullptr, HC_CUDA_ERR_INVALID_ARGUMENT, "id must hold at least %zu bytes",
+                sizeof(ncclUniqueId));
+  NcclApi &api = nccl_api();
+  if (!api.ok)
+    return fail(nullptr, HC_CUDA_ERR_COMM, "NCCL (libnccl.so.2) could not be loaded");
+  ncclUniqueId uid;
+  const ncclResult_t res = api.GetUniqueId(&uid);
+  if (res != ncclSuccess)
+    return fail(nullptr, HC_CUDA_ERR_COMM, "ncclGetUniqueId: %s", api.GetErrorString(res));
+  std::memset(id, 0, id_bytes);
+  std::memcpy(id, &uid, sizeof(uid));
+  return HC_CUDA_OK;
+}
+
+int hcCudaCommInitRank(HcCudaContext *ctx, const void *id, size_t id_bytes, int nranks, int rank) {
+  if (ctx == nullptr)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "ctx must not be null");
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  if (id == nullptr || id_bytes < sizeof(ncclUniqueId))
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "id must hold at least %zu bytes", sizeof(ncclUniqueId));
+  if (nranks < 1 || rank < 0 || rank >= nranks)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "rank %d is not in [0, %d)", rank, nranks);
+  if (ctx->comm != nullptr)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "the context already has a communicator");
+  NcclApi &api = nccl_api();
+  if (!api.ok)
+    return fail(ctx, HC_CUDA_ERR_COMM, "NCCL (libnccl.so.2) could not be loaded");
+  HC_TRY_CUDA(ctx, cudaSetDevice(ctx->device));
+  ncclUniqueId uid;
+  std::memcpy(&uid, id, sizeof(uid));
+  const ncclResult_t res = api.CommInitRank(&ctx->comm, nranks, uid, rank);
+  if (res != ncclSuccess) {
+    ctx->comm = nullptr;
+    return fail(ctx, HC_CUDA_ERR_COMM, "ncclCommInitRank: %s", api.GetErrorString(res));
+  }
+  ctx->nranks = nranks;
+  ctx->rank = rank;
+  return HC_CUDA_OK;
+}
+
+int hcCudaCommAllGather(HcCudaContext *ctx, const void *send, void *recv, size_t bytes_per_rank) {
+  if (ctx == nullptr)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "ctx must not be null");
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  if (ctx->comm == nullptr)
+    return fail(ctx, HC_CUDA_ERR_COMM, "no communicator: call hcCudaCommInitRank first");
+  if (bytes_per_rank == 0)
+    return HC_CUDA_OK;
+  if (send == nullptr || recv == nullptr)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "send and recv must not be null");
+  HC_TRY_CUDA(ctx, cudaSetDevice(ctx->device));
+  NcclApi &api = nccl_api();
+  const ncclResult_t res = api.AllGather(send, recv, bytes_per_rank, ncclInt8, ctx->comm, ctx->stream);
+  if (res != ncclSuccess)
+    return fail(ctx, HC_CUDA_ERR_COMM, "ncclAllGather: %s", api.GetErrorString(res));
+  return HC_CUDA_OK;
+}
+
+int hcCudaCommDestroy(HcCudaContext *ctx) {
+  if (ctx == nullptr)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "ctx must not be null");
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  if (ctx->comm == nullptr)
+    return HC_CUDA_OK;
+  HC_TRY_CUDA(ctx, cudaSetDevice(ctx->device));
+  HC_TRY_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  nccl_api().CommDestroy(ctx->comm);
+  ctx->comm = nullptr;
+  ctx->nranks = 0;
+  ctx->rank = -1;
+  return HC_CUDA_OK;
+}
+
+} // extern "C"

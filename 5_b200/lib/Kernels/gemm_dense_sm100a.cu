@@ -1,0 +1,332 @@
+// Dense tiled GEMM for sm_100a:  C[M,N] (fp32) = A[M,K] * B[K,N], A and B fp16 or bf16,
+// all row-major, fp32 accumulation.
+//
+// This is the B200 replacement for the work that the hc example kernel
+// `tiled_gfx11_wmma_matmul` (examples/amdgpu_gfx11_wmma_matmul.py:301-326) describes as a
+// grid of 16x16x16 WMMA tiles: zero-initialised accumulator, k-loop of masked tile loads
+// (out-of-range elements read as 0), one multiply-accumulate per k-step, masked store.
+// Here one CTA owns a 128x256 tile of C:
+//
+//   warp 0   : TMA producer. Per k-block of 64 it loads one 128x64 box of A (K-major) and
+//              four 64x64 boxes of B (N-major) into a 4-deep ring of 128-byte-swizzled
+//              shared-memory stages; out-of-range rows/columns/k are zero-filled by TMA.
+//   warp 1   : allocates TMEM and issues tcgen05.mma (128x256x16, fp32 accumulate in
+//              TMEM); tcgen05.commit hands each ring slot back to the producer.
+//   warps 2-5: epilogue. tcgen05.ld the finished accumulator (two accumulators of 256
+//              columns alternate, so this overlaps the next tile's main loop), transpose
+//              through shared memory and write C with coalesced 128-bit stores,
+//              predicated on the matrix edge.
+//
+// The kernel is persistent: CTA b processes tiles b, b+grid, ... in an order that walks
+// groups of `group_n` tile columns so that concurrently running CTAs share A and B
+// through L2.
+#include "gemm_launch.h"
+#include "sm100_ptx.cuh"
+
+namespace hc {
+namespace sm100 {
+
+namespace dense {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockN = 256;
+constexpr int kBlockK = 64;  // 64 x 2 bytes = one 128-byte swizzle row
+constexpr int kUmmaK = 16;
+constexpr int kStages = 4;
+constexpr int kNumThreads = 192;
+constexpr int kNumEpilogueWarps = 4;
+constexpr int kTmemColumns = 512;  // two fp32 accumulators of kBlockN columns
+
+constexpr uint32_t kATileBytes = kBlockM * kBlockK * 2;            // 16 KiB
+constexpr uint32_t kBChunkBytes = 64 * kBlockK * 2;                // 64 columns x 64 k-rows
+constexpr uint32_t kBTileBytes = kBChunkBytes * (kBlockN / 64);    // 32 KiB
+constexpr uint32_t kStageBytes = kATileBytes + kBTileBytes;        // 48 KiB
+constexpr uint32_t kEpilogueWarpBytes = 32 * 32 * 4;               // one 32x32 fp32 block
+constexpr uint32_t kBarrierBytes = 256;
+constexpr uint32_t kSmemBytes = kStages * kStageBytes + kNumEpilogueWarps * kEpilogueWarpBytes +
+                                kBarrierBytes + 1024 /* alignment slack */;
+
+struct TileCoord {
+  int m_blk;
+  int n_blk;
+};
+
+// Tiles are numbered so that `group_n` neighbouring tile columns are walked row by row
+// before moving on: the CTAs running at any moment then cover a compact rectangle of C.
+__device__ __forceinline__ TileCoord tile_coord(int tile, int tiles_m, int tiles_n, int group_n) {
+  const int tiles_per_group = group_n * tiles_m;
+  const int group = tile / tiles_per_group;
+  const int first_n = group * group_n;
+  const int width = min(group_n, tiles_n - first_n);
+  const int in_group = tile - group * tiles_per_group;
+  TileCoord tc;
+  tc.m_blk = in_group / width;
+  tc.n_blk = first_n + in_group % width;
+  return tc;
+}
+
+__global__ void __launch_bounds__(kNumThreads, 1)
+gemm_dense_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                  const __grid_constant__ CUtensorMap tmap_b, float *__restrict__ c, int m, int n,
+                  int k, long long ldc, uint32_t idesc, int tiles_m, int tiles_n, int group_n,
+                  int *status) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t smem_base = (raw_addr + 1023u) & ~1023u;  // swizzled tiles need 1 KiB alignment
+  uint8_t *smem_gen = smem_raw + (smem_base - raw_addr);
+
+  const uint32_t epi_base = smem_base + kStages * kStageBytes;
+  const uint32_t bar_base = epi_base + kNumEpilogueWarps * kEpilogueWarpBytes;
+  auto full_bar = [&](uint32_t s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](uint32_t s) { return bar_base + 8u * (kStages + s); };
+  auto tmem_full_bar = [&](uint32_t a) { return bar_base + 8u * (2 * kStages + a); };
+  auto tmem_empty_bar = [&](uint32_t a) { return bar_base + 8u * (2 * kStages + 2 + a); };
+  const uint32_t misc_off = (bar_base - smem_base) + 8u * (2 * kStages + 4);
+  volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem_gen + misc_off);
+  volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(smem_gen + misc_off + 4);
+
+  const int warp = static_cast<int>(threadIdx.x >> 5);
+  const int lane = static_cast<int>(threadIdx.x & 31);
+
+  if (threadIdx.x == 0) {
+    for (uint32_t s = 0; s < kStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (uint32_t a = 0; a < 2; ++a) {
+      mbar_init(tmem_full_bar(a), 1);
+      mbar_init(tmem_empty_bar(a), kNumEpilogueWarps);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_descriptor(&tmap_a);
+    tma_prefetch_descriptor(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(const_cast<uint32_t *>(tmem_slot)), kTmemColumns);
+    tmem_relinquish_alloc_permit();
+  }
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  tcgen05_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (k + kBlockK - 1) / kBlockK;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer ------
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+        const TileCoord tc = tile_coord(tile, tiles_m, tiles_n, group_n);
+        const int m0 = tc.m_blk * kBlockM;
+        const int n0 = tc.n_blk * kBlockN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
+            ok = false;
+            break;
+          }
+          const uint32_t a_dst = smem_base + stage * kStageBytes;
+          const uint32_t b_dst = a_dst + kATileBytes;
+          mbar_arrive_expect_tx(full_bar(stage), kStageBytes);
+          tma_load_2d(a_dst, &tmap_a, full_bar(stage), kb * kBlockK, m0);
+#pragma unroll
+          for (int j = 0; j < kBlockN / 64; ++j)
+            tma_load_2d(b_dst + j * kBChunkBytes, &tmap_b, full_bar(stage), n0 + j * 64,
+                        kb * kBlockK);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer --------
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      uint32_t iter = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++iter) {
+        const uint32_t acc = iter & 1u;
+        const uint32_t acc_phase = (iter >> 1) & 1u;
+        if (!mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, abort_flag))
+          break;
+        tcgen05_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * kBlockN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
+            ok = false;
+            break;
+          }
+          tcgen05_fence_after_sync();
+          const uint32_t a_addr = smem_base + stage * kStageBytes;
+          const uint32_t b_addr = a_addr + kATileBytes;
+          // A: K-major, groups of 8 rows are 1024 bytes apart.
+          const uint64_t a_desc = make_smem_desc_sw128(a_addr, 16, 1024);
+          // B: N-major, 64-column chunks are kBChunkBytes apart, groups of 8 k-rows 1024.
+          const uint64_t b_desc = make_smem_desc_sw128(b_addr, kBChunkBytes, 1024);
+#pragma unroll
+          for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
+            // Per 16-wide k-step: A advances 32 bytes inside the swizzle row, B advances
+            // two groups of 8 k-rows (2048 bytes); both in 16-byte descriptor units.
+            umma_f16_ss(d_tmem, a_desc + static_cast<uint64_t>(kk * 2),
+                        b_desc + static_cast<uint64_t>(kk * 128), idesc,
+                        (kb | kk) != 0 ? 1u : 0u);
+          }
+          umma_commit(empty_bar(stage));
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok)
+          umma_commit(tmem_full_bar(acc));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue ----------
+    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
+    const uint32_t stage_smem = epi_base + (warp - 2) * kEpilogueWarpBytes;
+    float *stage_gen = reinterpret_cast<float *>(smem_gen + (stage_smem - smem_base));
+    const bool vec_ok = ((ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(c) & 15) == 0);
+    uint32_t iter = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++iter) {
+      const TileCoord tc = tile_coord(tile, tiles_m, tiles_n, group_n);
+      const uint32_t acc = iter & 1u;
+      const uint32_t acc_phase = (iter >> 1) & 1u;
+      const bool ready = mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag);
+      if (!__all_sync(0xffffffffu, ready))
+        break;
+      tcgen05_fence_after_sync();
+      const int row_base = tc.m_blk * kBlockM + quarter * 32;
+      const int col_base = tc.n_blk * kBlockN;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kBlockN;
+#pragma unroll 1
+      for (int chunk = 0; chunk < kBlockN / 32; ++chunk) {
+        uint32_t r[32];
+        tmem_load_32x32b_x32(taddr + chunk * 32, r);
+        tmem_load_wait();
+        if (chunk == kBlockN / 32 - 1) {
+          // Accumulator fully read: hand it back to the MMA warp.
+          tcgen05_fence_before_sync();
+          __syncwarp();
+          if (lane == 0)
+            mbar_arrive(tmem_empty_bar(acc));
+        }
+        const int col0 = col_base + chunk * 32;
+        if (col0 >= n)
+          continue;  // warp-uniform
+        // Lane `lane` holds row (row_base+lane), columns col0..col0+31. Write it to the
+        // staging block with the 16-byte pieces XOR-swizzled by the row so that both this
+        // write and the row-wise read below are bank-conflict free.
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          float4 v = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                                 __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+          *reinterpret_cast<float4 *>(stage_gen + lane * 32 + ((q ^ (lane & 7)) << 2)) = v;
+        }
+        __syncwarp();
+        if (vec_ok) {
+          // 8 lanes cover one 128-byte row segment; a warp store covers 4 rows.
+          const int piece = lane & 7;
+          const int col = col0 + piece * 4;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int rr = i * 4 + (lane >> 3);
+            const int row = row_base + rr;
+            const float4 v =
+                *reinterpret_cast<const float4 *>(stage_gen + rr * 32 + ((piece ^ (rr & 7)) << 2));
+            if (row < m) {
+              float *dst = c + static_cast<long long>(row) * ldc + col;
+              if (col + 3 < n) {
+                __stcs(reinterpret_cast<float4 *>(dst), v);
+              } else {
+                if (col < n) __stcs(dst, v.x);
+                if (col + 1 < n) __stcs(dst + 1, v.y);
+                if (col + 2 < n) __stcs(dst + 2, v.z);
+              }
+            }
+          }
+        } else {
+          // Row pitch or base not 16-byte aligned: one 128-byte row segment per store,
+          // 32-bit per lane.
+          const int col = col0 + lane;
+#pragma unroll 4
+          for (int rr = 0; rr < 32; ++rr) {
+            const int row = row_base + rr;
+            const float v = stage_gen[rr * 32 + ((((lane >> 2) ^ (rr & 7)) << 2) | (lane & 3))];
+            if (row < m && col < n)
+              __stcs(c + static_cast<long long>(row) * ldc + col, v);
+          }
+        }
+        __syncwarp();
+      }
+    }
+  }
+
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  tcgen05_fence_after_sync();
+  if (*abort_flag != 0) {
+    // A wait ran out. Record it, then give copies that may still be in flight time to
+    // land before the shared memory and TMEM of this CTA are released.
+    if (threadIdx.x == 0)
+      atomicExch(status, kStatusDeviceWaitTimeout);
+    const long long start = clock64();
+    while (clock64() - start < 2000000LL) {
+    }
+    __syncthreads();
+  }
+  if (warp == 1)
+    tmem_dealloc(tmem_base, kTmemColumns);
+}
+
+} // namespace dense
+
+cudaError_t launch_gemm_dense(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, float *c,
+                              int m, int n, int k, long long ldc, int dtype, int group_n,
+                              int max_ctas, int *status, cudaStream_t stream) {
+  using namespace dense;
+  static thread_local int configured_device = -1;
+  int device = 0;
+  cudaError_t err = cudaGetDevice(&device);
+  if (err != cudaSuccess)
+    return err;
+  if (configured_device != device) {
+    err = cudaFuncSetAttribute(gemm_dense_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(kSmemBytes));
+    if (err != cudaSuccess)
+      return err;
+    configured_device = device;
+  }
+  const int tiles_m = (m + kBlockM - 1) / kBlockM;
+  const int tiles_n = (n + kBlockN - 1) / kBlockN;
+  const long long num_tiles = static_cast<long long>(tiles_m) * tiles_n;
+  if (num_tiles <= 0 || num_tiles > 0x7fffffffLL)
+    return cudaErrorInvalidValue;
+  const int grid = static_cast<int>(num_tiles < max_ctas ? num_tiles : max_ctas);
+  const uint32_t idesc = make_idesc_f16(dtype == kDTypeBF16 ? 1u : 0u, /*a_mn_major=*/false,
+                                        /*b_mn_major=*/true, kBlockM, kBlockN);
+  if (group_n < 1)
+    group_n = 1;
+  gemm_dense_kernel<<<grid, kNumThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, c, m, n, k, ldc,
+                                                               idesc, tiles_m, tiles_n, group_n,
+                                                               status);
+  return cudaGetLastError();
+}
+
+DenseTileShape dense_tile_shape() {
+  DenseTileShape s;
+  s.block_m = dense::kBlockM;
+  s.block_n = dense::kBlockN;
+  s.block_k = dense::kBlockK;
+  s.stages = dense::kStages;
+  s.smem_bytes = dense::kSmemBytes;
+  return s;
+}
+
+} // namespace sm100
+} // namespace hc

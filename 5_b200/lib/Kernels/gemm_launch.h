@@ -1,0 +1,65 @@
+// Host-side launch interface of the sm_100a kernels. The C-ABI layer (lib/CAPI/Cuda.cpp)
+// is the only caller; it owns argument validation, tensor-map encoding and scratch memory.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cstddef>
+#include <cstdint>
+
+namespace hc {
+namespace sm100 {
+
+constexpr int kDTypeF16 = 0;
+constexpr int kDTypeBF16 = 1;
+
+// Value a kernel writes to the status word when one of its bounded waits ran out.
+constexpr int kStatusDeviceWaitTimeout = 5;
+
+struct DenseTileShape {
+  int block_m, block_n, block_k, stages;
+  unsigned smem_bytes;
+};
+DenseTileShape dense_tile_shape();
+
+// C[m,n] = A * B through the TMA + tcgen05 persistent kernel.
+//   tmap_a: A as a 2-D tensor {k (inner), m}, box {64, 128}, 128-byte swizzle.
+//   tmap_b: B as a 2-D tensor {n (inner), k}, box {64, 64},  128-byte swizzle.
+cudaError_t launch_gemm_dense(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, float *c,
+                              int m, int n, int k, long long ldc, int dtype, int group_n,
+                              int max_ctas, int *status, cudaStream_t stream);
+
+struct SkinnyShape {
+  int block_n;     // columns of C per work unit
+  int block_k;
+  int max_m;       // largest M the skinny kernel accepts
+  int stages;
+  unsigned smem_bytes;
+};
+SkinnyShape skinny_shape(int m);
+
+// Number of k-splits the skinny kernel would use for this problem on `sm_count` SMs.
+int skinny_choose_splits(int n, int k, int sm_count);
+
+// Scratch the skinny kernel needs for `splits` > 1: partial sums then arrival counters.
+size_t skinny_partials_bytes(int m, int n, int splits);
+size_t skinny_counters_bytes(int n);
+
+// C[m,n] = A * B for m <= 64: streams B once, split over k, partial sums reduced in a
+// fixed order by the last work unit to finish each block of columns.
+//   tmap_a: A as {k (inner), m}, box {64, padded m}; tmap_b as for the dense kernel.
+//   partials / counters: scratch (ignored when splits == 1); counters must be zero on
+//   entry and are zero again on exit.
+cudaError_t launch_gemm_skinny(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, float *c,
+                               int m, int n, int k, long long ldc, int dtype, int splits,
+                               float *partials, unsigned *counters, int max_ctas, int *status,
+                               cudaStream_t stream);
+
+// Copies a rows x cols matrix of 16-bit elements into a buffer whose row pitch is a
+// multiple of 8 elements (16 bytes), as TMA requires. Columns [cols, round_up(cols, 8))
+// of the destination are zeroed.
+cudaError_t launch_repack_pitch(const void *src, long long src_ld, void *dst, long long dst_ld,
+                                int rows, int cols, cudaStream_t stream);
+
+} // namespace sm100
+} // namespace hc

@@ -1,0 +1,366 @@
+// Skinny GEMM for sm_100a:  C[M,N] (fp32) = A[M,K] * B[K,N] with M <= 64, where the time
+// is the time to stream B from HBM once. Same contract as the dense kernel (the hc example
+// kernel examples/amdgpu_gfx11_wmma_matmul.py:301-326: fp32 accumulate, out-of-range
+// elements count as 0, only in-range C is written), different mapping:
+//
+//   * The product is computed transposed, C^T = B^T * A^T, so that the long N axis sits on
+//     the 128 TMEM lanes and the short M axis (padded to 16/32/64) on the UMMA N side.
+//     B is N-major in memory, which tcgen05.mma accepts directly as an MN-major operand:
+//     no register staging and no transposing loads, TMA -> shared memory -> tensor core.
+//   * Work unit = (block of 128 columns of C, one of `splits` ranges of k). Units are
+//     spread over persistent CTAs, two per SM, each with its own multi-stage TMA ring so
+//     that enough bytes are in flight to cover HBM latency.
+//   * Split-k partial sums go to scratch memory; a per-32-column arrival counter tells the
+//     last warp to finish a column block to add the partials in split order 0..S-1 (so the
+//     result does not depend on which unit finished last) and to write C with coalesced
+//     128-byte row segments. The counters are reset to zero by that warp.
+//
+// Warp roles: warp 0 TMA producer, warp 1 TMEM owner + tcgen05.mma issuer, warps 2-5
+// epilogue (TMEM -> registers -> partials / C).
+#include "gemm_launch.h"
+#include "sm100_ptx.cuh"
+
+namespace hc {
+namespace sm100 {
+
+namespace skinny {
+
+constexpr int kBlockN = 128;  // TMEM lanes
+constexpr int kBlockK = 64;
+constexpr int kUmmaK = 16;
+constexpr int kNumThreads = 192;
+constexpr int kCtasPerSm = 2;
+constexpr uint32_t kBChunkBytes = 64 * kBlockK * 2;                   // 64 columns x 64 k-rows
+constexpr uint32_t kBTileBytes = kBChunkBytes * (kBlockN / 64);       // 16 KiB
+constexpr uint32_t kBarrierBytes = 256;
+
+template <int kMp>
+struct Config {
+  static constexpr uint32_t kATileBytes = kMp * kBlockK * 2;
+  static constexpr uint32_t kStageBytes = kBTileBytes + kATileBytes;
+  static constexpr int kStages = kMp == 16 ? 6 : (kMp == 32 ? 5 : 4);
+  static constexpr uint32_t kTmemColumns = 2 * kMp < 32 ? 32 : 2 * kMp;
+  static constexpr uint32_t kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;
+};
+
+template <int kMp>
+__global__ void __launch_bounds__(kNumThreads, kCtasPerSm)
+gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                   const __grid_constant__ CUtensorMap tmap_b, float *__restrict__ c, int m, int n,
+                   int k, long long ldc, uint32_t idesc, int n_tiles, int splits,
+                   float *__restrict__ partials, unsigned *__restrict__ counters, int *status) {
+  using Cfg = Config<kMp>;
+  constexpr int kStages = Cfg::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t smem_base = (raw_addr + 1023u) & ~1023u;
+  uint8_t *smem_gen = smem_raw + (smem_base - raw_addr);
+
+  const uint32_t bar_base = smem_base + kStages * Cfg::kStageBytes;
+  auto full_bar = [&](uint32_t s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](uint32_t s) { return bar_base + 8u * (kStages + s); };
+  auto tmem_full_bar = [&](uint32_t a) { return bar_base + 8u * (2 * kStages + a); };
+  auto tmem_empty_bar = [&](uint32_t a) { return bar_base + 8u * (2 * kStages + 2 + a); };
+  const uint32_t misc_off = (bar_base - smem_base) + 8u * (2 * kStages + 4);
+  volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem_gen + misc_off);
+  volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(smem_gen + misc_off + 4);
+
+  const int warp = static_cast<int>(threadIdx.x >> 5);
+  const int lane = static_cast<int>(threadIdx.x & 31);
+
+  if (threadIdx.x == 0) {
+    for (uint32_t s = 0; s < kStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (uint32_t a = 0; a < 2; ++a) {
+      mbar_init(tmem_full_bar(a), 1);
+      mbar_init(tmem_empty_bar(a), 4);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_descriptor(&tmap_a);
+    tma_prefetch_descriptor(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(const_cast<uint32_t *>(tmem_slot)), Cfg::kTmemColumns);
+    tmem_relinquish_alloc_permit();
+  }
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  tcgen05_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int kb_total = (k + kBlockK - 1) / kBlockK;
+  const int num_units = n_tiles * splits;
+  const int n_pad = n_tiles * kBlockN;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer ------
+    if (lane == 0) {
+      const uint64_t stream_policy = l2_policy_evict_first();  // B is read exactly once
+      const uint64_t keep_policy = l2_policy_evict_last();     // A is re-read by every unit
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int unit = blockIdx.x; ok && unit < num_units; unit += gridDim.x) {
+        const int n_tile = unit % n_tiles;
+        const int split = unit / n_tiles;
+        const int kb_begin = static_cast<int>(static_cast<long long>(split) * kb_total / splits);
+        const int kb_end = static_cast<int>(static_cast<long long>(split + 1) * kb_total / splits);
+        const int n0 = n_tile * kBlockN;
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
+            ok = false;
+            break;
+          }
+          const uint32_t b_dst = smem_base + stage * Cfg::kStageBytes;
+          const uint32_t a_dst = b_dst + kBTileBytes;
+          mbar_arrive_expect_tx(full_bar(stage), Cfg::kStageBytes);
+#pragma unroll
+          for (int j = 0; j < kBlockN / 64; ++j)
+            tma_load_2d_hint(b_dst + j * kBChunkBytes, &tmap_b, full_bar(stage), n0 + j * 64,
+                             kb * kBlockK, stream_policy);
+          tma_load_2d_hint(a_dst, &tmap_a, full_bar(stage), kb * kBlockK, 0, keep_policy);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer --------
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      uint32_t iter = 0;
+      bool ok = true;
+      for (int unit = blockIdx.x; ok && unit < num_units; unit += gridDim.x, ++iter) {
+        const int split = unit / n_tiles;
+        const int kb_begin = static_cast<int>(static_cast<long long>(split) * kb_total / splits);
+        const int kb_end = static_cast<int>(static_cast<long long>(split + 1) * kb_total / splits);
+        const uint32_t acc = iter & 1u;
+        const uint32_t acc_phase = (iter >> 1) & 1u;
+        if (!mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, abort_flag))
+          break;
+        tcgen05_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * kMp;
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
+            ok = false;
+            break;
+          }
+          tcgen05_fence_after_sync();
+          const uint32_t bt_addr = smem_base + stage * Cfg::kStageBytes;
+          const uint32_t a_addr = bt_addr + kBTileBytes;
+          // UMMA "A" operand = B^T tile (128 n x 64 k), n contiguous: MN-major.
+          const uint64_t bt_desc = make_smem_desc_sw128(bt_addr, kBChunkBytes, 1024);
+          // UMMA "B" operand = A tile (kMp rows x 64 k), k contiguous: K-major.
+          const uint64_t a_desc = make_smem_desc_sw128(a_addr, 16, 1024);
+#pragma unroll
+          for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
+            umma_f16_ss(d_tmem, bt_desc + static_cast<uint64_t>(kk * 128),
+                        a_desc + static_cast<uint64_t>(kk * 2), idesc,
+                        (kb != kb_begin || kk != 0) ? 1u : 0u);
+          }
+          umma_commit(empty_bar(stage));
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok)
+          umma_commit(tmem_full_bar(acc));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue ----------
+    const int quarter = warp & 3;
+    uint32_t iter = 0;
+    for (int unit = blockIdx.x; unit < num_units; unit += gridDim.x, ++iter) {
+      const int n_tile = unit % n_tiles;
+      const int split = unit / n_tiles;
+      const uint32_t acc = iter & 1u;
+      const uint32_t acc_phase = (iter >> 1) & 1u;
+      const bool ready = mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag);
+      if (!__all_sync(0xffffffffu, ready))
+        break;
+      tcgen05_fence_after_sync();
+      // Lane `lane` of this warp holds column (n_tile*128 + quarter*32 + lane) of C; its
+      // TMEM columns are the rows of C.
+      uint32_t r[kMp];
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kMp;
+#pragma unroll
+      for (int g = 0; g < kMp / 16; ++g) {
+        uint32_t part[16];
+        tmem_load_32x32b_x16(taddr + g * 16, part);
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          r[g * 16 + i] = part[i];
+      }
+      tmem_load_wait();
+      tcgen05_fence_before_sync();
+      __syncwarp();
+      if (lane == 0)
+        mbar_arrive(tmem_empty_bar(acc));
+
+      const int col = n_tile * kBlockN + quarter * 32 + lane;
+      if (splits == 1) {
+#pragma unroll
+        for (int mm = 0; mm < kMp; ++mm)
+          if (mm < m && col < n)
+            __stcs(c + static_cast<long long>(mm) * ldc + col, __uint_as_float(r[mm]));
+        continue;
+      }
+      float *my_partial = partials + static_cast<size_t>(split) * m * n_pad + col;
+#pragma unroll
+      for (int mm = 0; mm < kMp; ++mm)
+        if (mm < m)
+          __stcg(my_partial + static_cast<size_t>(mm) * n_pad, __uint_as_float(r[mm]));
+      __threadfence();
+      __syncwarp();
+      unsigned arrived = 0;
+      unsigned *counter = counters + n_tile * 4 + quarter;
+      if (lane == 0)
+        arrived = atomicAdd(counter, 1u);
+      arrived = __shfl_sync(0xffffffffu, arrived, 0);
+      if (arrived == static_cast<unsigned>(splits - 1)) {
+        // Every split of this 32-column block has published its partial sums.
+        __threadfence();
+        const float *col_partials = partials + col;
+        for (int mm = 0; mm < m; ++mm) {
+          float sum = 0.0f;
+          for (int s = 0; s < splits; ++s)
+            sum += __ldcg(col_partials + (static_cast<size_t>(s) * m + mm) * n_pad);
+          if (col < n)
+            __stcs(c + static_cast<long long>(mm) * ldc + col, sum);
+        }
+        if (lane == 0)
+          *counter = 0u;
+      }
+    }
+  }
+
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  tcgen05_fence_after_sync();
+  if (*abort_flag != 0) {
+    if (threadIdx.x == 0)
+      atomicExch(status, kStatusDeviceWaitTimeout);
+    const long long start = clock64();
+    while (clock64() - start < 2000000LL) {
+    }
+    __syncthreads();
+  }
+  if (warp == 1)
+    tmem_dealloc(tmem_base, Cfg::kTmemColumns);
+}
+
+template <int kMp>
+cudaError_t launch(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, float *c, int m, int n,
+                   int k, long long ldc, int dtype, int splits, float *partials,
+                   unsigned *counters, int max_ctas, int *status, cudaStream_t stream) {
+  using Cfg = Config<kMp>;
+  static thread_local int configured_device = -1;
+  int device = 0;
+  cudaError_t err = cudaGetDevice(&device);
+  if (err != cudaSuccess)
+    return err;
+  if (configured_device != device) {
+    err = cudaFuncSetAttribute(gemm_skinny_kernel<kMp>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(Cfg::kSmemBytes));
+    if (err != cudaSuccess)
+      return err;
+    configured_device = device;
+  }
+  const int n_tiles = (n + kBlockN - 1) / kBlockN;
+  const long long units = static_cast<long long>(n_tiles) * splits;
+  const int grid = static_cast<int>(units < max_ctas ? units : max_ctas);
+  const uint32_t idesc = make_idesc_f16(dtype == kDTypeBF16 ? 1u : 0u, /*a_mn_major=*/true,
+                                        /*b_mn_major=*/false, kBlockN, kMp);
+  gemm_skinny_kernel<kMp><<<grid, kNumThreads, Cfg::kSmemBytes, stream>>>(
+      tmap_a, tmap_b, c, m, n, k, ldc, idesc, n_tiles, splits, partials, counters, status);
+  return cudaGetLastError();
+}
+
+inline int padded_m(int m) { return m <= 16 ? 16 : (m <= 32 ? 32 : 64); }
+
+} // namespace skinny
+
+SkinnyShape skinny_shape(int m) {
+  SkinnyShape s;
+  s.block_n = skinny::kBlockN;
+  s.block_k = skinny::kBlockK;
+  s.max_m = 64;
+  const int mp = skinny::padded_m(m);
+  if (mp == 16) {
+    s.stages = skinny::Config<16>::kStages;
+    s.smem_bytes = skinny::Config<16>::kSmemBytes;
+  } else if (mp == 32) {
+    s.stages = skinny::Config<32>::kStages;
+    s.smem_bytes = skinny::Config<32>::kSmemBytes;
+  } else {
+    s.stages = skinny::Config<64>::kStages;
+    s.smem_bytes = skinny::Config<64>::kSmemBytes;
+  }
+  return s;
+}
+
+int skinny_choose_splits(int n, int k, int sm_count) {
+  // Pick the split count whose units fill the resident CTAs most evenly; every split
+  // keeps at least 4 k-blocks so that its ring fills, and ties go to fewer splits
+  // (less partial-sum traffic).
+  const int n_tiles = (n + skinny::kBlockN - 1) / skinny::kBlockN;
+  const int kb_total = (k + skinny::kBlockK - 1) / skinny::kBlockK;
+  const long long slots = static_cast<long long>(sm_count) * skinny::kCtasPerSm;
+  int best = 1;
+  double best_eff = 0.0;
+  for (int s = 1; s <= 32; ++s) {
+    if (s > 1 && kb_total / s < 4)
+      break;
+    const long long units = static_cast<long long>(n_tiles) * s;
+    const long long waves = (units + slots - 1) / slots;
+    // Longest CTA does `waves` units of ceil(kb_total/s) k-blocks.
+    const double longest = static_cast<double>(waves) * ((kb_total + s - 1) / s);
+    const double ideal = static_cast<double>(n_tiles) * kb_total / static_cast<double>(slots);
+    const double eff = ideal / longest;
+    if (eff > best_eff + 0.02) {
+      best_eff = eff;
+      best = s;
+    }
+  }
+  return best;
+}
+
+size_t skinny_partials_bytes(int m, int n, int splits) {
+  if (splits <= 1)
+    return 0;
+  const size_t n_tiles = (static_cast<size_t>(n) + skinny::kBlockN - 1) / skinny::kBlockN;
+  return static_cast<size_t>(splits) * static_cast<size_t>(m) * n_tiles * skinny::kBlockN *
+         sizeof(float);
+}
+
+size_t skinny_counters_bytes(int n) {
+  const size_t n_tiles = (static_cast<size_t>(n) + skinny::kBlockN - 1) / skinny::kBlockN;
+  return n_tiles * 4 * sizeof(unsigned);
+}
+
+cudaError_t launch_gemm_skinny(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, float *c,
+                               int m, int n, int k, long long ldc, int dtype, int splits,
+                               float *partials, unsigned *counters, int max_ctas, int *status,
+                               cudaStream_t stream) {
+  if (m < 1 || m > 64 || splits < 1)
+    return cudaErrorInvalidValue;
+  const int mp = skinny::padded_m(m);
+  if (mp == 16)
+    return skinny::launch<16>(tmap_a, tmap_b, c, m, n, k, ldc, dtype, splits, partials, counters,
+                              max_ctas, status, stream);
+  if (mp == 32)
+    return skinny::launch<32>(tmap_a, tmap_b, c, m, n, k, ldc, dtype, splits, partials, counters,
+                              max_ctas, status, stream);
+  return skinny::launch<64>(tmap_a, tmap_b, c, m, n, k, ldc, dtype, splits, partials, counters,
+                            max_ctas, status, stream);
+}
+
+} // namespace sm100
+} // namespace hc

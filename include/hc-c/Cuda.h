@@ -1,0 +1,219 @@
+/* hc-c/Cuda.h -- C ABI of the NVIDIA sm_100a (B200) launch backend for hc's tiled matmul.
+ *
+ * The reference project can execute its matmul kernel
+ * (examples/amdgpu_gfx11_wmma_matmul.py:301-326, `tiled_gfx11_wmma_matmul`) only through
+ * the host simulator (`hc.simulator.launch`, hc/simulator.py:165-186); the compiled handle
+ * refuses to run (`CompiledKernel.__call__`, hc/_compile.py:57-62). This header is the
+ * launch half that is missing there: a plain-C interface (pointers and sizes, no MLIR, no
+ * C++ types) that `hc.compile(..., target="nvidia-sm100a")` binds through ctypes, placed
+ * beside the reference's own C API (include/hc-c/HC.h:18-30, include/hc-c/Front.h:14-22)
+ * and written in the same style (extern "C", an export macro, one prefix).
+ *
+ * Conventions
+ *   - Every function returns an `HcCudaStatus` (0 = success). No C++ exception crosses the
+ *     boundary. `hcCudaContextLastError` gives the text of the last failure on a context.
+ *   - Buffers are caller-owned. The library never frees or reallocates caller memory; what
+ *     it allocates itself (stream, scratch, status word) belongs to the context and is
+ *     released by `hcCudaContextDestroy`.
+ *   - One context per device. Calls on one context are serialised by an internal mutex;
+ *     different contexts may be used from different threads concurrently.
+ *   - Work is ordered on the context's own stream. Functions documented as asynchronous
+ *     return once the work is enqueued; `hcCudaContextSynchronize` waits for it and reports
+ *     device-side failures (a bounded wait inside a kernel that ran out).
+ *   - There is no CPU fallback: without a usable sm_100 device every compute entry point
+ *     fails with HC_CUDA_ERR_NO_DEVICE or HC_CUDA_ERR_UNSUPPORTED.
+ */
+#ifndef HC_C_CUDA_H
+#define HC_C_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(_WIN32)
+#define HC_CUDA_CAPI_EXPORTED __declspec(dllexport)
+#else
+#define HC_CUDA_CAPI_EXPORTED __attribute__((visibility("default")))
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define HC_CUDA_API_VERSION 1
+
+typedef enum HcCudaStatus {
+  HC_CUDA_OK = 0,
+  HC_CUDA_ERR_INVALID_ARGUMENT = 1, /* null/misaligned/overlapping pointer, bad size or enum */
+  HC_CUDA_ERR_UNSUPPORTED = 2,      /* valid request this backend cannot serve */
+  HC_CUDA_ERR_CUDA = 3,             /* a CUDA runtime/driver call failed */
+  HC_CUDA_ERR_NO_DEVICE = 4,        /* no such device, or not an sm_100 device */
+  HC_CUDA_ERR_DEVICE_TIMEOUT = 5,   /* a bounded wait inside a kernel ran out */
+  HC_CUDA_ERR_COMM = 6,             /* NCCL missing, not initialised, or a collective failed */
+  HC_CUDA_ERR_OUT_OF_MEMORY = 7
+} HcCudaStatus;
+
+/* Element type of A and B. C is always float32 (fp32 accumulate and output), as in the
+ * reference kernel's `Buffer[M, N, np.float32]` (examples/amdgpu_gfx11_wmma_matmul.py:310). */
+typedef enum HcCudaDType { HC_CUDA_F16 = 0, HC_CUDA_BF16 = 1 } HcCudaDType;
+
+typedef enum HcCudaGemmVariant {
+  HC_CUDA_GEMM_AUTO = 0,   /* skinny when m <= 64, dense otherwise */
+  HC_CUDA_GEMM_DENSE = 1,  /* 128x256x64 tiles, TMA ring, tcgen05.mma, persistent CTAs */
+  HC_CUDA_GEMM_SKINNY = 2, /* m <= 64: B streamed once, split over k, ordered reduction */
+  /* Reported by hcCudaGemmPlan only: */
+  HC_CUDA_GEMM_NOOP = 3,     /* m == 0 or n == 0: nothing to write */
+  HC_CUDA_GEMM_ZERO_FILL = 4 /* k == 0: C is set to zero, no kernel */
+} HcCudaGemmVariant;
+
+/* C[m,n] = A[m,k] * B[k,n]; all three row-major with element pitches lda/ldb/ldc.
+ * Mirrors the launch arguments of the reference kernel, `(a, b, c)` with
+ * a: Buffer[M, K], b: Buffer[K, N], c: Buffer[M, N] (examples/...:306-311), the symbols
+ * M, N, K being what `_bind_buffer` derives from the array shapes (hc/simulator.py:752-768).
+ * Every in-range element of C is overwritten; nothing outside C is written; A and B are
+ * read only. A, B 2-byte aligned, C 4-byte aligned; other alignments and pitches are
+ * accepted (unaligned ones cost a repack pass through context scratch memory). */
+typedef struct HcCudaGemmArgs {
+  int64_t m, n, k;
+  int32_t dtype;   /* HcCudaDType */
+  int32_t variant; /* HcCudaGemmVariant: AUTO, DENSE or SKINNY */
+  const void *a;
+  int64_t lda;
+  const void *b;
+  int64_t ldb;
+  float *c;
+  int64_t ldc;
+} HcCudaGemmArgs;
+
+/* What a GEMM call will do; computed on the host without touching a device. */
+typedef struct HcCudaGemmPlanInfo {
+  int32_t variant;         /* DENSE, SKINNY, NOOP or ZERO_FILL */
+  int32_t tiles_m;         /* C tiles along m (dense) or 1 (skinny) */
+  int32_t tiles_n;         /* C tiles along n */
+  int32_t splits;          /* k-splits (skinny), 1 otherwise */
+  int32_t grid;            /* CTAs of the GEMM kernel */
+  int32_t repack_a;        /* 1: A is first copied to a 16-byte-aligned pitch */
+  int32_t repack_b;        /* 1: B likewise */
+  int32_t kernel_launches; /* kernels this call enqueues */
+  int64_t scratch_bytes;   /* context scratch the call needs */
+} HcCudaGemmPlanInfo;
+
+typedef struct HcCudaDeviceInfo {
+  char name[128];
+  int32_t device;
+  int32_t cc_major, cc_minor;
+  int32_t sm_count;
+  int64_t total_memory_bytes;
+  int32_t l2_bytes;
+  int32_t sm_clock_khz; /* nominal max SM clock */
+} HcCudaDeviceInfo;
+
+typedef struct HcCudaContext HcCudaContext;
+typedef struct HcCudaEvent HcCudaEvent;
+
+/* ---- library ------------------------------------------------------------------------ */
+
+/* Returns HC_CUDA_API_VERSION of the built library. */
+HC_CUDA_CAPI_EXPORTED int hcCudaApiVersion(void);
+
+/* Static, never-null name of a status code. */
+HC_CUDA_CAPI_EXPORTED const char *hcCudaStatusString(int status);
+
+/* Number of CUDA devices visible; 0 with HC_CUDA_OK when there is no driver or device. */
+HC_CUDA_CAPI_EXPORTED int hcCudaGetDeviceCount(int *count);
+
+/* ---- context ------------------------------------------------------------------------ */
+
+/* Creates the context of `device` (stream, status word, scratch bookkeeping). Fails with
+ * HC_CUDA_ERR_NO_DEVICE when the device does not exist or is not compute capability 10.x.
+ * Replaces the process-wide, idempotent registration entry point of the reference C API
+ * (`mlirRegisterHCAllPasses`, lib/CAPI/HC.cpp:22-29) as the library's set-up call. */
+HC_CUDA_CAPI_EXPORTED int hcCudaContextCreate(int device, HcCudaContext **out);
+HC_CUDA_CAPI_EXPORTED int hcCudaContextDestroy(HcCudaContext *ctx);
+
+/* Text of the most recent failure on `ctx` ("" if none). Owned by the context; valid until
+ * the next failing call on it. `ctx == NULL` reports failures of calls that take no context
+ * (or a null one), per thread. */
+HC_CUDA_CAPI_EXPORTED const char *hcCudaContextLastError(const HcCudaContext *ctx);
+
+HC_CUDA_CAPI_EXPORTED int hcCudaContextGetDeviceInfo(HcCudaContext *ctx, HcCudaDeviceInfo *out);
+
+/* Waits for all work enqueued on the context. Returns HC_CUDA_ERR_DEVICE_TIMEOUT if a
+ * kernel reported that one of its waits ran out (the results of that launch are invalid;
+ * the context stays usable). The reference launch is synchronous
+ * (hc/simulator.py:165-186); `handle(a, b, c)` gets that behaviour by calling this. */
+HC_CUDA_CAPI_EXPORTED int hcCudaContextSynchronize(HcCudaContext *ctx);
+
+/* ---- memory ------------------------------------------------------------------------- */
+
+HC_CUDA_CAPI_EXPORTED int hcCudaMalloc(HcCudaContext *ctx, size_t bytes, void **device_ptr);
+HC_CUDA_CAPI_EXPORTED int hcCudaFree(HcCudaContext *ctx, void *device_ptr);
+
+/* Page-locked host memory (full-speed, truly asynchronous copies). */
+HC_CUDA_CAPI_EXPORTED int hcCudaHostAlloc(size_t bytes, void **host_ptr);
+HC_CUDA_CAPI_EXPORTED int hcCudaHostFree(void *host_ptr);
+
+/* Copies, ordered on the context stream; they return after the copy has completed. */
+HC_CUDA_CAPI_EXPORTED int hcCudaMemcpyHtoD(HcCudaContext *ctx, void *device_dst,
+                                           const void *host_src, size_t bytes);
+HC_CUDA_CAPI_EXPORTED int hcCudaMemcpyDtoH(HcCudaContext *ctx, void *host_dst,
+                                           const void *device_src, size_t bytes);
+/* Strided forms: `rows` rows of `width_bytes`, pitches in bytes (column slabs of a
+ * row-major host matrix to/from a compact device buffer). */
+HC_CUDA_CAPI_EXPORTED int hcCudaMemcpy2DHtoD(HcCudaContext *ctx, void *device_dst,
+                                             size_t dst_pitch, const void *host_src,
+                                             size_t src_pitch, size_t width_bytes, size_t rows);
+HC_CUDA_CAPI_EXPORTED int hcCudaMemcpy2DDtoH(HcCudaContext *ctx, void *host_dst, size_t dst_pitch,
+                                             const void *device_src, size_t src_pitch,
+                                             size_t width_bytes, size_t rows);
+/* Asynchronous fill with a byte value. */
+HC_CUDA_CAPI_EXPORTED int hcCudaMemset(HcCudaContext *ctx, void *device_ptr, int byte_value,
+                                       size_t bytes);
+
+/* ---- the hot path ------------------------------------------------------------------- */
+
+/* Validates `args` exactly as hcCudaGemm does (pointers are checked for null, alignment
+ * and overlap but never dereferenced) and reports what would be launched on a device with
+ * `sm_count` SMs. Needs no device. */
+HC_CUDA_CAPI_EXPORTED int hcCudaGemmPlan(const HcCudaGemmArgs *args, int sm_count,
+                                         HcCudaGemmPlanInfo *out);
+
+/* Asynchronous. a, b, c are device pointers on the context's device. This is what
+ * `CompiledKernel.__call__` (hc/_compile.py:57-62) resolves to for device buffers. */
+HC_CUDA_CAPI_EXPORTED int hcCudaGemm(HcCudaContext *ctx, const HcCudaGemmArgs *args);
+
+/* Synchronous. a, b, c are host pointers (NumPy buffers): copies A and B to the device,
+ * runs the GEMM, copies C back into the caller's array, returns when C is complete --
+ * the in-place, synchronous behaviour of `hc.simulator.launch` (hc/simulator.py:165-186,
+ * doc/simulator.md:201-207). Device staging memory is kept by the context between calls. */
+HC_CUDA_CAPI_EXPORTED int hcCudaGemmHost(HcCudaContext *ctx, const HcCudaGemmArgs *args);
+
+/* ---- timing ------------------------------------------------------------------------- */
+
+HC_CUDA_CAPI_EXPORTED int hcCudaEventCreate(HcCudaContext *ctx, HcCudaEvent **out);
+HC_CUDA_CAPI_EXPORTED int hcCudaEventDestroy(HcCudaContext *ctx, HcCudaEvent *event);
+/* Records on the context stream (asynchronous). */
+HC_CUDA_CAPI_EXPORTED int hcCudaEventRecord(HcCudaContext *ctx, HcCudaEvent *event);
+/* Waits for `stop`, then returns the device time between the two records. */
+HC_CUDA_CAPI_EXPORTED int hcCudaEventElapsedMs(HcCudaContext *ctx, HcCudaEvent *start,
+                                               HcCudaEvent *stop, float *milliseconds);
+
+/* ---- multi-GPU (one process per GPU; the N-sharded GEMM) ---------------------------- */
+
+#define HC_CUDA_COMM_ID_BYTES 128
+
+/* Rank 0 creates an id and hands it to the other ranks by any host channel. */
+HC_CUDA_CAPI_EXPORTED int hcCudaCommGetUniqueId(void *id, size_t id_bytes);
+/* Collective over all ranks: joins this context to a communicator of `nranks`. */
+HC_CUDA_CAPI_EXPORTED int hcCudaCommInitRank(HcCudaContext *ctx, const void *id, size_t id_bytes,
+                                             int nranks, int rank);
+/* Asynchronous all-gather over NVLink: every rank contributes `bytes_per_rank` bytes from
+ * `send`; `recv` (nranks * bytes_per_rank) receives them in rank order (slab-major C). */
+HC_CUDA_CAPI_EXPORTED int hcCudaCommAllGather(HcCudaContext *ctx, const void *send, void *recv,
+                                              size_t bytes_per_rank);
+HC_CUDA_CAPI_EXPORTED int hcCudaCommDestroy(HcCudaContext *ctx);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* HC_C_CUDA_H */
