@@ -1,0 +1,60 @@
+"""hc -- the kernel-DSL surface of the tiled-matmul path, with a B200 launch backend.
+
+The public names are those of the reference package (hc/__init__.py:11-63). `hc.compile`
+gains `target="nvidia-sm100a"`, which makes the returned handle launch hand-written sm_100a
+kernels through the C ABI of include/hc-c/Cuda.h; `hc.cuda` exposes that ABI (contexts,
+device buffers, pinned arrays) and `hc.distributed` the N-sharding helpers. `hc.symbols`
+and `hc.cuda` load lazily, as `symbols` does in the reference.
+"""
+
+from __future__ import annotations
+
+import importlib
+from typing import Any
+
+from ._compile import CompiledKernel, compile
+from .core import (
+    Buffer,
+    BufferSpec,
+    CurrentGroup,
+    IdxTypeSpec,
+    IndexMap,
+    Result,
+    Scope,
+    SubGroup,
+    TensorTypeSpec,
+    UndefTypeSpec,
+    VectorTypeSpec,
+    WorkGroup,
+    WorkItem,
+    as_layout,
+    idx_type,
+    index_map,
+    kernel,
+    tensor_type,
+    undef_type,
+    vector_type,
+)
+from .errors import DeviceError, LaunchError, SimulatorError
+
+__all__ = [
+    "Buffer", "BufferSpec", "CompiledKernel", "CurrentGroup", "DeviceError", "IdxTypeSpec",
+    "IndexMap", "LaunchError", "Result", "Scope", "SimulatorError", "SubGroup", "Symbol",
+    "TensorTypeSpec", "UndefTypeSpec", "VectorTypeSpec", "WorkGroup", "WorkItem", "as_layout",
+    "compile", "cuda", "distributed", "idx_type", "index_map", "kernel", "sym", "symbols",
+    "tensor_type", "undef_type", "vector_type",
+]
+
+_LAZY_MODULES = {"symbols", "cuda", "distributed"}
+
+
+def __getattr__(name: str) -> Any:
+    if name in _LAZY_MODULES:
+        return importlib.import_module(f".{name}", __name__)
+    if name in ("Symbol", "sym"):
+        return getattr(importlib.import_module(".symbols", __name__), name)
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
+
+
+def __dir__() -> list[str]:
+    return sorted(__all__)

@@ -1,0 +1,199 @@
+"""`hc.compile`: turn a `@kernel` function into a handle, and -- new here -- launch it.
+
+Signature, argument checks and the handle's fields follow the reference
+(hc/_compile.py:41-150): `compile(kernel_fn, symbols=None, *, schedule=None)` returns a
+frozen `CompiledKernel` carrying the kernel, the normalised literal bindings and the IR
+fields. Two things differ:
+
+  * `target=` selects a backend. With `target="nvidia-sm100a"` the handle's `__call__`
+    runs the kernel on a B200 through include/hc-c/Cuda.h instead of raising
+    `NotImplementedError` (hc/_compile.py:57-62). The call takes the kernel's arguments
+    without the group (doc/langref.md:133-142), writes C in place and returns None once
+    the result is complete, like `hc.simulator.launch` (hc/simulator.py:165-186).
+  * The MLIR front half is not part of this package: `front_ir`/`hc_ir` stay None and
+    `pipeline_diagnostics` says so, the same non-fatal convention the reference uses when
+    its pipeline fails (hc/_pipeline.py:100-108). `schedule=` is accepted and recorded.
+"""
+
+from __future__ import annotations
+
+from collections.abc import Mapping
+from dataclasses import dataclass, field
+from typing import Any
+
+import numpy as np
+
+from ._launch import PreparedLaunch, prepare_launch
+from ._pipeline import GemmContract, ScheduleSource, lower_for_target
+from .errors import LaunchError
+
+__all__ = ["CompiledKernel", "ScheduleSource", "compile"]
+
+_NO_MLIR = ("hc_front / hc MLIR is not produced by this package: the MLIR front half of hc is "
+            "outside the B200 launch path")
+
+
+@dataclass(frozen=True)
+class CompiledKernel:
+    """Handle returned by `hc.compile`."""
+
+    kernel: Any
+    bindings: Mapping[str, int]
+    front_ir: Any = None
+    front_ir_text: str | None = None
+    front_ir_symbols: tuple[str, ...] = field(default=())
+    hc_ir: Any | None = field(default=None)
+    hc_ir_text: str | None = field(default=None)
+    pipeline_diagnostics: tuple[str, ...] = field(default=())
+    # Extensions of the NVIDIA path.
+    target: str | None = field(default=None)
+    plan: GemmContract | None = field(default=None)
+    schedule: ScheduleSource = field(default=None)
+    device: int | None = field(default=None)
+
+    # -- launch -------------------------------------------------------------------------
+    def __call__(self, *args: Any, **kwargs: Any) -> None:
+        if self.target is None:
+            raise NotImplementedError(
+                "this handle was compiled without a target; pass target='nvidia-sm100a' to "
+                "hc.compile to get a launchable kernel")
+        if self.plan is None:
+            reasons = "; ".join(self.pipeline_diagnostics) or "kernel not recognised"
+            raise NotImplementedError(
+                f"target {self.target!r} cannot launch {self._name()}: {reasons}")
+        launch = prepare_launch(self.kernel, args, kwargs, dict(self.bindings))
+        if launch.is_empty:
+            return None
+        self._launch_gemm(launch)
+        return None
+
+    def prepare(self, *args: Any, **kwargs: Any) -> PreparedLaunch:
+        """Binding and geometry of a call, without launching (symbols, work/group shape)."""
+        return prepare_launch(self.kernel, args, kwargs, dict(self.bindings))
+
+    def _launch_gemm(self, launch: PreparedLaunch) -> None:
+        from . import cuda  # imported on first launch so that compile() needs no CUDA library
+
+        plan = self.plan
+        assert plan is not None
+        a, b, c = (launch.arguments[p] for p in (plan.a_param, plan.b_param, plan.c_param))
+        on_device = [type(x).__name__ == "DeviceBuffer" for x in (a, b, c)]
+        if any(on_device) and not all(on_device):
+            raise LaunchError("buffers must be all numpy.ndarray or all DeviceBuffer")
+        if all(on_device):
+            ctx = a.ctx
+            if b.ctx is not ctx or c.ctx is not ctx:
+                raise LaunchError("device buffers must belong to one context")
+            ctx.gemm(a, b, c)
+            ctx.synchronize()
+            return
+        ctx = cuda.default_context(self.device)
+        a_host = _row_major(a)
+        b_host = _row_major(b)
+        if _is_row_major(c) and c.flags.writeable:
+            ctx.gemm_host(a_host, b_host, c)
+            return
+        if not c.flags.writeable:
+            raise LaunchError(f"{plan.c_param} must be writeable")
+        staged = np.empty(c.shape, np.float32)
+        ctx.gemm_host(a_host, b_host, staged)
+        c[...] = staged
+
+    # -- text ---------------------------------------------------------------------------
+    def _name(self) -> str:
+        return getattr(self.kernel, "__name__", "<kernel>")
+
+    def __repr__(self) -> str:
+        joined = ", ".join(f"{k}={v}" for k, v in sorted(self.bindings.items()))
+        if self.target is not None:
+            stage = self.target if self.plan is not None else f"{self.target}:unsupported"
+        else:
+            stage = "hc" if self.hc_ir_text is not None else "hc_front"
+        return f"CompiledKernel({self._name()}, {{{joined}}}, stage={stage})"
+
+
+def _is_row_major(x: np.ndarray) -> bool:
+    """Rows contiguous, row pitch a whole non-negative number of elements."""
+    if x.ndim != 2:
+        return False
+    if x.shape[0] == 0 or x.shape[1] == 0:
+        return True
+    item = x.itemsize
+    inner_ok = x.shape[1] == 1 or x.strides[1] == item
+    outer_ok = x.shape[0] == 1 or (x.strides[0] % item == 0 and x.strides[0] >= x.shape[1] * item)
+    return inner_ok and outer_ok
+
+
+def _row_major(x: np.ndarray) -> np.ndarray:
+    return x if _is_row_major(x) else np.ascontiguousarray(x)
+
+
+def compile(  # noqa: A001 - public name fixed by the reference API
+    kernel_fn: Any,
+    symbols: Mapping[Any, int] | None = None,
+    *,
+    schedule: ScheduleSource = None,
+    target: str | None = None,
+    device: int | None = None,
+) -> CompiledKernel:
+    """Compile a `@kernel` function.
+
+    `symbols` binds literal symbols (keys: `Symbol` or `str`; values: `int`). Keys must be in
+    the kernel's `literals=` set when it declared one. With `target="nvidia-sm100a"` the
+    returned handle is callable; bound symbols are checked against the buffer shapes of
+    every call. `device` picks the GPU for NumPy-buffer launches (default `$HC_CUDA_DEVICE`
+    or 0).
+    """
+    metadata = getattr(kernel_fn, "__hc_kernel__", None)
+    if metadata is None or not hasattr(metadata, "work_shape"):
+        raise TypeError(f"hc.compile expects a @kernel-decorated function, got {kernel_fn!r}")
+    if symbols is None:
+        symbols = {}
+    elif not isinstance(symbols, Mapping):
+        raise TypeError(f"symbols must be a Mapping, got {type(symbols).__name__}")
+    bindings = normalise_bindings(symbols, metadata)
+
+    diagnostics = [_NO_MLIR]
+    plan = None
+    if target is not None:
+        result = lower_for_target(kernel_fn, target)
+        plan = result.plan
+        diagnostics.extend(result.diagnostics)
+    return CompiledKernel(
+        kernel=kernel_fn,
+        bindings=bindings,
+        pipeline_diagnostics=tuple(diagnostics),
+        target=target,
+        plan=plan,
+        schedule=schedule,
+        device=device,
+    )
+
+
+def symbol_name(obj: Any) -> str:
+    if isinstance(obj, str):
+        return obj
+    name = getattr(obj, "name", None)
+    if isinstance(name, str) and hasattr(obj, "free_symbols"):
+        return name
+    raise TypeError(f"cannot interpret {obj!r} as a symbol name")
+
+
+def normalise_bindings(symbols: Mapping[Any, int], metadata: Any) -> dict[str, int]:
+    """`symbols=` -> {name: int}; same rules and messages as hc/_compile.py:153-181."""
+    allowed = {symbol_name(s) for s in metadata.literals}
+    out: dict[str, int] = {}
+    for key, value in symbols.items():
+        name = symbol_name(key)
+        if allowed and name not in allowed:
+            raise ValueError(
+                f"'{name}' is not a declared literal symbol; kernel declares {sorted(allowed)}")
+        if isinstance(value, bool) or not isinstance(value, int):
+            raise TypeError(
+                f"literal symbol '{name}' must bind to an int, got {type(value).__name__}")
+        if name in out and out[name] != value:
+            raise ValueError(
+                f"literal symbol '{name}' bound twice with conflicting values "
+                f"({out[name]!r} and {value!r})")
+        out[name] = value
+    return out

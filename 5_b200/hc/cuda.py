@@ -1,0 +1,468 @@
+"""ctypes binding of include/hc-c/Cuda.h plus the small device-memory objects a launch needs.
+
+Host code stays NumPy: a `DeviceBuffer` is a (pointer, shape, dtype, pitch) record whose
+memory lives on the GPU, and `pinned_empty` gives NumPy arrays in page-locked memory so that
+host<->device copies run at full PCIe speed. There is no CPU fallback anywhere in this
+module: when the shared library is missing or no sm_100 device is present, the calls raise.
+
+The library is looked up at `$HC_CUDA_LIB`, else at `lib/libhc_cuda.so` beside this package
+(built by `5_b200/build.py`).
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+from pathlib import Path
+from typing import Any
+
+import numpy as np
+
+from .errors import DeviceError
+
+__all__ = [
+    "Context",
+    "DeviceBuffer",
+    "GemmPlan",
+    "default_context",
+    "device_count",
+    "library",
+    "library_path",
+    "pinned_empty",
+    "plan_gemm",
+]
+
+F16, BF16 = 0, 1
+VARIANT_AUTO, VARIANT_DENSE, VARIANT_SKINNY, VARIANT_NOOP, VARIANT_ZERO_FILL = 0, 1, 2, 3, 4
+VARIANT_NAMES = {0: "auto", 1: "dense", 2: "skinny", 3: "noop", 4: "zero_fill"}
+COMM_ID_BYTES = 128
+
+EXPORTS = (
+    "hcCudaApiVersion", "hcCudaStatusString", "hcCudaGetDeviceCount", "hcCudaContextCreate",
+    "hcCudaContextDestroy", "hcCudaContextLastError", "hcCudaContextGetDeviceInfo",
+    "hcCudaContextSynchronize", "hcCudaMalloc", "hcCudaFree", "hcCudaHostAlloc", "hcCudaHostFree",
+    "hcCudaMemcpyHtoD", "hcCudaMemcpyDtoH", "hcCudaMemcpy2DHtoD", "hcCudaMemcpy2DDtoH",
+    "hcCudaMemset", "hcCudaGemmPlan", "hcCudaGemm", "hcCudaGemmHost", "hcCudaEventCreate",
+    "hcCudaEventDestroy", "hcCudaEventRecord", "hcCudaEventElapsedMs", "hcCudaCommGetUniqueId",
+    "hcCudaCommInitRank", "hcCudaCommAllGather", "hcCudaCommDestroy",
+)
+
+
+class _GemmArgs(ctypes.Structure):
+    _fields_ = [
+        ("m", ctypes.c_int64), ("n", ctypes.c_int64), ("k", ctypes.c_int64),
+        ("dtype", ctypes.c_int32), ("variant", ctypes.c_int32),
+        ("a", ctypes.c_void_p), ("lda", ctypes.c_int64),
+        ("b", ctypes.c_void_p), ("ldb", ctypes.c_int64),
+        ("c", ctypes.c_void_p), ("ldc", ctypes.c_int64),
+    ]
+
+
+class _PlanInfo(ctypes.Structure):
+    _fields_ = [
+        ("variant", ctypes.c_int32), ("tiles_m", ctypes.c_int32), ("tiles_n", ctypes.c_int32),
+        ("splits", ctypes.c_int32), ("grid", ctypes.c_int32), ("repack_a", ctypes.c_int32),
+        ("repack_b", ctypes.c_int32), ("kernel_launches", ctypes.c_int32),
+        ("scratch_bytes", ctypes.c_int64),
+    ]
+
+
+class _DeviceInfo(ctypes.Structure):
+    _fields_ = [
+        ("name", ctypes.c_char * 128), ("device", ctypes.c_int32), ("cc_major", ctypes.c_int32),
+        ("cc_minor", ctypes.c_int32), ("sm_count", ctypes.c_int32),
+        ("total_memory_bytes", ctypes.c_int64), ("l2_bytes", ctypes.c_int32),
+        ("sm_clock_khz", ctypes.c_int32),
+    ]
+
+
+_LIB: ctypes.CDLL | None = None
+_LIB_LOCK = threading.Lock()
+
+
+def library_path() -> Path:
+    override = os.environ.get("HC_CUDA_LIB")
+    if override:
+        return Path(override)
+    return Path(__file__).resolve().parent.parent / "lib" / "libhc_cuda.so"
+
+
+def library() -> ctypes.CDLL:
+    """Loads libhc_cuda.so once. Raises ImportError (never falls back) when it is missing."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    with _LIB_LOCK:
+        if _LIB is not None:
+            return _LIB
+        path = library_path()
+        if not path.exists():
+            raise ImportError(
+                f"the hc CUDA library was not found at {path}; build it with "
+                "`python 5_b200/build.py` or point HC_CUDA_LIB at it"
+            )
+        lib = ctypes.CDLL(str(path))
+        vp, i, sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
+        pvp = ctypes.POINTER(ctypes.c_void_p)
+        lib.hcCudaApiVersion.restype = i
+        lib.hcCudaStatusString.restype = ctypes.c_char_p
+        lib.hcCudaStatusString.argtypes = [i]
+        lib.hcCudaGetDeviceCount.argtypes = [ctypes.POINTER(i)]
+        lib.hcCudaContextCreate.argtypes = [i, pvp]
+        lib.hcCudaContextDestroy.argtypes = [vp]
+        lib.hcCudaContextLastError.restype = ctypes.c_char_p
+        lib.hcCudaContextLastError.argtypes = [vp]
+        lib.hcCudaContextGetDeviceInfo.argtypes = [vp, ctypes.POINTER(_DeviceInfo)]
+        lib.hcCudaContextSynchronize.argtypes = [vp]
+        lib.hcCudaMalloc.argtypes = [vp, sz, pvp]
+        lib.hcCudaFree.argtypes = [vp, vp]
+        lib.hcCudaHostAlloc.argtypes = [sz, pvp]
+        lib.hcCudaHostFree.argtypes = [vp]
+        lib.hcCudaMemcpyHtoD.argtypes = [vp, vp, vp, sz]
+        lib.hcCudaMemcpyDtoH.argtypes = [vp, vp, vp, sz]
+        lib.hcCudaMemcpy2DHtoD.argtypes = [vp, vp, sz, vp, sz, sz, sz]
+        lib.hcCudaMemcpy2DDtoH.argtypes = [vp, vp, sz, vp, sz, sz, sz]
+        lib.hcCudaMemset.argtypes = [vp, vp, i, sz]
+        lib.hcCudaGemmPlan.argtypes = [ctypes.POINTER(_GemmArgs), i, ctypes.POINTER(_PlanInfo)]
+        lib.hcCudaGemm.argtypes = [vp, ctypes.POINTER(_GemmArgs)]
+        lib.hcCudaGemmHost.argtypes = [vp, ctypes.POINTER(_GemmArgs)]
+        lib.hcCudaEventCreate.argtypes = [vp, pvp]
+        lib.hcCudaEventDestroy.argtypes = [vp, vp]
+        lib.hcCudaEventRecord.argtypes = [vp, vp]
+        lib.hcCudaEventElapsedMs.argtypes = [vp, vp, vp, ctypes.POINTER(ctypes.c_float)]
+        lib.hcCudaCommGetUniqueId.argtypes = [vp, sz]
+        lib.hcCudaCommInitRank.argtypes = [vp, vp, sz, i, i]
+        lib.hcCudaCommAllGather.argtypes = [vp, vp, vp, sz]
+        lib.hcCudaCommDestroy.argtypes = [vp]
+        for name in EXPORTS:
+            getattr(lib, name)  # AttributeError here means a stale or foreign library
+        _LIB = lib
+    return _LIB
+
+
+def _raise(status: int, ctx_handle: Any = None) -> None:
+    lib = library()
+    name = lib.hcCudaStatusString(status).decode()
+    detail = lib.hcCudaContextLastError(ctx_handle).decode(errors="replace")
+    raise DeviceError(status, name, detail)
+
+
+def device_count() -> int:
+    count = ctypes.c_int(0)
+    status = library().hcCudaGetDeviceCount(ctypes.byref(count))
+    if status:
+        _raise(status)
+    return count.value
+
+
+def dtype_code(dtype: Any) -> int:
+    name = dtype if isinstance(dtype, str) else np.dtype(dtype).name
+    if name == "float16":
+        return F16
+    if name == "bfloat16":
+        return BF16
+    raise ValueError(f"the CUDA backend multiplies float16 or bfloat16 matrices, got {name}")
+
+
+class GemmPlan:
+    """What one GEMM call does on the device (`hcCudaGemmPlan`)."""
+
+    def __init__(self, info: _PlanInfo) -> None:
+        self.variant = VARIANT_NAMES.get(info.variant, str(info.variant))
+        self.tiles_m = info.tiles_m
+        self.tiles_n = info.tiles_n
+        self.splits = info.splits
+        self.grid = info.grid
+        self.repack_a = bool(info.repack_a)
+        self.repack_b = bool(info.repack_b)
+        self.kernel_launches = info.kernel_launches
+        self.scratch_bytes = info.scratch_bytes
+
+    def __repr__(self) -> str:
+        return (f"GemmPlan({self.variant}, tiles={self.tiles_m}x{self.tiles_n}, splits={self.splits}, "
+                f"grid={self.grid}, repack=({self.repack_a}, {self.repack_b}), "
+                f"launches={self.kernel_launches}, scratch={self.scratch_bytes})")
+
+
+def _gemm_args(m: int, n: int, k: int, dtype: Any, a: int | None, lda: int, b: int | None, ldb: int,
+               c: int | None, ldc: int, variant: int) -> _GemmArgs:
+    return _GemmArgs(m, n, k, dtype_code(dtype), variant, a, lda, b, ldb, c, ldc)
+
+
+def plan_gemm(m: int, n: int, k: int, dtype: Any, *, a: int = 0x1000, lda: int | None = None,
+              b: int = 0x40000000, ldb: int | None = None, c: int = 0x80000000,
+              ldc: int | None = None, variant: int = VARIANT_AUTO, sm_count: int = 148) -> GemmPlan:
+    """Validates a problem and returns its launch plan without touching a device.
+
+    The pointer arguments are plain integers that are only inspected (null, alignment,
+    overlap); the defaults are well-aligned, far-apart placeholders.
+    """
+    args = _gemm_args(m, n, k, dtype, a, k if lda is None else lda, b, n if ldb is None else ldb,
+                      c, n if ldc is None else ldc, variant)
+    info = _PlanInfo()
+    status = library().hcCudaGemmPlan(ctypes.byref(args), sm_count, ctypes.byref(info))
+    if status:
+        _raise(status)
+    return GemmPlan(info)
+
+
+class Context:
+    """One device: its stream, scratch memory and (optionally) its NCCL communicator."""
+
+    def __init__(self, device: int = 0) -> None:
+        self._lib = library()
+        handle = ctypes.c_void_p()
+        status = self._lib.hcCudaContextCreate(device, ctypes.byref(handle))
+        if status:
+            _raise(status)
+        self._handle = handle
+        self.device = device
+        info = _DeviceInfo()
+        self._check(self._lib.hcCudaContextGetDeviceInfo(self._handle, ctypes.byref(info)))
+        self.name = info.name.decode()
+        self.sm_count = info.sm_count
+        self.compute_capability = (info.cc_major, info.cc_minor)
+        self.total_memory_bytes = info.total_memory_bytes
+        self.l2_bytes = info.l2_bytes
+        self.sm_clock_khz = info.sm_clock_khz
+
+    # -- plumbing -----------------------------------------------------------------------
+    def _check(self, status: int) -> None:
+        if status:
+            _raise(status, self._handle)
+
+    def close(self) -> None:
+        if getattr(self, "_handle", None):
+            self._lib.hcCudaContextDestroy(self._handle)
+            self._handle = None
+
+    def __del__(self) -> None:  # pragma: no cover - best effort
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def __enter__(self) -> "Context":
+        return self
+
+    def __exit__(self, *exc: Any) -> None:
+        self.close()
+
+    def synchronize(self) -> None:
+        self._check(self._lib.hcCudaContextSynchronize(self._handle))
+
+    # -- memory -------------------------------------------------------------------------
+    def malloc(self, nbytes: int) -> int:
+        ptr = ctypes.c_void_p()
+        self._check(self._lib.hcCudaMalloc(self._handle, nbytes, ctypes.byref(ptr)))
+        return ptr.value or 0
+
+    def free(self, ptr: int) -> None:
+        if ptr:
+            self._check(self._lib.hcCudaFree(self._handle, ptr))
+
+    def memset(self, ptr: int, byte_value: int, nbytes: int) -> None:
+        self._check(self._lib.hcCudaMemset(self._handle, ptr, byte_value, nbytes))
+
+    def empty(self, shape: tuple[int, ...], dtype: Any) -> "DeviceBuffer":
+        return DeviceBuffer(self, shape, dtype)
+
+    def to_device(self, array: np.ndarray) -> "DeviceBuffer":
+        buf = DeviceBuffer(self, array.shape, array.dtype)
+        buf.copy_from_host(array)
+        return buf
+
+    # -- the hot path -------------------------------------------------------------------
+    def gemm(self, a: "DeviceBuffer", b: "DeviceBuffer", c: "DeviceBuffer", *,
+             variant: int = VARIANT_AUTO) -> None:
+        """Enqueues C = A @ B on device buffers (asynchronous; see `synchronize`)."""
+        m, k = a.shape
+        n = b.shape[1]
+        args = _gemm_args(m, n, k, a.dtype, a.ptr, a.ld, b.ptr, b.ld, c.ptr, c.ld, variant)
+        self._check(self._lib.hcCudaGemm(self._handle, ctypes.byref(args)))
+
+    def gemm_host(self, a: np.ndarray, b: np.ndarray, c: np.ndarray, *,
+                  variant: int = VARIANT_AUTO) -> None:
+        """C = A @ B on host arrays: copies in, multiplies on the GPU, copies C back in place."""
+        m, k = a.shape
+        n = b.shape[1]
+        args = _gemm_args(m, n, k, a.dtype, a.ctypes.data, a.strides[0] // a.itemsize if m > 1 else max(k, 1),
+                          b.ctypes.data, b.strides[0] // b.itemsize if k > 1 else max(n, 1),
+                          c.ctypes.data, c.strides[0] // c.itemsize if m > 1 else max(n, 1), variant)
+        self._check(self._lib.hcCudaGemmHost(self._handle, ctypes.byref(args)))
+
+    def plan(self, m: int, n: int, k: int, dtype: Any, **kwargs: Any) -> GemmPlan:
+        kwargs.setdefault("sm_count", self.sm_count)
+        return plan_gemm(m, n, k, dtype, **kwargs)
+
+    # -- timing -------------------------------------------------------------------------
+    def event(self) -> "Event":
+        return Event(self)
+
+    # -- multi-GPU ----------------------------------------------------------------------
+    @staticmethod
+    def comm_unique_id() -> bytes:
+        buf = ctypes.create_string_buffer(COMM_ID_BYTES)
+        status = library().hcCudaCommGetUniqueId(buf, COMM_ID_BYTES)
+        if status:
+            _raise(status)
+        return buf.raw
+
+    def comm_init(self, unique_id: bytes, world_size: int, rank: int) -> None:
+        buf = ctypes.create_string_buffer(bytes(unique_id), COMM_ID_BYTES)
+        self._check(self._lib.hcCudaCommInitRank(self._handle, buf, COMM_ID_BYTES, world_size, rank))
+
+    def all_gather(self, send: "DeviceBuffer", recv: "DeviceBuffer") -> None:
+        """Asynchronous all-gather of whole buffers; `recv` holds world_size copies of `send`."""
+        self._check(self._lib.hcCudaCommAllGather(self._handle, send.ptr, recv.ptr, send.nbytes))
+
+    def comm_destroy(self) -> None:
+        self._check(self._lib.hcCudaCommDestroy(self._handle))
+
+
+class Event:
+    def __init__(self, ctx: Context) -> None:
+        self._ctx = ctx
+        handle = ctypes.c_void_p()
+        ctx._check(ctx._lib.hcCudaEventCreate(ctx._handle, ctypes.byref(handle)))
+        self._handle = handle
+
+    def record(self) -> None:
+        self._ctx._check(self._ctx._lib.hcCudaEventRecord(self._ctx._handle, self._handle))
+
+    def elapsed_ms_since(self, start: "Event") -> float:
+        """Waits for this event, then returns the device time since `start` in milliseconds."""
+        ms = ctypes.c_float()
+        self._ctx._check(self._ctx._lib.hcCudaEventElapsedMs(self._ctx._handle, start._handle,
+                                                             self._handle, ctypes.byref(ms)))
+        return ms.value
+
+    def close(self) -> None:
+        if self._handle and self._ctx._handle:
+            self._ctx._lib.hcCudaEventDestroy(self._ctx._handle, self._handle)
+        self._handle = None
+
+    def __del__(self) -> None:  # pragma: no cover
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class DeviceBuffer:
+    """A row-major matrix (or vector) in device memory. `ld` is the row pitch in elements."""
+
+    def __init__(self, ctx: Context, shape: tuple[int, ...], dtype: Any, *, ld: int | None = None) -> None:
+        self.ctx = ctx
+        self.shape = tuple(int(s) for s in shape)
+        self.dtype = np.dtype(dtype)
+        self.ndim = len(self.shape)
+        cols = self.shape[-1] if self.shape else 1
+        self.ld = int(cols if ld is None else ld)
+        if self.ld < cols:
+            raise ValueError("ld must be at least the number of columns")
+        rows = int(np.prod(self.shape[:-1])) if self.ndim > 1 else 1
+        self._rows = rows
+        self.nbytes = rows * self.ld * self.dtype.itemsize
+        self.ptr = ctx.malloc(self.nbytes) if self.nbytes else 0
+
+    def copy_from_host(self, array: np.ndarray) -> None:
+        if tuple(array.shape) != self.shape or array.dtype != self.dtype:
+            raise ValueError("host array does not match the device buffer")
+        if not self.nbytes:
+            return
+        src = np.ascontiguousarray(array)
+        width = self.shape[-1] * self.dtype.itemsize
+        self.ctx._check(self.ctx._lib.hcCudaMemcpy2DHtoD(
+            self.ctx._handle, self.ptr, self.ld * self.dtype.itemsize, src.ctypes.data, width, width,
+            self._rows))
+
+    def copy_from_host_columns(self, array: np.ndarray, col_begin: int, col_end: int) -> None:
+        """Fills the buffer from columns [col_begin, col_end) of a wider row-major host matrix."""
+        if array.ndim != 2 or array.dtype != self.dtype or self.shape != (array.shape[0], col_end - col_begin):
+            raise ValueError("host slab does not match the device buffer")
+        if not array.flags.c_contiguous:
+            array = np.ascontiguousarray(array)
+        item = self.dtype.itemsize
+        self.ctx._check(self.ctx._lib.hcCudaMemcpy2DHtoD(
+            self.ctx._handle, self.ptr, self.ld * item, array.ctypes.data + col_begin * item,
+            array.shape[1] * item, (col_end - col_begin) * item, array.shape[0]))
+
+    def to_numpy(self, out: np.ndarray | None = None) -> np.ndarray:
+        if out is None:
+            out = np.empty(self.shape, self.dtype)
+        if tuple(out.shape) != self.shape or out.dtype != self.dtype or not out.flags.c_contiguous:
+            raise ValueError("output array must be C-contiguous and match the device buffer")
+        if self.nbytes:
+            width = self.shape[-1] * self.dtype.itemsize
+            self.ctx._check(self.ctx._lib.hcCudaMemcpy2DDtoH(
+                self.ctx._handle, out.ctypes.data, width, self.ptr, self.ld * self.dtype.itemsize,
+                width, self._rows))
+        return out
+
+    def fill_bytes(self, byte_value: int) -> None:
+        if self.nbytes:
+            self.ctx.memset(self.ptr, byte_value, self.nbytes)
+
+    def free(self) -> None:
+        if self.ptr and self.ctx._handle:
+            self.ctx.free(self.ptr)
+        self.ptr = 0
+
+    def __del__(self) -> None:  # pragma: no cover
+        try:
+            self.free()
+        except Exception:
+            pass
+
+    def __repr__(self) -> str:
+        return f"DeviceBuffer(shape={self.shape}, dtype={self.dtype.name}, ld={self.ld}, device={self.ctx.device})"
+
+
+class _PinnedOwner:
+    """Keeps a page-locked allocation alive for the NumPy arrays that view it."""
+
+    def __init__(self, nbytes: int) -> None:
+        ptr = ctypes.c_void_p()
+        status = library().hcCudaHostAlloc(nbytes, ctypes.byref(ptr))
+        if status:
+            _raise(status)
+        self.ptr = ptr.value
+        self.nbytes = nbytes
+        self.__array_interface__ = {
+            "shape": (nbytes,), "typestr": "|u1", "data": (self.ptr, False), "version": 3,
+        }
+
+    def __del__(self) -> None:  # pragma: no cover
+        try:
+            if self.ptr:
+                library().hcCudaHostFree(self.ptr)
+        except Exception:
+            pass
+        self.ptr = None
+
+
+def pinned_empty(shape: tuple[int, ...], dtype: Any) -> np.ndarray:
+    """NumPy array in page-locked host memory (needs a CUDA driver)."""
+    dtype = np.dtype(dtype)
+    nbytes = int(np.prod(shape)) * dtype.itemsize
+    if nbytes == 0:
+        return np.empty(shape, dtype)
+    owner = _PinnedOwner(nbytes)
+    return np.asarray(owner).view(dtype).reshape(shape)
+
+
+_DEFAULT: dict[int, Context] = {}
+_DEFAULT_LOCK = threading.Lock()
+
+
+def default_context(device: int | None = None) -> Context:
+    """Process-wide context of a device; `device=None` means `$HC_CUDA_DEVICE` or 0."""
+    if device is None:
+        device = int(os.environ.get("HC_CUDA_DEVICE", "0"))
+    with _DEFAULT_LOCK:
+        ctx = _DEFAULT.get(device)
+        if ctx is None or not ctx._handle:
+            ctx = _DEFAULT[device] = Context(device)
+        return ctx

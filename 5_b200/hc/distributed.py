@@ -1,0 +1,107 @@
+"""N-sharding of the matmul across the GPUs of one box: one process per GPU.
+
+The product splits by columns with no exchange: rank r owns the column slab
+`B[:, lo:hi]` and writes `C[:, lo:hi]`; A is replicated. A slab is just a matmul with a
+smaller N, so each rank launches the same compiled handle on its own buffers. The only
+collective is optional: an all-gather of the C slabs over NVLink (NCCL), which yields C
+slab-major, `[rank][M][slab columns]`; `assemble_row_major` describes the host-side view that
+turns that back into a row-major matrix. The reference has no multi-device notion at all;
+this module is the whole of it here.
+"""
+
+from __future__ import annotations
+
+from collections.abc import Callable
+from dataclasses import dataclass
+from typing import Any
+
+import numpy as np
+
+__all__ = ["ColumnSlab", "ShardedMatmul", "assemble_row_major", "column_slab", "init_communicator"]
+
+
+@dataclass(frozen=True)
+class ColumnSlab:
+    rank: int
+    world_size: int
+    begin: int
+    end: int
+
+    @property
+    def width(self) -> int:
+        return self.end - self.begin
+
+
+def column_slab(n: int, world_size: int, rank: int, *, align: int = 1) -> ColumnSlab:
+    """Columns [begin, end) of rank `rank` when `n` columns are split over `world_size`.
+
+    Slabs are contiguous and cover [0, n) exactly once. The columns are dealt out in blocks
+    of `align` (the last block may be partial), so boundaries are multiples of `align` (use
+    the CTA tile width, 256, to keep every slab tile-aligned) and slabs differ by at most one
+    block. Ranks past the last column get an empty slab.
+    """
+    if world_size < 1 or not 0 <= rank < world_size:
+        raise ValueError(f"rank {rank} is not in [0, {world_size})")
+    if n < 0 or align < 1:
+        raise ValueError("n must be non-negative and align positive")
+    blocks = -(-n // align)
+    base, extra = divmod(blocks, world_size)
+    first = rank * base + min(rank, extra)
+    count = base + (1 if rank < extra else 0)
+    begin = min(first * align, n)
+    end = min((first + count) * align, n)
+    return ColumnSlab(rank, world_size, begin, end)
+
+
+def init_communicator(ctx: Any, world_size: int, rank: int,
+                      broadcast: Callable[[bytes | None], bytes]) -> None:
+    """Joins `ctx` to a NCCL communicator of `world_size` ranks.
+
+    `broadcast(payload)` must return rank 0's payload on every rank (rank 0 passes the id it
+    created, the others pass None); any host channel will do, e.g. a `torch.distributed`
+    object broadcast or a file.
+    """
+    payload = ctx.comm_unique_id() if rank == 0 else None
+    unique_id = broadcast(payload)
+    if not isinstance(unique_id, (bytes, bytearray)) or len(unique_id) == 0:
+        raise RuntimeError("broadcast() did not deliver rank 0's communicator id")
+    ctx.comm_init(bytes(unique_id), world_size, rank)
+
+
+class ShardedMatmul:
+    """Per-rank driver of the N-sharded product."""
+
+    def __init__(self, handle: Any, ctx: Any, n: int, world_size: int, rank: int, *, align: int = 256) -> None:
+        self.handle = handle
+        self.ctx = ctx
+        self.n = n
+        self.slab = column_slab(n, world_size, rank, align=align)
+        self.world_size = world_size
+        self.rank = rank
+
+    def upload(self, a: np.ndarray, b: np.ndarray) -> tuple[Any, Any, Any]:
+        """Device copies of A (whole), this rank's slab of B, and an empty slab of C."""
+        if b.shape[1] != self.n:
+            raise ValueError(f"B has {b.shape[1]} columns, the sharding was built for {self.n}")
+        da = self.ctx.to_device(a)
+        db = self.ctx.empty((b.shape[0], self.slab.width), b.dtype)
+        db.copy_from_host_columns(b, self.slab.begin, self.slab.end)
+        dc = self.ctx.empty((a.shape[0], self.slab.width), np.float32)
+        return da, db, dc
+
+    def run(self, da: Any, db_slab: Any, dc_slab: Any) -> None:
+        """C slab = A @ B slab (asynchronous on the rank's stream)."""
+        if self.slab.width:
+            self.ctx.gemm(da, db_slab, dc_slab)
+
+    def all_gather(self, dc_slab: Any, gathered: Any) -> None:
+        """Gathers equal-width C slabs into `gathered`, shape (world_size, M, slab width)."""
+        if self.n % self.world_size != 0 or self.slab.width * self.world_size != self.n:
+            raise ValueError("all_gather needs equal slabs (n divisible by world_size * align)")
+        self.ctx.all_gather(dc_slab, gathered)
+
+
+def assemble_row_major(gathered: np.ndarray) -> np.ndarray:
+    """(world, M, w) slab-major array -> (M, world * w) row-major matrix (host-side copy)."""
+    world, m, width = gathered.shape
+    return np.ascontiguousarray(gathered.transpose(1, 0, 2)).reshape(m, world * width)

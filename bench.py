@@ -1,0 +1,494 @@
+"""Benchmark of the hc tiled-matmul hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload NAME]
+
+One "step" is one pass of the hot path (one GEMM) over one batch of seeded synthetic input.
+
+  N = 1   workload "gemm_8192": M=N=K=8192, float16, fp32 accumulate/output (the configuration
+          the metric is quoted on). `--workload skinny|ragged|sim_64|sharded` time the others.
+  N > 1   workload "sharded": M=16384, N=32768, K=16384 with B and C split by columns over the
+          ranks and A replicated; no data-path collective (strong scaling: the total work is
+          fixed). The optional NCCL all-gather of the C slabs is timed separately.
+
+The JSON line printed by rank 0 carries: `value` (aggregate TFLOP/s, inputs resident in HBM,
+CUDA-event time, max over ranks), `e2e` (the same metric through the public
+`hc.compile(..., target="nvidia-sm100a")` handle on pinned NumPy buffers, host<->device copies
+inside the timed region), `roofline` for the dominant kernel, `cpu_baseline` (the CPU oracle
+timed on this box's host cores on a bounded sample) and the SM clocks sampled while timing.
+
+`--impl reference` times the reference's own CPU implementation of the path instead. The
+reference is Python and cannot run here without its un-vendored dependencies, so this arm
+runs the bit-exact C restatement of its arithmetic (oracle/) on all host threads, on a
+bounded sample of the same workload.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+REPO = Path(__file__).resolve().parent
+for _entry in (str(REPO), str(REPO / "5_b200")):
+    if _entry not in sys.path:
+        sys.path.insert(0, _entry)
+
+import workloads  # noqa: E402
+
+METRIC = "gemm_tflops"
+UNIT = "TFLOP/s"
+NOMINAL_PEAK_TFLOPS = 2250.0  # dense fp16/bf16, for context
+NOMINAL_HBM_GBS = 8000.0
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+# DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum),
+# from the ncu captures summarised under profiles/. None = not captured for that workload.
+NCU_DRAM_TRAFFIC_BYTES = {
+    "gemm_8192": None,
+    "skinny": None,
+}
+
+
+def measured_peaks() -> tuple[dict, str]:
+    path = REPO / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            return json.loads(path.read_text()), "measured"
+        except (OSError, ValueError):
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+# ---------------------------------------------------------------- clocks ----------------
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU in a background thread (read-only)."""
+
+    REASONS = {
+        0x0000000000000004: "sw_power_cap",
+        0x0000000000000008: "hw_slowdown",
+        0x0000000000000020: "sw_thermal_slowdown",
+        0x0000000000000040: "hw_thermal_slowdown",
+        0x0000000000000080: "hw_power_brake_slowdown",
+    }
+
+    def __init__(self, device_index: int, period_s: float = 0.01) -> None:
+        self.device_index = device_index
+        self.period_s = period_s
+        self.samples: list[tuple[float, int, int]] = []  # (time, sm_mhz, reasons bitmask)
+        self.sm_max_mhz: int | None = None
+        self._stop = threading.Event()
+        self._thread: threading.Thread | None = None
+        self._nvml = None
+        self._handle = None
+        self.error: str | None = None
+
+    def start(self) -> None:
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nvml = pynvml
+            self._handle = pynvml.nvmlDeviceGetHandleByIndex(self.device_index)
+            self.sm_max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM))
+        except Exception as exc:  # NVML missing: report, do not fail the benchmark
+            self.error = f"{type(exc).__name__}: {exc}"
+            return
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
+
+    def _run(self) -> None:
+        nv = self._nvml
+        while not self._stop.is_set():
+            try:
+                mhz = int(nv.nvmlDeviceGetClockInfo(self._handle, nv.NVML_CLOCK_SM))
+                try:
+                    reasons = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self._handle))
+                except Exception:
+                    reasons = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._handle))
+                self.samples.append((time.perf_counter(), mhz, reasons))
+            except Exception as exc:
+                self.error = f"{type(exc).__name__}: {exc}"
+                return
+            self._stop.wait(self.period_s)
+
+    def stop(self) -> None:
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=2.0)
+
+    def summary(self, begin: float, end: float) -> dict:
+        inside = [(mhz, reasons) for t, mhz, reasons in self.samples if begin <= t <= end]
+        if not inside:
+            return {"sm_mhz": None, "sm_max_mhz": self.sm_max_mhz, "reasons": [], "samples": 0,
+                    "note": self.error or "no sample fell inside the timed region"}
+        clocks = sorted(mhz for mhz, _ in inside)
+        mask = 0
+        for _, reasons in inside:
+            mask |= reasons
+        names = sorted(name for bit, name in self.REASONS.items() if mask & bit)
+        return {"sm_mhz": clocks[len(clocks) // 2], "sm_max_mhz": self.sm_max_mhz, "reasons": names,
+                "samples": len(inside)}
+
+
+# ---------------------------------------------------------------- distributed plumbing ---
+
+
+class Ranks:
+    """torch.distributed used for rendezvous only: barrier, max-reduce of a float, broadcast."""
+
+    def __init__(self, connect: bool = True) -> None:
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        self.dist = None
+        self.torch = None
+        if self.world > 1 and connect:
+            import torch
+            import torch.distributed as dist
+
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            torch.cuda.set_device(self.local_rank)
+            dist.init_process_group("cpu:gloo,cuda:nccl", rank=self.rank, world_size=self.world)
+            self.dist, self.torch = dist, torch
+
+    def barrier(self) -> None:
+        if self.dist is not None:
+            self.dist.all_reduce(self.torch.zeros(1))  # CPU tensor: goes over gloo
+
+    def device_sync(self) -> None:
+        if self.torch is not None:
+            self.torch.cuda.synchronize()
+
+    def max(self, value: float) -> float:
+        if self.dist is None:
+            return value
+        box = self.torch.tensor([value], dtype=self.torch.float64)
+        self.dist.all_reduce(box, op=self.dist.ReduceOp.MAX)
+        return float(box[0])
+
+    def gather_objects(self, obj):
+        if self.dist is None:
+            return [obj]
+        out = [None] * self.world
+        self.dist.all_gather_object(out, obj)
+        return out
+
+    def broadcast_bytes(self, payload):
+        if self.dist is None:
+            return payload
+        box = [payload]
+        self.dist.broadcast_object_list(box, src=0)
+        return box[0]
+
+    def close(self) -> None:
+        if self.dist is not None:
+            self.dist.destroy_process_group()
+
+
+# ---------------------------------------------------------------- CPU legs ---------------
+
+
+def time_cpu_oracle(a: np.ndarray, b: np.ndarray, target_seconds: float = 12.0) -> dict:
+    """Times the CPU oracle (C restatement of the reference's arithmetic, all host threads) on
+    a bounded sample: the first R rows of C, R chosen so the run takes about `target_seconds`."""
+    from oracle import cpu_ref
+
+    m, k = a.shape
+    n = b.shape[1]
+    threads = cpu_ref.max_threads()
+    probe_rows = min(m, max(threads, 8))
+    start = time.perf_counter()
+    cpu_ref.matmul_k_ascending(a, b, rows=(0, probe_rows))
+    probe = time.perf_counter() - start
+    # The probe includes widening B once; assume the same fixed cost in the real sample.
+    rows = int(min(m, max(probe_rows, probe_rows * target_seconds / max(probe, 1e-3))))
+    rows = max(threads, rows - rows % threads) if rows >= threads else rows
+    rows = min(rows, m)
+    start = time.perf_counter()
+    cpu_ref.matmul_k_ascending(a, b, rows=(0, rows))
+    seconds = time.perf_counter() - start
+    return {
+        "value": workloads.flops(rows, n, k) / seconds / 1e12,
+        "unit": UNIT,
+        "cores": threads,
+        "kind": "port",
+        "seconds": seconds,
+        "sample": f"rows [0,{rows}) of C: {rows}x{n}x{k} multiply-accumulates of the {m}x{n}x{k} workload",
+    }
+
+
+def time_numpy_matmul(a: np.ndarray, b: np.ndarray, budget_rows: int = 8192) -> dict:
+    """NumPy/BLAS float32 matmul of the same shape (inputs widened first), for context."""
+    rows = min(a.shape[0], budget_rows)
+    a32 = a[:rows].astype(np.float32)
+    b32 = b.astype(np.float32)
+    start = time.perf_counter()
+    _ = a32 @ b32
+    seconds = time.perf_counter() - start
+    threads = os.cpu_count() or 1
+    try:
+        from threadpoolctl import threadpool_info
+
+        pools = [p.get("num_threads") for p in threadpool_info() if p.get("user_api") == "blas"]
+        if pools:
+            threads = int(pools[0])
+    except Exception:
+        pass
+    return {"value": workloads.flops(rows, b.shape[1], a.shape[1]) / seconds / 1e12, "unit": UNIT,
+            "threads": threads, "seconds": seconds, "sample": f"{rows}x{b.shape[1]}x{a.shape[1]} float32 matmul"}
+
+
+# ---------------------------------------------------------------- arms -------------------
+
+
+def choose_workload(args, world: int) -> str:
+    if args.workload:
+        return args.workload
+    return "gemm_8192" if world == 1 else "sharded"
+
+
+def run_reference_arm(args, ranks: Ranks) -> None:
+    if ranks.rank != 0:
+        return
+    name = choose_workload(args, ranks.world)
+    w = workloads.CONFIGS[name]
+    if name == "sharded":
+        # One 2048-column block of B is a faithful sample of the sharded product.
+        a, b = workloads.make_sharded_inputs(0, workloads.SHARDED_BLOCK_COLUMNS)
+    else:
+        a, b = workloads.make_inputs(name)
+    per_step = max(2.0, min(20.0, 120.0 / max(1, args.steps + args.warmup)))
+    results = [time_cpu_oracle(a, b, target_seconds=per_step) for _ in range(args.warmup + args.steps)]
+    timed = results[args.warmup:]
+    seconds = sum(r["seconds"] for r in timed)
+    value = sum(float(r["value"]) * r["seconds"] for r in timed) / seconds
+    baseline = dict(timed[-1])
+    baseline["value"] = value
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": ranks.world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": seconds / len(timed) * 1e3,
+        "higher_is_better": True, "scaling": "strong" if ranks.world > 1 else "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": name, "m": w.m, "n": w.n, "k": w.k, "input_dtype": w.dtype,
+                   "note": "CPU restatement of the reference simulator's arithmetic on host cores; "
+                           "each step is the bounded sample named in cpu_baseline.sample"},
+        "cpu_baseline": baseline,
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_gpu_arm(args, ranks: Ranks) -> None:
+    from examples.b200_wmma_matmul import compiled_for
+    from hc import cuda
+    from hc.distributed import column_slab, init_communicator
+
+    name = choose_workload(args, ranks.world)
+    w = workloads.CONFIGS[name]
+    ctx = cuda.Context(ranks.local_rank)
+    handle = compiled_for(w.dtype, ranks.local_rank)
+    if handle.plan is None:
+        raise SystemExit(f"kernel not recognised: {handle.pipeline_diagnostics}")
+
+    # ---- inputs -------------------------------------------------------------------------
+    if name == "sharded":
+        slab = column_slab(w.n, ranks.world, ranks.rank, align=workloads.SHARDED_BLOCK_COLUMNS)
+        a, b = workloads.make_sharded_inputs(slab.begin, slab.end)
+        local_n = slab.width
+    else:
+        if ranks.world > 1:
+            raise SystemExit(f"workload {name} does not shard; run it with --gpus 1")
+        a, b = workloads.make_inputs(name)
+        local_n = w.n
+    m, k = w.m, w.k
+    da, db = ctx.to_device(a), ctx.to_device(b)
+    dc = ctx.empty((m, local_n), np.float32)
+    plan = ctx.plan(m, local_n, k, w.dtype)
+    local_flops = workloads.flops(m, local_n, k)
+    total_flops = workloads.flops(w.m, w.n, w.k)
+
+    # ---- warm-up, then the timed region (device time, max over ranks) ----------------------
+    for _ in range(max(args.warmup, 3)):
+        ctx.gemm(da, db, dc)
+    ctx.synchronize()
+    sampler = ClockSampler(ranks.local_rank)
+    sampler.start()
+    start_ev, stop_ev = ctx.event(), ctx.event()
+    ranks.barrier()
+    ctx.synchronize()
+    ranks.device_sync()
+    t_begin = time.perf_counter()
+    start_ev.record()
+    for _ in range(args.steps):
+        ctx.gemm(da, db, dc)
+    stop_ev.record()
+    elapsed_ms = stop_ev.elapsed_ms_since(start_ev)
+    ctx.synchronize()
+    ranks.device_sync()
+    t_end = time.perf_counter()
+    ranks.barrier()
+    clocks = sampler.summary(t_begin, t_end)
+    if clocks["samples"] < 3:
+        # The timed region was shorter than the sampling period: keep the same launches
+        # running for half a second more and sample the clocks over that continuation.
+        c_begin = time.perf_counter()
+        while time.perf_counter() - c_begin < 0.5:
+            for _ in range(8):
+                ctx.gemm(da, db, dc)
+            ctx.synchronize()
+        clocks = sampler.summary(c_begin, time.perf_counter())
+        clocks["note"] = "sampled over a 0.5 s continuation of the timed launches"
+    elapsed_ms = ranks.max(elapsed_ms)
+    ms_per_step = elapsed_ms / args.steps
+    value = total_flops / (ms_per_step * 1e-3) / 1e12
+    kernel_tflops = local_flops / (ms_per_step * 1e-3) / 1e12
+
+    # ---- correctness of what was timed (sampled rows, float64 rule) ------------------------
+    c = dc.to_numpy()
+    rows = np.unique(np.linspace(0, m - 1, 16).astype(np.int64))
+    parity = workloads.check_against_float64(c, a, b, rows=rows)
+    parity_all = ranks.gather_objects(parity)
+
+    # ---- end to end through the public handle on pinned host buffers ---------------------
+    e2e_steps = max(1, min(args.steps, args.e2e_steps))
+    pa = cuda.pinned_empty(a.shape, a.dtype)
+    pb = cuda.pinned_empty(b.shape, b.dtype)
+    pc = cuda.pinned_empty((m, local_n), np.float32)
+    pa[...] = a
+    pb[...] = b
+    handle(pa, pb, pc)  # warm-up: allocates the context's staging buffers
+    default_ctx = cuda.default_context(ranks.local_rank)
+    e0, e1 = default_ctx.event(), default_ctx.event()
+    ranks.barrier()
+    default_ctx.synchronize()
+    e0.record()
+    for _ in range(e2e_steps):
+        handle(pa, pb, pc)
+    e1.record()
+    e2e_ms = ranks.max(e1.elapsed_ms_since(e0)) / e2e_steps
+    e2e_ok = bool(np.array_equal(pc[rows], c[rows]))
+    e2e = {"value": total_flops / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_ms,
+           "steps": e2e_steps, "h2d_bytes_per_step": int(a.nbytes + b.nbytes),
+           "d2h_bytes_per_step": int(pc.nbytes), "matches_device_path": e2e_ok,
+           "api": "hc.compile(kernel, target='nvidia-sm100a')(a, b, c) on pinned NumPy arrays"}
+    sampler.stop()
+
+    # ---- optional all-gather of the C slabs (N > 1), reported separately ---------------------
+    gather = None
+    if ranks.world > 1 and not args.no_gather:
+        try:
+            init_communicator(ctx, ranks.world, ranks.rank, ranks.broadcast_bytes)
+            gathered = ctx.empty((ranks.world, m, local_n), np.float32)
+            g0, g1 = ctx.event(), ctx.event()
+            ctx.all_gather(dc, gathered)
+            ctx.synchronize()
+            ranks.barrier()
+            g0.record()
+            for _ in range(3):
+                ctx.all_gather(dc, gathered)
+            g1.record()
+            gather_ms = ranks.max(g1.elapsed_ms_since(g0)) / 3
+            received = (ranks.world - 1) * dc.nbytes
+            gather = {"ms": gather_ms, "bytes_received_per_gpu": int(received),
+                      "gbs_per_gpu": received / (gather_ms * 1e-3) / 1e9, "layout": "slab-major [rank][M][N/ranks]",
+                      "library": "NCCL over NVLink"}
+            ctx.comm_destroy()
+        except Exception as exc:
+            gather = {"error": f"{type(exc).__name__}: {exc}"}
+
+    if ranks.rank != 0:
+        return
+
+    # ---- roofline of the dominant kernel ----------------------------------------------------
+    peaks, peaks_source = measured_peaks()
+    if plan.variant == "skinny":
+        algo_bytes = workloads.algorithmic_bytes(m, local_n, k)
+        achieved = algo_bytes / (ms_per_step * 1e-3) / 1e9
+        peak = float(peaks["hbm_gbs"])
+        roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                    "traffic": NCU_DRAM_TRAFFIC_BYTES.get(name), "kernel": "gemm_skinny_kernel",
+                    "algorithmic_bytes_per_launch": algo_bytes, "peak_source": f"{peaks_source} HBM copy bandwidth",
+                    "frac_of_nominal": achieved / NOMINAL_HBM_GBS}
+    else:
+        long_step = args.steps * ms_per_step > 1000.0
+        peak = float(peaks["bf16_tflops_sustained"] if long_step else peaks["bf16_tflops"])
+        roofline = {"bound": "tensor", "achieved": kernel_tflops, "peak": peak, "unit": "TFLOP/s",
+                    "frac": kernel_tflops / peak, "traffic": NCU_DRAM_TRAFFIC_BYTES.get(name),
+                    "kernel": "gemm_dense_kernel", "flops_per_launch": local_flops,
+                    "peak_source": f"{peaks_source} cuBLAS bf16 8192^3, {'sustained' if long_step else 'burst'}",
+                    "frac_of_sustained_peak": kernel_tflops / float(peaks["bf16_tflops_sustained"]),
+                    "frac_of_nominal": kernel_tflops / NOMINAL_PEAK_TFLOPS}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": ranks.world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "strong" if ranks.world > 1 else "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": name, "m": w.m, "n": w.n, "k": w.k, "input_dtype": w.dtype,
+                   "accumulate": "fp32", "variant": plan.variant, "per_gpu_n": local_n,
+                   "parallelism": f"n-sharded x{ranks.world}" if ranks.world > 1 else "single GPU",
+                   "l2": "inputs larger than L2 (A+B+C per GPU exceed 126 MB)"
+                   if a.nbytes + b.nbytes + c.nbytes > 126e6 else "working set fits L2",
+                   "device": ctx.name, "sm_count": ctx.sm_count},
+        "roofline": roofline,
+        "e2e": e2e,
+        "gpu_launches": args.steps * plan.kernel_launches,
+        "clocks": clocks,
+        "parity": {"rule": "vs float64 product: rel Frobenius <= 1e-3, |err| <= 1e-2*(|A||B|)",
+                   "rows_checked_per_rank": int(len(rows)), "ok": all(p["ok"] for p in parity_all),
+                   "rel_frobenius": max(p["rel_frobenius"] for p in parity_all),
+                   "max_element_ratio": max(p["max_element_ratio"] for p in parity_all)},
+    }
+    if gather is not None:
+        line["all_gather"] = gather
+    if ranks.world == 1 and not args.no_cpu_baseline:
+        baseline = time_cpu_oracle(a, b)
+        baseline["numpy_f32_matmul"] = time_numpy_matmul(a, b)
+        line["cpu_baseline"] = baseline
+    print(json.dumps(line), flush=True)
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=200)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--impl", choices=("b200", "reference"), default="b200")
+    parser.add_argument("--workload", choices=sorted(workloads.CONFIGS), default=None)
+    parser.add_argument("--e2e-steps", type=int, default=5)
+    parser.add_argument("--no-gather", action="store_true")
+    parser.add_argument("--no-cpu-baseline", action="store_true")
+    args = parser.parse_args()
+    if args.steps < 1:
+        parser.error("--steps must be at least 1")
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.gpus > 1 and world == 1 and args.impl != "reference":
+        # Launched without torchrun: start one rank per GPU ourselves.
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--standalone", "--local-addr", "127.0.0.1",
+               "--nnodes=1", f"--nproc-per-node={args.gpus}", str(Path(__file__).resolve()), *sys.argv[1:]]
+        return subprocess.call(cmd)
+
+    ranks = Ranks(connect=args.impl != "reference")  # the CPU arm runs on rank 0 alone
+    try:
+        if args.impl == "reference":
+            run_reference_arm(args, ranks)
+        else:
+            run_gpu_arm(args, ranks)
+    finally:
+        ranks.close()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,128 @@
+"""Python face of the CPU oracle (TEST INFRASTRUCTURE ONLY).
+
+Only `tests/`, `__graft_entry__.smoke()` and the CPU-baseline / reference legs of
+`bench.py` may import this module; the product (`5_b200/`) never does and fails loudly
+when its CUDA library is missing instead of falling back to anything here.
+
+What is restated: the arithmetic of the reference example kernel as its simulator executes
+it (examples/amdgpu_gfx11_wmma_matmul.py:178-190 per-lane multiply-accumulate, :315-326
+k-loop and store; hc/simulator.py:1338-1357 masked loads, :1441-1458 clipped stores):
+
+    C[i, j] = sum over k ascending of fp32(A[i, k]) * fp32(B[k, j]),  fp32 at every step.
+
+Pinning: `tests/test_oracle.py` checks every function here bit-for-bit against fixtures that
+`tests/golden/make_golden.py` produced by running the unmodified reference simulator
+(shapes of the reference's own tests/test_examples.py:22-33 and example main(), config 1 of
+the benchmark, and a bfloat16 twin).
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+from pathlib import Path
+
+import numpy as np
+
+_HERE = Path(__file__).resolve().parent
+_LIB_PATH = _HERE / "_build" / "libhc_oracle.so"
+_LIB: ctypes.CDLL | None = None
+
+F16 = 0
+BF16 = 1
+
+
+def build(force: bool = False) -> Path:
+    """Compiles hc_matmul_oracle.c with the Makefile beside it (gcc, seconds)."""
+    if force or not _LIB_PATH.exists() or (
+        _LIB_PATH.stat().st_mtime < (_HERE / "hc_matmul_oracle.c").stat().st_mtime
+    ):
+        env = dict(os.environ)
+        env.setdefault("CC", "gcc")
+        subprocess.run(["make", "-C", str(_HERE), "-B" if force else "-s"], check=True, env=env)
+    return _LIB_PATH
+
+
+def load() -> ctypes.CDLL:
+    global _LIB
+    if _LIB is None:
+        if not _LIB_PATH.exists():
+            build()
+        lib = ctypes.CDLL(str(_LIB_PATH))
+        i64, vp, ci = ctypes.c_int64, ctypes.c_void_p, ctypes.c_int
+        lib.hc_oracle_matmul.argtypes = [vp, i64, vp, i64, vp, i64, i64, i64, i64, ci, ci]
+        lib.hc_oracle_matmul.restype = ci
+        lib.hc_oracle_matmul_rows.argtypes = [vp, i64, vp, i64, vp, i64, i64, i64, i64, ci, i64, i64, ci]
+        lib.hc_oracle_matmul_rows.restype = ci
+        lib.hc_oracle_matmul_tiled.argtypes = [vp, i64, vp, i64, vp, i64, i64, i64, i64, ci]
+        lib.hc_oracle_matmul_tiled.restype = ci
+        lib.hc_oracle_max_threads.restype = ci
+        _LIB = lib
+    return _LIB
+
+
+def max_threads() -> int:
+    return int(load().hc_oracle_max_threads())
+
+
+def dtype_code(dtype: np.dtype) -> int:
+    name = np.dtype(dtype).name
+    if name == "float16":
+        return F16
+    if name == "bfloat16":
+        return BF16
+    raise ValueError(f"the oracle handles float16 and bfloat16 inputs, got {name}")
+
+
+def _as_bits(x: np.ndarray) -> np.ndarray:
+    if x.ndim != 2:
+        raise ValueError("the oracle expects rank-2 matrices")
+    return np.ascontiguousarray(x).view(np.uint16)
+
+
+def _check(a: np.ndarray, b: np.ndarray) -> tuple[int, int, int, int]:
+    if a.ndim != 2 or b.ndim != 2 or a.shape[1] != b.shape[0]:
+        raise ValueError(f"shape mismatch: A {a.shape}, B {b.shape}")
+    if a.dtype != b.dtype:
+        raise ValueError("A and B must have the same dtype")
+    return a.shape[0], b.shape[1], a.shape[1], dtype_code(a.dtype)
+
+
+def matmul_k_ascending(a: np.ndarray, b: np.ndarray, *, threads: int = 0,
+                       rows: tuple[int, int] | None = None) -> np.ndarray:
+    """k-ascending fp32 product via the C restatement (fast form).
+
+    With `rows=(r0, r1)` only those rows of C are computed (the others are left 0), which
+    bounds the CPU time on large problems.
+    """
+    m, n, k, code = _check(a, b)
+    abits, bbits = _as_bits(a), _as_bits(b)
+    c = np.zeros((m, n), np.float32)
+    r0, r1 = (0, m) if rows is None else rows
+    rc = load().hc_oracle_matmul_rows(abits.ctypes.data, max(k, 1), bbits.ctypes.data, max(n, 1),
+                                      c.ctypes.data, max(n, 1), m, n, k, code, r0, r1, threads)
+    if rc != 0:
+        raise MemoryError("the oracle could not allocate its widened copy of B")
+    return c
+
+
+def matmul_tiled(a: np.ndarray, b: np.ndarray) -> np.ndarray:
+    """Literal workgroup / k-step / lane restatement (slow; small shapes)."""
+    m, n, k, code = _check(a, b)
+    abits, bbits = _as_bits(a), _as_bits(b)
+    c = np.zeros((m, n), np.float32)
+    load().hc_oracle_matmul_tiled(abits.ctypes.data, max(k, 1), bbits.ctypes.data, max(n, 1),
+                                  c.ctypes.data, max(n, 1), m, n, k, code)
+    return c
+
+
+def matmul_numpy(a: np.ndarray, b: np.ndarray) -> np.ndarray:
+    """The same arithmetic in NumPy: one fp32 rank-1 update per k, k ascending."""
+    m, n, k, _ = _check(a, b)
+    a32 = a.astype(np.float32)
+    b32 = b.astype(np.float32)
+    c = np.zeros((m, n), np.float32)
+    for kk in range(k):
+        c += a32[:, kk : kk + 1] * b32[kk : kk + 1, :]
+    return c

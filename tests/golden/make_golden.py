@@ -1,0 +1,107 @@
+"""Generates tests/golden/*.npz by running the UNMODIFIED reference simulator.
+
+    python tests/golden/make_golden.py [--reference /path/to/reference]
+
+The reference (a Python package) is imported from its own checkout; nothing of it is copied
+here. Its two absent third-party dependencies are replaced by the stand-ins under
+oracle/standins/ (an integer-expression evaluator for launch shapes, and run-to-completion
+coroutines); neither carries any of the matmul arithmetic. Each fixture stores the inputs as
+raw 16-bit patterns and the simulator's fp32 output, so the parity tests need neither the
+reference nor the stand-ins.
+
+Fixtures (all produced by `hc.simulator.launch` on the example kernel):
+  sim_f16_m16_n16_k16_seed7, sim_f16_m32_n32_k32_seed7, sim_f16_m17_n19_k18_seed7
+      the three shapes of the reference's tests/test_examples.py:22-33, inputs from its
+      make_demo_inputs (uniform(-1, 1), seed 7)
+  sim_f16_m32_n32_k32_seed0
+      the example's own main() (examples/amdgpu_gfx11_wmma_matmul.py:438-441)
+  sim_f16_m64_n64_k64_normal_seed0
+      benchmark config 1: A, B ~ N(0, 1) from default_rng(0), A drawn first
+  sim_bf16_m33_n17_k40_seed5
+      a bfloat16 twin of the kernel: the example's source with its element type replaced,
+      executed in memory by the same simulator
+The file blocked_reference.npz holds `reference_blocked_matmul` of the first four (the
+reference test's own comparison value, atol 2e-6).
+"""
+
+from __future__ import annotations
+
+import argparse
+import importlib
+import os
+import sys
+import types
+from pathlib import Path
+
+import numpy as np
+
+HERE = Path(__file__).resolve().parent
+REPO = HERE.parent.parent
+
+
+def _import_reference(reference: Path):
+    os.environ["HC_IXSIMPL_VENDOR_DIR"] = str(REPO / "oracle" / "standins" / "ixsimpl_vendor")
+    sys.path.insert(0, str(REPO / "oracle" / "standins"))
+    sys.path.insert(0, str(reference))
+    return importlib.import_module("examples.amdgpu_gfx11_wmma_matmul")
+
+
+def _bf16_twin(example_module):
+    """The example kernel with bfloat16 operands, built from its source text in memory."""
+    import ml_dtypes
+
+    source = Path(example_module.__file__).read_text(encoding="utf-8")
+    source = source.replace("np.float16", "BF16")
+    twin = types.ModuleType("examples.amdgpu_gfx11_wmma_matmul_bf16")
+    twin.__file__ = example_module.__file__
+    twin.__dict__["BF16"] = ml_dtypes.bfloat16
+    sys.modules[twin.__name__] = twin
+    exec(compile(source, example_module.__file__, "exec"), twin.__dict__)
+    return twin
+
+
+def _save(name: str, a: np.ndarray, b: np.ndarray, c: np.ndarray) -> None:
+    np.savez_compressed(
+        HERE / f"{name}.npz",
+        a_bits=a.view(np.uint16),
+        b_bits=b.view(np.uint16),
+        c=c,
+        dtype=np.array(a.dtype.name),
+    )
+    print(f"{name}: A{a.shape} B{b.shape} -> C{c.shape}", flush=True)
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--reference", default="/root/reference")
+    args = parser.parse_args()
+    ex = _import_reference(Path(args.reference))
+
+    blocked = {}
+    for m, n, k, seed in [(16, 16, 16, 7), (32, 32, 32, 7), (17, 19, 18, 7), (32, 32, 32, 0)]:
+        a, b = ex.make_demo_inputs(m=m, n=n, k=k, seed=seed)
+        c = ex.simulate_gfx11_wmma_matmul(a, b)
+        name = f"sim_f16_m{m}_n{n}_k{k}_seed{seed}"
+        _save(name, a, b, c)
+        blocked[name] = ex.reference_blocked_matmul(a, b)
+    np.savez_compressed(HERE / "blocked_reference.npz", **blocked)
+
+    rng = np.random.default_rng(0)
+    a = rng.standard_normal((64, 64)).astype(np.float16)
+    b = rng.standard_normal((64, 64)).astype(np.float16)
+    _save("sim_f16_m64_n64_k64_normal_seed0", a, b, ex.simulate_gfx11_wmma_matmul(a, b))
+
+    import ml_dtypes
+
+    twin = _bf16_twin(ex)
+    rng = np.random.default_rng(5)
+    a = rng.uniform(-1.0, 1.0, size=(33, 40)).astype(ml_dtypes.bfloat16)
+    b = rng.uniform(-1.0, 1.0, size=(40, 17)).astype(ml_dtypes.bfloat16)
+    c = np.zeros((33, 17), np.float32)
+    twin.sim.launch(twin.tiled_gfx11_wmma_matmul, a, b, c)
+    _save("sim_bf16_m33_n17_k40_seed5", a, b, c)
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

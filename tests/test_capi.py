@@ -1,0 +1,134 @@
+"""The C ABI on a machine without a GPU: the library loads, exports every declared symbol,
+and its host-side validation / planning behaves. No compute call is made here."""
+
+from __future__ import annotations
+
+import ctypes
+import re
+
+import pytest
+
+from conftest import REPO
+from hc import cuda
+from hc.errors import DeviceError
+
+HEADER = REPO / "include" / "hc-c" / "Cuda.h"
+
+
+def _declared_functions() -> list[str]:
+    text = HEADER.read_text(encoding="utf-8")
+    return re.findall(r"HC_CUDA_CAPI_EXPORTED\s+[\w\s\*]+?\b(hcCuda\w+)\s*\(", text)
+
+
+def test_library_exports_every_declared_symbol() -> None:
+    lib = cuda.library()
+    declared = _declared_functions()
+    assert len(declared) >= 28 and len(set(declared)) == len(declared)
+    for name in declared:
+        assert hasattr(lib, name), f"{name} is declared in hc-c/Cuda.h but not exported"
+    assert set(declared) == set(cuda.EXPORTS)
+    assert lib.hcCudaApiVersion() == 1
+
+
+def test_every_declaration_cites_or_describes_its_reference_counterpart() -> None:
+    text = HEADER.read_text(encoding="utf-8")
+    for anchor in ("hc/_compile.py:57-62", "hc/simulator.py:165-186", "hc/simulator.py:752-768",
+                   "include/hc-c/HC.h", "lib/CAPI/HC.cpp:22-29"):
+        assert anchor in text
+
+
+def test_status_strings() -> None:
+    lib = cuda.library()
+    assert lib.hcCudaStatusString(0) == b"HC_CUDA_OK"
+    assert lib.hcCudaStatusString(5) == b"HC_CUDA_ERR_DEVICE_TIMEOUT"
+    assert lib.hcCudaStatusString(99) == b"HC_CUDA_ERR_UNKNOWN"
+
+
+def test_missing_device_is_reported_not_papered_over() -> None:
+    if cuda.device_count() > 0:
+        pytest.skip("a GPU is present")
+    with pytest.raises(DeviceError, match="HC_CUDA_ERR_NO_DEVICE"):
+        cuda.Context(0)
+    lib = cuda.library()
+    assert lib.hcCudaContextCreate(0, None) == 1  # null out-pointer
+    assert lib.hcCudaContextSynchronize(None) == 1
+    assert lib.hcCudaGemm(None, None) == 1
+
+
+def test_plan_chooses_variants() -> None:
+    dense = cuda.plan_gemm(8192, 8192, 8192, "float16")
+    assert (dense.variant, dense.tiles_m, dense.tiles_n, dense.grid, dense.splits) == ("dense", 64, 32, 148, 1)
+    assert dense.kernel_launches == 1 and dense.scratch_bytes == 0 and not dense.repack_a
+    small = cuda.plan_gemm(100, 300, 64, "bfloat16")
+    assert (small.variant, small.tiles_m, small.tiles_n, small.grid) == ("dense", 1, 2, 2)
+    skinny = cuda.plan_gemm(8, 16384, 8192, "float16")
+    assert skinny.variant == "skinny" and skinny.tiles_n == 128 and skinny.splits >= 2
+    assert skinny.grid <= 296 and skinny.scratch_bytes == skinny.splits * 8 * 16384 * 4
+    assert cuda.plan_gemm(64, 512, 512, "float16").variant == "skinny"
+    assert cuda.plan_gemm(65, 512, 512, "float16").variant == "dense"
+    assert cuda.plan_gemm(8, 512, 512, "float16", variant=cuda.VARIANT_DENSE).variant == "dense"
+    assert cuda.plan_gemm(8, 128, 64, "float16", variant=cuda.VARIANT_SKINNY).splits == 1
+
+
+def test_plan_flags_pitches_that_need_a_repack() -> None:
+    ragged = cuda.plan_gemm(4095, 3073, 1031, "bfloat16")
+    assert ragged.variant == "dense" and ragged.repack_a and ragged.repack_b and ragged.kernel_launches == 3
+    assert (ragged.tiles_m, ragged.tiles_n) == (32, 13)
+    assert ragged.scratch_bytes >= 4095 * 1032 * 2 + 1031 * 3080 * 2
+    padded = cuda.plan_gemm(4095, 3073, 1031, "bfloat16", lda=1032, ldb=3080)
+    assert not padded.repack_a and not padded.repack_b and padded.kernel_launches == 1
+    misaligned_base = cuda.plan_gemm(128, 256, 64, "float16", a=0x1002)
+    assert misaligned_base.repack_a and not misaligned_base.repack_b
+
+
+def test_plan_degenerate_shapes() -> None:
+    assert cuda.plan_gemm(0, 5, 7, "float16").variant == "noop"
+    assert cuda.plan_gemm(5, 0, 7, "float16").kernel_launches == 0
+    zero_k = cuda.plan_gemm(5, 6, 0, "float16")
+    assert zero_k.variant == "zero_fill" and zero_k.kernel_launches == 0
+
+
+@pytest.mark.parametrize(
+    ("kwargs", "status", "message"),
+    [
+        ({"m": -1}, "INVALID_ARGUMENT", "non-negative"),
+        ({"m": (1 << 30) + 1}, "UNSUPPORTED", "at most 2\\^30"),
+        ({"a": 0}, "INVALID_ARGUMENT", "a and b must not be null"),
+        ({"c": 0}, "INVALID_ARGUMENT", "c must not be null"),
+        ({"c": 0x80000002}, "INVALID_ARGUMENT", "4-byte aligned"),
+        ({"b": 0x40000001}, "INVALID_ARGUMENT", "2-byte aligned"),
+        ({"lda": 63}, "INVALID_ARGUMENT", "lda \\(63\\) must be at least k \\(64\\)"),
+        ({"ldb": 10}, "INVALID_ARGUMENT", "ldb"),
+        ({"ldc": 10}, "INVALID_ARGUMENT", "ldc"),
+        ({"c": 0x1000}, "INVALID_ARGUMENT", "must not overlap"),
+        ({"c": 0x40000000 + 64}, "INVALID_ARGUMENT", "must not overlap"),
+        ({"variant": 7}, "INVALID_ARGUMENT", "variant must be"),
+        ({"m": 65, "variant": cuda.VARIANT_SKINNY}, "UNSUPPORTED", "skinny variant needs m <= 64"),
+    ],
+)
+def test_plan_rejects_bad_arguments(kwargs: dict, status: str, message: str) -> None:
+    args = {"m": 128, "n": 256, "k": 64, "dtype": "float16"}
+    args.update(kwargs)
+    with pytest.raises(DeviceError, match=message) as info:
+        cuda.plan_gemm(args.pop("m"), args.pop("n"), args.pop("k"), args.pop("dtype"), **args)
+    assert info.value.status_name == f"HC_CUDA_ERR_{status}"
+
+
+def test_plan_rejects_unknown_dtype_code() -> None:
+    lib = cuda.library()
+    args = cuda._GemmArgs(1, 1, 1, 5, 0, 0x1000, 1, 0x2000, 1, 0x3000, 1)
+    info = cuda._PlanInfo()
+    assert lib.hcCudaGemmPlan(ctypes.byref(args), 148, ctypes.byref(info)) == 1
+    assert b"dtype" in lib.hcCudaContextLastError(None)
+    assert lib.hcCudaGemmPlan(None, 148, ctypes.byref(info)) == 1
+    with pytest.raises(ValueError):
+        cuda.plan_gemm(1, 1, 1, "float32")
+
+
+def test_comm_entry_points_validate_before_touching_nccl() -> None:
+    lib = cuda.library()
+    assert lib.hcCudaCommGetUniqueId(None, 128) == 1
+    buf = ctypes.create_string_buffer(16)
+    assert lib.hcCudaCommGetUniqueId(buf, 16) == 1
+    assert lib.hcCudaCommAllGather(None, None, None, 0) == 1
+    assert lib.hcCudaCommInitRank(None, buf, 16, 2, 0) == 1

@@ -1,0 +1,249 @@
+"""`hc.compile(..., target="nvidia-sm100a")`: argument checks, kernel recognition, launch binding."""
+
+import subprocess
+import sys
+import os
+
+import numpy as np
+import pytest
+
+import hc
+from hc import Buffer, WorkGroup, WorkItem, idx_type, kernel, sym, tensor_type, undef_type, vector_type
+from hc._pipeline import NVIDIA_SM100A, known_targets, recognise_tiled_matmul
+from hc.symbols import ceil_div
+
+from conftest import REFERENCE, REPO
+from examples.b200_wmma_matmul import compiled_for, tiled_wmma_matmul_for
+
+M, N, K = sym.M, sym.N, sym.K
+
+
+def _family(*, tile=(16, 16, 16), wave=32, acc=8, in_dtype=np.float16, out_dtype=np.float32,
+            effects="pure", k_step=None, work_shape=None, loop=True, b_dims=None):
+    """A matmul kernel of the example's family with one aspect varied."""
+    tm, tn, tk = tile
+    step = tk if k_step is None else k_step
+
+    @kernel.intrinsic(
+        scope=WorkItem, effects=effects, const_attrs={"wave_size", "arch"},
+        operand_types=(undef_type(), tensor_type((tm, tk), in_dtype), tensor_type((tk, tn), in_dtype),
+                       vector_type((tk,), in_dtype), vector_type((tk,), in_dtype),
+                       vector_type((acc,), np.float32), idx_type()),
+        result_types=(vector_type((acc,), np.float32),))
+    def mma(group, a_tile, b_tile, a_frag, b_frag, acc_frag, *, lane, wave_size, arch):
+        return acc_frag
+
+    @kernel.func(scope=WorkGroup)
+    def step_fn(group, a_tile, b_tile, acc):
+        return mma(group, a_tile, b_tile, None, None, acc, lane=0, wave_size=wave, arch="x")
+
+    @kernel.func(scope=WorkGroup)
+    def store(group, c, acc):
+        group.store(c, acc)
+
+    shape = work_shape if work_shape is not None else (ceil_div(M, tm) * wave, ceil_div(N, tn))
+    bd = b_dims if b_dims is not None else (K, N)
+
+    if loop:
+        @kernel(work_shape=shape, group_shape=(wave, 1), subgroup_size=wave)
+        def matmul(group, a: Buffer[M, K, in_dtype], b: Buffer[bd[0], bd[1], in_dtype],
+                   c: Buffer[M, N, out_dtype]) -> None:
+            acc = 0
+            for k0 in range(0, a.shape[1], step):
+                a_tile = group.load(a[0:tm, k0 : k0 + tk], shape=(tm, tk))
+                b_tile = group.load(b[k0 : k0 + tk, 0:tn], shape=(tk, tn))
+                acc = step_fn(group, a_tile, b_tile, acc)
+            store(group, c, acc)
+    else:
+        @kernel(work_shape=shape, group_shape=(wave, 1), subgroup_size=wave)
+        def matmul(group, a: Buffer[M, K, in_dtype], b: Buffer[bd[0], bd[1], in_dtype],
+                   c: Buffer[M, N, out_dtype]) -> None:
+            a_tile = group.load(a[0:tm, 0:tk], shape=(tm, tk))
+            b_tile = group.load(b[0:tk, 0:tn], shape=(tk, tn))
+            store(group, c, step_fn(group, a_tile, b_tile, 0))
+
+    return matmul
+
+
+# ---------------------------------------------------------------- compile() arguments ----
+
+
+def test_compile_rejects_non_kernels_and_bad_symbols() -> None:
+    with pytest.raises(TypeError, match="@kernel-decorated"):
+        hc.compile(lambda group: None)
+    kern = tiled_wmma_matmul_for("float16")
+    with pytest.raises(TypeError, match="symbols must be a Mapping"):
+        hc.compile(kern, [("M", 1)])
+    with pytest.raises(TypeError, match="must bind to an int"):
+        hc.compile(kern, {"M": 1.5})
+    with pytest.raises(TypeError, match="must bind to an int"):
+        hc.compile(kern, {"M": True})
+    with pytest.raises(ValueError, match="bound twice with conflicting"):
+        hc.compile(kern, {"M": 1, sym.M: 2})
+    with pytest.raises(TypeError, match="cannot interpret"):
+        hc.compile(kern, {3: 1})
+    with pytest.raises(ValueError, match="unknown hc.compile target"):
+        hc.compile(kern, target="amdgpu-gfx11")
+
+    @kernel(work_shape=(M,), literals={M})
+    def with_literals(group) -> None:
+        pass
+
+    with pytest.raises(ValueError, match="'N' is not a declared literal symbol"):
+        hc.compile(with_literals, {"N": 1})
+    assert hc.compile(with_literals, {"M": 4, sym.M: 4}).bindings == {"M": 4}
+
+
+def test_handle_fields_and_repr() -> None:
+    kern = tiled_wmma_matmul_for("float16")
+    plain = hc.compile(kern, {"K": 64})
+    assert plain.kernel is kern and plain.bindings == {"K": 64}
+    assert plain.front_ir is None and plain.hc_ir is None and plain.hc_ir_text is None
+    assert any("MLIR" in d for d in plain.pipeline_diagnostics)
+    assert repr(plain) == "CompiledKernel(tiled_wmma_matmul_float16, {K=64}, stage=hc_front)"
+    with pytest.raises(NotImplementedError, match="without a target"):
+        plain(None, None, None)
+    with pytest.raises(Exception):
+        plain.target = "x"  # frozen
+    handle = hc.compile(kern, target=NVIDIA_SM100A, schedule="module {}")
+    assert handle.schedule == "module {}" and handle.target in known_targets()
+    assert repr(handle).endswith("stage=nvidia-sm100a)")
+
+
+# ---------------------------------------------------------------- recognition -----------
+
+
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+def test_example_kernel_is_recognised(dtype: str) -> None:
+    plan = compiled_for(dtype).plan
+    assert plan is not None
+    assert (plan.a_param, plan.b_param, plan.c_param) == ("a", "b", "c")
+    assert (plan.m_dim, plan.n_dim, plan.k_dim) == ("M", "N", "K")
+    assert plan.input_dtype == dtype and plan.output_dtype == "float32"
+    assert plan.tile == (16, 16, 16) and plan.wave_size == 32 and plan.accumulators_per_lane == 8
+    assert plan.intrinsic_name == "wmma_16x16x16" and plan.has_target_lowering
+    assert plan.intrinsic_const_attrs == ("arch", "wave_size")
+
+
+def test_family_members_are_recognised() -> None:
+    for kwargs in ({}, {"in_dtype": __import__("ml_dtypes").bfloat16}, {"tile": (32, 16, 16), "acc": 16},
+                   {"tile": (16, 16, 32)}, {"wave": 64, "acc": 4}):
+        plan, diagnostics = recognise_tiled_matmul(_family(**kwargs))
+        assert plan is not None, diagnostics
+        assert plan.tile == kwargs.get("tile", (16, 16, 16))
+
+
+@pytest.mark.parametrize(
+    ("kwargs", "message"),
+    [
+        ({"in_dtype": np.float32}, "are not a\\[M,K\\], b\\[K,N\\]"),
+        ({"out_dtype": np.float16}, "c\\[M,N\\] float32"),
+        ({"b_dims": (N, K)}, "are not a\\[M,K\\], b\\[K,N\\]"),
+        ({"effects": "write"}, "expected 'pure'"),
+        ({"acc": 4}, "accumulator values per lane"),
+        ({"k_step": 8}, "k-loop must be"),
+        ({"loop": False}, "exactly one k-loop"),
+        ({"work_shape": (ceil_div(M, 16) * 32, ceil_div(N, 32))}, "work_shape evaluates to"),
+        ({"work_shape": (M, N, K)}, "work_shape must be a pair"),
+    ],
+)
+def test_other_kernels_are_refused_with_a_reason(kwargs: dict, message: str) -> None:
+    kern = _family(**kwargs)
+    handle = hc.compile(kern, target=NVIDIA_SM100A)
+    assert handle.plan is None
+    assert any(__import__("re").search(message, d) for d in handle.pipeline_diagnostics), handle.pipeline_diagnostics
+    assert "unsupported" in repr(handle)
+    with pytest.raises(NotImplementedError, match="cannot launch"):
+        handle(np.zeros((1, 1), np.float16), np.zeros((1, 1), np.float16), np.zeros((1, 1), np.float32))
+
+
+def test_kernel_without_intrinsic_is_refused() -> None:
+    @kernel(work_shape=(ceil_div(M, 16) * 32, ceil_div(N, 16)), group_shape=(32, 1), subgroup_size=32)
+    def plain(group, a: Buffer[M, K, np.float16], b: Buffer[K, N, np.float16], c: Buffer[M, N, np.float32]) -> None:
+        pass
+
+    plan, diagnostics = recognise_tiled_matmul(plain)
+    assert plan is None and "no @kernel.intrinsic is reachable" in diagnostics[0]
+
+
+# ---------------------------------------------------------------- launch binding --------
+
+
+def _buffers(m: int, n: int, k: int, dtype=np.float16):
+    return np.zeros((m, k), dtype), np.zeros((k, n), dtype), np.zeros((m, n), np.float32)
+
+
+def test_prepare_binds_symbols_and_geometry() -> None:
+    handle = compiled_for("float16")
+    launch = handle.prepare(*_buffers(17, 19, 18))
+    assert launch.symbols == {"M": 17, "K": 18, "N": 19}
+    assert launch.work_shape == (64, 2) and launch.group_shape == (32, 1) and launch.subgroup_size == 32
+    assert launch.group_counts == (2, 2) and not launch.is_empty
+    a, b, c = _buffers(4, 5, 6)
+    assert handle.prepare(a, c=c, b=b).symbols == {"M": 4, "K": 6, "N": 5}
+
+
+def test_launch_errors_use_the_simulator_messages() -> None:
+    handle = compiled_for("float16")
+    a, b, c = _buffers(16, 16, 16)
+    cases = [
+        ((a.tolist(), b, c), "a must be a numpy.ndarray buffer"),
+        ((a[0], b, c), "a rank does not match its Buffer annotation"),
+        ((a, b.astype(np.float32), c), "b dtype expected float16, got float32"),
+        ((a, b, c.astype(np.float64)), "c dtype expected float32, got float64"),
+        ((a, np.zeros((17, 16), np.float16), c), "conflicting binding for K: 16 from 'a.shape\\[1\\]' vs 17 from 'b.shape\\[0\\]'"),
+        ((a, b, np.zeros((16, 15), np.float32)), "conflicting binding for N"),
+        ((a, b), "missing a required argument: 'c'"),
+    ]
+    for args, message in cases:
+        with pytest.raises(hc.LaunchError, match=message):
+            handle(*args)
+    assert issubclass(hc.LaunchError, hc.SimulatorError)
+
+
+def test_compile_time_symbols_constrain_every_call() -> None:
+    handle = hc.compile(tiled_wmma_matmul_for("float16"), {"K": 32}, target=NVIDIA_SM100A)
+    assert handle.prepare(*_buffers(8, 8, 32)).symbols["K"] == 32
+    with pytest.raises(hc.LaunchError, match="conflicting binding for K: 32 from 'hc.compile\\(symbols=...\\)' vs 16"):
+        handle(*_buffers(8, 8, 16))
+
+
+def test_zero_sized_work_is_a_no_op_without_a_device() -> None:
+    handle = compiled_for("float16")
+    for shape in ((0, 5, 7), (5, 0, 7)):
+        a, b, c = _buffers(*shape)
+        assert handle.prepare(a, b, c).is_empty
+        assert handle(a, b, c) is None  # returns before any CUDA library is touched
+
+
+@pytest.mark.skipif(not REFERENCE.exists(), reason="the reference checkout is not on this machine")
+def test_the_reference_kernel_object_is_accepted_unchanged() -> None:
+    """The decorated kernel of the reference's own example (made with the reference's `hc`)
+    compiles for the NVIDIA target of this package: the drop-in is by duck typing."""
+    script = r"""
+import importlib.util, sys
+import numpy as np
+from examples.amdgpu_gfx11_wmma_matmul import tiled_gfx11_wmma_matmul
+spec = importlib.util.spec_from_file_location("hc_b200", sys.argv[1] + "/__init__.py", submodule_search_locations=[sys.argv[1]])
+ours = importlib.util.module_from_spec(spec); sys.modules["hc_b200"] = ours; spec.loader.exec_module(ours)
+handle = ours.compile(tiled_gfx11_wmma_matmul, target="nvidia-sm100a")
+plan = handle.plan
+assert plan is not None, handle.pipeline_diagnostics
+assert (plan.tile, plan.wave_size, plan.input_dtype, plan.intrinsic_name) == ((16, 16, 16), 32, "float16", "wmma_gfx11")
+launch = handle.prepare(np.zeros((17, 18), np.float16), np.zeros((18, 19), np.float16), np.zeros((17, 19), np.float32))
+assert launch.symbols == {"M": 17, "K": 18, "N": 19} and launch.work_shape == (64, 2)
+try:
+    handle.prepare(np.zeros((17, 18), np.float16), np.zeros((17, 19), np.float16), np.zeros((17, 19), np.float32))
+except ours.LaunchError as exc:
+    assert "conflicting binding for K" in str(exc)
+else:
+    raise AssertionError("conflict not detected")
+print("ok")
+"""
+    env = dict(os.environ)
+    env["HC_IXSIMPL_VENDOR_DIR"] = str(REPO / "oracle" / "standins" / "ixsimpl_vendor")
+    env["PYTHONPATH"] = os.pathsep.join([str(REFERENCE), str(REPO / "oracle" / "standins")])
+    result = subprocess.run([sys.executable, "-c", script, str(REPO / "5_b200" / "hc")], env=env,
+                            capture_output=True, text=True, timeout=120, cwd=str(REPO / "tests"))
+    assert result.returncode == 0, result.stderr
+    assert result.stdout.strip() == "ok"

@@ -1,0 +1,320 @@
+"""Parity of the CUDA path with the oracle, on a B200. Everything goes through the public
+surface (`hc.compile(..., target="nvidia-sm100a")` handle or `hc.cuda`), i.e. the C ABI.
+
+Tolerance (tensor cores add in a different order than the oracle's k-ascending fp32 chain, so
+bit equality is not expected): versus a float64 product of the same low-precision inputs,
+relative Frobenius error <= 1e-3 and |C - ref| <= 1e-2 * (|A| |B|) element-wise. Versus the
+oracle / the reference simulator's stored output the same bound is applied with the oracle in
+place of the float64 product.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+
+import hc
+import workloads
+from conftest import GOLDEN_NAMES, load_golden, np_dtype
+from examples.b200_wmma_matmul import compiled_for, gpu_wmma_matmul
+from hc import cuda
+from oracle import cpu_ref
+
+pytestmark = pytest.mark.gpu
+
+REL_FROBENIUS = 1e-3
+ELEMENT_RATIO = 1e-2
+
+
+def assert_close_to_oracle(c: np.ndarray, a: np.ndarray, b: np.ndarray, expect: np.ndarray | None = None) -> None:
+    expect = cpu_ref.matmul_k_ascending(a, b) if expect is None else expect
+    assert c.shape == expect.shape and c.dtype == np.float32
+    assert np.isfinite(c).all()
+    bound = np.abs(a.astype(np.float64)) @ np.abs(b.astype(np.float64))
+    diff = np.abs(c.astype(np.float64) - expect.astype(np.float64))
+    assert (diff <= ELEMENT_RATIO * bound + 1e-30).all(), float((diff / np.maximum(bound, 1e-30)).max())
+    norm = np.linalg.norm(expect.astype(np.float64))
+    assert np.linalg.norm(diff) <= REL_FROBENIUS * max(norm, 1e-30)
+    assert workloads.check_against_float64(c, a, b)["ok"]
+
+
+def random_inputs(m: int, n: int, k: int, dtype: str, seed: int = 0, scale: float = 1.0):
+    rng = np.random.default_rng([seed, m, n, k])
+    a = (rng.standard_normal((m, k)) * scale).astype(np_dtype(dtype))
+    b = (rng.standard_normal((k, n)) * scale).astype(np_dtype(dtype))
+    return a, b
+
+
+# ---------------------------------------------------------------- golden vectors --------
+
+
+@pytest.mark.parametrize("name", GOLDEN_NAMES)
+def test_handle_matches_reference_simulator_output(name: str) -> None:
+    a, b, c_sim = load_golden(name)
+    c = np.full(c_sim.shape, np.nan, np.float32)
+    handle = compiled_for(a.dtype.name)
+    assert handle(a, b, c) is None
+    assert_close_to_oracle(c, a, b, expect=c_sim)
+
+
+def test_reference_tests_own_tolerance_on_its_shapes() -> None:
+    # tests/test_examples.py:22-33 of the reference uses atol=2e-6 against its blocked product;
+    # the tensor-core result stays inside 1e-5 of it at these sizes (K <= 32, |values| <= 1).
+    with np.load(load_golden.__globals__["GOLDEN"] / "blocked_reference.npz") as blocked:
+        for name in blocked.files:
+            a, b, _ = load_golden(name)
+            np.testing.assert_allclose(gpu_wmma_matmul(a, b), blocked[name], rtol=0.0, atol=1e-5)
+
+
+# ---------------------------------------------------------------- shape ladder ----------
+
+DENSE_SHAPES = [
+    (65, 1, 1), (65, 17, 3), (128, 256, 64), (128, 256, 16), (129, 257, 65), (127, 255, 63),
+    (200, 200, 8), (256, 512, 200), (300, 520, 1000), (1024, 96, 130), (65, 3000, 100), (2048, 2048, 512),
+]
+
+
+@pytest.mark.parametrize("shape", DENSE_SHAPES)
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+def test_dense_ladder(shape: tuple[int, int, int], dtype: str) -> None:
+    m, n, k = shape
+    a, b = random_inputs(m, n, k, dtype)
+    assert cuda.plan_gemm(m, n, k, dtype).variant == "dense"
+    assert_close_to_oracle(gpu_wmma_matmul(a, b), a, b)
+
+
+SKINNY_SHAPES = [
+    (1, 1, 1), (1, 128, 64), (8, 128, 64), (8, 129, 65), (7, 1000, 777), (16, 640, 4096), (17, 640, 1024),
+    (32, 255, 300), (33, 512, 2048), (64, 3000, 520), (8, 4096, 8192), (3, 100, 16384),
+]
+
+
+@pytest.mark.parametrize("shape", SKINNY_SHAPES)
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+def test_skinny_ladder(shape: tuple[int, int, int], dtype: str) -> None:
+    m, n, k = shape
+    a, b = random_inputs(m, n, k, dtype, scale=0.25)
+    assert cuda.plan_gemm(m, n, k, dtype).variant == "skinny"
+    assert_close_to_oracle(gpu_wmma_matmul(a, b), a, b)
+
+
+def test_skinny_split_k_is_deterministic(gpu_ctx) -> None:
+    a, b = random_inputs(8, 2048, 8192, "float16", scale=0.1)
+    assert gpu_ctx.plan(8, 2048, 8192, "float16").splits > 1
+    first = gpu_wmma_matmul(a, b)
+    for _ in range(5):
+        assert np.array_equal(first, gpu_wmma_matmul(a, b))
+
+
+def test_forced_variants_agree(gpu_ctx) -> None:
+    a, b = random_inputs(48, 700, 900, "float16")
+    da, db = gpu_ctx.to_device(a), gpu_ctx.to_device(b)
+    outs = []
+    for variant in (cuda.VARIANT_DENSE, cuda.VARIANT_SKINNY):
+        dc = gpu_ctx.empty((48, 700), np.float32)
+        dc.fill_bytes(0xFF)
+        gpu_ctx.gemm(da, db, dc, variant=variant)
+        gpu_ctx.synchronize()
+        outs.append(dc.to_numpy())
+        assert_close_to_oracle(outs[-1], a, b)
+    assert np.allclose(outs[0], outs[1], rtol=0, atol=1e-3)
+
+
+# ---------------------------------------------------------------- edges ------------------
+
+
+def test_zero_k_writes_zeros_and_empty_shapes_write_nothing() -> None:
+    handle = compiled_for("float16")
+    c = np.full((5, 7), 3.0, np.float32)
+    handle(np.zeros((5, 0), np.float16), np.zeros((0, 7), np.float16), c)
+    assert not c.any()
+    c = np.full((0, 7), 3.0, np.float32)
+    handle(np.zeros((0, 4), np.float16), np.zeros((4, 7), np.float16), c)
+    c = np.full((5, 0), 3.0, np.float32)
+    handle(np.zeros((5, 4), np.float16), np.zeros((4, 0), np.float16), c)
+
+
+@pytest.mark.parametrize("shape", [(130, 300, 70), (9, 300, 130)])
+def test_nothing_outside_c_is_written(gpu_ctx, shape) -> None:
+    """C sits inside a wider device matrix filled with a sentinel; after the launch only the
+    M x N window may differ, and A and B must be unchanged."""
+    m, n, k = shape
+    a, b = random_inputs(m, n, k, "float16")
+    da, db = gpu_ctx.to_device(a), gpu_ctx.to_device(b)
+    pad = 12
+    frame = cuda.DeviceBuffer(gpu_ctx, (m + 2, n + pad), np.float32)
+    frame.fill_bytes(0x7F)
+    window = cuda.DeviceBuffer.__new__(cuda.DeviceBuffer)
+    window.ctx, window.shape, window.dtype, window.ndim = gpu_ctx, (m, n), np.dtype(np.float32), 2
+    window.ld, window._rows = n + pad, m
+    window.nbytes = 0  # the window does not own memory
+    window.ptr = frame.ptr + ((n + pad) + 4) * 4  # one row down, four columns in (16-byte aligned)
+    gpu_ctx.gemm(da, db, window)
+    gpu_ctx.synchronize()
+    whole = frame.to_numpy()
+    sentinel = np.frombuffer(b"\x7f\x7f\x7f\x7f", np.float32)[0]
+    inside = whole[1 : m + 1, 4 : n + 4]
+    assert_close_to_oracle(np.ascontiguousarray(inside), a, b)
+    mask = np.ones_like(whole, bool)
+    mask[1 : m + 1, 4 : n + 4] = False
+    assert (whole[mask].view(np.uint32) == sentinel.view(np.uint32)).all()
+    assert np.array_equal(da.to_numpy().view(np.uint16), a.view(np.uint16))
+    assert np.array_equal(db.to_numpy().view(np.uint16), b.view(np.uint16))
+    window.ptr = 0
+
+
+def test_unaligned_pitches_and_bases_on_device(gpu_ctx) -> None:
+    """Odd pitches (K=1031-like) and a base that is only 2-byte aligned take the repack path."""
+    m, n, k = 150, 333, 77
+    a, b = random_inputs(m, n, k, "bfloat16")
+    plan = gpu_ctx.plan(m, n, k, "bfloat16")
+    assert plan.repack_a and plan.repack_b and plan.kernel_launches == 3
+    da, db = gpu_ctx.to_device(a), gpu_ctx.to_device(b)
+    dc = gpu_ctx.empty((m, n), np.float32)
+    gpu_ctx.gemm(da, db, dc)
+    gpu_ctx.synchronize()
+    assert_close_to_oracle(dc.to_numpy(), a, b)
+
+
+def test_numpy_views_and_strides() -> None:
+    rng = np.random.default_rng(3)
+    big_a = rng.standard_normal((100, 200)).astype(np.float16)
+    big_b = rng.standard_normal((200, 300)).astype(np.float16)
+    a = big_a[10:75, 8:136]            # row-major view with a pitch
+    b = big_b[8:136, 20:290]
+    c_store = np.full((65, 400), np.nan, np.float32)
+    c = c_store[:, 100:370]
+    compiled_for("float16")(a, b, c)
+    assert_close_to_oracle(np.ascontiguousarray(c), np.ascontiguousarray(a), np.ascontiguousarray(b))
+    assert np.isnan(c_store[:, :100]).all() and np.isnan(c_store[:, 370:]).all()
+    at = np.ascontiguousarray(a).T.copy().T  # column-major A: staged through a contiguous copy
+    assert not at.flags.c_contiguous
+    c2 = np.zeros((65, 270), np.float32)
+    compiled_for("float16")(at, b, c2)
+    assert np.array_equal(c2, np.ascontiguousarray(c))
+    c3 = np.zeros((270, 65), np.float32).T  # column-major C: written through a staged copy
+    compiled_for("float16")(a, b, c3)
+    assert np.array_equal(c3, c2)
+
+
+def test_device_buffers_through_the_handle(gpu_ctx) -> None:
+    a, b = random_inputs(200, 264, 96, "float16")
+    da, db = gpu_ctx.to_device(a), gpu_ctx.to_device(b)
+    dc = gpu_ctx.empty((200, 264), np.float32)
+    handle = compiled_for("float16")
+    assert handle(da, db, dc) is None  # synchronous, like the simulator
+    assert_close_to_oracle(dc.to_numpy(), a, b)
+    with pytest.raises(hc.LaunchError, match="all numpy.ndarray or all DeviceBuffer"):
+        handle(a, db, dc)
+    with pytest.raises(hc.LaunchError, match="conflicting binding for N"):
+        handle(da, db, gpu_ctx.empty((200, 265), np.float32))
+
+
+def test_device_call_rejects_bad_arguments(gpu_ctx) -> None:
+    a, b = random_inputs(128, 256, 64, "float16")
+    da, db = gpu_ctx.to_device(a), gpu_ctx.to_device(b)
+    with pytest.raises(hc.DeviceError, match="must not overlap"):
+        alias = cuda.DeviceBuffer.__new__(cuda.DeviceBuffer)
+        alias.ctx, alias.shape, alias.dtype, alias.ndim, alias.ld, alias._rows, alias.nbytes = (
+            gpu_ctx, (128, 256), np.dtype(np.float32), 2, 256, 128, 0)
+        alias.ptr = db.ptr
+        try:
+            gpu_ctx.gemm(da, db, alias)
+        finally:
+            alias.ptr = 0
+    dc = gpu_ctx.empty((128, 256), np.float32)
+    with pytest.raises(hc.DeviceError, match="skinny variant needs m <= 64"):
+        gpu_ctx.gemm(da, db, dc, variant=cuda.VARIANT_SKINNY)
+    gpu_ctx.gemm(da, db, dc)  # the context is still usable
+    gpu_ctx.synchronize()
+    assert_close_to_oracle(dc.to_numpy(), a, b)
+
+
+def test_pinned_arrays_round_trip(gpu_ctx) -> None:
+    a_src, b_src = random_inputs(70, 80, 90, "float16")
+    a = cuda.pinned_empty(a_src.shape, a_src.dtype)
+    b = cuda.pinned_empty(b_src.shape, b_src.dtype)
+    c = cuda.pinned_empty((70, 80), np.float32)
+    a[...] = a_src
+    b[...] = b_src
+    compiled_for("float16")(a, b, c)
+    assert_close_to_oracle(np.array(c), a_src, b_src)
+
+
+# ---------------------------------------------------------------- properties at full size
+
+
+def _sample_rows(m: int, count: int = 24) -> np.ndarray:
+    rows = np.unique(np.concatenate([np.arange(0, m, max(1, m // count)), [m - 1]]))
+    return rows.astype(np.int64)
+
+
+@pytest.mark.parametrize("name", ["gemm_8192", "ragged", "skinny"])
+def test_full_size_configs(name: str, gpu_ctx) -> None:
+    """Configs 2-4 at full size: sampled rows against float64 and against the oracle, plus
+    properties that need no reference: the result is reproducible, scaling A by 2 scales C by
+    exactly 2 (a power of two commutes with every rounding), and a row permutation of A
+    permutes the rows of C."""
+    a, b = workloads.make_inputs(name)
+    w = workloads.CONFIGS[name]
+    da, db = gpu_ctx.to_device(a), gpu_ctx.to_device(b)
+    dc = gpu_ctx.empty((w.m, w.n), np.float32)
+    dc.fill_bytes(0xFF)
+    gpu_ctx.gemm(da, db, dc)
+    gpu_ctx.synchronize()
+    c = dc.to_numpy()
+    assert np.isfinite(c).all()
+    rows = _sample_rows(w.m)
+    report = workloads.check_against_float64(c, a, b, rows=rows)
+    assert report["ok"], report
+    sample = np.ascontiguousarray(a[rows])
+    expect = cpu_ref.matmul_k_ascending(sample, b)
+    assert_close_to_oracle(np.ascontiguousarray(c[rows]), sample, b, expect=expect)
+
+    gpu_ctx.gemm(da, db, dc)
+    gpu_ctx.synchronize()
+    assert np.array_equal(dc.to_numpy(), c)
+
+    doubled = gpu_ctx.to_device((a.astype(np.float32) * 2).astype(a.dtype))
+    gpu_ctx.gemm(doubled, db, dc)
+    gpu_ctx.synchronize()
+    assert np.array_equal(dc.to_numpy(), c * np.float32(2))
+    doubled.free()
+
+    if w.m >= 128:
+        perm = np.random.default_rng(0).permutation(w.m)
+        permuted = gpu_ctx.to_device(np.ascontiguousarray(a[perm]))
+        gpu_ctx.gemm(permuted, db, dc)
+        gpu_ctx.synchronize()
+        assert np.array_equal(dc.to_numpy(), c[perm])
+        permuted.free()
+    for buf in (da, db, dc):
+        buf.free()
+
+
+def test_config1_through_the_example_entry_point() -> None:
+    a, b = workloads.make_inputs("sim_64")
+    golden_a, golden_b, c_sim = load_golden("sim_f16_m64_n64_k64_normal_seed0")
+    assert np.array_equal(a.view(np.uint16), golden_a.view(np.uint16))
+    assert np.array_equal(b.view(np.uint16), golden_b.view(np.uint16))
+    assert_close_to_oracle(gpu_wmma_matmul(a, b), a, b, expect=c_sim)
+
+
+def test_sharded_config_scaled_down_on_one_gpu(gpu_ctx) -> None:
+    """Config 5's structure on one device: two column slabs computed separately and
+    assembled equal the unsharded product bit for bit (slabs are tile-aligned)."""
+    from hc.distributed import ShardedMatmul, assemble_row_major
+
+    m, k, n = 384, 640, 4096
+    a, b = workloads.make_sharded_inputs(0, n, m=m, k=k)
+    handle = compiled_for("float16")
+    slabs = []
+    for rank in range(2):
+        sharded = ShardedMatmul(handle, gpu_ctx, n, 2, rank, align=256)
+        da, db, dc = sharded.upload(a, b)
+        sharded.run(da, db, dc)
+        gpu_ctx.synchronize()
+        slabs.append(dc.to_numpy())
+    whole = gpu_wmma_matmul(a, b)
+    assert np.array_equal(assemble_row_major(np.stack(slabs)), whole)
+    assert_close_to_oracle(whole, a, b)

@@ -1,0 +1,118 @@
+"""The CPU oracle is pinned against outputs of the reference simulator itself."""
+
+from __future__ import annotations
+
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+from conftest import GOLDEN, GOLDEN_NAMES, REFERENCE, REPO, load_golden, np_dtype
+from oracle import cpu_ref
+
+
+def test_fixtures_are_present() -> None:
+    assert len(GOLDEN_NAMES) == 6
+    assert (GOLDEN / "blocked_reference.npz").exists()
+
+
+@pytest.mark.parametrize("name", GOLDEN_NAMES)
+def test_oracle_is_bit_identical_to_the_reference_simulator(name: str) -> None:
+    a, b, c_sim = load_golden(name)
+    for fn in (cpu_ref.matmul_k_ascending, cpu_ref.matmul_tiled, cpu_ref.matmul_numpy):
+        out = fn(a, b)
+        assert out.dtype == np.float32
+        assert np.array_equal(out.view(np.uint32), c_sim.view(np.uint32)), fn.__name__
+
+
+def test_oracle_meets_the_reference_tests_own_tolerance() -> None:
+    # tests/test_examples.py:22-33 of the reference: atol 2e-6 against its blocked product.
+    with np.load(GOLDEN / "blocked_reference.npz") as blocked:
+        for name in blocked.files:
+            a, b, _ = load_golden(name)
+            np.testing.assert_allclose(cpu_ref.matmul_k_ascending(a, b), blocked[name], rtol=0.0, atol=2e-6)
+
+
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+@pytest.mark.parametrize("shape", [(1, 1, 1), (16, 16, 16), (17, 19, 18), (3, 130, 77), (40, 5, 129), (8, 256, 96)])
+def test_tiled_and_flat_restatements_agree(dtype: str, shape: tuple[int, int, int]) -> None:
+    m, n, k = shape
+    rng = np.random.default_rng(hash((dtype, shape)) % 2**32)
+    a = rng.standard_normal((m, k)).astype(np_dtype(dtype))
+    b = rng.standard_normal((k, n)).astype(np_dtype(dtype))
+    flat = cpu_ref.matmul_k_ascending(a, b)
+    assert np.array_equal(flat, cpu_ref.matmul_tiled(a, b))
+    assert np.array_equal(flat, cpu_ref.matmul_numpy(a, b))
+    assert np.array_equal(flat, cpu_ref.matmul_k_ascending(a, b, threads=1))
+
+
+def test_empty_and_zero_k() -> None:
+    f16 = np.float16
+    assert cpu_ref.matmul_k_ascending(np.zeros((0, 4), f16), np.zeros((4, 5), f16)).shape == (0, 5)
+    assert cpu_ref.matmul_k_ascending(np.zeros((3, 4), f16), np.zeros((4, 0), f16)).shape == (3, 0)
+    out = cpu_ref.matmul_k_ascending(np.zeros((3, 0), f16), np.zeros((0, 5), f16))
+    assert out.shape == (3, 5) and not out.any()
+    assert np.array_equal(out, cpu_ref.matmul_tiled(np.zeros((3, 0), f16), np.zeros((0, 5), f16)))
+
+
+def test_row_sample_matches_full_product() -> None:
+    rng = np.random.default_rng(11)
+    a = rng.standard_normal((50, 64)).astype(np.float16)
+    b = rng.standard_normal((64, 33)).astype(np.float16)
+    full = cpu_ref.matmul_k_ascending(a, b)
+    part = cpu_ref.matmul_k_ascending(a, b, rows=(10, 25))
+    assert np.array_equal(part[10:25], full[10:25])
+    assert not part[:10].any() and not part[25:].any()
+
+
+def test_every_16_bit_pattern_widens_exactly() -> None:
+    one = np.ones((1, 1), np.float16)
+    for dtype in ("float16", "bfloat16"):
+        values = np.arange(65536, dtype=np.uint16).view(np_dtype(dtype)).reshape(1, -1)
+        with np.errstate(all="ignore"):
+            out = cpu_ref.matmul_k_ascending(one.astype(np_dtype(dtype)), values)
+        ref = values.astype(np.float32)
+        finite = ~np.isnan(ref)
+        assert np.array_equal(out[finite], ref[finite] + np.float32(0))
+        assert np.array_equal(np.isnan(out), np.isnan(ref))
+
+
+def test_rejects_mismatched_inputs() -> None:
+    with pytest.raises(ValueError):
+        cpu_ref.matmul_k_ascending(np.zeros((2, 3), np.float16), np.zeros((4, 2), np.float16))
+    with pytest.raises(ValueError):
+        cpu_ref.matmul_k_ascending(np.zeros((2, 3), np.float32), np.zeros((3, 2), np.float32))
+
+
+@pytest.mark.skipif(not REFERENCE.exists(), reason="the reference checkout is not on this machine")
+def test_reference_simulator_reproduces_a_fixture_and_runs_our_example() -> None:
+    """Re-runs the unmodified reference simulator (with the two stand-in dependencies) on the
+    ragged fixture, and runs this repository's example kernel through it as well: both must
+    reproduce the stored output bit for bit."""
+    script = r"""
+import importlib.util, sys
+import numpy as np
+import hc.simulator as sim
+from examples.amdgpu_gfx11_wmma_matmul import simulate_gfx11_wmma_matmul
+data = np.load(sys.argv[1])
+a = data["a_bits"].view(np.float16); b = data["b_bits"].view(np.float16)
+assert np.array_equal(simulate_gfx11_wmma_matmul(a, b), data["c"])
+spec = importlib.util.spec_from_file_location("b200_example", sys.argv[2])
+mod = importlib.util.module_from_spec(spec); mod.__package__ = "loaded_by_test"
+sys.modules["b200_example"] = mod; spec.loader.exec_module(mod)
+c = np.zeros_like(data["c"])
+sim.launch(mod.tiled_wmma_matmul_for("float16"), a, b, c)
+assert np.array_equal(c, data["c"])
+print("ok")
+"""
+    env = dict(os.environ)
+    env["HC_IXSIMPL_VENDOR_DIR"] = str(REPO / "oracle" / "standins" / "ixsimpl_vendor")
+    env["PYTHONPATH"] = os.pathsep.join([str(REFERENCE), str(REPO / "oracle" / "standins")])
+    result = subprocess.run(
+        [sys.executable, "-c", script, str(GOLDEN / "sim_f16_m17_n19_k18_seed7.npz"),
+         str(REPO / "5_b200" / "examples" / "b200_wmma_matmul.py")],
+        env=env, capture_output=True, text=True, timeout=120, cwd=str(REPO / "tests"))
+    assert result.returncode == 0, result.stderr
+    assert result.stdout.strip() == "ok"
