@@ -45,7 +45,7 @@ EXPORTS = (
     "hcCudaMemcpyHtoD", "hcCudaMemcpyDtoH", "hcCudaMemcpy2DHtoD", "hcCudaMemcpy2DDtoH",
     "hcCudaMemset", "hcCudaGemmPlan", "hcCudaGemm", "hcCudaGemmHost", "hcCudaEventCreate",
     "hcCudaEventDestroy", "hcCudaEventRecord", "hcCudaEventElapsedMs", "hcCudaCommGetUniqueId",
-    "hcCudaCommInitRank", "hcCudaCommAllGather", "hcCudaCommDestroy",
+    "hcCudaCommInitRank", "hcCudaCommAllGather", "hcCudaCommDestroy", "hcCudaGemmSkinnyStatic",
 )
 
 
@@ -135,6 +135,7 @@ def library() -> ctypes.CDLL:
         lib.hcCudaCommInitRank.argtypes = [vp, vp, sz, i, i]
         lib.hcCudaCommAllGather.argtypes = [vp, vp, vp, sz]
         lib.hcCudaCommDestroy.argtypes = [vp]
+        lib.hcCudaGemmSkinnyStatic.argtypes = [ctypes.POINTER(_GemmArgs), vp, i, ctypes.c_char_p, sz]
         for name in EXPORTS:
             getattr(lib, name)  # AttributeError here means a stale or foreign library
         _LIB = lib

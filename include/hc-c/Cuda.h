@@ -187,6 +187,36 @@ HC_CUDA_CAPI_EXPORTED int hcCudaGemm(HcCudaContext *ctx, const HcCudaGemmArgs *a
  * doc/simulator.md:201-207). Device staging memory is kept by the context between calls. */
 HC_CUDA_CAPI_EXPORTED int hcCudaGemmHost(HcCudaContext *ctx, const HcCudaGemmArgs *args);
 
+/* ---- launching without allocating ---------------------------------------------------- */
+
+/* Bytes of device memory every GPU that loads this library sets aside for the entry point
+ * below (a file-scope __device__ array; held until the process exits). */
+#define HC_CUDA_STATIC_SCRATCH_BYTES (256 + 16 * 1024 + 8 * 1024 * 1024)
+
+/* The skinny GEMM (m <= 64) with all of its scratch in that static array: this call never
+ * allocates or frees device memory, in contrast to hcCudaGemm, whose context grows its scratch
+ * with cudaMalloc. It has no counterpart in the reference (which never touches a device); it is
+ * for callers that cannot allocate at launch time -- a process whose GPU memory is already
+ * reserved in full by another allocator, or a latency-critical loop that must avoid the
+ * device-wide synchronisation cudaMalloc and cudaFree imply.
+ *
+ * Runs on the calling thread's current device and on `stream` (a cudaStream_t; NULL = the
+ * default stream). a, b, c are device pointers; a and b must be 16-byte aligned with lda and ldb
+ * multiples of 8 elements (no repack is possible without scratch). The split-k partial sums
+ * must fit: splits * m * round_up(n, 128) * 4 <= 8 MiB and n <= 131072, otherwise
+ * HC_CUDA_ERR_UNSUPPORTED. `synchronize` != 0 waits for the result and reports a device-side
+ * timeout; with 0 the call returns once the work is enqueued. On failure a message is copied
+ * into `error_text` (may be NULL).
+ *
+ * The first call on each device looks up the array's device address and the driver's tensor-map
+ * encoder; make that first call outside any stream capture. All calls on a device share the one
+ * array: calls whose kernels could overlap on the GPU (different streams) race and must be
+ * serialised by the caller. The array keeps the previous call's contents; the call clears the
+ * words that have to start at zero itself. */
+HC_CUDA_CAPI_EXPORTED int hcCudaGemmSkinnyStatic(const HcCudaGemmArgs *args, void *stream,
+                                                 int synchronize, char *error_text,
+                                                 size_t error_text_bytes);
+
 /* ---- timing ------------------------------------------------------------------------- */
 
 HC_CUDA_CAPI_EXPORTED int hcCudaEventCreate(HcCudaContext *ctx, HcCudaEvent **out);
