@@ -338,7 +338,7 @@ def run_gpu_arm(args, ranks: Ranks) -> None:
     t_end = time.perf_counter()
     ranks.barrier()
     clocks = sampler.summary(t_begin, t_end)
-    if clocks["samples"] < 3:
+    if clocks["samples"] < 3 and not args.quick:
         # The timed region was shorter than the sampling period: keep the same launches
         # running for half a second more and sample the clocks over that continuation.
         c_begin = time.perf_counter()
@@ -360,6 +360,15 @@ def run_gpu_arm(args, ranks: Ranks) -> None:
     parity_all = ranks.gather_objects(parity)
 
     # ---- end to end through the public handle on pinned host buffers ---------------------
+    if args.quick:
+        sampler.stop()
+        if ranks.rank == 0:
+            print(json.dumps({"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": ranks.world,
+                              "steps": args.steps, "ms_per_step": ms_per_step, "quick": True,
+                              "config": {"workload": name, "variant": plan.variant, "splits": plan.splits,
+                                         "grid": plan.grid, "launches_per_step": plan.kernel_launches},
+                              "parity_ok": all(p["ok"] for p in parity_all), "clocks": clocks}), flush=True)
+        return
     e2e_steps = max(1, min(args.steps, args.e2e_steps))
     pa = cuda.pinned_empty(a.shape, a.dtype)
     pb = cuda.pinned_empty(b.shape, b.dtype)
@@ -468,6 +477,8 @@ def main() -> int:
     parser.add_argument("--e2e-steps", type=int, default=5)
     parser.add_argument("--no-gather", action="store_true")
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--quick", action="store_true",
+                        help="timed region and parity only (for profiler captures): no e2e, CPU or gather legs")
     args = parser.parse_args()
     if args.steps < 1:
         parser.error("--steps must be at least 1")
