@@ -25,6 +25,7 @@ OUTPUT = LIB_DIR / "libhc_cuda.so"
 
 SOURCES = [
     LIB_DIR / "Kernels" / "gemm_dense_sm100a.cu",
+    LIB_DIR / "Kernels" / "gemm_dense_pair_sm100a.cu",
     LIB_DIR / "Kernels" / "gemm_skinny_sm100a.cu",
     LIB_DIR / "Kernels" / "repack_sm100a.cu",
     LIB_DIR / "Kernels" / "gemm_skinny_static_sm100a.cu",
@@ -33,6 +34,7 @@ SOURCES = [
 HEADERS = [
     LIB_DIR / "Kernels" / "gemm_launch.h",
     LIB_DIR / "Kernels" / "sm100_ptx.cuh",
+    LIB_DIR / "Kernels" / "gemm_epilogue.cuh",
     REPO_ROOT / "include" / "hc-c" / "Cuda.h",
 ]
 

@@ -29,6 +29,10 @@ using hc::sm100::kDTypeBF16;
 constexpr int kDefaultSmCount = 148;
 constexpr int64_t kMaxDim = int64_t(1) << 30;
 constexpr int64_t kMaxPitch = int64_t(1) << 38;
+// Pitch granularity of operands the library lays out itself (repacked or staged copies): 64
+// elements = 128 bytes, so that every 128-byte TMA box row is one aligned line. (TMA itself only
+// needs 16 bytes; rows that straddle lines cost about a third more time on the ragged config.)
+constexpr int64_t kRepackPitchElems = 64;
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
                                    const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
@@ -211,24 +215,37 @@ int plan_gemm(const HcCudaContext *ctx, const HcCudaGemmArgs *args, int sm_count
   }
   int64_t scratch = 0;
   if (plan->repack_a)
-    scratch += round_up(m * round_up(k, 8) * 2, 1024);
+    scratch += round_up(m * round_up(k, kRepackPitchElems) * 2, 1024);
   if (plan->repack_b)
-    scratch += round_up(k * round_up(n, 8) * 2, 1024);
+    scratch += round_up(k * round_up(n, kRepackPitchElems) * 2, 1024);
   plan->kernel_launches = 1 + plan->repack_a + plan->repack_b;
 
   if (variant == HC_CUDA_GEMM_DENSE) {
     const hc::sm100::DenseTileShape t = hc::sm100::dense_tile_shape();
-    plan->tiles_m = static_cast<int32_t>((m + t.block_m - 1) / t.block_m);
+    const bool pairs = hc::sm100::dense_uses_pairs(m, n, k, sm_count);
+    const int64_t tile_m = pairs ? 2 * t.block_m : t.block_m;
+    plan->tiles_m = static_cast<int32_t>((m + tile_m - 1) / tile_m);
     plan->tiles_n = static_cast<int32_t>((n + t.block_n - 1) / t.block_n);
     const int64_t tiles = static_cast<int64_t>(plan->tiles_m) * plan->tiles_n;
-    if (tiles > 0x7fffffffLL)
+    if (tiles > 0x3fffffffLL)
       return fail(ctx, HC_CUDA_ERR_UNSUPPORTED, "too many tiles");
-    plan->grid = static_cast<int32_t>(tiles < sm_count ? tiles : sm_count);
+    if (pairs) {
+      const int64_t clusters = sm_count / 2;
+      plan->grid = static_cast<int32_t>(2 * (tiles < clusters ? tiles : clusters));
+    } else {
+      plan->grid = static_cast<int32_t>(tiles < sm_count ? tiles : sm_count);
+    }
   } else {
     const hc::sm100::SkinnyShape s = hc::sm100::skinny_shape(static_cast<int>(m));
     plan->tiles_m = 1;
     plan->tiles_n = static_cast<int32_t>((n + s.block_n - 1) / s.block_n);
     plan->splits = hc::sm100::skinny_choose_splits(static_cast<int>(n), static_cast<int>(k), sm_count);
+    if (const char *forced = std::getenv("HC_CUDA_SKINNY_SPLITS")) {  // tuning aid
+      const int v = std::atoi(forced);
+      const int64_t kb_total = (k + s.block_k - 1) / s.block_k;
+      if (v >= 1 && v <= kb_total)
+        plan->splits = v;
+    }
     const int64_t units = static_cast<int64_t>(plan->tiles_n) * plan->splits;
     const int64_t slots = static_cast<int64_t>(sm_count) * 2;
     plan->grid = static_cast<int32_t>(units < slots ? units : slots);
@@ -324,14 +341,14 @@ int enqueue_gemm(HcCudaContext *ctx, const HcCudaGemmArgs *args, const HcCudaGem
   int64_t lda = args->lda, ldb = args->ldb;
   char *cursor = static_cast<char *>(ctx->scratch);
   if (plan.repack_a) {
-    const int64_t ld = round_up(k, 8);
+    const int64_t ld = round_up(k, kRepackPitchElems);
     HC_TRY_CUDA(ctx, hc::sm100::launch_repack_pitch(a, lda, cursor, ld, m, k, ctx->stream));
     a = cursor;
     lda = ld;
     cursor += round_up(static_cast<int64_t>(m) * ld * 2, 1024);
   }
   if (plan.repack_b) {
-    const int64_t ld = round_up(n, 8);
+    const int64_t ld = round_up(n, kRepackPitchElems);
     HC_TRY_CUDA(ctx, hc::sm100::launch_repack_pitch(b, ldb, cursor, ld, k, n, ctx->stream));
     b = cursor;
     ldb = ld;
@@ -347,9 +364,15 @@ int enqueue_gemm(HcCudaContext *ctx, const HcCudaGemmArgs *args, const HcCudaGem
     if (int rc = encode_map(ctx, &tmap_b, args->dtype, b, n, k, static_cast<uint64_t>(ldb) * 2, 64,
                             t.block_k))
       return rc;
-    HC_TRY_CUDA(ctx, hc::sm100::launch_gemm_dense(tmap_a, tmap_b, args->c, m, n, k, args->ldc,
-                                                  args->dtype, ctx->group_n, plan.grid,
-                                                  ctx->status_dev, ctx->stream));
+    if (hc::sm100::dense_uses_pairs(m, n, k, ctx->prop.multiProcessorCount)) {
+      HC_TRY_CUDA(ctx, hc::sm100::launch_gemm_dense_pair(tmap_a, tmap_b, args->c, m, n, k, args->ldc,
+                                                         args->dtype, ctx->group_n, plan.grid,
+                                                         ctx->status_dev, ctx->stream));
+    } else {
+      HC_TRY_CUDA(ctx, hc::sm100::launch_gemm_dense(tmap_a, tmap_b, args->c, m, n, k, args->ldc,
+                                                    args->dtype, ctx->group_n, plan.grid,
+                                                    ctx->status_dev, ctx->stream));
+    }
     return HC_CUDA_OK;
   }
 
@@ -688,8 +711,8 @@ int hcCudaGemmHost(HcCudaContext *ctx, const HcCudaGemmArgs *args) {
   }
   HC_TRY_CUDA(ctx, cudaSetDevice(ctx->device));
   // Device copies get pitches that satisfy TMA (16 bytes), so no repack pass is needed.
-  const size_t lda = static_cast<size_t>(round_up(args->k, 8));
-  const size_t ldb = static_cast<size_t>(round_up(args->n, 8));
+  const size_t lda = static_cast<size_t>(round_up(args->k, kRepackPitchElems));
+  const size_t ldb = static_cast<size_t>(round_up(args->n, kRepackPitchElems));
   const size_t ldc = static_cast<size_t>(round_up(args->n, 4));
   if (int rc = ensure_stage(ctx, 0, m * lda * 2))
     return rc;

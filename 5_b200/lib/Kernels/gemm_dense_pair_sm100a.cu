@@ -1,0 +1,296 @@
+// Dense tiled GEMM for sm_100a on CTA pairs: C[M,N] (fp32) = A[M,K] * B[K,N], fp16/bf16 in.
+//
+// Same contract as gemm_dense_kernel (the hc kernel of
+// examples/amdgpu_gfx11_wmma_matmul.py:301-326), larger unit of work: a cluster of two CTAs on
+// neighbouring SMs owns a 256x256 tile of C and drives one tcgen05.mma.cta_group::2
+// (256x256x16) together.
+//
+//   CTA r of the pair loads rows [128 r, 128 r + 128) of the A tile and columns
+//   [128 r, 128 r + 128) of the B tile into its own shared memory, holds rows
+//   [128 r, 128 r + 128) of the accumulator in its own TMEM and writes those rows of C.
+//   The instruction, issued by CTA 0, reads both halves of both operands, so each SM fetches
+//   32 KiB per 64-deep k-block for 256x256 outputs instead of 48 KiB for 128x256: a third less
+//   L2 and shared-memory traffic per flop than the single-CTA kernel.
+//
+// Synchronisation (mbarriers at identical shared-memory offsets in both CTAs):
+//   full[s]       CTA 0 only. One arrival (CTA 0's producer, with expect_tx for both CTAs'
+//                 bytes); both producers' TMA loads count their bytes on it.
+//   empty[s]      one per CTA. CTA 0's MMA thread commits to its own and to its partner's when the
+//                 MMAs that read ring slot s have finished.
+//   tmem_full[a]  one per CTA, committed by CTA 0 after the last k-block of a tile.
+//   tmem_empty[a] CTA 0 only, 8 arrivals: the four epilogue warps of each CTA.
+// No load uses multicast; every CTA fetches its own operand halves.
+#include "gemm_epilogue.cuh"
+#include "gemm_launch.h"
+#include "sm100_ptx.cuh"
+
+#include <cstdlib>
+#include <cstring>
+
+namespace hc {
+namespace sm100 {
+
+namespace dense_pair {
+
+constexpr int kTileM = 256;      // per pair
+constexpr int kTileN = 256;      // per pair
+constexpr int kCtaM = 128;       // rows of A / C per CTA
+constexpr int kCtaN = 128;       // columns of B loaded per CTA
+constexpr int kBlockK = 64;
+constexpr int kUmmaK = 16;
+constexpr int kStages = 6;
+constexpr int kNumThreads = 192;
+constexpr int kNumEpilogueWarps = 4;
+constexpr int kTmemColumns = 512;  // two accumulators of kTileN fp32 columns
+
+constexpr uint32_t kATileBytes = kCtaM * kBlockK * 2;             // 16 KiB
+constexpr uint32_t kBChunkBytes = 64 * kBlockK * 2;               // 64 columns x 64 k-rows
+constexpr uint32_t kBTileBytes = kBChunkBytes * (kCtaN / 64);     // 16 KiB
+constexpr uint32_t kStageBytes = kATileBytes + kBTileBytes;       // 32 KiB per CTA
+constexpr uint32_t kEpilogueWarpBytes = 32 * 32 * 4;
+constexpr uint32_t kBarrierBytes = 256;
+constexpr uint32_t kSmemBytes = kStages * kStageBytes + kNumEpilogueWarps * kEpilogueWarpBytes +
+                                kBarrierBytes + 1024;
+
+struct TileCoord {
+  int m_blk;
+  int n_blk;
+};
+
+__device__ __forceinline__ TileCoord tile_coord(int tile, int tiles_m, int tiles_n, int group_n) {
+  const int tiles_per_group = group_n * tiles_m;
+  const int group = tile / tiles_per_group;
+  const int first_n = group * group_n;
+  const int width = min(group_n, tiles_n - first_n);
+  const int in_group = tile - group * tiles_per_group;
+  TileCoord tc;
+  tc.m_blk = in_group / width;
+  tc.n_blk = first_n + in_group % width;
+  return tc;
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
+gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                       const __grid_constant__ CUtensorMap tmap_b, float *__restrict__ c, int m, int n,
+                       int k, long long ldc, uint32_t idesc, int tiles_m, int tiles_n, int group_n,
+                       int *status) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t smem_base = (raw_addr + 1023u) & ~1023u;
+  uint8_t *smem_gen = smem_raw + (smem_base - raw_addr);
+
+  const uint32_t epi_base = smem_base + kStages * kStageBytes;
+  const uint32_t bar_base = epi_base + kNumEpilogueWarps * kEpilogueWarpBytes;
+  auto full_bar = [&](uint32_t s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](uint32_t s) { return bar_base + 8u * (kStages + s); };
+  auto tmem_full_bar = [&](uint32_t a) { return bar_base + 8u * (2 * kStages + a); };
+  auto tmem_empty_bar = [&](uint32_t a) { return bar_base + 8u * (2 * kStages + 2 + a); };
+  const uint32_t misc_off = (bar_base - smem_base) + 8u * (2 * kStages + 4);
+  volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem_gen + misc_off);
+  volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(smem_gen + misc_off + 4);
+
+  const int warp = static_cast<int>(threadIdx.x >> 5);
+  const int lane = static_cast<int>(threadIdx.x & 31);
+  const uint32_t cta_rank = cluster_cta_rank();  // 0: issues the MMAs, 1: partner
+
+  if (threadIdx.x == 0) {
+    for (uint32_t s = 0; s < kStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (uint32_t a = 0; a < 2; ++a) {
+      mbar_init(tmem_full_bar(a), 1);
+      mbar_init(tmem_empty_bar(a), 2 * kNumEpilogueWarps);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_descriptor(&tmap_a);
+    tma_prefetch_descriptor(&tmap_b);
+  }
+  // Both CTAs' barriers must exist before either CTA signals across the pair.
+  cluster_sync_all();
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(const_cast<uint32_t *>(tmem_slot)), kTmemColumns);
+    tmem_relinquish_alloc_permit_pair();
+  }
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  tcgen05_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (k + kBlockK - 1) / kBlockK;
+  const int cluster_id = static_cast<int>(blockIdx.x >> 1);
+  const int num_clusters = static_cast<int>(gridDim.x >> 1);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer ------
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters) {
+        const TileCoord tc = tile_coord(tile, tiles_m, tiles_n, group_n);
+        const int m0 = tc.m_blk * kTileM + static_cast<int>(cta_rank) * kCtaM;
+        const int n0 = tc.n_blk * kTileN + static_cast<int>(cta_rank) * kCtaN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
+            ok = false;
+            break;
+          }
+          const uint32_t a_dst = smem_base + stage * kStageBytes;
+          const uint32_t b_dst = a_dst + kATileBytes;
+          const uint32_t leader_full = map_to_cta(full_bar(stage), 0);
+          if (cta_rank == 0)
+            mbar_arrive_expect_tx(full_bar(stage), 2 * kStageBytes);
+          tma_load_2d_pair(a_dst, &tmap_a, leader_full, kb * kBlockK, m0);
+#pragma unroll
+          for (int j = 0; j < kCtaN / 64; ++j)
+            tma_load_2d_pair(b_dst + j * kBChunkBytes, &tmap_b, leader_full, n0 + j * 64, kb * kBlockK);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (CTA 0) -
+    if (lane == 0 && cta_rank == 0) {
+      uint32_t stage = 0, phase = 0;
+      uint32_t iter = 0;
+      bool ok = true;
+      for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters, ++iter) {
+        const uint32_t acc = iter & 1u;
+        const uint32_t acc_phase = (iter >> 1) & 1u;
+        if (!mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, abort_flag))
+          break;
+        tcgen05_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * kTileN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
+            ok = false;
+            break;
+          }
+          tcgen05_fence_after_sync();
+          const uint32_t a_addr = smem_base + stage * kStageBytes;
+          const uint32_t b_addr = a_addr + kATileBytes;
+          const uint64_t a_desc = make_smem_desc_sw128(a_addr, 16, 1024);
+          const uint64_t b_desc = make_smem_desc_sw128(b_addr, kBChunkBytes, 1024);
+#pragma unroll
+          for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
+            umma_f16_ss_pair(d_tmem, a_desc + static_cast<uint64_t>(kk * 2),
+                             b_desc + static_cast<uint64_t>(kk * 128), idesc, (kb | kk) != 0 ? 1u : 0u);
+          }
+          // Hand ring slot `stage` back to both producers.
+          umma_commit_pair(map_to_cta(empty_bar(stage), 0));
+          umma_commit_pair(map_to_cta(empty_bar(stage), 1));
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) {
+          umma_commit_pair(map_to_cta(tmem_full_bar(acc), 0));
+          umma_commit_pair(map_to_cta(tmem_full_bar(acc), 1));
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue ----------
+    const int quarter = warp & 3;
+    float *stage_gen = reinterpret_cast<float *>(smem_gen + (epi_base - smem_base) +
+                                                 (warp - 2) * kEpilogueWarpBytes);
+    const bool vec_ok = ((ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(c) & 15) == 0);
+    uint32_t iter = 0;
+    for (int tile = cluster_id; tile < num_tiles; tile += num_clusters, ++iter) {
+      const TileCoord tc = tile_coord(tile, tiles_m, tiles_n, group_n);
+      const uint32_t acc = iter & 1u;
+      const uint32_t acc_phase = (iter >> 1) & 1u;
+      const bool ready = mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag);
+      if (!__all_sync(0xffffffffu, ready))
+        break;
+      tcgen05_fence_after_sync();
+      const int row_base = tc.m_blk * kTileM + static_cast<int>(cta_rank) * kCtaM + quarter * 32;
+      const int col_base = tc.n_blk * kTileN;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kTileN;
+      drain_accumulator_rows<kTileN>(taddr, stage_gen, c, ldc, m, n, row_base, col_base, vec_ok, lane,
+                                     map_to_cta(tmem_empty_bar(acc), 0), /*release_remote=*/true);
+    }
+  }
+
+  // Neither CTA may leave (or free TMEM) while its partner can still read its shared memory,
+  // write its TMEM or signal its barriers.
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag != 0) {
+    if (threadIdx.x == 0)
+      atomicExch(status, kStatusDeviceWaitTimeout);
+    const long long start = clock64();
+    while (clock64() - start < 2000000LL) {
+    }
+  }
+  cluster_sync_all();
+  tcgen05_fence_after_sync();
+  if (warp == 1)
+    tmem_dealloc_pair(tmem_base, kTmemColumns);
+}
+
+} // namespace dense_pair
+
+cudaError_t launch_gemm_dense_pair(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, float *c,
+                                   int m, int n, int k, long long ldc, int dtype, int group_n,
+                                   int max_ctas, int *status, cudaStream_t stream) {
+  using namespace dense_pair;
+  static thread_local int configured_device = -1;
+  int device = 0;
+  cudaError_t err = cudaGetDevice(&device);
+  if (err != cudaSuccess)
+    return err;
+  if (configured_device != device) {
+    err = cudaFuncSetAttribute(gemm_dense_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(kSmemBytes));
+    if (err != cudaSuccess)
+      return err;
+    configured_device = device;
+  }
+  const int tiles_m = (m + kTileM - 1) / kTileM;
+  const int tiles_n = (n + kTileN - 1) / kTileN;
+  const long long num_tiles = static_cast<long long>(tiles_m) * tiles_n;
+  if (num_tiles <= 0 || num_tiles > 0x3fffffffLL)
+    return cudaErrorInvalidValue;
+  long long clusters = max_ctas / 2;
+  if (clusters < 1)
+    clusters = 1;
+  if (num_tiles < clusters)
+    clusters = num_tiles;
+  const uint32_t idesc = make_idesc_f16(dtype == kDTypeBF16 ? 1u : 0u, /*a_mn_major=*/false,
+                                        /*b_mn_major=*/true, kTileM, kTileN);
+  if (group_n < 1)
+    group_n = 1;
+  gemm_dense_pair_kernel<<<static_cast<unsigned>(clusters * 2), kNumThreads, kSmemBytes, stream>>>(
+      tmap_a, tmap_b, c, m, n, k, ldc, idesc, tiles_m, tiles_n, group_n, status);
+  return cudaGetLastError();
+}
+
+bool dense_uses_pairs(long long m, long long n, long long k, int sm_count) {
+  (void)k;
+  // HC_CUDA_DENSE_MODE=single|pair forces a mode (tuning aid).
+  if (const char *mode = std::getenv("HC_CUDA_DENSE_MODE")) {
+    if (std::strcmp(mode, "single") == 0)
+      return false;
+    if (std::strcmp(mode, "pair") == 0)
+      return true;
+  }
+  if (m <= 128 || sm_count < 2)
+    return false;
+  // Compare the number of tile rounds each mode needs; a 256x256 pair tile takes about as long
+  // as a 128x256 single tile does on one SM, and moves a third less data per flop.
+  const long long single_tiles = ((m + 127) / 128) * ((n + 255) / 256);
+  const long long pair_tiles = ((m + 255) / 256) * ((n + 255) / 256);
+  const long long single_rounds = (single_tiles + sm_count - 1) / sm_count;
+  const long long pair_rounds = (pair_tiles + sm_count / 2 - 1) / (sm_count / 2);
+  return pair_rounds * 9 <= single_rounds * 10;
+}
+
+} // namespace sm100
+} // namespace hc

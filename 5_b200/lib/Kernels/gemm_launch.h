@@ -29,6 +29,16 @@ cudaError_t launch_gemm_dense(const CUtensorMap &tmap_a, const CUtensorMap &tmap
                               int m, int n, int k, long long ldc, int dtype, int group_n,
                               int max_ctas, int *status, cudaStream_t stream);
 
+// Same product on CTA pairs: clusters of two CTAs own 256x256 tiles and issue
+// tcgen05.mma.cta_group::2. Takes the same tensor maps as launch_gemm_dense. `max_ctas` is
+// rounded down to an even number of CTAs.
+cudaError_t launch_gemm_dense_pair(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, float *c,
+                                   int m, int n, int k, long long ldc, int dtype, int group_n,
+                                   int max_ctas, int *status, cudaStream_t stream);
+
+// Whether the dense variant runs on CTA pairs for this problem.
+bool dense_uses_pairs(long long m, long long n, long long k, int sm_count);
+
 struct SkinnyShape {
   int block_n;     // columns of C per work unit
   int block_k;

@@ -307,29 +307,23 @@ SkinnyShape skinny_shape(int m) {
 }
 
 int skinny_choose_splits(int n, int k, int sm_count) {
-  // Pick the split count whose units fill the resident CTAs most evenly; every split
-  // keeps at least 4 k-blocks so that its ring fills, and ties go to fewer splits
-  // (less partial-sum traffic).
+  // Splitting k costs a round trip of partial sums through L2 and a counter handshake per
+  // unit, and measurements show that B streams at full HBM rate as soon as roughly 0.8 CTAs
+  // per SM are loading. So: no split when there are that many column blocks (8x16384x8192:
+  // 128 blocks, 43 us unsplit against 52-66 us with 2-16 splits); otherwise just enough
+  // splits to get there, each keeping at least 4 k-blocks so that its ring fills.
   const int n_tiles = (n + skinny::kBlockN - 1) / skinny::kBlockN;
   const int kb_total = (k + skinny::kBlockK - 1) / skinny::kBlockK;
-  const long long slots = static_cast<long long>(sm_count) * skinny::kCtasPerSm;
-  int best = 1;
-  double best_eff = 0.0;
-  for (int s = 1; s <= 32; ++s) {
-    if (s > 1 && kb_total / s < 4)
-      break;
-    const long long units = static_cast<long long>(n_tiles) * s;
-    const long long waves = (units + slots - 1) / slots;
-    // Longest CTA does `waves` units of ceil(kb_total/s) k-blocks.
-    const double longest = static_cast<double>(waves) * ((kb_total + s - 1) / s);
-    const double ideal = static_cast<double>(n_tiles) * kb_total / static_cast<double>(slots);
-    const double eff = ideal / longest;
-    if (eff > best_eff + 0.02) {
-      best_eff = eff;
-      best = s;
-    }
-  }
-  return best;
+  const int wanted_units = sm_count * 4 / 5 > 0 ? sm_count * 4 / 5 : 1;
+  if (n_tiles >= wanted_units)
+    return 1;
+  int splits = (wanted_units + n_tiles - 1) / n_tiles;
+  const int most = kb_total / 4 > 0 ? kb_total / 4 : 1;
+  if (splits > most)
+    splits = most;
+  if (splits > 32)
+    splits = 32;
+  return splits < 1 ? 1 : splits;
 }
 
 size_t skinny_partials_bytes(int m, int n, int splits) {

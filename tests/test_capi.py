@@ -57,13 +57,15 @@ def test_missing_device_is_reported_not_papered_over() -> None:
 
 def test_plan_chooses_variants() -> None:
     dense = cuda.plan_gemm(8192, 8192, 8192, "float16")
-    assert (dense.variant, dense.tiles_m, dense.tiles_n, dense.grid, dense.splits) == ("dense", 64, 32, 148, 1)
+    assert (dense.variant, dense.tiles_m, dense.tiles_n, dense.grid, dense.splits) == ("dense", 32, 32, 148, 1)  # 256x256 pair tiles
     assert dense.kernel_launches == 1 and dense.scratch_bytes == 0 and not dense.repack_a
     small = cuda.plan_gemm(100, 300, 64, "bfloat16")
     assert (small.variant, small.tiles_m, small.tiles_n, small.grid) == ("dense", 1, 2, 2)
     skinny = cuda.plan_gemm(8, 16384, 8192, "float16")
-    assert skinny.variant == "skinny" and skinny.tiles_n == 128 and skinny.splits >= 2
-    assert skinny.grid <= 296 and skinny.scratch_bytes == skinny.splits * 8 * 16384 * 4
+    assert (skinny.variant, skinny.tiles_n, skinny.splits, skinny.grid) == ("skinny", 128, 1, 128)
+    assert skinny.scratch_bytes == 0  # enough column blocks to fill the GPU: no split over k
+    narrow = cuda.plan_gemm(8, 2048, 8192, "float16")
+    assert narrow.splits == 8 and narrow.grid == 128 and narrow.scratch_bytes == 8 * 8 * 2048 * 4
     assert cuda.plan_gemm(64, 512, 512, "float16").variant == "skinny"
     assert cuda.plan_gemm(65, 512, 512, "float16").variant == "dense"
     assert cuda.plan_gemm(8, 512, 512, "float16", variant=cuda.VARIANT_DENSE).variant == "dense"
@@ -73,8 +75,8 @@ def test_plan_chooses_variants() -> None:
 def test_plan_flags_pitches_that_need_a_repack() -> None:
     ragged = cuda.plan_gemm(4095, 3073, 1031, "bfloat16")
     assert ragged.variant == "dense" and ragged.repack_a and ragged.repack_b and ragged.kernel_launches == 3
-    assert (ragged.tiles_m, ragged.tiles_n) == (32, 13)
-    assert ragged.scratch_bytes >= 4095 * 1032 * 2 + 1031 * 3080 * 2
+    assert (ragged.tiles_m, ragged.tiles_n) == (16, 13)
+    assert ragged.scratch_bytes >= 4095 * 1088 * 2 + 1031 * 3136 * 2
     padded = cuda.plan_gemm(4095, 3073, 1031, "bfloat16", lda=1032, ldb=3080)
     assert not padded.repack_a and not padded.repack_b and padded.kernel_launches == 1
     misaligned_base = cuda.plan_gemm(128, 256, 64, "float16", a=0x1002)

@@ -67,14 +67,19 @@ def test_static_scratch_entry_point_matches_the_allocating_one(gpu_ctx) -> None:
             buf.free()
 
 
-def test_static_scratch_entry_point_rejects_what_does_not_fit(gpu_ctx) -> None:
+def test_static_scratch_entry_point_rejects_what_does_not_fit(gpu_ctx, monkeypatch) -> None:
+    """Rejections happen during validation, before anything is launched, so placeholder
+    addresses are safe here."""
     lib = cuda.library()
     text = ctypes.create_string_buffer(512)
-    # 64 x 131072 with several splits needs far more than 8 MiB of partial sums.
-    args = cuda._GemmArgs(64, 131072, 8192, cuda.F16, 0, 0x7F0000000000, 8192, 0x7F1000000000, 131072,
-                          0x7F8000000000, 131072)
+    # Forcing 32 splits makes 64 x 16384 need 128 MiB of partial sums, far beyond the 8 MiB array.
+    monkeypatch.setenv("HC_CUDA_SKINNY_SPLITS", "32")
+    args = cuda._GemmArgs(64, 16384, 8192, cuda.F16, 0, 0x7F0000000000, 8192, 0x7F1000000000, 16384,
+                          0x7F8000000000, 16384)
+    assert cuda.plan_gemm(64, 16384, 8192, "float16").splits == 32
     status = lib.hcCudaGemmSkinnyStatic(ctypes.byref(args), None, 1, text, len(text))
     assert status == 2 and b"static" in text.value
+    monkeypatch.delenv("HC_CUDA_SKINNY_SPLITS")
     # An unaligned pitch would need a repack, i.e. scratch the entry point does not have.
     args = cuda._GemmArgs(8, 1001, 512, cuda.F16, 0, 0x7F0000000000, 512, 0x7F1000000000, 1001,
                           0x7F8000000000, 1001)
