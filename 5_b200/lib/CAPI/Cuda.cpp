@@ -100,6 +100,14 @@ struct HcCudaContext {
   size_t counters_bytes = 0;
   void *stage[3] = {nullptr, nullptr, nullptr};  // device staging for host-buffer calls
   size_t stage_bytes[3] = {0, 0, 0};
+  // Host-buffer calls on large dense problems overlap copies with compute: A arrives in row
+  // panels on `copy_in`, each panel's GEMM runs on `stream`, its rows of C leave on `copy_out`.
+  static constexpr int kMaxPanels = 8;
+  cudaStream_t copy_in = nullptr;
+  cudaStream_t copy_out = nullptr;
+  cudaEvent_t panel_in[kMaxPanels] = {};
+  cudaEvent_t panel_done[kMaxPanels] = {};
+  cudaEvent_t fence_event = nullptr;
   EncodeTiledFn encode = nullptr;
   int group_n = 8;
   ncclComm_t comm = nullptr;
@@ -396,6 +404,19 @@ int enqueue_gemm(HcCudaContext *ctx, const HcCudaGemmArgs *args, const HcCudaGem
   return HC_CUDA_OK;
 }
 
+int ensure_copy_streams(HcCudaContext *ctx) {
+  if (ctx->copy_in != nullptr)
+    return HC_CUDA_OK;
+  HC_TRY_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->copy_in, cudaStreamNonBlocking));
+  HC_TRY_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->copy_out, cudaStreamNonBlocking));
+  for (int i = 0; i < HcCudaContext::kMaxPanels; ++i) {
+    HC_TRY_CUDA(ctx, cudaEventCreateWithFlags(&ctx->panel_in[i], cudaEventDisableTiming));
+    HC_TRY_CUDA(ctx, cudaEventCreateWithFlags(&ctx->panel_done[i], cudaEventDisableTiming));
+  }
+  HC_TRY_CUDA(ctx, cudaEventCreateWithFlags(&ctx->fence_event, cudaEventDisableTiming));
+  return HC_CUDA_OK;
+}
+
 int synchronize_locked(HcCudaContext *ctx) {
   HC_TRY_CUDA(ctx, cudaMemcpyAsync(ctx->status_host, ctx->status_dev, sizeof(int),
                                    cudaMemcpyDeviceToHost, ctx->stream));
@@ -515,6 +536,18 @@ int hcCudaContextDestroy(HcCudaContext *ctx) {
     for (void *p : ctx->stage)
       if (p != nullptr)
         cudaFree(p);
+    for (int i = 0; i < HcCudaContext::kMaxPanels; ++i) {
+      if (ctx->panel_in[i] != nullptr)
+        cudaEventDestroy(ctx->panel_in[i]);
+      if (ctx->panel_done[i] != nullptr)
+        cudaEventDestroy(ctx->panel_done[i]);
+    }
+    if (ctx->fence_event != nullptr)
+      cudaEventDestroy(ctx->fence_event);
+    if (ctx->copy_in != nullptr)
+      cudaStreamDestroy(ctx->copy_in);
+    if (ctx->copy_out != nullptr)
+      cudaStreamDestroy(ctx->copy_out);
     if (ctx->scratch != nullptr)
       cudaFree(ctx->scratch);
     if (ctx->counters != nullptr)
@@ -720,10 +753,6 @@ int hcCudaGemmHost(HcCudaContext *ctx, const HcCudaGemmArgs *args) {
     return rc;
   if (int rc = ensure_stage(ctx, 2, m * ldc * 4))
     return rc;
-  HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(ctx->stage[0], lda * 2, args->a, static_cast<size_t>(args->lda) * 2,
-                                     k * 2, m, cudaMemcpyHostToDevice, ctx->stream));
-  HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(ctx->stage[1], ldb * 2, args->b, static_cast<size_t>(args->ldb) * 2,
-                                     n * 2, k, cudaMemcpyHostToDevice, ctx->stream));
   HcCudaGemmArgs dev = *args;
   dev.a = ctx->stage[0];
   dev.lda = static_cast<int64_t>(lda);
@@ -731,12 +760,64 @@ int hcCudaGemmHost(HcCudaContext *ctx, const HcCudaGemmArgs *args) {
   dev.ldb = static_cast<int64_t>(ldb);
   dev.c = static_cast<float *>(ctx->stage[2]);
   dev.ldc = static_cast<int64_t>(ldc);
-  if (int rc = plan_gemm(ctx, &dev, ctx->prop.multiProcessorCount, false, &plan))
+
+  const size_t total_bytes = (m * k + k * n) * 2 + m * n * 4;
+  const bool pipelined = plan.variant == HC_CUDA_GEMM_DENSE && m >= 1024 && total_bytes >= (size_t(32) << 20) &&
+                         std::getenv("HC_CUDA_NO_COPY_OVERLAP") == nullptr;
+  if (!pipelined) {
+    HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(ctx->stage[0], lda * 2, args->a, static_cast<size_t>(args->lda) * 2,
+                                       k * 2, m, cudaMemcpyHostToDevice, ctx->stream));
+    HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(ctx->stage[1], ldb * 2, args->b, static_cast<size_t>(args->ldb) * 2,
+                                       n * 2, k, cudaMemcpyHostToDevice, ctx->stream));
+    if (int rc = plan_gemm(ctx, &dev, ctx->prop.multiProcessorCount, false, &plan))
+      return rc;
+    if (int rc = enqueue_gemm(ctx, &dev, plan))
+      return rc;
+    HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(args->c, static_cast<size_t>(args->ldc) * 4, ctx->stage[2], ldc * 4,
+                                       n * 4, m, cudaMemcpyDeviceToHost, ctx->stream));
+    return synchronize_locked(ctx);
+  }
+
+  // Pipelined form. PCIe carries both directions at once, so the rows of C of one panel travel
+  // back while the next panels of A are still arriving and being multiplied; the call then takes
+  // about (time to send B) + max(time to send A, time to fetch C) instead of the sum of all four.
+  if (int rc = ensure_copy_streams(ctx))
     return rc;
-  if (int rc = enqueue_gemm(ctx, &dev, plan))
-    return rc;
-  HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(args->c, static_cast<size_t>(args->ldc) * 4, ctx->stage[2], ldc * 4,
-                                     n * 4, m, cudaMemcpyDeviceToHost, ctx->stream));
+  size_t panel_rows = (m + HcCudaContext::kMaxPanels - 1) / HcCudaContext::kMaxPanels;
+  panel_rows = static_cast<size_t>(round_up(static_cast<int64_t>(panel_rows), 256));
+  const int panels = static_cast<int>((m + panel_rows - 1) / panel_rows);
+  // Everything already queued on the main stream comes first.
+  HC_TRY_CUDA(ctx, cudaEventRecord(ctx->fence_event, ctx->stream));
+  HC_TRY_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_in, ctx->fence_event, 0));
+  HC_TRY_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_out, ctx->fence_event, 0));
+  HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(ctx->stage[1], ldb * 2, args->b, static_cast<size_t>(args->ldb) * 2,
+                                     n * 2, k, cudaMemcpyHostToDevice, ctx->copy_in));
+  for (int p = 0; p < panels; ++p) {
+    const size_t row0 = static_cast<size_t>(p) * panel_rows;
+    const size_t rows = row0 + panel_rows <= m ? panel_rows : m - row0;
+    const char *a_src = static_cast<const char *>(args->a) + row0 * static_cast<size_t>(args->lda) * 2;
+    char *a_dst = static_cast<char *>(ctx->stage[0]) + row0 * lda * 2;
+    HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(a_dst, lda * 2, a_src, static_cast<size_t>(args->lda) * 2, k * 2, rows,
+                                       cudaMemcpyHostToDevice, ctx->copy_in));
+    HC_TRY_CUDA(ctx, cudaEventRecord(ctx->panel_in[p], ctx->copy_in));
+    HC_TRY_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->panel_in[p], 0));
+    HcCudaGemmArgs part = dev;
+    part.m = static_cast<int64_t>(rows);
+    part.a = a_dst;
+    part.c = static_cast<float *>(ctx->stage[2]) + row0 * ldc;
+    HcCudaGemmPlanInfo part_plan;
+    if (int rc = plan_gemm(ctx, &part, ctx->prop.multiProcessorCount, false, &part_plan))
+      return rc;
+    if (int rc = enqueue_gemm(ctx, &part, part_plan))
+      return rc;
+    HC_TRY_CUDA(ctx, cudaEventRecord(ctx->panel_done[p], ctx->stream));
+    HC_TRY_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_out, ctx->panel_done[p], 0));
+    HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(args->c + row0 * static_cast<size_t>(args->ldc),
+                                       static_cast<size_t>(args->ldc) * 4, part.c, ldc * 4, n * 4, rows,
+                                       cudaMemcpyDeviceToHost, ctx->copy_out));
+  }
+  HC_TRY_CUDA(ctx, cudaEventRecord(ctx->fence_event, ctx->copy_out));
+  HC_TRY_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->fence_event, 0));
   return synchronize_locked(ctx);
 }
 

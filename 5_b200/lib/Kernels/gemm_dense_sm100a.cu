@@ -20,6 +20,7 @@
 // The kernel is persistent: CTA b processes tiles b, b+grid, ... in an order that walks
 // groups of `group_n` tile columns so that concurrently running CTAs share A and B
 // through L2.
+#include "gemm_epilogue.cuh"
 #include "gemm_launch.h"
 #include "sm100_ptx.cuh"
 
@@ -204,66 +205,8 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int row_base = tc.m_blk * kBlockM + quarter * 32;
       const int col_base = tc.n_blk * kBlockN;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kBlockN;
-#pragma unroll 1
-      for (int chunk = 0; chunk < kBlockN / 32; ++chunk) {
-        uint32_t r[32];
-        tmem_load_32x32b_x32(taddr + chunk * 32, r);
-        tmem_load_wait();
-        if (chunk == kBlockN / 32 - 1) {
-          // Accumulator fully read: hand it back to the MMA warp.
-          tcgen05_fence_before_sync();
-          __syncwarp();
-          if (lane == 0)
-            mbar_arrive(tmem_empty_bar(acc));
-        }
-        const int col0 = col_base + chunk * 32;
-        if (col0 >= n)
-          continue;  // warp-uniform
-        // Lane `lane` holds row (row_base+lane), columns col0..col0+31. Write it to the
-        // staging block with the 16-byte pieces XOR-swizzled by the row so that both this
-        // write and the row-wise read below are bank-conflict free.
-#pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          float4 v = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
-                                 __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
-          *reinterpret_cast<float4 *>(stage_gen + lane * 32 + ((q ^ (lane & 7)) << 2)) = v;
-        }
-        __syncwarp();
-        if (vec_ok) {
-          // 8 lanes cover one 128-byte row segment; a warp store covers 4 rows.
-          const int piece = lane & 7;
-          const int col = col0 + piece * 4;
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int rr = i * 4 + (lane >> 3);
-            const int row = row_base + rr;
-            const float4 v =
-                *reinterpret_cast<const float4 *>(stage_gen + rr * 32 + ((piece ^ (rr & 7)) << 2));
-            if (row < m) {
-              float *dst = c + static_cast<long long>(row) * ldc + col;
-              if (col + 3 < n) {
-                __stcs(reinterpret_cast<float4 *>(dst), v);
-              } else {
-                if (col < n) __stcs(dst, v.x);
-                if (col + 1 < n) __stcs(dst + 1, v.y);
-                if (col + 2 < n) __stcs(dst + 2, v.z);
-              }
-            }
-          }
-        } else {
-          // Row pitch or base not 16-byte aligned: one 128-byte row segment per store,
-          // 32-bit per lane.
-          const int col = col0 + lane;
-#pragma unroll 4
-          for (int rr = 0; rr < 32; ++rr) {
-            const int row = row_base + rr;
-            const float v = stage_gen[rr * 32 + ((((lane >> 2) ^ (rr & 7)) << 2) | (lane & 3))];
-            if (row < m && col < n)
-              __stcs(c + static_cast<long long>(row) * ldc + col, v);
-          }
-        }
-        __syncwarp();
-      }
+      drain_accumulator_rows<kBlockN>(taddr, stage_gen, c, ldc, m, n, row_base, col_base, vec_ok, lane,
+                                      tmem_empty_bar(acc), /*release_remote=*/false);
     }
   }
 

@@ -6,8 +6,8 @@
 // both ways), and written so that 8 lanes cover one 128-byte row segment: coalesced 128-bit
 // stores, four rows per warp instruction. Rows >= m and columns >= n are predicated off, which
 // is the clipped store of the hc kernel (examples/amdgpu_gfx11_wmma_matmul.py:284-298). When C's
-// base or pitch is not 16-byte aligned the same data goes out as 32-bit stores, one 128-byte row
-// segment per instruction.
+// base or pitch is not 16-byte aligned the rows are still written with aligned 128-bit stores, one row
+// segment per instruction, after a per-row peel to the next 16-byte boundary.
 #pragma once
 
 #include "sm100_ptx.cuh"
@@ -67,13 +67,51 @@ __device__ __forceinline__ void drain_accumulator_rows(uint32_t taddr, float *st
         }
       }
     } else {
-      const int col = col0 + lane;
-#pragma unroll 4
-      for (int rr = 0; rr < 32; ++rr) {
-        const int row = row_base + rr;
-        const float v = stage[rr * 32 + ((((lane >> 2) ^ (rr & 7)) << 2) | (lane & 3))];
-        if (row < m && col < n)
-          __stcs(c + static_cast<long long>(row) * ldc + col, v);
+      // C's rows do not start on 16-byte boundaries (odd pitch or base). Each row segment is
+      // still written mostly with aligned 128-bit stores: `shift` elements bring the address
+      // to a 16-byte boundary, then up to 8 aligned float4, and the few elements left over at
+      // both ends go out as 32-bit stores. 8 lanes serve one row, 4 rows per instruction.
+      const int piece = lane & 7;
+      // Phase (in elements, mod 4) of the address of C[row_base, col0]; it advances by ldc mod 4
+      // per row.
+      const unsigned phase0 = (static_cast<unsigned>(reinterpret_cast<uintptr_t>(c) >> 2) +
+                               static_cast<unsigned>(row_base) * static_cast<unsigned>(ldc & 3) +
+                               static_cast<unsigned>(col0)) & 3u;
+      const unsigned phase_step = static_cast<unsigned>(ldc & 3);
+      float *tile_dst = c + static_cast<long long>(row_base) * ldc + col0;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int rr = i * 4 + (lane >> 3);
+        const int shift = static_cast<int>((4u - ((phase0 + static_cast<unsigned>(rr) * phase_step) & 3u)) & 3u);
+        const float *src = stage + rr * 32;
+        const int swz = rr & 7;
+        if (row_base + rr < m) {
+          float *dst = tile_dst + static_cast<long long>(rr) * ldc;
+          const int e0 = shift + piece * 4;
+          if (e0 + 3 < 32) {
+            // Elements e0..e0+3 sit in staging pieces (e0>>2) and (e0>>2)+1, split at 4-shift.
+            const float4 lo = *reinterpret_cast<const float4 *>(src + (((e0 >> 2) ^ swz) << 2));
+            const float4 hi = *reinterpret_cast<const float4 *>(src + ((((e0 >> 2) + (shift != 0 ? 1 : 0)) ^ swz) << 2));
+            float4 v;
+            if (shift == 0) v = lo;
+            else if (shift == 1) v = make_float4(lo.y, lo.z, lo.w, hi.x);
+            else if (shift == 2) v = make_float4(lo.z, lo.w, hi.x, hi.y);
+            else v = make_float4(lo.w, hi.x, hi.y, hi.z);
+            if (col0 + e0 + 3 < n) {
+              __stcs(reinterpret_cast<float4 *>(dst + e0), v);
+            } else {
+              if (col0 + e0 < n) __stcs(dst + e0, v.x);
+              if (col0 + e0 + 1 < n) __stcs(dst + e0 + 1, v.y);
+              if (col0 + e0 + 2 < n) __stcs(dst + e0 + 2, v.z);
+            }
+          }
+          if (shift != 0 && piece < 4) {
+            // Elements [0, shift) before the first aligned group and [28 + shift, 32) after the last.
+            const int e = piece < shift ? piece : 28 + piece;
+            if (col0 + e < n)
+              __stcs(dst + e, src[(((e >> 2) ^ swz) << 2) | (e & 3)]);
+          }
+        }
       }
     }
     __syncwarp();

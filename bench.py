@@ -73,6 +73,10 @@ class ClockSampler:
     """Samples SM clock and throttle reasons of one GPU in a background thread (read-only)."""
 
     REASONS = {
+        0x0000000000000001: "gpu_idle",
+        0x0000000000000002: "applications_clocks_setting",
+        0x0000000000000010: "sync_boost",
+        0x0000000000000100: "display_clock_setting",
         0x0000000000000004: "sw_power_cap",
         0x0000000000000008: "hw_slowdown",
         0x0000000000000020: "sw_thermal_slowdown",
@@ -136,7 +140,7 @@ class ClockSampler:
             mask |= reasons
         names = sorted(name for bit, name in self.REASONS.items() if mask & bit)
         return {"sm_mhz": clocks[len(clocks) // 2], "sm_max_mhz": self.sm_max_mhz, "reasons": names,
-                "samples": len(inside)}
+                "samples": len(inside), "sm_mhz_min": clocks[0], "sm_mhz_highest": clocks[-1]}
 
 
 # ---------------------------------------------------------------- distributed plumbing ---
@@ -245,6 +249,42 @@ def time_numpy_matmul(a: np.ndarray, b: np.ndarray, budget_rows: int = 8192) -> 
         pass
     return {"value": workloads.flops(rows, b.shape[1], a.shape[1]) / seconds / 1e12, "unit": UNIT,
             "threads": threads, "seconds": seconds, "sample": f"{rows}x{b.shape[1]}x{a.shape[1]} float32 matmul"}
+
+
+def time_cublas(a: np.ndarray, b: np.ndarray, steps: int) -> dict:
+    """Library yardstick, same protocol as the timed region: cuBLAS through torch.mm on the same
+    inputs, once with fp32 output (the same problem as the hc kernel) and once with 16-bit output
+    (what the pod's measured tensor peak was taken with). Context only; never on the hot path."""
+    try:
+        import torch
+    except Exception as exc:  # pragma: no cover
+        return {"error": f"{type(exc).__name__}: {exc}"}
+    if a.dtype.name == "bfloat16":
+        ta = torch.from_numpy(a.view(np.uint16).copy()).view(torch.bfloat16).cuda()
+        tb = torch.from_numpy(b.view(np.uint16).copy()).view(torch.bfloat16).cuda()
+    else:
+        ta, tb = torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda()
+    flops = workloads.flops(a.shape[0], b.shape[1], a.shape[1])
+    out = {}
+    variants = {"out_16bit": lambda: torch.mm(ta, tb)}
+    try:
+        torch.mm(ta, tb, out_dtype=torch.float32)
+        variants["out_fp32"] = lambda: torch.mm(ta, tb, out_dtype=torch.float32)
+    except Exception as exc:
+        out["out_fp32"] = {"error": f"{type(exc).__name__}: {exc}"}
+    for name, fn in variants.items():
+        for _ in range(5):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        out[name] = {"ms_per_step": ms, "tflops": flops / (ms * 1e-3) / 1e12}
+    return out
 
 
 # ---------------------------------------------------------------- arms -------------------
@@ -433,7 +473,8 @@ def run_gpu_arm(args, ranks: Ranks) -> None:
         peak = float(peaks["bf16_tflops_sustained"] if long_step else peaks["bf16_tflops"])
         roofline = {"bound": "tensor", "achieved": kernel_tflops, "peak": peak, "unit": "TFLOP/s",
                     "frac": kernel_tflops / peak, "traffic": NCU_DRAM_TRAFFIC_BYTES.get(name),
-                    "kernel": "gemm_dense_kernel", "flops_per_launch": local_flops,
+                    "kernel": "gemm_dense_pair_kernel" if m > 128 and plan.tiles_m == -(-m // 256)
+                    else "gemm_dense_kernel", "flops_per_launch": local_flops,
                     "peak_source": f"{peaks_source} cuBLAS bf16 8192^3, {'sustained' if long_step else 'burst'}",
                     "frac_of_sustained_peak": kernel_tflops / float(peaks["bf16_tflops_sustained"]),
                     "frac_of_nominal": kernel_tflops / NOMINAL_PEAK_TFLOPS}
@@ -460,6 +501,8 @@ def run_gpu_arm(args, ranks: Ranks) -> None:
     }
     if gather is not None:
         line["all_gather"] = gather
+    if args.cublas and ranks.world == 1:
+        line["cublas"] = time_cublas(a, b, args.steps)
     if ranks.world == 1 and not args.no_cpu_baseline:
         baseline = time_cpu_oracle(a, b)
         baseline["numpy_f32_matmul"] = time_numpy_matmul(a, b)
@@ -477,6 +520,8 @@ def main() -> int:
     parser.add_argument("--e2e-steps", type=int, default=5)
     parser.add_argument("--no-gather", action="store_true")
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--cublas", action="store_true",
+                        help="also time cuBLAS (torch.mm) on the same inputs with the same loop, for context")
     parser.add_argument("--quick", action="store_true",
                         help="timed region and parity only (for profiler captures): no e2e, CPU or gather legs")
     args = parser.parse_args()

@@ -1,0 +1,95 @@
+"""The N-sharded product on two GPUs of one box: one process per GPU, each computing its own
+column slab through the C ABI, then an NCCL all-gather of the C slabs. Skipped on a box with
+fewer than two GPUs. NVLS is switched off so that a rank that dies never leaves NVLink multicast
+state behind."""
+
+from __future__ import annotations
+
+import multiprocessing as mp
+import os
+import sys
+import time
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from conftest import PACKAGE, REPO
+
+pytestmark = pytest.mark.gpu
+
+M, K, N = 512, 1024, 4096
+
+
+def _rank_main(rank: int, world: int, out_dir: str) -> None:
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    for entry in (str(REPO), str(PACKAGE)):
+        if entry not in sys.path:
+            sys.path.insert(0, entry)
+    import workloads
+    from examples.b200_wmma_matmul import compiled_for
+    from hc import cuda
+    from hc.distributed import ShardedMatmul, init_communicator
+
+    ctx = cuda.Context(rank)
+    id_file = Path(out_dir) / "nccl_id.bin"
+
+    def broadcast(payload):
+        if payload is not None:
+            tmp = id_file.with_suffix(".tmp")
+            tmp.write_bytes(payload)
+            tmp.rename(id_file)
+            return payload
+        deadline = time.time() + 60
+        while not id_file.exists():
+            if time.time() > deadline:
+                raise TimeoutError("rank 0 never published the communicator id")
+            time.sleep(0.05)
+        return id_file.read_bytes()
+
+    init_communicator(ctx, world, rank, broadcast)
+    sharded = ShardedMatmul(compiled_for("float16"), ctx, N, world, rank, align=workloads.SHARDED_BLOCK_COLUMNS)
+    a, b_slab = workloads.make_sharded_inputs(sharded.slab.begin, sharded.slab.end, m=M, k=K)
+    da = ctx.to_device(a)
+    db = ctx.to_device(b_slab)
+    dc = ctx.empty((M, sharded.slab.width), np.float32)
+    sharded.run(da, db, dc)
+    gathered = ctx.empty((world, M, sharded.slab.width), np.float32)
+    sharded.all_gather(dc, gathered)
+    ctx.synchronize()
+    np.save(Path(out_dir) / f"gathered_{rank}.npy", gathered.to_numpy())
+    ctx.comm_destroy()
+    ctx.close()
+
+
+def test_two_gpus_shard_and_gather(tmp_path) -> None:
+    from hc import cuda
+
+    if cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import workloads
+    from hc.distributed import assemble_row_major
+    from oracle import cpu_ref
+
+    world = 2
+    spawn = mp.get_context("spawn")
+    procs = [spawn.Process(target=_rank_main, args=(r, world, str(tmp_path))) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=300)
+    for p in procs:
+        if p.is_alive():
+            p.kill()
+            pytest.fail("a rank did not finish")
+        assert p.exitcode == 0
+    a, b = workloads.make_sharded_inputs(0, N, m=M, k=K)
+    expect = cpu_ref.matmul_k_ascending(a, b)
+    bound = np.abs(a.astype(np.float64)) @ np.abs(b.astype(np.float64))
+    first = None
+    for r in range(world):
+        full = assemble_row_major(np.load(tmp_path / f"gathered_{r}.npy"))
+        assert (np.abs(full.astype(np.float64) - expect) <= 1e-2 * bound + 1e-30).all()
+        assert workloads.check_against_float64(full, a, b)["ok"]
+        first = full if first is None else first
+        assert np.array_equal(full, first)  # every rank holds the same gathered C
