@@ -12,6 +12,7 @@ ndarray of the same shape and dtype that already lives on the GPU.
 
 from __future__ import annotations
 
+import functools
 import inspect
 from dataclasses import dataclass
 from typing import Any
@@ -124,24 +125,32 @@ def _resolve_shape(spec: Any, names: dict[str, int], what: str) -> tuple[int, ..
     return tuple(_resolve_dim(v, names, what) for v in values)
 
 
+@functools.lru_cache(maxsize=256)
+def _launch_signature(kernel_fn: Any) -> tuple[inspect.Signature | None, dict[str, Any]]:
+    """Signature without the group parameter, and resolved annotations; fixed per kernel."""
+    params = list(inspect.signature(kernel_fn).parameters.values())
+    if not params:
+        return None, {}
+    return inspect.Signature(params[1:]), resolved_annotations(kernel_fn)
+
+
 def prepare_launch(kernel_fn: Any, args: tuple[Any, ...], kwargs: dict[str, Any],
                    literal_bindings: dict[str, int] | None = None) -> PreparedLaunch:
     """Binds a call to `kernel_fn` (without the group parameter) and checks its geometry."""
     meta = getattr(kernel_fn, "__hc_kernel__", None)
     if meta is None:
         raise LaunchError("launch() expects a function decorated with @kernel")
-    params = list(inspect.signature(kernel_fn).parameters.values())
-    if not params:
+    signature, annotations = _launch_signature(kernel_fn)
+    if signature is None:
         raise LaunchError("kernel must accept a CurrentGroup parameter")
     try:
-        bound = inspect.Signature(params[1:]).bind(*args, **kwargs)
+        bound = signature.bind(*args, **kwargs)
     except TypeError as exc:
         raise LaunchError(str(exc)) from exc
 
     store = _ForeignBindings()
     for name, value in (literal_bindings or {}).items():
         store.bind(name, int(value), "hc.compile(symbols=...)")
-    annotations = resolved_annotations(kernel_fn)
     for name, value in bound.arguments.items():
         spec = annotations.get(name)
         if type(spec).__name__ == "BufferSpec":

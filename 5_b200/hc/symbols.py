@@ -56,11 +56,12 @@ class NonConstantError(SymbolError):
 class Expr:
     """Immutable expression tree over integer symbols and rational constants."""
 
-    __slots__ = ("_op", "_args")
+    __slots__ = ("_op", "_args", "_free")
 
     def __init__(self, op: str, args: tuple[Any, ...]) -> None:
         self._op = op
         self._args = args
+        self._free: frozenset[Symbol] | None = None  # filled on first use; nodes are immutable
 
     # -- structure ----------------------------------------------------------------------
     @property
@@ -72,6 +73,8 @@ class Expr:
         return tuple(arg for arg in self._args if isinstance(arg, Expr))
 
     def free_symbols(self) -> frozenset["Symbol"]:
+        if self._free is not None:
+            return self._free
         found: set[Symbol] = set()
         stack: list[Expr] = [self]
         while stack:
@@ -79,7 +82,8 @@ class Expr:
             if isinstance(node, Symbol):
                 found.add(node)
             stack.extend(node.children)
-        return frozenset(found)
+        self._free = frozenset(found)
+        return self._free
 
     def _key(self) -> tuple[Any, ...]:
         return (self._op, tuple(a._key() if isinstance(a, Expr) else a for a in self._args))

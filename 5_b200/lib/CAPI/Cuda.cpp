@@ -226,7 +226,7 @@ int plan_gemm(const HcCudaContext *ctx, const HcCudaGemmArgs *args, int sm_count
     scratch += round_up(m * round_up(k, kRepackPitchElems) * 2, 1024);
   if (plan->repack_b)
     scratch += round_up(k * round_up(n, kRepackPitchElems) * 2, 1024);
-  plan->kernel_launches = 1 + plan->repack_a + plan->repack_b;
+  plan->kernel_launches = 1 + ((plan->repack_a || plan->repack_b) ? 1 : 0);
 
   if (variant == HC_CUDA_GEMM_DENSE) {
     const hc::sm100::DenseTileShape t = hc::sm100::dense_tile_shape();
@@ -348,19 +348,34 @@ int enqueue_gemm(HcCudaContext *ctx, const HcCudaGemmArgs *args, const HcCudaGem
   const void *b = args->b;
   int64_t lda = args->lda, ldb = args->ldb;
   char *cursor = static_cast<char *>(ctx->scratch);
-  if (plan.repack_a) {
-    const int64_t ld = round_up(k, kRepackPitchElems);
-    HC_TRY_CUDA(ctx, hc::sm100::launch_repack_pitch(a, lda, cursor, ld, m, k, ctx->stream));
-    a = cursor;
-    lda = ld;
-    cursor += round_up(static_cast<int64_t>(m) * ld * 2, 1024);
-  }
-  if (plan.repack_b) {
-    const int64_t ld = round_up(n, kRepackPitchElems);
-    HC_TRY_CUDA(ctx, hc::sm100::launch_repack_pitch(b, ldb, cursor, ld, k, n, ctx->stream));
-    b = cursor;
-    ldb = ld;
-    cursor += round_up(static_cast<int64_t>(k) * ld * 2, 1024);
+  if (plan.repack_a || plan.repack_b) {
+    // One launch copies whichever operands need it into scratch with 128-byte-aligned pitches.
+    const void *src_a = nullptr, *src_b = nullptr;
+    char *dst_a = nullptr, *dst_b = nullptr;
+    int64_t pitch_a = 0, pitch_b = 0;
+    if (plan.repack_a) {
+      pitch_a = round_up(k, kRepackPitchElems);
+      src_a = a;
+      dst_a = cursor;
+      cursor += round_up(static_cast<int64_t>(m) * pitch_a * 2, 1024);
+    }
+    if (plan.repack_b) {
+      pitch_b = round_up(n, kRepackPitchElems);
+      src_b = b;
+      dst_b = cursor;
+      cursor += round_up(static_cast<int64_t>(k) * pitch_b * 2, 1024);
+    }
+    HC_TRY_CUDA(ctx, hc::sm100::launch_repack_pitch_two(src_a, lda, dst_a, pitch_a, plan.repack_a ? m : 0, k,
+                                                        src_b, ldb, dst_b, pitch_b, plan.repack_b ? k : 0, n,
+                                                        ctx->stream));
+    if (plan.repack_a) {
+      a = dst_a;
+      lda = pitch_a;
+    }
+    if (plan.repack_b) {
+      b = dst_b;
+      ldb = pitch_b;
+    }
   }
 
   CUtensorMap tmap_a, tmap_b;

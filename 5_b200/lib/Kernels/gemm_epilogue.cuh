@@ -6,8 +6,8 @@
 // both ways), and written so that 8 lanes cover one 128-byte row segment: coalesced 128-bit
 // stores, four rows per warp instruction. Rows >= m and columns >= n are predicated off, which
 // is the clipped store of the hc kernel (examples/amdgpu_gfx11_wmma_matmul.py:284-298). When C's
-// base or pitch is not 16-byte aligned the rows are still written with aligned 128-bit stores, one row
-// segment per instruction, after a per-row peel to the next 16-byte boundary.
+// base or pitch is not 16-byte aligned the rows are still written with aligned 128-bit stores:
+// each row is rotated to its own 16-byte phase while it is staged.
 #pragma once
 
 #include "sm100_ptx.cuh"
@@ -16,27 +16,39 @@ namespace hc {
 namespace sm100 {
 
 // Writes one 32-column chunk (already in registers, lane = row) of this warp's 32 rows to C.
-__device__ __forceinline__ void write_chunk(const uint32_t (&r)[32], int chunk, float *stage,
+// Stages this lane's 32 values with the row rotated left by kShift elements, so that the
+// 16-byte groups of the row *in memory* (which start kShift elements into the chunk) land on
+// 16-byte pieces of the staging block.
+template <int kShift>
+__device__ __forceinline__ void stage_row_shifted(const uint32_t (&r)[32], float *buf, int lane) {
+#pragma unroll
+  for (int q = 0; q < (kShift == 0 ? 8 : 7); ++q) {
+    const float4 v = make_float4(__uint_as_float(r[4 * q + kShift]), __uint_as_float(r[4 * q + kShift + 1]),
+                                 __uint_as_float(r[4 * q + kShift + 2]), __uint_as_float(r[4 * q + kShift + 3]));
+    *reinterpret_cast<float4 *>(buf + lane * 32 + ((q ^ (lane & 7)) << 2)) = v;
+  }
+}
+
+// Writes one 32-column chunk (already in registers, lane = row) of this warp's 32 rows to C.
+// `carry` holds the last three values of this lane's row from the previous chunk (odd-pitch
+// path only); `last_chunk` says that no further chunk of the tile follows.
+__device__ __forceinline__ void write_chunk(const uint32_t (&r)[32], int chunk, bool last_chunk, float *buf,
                                             float *__restrict__ c, long long ldc, int m, int n,
-                                            int row_base, int col_base, bool vec_ok, int lane) {
+                                            int row_base, int col_base, bool vec_ok, int lane,
+                                            float (&carry)[3]) {
   const int col0 = col_base + chunk * 32;
   if (col0 >= n)
     return;  // warp-uniform
-#pragma unroll
-  for (int q = 0; q < 8; ++q) {
-    const float4 v = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
-                                 __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
-    *reinterpret_cast<float4 *>(stage + lane * 32 + ((q ^ (lane & 7)) << 2)) = v;
-  }
-  __syncwarp();
+  const int piece = lane & 7;
   if (vec_ok) {
-    const int piece = lane & 7;
+    stage_row_shifted<0>(r, buf, lane);
+    __syncwarp();
     const int col = col0 + piece * 4;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const int rr = i * 4 + (lane >> 3);
       const int row = row_base + rr;
-      const float4 v = *reinterpret_cast<const float4 *>(stage + rr * 32 + ((piece ^ (rr & 7)) << 2));
+      const float4 v = *reinterpret_cast<const float4 *>(buf + rr * 32 + ((piece ^ (rr & 7)) << 2));
       if (row < m) {
         float *dst = c + static_cast<long long>(row) * ldc + col;
         if (col + 3 < n) {
@@ -49,43 +61,82 @@ __device__ __forceinline__ void write_chunk(const uint32_t (&r)[32], int chunk, 
       }
     }
   } else {
-    // C's rows do not start on 16-byte boundaries (odd pitch or base). Each row segment is
-    // still written mostly with aligned 128-bit stores: `shift` elements bring the address
-    // to a 16-byte boundary, then up to 8 aligned float4, and the few elements left over at
-    // both ends go out as 32-bit stores. 8 lanes serve one row, 4 rows per instruction.
-    const int piece = lane & 7;
-    // Phase (in elements, mod 4) of the address of C[row_base, col0]; it advances by ldc mod 4
-    // per row.
+    // C's rows do not start on 16-byte boundaries (odd pitch or base). For row r, `shift(r)`
+    // elements separate C[r, col0] from the next 16-byte boundary. The lane that owns the row
+    // stages it rotated by that shift (so memory-aligned groups become staging pieces); the one
+    // group that straddles two chunks it writes itself, joining the end of the previous chunk
+    // with the start of this one, and only at the two ends of the tile row do single elements
+    // go out as 32-bit stores. The staged groups then leave exactly as on the aligned path:
+    // 8 lanes x 128-bit per row, four rows per instruction.
     const unsigned phase0 = (static_cast<unsigned>(reinterpret_cast<uintptr_t>(c) >> 2) +
                              static_cast<unsigned>(row_base) * static_cast<unsigned>(ldc & 3) +
                              static_cast<unsigned>(col0)) & 3u;
     const unsigned phase_step = static_cast<unsigned>(ldc & 3);
+    auto shift_of = [&](int rr) {
+      return static_cast<int>((4u - ((phase0 + static_cast<unsigned>(rr) * phase_step) & 3u)) & 3u);
+    };
     float *tile_dst = c + static_cast<long long>(row_base) * ldc + col0;
+    {
+      const int shift = shift_of(lane);
+      float *dst = tile_dst + static_cast<long long>(lane) * ldc;
+      const bool row_ok = row_base + lane < m;
+      if (shift == 0)
+        stage_row_shifted<0>(r, buf, lane);
+      else if (shift == 1)
+        stage_row_shifted<1>(r, buf, lane);
+      else if (shift == 2)
+        stage_row_shifted<2>(r, buf, lane);
+      else
+        stage_row_shifted<3>(r, buf, lane);
+      if (shift != 0 && row_ok) {
+        const float f0 = __uint_as_float(r[0]), f1 = __uint_as_float(r[1]), f2 = __uint_as_float(r[2]);
+        if (chunk == 0) {
+          // Elements before the first aligned group of the tile row.
+          if (col0 < n) __stcs(dst, f0);
+          if (shift >= 2 && col0 + 1 < n) __stcs(dst + 1, f1);
+          if (shift == 3 && col0 + 2 < n) __stcs(dst + 2, f2);
+        } else {
+          // The group that straddles the previous chunk and this one: its first 4 - shift
+          // elements were kept from the previous chunk in `carry`.
+          const float4 v = shift == 1 ? make_float4(carry[0], carry[1], carry[2], f0)
+                         : shift == 2 ? make_float4(carry[1], carry[2], f0, f1)
+                                      : make_float4(carry[2], f0, f1, f2);
+          float *group = dst + shift - 4;
+          if (col0 + shift - 1 < n) {
+            __stcs(reinterpret_cast<float4 *>(group), v);
+          } else {
+            // Only the elements left of column n exist (the previous chunk's are always inside).
+            __stcs(group, v.x);
+            if (col0 + shift - 3 < n) __stcs(group + 1, v.y);
+            if (col0 + shift - 2 < n) __stcs(group + 2, v.z);
+          }
+        }
+        if (last_chunk || col0 + 32 >= n) {
+          // No next chunk will complete the trailing group: write its elements singly.
+          for (int e = 28 + shift; e < 32; ++e)
+            if (col0 + e < n)
+              __stcs(dst + e, __uint_as_float(e == 29 ? r[29] : (e == 30 ? r[30] : r[31])));
+        }
+      }
+      carry[0] = __uint_as_float(r[29]);
+      carry[1] = __uint_as_float(r[30]);
+      carry[2] = __uint_as_float(r[31]);
+    }
+    __syncwarp();
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const int rr = i * 4 + (lane >> 3);
-      const int shift = static_cast<int>((4u - ((phase0 + static_cast<unsigned>(rr) * phase_step) & 3u)) & 3u);
-      const float *src = stage + rr * 32;
-      const int swz = rr & 7;
-      if (row_base + rr < m) {
-        float *dst = tile_dst + static_cast<long long>(rr) * ldc;
-        const int e0 = shift + piece * 4;
-        if (e0 + 3 < 32) {
-          auto elem = [&](int e) { return src[(((e >> 2) ^ swz) << 2) | (e & 3)]; };
-          const float4 v = make_float4(elem(e0), elem(e0 + 1), elem(e0 + 2), elem(e0 + 3));
-          if (col0 + e0 + 3 < n) {
-            __stcs(reinterpret_cast<float4 *>(dst + e0), v);
-          } else {
-            if (col0 + e0 < n) __stcs(dst + e0, v.x);
-            if (col0 + e0 + 1 < n) __stcs(dst + e0 + 1, v.y);
-            if (col0 + e0 + 2 < n) __stcs(dst + e0 + 2, v.z);
-          }
-        }
-        if (shift != 0 && piece < 4) {
-          // Elements [0, shift) before the first aligned group and [28 + shift, 32) after the last.
-          const int e = piece < shift ? piece : 28 + piece;
-          if (col0 + e < n)
-            __stcs(dst + e, src[(((e >> 2) ^ swz) << 2) | (e & 3)]);
+      const int shift = shift_of(rr);
+      const float4 v = *reinterpret_cast<const float4 *>(buf + rr * 32 + ((piece ^ (rr & 7)) << 2));
+      const int e0 = shift + piece * 4;
+      if (row_base + rr < m && e0 + 3 < 32) {
+        float *dst = tile_dst + static_cast<long long>(rr) * ldc + e0;
+        if (col0 + e0 + 3 < n) {
+          __stcs(reinterpret_cast<float4 *>(dst), v);
+        } else {
+          if (col0 + e0 < n) __stcs(dst, v.x);
+          if (col0 + e0 + 1 < n) __stcs(dst + 1, v.y);
+          if (col0 + e0 + 2 < n) __stcs(dst + 2, v.z);
         }
       }
     }
@@ -106,12 +157,13 @@ __device__ __forceinline__ void drain_accumulator_rows(uint32_t taddr, float *st
   constexpr int kChunks = kColumns / 32;
   static_assert(kChunks % 2 == 0, "chunks are processed in pairs");
   uint32_t ra[32], rb[32];
+  float carry[3] = {0.0f, 0.0f, 0.0f};
   tmem_load_32x32b_x32(taddr, ra);
 #pragma unroll 1
   for (int chunk = 0; chunk < kChunks; chunk += 2) {
     tmem_load_wait_for(ra);
     tmem_load_32x32b_x32(taddr + (chunk + 1) * 32, rb);
-    write_chunk(ra, chunk, stage, c, ldc, m, n, row_base, col_base, vec_ok, lane);
+    write_chunk(ra, chunk, false, stage, c, ldc, m, n, row_base, col_base, vec_ok, lane, carry);
     tmem_load_wait_for(rb);
     if (chunk + 2 < kChunks) {
       tmem_load_32x32b_x32(taddr + (chunk + 2) * 32, ra);
@@ -126,7 +178,7 @@ __device__ __forceinline__ void drain_accumulator_rows(uint32_t taddr, float *st
           mbar_arrive(release_bar);
       }
     }
-    write_chunk(rb, chunk + 1, stage, c, ldc, m, n, row_base, col_base, vec_ok, lane);
+    write_chunk(rb, chunk + 1, chunk + 2 >= kChunks, stage, c, ldc, m, n, row_base, col_base, vec_ok, lane, carry);
   }
 }
 

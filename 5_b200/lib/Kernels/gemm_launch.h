@@ -71,5 +71,10 @@ cudaError_t launch_gemm_skinny(const CUtensorMap &tmap_a, const CUtensorMap &tma
 cudaError_t launch_repack_pitch(const void *src, long long src_ld, void *dst, long long dst_ld,
                                 int rows, int cols, cudaStream_t stream);
 
+// Two such copies in one launch (either may be empty: rows or cols 0).
+cudaError_t launch_repack_pitch_two(const void *src0, long long src0_ld, void *dst0, long long dst0_ld,
+                                    int rows0, int cols0, const void *src1, long long src1_ld, void *dst1,
+                                    long long dst1_ld, int rows1, int cols1, cudaStream_t stream);
+
 } // namespace sm100
 } // namespace hc

@@ -16,43 +16,76 @@ namespace sm100 {
 
 namespace {
 
+struct RepackJob {
+  const uint16_t *src;
+  long long src_ld;
+  uint16_t *dst;
+  long long dst_ld;
+  int rows;
+  int cols;
+};
+
+// Blocks [0, blocks0) copy job0, the rest copy job1 (which may be empty): both operands of a
+// GEMM are repacked by one launch.
 __global__ void __launch_bounds__(256)
-repack_pitch_kernel(const uint16_t *__restrict__ src, long long src_ld, uint16_t *__restrict__ dst,
-                    long long dst_ld, int rows, int cols) {
-  const int pieces_per_row = (cols + 7) >> 3;
-  const long long total = static_cast<long long>(rows) * pieces_per_row;
-  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
-       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+repack_pitch_kernel(RepackJob job0, RepackJob job1, int blocks0) {
+  const bool second = static_cast<int>(blockIdx.x) >= blocks0;
+  const RepackJob job = second ? job1 : job0;
+  const long long block = second ? blockIdx.x - blocks0 : blockIdx.x;
+  const long long blocks = second ? gridDim.x - blocks0 : blocks0;
+  const int pieces_per_row = (job.cols + 7) >> 3;
+  const long long total = static_cast<long long>(job.rows) * pieces_per_row;
+  for (long long idx = block * blockDim.x + threadIdx.x; idx < total; idx += blocks * blockDim.x) {
     const int row = static_cast<int>(idx / pieces_per_row);
     const int col0 = static_cast<int>(idx - static_cast<long long>(row) * pieces_per_row) << 3;
-    const uint16_t *s = src + row * src_ld + col0;
+    const uint16_t *s = job.src + row * job.src_ld + col0;
     uint16_t v[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i)
-      v[i] = (col0 + i < cols) ? __ldg(s + i) : static_cast<uint16_t>(0);
+      v[i] = (col0 + i < job.cols) ? __ldg(s + i) : static_cast<uint16_t>(0);
     uint4 packed;
     packed.x = v[0] | (static_cast<uint32_t>(v[1]) << 16);
     packed.y = v[2] | (static_cast<uint32_t>(v[3]) << 16);
     packed.z = v[4] | (static_cast<uint32_t>(v[5]) << 16);
     packed.w = v[6] | (static_cast<uint32_t>(v[7]) << 16);
-    *reinterpret_cast<uint4 *>(dst + row * dst_ld + col0) = packed;
+    *reinterpret_cast<uint4 *>(job.dst + row * job.dst_ld + col0) = packed;
   }
+}
+
+int blocks_for(const RepackJob &job) {
+  if (job.rows <= 0 || job.cols <= 0)
+    return 0;
+  const long long total = static_cast<long long>(job.rows) * ((job.cols + 7) >> 3);
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148LL * 8)
+    blocks = 148LL * 8;
+  return static_cast<int>(blocks);
+}
+
+bool valid_destination(const RepackJob &job) {
+  return (job.dst_ld & 7) == 0 && (reinterpret_cast<uintptr_t>(job.dst) & 15) == 0;
 }
 
 } // namespace
 
 cudaError_t launch_repack_pitch(const void *src, long long src_ld, void *dst, long long dst_ld,
                                 int rows, int cols, cudaStream_t stream) {
-  if (rows <= 0 || cols <= 0)
+  return launch_repack_pitch_two(src, src_ld, dst, dst_ld, rows, cols, nullptr, 0, nullptr, 0, 0, 0, stream);
+}
+
+cudaError_t launch_repack_pitch_two(const void *src0, long long src0_ld, void *dst0, long long dst0_ld,
+                                    int rows0, int cols0, const void *src1, long long src1_ld, void *dst1,
+                                    long long dst1_ld, int rows1, int cols1, cudaStream_t stream) {
+  const RepackJob job0{static_cast<const uint16_t *>(src0), src0_ld, static_cast<uint16_t *>(dst0), dst0_ld,
+                       rows0, cols0};
+  const RepackJob job1{static_cast<const uint16_t *>(src1), src1_ld, static_cast<uint16_t *>(dst1), dst1_ld,
+                       rows1, cols1};
+  const int blocks0 = blocks_for(job0), blocks1 = blocks_for(job1);
+  if (blocks0 + blocks1 == 0)
     return cudaSuccess;
-  if ((dst_ld & 7) != 0 || (reinterpret_cast<uintptr_t>(dst) & 15) != 0)
+  if ((blocks0 > 0 && !valid_destination(job0)) || (blocks1 > 0 && !valid_destination(job1)))
     return cudaErrorInvalidValue;
-  const long long total = static_cast<long long>(rows) * ((cols + 7) >> 3);
-  long long blocks = (total + 255) / 256;
-  if (blocks > 148LL * 16)
-    blocks = 148LL * 16;
-  repack_pitch_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
-      static_cast<const uint16_t *>(src), src_ld, static_cast<uint16_t *>(dst), dst_ld, rows, cols);
+  repack_pitch_kernel<<<static_cast<unsigned>(blocks0 + blocks1), 256, 0, stream>>>(job0, job1, blocks0);
   return cudaGetLastError();
 }
 

@@ -470,13 +470,18 @@ def run_gpu_arm(args, ranks: Ranks) -> None:
                     "algorithmic_bytes_per_launch": algo_bytes, "peak_source": f"{peaks_source} HBM copy bandwidth",
                     "frac_of_nominal": achieved / NOMINAL_HBM_GBS}
     else:
-        long_step = args.steps * ms_per_step > 1000.0
-        peak = float(peaks["bf16_tflops_sustained"] if long_step else peaks["bf16_tflops"])
+        # Which measured cuBLAS figure the launch is compared with: the burst one for launches
+        # that ran at full clocks, the sustained one when the timed region ran under the power cap
+        # (sw_power_cap seen by NVML during it) or lasted longer than a second.
+        capped = "sw_power_cap" in clocks.get("reasons", []) or args.steps * ms_per_step > 1000.0
+        peak = float(peaks["bf16_tflops_sustained"] if capped else peaks["bf16_tflops"])
         roofline = {"bound": "tensor", "achieved": kernel_tflops, "peak": peak, "unit": "TFLOP/s",
                     "frac": kernel_tflops / peak, "traffic": NCU_DRAM_TRAFFIC_BYTES.get(name),
                     "kernel": "gemm_dense_pair_kernel" if m > 128 and plan.tiles_m == -(-m // 256)
                     else "gemm_dense_kernel", "flops_per_launch": local_flops,
-                    "peak_source": f"{peaks_source} cuBLAS bf16 8192^3, {'sustained' if long_step else 'burst'}",
+                    "peak_source": f"{peaks_source} cuBLAS bf16 8192^3 (16-bit output), "
+                                   f"{'sustained: the timed region ran under sw_power_cap' if capped else 'burst'}",
+                    "frac_of_burst_peak": kernel_tflops / float(peaks["bf16_tflops"]),
                     "frac_of_sustained_peak": kernel_tflops / float(peaks["bf16_tflops_sustained"]),
                     "frac_of_nominal": kernel_tflops / NOMINAL_PEAK_TFLOPS}
 

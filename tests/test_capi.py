@@ -74,7 +74,7 @@ def test_plan_chooses_variants() -> None:
 
 def test_plan_flags_pitches_that_need_a_repack() -> None:
     ragged = cuda.plan_gemm(4095, 3073, 1031, "bfloat16")
-    assert ragged.variant == "dense" and ragged.repack_a and ragged.repack_b and ragged.kernel_launches == 3
+    assert ragged.variant == "dense" and ragged.repack_a and ragged.repack_b and ragged.kernel_launches == 2
     assert (ragged.tiles_m, ragged.tiles_n) == (16, 13)
     assert ragged.scratch_bytes >= 4095 * 1088 * 2 + 1031 * 3136 * 2
     padded = cuda.plan_gemm(4095, 3073, 1031, "bfloat16", lda=1032, ldb=3080)

@@ -134,29 +134,31 @@ def test_zero_k_writes_zeros_and_empty_shapes_write_nothing() -> None:
     handle(np.zeros((5, 4), np.float16), np.zeros((4, 0), np.float16), c)
 
 
-@pytest.mark.parametrize("shape", [(130, 300, 70), (9, 300, 130)])
-def test_nothing_outside_c_is_written(gpu_ctx, shape) -> None:
+@pytest.mark.parametrize("frame", [(12, 4), (13, 3), (1, 1), (35, 0)])
+@pytest.mark.parametrize("shape", [(130, 300, 70), (9, 300, 130), (515, 770, 96)])
+def test_nothing_outside_c_is_written(gpu_ctx, shape, frame) -> None:
     """C sits inside a wider device matrix filled with a sentinel; after the launch only the
-    M x N window may differ, and A and B must be unchanged."""
+    M x N window may differ, and A and B must be unchanged. The frames cover a 16-byte-aligned
+    window as well as odd pitches and bases (rows that start on arbitrary 4-byte boundaries)."""
     m, n, k = shape
+    pad, col_off = frame
     a, b = random_inputs(m, n, k, "float16")
     da, db = gpu_ctx.to_device(a), gpu_ctx.to_device(b)
-    pad = 12
-    frame = cuda.DeviceBuffer(gpu_ctx, (m + 2, n + pad), np.float32)
-    frame.fill_bytes(0x7F)
+    frame_buf = cuda.DeviceBuffer(gpu_ctx, (m + 2, n + pad), np.float32)
+    frame_buf.fill_bytes(0x7F)
     window = cuda.DeviceBuffer.__new__(cuda.DeviceBuffer)
     window.ctx, window.shape, window.dtype, window.ndim = gpu_ctx, (m, n), np.dtype(np.float32), 2
     window.ld, window._rows = n + pad, m
     window.nbytes = 0  # the window does not own memory
-    window.ptr = frame.ptr + ((n + pad) + 4) * 4  # one row down, four columns in (16-byte aligned)
+    window.ptr = frame_buf.ptr + ((n + pad) + col_off) * 4  # one row down, col_off columns in
     gpu_ctx.gemm(da, db, window)
     gpu_ctx.synchronize()
-    whole = frame.to_numpy()
+    whole = frame_buf.to_numpy()
     sentinel = np.frombuffer(b"\x7f\x7f\x7f\x7f", np.float32)[0]
-    inside = whole[1 : m + 1, 4 : n + 4]
+    inside = whole[1 : m + 1, col_off : n + col_off]
     assert_close_to_oracle(np.ascontiguousarray(inside), a, b)
     mask = np.ones_like(whole, bool)
-    mask[1 : m + 1, 4 : n + 4] = False
+    mask[1 : m + 1, col_off : n + col_off] = False
     assert (whole[mask].view(np.uint32) == sentinel.view(np.uint32)).all()
     assert np.array_equal(da.to_numpy().view(np.uint16), a.view(np.uint16))
     assert np.array_equal(db.to_numpy().view(np.uint16), b.view(np.uint16))
@@ -164,11 +166,11 @@ def test_nothing_outside_c_is_written(gpu_ctx, shape) -> None:
 
 
 def test_unaligned_pitches_and_bases_on_device(gpu_ctx) -> None:
-    """Odd pitches (K=1031-like) and a base that is only 2-byte aligned take the repack path."""
+    """Odd pitches (K=1031-like) and a base that is only 2-byte aligned take the repack path (one copy launch for both operands, then the GEMM)."""
     m, n, k = 150, 333, 77
     a, b = random_inputs(m, n, k, "bfloat16")
     plan = gpu_ctx.plan(m, n, k, "bfloat16")
-    assert plan.repack_a and plan.repack_b and plan.kernel_launches == 3
+    assert plan.repack_a and plan.repack_b and plan.kernel_launches == 2
     da, db = gpu_ctx.to_device(a), gpu_ctx.to_device(b)
     dc = gpu_ctx.empty((m, n), np.float32)
     gpu_ctx.gemm(da, db, dc)
