@@ -12,29 +12,14 @@ from __future__ import annotations
 import importlib
 from typing import Any
 
+from . import core as _core
 from ._compile import CompiledKernel, compile
-from .core import (
-    Buffer,
-    BufferSpec,
-    CurrentGroup,
-    IdxTypeSpec,
-    IndexMap,
-    Result,
-    Scope,
-    SubGroup,
-    TensorTypeSpec,
-    UndefTypeSpec,
-    VectorTypeSpec,
-    WorkGroup,
-    WorkItem,
-    as_layout,
-    idx_type,
-    index_map,
-    kernel,
-    tensor_type,
-    undef_type,
-    vector_type,
-)
+
+# The definition surface, re-exported under the names kernels import from `hc`.
+for _name in _core.__all__:
+    if not _name.endswith("Metadata"):
+        globals()[_name] = getattr(_core, _name)
+del _name
 from .errors import DeviceError, LaunchError, SimulatorError
 
 __all__ = [

@@ -58,8 +58,10 @@ typedef enum HcCudaDType { HC_CUDA_F16 = 0, HC_CUDA_BF16 = 1 } HcCudaDType;
 
 typedef enum HcCudaGemmVariant {
   HC_CUDA_GEMM_AUTO = 0,   /* skinny when m <= 64, dense otherwise */
-  HC_CUDA_GEMM_DENSE = 1,  /* 128x256x64 tiles, TMA ring, tcgen05.mma, persistent CTAs */
-  HC_CUDA_GEMM_SKINNY = 2, /* m <= 64: B streamed once, split over k, ordered reduction */
+  HC_CUDA_GEMM_DENSE = 1,  /* TMA ring + tcgen05.mma, persistent; 256x256 tiles on CTA pairs
+                              (cta_group::2) or 128x256 on single CTAs, chosen per shape */
+  HC_CUDA_GEMM_SKINNY = 2, /* m <= 64: B streamed once; split over k (ordered reduction) only
+                              when there are too few column blocks to fill the GPU */
   /* Reported by hcCudaGemmPlan only: */
   HC_CUDA_GEMM_NOOP = 3,     /* m == 0 or n == 0: nothing to write */
   HC_CUDA_GEMM_ZERO_FILL = 4 /* k == 0: C is set to zero, no kernel */
@@ -71,7 +73,8 @@ typedef enum HcCudaGemmVariant {
  * M, N, K being what `_bind_buffer` derives from the array shapes (hc/simulator.py:752-768).
  * Every in-range element of C is overwritten; nothing outside C is written; A and B are
  * read only. A, B 2-byte aligned, C 4-byte aligned; other alignments and pitches are
- * accepted (unaligned ones cost a repack pass through context scratch memory). */
+ * accepted (a or b not 16-byte aligned, or lda/ldb not a multiple of 8 elements, costs one
+ * repack launch through context scratch memory). */
 typedef struct HcCudaGemmArgs {
   int64_t m, n, k;
   int32_t dtype;   /* HcCudaDType */
@@ -91,9 +94,9 @@ typedef struct HcCudaGemmPlanInfo {
   int32_t tiles_n;         /* C tiles along n */
   int32_t splits;          /* k-splits (skinny), 1 otherwise */
   int32_t grid;            /* CTAs of the GEMM kernel */
-  int32_t repack_a;        /* 1: A is first copied to a 16-byte-aligned pitch */
+  int32_t repack_a;        /* 1: A is first copied to a 128-byte-aligned pitch */
   int32_t repack_b;        /* 1: B likewise */
-  int32_t kernel_launches; /* kernels this call enqueues */
+  int32_t kernel_launches; /* kernels this call enqueues (the GEMM, plus one repack if needed) */
   int64_t scratch_bytes;   /* context scratch the call needs */
 } HcCudaGemmPlanInfo;
 
@@ -184,7 +187,10 @@ HC_CUDA_CAPI_EXPORTED int hcCudaGemm(HcCudaContext *ctx, const HcCudaGemmArgs *a
 /* Synchronous. a, b, c are host pointers (NumPy buffers): copies A and B to the device,
  * runs the GEMM, copies C back into the caller's array, returns when C is complete --
  * the in-place, synchronous behaviour of `hc.simulator.launch` (hc/simulator.py:165-186,
- * doc/simulator.md:201-207). Device staging memory is kept by the context between calls. */
+ * doc/simulator.md:201-207). Device staging memory is kept by the context between calls.
+ * Large dense problems are pipelined in row panels so that the copy of C back overlaps the
+ * copy of A in and the compute. Page-locked host buffers (hcCudaHostAlloc) make the copies
+ * asynchronous and about twice as fast. */
 HC_CUDA_CAPI_EXPORTED int hcCudaGemmHost(HcCudaContext *ctx, const HcCudaGemmArgs *args);
 
 /* ---- launching without allocating ---------------------------------------------------- */
