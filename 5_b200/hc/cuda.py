@@ -45,7 +45,7 @@ EXPORTS = (
     "hcCudaMemcpyHtoD", "hcCudaMemcpyDtoH", "hcCudaMemcpy2DHtoD", "hcCudaMemcpy2DDtoH",
     "hcCudaMemset", "hcCudaGemmPlan", "hcCudaGemm", "hcCudaGemmHost", "hcCudaEventCreate",
     "hcCudaEventDestroy", "hcCudaEventRecord", "hcCudaEventElapsedMs", "hcCudaCommGetUniqueId",
-    "hcCudaCommInitRank", "hcCudaCommAllGather", "hcCudaCommDestroy", "hcCudaGemmSkinnyStatic",
+    "hcCudaCommInitRank", "hcCudaCommAllGather", "hcCudaCommDestroy", "hcCudaGemmSkinnyStatic", "hcCudaSelfTestDeviceTimeout",
 )
 
 
@@ -135,6 +135,7 @@ def library() -> ctypes.CDLL:
         lib.hcCudaCommInitRank.argtypes = [vp, vp, sz, i, i]
         lib.hcCudaCommAllGather.argtypes = [vp, vp, vp, sz]
         lib.hcCudaCommDestroy.argtypes = [vp]
+        lib.hcCudaSelfTestDeviceTimeout.argtypes = [vp, ctypes.c_int64]
         lib.hcCudaGemmSkinnyStatic.argtypes = [ctypes.POINTER(_GemmArgs), vp, i, ctypes.c_char_p, sz]
         for name in EXPORTS:
             getattr(lib, name)  # AttributeError here means a stale or foreign library
@@ -292,6 +293,11 @@ class Context:
                           b.ctypes.data, b.strides[0] // b.itemsize if k > 1 else max(n, 1),
                           c.ctypes.data, c.strides[0] // c.itemsize if m > 1 else max(n, 1), variant)
         self._check(self._lib.hcCudaGemmHost(self._handle, ctypes.byref(args)))
+
+    def selftest_device_timeout(self, budget_cycles: int = 2_000_000) -> None:
+        """Enqueues a kernel whose bounded wait runs out; the next `synchronize` raises
+        DeviceError (HC_CUDA_ERR_DEVICE_TIMEOUT) and the context stays usable."""
+        self._check(self._lib.hcCudaSelfTestDeviceTimeout(self._handle, budget_cycles))
 
     def plan(self, m: int, n: int, k: int, dtype: Any, **kwargs: Any) -> GemmPlan:
         kwargs.setdefault("sm_count", self.sm_count)

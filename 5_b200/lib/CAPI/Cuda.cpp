@@ -836,6 +836,15 @@ int hcCudaGemmHost(HcCudaContext *ctx, const HcCudaGemmArgs *args) {
   return synchronize_locked(ctx);
 }
 
+int hcCudaSelfTestDeviceTimeout(HcCudaContext *ctx, int64_t budget_cycles) {
+  if (ctx == nullptr)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "ctx must not be null");
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  HC_TRY_CUDA(ctx, cudaSetDevice(ctx->device));
+  HC_TRY_CUDA(ctx, hc::sm100::launch_wait_selftest(budget_cycles, ctx->status_dev, ctx->stream));
+  return HC_CUDA_OK;
+}
+
 int hcCudaEventCreate(HcCudaContext *ctx, HcCudaEvent **out) {
   if (ctx == nullptr || out == nullptr)
     return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "ctx and out must not be null");

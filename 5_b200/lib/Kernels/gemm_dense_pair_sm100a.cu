@@ -81,7 +81,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
 gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                        const __grid_constant__ CUtensorMap tmap_b, float *__restrict__ c, int m, int n,
                        int k, long long ldc, uint32_t idesc, int tiles_m, int tiles_n, int group_n,
-                       int *status) {
+                       int l2_hints, int *status) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t smem_base = (raw_addr + 1023u) & ~1023u;
@@ -134,6 +134,13 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer ------
     if (lane == 0) {
+      // L2 policy per operand. Default (3): B evict-last, A normal. The group of B tile
+      // columns is what every tile row of the group re-reads, so it should outlive the A rows
+      // streaming past it; measured +2 % on 8192^3 against no hints (0), while marking A
+      // evict-first (1) or both evict-last (2) was no better or worse.
+      const uint64_t pol_a = l2_hints == 1 ? l2_policy_evict_first()
+                                           : (l2_hints == 2 ? l2_policy_evict_last() : l2_policy_evict_normal());
+      const uint64_t pol_b = l2_hints == 0 ? l2_policy_evict_normal() : l2_policy_evict_last();
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters) {
@@ -153,11 +160,11 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
           for (int sub = 0; sub < kKSub; ++sub) {
             const int k0 = kb * kBlockK + sub * 64;
-            tma_load_2d_pair(a_dst + sub * kASubBytes, &tmap_a, leader_full, k0, m0);
+            tma_load_2d_pair_hint(a_dst + sub * kASubBytes, &tmap_a, leader_full, k0, m0, pol_a);
 #pragma unroll
             for (int j = 0; j < kCtaN / 64; ++j)
-              tma_load_2d_pair(b_dst + j * kBChunkBytes + sub * kBBoxBytes, &tmap_b, leader_full,
-                               n0 + j * 64, k0);
+              tma_load_2d_pair_hint(b_dst + j * kBChunkBytes + sub * kBBoxBytes, &tmap_b, leader_full,
+                                    n0 + j * 64, k0, pol_b);
           }
           if (++stage == kStages) {
             stage = 0;
@@ -282,8 +289,11 @@ cudaError_t launch_gemm_dense_pair(const CUtensorMap &tmap_a, const CUtensorMap 
                                         /*b_mn_major=*/true, kTileM, kTileN);
   if (group_n < 1)
     group_n = 1;
+  int l2_hints = 3;
+  if (const char *h = std::getenv("HC_CUDA_L2_HINTS"))  // tuning aid
+    l2_hints = std::atoi(h);
   gemm_dense_pair_kernel<<<static_cast<unsigned>(clusters * 2), kNumThreads, kSmemBytes, stream>>>(
-      tmap_a, tmap_b, c, m, n, k, ldc, idesc, tiles_m, tiles_n, group_n, status);
+      tmap_a, tmap_b, c, m, n, k, ldc, idesc, tiles_m, tiles_n, group_n, l2_hints, status);
   return cudaGetLastError();
 }
 

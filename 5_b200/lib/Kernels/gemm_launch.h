@@ -71,6 +71,11 @@ cudaError_t launch_gemm_skinny(const CUtensorMap &tmap_a, const CUtensorMap &tma
 cudaError_t launch_repack_pitch(const void *src, long long src_ld, void *dst, long long dst_ld,
                                 int rows, int cols, cudaStream_t stream);
 
+// Launches one thread that waits `budget_cycles` (clamped to [1e3, 2e8]) on a barrier nobody
+// signals and then reports kStatusDeviceWaitTimeout through `status`, like a GEMM kernel whose
+// wait ran out.
+cudaError_t launch_wait_selftest(long long budget_cycles, int *status, cudaStream_t stream);
+
 // Two such copies in one launch (either may be empty: rows or cols 0).
 cudaError_t launch_repack_pitch_two(const void *src0, long long src0_ld, void *dst0, long long dst0_ld,
                                     int rows0, int cols0, const void *src1, long long src1_ld, void *dst1,

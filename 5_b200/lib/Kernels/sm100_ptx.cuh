@@ -56,8 +56,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Waits for the phase with the given parity to complete. Returns false when the wait ran
 // out of time or when another role of the CTA has already raised `*abort_flag` (a word
 // in shared memory); the caller then stops its role loop.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
-                                          volatile uint32_t *abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
+                                          long long timeout_cycles = kWaitTimeoutCycles) {
   if (mbar_try_wait(bar, parity))
     return true;
   const long long start = clock64();
@@ -66,7 +66,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
     if ((++spins & 0xffu) == 0) {
       if (*abort_flag != 0)
         return false;
-      if (clock64() - start > kWaitTimeoutCycles) {
+      if (clock64() - start > timeout_cycles) {
         *abort_flag = 1;
         return false;
       }
@@ -84,6 +84,12 @@ __device__ __forceinline__ void tma_prefetch_descriptor(const CUtensorMap *map) 
 __device__ __forceinline__ uint64_t l2_policy_evict_first() {
   uint64_t policy;
   asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+  return policy;
+}
+
+__device__ __forceinline__ uint64_t l2_policy_evict_normal() {
+  uint64_t policy;
+  asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(policy));
   return policy;
 }
 
@@ -251,6 +257,18 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst_smem, const CUtens
       " [%0], [%1, {%3, %4}], [%2];"
       :
       : "r"(dst_smem), "l"(reinterpret_cast<uint64_t>(map)), "r"(cluster_bar), "r"(x), "r"(y)
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_load_2d_pair_hint(uint32_t dst_smem, const CUtensorMap *map,
+                                                      uint32_t cluster_bar, int32_t x, int32_t y,
+                                                      uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      ".L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
+      :
+      : "r"(dst_smem), "l"(reinterpret_cast<uint64_t>(map)), "r"(cluster_bar), "r"(x), "r"(y),
+        "l"(policy)
       : "memory");
 }
 

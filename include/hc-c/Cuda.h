@@ -223,6 +223,13 @@ HC_CUDA_CAPI_EXPORTED int hcCudaGemmSkinnyStatic(const HcCudaGemmArgs *args, voi
                                                  int synchronize, char *error_text,
                                                  size_t error_text_bytes);
 
+/* Asynchronous self-test of the bounded-wait path: enqueues a one-thread kernel that waits
+ * `budget_cycles` SM cycles (clamped to [1e3, 2e8], i.e. at most about 0.1 s) on a barrier that
+ * nothing signals and then gives up exactly as a GEMM kernel would. The next
+ * hcCudaContextSynchronize therefore returns HC_CUDA_ERR_DEVICE_TIMEOUT, clears the status and
+ * leaves the context usable. Nothing faults or hangs. No counterpart in the reference. */
+HC_CUDA_CAPI_EXPORTED int hcCudaSelfTestDeviceTimeout(HcCudaContext *ctx, int64_t budget_cycles);
+
 /* ---- timing ------------------------------------------------------------------------- */
 
 HC_CUDA_CAPI_EXPORTED int hcCudaEventCreate(HcCudaContext *ctx, HcCudaEvent **out);

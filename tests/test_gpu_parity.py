@@ -232,6 +232,26 @@ def test_device_call_rejects_bad_arguments(gpu_ctx) -> None:
     assert_close_to_oracle(dc.to_numpy(), a, b)
 
 
+def test_a_wait_that_runs_out_is_reported_and_survivable(gpu_ctx) -> None:
+    """The give-up path of the kernels' bounded waits, made to happen on purpose: a one-thread
+    kernel waits about a millisecond on a barrier nobody signals, then reports it. Nothing
+    faults; the context reports the timeout once and keeps working."""
+    gpu_ctx.synchronize()
+    gpu_ctx.selftest_device_timeout(2_000_000)
+    with pytest.raises(hc.DeviceError, match="HC_CUDA_ERR_DEVICE_TIMEOUT") as info:
+        gpu_ctx.synchronize()
+    assert info.value.status == 5
+    gpu_ctx.synchronize()  # the status was cleared
+    a, b = random_inputs(8, 2048, 8192, "float16", scale=0.1)  # split-k: uses the counters that were reset
+    assert_close_to_oracle(gpu_wmma_matmul(a, b), a, b)
+    a, b = random_inputs(300, 300, 300, "float16")
+    da, db = gpu_ctx.to_device(a), gpu_ctx.to_device(b)
+    dc = gpu_ctx.empty((300, 300), np.float32)
+    gpu_ctx.gemm(da, db, dc)
+    gpu_ctx.synchronize()
+    assert_close_to_oracle(dc.to_numpy(), a, b)
+
+
 def test_pinned_arrays_round_trip(gpu_ctx) -> None:
     a_src, b_src = random_inputs(70, 80, 90, "float16")
     a = cuda.pinned_empty(a_src.shape, a_src.dtype)
