@@ -8,8 +8,9 @@
 //     B is N-major in memory, which tcgen05.mma accepts directly as an MN-major operand:
 //     no register staging and no transposing loads, TMA -> shared memory -> tensor core.
 //   * Work unit = (block of 128 columns of C, one of `splits` ranges of k). Units are
-//     spread over persistent CTAs, two per SM, each with its own multi-stage TMA ring so
-//     that enough bytes are in flight to cover HBM latency.
+//     spread over persistent CTAs, each with its own multi-stage TMA ring so that enough
+//     bytes are in flight to cover HBM latency: two CTAs per SM with 6/5/4 stages, or, when the
+//     grid has no more CTAs than there are SMs, one with 12/11/9.
 //   * Split-k partial sums go to scratch memory; a per-32-column arrival counter tells the
 //     last warp to finish a column block to add the partials in split order 0..S-1 (so the
 //     result does not depend on which unit finished last) and to write C with coalesced
@@ -32,25 +33,34 @@ constexpr int kNumThreads = 192;
 constexpr int kCtasPerSm = 2;
 constexpr uint32_t kBChunkBytes = 64 * kBlockK * 2;                   // 64 columns x 64 k-rows
 constexpr uint32_t kBTileBytes = kBChunkBytes * (kBlockN / 64);       // 16 KiB
-constexpr uint32_t kBarrierBytes = 256;
+constexpr int kMaxStages = 16;
+constexpr uint32_t kBarrierBytes = 512;  // full/empty[kMaxStages], TMEM barriers, slot, abort flag
+constexpr uint32_t kMaxSmemPerCta = 232448;  // 227 KiB
 
 template <int kMp>
 struct Config {
   static constexpr uint32_t kATileBytes = kMp * kBlockK * 2;
   static constexpr uint32_t kStageBytes = kBTileBytes + kATileBytes;
-  static constexpr int kStages = kMp == 16 ? 6 : (kMp == 32 ? 5 : 4);
   static constexpr uint32_t kTmemColumns = 2 * kMp < 32 ? 32 : 2 * kMp;
-  static constexpr uint32_t kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;
+  // Ring depth: as deep as shared memory allows, for two resident CTAs per SM or, when the grid
+  // does not exceed the SM count anyway, for one (twice the bytes in flight per CTA).
+  static constexpr int stages_for(uint32_t smem_budget) {
+    const int fit = static_cast<int>((smem_budget - kBarrierBytes - 1024) / kStageBytes);
+    return fit > kMaxStages ? kMaxStages : fit;
+  }
+  static constexpr int kStagesShared = stages_for(kMaxSmemPerCta / 2 - 1024);  // 6 / 5 / 4
+  static constexpr int kStagesAlone = stages_for(kMaxSmemPerCta);              // 12 / 11 / 9
+  static constexpr uint32_t smem_bytes(int stages) { return stages * kStageBytes + kBarrierBytes + 1024; }
 };
 
 template <int kMp>
 __global__ void __launch_bounds__(kNumThreads, kCtasPerSm)
 gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a,
                    const __grid_constant__ CUtensorMap tmap_b, float *__restrict__ c, int m, int n,
-                   int k, long long ldc, uint32_t idesc, int n_tiles, int splits,
+                   int k, long long ldc, uint32_t idesc, int n_tiles, int splits, int num_stages,
                    float *__restrict__ partials, unsigned *__restrict__ counters, int *status) {
   using Cfg = Config<kMp>;
-  constexpr int kStages = Cfg::kStages;
+  const uint32_t kStages = static_cast<uint32_t>(num_stages);  // ring depth of this launch
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t smem_base = (raw_addr + 1023u) & ~1023u;
@@ -58,10 +68,10 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
   const uint32_t bar_base = smem_base + kStages * Cfg::kStageBytes;
   auto full_bar = [&](uint32_t s) { return bar_base + 8u * s; };
-  auto empty_bar = [&](uint32_t s) { return bar_base + 8u * (kStages + s); };
-  auto tmem_full_bar = [&](uint32_t a) { return bar_base + 8u * (2 * kStages + a); };
-  auto tmem_empty_bar = [&](uint32_t a) { return bar_base + 8u * (2 * kStages + 2 + a); };
-  const uint32_t misc_off = (bar_base - smem_base) + 8u * (2 * kStages + 4);
+  auto empty_bar = [&](uint32_t s) { return bar_base + 8u * (kMaxStages + s); };
+  auto tmem_full_bar = [&](uint32_t a) { return bar_base + 8u * (2 * kMaxStages + a); };
+  auto tmem_empty_bar = [&](uint32_t a) { return bar_base + 8u * (2 * kMaxStages + 2 + a); };
+  const uint32_t misc_off = (bar_base - smem_base) + 8u * (2 * kMaxStages + 4);
   volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem_gen + misc_off);
   volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(smem_gen + misc_off + 4);
 
@@ -227,12 +237,26 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a,
         // Every split of this 32-column block has published its partial sums.
         __threadfence();
         const float *col_partials = partials + col;
-        for (int mm = 0; mm < m; ++mm) {
-          float sum = 0.0f;
-          for (int s = 0; s < splits; ++s)
-            sum += __ldcg(col_partials + (static_cast<size_t>(s) * m + mm) * n_pad);
-          if (col < n)
-            __stcs(c + static_cast<long long>(mm) * ldc + col, sum);
+        // Eight rows at a time, their loads issued together: the additions of one row stay in
+        // split order, but the L2 round trips of different rows and splits overlap.
+        for (int mm0 = 0; mm0 < m; mm0 += 8) {
+          float sums[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll 4
+          for (int s = 0; s < splits; ++s) {
+            float part[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              part[j] = mm0 + j < m ? __ldcg(col_partials + (static_cast<size_t>(s) * m + mm0 + j) * n_pad) : 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              sums[j] += part[j];
+          }
+          if (col < n) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (mm0 + j < m)
+                __stcs(c + static_cast<long long>(mm0 + j) * ldc + col, sums[j]);
+          }
         }
         if (lane == 0)
           *counter = 0u;
@@ -266,9 +290,8 @@ cudaError_t launch(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, float *
   if (err != cudaSuccess)
     return err;
   if (configured_device != device) {
-    err = cudaFuncSetAttribute(gemm_skinny_kernel<kMp>,
-                               cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               static_cast<int>(Cfg::kSmemBytes));
+    err = cudaFuncSetAttribute(gemm_skinny_kernel<kMp>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(Cfg::smem_bytes(Cfg::kStagesAlone)));
     if (err != cudaSuccess)
       return err;
     configured_device = device;
@@ -276,10 +299,12 @@ cudaError_t launch(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, float *
   const int n_tiles = (n + kBlockN - 1) / kBlockN;
   const long long units = static_cast<long long>(n_tiles) * splits;
   const int grid = static_cast<int>(units < max_ctas ? units : max_ctas);
+  // max_ctas is two per SM; a grid of at most half of that leaves one CTA per SM.
+  const int num_stages = grid * 2 <= max_ctas ? Cfg::kStagesAlone : Cfg::kStagesShared;
   const uint32_t idesc = make_idesc_f16(dtype == kDTypeBF16 ? 1u : 0u, /*a_mn_major=*/true,
                                         /*b_mn_major=*/false, kBlockN, kMp);
-  gemm_skinny_kernel<kMp><<<grid, kNumThreads, Cfg::kSmemBytes, stream>>>(
-      tmap_a, tmap_b, c, m, n, k, ldc, idesc, n_tiles, splits, partials, counters, status);
+  gemm_skinny_kernel<kMp><<<grid, kNumThreads, Cfg::smem_bytes(num_stages), stream>>>(
+      tmap_a, tmap_b, c, m, n, k, ldc, idesc, n_tiles, splits, num_stages, partials, counters, status);
   return cudaGetLastError();
 }
 
@@ -294,14 +319,14 @@ SkinnyShape skinny_shape(int m) {
   s.max_m = 64;
   const int mp = skinny::padded_m(m);
   if (mp == 16) {
-    s.stages = skinny::Config<16>::kStages;
-    s.smem_bytes = skinny::Config<16>::kSmemBytes;
+    s.stages = skinny::Config<16>::kStagesAlone;
+    s.smem_bytes = skinny::Config<16>::smem_bytes(s.stages);
   } else if (mp == 32) {
-    s.stages = skinny::Config<32>::kStages;
-    s.smem_bytes = skinny::Config<32>::kSmemBytes;
+    s.stages = skinny::Config<32>::kStagesAlone;
+    s.smem_bytes = skinny::Config<32>::smem_bytes(s.stages);
   } else {
-    s.stages = skinny::Config<64>::kStages;
-    s.smem_bytes = skinny::Config<64>::kSmemBytes;
+    s.stages = skinny::Config<64>::kStagesAlone;
+    s.smem_bytes = skinny::Config<64>::smem_bytes(s.stages);
   }
   return s;
 }

@@ -199,6 +199,25 @@ def test_numpy_views_and_strides() -> None:
     assert np.array_equal(c3, c2)
 
 
+def test_large_ragged_product_on_pageable_numpy_buffers(gpu_ctx) -> None:
+    """Config 3 through the handle on ordinary (pageable) NumPy arrays: large enough for the
+    host call to pipeline its copies in row panels. The result must equal the device-buffer
+    path bit for bit and leave the arrays' surroundings alone."""
+    a, b = workloads.make_inputs("ragged")
+    c_store = np.full((4095 + 2, 3073 + 5), np.nan, np.float32)
+    c = c_store[1:-1, 2:-3]
+    compiled_for("bfloat16")(a, b, c)
+    da, db = gpu_ctx.to_device(a), gpu_ctx.to_device(b)
+    dc = gpu_ctx.empty((4095, 3073), np.float32)
+    gpu_ctx.gemm(da, db, dc)
+    gpu_ctx.synchronize()
+    assert np.array_equal(np.ascontiguousarray(c), dc.to_numpy())
+    assert np.isnan(c_store[0]).all() and np.isnan(c_store[-1]).all()
+    assert np.isnan(c_store[:, :2]).all() and np.isnan(c_store[:, -3:]).all()
+    rows = _sample_rows(4095)
+    assert workloads.check_against_float64(np.ascontiguousarray(c), a, b, rows=rows)["ok"]
+
+
 def test_device_buffers_through_the_handle(gpu_ctx) -> None:
     a, b = random_inputs(200, 264, 96, "float16")
     da, db = gpu_ctx.to_device(a), gpu_ctx.to_device(b)
