@@ -88,14 +88,16 @@ def build_tiled_wmma_matmul(element_type):
         return group.vload(out, shape=(ACC_PER_LANE,))
 
     @wmma_16x16x16.lower(target=NVIDIA_TARGET)
-    def _lower_to_umma(*operands, **attrs):
-        """What the NVIDIA target does with this intrinsic instead of a per-lane op: the
-        whole k-loop of 16x16x16 steps becomes tcgen05.mma instructions on CTA tiles."""
+    def _lower_to_umma(ctx, *operands, **attrs):
+        """What the NVIDIA target does with this intrinsic instead of emitting a per-lane op: the
+        whole k-loop of 16x16x16 steps becomes tcgen05.mma instructions on CTA tiles. The hook
+        may steer the kernel family; here it leaves the choice to the launcher."""
         del operands, attrs
         return {
-            "instruction": "tcgen05.mma.cta_group::1.kind::f16",
+            "variant": "auto",
+            "instruction": getattr(ctx, "instruction", "tcgen05.mma.kind::f16"),
             "accumulator": "tensor memory, fp32",
-            "cta_tile": (128, 256, 64),
+            "cta_tiles": getattr(ctx, "cta_tiles", ()),
             "input_dtype": np.dtype(element_type).name,
         }
 

@@ -77,6 +77,8 @@ class CompiledKernel:
         plan = self.plan
         assert plan is not None
         a, b, c = (launch.arguments[p] for p in (plan.a_param, plan.b_param, plan.c_param))
+        variant = {"auto": cuda.VARIANT_AUTO, "dense": cuda.VARIANT_DENSE, "skinny": cuda.VARIANT_SKINNY}[
+            (plan.lowering or {}).get("variant", "auto")]
         on_device = [type(x).__name__ == "DeviceBuffer" for x in (a, b, c)]
         if any(on_device) and not all(on_device):
             raise LaunchError("buffers must be all numpy.ndarray or all DeviceBuffer")
@@ -84,19 +86,19 @@ class CompiledKernel:
             ctx = a.ctx
             if b.ctx is not ctx or c.ctx is not ctx:
                 raise LaunchError("device buffers must belong to one context")
-            ctx.gemm(a, b, c)
+            ctx.gemm(a, b, c, variant=variant)
             ctx.synchronize()
             return
         ctx = cuda.default_context(self.device)
         a_host = _row_major(a)
         b_host = _row_major(b)
         if _is_row_major(c) and c.flags.writeable:
-            ctx.gemm_host(a_host, b_host, c)
+            ctx.gemm_host(a_host, b_host, c, variant=variant)
             return
         if not c.flags.writeable:
             raise LaunchError(f"{plan.c_param} must be writeable")
         staged = np.empty(c.shape, np.float32)
-        ctx.gemm_host(a_host, b_host, staged)
+        ctx.gemm_host(a_host, b_host, staged, variant=variant)
         c[...] = staged
 
     # -- text ---------------------------------------------------------------------------

@@ -38,6 +38,7 @@ from ._intrinsic_contracts import serialize_intrinsic_type_spec
 __all__ = [
     "NVIDIA_SM100A",
     "GemmContract",
+    "LoweringContext",
     "ScheduleSource",
     "TargetResult",
     "known_targets",
@@ -71,6 +72,8 @@ class GemmContract:
     intrinsic_name: str
     intrinsic_const_attrs: tuple[str, ...]
     has_target_lowering: bool  # intrinsic registered `.lower(target="nvidia-sm100a")`
+    # What that lowering hook returned (a mapping; see `_run_lowering_hook`), or None.
+    lowering: Any = None
 
 
 @dataclass(frozen=True)
@@ -362,6 +365,47 @@ def _check_body(kernel_fn: Any, params: list[str], a: str, b: str, c: str, tile:
     return problems
 
 
+@dataclass(frozen=True)
+class LoweringContext:
+    """What an intrinsic's `.lower(target="nvidia-sm100a")` hook receives as its first argument.
+
+    In the reference a lowering hook gets a builder context and returns IR values
+    (examples/amdgpu_gfx11_wmma_matmul.py:200-228; nothing ever calls those hooks). This target
+    does not build IR: the whole k-loop of WMMA steps becomes tcgen05.mma instructions, so the
+    hook's role is to describe or steer that mapping. It may return a mapping with any of
+        "variant": "auto" | "dense" | "skinny"   which kernel family launches use
+    plus free-form descriptive entries, which are kept on the plan.
+    """
+
+    target: str
+    tile: tuple[int, int, int]
+    wave_size: int
+    input_dtype: str
+    cta_tiles: tuple[tuple[int, int, int], ...] = ((256, 256, 128), (128, 256, 64))
+    instruction: str = "tcgen05.mma.kind::f16 (fp32 accumulate in tensor memory)"
+
+
+_VARIANTS = ("auto", "dense", "skinny")
+
+
+def _run_lowering_hook(intrinsic: Any, tile: tuple[int, int, int], wave: int, dtype: str) -> tuple[Any, list[str]]:
+    hook = (getattr(intrinsic, "__hc_lowerings__", {}) or {}).get(NVIDIA_SM100A)
+    if hook is None:
+        return None, []
+    try:
+        result = hook(LoweringContext(NVIDIA_SM100A, tile, wave, dtype))
+    except Exception as exc:  # a user's hook must not break compilation
+        return None, [f"lowering hook of {intrinsic.__name__} raised {type(exc).__name__}: {exc}"]
+    if result is None:
+        return None, []
+    if not isinstance(result, dict):
+        return None, [f"lowering hook of {intrinsic.__name__} must return a mapping or None"]
+    variant = result.get("variant", "auto")
+    if variant not in _VARIANTS:
+        return None, [f"lowering hook of {intrinsic.__name__}: variant must be one of {list(_VARIANTS)}"]
+    return dict(result), []
+
+
 # ------------------------------------------------------------------ recogniser ----------
 
 
@@ -434,11 +478,15 @@ def recognise_tiled_matmul(kernel_fn: Any) -> tuple[GemmContract | None, list[st
         return None, [f"{name}: {p}" for p in problems]
 
     lowerings = getattr(intrinsic, "__hc_lowerings__", {}) or {}
+    lowering, hook_problems = _run_lowering_hook(intrinsic, tile, wave, input_dtype)
+    if hook_problems:
+        return None, [f"{name}: {p}" for p in hook_problems]
     contract = GemmContract(
         kernel_name=name, a_param=a, b_param=b, c_param=c, m_dim=m_dim, n_dim=n_dim, k_dim=k_dim,
         input_dtype=input_dtype, output_dtype="float32", tile=tile, wave_size=wave,
         accumulators_per_lane=acc_len, intrinsic_name=intrinsic.__name__,
         intrinsic_const_attrs=tuple(sorted(intrinsic.__hc_intrinsic__.const_attrs)),
         has_target_lowering=NVIDIA_SM100A in lowerings,
+        lowering=lowering,
     )
     return contract, []

@@ -125,6 +125,29 @@ def test_example_kernel_is_recognised(dtype: str) -> None:
     assert plan.intrinsic_const_attrs == ("arch", "wave_size")
 
 
+def test_lowering_hook_is_called_and_steers_the_variant() -> None:
+    plan = compiled_for("float16").plan
+    assert plan.lowering["variant"] == "auto" and plan.lowering["input_dtype"] == "float16"
+    assert "tcgen05.mma" in plan.lowering["instruction"] and (256, 256, 128) in plan.lowering["cta_tiles"]
+
+    def with_hook(hook):
+        kern = _family()
+        mma = next(fn for fn in __import__("hc._pipeline", fromlist=["x"])._reachable_callables(kern)
+                   if hasattr(fn, "__hc_intrinsic__"))
+        mma.lower(target=NVIDIA_SM100A)(hook)
+        return hc.compile(kern, target=NVIDIA_SM100A)
+
+    forced = with_hook(lambda ctx, *a, **k: {"variant": "dense", "why": f"{ctx.tile} on {ctx.target}"})
+    assert forced.plan.lowering == {"variant": "dense", "why": "(16, 16, 16) on nvidia-sm100a"}
+    assert with_hook(lambda ctx, *a, **k: None).plan.lowering is None
+    bad = with_hook(lambda ctx, *a, **k: {"variant": "fastest"})
+    assert bad.plan is None and any("variant must be one of" in d for d in bad.pipeline_diagnostics)
+    broken = with_hook(lambda ctx, *a, **k: 1 / 0)
+    assert broken.plan is None and any("raised ZeroDivisionError" in d for d in broken.pipeline_diagnostics)
+    other = _family()
+    assert hc.compile(other, target=NVIDIA_SM100A).plan.lowering is None  # no hook registered
+
+
 def test_family_members_are_recognised() -> None:
     for kwargs in ({}, {"in_dtype": __import__("ml_dtypes").bfloat16}, {"tile": (32, 16, 16), "acc": 16},
                    {"tile": (16, 16, 32)}, {"wave": 64, "acc": 4}):

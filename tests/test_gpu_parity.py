@@ -120,6 +120,25 @@ def test_forced_variants_agree(gpu_ctx) -> None:
     assert np.allclose(outs[0], outs[1], rtol=0, atol=1e-3)
 
 
+def test_lowering_hook_chooses_the_kernel_family() -> None:
+    """A kernel whose intrinsic registers `.lower(target="nvidia-sm100a")` returning
+    {"variant": "dense"} runs the dense kernels even for a shape that would go to the skinny one."""
+    from examples.b200_wmma_matmul import build_tiled_wmma_matmul
+    from hc._pipeline import NVIDIA_SM100A, _reachable_callables
+
+    kern = build_tiled_wmma_matmul(np.float16)
+    mma = next(fn for fn in _reachable_callables(kern) if hasattr(fn, "__hc_intrinsic__"))
+    mma.lower(target=NVIDIA_SM100A)(lambda ctx, *args, **kwargs: {"variant": "dense"})
+    handle = hc.compile(kern, target=NVIDIA_SM100A)
+    assert handle.plan.lowering == {"variant": "dense"}
+    a, b = random_inputs(40, 520, 300, "float16")
+    c = np.zeros((40, 520), np.float32)
+    handle(a, b, c)
+    assert_close_to_oracle(c, a, b)
+    # The skinny kernel (default for m <= 64) sums in a different order: close, not identical.
+    assert np.allclose(c, gpu_wmma_matmul(a, b), rtol=0, atol=1e-3)
+
+
 # ---------------------------------------------------------------- edges ------------------
 
 
