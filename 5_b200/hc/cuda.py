@@ -37,6 +37,8 @@ F16, BF16 = 0, 1
 VARIANT_AUTO, VARIANT_DENSE, VARIANT_SKINNY, VARIANT_NOOP, VARIANT_ZERO_FILL = 0, 1, 2, 3, 4
 VARIANT_NAMES = {0: "auto", 1: "dense", 2: "skinny", 3: "noop", 4: "zero_fill"}
 COMM_ID_BYTES = 128
+IPC_HANDLE_BYTES = 64
+MAX_PUSH_TARGETS = 7
 
 EXPORTS = (
     "hcCudaApiVersion", "hcCudaStatusString", "hcCudaGetDeviceCount", "hcCudaContextCreate",
@@ -45,7 +47,8 @@ EXPORTS = (
     "hcCudaMemcpyHtoD", "hcCudaMemcpyDtoH", "hcCudaMemcpy2DHtoD", "hcCudaMemcpy2DDtoH",
     "hcCudaMemset", "hcCudaGemmPlan", "hcCudaGemm", "hcCudaGemmHost", "hcCudaEventCreate",
     "hcCudaEventDestroy", "hcCudaEventRecord", "hcCudaEventElapsedMs", "hcCudaCommGetUniqueId",
-    "hcCudaCommInitRank", "hcCudaCommAllGather", "hcCudaCommDestroy", "hcCudaGemmSkinnyStatic", "hcCudaSelfTestDeviceTimeout",
+    "hcCudaCommInitRank", "hcCudaCommAllGather", "hcCudaCommDestroy", "hcCudaGemmSkinnyStatic", "hcCudaSelfTestDeviceTimeout", "hcCudaGemmPush", "hcCudaIpcExport",
+    "hcCudaIpcOpen", "hcCudaIpcClose",
 )
 
 
@@ -136,6 +139,10 @@ def library() -> ctypes.CDLL:
         lib.hcCudaCommAllGather.argtypes = [vp, vp, vp, sz]
         lib.hcCudaCommDestroy.argtypes = [vp]
         lib.hcCudaSelfTestDeviceTimeout.argtypes = [vp, ctypes.c_int64]
+        lib.hcCudaGemmPush.argtypes = [vp, ctypes.POINTER(_GemmArgs), ctypes.POINTER(ctypes.c_void_p), i]
+        lib.hcCudaIpcExport.argtypes = [vp, vp, vp, sz]
+        lib.hcCudaIpcOpen.argtypes = [vp, vp, sz, pvp]
+        lib.hcCudaIpcClose.argtypes = [vp, vp]
         lib.hcCudaGemmSkinnyStatic.argtypes = [ctypes.POINTER(_GemmArgs), vp, i, ctypes.c_char_p, sz]
         for name in EXPORTS:
             getattr(lib, name)  # AttributeError here means a stale or foreign library
@@ -277,12 +284,41 @@ class Context:
 
     # -- the hot path -------------------------------------------------------------------
     def gemm(self, a: "DeviceBuffer", b: "DeviceBuffer", c: "DeviceBuffer", *,
-             variant: int = VARIANT_AUTO) -> None:
-        """Enqueues C = A @ B on device buffers (asynchronous; see `synchronize`)."""
+             variant: int = VARIANT_AUTO, push: "list[DeviceBuffer] | None" = None) -> None:
+        """Enqueues C = A @ B on device buffers (asynchronous; see `synchronize`).
+
+        `push`: up to 7 more buffers shaped and pitched like `c` (typically windows of peer
+        GPUs' copies of C, see `ipc_open`) that receive every tile of C as well.
+        """
         m, k = a.shape
         n = b.shape[1]
         args = _gemm_args(m, n, k, a.dtype, a.ptr, a.ld, b.ptr, b.ld, c.ptr, c.ld, variant)
-        self._check(self._lib.hcCudaGemm(self._handle, ctypes.byref(args)))
+        if not push:
+            self._check(self._lib.hcCudaGemm(self._handle, ctypes.byref(args)))
+            return
+        for target in push:
+            if target.shape != c.shape or target.ld != c.ld or target.dtype != c.dtype:
+                raise ValueError("push targets must have the shape, pitch and dtype of c")
+        pointers = (ctypes.c_void_p * len(push))(*[t.ptr for t in push])
+        self._check(self._lib.hcCudaGemmPush(self._handle, ctypes.byref(args), pointers, len(push)))
+
+    # -- sharing device memory between the processes of one node ----------------------------
+    def ipc_export(self, buf: "DeviceBuffer") -> bytes:
+        """Handle (64 bytes) of the allocation behind `buf`, for `ipc_open` in another process."""
+        handle = ctypes.create_string_buffer(IPC_HANDLE_BYTES)
+        self._check(self._lib.hcCudaIpcExport(self._handle, buf.ptr, handle, IPC_HANDLE_BYTES))
+        return handle.raw
+
+    def ipc_open(self, handle: bytes) -> int:
+        """Maps another process's allocation into this one; returns its device address here."""
+        raw = ctypes.create_string_buffer(bytes(handle), IPC_HANDLE_BYTES)
+        ptr = ctypes.c_void_p()
+        self._check(self._lib.hcCudaIpcOpen(self._handle, raw, IPC_HANDLE_BYTES, ctypes.byref(ptr)))
+        return ptr.value or 0
+
+    def ipc_close(self, ptr: int) -> None:
+        if ptr:
+            self._check(self._lib.hcCudaIpcClose(self._handle, ptr))
 
     def gemm_host(self, a: np.ndarray, b: np.ndarray, c: np.ndarray, *,
                   variant: int = VARIANT_AUTO) -> None:
@@ -373,6 +409,31 @@ class DeviceBuffer:
         self._rows = rows
         self.nbytes = rows * self.ld * self.dtype.itemsize
         self.ptr = ctx.malloc(self.nbytes) if self.nbytes else 0
+        self._owned = True
+
+    @classmethod
+    def wrap(cls, ctx: Context, ptr: int, shape: tuple[int, ...], dtype: Any, *, ld: int | None = None) -> "DeviceBuffer":
+        """A buffer object over device memory it does not own (a window of another buffer, or
+        memory opened with `Context.ipc_open`); `free` and garbage collection leave it alone."""
+        self = cls.__new__(cls)
+        self.ctx = ctx
+        self.shape = tuple(int(s) for s in shape)
+        self.dtype = np.dtype(dtype)
+        self.ndim = len(self.shape)
+        cols = self.shape[-1] if self.shape else 1
+        self.ld = int(cols if ld is None else ld)
+        self._rows = int(np.prod(self.shape[:-1])) if self.ndim > 1 else 1
+        self.nbytes = self._rows * self.ld * self.dtype.itemsize
+        self.ptr = int(ptr)
+        self._owned = False
+        return self
+
+    def window(self, row0: int, row1: int, col0: int, col1: int) -> "DeviceBuffer":
+        """Non-owning view of rows [row0, row1), columns [col0, col1) of a matrix."""
+        if self.ndim != 2 or not (0 <= row0 <= row1 <= self.shape[0] and 0 <= col0 <= col1 <= self.shape[1]):
+            raise ValueError("window out of range")
+        offset = (row0 * self.ld + col0) * self.dtype.itemsize
+        return DeviceBuffer.wrap(self.ctx, self.ptr + offset, (row1 - row0, col1 - col0), self.dtype, ld=self.ld)
 
     def copy_from_host(self, array: np.ndarray) -> None:
         if tuple(array.shape) != self.shape or array.dtype != self.dtype:
@@ -413,7 +474,7 @@ class DeviceBuffer:
             self.ctx.memset(self.ptr, byte_value, self.nbytes)
 
     def free(self) -> None:
-        if self.ptr and self.ctx._handle:
+        if self.ptr and getattr(self, "_owned", True) and self.ctx._handle:
             self.ctx.free(self.ptr)
         self.ptr = 0
 

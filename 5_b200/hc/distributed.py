@@ -2,10 +2,11 @@
 
 The product splits by columns with no exchange: rank r owns the column slab
 `B[:, lo:hi]` and writes `C[:, lo:hi]`; A is replicated. A slab is just a matmul with a
-smaller N, so each rank launches the same compiled handle on its own buffers. The only
-collective is optional: an all-gather of the C slabs over NVLink (NCCL), which yields C
-slab-major, `[rank][M][slab columns]`; `assemble_row_major` describes the host-side view that
-turns that back into a row-major matrix. The reference has no multi-device notion at all;
+smaller N, so each rank launches the same compiled handle on its own buffers. Gathering C on
+every rank is optional and comes in two forms: an NCCL all-gather of the finished slabs (C
+arrives slab-major, `[rank][M][slab columns]`; `assemble_row_major` turns that into a row-major
+matrix on the host), or `PushedMatmul`, where the GEMM's own epilogue stores each tile into all
+ranks' row-major C over NVLink while the rest of the product is still running. The reference has no multi-device notion at all;
 this module is the whole of it here.
 """
 
@@ -17,7 +18,7 @@ from typing import Any
 
 import numpy as np
 
-__all__ = ["ColumnSlab", "ShardedMatmul", "assemble_row_major", "column_slab", "init_communicator"]
+__all__ = ["ColumnSlab", "PushedMatmul", "ShardedMatmul", "assemble_row_major", "column_slab", "init_communicator"]
 
 
 @dataclass(frozen=True)
@@ -99,6 +100,61 @@ class ShardedMatmul:
         if self.n % self.world_size != 0 or self.slab.width * self.world_size != self.n:
             raise ValueError("all_gather needs equal slabs (n divisible by world_size * align)")
         self.ctx.all_gather(dc_slab, gathered)
+
+
+class PushedMatmul:
+    """The N-sharded product with the gather fused into the GEMM's epilogue.
+
+    Every rank holds a full row-major C[M, N]. Rank r computes its column slab and its kernel
+    stores each finished tile into the slab's window of *every* rank's C: locally, and over NVLink
+    through pointers opened with CUDA IPC. Transfers overlap the remaining tiles' math, and the
+    result is row-major everywhere (the NCCL all-gather yields slab-major C and runs after the
+    product). Usage per rank: `setup` (collective), then `run` + `ctx.synchronize()` + a host
+    barrier per product, `close` (collective) at the end.
+    """
+
+    def __init__(self, ctx: Any, m: int, n: int, world_size: int, rank: int, *, align: int = 256) -> None:
+        if world_size - 1 > 7:
+            raise ValueError("at most 8 ranks (7 push targets)")
+        self.ctx = ctx
+        self.m, self.n = m, n
+        self.world_size, self.rank = world_size, rank
+        self.slab = column_slab(n, world_size, rank, align=align)
+        self.full_c: Any = None
+        self._peer_ptrs: list[int] = []
+        self._targets: list[Any] = []
+
+    def setup(self, all_gather: Callable[[bytes], "list[bytes]"]) -> Any:
+        """Allocates this rank's full C and maps the peers'. `all_gather(payload)` must return
+        the payloads of all ranks in rank order (any host channel). Returns the full C."""
+        import numpy as _np
+
+        self.full_c = self.ctx.empty((self.m, self.n), _np.float32)
+        handles = all_gather(self.ctx.ipc_export(self.full_c))
+        if len(handles) != self.world_size:
+            raise RuntimeError("all_gather() must return one handle per rank")
+        for peer, handle in enumerate(handles):
+            if peer == self.rank:
+                continue
+            ptr = self.ctx.ipc_open(handle)
+            self._peer_ptrs.append(ptr)
+            whole = type(self.full_c).wrap(self.ctx, ptr, (self.m, self.n), _np.float32)
+            self._targets.append(whole.window(0, self.m, self.slab.begin, self.slab.end))
+        return self.full_c
+
+    def run(self, da: Any, db_slab: Any) -> None:
+        """Enqueues the slab product; its tiles go to this rank's C and to all peers'."""
+        if self.slab.width == 0:
+            return
+        local = self.full_c.window(0, self.m, self.slab.begin, self.slab.end)
+        self.ctx.gemm(da, db_slab, local, push=self._targets)
+
+    def close(self) -> None:
+        """Unmaps the peers' memory. Call on every rank before any rank frees its C."""
+        self.ctx.synchronize()
+        for ptr in self._peer_ptrs:
+            self.ctx.ipc_close(ptr)
+        self._peer_ptrs, self._targets = [], []
 
 
 def assemble_row_major(gathered: np.ndarray) -> np.ndarray:

@@ -332,7 +332,8 @@ int encode_map(HcCudaContext *ctx, CUtensorMap *map, int dtype, const void *base
 
 // Enqueues the GEMM on device-resident buffers. The caller holds ctx->mu and has made the
 // context's device current.
-int enqueue_gemm(HcCudaContext *ctx, const HcCudaGemmArgs *args, const HcCudaGemmPlanInfo &plan) {
+int enqueue_gemm(HcCudaContext *ctx, const HcCudaGemmArgs *args, const HcCudaGemmPlanInfo &plan,
+                 const hc::sm100::PushTargets &push = hc::sm100::PushTargets{}) {
   if (plan.variant == HC_CUDA_GEMM_NOOP)
     return HC_CUDA_OK;
   const int m = static_cast<int>(args->m), n = static_cast<int>(args->n), k = static_cast<int>(args->k);
@@ -389,11 +390,11 @@ int enqueue_gemm(HcCudaContext *ctx, const HcCudaGemmArgs *args, const HcCudaGem
       return rc;
     if (hc::sm100::dense_uses_pairs(m, n, k, ctx->prop.multiProcessorCount)) {
       HC_TRY_CUDA(ctx, hc::sm100::launch_gemm_dense_pair(tmap_a, tmap_b, args->c, m, n, k, args->ldc,
-                                                         args->dtype, ctx->group_n, plan.grid,
+                                                         args->dtype, ctx->group_n, plan.grid, push,
                                                          ctx->status_dev, ctx->stream));
     } else {
       HC_TRY_CUDA(ctx, hc::sm100::launch_gemm_dense(tmap_a, tmap_b, args->c, m, n, k, args->ldc,
-                                                    args->dtype, ctx->group_n, plan.grid,
+                                                    args->dtype, ctx->group_n, plan.grid, push,
                                                     ctx->status_dev, ctx->stream));
     }
     return HC_CUDA_OK;
@@ -739,6 +740,86 @@ int hcCudaGemm(HcCudaContext *ctx, const HcCudaGemmArgs *args) {
     return rc;
   HC_TRY_CUDA(ctx, cudaSetDevice(ctx->device));
   return enqueue_gemm(ctx, args, plan);
+}
+
+int hcCudaGemmPush(HcCudaContext *ctx, const HcCudaGemmArgs *args, float *const *targets, int n_targets) {
+  if (ctx == nullptr)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "ctx must not be null");
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  if (n_targets < 0 || n_targets > HC_CUDA_MAX_PUSH_TARGETS || (n_targets > 0 && targets == nullptr))
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "n_targets must be in [0, %d] with a non-null array",
+                HC_CUDA_MAX_PUSH_TARGETS);
+  if (args == nullptr)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "args must not be null");
+  HcCudaGemmArgs dense = *args;
+  if (dense.variant == HC_CUDA_GEMM_AUTO)
+    dense.variant = HC_CUDA_GEMM_DENSE;
+  if (dense.variant != HC_CUDA_GEMM_DENSE)
+    return fail(ctx, HC_CUDA_ERR_UNSUPPORTED, "pushing C to other buffers is implemented by the dense kernels only");
+  HcCudaGemmPlanInfo plan;
+  if (int rc = plan_gemm(ctx, &dense, ctx->prop.multiProcessorCount, false, &plan))
+    return rc;
+  hc::sm100::PushTargets push{};
+  if (plan.variant == HC_CUDA_GEMM_DENSE && n_targets > 0) {
+    if ((dense.ldc & 3) != 0 || (reinterpret_cast<uintptr_t>(dense.c) & 15) != 0)
+      return fail(ctx, HC_CUDA_ERR_UNSUPPORTED, "pushing needs c 16-byte aligned and ldc a multiple of 4");
+    const size_t c_bytes = (static_cast<size_t>(dense.m - 1) * dense.ldc + dense.n) * 4;
+    for (int i = 0; i < n_targets; ++i) {
+      if (targets[i] == nullptr || (reinterpret_cast<uintptr_t>(targets[i]) & 15) != 0)
+        return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "push target %d must be a 16-byte-aligned device pointer", i);
+      if (ranges_overlap(targets[i], c_bytes, dense.c, c_bytes))
+        return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "push target %d overlaps c", i);
+      push.c[i] = targets[i];
+    }
+    push.count = n_targets;
+  } else if (n_targets > 0 && plan.variant == HC_CUDA_GEMM_ZERO_FILL) {
+    return fail(ctx, HC_CUDA_ERR_UNSUPPORTED, "k == 0 with push targets is not supported");
+  }
+  HC_TRY_CUDA(ctx, cudaSetDevice(ctx->device));
+  return enqueue_gemm(ctx, &dense, plan, push);
+}
+
+int hcCudaIpcExport(HcCudaContext *ctx, const void *device_ptr, void *handle, size_t handle_bytes) {
+  static_assert(sizeof(cudaIpcMemHandle_t) <= HC_CUDA_IPC_HANDLE_BYTES, "handle buffer too small");
+  if (ctx == nullptr)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "ctx must not be null");
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  if (device_ptr == nullptr || handle == nullptr || handle_bytes < sizeof(cudaIpcMemHandle_t))
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "device_ptr and a handle buffer of at least %zu bytes are required",
+                sizeof(cudaIpcMemHandle_t));
+  HC_TRY_CUDA(ctx, cudaSetDevice(ctx->device));
+  cudaIpcMemHandle_t h;
+  HC_TRY_CUDA(ctx, cudaIpcGetMemHandle(&h, const_cast<void *>(device_ptr)));
+  std::memset(handle, 0, handle_bytes);
+  std::memcpy(handle, &h, sizeof(h));
+  return HC_CUDA_OK;
+}
+
+int hcCudaIpcOpen(HcCudaContext *ctx, const void *handle, size_t handle_bytes, void **device_ptr) {
+  if (ctx == nullptr)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "ctx must not be null");
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  if (device_ptr == nullptr || handle == nullptr || handle_bytes < sizeof(cudaIpcMemHandle_t))
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "a handle of at least %zu bytes and device_ptr are required",
+                sizeof(cudaIpcMemHandle_t));
+  *device_ptr = nullptr;
+  HC_TRY_CUDA(ctx, cudaSetDevice(ctx->device));
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, handle, sizeof(h));
+  HC_TRY_CUDA(ctx, cudaIpcOpenMemHandle(device_ptr, h, cudaIpcMemLazyEnablePeerAccess));
+  return HC_CUDA_OK;
+}
+
+int hcCudaIpcClose(HcCudaContext *ctx, void *device_ptr) {
+  if (ctx == nullptr)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "ctx must not be null");
+  if (device_ptr == nullptr)
+    return HC_CUDA_OK;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  HC_TRY_CUDA(ctx, cudaSetDevice(ctx->device));
+  HC_TRY_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  HC_TRY_CUDA(ctx, cudaIpcCloseMemHandle(device_ptr));
+  return HC_CUDA_OK;
 }
 
 int hcCudaGemmHost(HcCudaContext *ctx, const HcCudaGemmArgs *args) {

@@ -10,6 +10,7 @@
 // each row is rotated to its own 16-byte phase while it is staged.
 #pragma once
 
+#include "gemm_launch.h"
 #include "sm100_ptx.cuh"
 
 namespace hc {
@@ -35,7 +36,7 @@ __device__ __forceinline__ void stage_row_shifted(const uint32_t (&r)[32], float
 __device__ __forceinline__ void write_chunk(const uint32_t (&r)[32], int chunk, bool last_chunk, float *buf,
                                             float *__restrict__ c, long long ldc, int m, int n,
                                             int row_base, int col_base, bool vec_ok, int lane,
-                                            float (&carry)[3]) {
+                                            float (&carry)[3], const PushTargets &push) {
   const int col0 = col_base + chunk * 32;
   if (col0 >= n)
     return;  // warp-uniform
@@ -50,13 +51,20 @@ __device__ __forceinline__ void write_chunk(const uint32_t (&r)[32], int chunk, 
       const int row = row_base + rr;
       const float4 v = *reinterpret_cast<const float4 *>(buf + rr * 32 + ((piece ^ (rr & 7)) << 2));
       if (row < m) {
-        float *dst = c + static_cast<long long>(row) * ldc + col;
+        const long long offset = static_cast<long long>(row) * ldc + col;
+        float *dst = c + offset;
         if (col + 3 < n) {
           __stcs(reinterpret_cast<float4 *>(dst), v);
+          // The same 128-byte row segments go to every push target (peer GPUs' copies of C).
+          for (int t = 0; t < push.count; ++t)
+            __stcs(reinterpret_cast<float4 *>(push.c[t] + offset), v);
         } else {
-          if (col < n) __stcs(dst, v.x);
-          if (col + 1 < n) __stcs(dst + 1, v.y);
-          if (col + 2 < n) __stcs(dst + 2, v.z);
+          for (int t = -1; t < push.count; ++t) {
+            float *edge = t < 0 ? dst : push.c[t] + offset;
+            if (col < n) __stcs(edge, v.x);
+            if (col + 1 < n) __stcs(edge + 1, v.y);
+            if (col + 2 < n) __stcs(edge + 2, v.z);
+          }
         }
       }
     }
@@ -153,7 +161,8 @@ template <int kColumns>
 __device__ __forceinline__ void drain_accumulator_rows(uint32_t taddr, float *stage, float *__restrict__ c,
                                                        long long ldc, int m, int n, int row_base,
                                                        int col_base, bool vec_ok, int lane,
-                                                       uint32_t release_bar, bool release_remote) {
+                                                       uint32_t release_bar, bool release_remote,
+                                                       const PushTargets &push) {
   constexpr int kChunks = kColumns / 32;
   static_assert(kChunks % 2 == 0, "chunks are processed in pairs");
   uint32_t ra[32], rb[32];
@@ -163,7 +172,7 @@ __device__ __forceinline__ void drain_accumulator_rows(uint32_t taddr, float *st
   for (int chunk = 0; chunk < kChunks; chunk += 2) {
     tmem_load_wait_for(ra);
     tmem_load_32x32b_x32(taddr + (chunk + 1) * 32, rb);
-    write_chunk(ra, chunk, false, stage, c, ldc, m, n, row_base, col_base, vec_ok, lane, carry);
+    write_chunk(ra, chunk, false, stage, c, ldc, m, n, row_base, col_base, vec_ok, lane, carry, push);
     tmem_load_wait_for(rb);
     if (chunk + 2 < kChunks) {
       tmem_load_32x32b_x32(taddr + (chunk + 2) * 32, ra);
@@ -178,7 +187,7 @@ __device__ __forceinline__ void drain_accumulator_rows(uint32_t taddr, float *st
           mbar_arrive(release_bar);
       }
     }
-    write_chunk(rb, chunk + 1, chunk + 2 >= kChunks, stage, c, ldc, m, n, row_base, col_base, vec_ok, lane, carry);
+    write_chunk(rb, chunk + 1, chunk + 2 >= kChunks, stage, c, ldc, m, n, row_base, col_base, vec_ok, lane, carry, push);
   }
 }
 

@@ -16,6 +16,16 @@ constexpr int kDTypeBF16 = 1;
 // Value a kernel writes to the status word when one of its bounded waits ran out.
 constexpr int kStatusDeviceWaitTimeout = 5;
 
+// Additional destinations of a dense GEMM's output: every tile of C is also stored, at the same
+// row/column offsets and with the same pitch, to each of these matrices. Used to push a rank's
+// column slab of C straight into its peers' memory over NVLink while later tiles are still being
+// computed (plain peer stores; nothing is ever loaded from a peer).
+constexpr int kMaxPushTargets = 7;
+struct PushTargets {
+  float *c[kMaxPushTargets];
+  int count;
+};
+
 struct DenseTileShape {
   int block_m, block_n, block_k, stages;
   unsigned smem_bytes;
@@ -27,14 +37,15 @@ DenseTileShape dense_tile_shape();
 //   tmap_b: B as a 2-D tensor {n (inner), k}, box {64, 64},  128-byte swizzle.
 cudaError_t launch_gemm_dense(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, float *c,
                               int m, int n, int k, long long ldc, int dtype, int group_n,
-                              int max_ctas, int *status, cudaStream_t stream);
+                              int max_ctas, const PushTargets &push, int *status, cudaStream_t stream);
 
 // Same product on CTA pairs: clusters of two CTAs own 256x256 tiles and issue
 // tcgen05.mma.cta_group::2. Takes the same tensor maps as launch_gemm_dense. `max_ctas` is
 // rounded down to an even number of CTAs.
 cudaError_t launch_gemm_dense_pair(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, float *c,
                                    int m, int n, int k, long long ldc, int dtype, int group_n,
-                                   int max_ctas, int *status, cudaStream_t stream);
+                                   int max_ctas, const PushTargets &push, int *status,
+                                   cudaStream_t stream);
 
 // Whether the dense variant runs on CTA pairs for this problem.
 bool dense_uses_pairs(long long m, long long n, long long k, int sm_count);

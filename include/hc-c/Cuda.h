@@ -193,6 +193,33 @@ HC_CUDA_CAPI_EXPORTED int hcCudaGemm(HcCudaContext *ctx, const HcCudaGemmArgs *a
  * asynchronous and about twice as fast. */
 HC_CUDA_CAPI_EXPORTED int hcCudaGemmHost(HcCudaContext *ctx, const HcCudaGemmArgs *args);
 
+/* ---- the product fused with its gather (N-sharded GEMM, one process per GPU) ------------- */
+
+#define HC_CUDA_MAX_PUSH_TARGETS 7
+#define HC_CUDA_IPC_HANDLE_BYTES 64
+
+/* Asynchronous. hcCudaGemm on device buffers (dense kernels; AUTO means DENSE here) whose
+ * epilogue also stores every tile of C, at the same offsets and pitch, to `targets[0 ..
+ * n_targets)`: device pointers usable from this device, normally the same window of a
+ * row-major C in each peer GPU's memory, opened with hcCudaIpcOpen. The slab of C a rank
+ * computes thus reaches all ranks over NVLink (plain peer stores) while later tiles are still
+ * being multiplied, instead of in a separate all-gather afterwards; nothing is ever loaded from
+ * a peer. c and the targets must be 16-byte aligned, ldc a multiple of 4. A rank's copy is
+ * complete when every rank has synchronised its own launch (host barrier after
+ * hcCudaContextSynchronize). No counterpart in the reference. */
+HC_CUDA_CAPI_EXPORTED int hcCudaGemmPush(HcCudaContext *ctx, const HcCudaGemmArgs *args,
+                                         float *const *targets, int n_targets);
+
+/* Cross-process sharing of a device allocation on one node (CUDA IPC): export the handle of an
+ * allocation made with hcCudaMalloc (pass its base pointer), carry the 64 bytes to another
+ * process by any host channel, open it there (peer access is enabled on demand), close it
+ * before the owner frees the memory. */
+HC_CUDA_CAPI_EXPORTED int hcCudaIpcExport(HcCudaContext *ctx, const void *device_ptr, void *handle,
+                                          size_t handle_bytes);
+HC_CUDA_CAPI_EXPORTED int hcCudaIpcOpen(HcCudaContext *ctx, const void *handle, size_t handle_bytes,
+                                        void **device_ptr);
+HC_CUDA_CAPI_EXPORTED int hcCudaIpcClose(HcCudaContext *ctx, void *device_ptr);
+
 /* ---- launching without allocating ---------------------------------------------------- */
 
 /* Bytes of device memory every GPU that loads this library sets aside for the entry point

@@ -1,5 +1,6 @@
 """The N-sharded product on two GPUs of one box: one process per GPU, each computing its own
-column slab through the C ABI, then an NCCL all-gather of the C slabs. Skipped on a box with
+column slab through the C ABI, then an NCCL all-gather of the C slabs; and the same product with
+the gather fused into the GEMM epilogue (tiles pushed to the peer over NVLink, CUDA IPC). Skipped on a box with
 fewer than two GPUs. NVLS is switched off so that a rank that dies never leaves NVLink multicast
 state behind."""
 
@@ -59,6 +60,39 @@ def _rank_main(rank: int, world: int, out_dir: str) -> None:
     ctx.synchronize()
     np.save(Path(out_dir) / f"gathered_{rank}.npy", gathered.to_numpy())
     ctx.comm_destroy()
+
+    # The same product with the gather fused into the epilogue: tiles are pushed into every
+    # rank's row-major C through CUDA IPC pointers.
+    from hc.distributed import PushedMatmul
+
+    def exchange(tag: str, payload: bytes) -> list[bytes]:
+        mine = Path(out_dir) / f"{tag}_{rank}.bin"
+        tmp = mine.with_suffix(".tmp")
+        tmp.write_bytes(payload)
+        tmp.rename(mine)
+        out = []
+        for r in range(world):
+            path = Path(out_dir) / f"{tag}_{r}.bin"
+            deadline = time.time() + 60
+            while not path.exists():
+                if time.time() > deadline:
+                    raise TimeoutError(f"rank {r} never published {tag}")
+                time.sleep(0.02)
+            out.append(path.read_bytes())
+        return out
+
+    pushed = PushedMatmul(ctx, M, N, world, rank, align=workloads.SHARDED_BLOCK_COLUMNS)
+    full_c = pushed.setup(lambda payload: exchange("ipc", payload))
+    full_c.fill_bytes(0xFF)
+    ctx.synchronize()
+    exchange("ready", b"1")          # nobody pushes before every C has been poisoned
+    pushed.run(da, db)
+    ctx.synchronize()
+    exchange("done", b"1")           # every rank's pushes have landed
+    np.save(Path(out_dir) / f"pushed_{rank}.npy", full_c.to_numpy())
+    exchange("saved", b"1")
+    pushed.close()
+    exchange("closed", b"1")         # no rank frees its C while a peer still maps it
     ctx.close()
 
 
@@ -93,3 +127,5 @@ def test_two_gpus_shard_and_gather(tmp_path) -> None:
         assert workloads.check_against_float64(full, a, b)["ok"]
         first = full if first is None else first
         assert np.array_equal(full, first)  # every rank holds the same gathered C
+        pushed = np.load(tmp_path / f"pushed_{r}.npy")
+        assert np.array_equal(pushed, first)  # the fused push yields the same C, row-major, on every rank

@@ -165,11 +165,7 @@ def test_nothing_outside_c_is_written(gpu_ctx, shape, frame) -> None:
     da, db = gpu_ctx.to_device(a), gpu_ctx.to_device(b)
     frame_buf = cuda.DeviceBuffer(gpu_ctx, (m + 2, n + pad), np.float32)
     frame_buf.fill_bytes(0x7F)
-    window = cuda.DeviceBuffer.__new__(cuda.DeviceBuffer)
-    window.ctx, window.shape, window.dtype, window.ndim = gpu_ctx, (m, n), np.dtype(np.float32), 2
-    window.ld, window._rows = n + pad, m
-    window.nbytes = 0  # the window does not own memory
-    window.ptr = frame_buf.ptr + ((n + pad) + col_off) * 4  # one row down, col_off columns in
+    window = frame_buf.window(1, m + 1, col_off, n + col_off)  # one row down, col_off columns in
     gpu_ctx.gemm(da, db, window)
     gpu_ctx.synchronize()
     whole = frame_buf.to_numpy()
@@ -181,7 +177,6 @@ def test_nothing_outside_c_is_written(gpu_ctx, shape, frame) -> None:
     assert (whole[mask].view(np.uint32) == sentinel.view(np.uint32)).all()
     assert np.array_equal(da.to_numpy().view(np.uint16), a.view(np.uint16))
     assert np.array_equal(db.to_numpy().view(np.uint16), b.view(np.uint16))
-    window.ptr = 0
 
 
 def test_unaligned_pitches_and_bases_on_device(gpu_ctx) -> None:
@@ -254,20 +249,39 @@ def test_device_call_rejects_bad_arguments(gpu_ctx) -> None:
     a, b = random_inputs(128, 256, 64, "float16")
     da, db = gpu_ctx.to_device(a), gpu_ctx.to_device(b)
     with pytest.raises(hc.DeviceError, match="must not overlap"):
-        alias = cuda.DeviceBuffer.__new__(cuda.DeviceBuffer)
-        alias.ctx, alias.shape, alias.dtype, alias.ndim, alias.ld, alias._rows, alias.nbytes = (
-            gpu_ctx, (128, 256), np.dtype(np.float32), 2, 256, 128, 0)
-        alias.ptr = db.ptr
-        try:
-            gpu_ctx.gemm(da, db, alias)
-        finally:
-            alias.ptr = 0
+        gpu_ctx.gemm(da, db, cuda.DeviceBuffer.wrap(gpu_ctx, db.ptr, (128, 256), np.float32))
     dc = gpu_ctx.empty((128, 256), np.float32)
     with pytest.raises(hc.DeviceError, match="skinny variant needs m <= 64"):
         gpu_ctx.gemm(da, db, dc, variant=cuda.VARIANT_SKINNY)
     gpu_ctx.gemm(da, db, dc)  # the context is still usable
     gpu_ctx.synchronize()
     assert_close_to_oracle(dc.to_numpy(), a, b)
+
+
+@pytest.mark.parametrize("shape", [(300, 520, 200), (100, 300, 96), (1024, 2048, 512)])
+def test_push_targets_receive_every_tile(gpu_ctx, shape) -> None:
+    """hcCudaGemmPush on one device: two extra buffers (here local ones; across GPUs they are
+    peers' memory) must end up identical to C, windows and edges included."""
+    m, n, k = shape
+    a, b = random_inputs(m, n, k, "float16")
+    da, db = gpu_ctx.to_device(a), gpu_ctx.to_device(b)
+    frames = [gpu_ctx.empty((m + 1, n + 8), np.float32) for _ in range(3)]
+    for frame in frames:
+        frame.fill_bytes(0x7F)
+    views = [frame.window(1, m + 1, 4, n + 4) for frame in frames]
+    gpu_ctx.gemm(da, db, views[0], push=views[1:])
+    gpu_ctx.synchronize()
+    results = [frame.to_numpy() for frame in frames]
+    assert_close_to_oracle(np.ascontiguousarray(results[0][1:, 4 : n + 4]), a, b)
+    assert np.array_equal(results[0], results[1]) and np.array_equal(results[0], results[2])
+    sentinel = np.frombuffer(b"\x7f\x7f\x7f\x7f", np.uint32)[0]
+    assert (results[0][0].view(np.uint32) == sentinel).all()
+    assert (results[0][:, :4].view(np.uint32) == sentinel).all() and (results[0][:, n + 4 :].view(np.uint32) == sentinel).all()
+    with pytest.raises(hc.DeviceError, match="overlaps c"):
+        gpu_ctx.gemm(da, db, views[0], push=[views[0]])
+    odd = gpu_ctx.empty((m, n + 1), np.float32)
+    with pytest.raises(hc.DeviceError, match="multiple of 4"):
+        gpu_ctx.gemm(da, db, odd.window(0, m, 0, n), push=[odd.window(0, m, 0, n)])
 
 
 def test_a_wait_that_runs_out_is_reported_and_survivable(gpu_ctx) -> None:
