@@ -48,9 +48,16 @@ def _tile_origin(tile_row, tile_col):
     return tile_row * TILE_M, tile_col * TILE_N
 
 
-def build_tiled_wmma_matmul(element_type):
-    """Returns the `@kernel` function for A, B of `element_type` (np.float16 or bfloat16)."""
+def build_tiled_wmma_matmul(element_type, b_transposed=False):
+    """Returns the `@kernel` function for A, B of `element_type` (np.float16 or bfloat16).
+
+    With `b_transposed` the kernel takes B stored transposed, `b: Buffer[N, K]` (the usual layout
+    of a weight matrix): its k-loop loads `b[col0:col0+16, k0:k0+16]` windows and the intrinsic's
+    B tile is (n, k). The arithmetic is the same, C = A @ B^T-as-stored.
+    """
     element_type = np.dtype(element_type).type
+    if b_transposed:
+        return _build_transposed_b(element_type)
 
     @kernel.intrinsic(
         scope=WorkItem,
@@ -172,35 +179,146 @@ def build_tiled_wmma_matmul(element_type):
     return tiled_wmma_matmul
 
 
+def _build_transposed_b(element_type):
+    """The kernel for B stored [N, K]; same structure as above with the B tile indexed (n, k)."""
+
+    @kernel.intrinsic(
+        scope=WorkItem,
+        effects="pure",
+        const_attrs={"wave_size", "arch"},
+        operand_types=(
+            undef_type(),
+            tensor_type((TILE_M, TILE_K), element_type),
+            tensor_type((TILE_N, TILE_K), element_type),
+            vector_type((TILE_K,), element_type),
+            vector_type((TILE_K,), element_type),
+            vector_type((ACC_PER_LANE,), np.float32),
+            idx_type(),
+        ),
+        result_types=(vector_type((ACC_PER_LANE,), np.float32),),
+    )
+    def wmma_16x16x16_bt(group, a_tile, bt_tile, a_frag, b_frag, acc_frag, *, lane, wave_size, arch):
+        """Host-simulator body: D = A.B^T + C for one 16x16x16 step, B tile given as (n, k)."""
+        del a_frag, b_frag, arch
+        a_vals = a_tile.with_inactive(value=element_type(0))
+        b_vals = bt_tile.with_inactive(value=element_type(0))
+        col = lane % TILE_N
+        row_step = wave_size // TILE_N
+        out = np.empty((ACC_PER_LANE,), dtype=np.float32)
+        for slot in range(ACC_PER_LANE):
+            row = lane // TILE_N + slot * row_step
+            total = np.float32(acc_frag[slot])
+            for kk in range(TILE_K):
+                total += np.float32(a_vals[row, kk]) * np.float32(b_vals[col, kk])
+            out[slot] = total
+        return group.vload(out, shape=(ACC_PER_LANE,))
+
+    @wmma_16x16x16_bt.lower(target=NVIDIA_TARGET)
+    def _lower_to_umma(ctx, *operands, **attrs):
+        del operands, attrs
+        return {"variant": "auto", "b_operand": "K-major", "input_dtype": np.dtype(element_type).name,
+                "instruction": getattr(ctx, "instruction", "tcgen05.mma.kind::f16")}
+
+    @kernel.func(scope=WorkItem)
+    def a_fragment(wi, a_tile):
+        return a_tile[wi.local_id()[0] % TILE_M, :].vec().with_inactive(value=element_type(0))
+
+    @kernel.func(scope=WorkItem)
+    def b_fragment(wi, bt_tile):
+        return bt_tile[wi.local_id()[0] % TILE_N, :].vec().with_inactive(value=element_type(0))
+
+    @kernel.func(scope=WorkGroup)
+    def zero_accumulators(group):
+        @group.workitems
+        def per_lane(wi):
+            del wi
+            return group.vzeros(shape=(ACC_PER_LANE,), dtype=np.float32)
+
+        return per_lane()
+
+    @kernel.func(scope=WorkGroup)
+    def multiply_accumulate(group, a_tile, bt_tile, acc):
+        @group.workitems
+        def per_lane(wi):
+            lane = wi.local_id()[0]
+            return wmma_16x16x16_bt(
+                group,
+                a_tile,
+                bt_tile,
+                a_fragment(wi, a_tile),
+                b_fragment(wi, bt_tile),
+                acc[:, lane, 0],
+                lane=lane,
+                wave_size=WAVE_LANES,
+                arch=ARCH,
+            )
+
+        return per_lane()
+
+    @kernel.func(scope=WorkGroup)
+    def store_accumulators(group, c, row0, col0, acc):
+        @group.workitems
+        def per_lane(wi):
+            lane = wi.local_id()[0]
+            col = col0 + lane % TILE_N
+            first = row0 + lane // TILE_N
+            group.store(c[first : row0 + TILE_M : WAVE_LANES // TILE_N, col : col + 1], acc[:, lane, :])
+
+        per_lane()
+
+    @kernel(
+        work_shape=(ceil_div(M, TILE_M) * WAVE_LANES, ceil_div(N, TILE_N)),
+        group_shape=(WAVE_LANES, 1),
+        subgroup_size=WAVE_LANES,
+    )
+    def tiled_wmma_matmul_bt(
+        group,
+        a: Buffer[M, K, element_type],
+        b: Buffer[N, K, element_type],
+        c: Buffer[M, N, np.float32],
+    ) -> None:
+        row0, col0 = _tile_origin(group.group_id[0], group.group_id[1])
+        acc = zero_accumulators(group)
+        for k0 in range(0, a.shape[1], TILE_K):
+            a_tile = group.load(a[row0 : row0 + TILE_M, k0 : k0 + TILE_K], shape=(TILE_M, TILE_K))
+            bt_tile = group.load(b[col0 : col0 + TILE_N, k0 : k0 + TILE_K], shape=(TILE_N, TILE_K))
+            acc = multiply_accumulate(group, a_tile, bt_tile, acc)
+        store_accumulators(group, c, row0, col0, acc)
+
+    tiled_wmma_matmul_bt.__name__ = f"tiled_wmma_matmul_bt_{np.dtype(element_type).name}"
+    return tiled_wmma_matmul_bt
+
+
 @functools.lru_cache(maxsize=None)
-def tiled_wmma_matmul_for(dtype_name):
+def tiled_wmma_matmul_for(dtype_name, b_transposed=False):
     """The kernel for "float16" or "bfloat16" (built once per process)."""
     if dtype_name == "bfloat16":
         import ml_dtypes
 
-        return build_tiled_wmma_matmul(ml_dtypes.bfloat16)
+        return build_tiled_wmma_matmul(ml_dtypes.bfloat16, b_transposed)
     if dtype_name == "float16":
-        return build_tiled_wmma_matmul(np.float16)
+        return build_tiled_wmma_matmul(np.float16, b_transposed)
     raise ValueError(f"unsupported element type {dtype_name!r}")
 
 
 @functools.lru_cache(maxsize=None)
-def compiled_for(dtype_name, device=None):
+def compiled_for(dtype_name, device=None, b_transposed=False):
     """`hc.compile(..., target="nvidia-sm100a")` of the kernel for one element type."""
-    return hc.compile(tiled_wmma_matmul_for(dtype_name), target=NVIDIA_TARGET, device=device)
+    return hc.compile(tiled_wmma_matmul_for(dtype_name, b_transposed), target=NVIDIA_TARGET, device=device)
 
 
-def gpu_wmma_matmul(a, b, *, device=None):
+def gpu_wmma_matmul(a, b, *, device=None, b_transposed=False):
     """C = A @ B on the GPU; the counterpart of the reference's simulate_gfx11_wmma_matmul
-    (examples/amdgpu_gfx11_wmma_matmul.py:338-348), with the same argument checks."""
+    (examples/amdgpu_gfx11_wmma_matmul.py:338-348), with the same argument checks. With
+    `b_transposed`, `b` holds B transposed (shape (n, k)) and the Buffer[N, K] kernel is used."""
     if a.ndim != 2 or b.ndim != 2:
         raise ValueError("A and B must be rank-2 matrices")
-    if a.shape[1] != b.shape[0]:
+    if a.shape[1] != (b.shape[1] if b_transposed else b.shape[0]):
         raise ValueError("A.shape[1] must match B.shape[0]")
     if a.dtype != b.dtype or a.dtype.name not in ("float16", "bfloat16"):
         raise ValueError("this example expects float16 or bfloat16 A and B operands of one type")
-    c = np.zeros((a.shape[0], b.shape[1]), dtype=np.float32)
-    compiled_for(a.dtype.name, device)(a, b, c)
+    c = np.zeros((a.shape[0], b.shape[0] if b_transposed else b.shape[1]), dtype=np.float32)
+    compiled_for(a.dtype.name, device, b_transposed)(a, b, c)
     return c
 
 

@@ -86,19 +86,19 @@ class CompiledKernel:
             ctx = a.ctx
             if b.ctx is not ctx or c.ctx is not ctx:
                 raise LaunchError("device buffers must belong to one context")
-            ctx.gemm(a, b, c, variant=variant)
+            ctx.gemm(a, b, c, variant=variant, b_transposed=plan.b_transposed)
             ctx.synchronize()
             return
         ctx = cuda.default_context(self.device)
         a_host = _row_major(a)
         b_host = _row_major(b)
         if _is_row_major(c) and c.flags.writeable:
-            ctx.gemm_host(a_host, b_host, c, variant=variant)
+            ctx.gemm_host(a_host, b_host, c, variant=variant, b_transposed=plan.b_transposed)
             return
         if not c.flags.writeable:
             raise LaunchError(f"{plan.c_param} must be writeable")
         staged = np.empty(c.shape, np.float32)
-        ctx.gemm_host(a_host, b_host, staged, variant=variant)
+        ctx.gemm_host(a_host, b_host, staged, variant=variant, b_transposed=plan.b_transposed)
         c[...] = staged
 
     # -- text ---------------------------------------------------------------------------

@@ -74,6 +74,9 @@ class GemmContract:
     has_target_lowering: bool  # intrinsic registered `.lower(target="nvidia-sm100a")`
     # What that lowering hook returned (a mapping; see `_run_lowering_hook`), or None.
     lowering: Any = None
+    # True when the kernel's b is Buffer[N, K] (B stored transposed) and its k-loop loads
+    # b[cols, k0:k0+tk] windows, with the intrinsic's B tile shaped (tn, tk).
+    b_transposed: bool = False
 
 
 @dataclass(frozen=True)
@@ -176,7 +179,7 @@ def _int_shape(record: dict[str, object]) -> tuple[int, ...] | None:
         return None
 
 
-def _match_mma_contract(fn: Any, input_dtype: str) -> tuple[tuple[int, int, int], int] | str:
+def _match_mma_contract(fn: Any, input_dtype: str, b_transposed: bool = False) -> tuple[tuple[int, int, int], int] | str:
     """Returns ((tm, tn, tk), accumulators per lane) or a text saying why it does not match."""
     meta = fn.__hc_intrinsic__
     if _scope_name(meta.scope) != "WorkItem":
@@ -198,6 +201,8 @@ def _match_mma_contract(fn: Any, input_dtype: str) -> tuple[tuple[int, int, int]
     if any(shape is None for shape in shapes):
         return "tile and fragment shapes must be integer literals"
     sa, sb, sfa, sfb, sacc, sres = shapes
+    if b_transposed:
+        sb = (sb[1], sb[0]) if len(sb) == 2 else sb  # the B tile is declared (tn, tk)
     if len(sa) != 2 or len(sb) != 2 or sa[1] != sb[0]:
         return f"tile shapes {sa} x {sb} do not chain"
     tm, tk, tn = sa[0], sa[1], sb[1]
@@ -298,7 +303,7 @@ def _names_in(node: ast.AST | None) -> set[str]:
 
 
 def _check_body(kernel_fn: Any, params: list[str], a: str, b: str, c: str, tile: tuple[int, int, int],
-                k_dim: Any) -> list[str]:
+                k_dim: Any, b_transposed: bool = False) -> list[str]:
     """Structural check of the k-loop: `for k0 in range(0, K, tk)` with one masked load of an
     A window `a[rows, k0:k0+tk]` and one of a B window `b[k0:k0+tk, cols]`, then a store
     that receives `c`. Returns problems (empty when the body has the expected shape)."""
@@ -337,7 +342,7 @@ def _check_body(kernel_fn: Any, params: list[str], a: str, b: str, c: str, tile:
         stop = it.args[1]
         # K may be spelled `a.shape[1]`, `b.shape[0]` or as the K symbol / literal itself.
         spelled = ast.unparse(stop).replace(" ", "")
-        k_names = {f"{a}.shape[1]", f"{b}.shape[0]"}
+        k_names = {f"{a}.shape[1]", f"{b}.shape[1]" if b_transposed else f"{b}.shape[0]"}
         if isinstance(k_dim, str):
             k_names.add(k_dim)
         if spelled not in k_names and const_value(stop) != k_dim:
@@ -345,7 +350,7 @@ def _check_body(kernel_fn: Any, params: list[str], a: str, b: str, c: str, tile:
     else:
         problems.append(f"k-loop must be `for k0 in range(0, K, {tk})`")
     k_var = loop.target.id if isinstance(loop.target, ast.Name) else None
-    for name, axis in ((a, 1), (b, 0)):
+    for name, axis in ((a, 1), (b, 1 if b_transposed else 0)):
         loads = shape.loads_in_loop[name]
         if len(loads) != 1:
             problems.append(f"expected one group.load of a window of `{name}` per k-step, found {len(loads)}")
@@ -440,16 +445,23 @@ def recognise_tiled_matmul(kernel_fn: Any) -> tuple[GemmContract | None, list[st
 
     # Operand roles from how the extents chain: a[M,K] b[K,N] c[M,N] in any parameter order.
     roles = None
+    b_transposed = False
     for ia, ib, ic in ((0, 1, 2), (0, 2, 1), (1, 0, 2), (1, 2, 0), (2, 0, 1), (2, 1, 0)):
-        (pa, (am, ak), da), (pb, (bk, bn), db), (pc, (cm, cn), dc) = specs[ia], specs[ib], specs[ic]
-        if ak == bk and am == cm and bn == cn and dc == "float32" and da == db and da in _SUPPORTED_INPUT_DTYPES:
-            roles = (pa, pb, pc, am, bn, ak, da)
-            if (ia, ib, ic) == (0, 1, 2):
-                break
+        (pa, (am, ak), da), (pb, b_dims, db), (pc, (cm, cn), dc) = specs[ia], specs[ib], specs[ic]
+        if not (am == cm and dc == "float32" and da == db and da in _SUPPORTED_INPUT_DTYPES):
+            continue
+        for transposed in (False, True):
+            bk, bn = (b_dims[1], b_dims[0]) if transposed else b_dims
+            # With m == n == k as fixed equal extents the untransposed reading wins.
+            if ak == bk and bn == cn and roles is None:
+                roles = (pa, pb, pc, am, bn, ak, da)
+                b_transposed = transposed
+        if roles is not None and (ia, ib, ic) == (0, 1, 2):
+            break
     if roles is None:
         described = ", ".join(f"{p}: Buffer{list(k)} {d}" for p, k, d in specs)
         return None, [
-            f"{name}: buffers ({described}) are not a[M,K], b[K,N] of one of "
+            f"{name}: buffers ({described}) are not a[M,K], b[K,N] (or b[N,K]) of one of "
             f"{list(_SUPPORTED_INPUT_DTYPES)} and c[M,N] float32"
         ]
     a, b, c, m_dim, n_dim, k_dim, input_dtype = roles
@@ -457,7 +469,7 @@ def recognise_tiled_matmul(kernel_fn: Any) -> tuple[GemmContract | None, list[st
     intrinsics = [fn for fn in _reachable_callables(kernel_fn) if hasattr(fn, "__hc_intrinsic__")]
     matches = []
     for fn in intrinsics:
-        outcome = _match_mma_contract(fn, input_dtype)
+        outcome = _match_mma_contract(fn, input_dtype, b_transposed)
         if isinstance(outcome, str):
             problems.append(f"intrinsic {fn.__name__}: {outcome}")
         else:
@@ -473,7 +485,7 @@ def recognise_tiled_matmul(kernel_fn: Any) -> tuple[GemmContract | None, list[st
 
     wave, geometry_problems = _check_geometry(meta, {"m": m_dim, "n": n_dim, "k": k_dim}, tile, acc_len)
     problems.extend(geometry_problems)
-    problems.extend(_check_body(kernel_fn, params, a, b, c, tile, k_dim))
+    problems.extend(_check_body(kernel_fn, params, a, b, c, tile, k_dim, b_transposed))
     if problems:
         return None, [f"{name}: {p}" for p in problems]
 
@@ -488,5 +500,6 @@ def recognise_tiled_matmul(kernel_fn: Any) -> tuple[GemmContract | None, list[st
         intrinsic_const_attrs=tuple(sorted(intrinsic.__hc_intrinsic__.const_attrs)),
         has_target_lowering=NVIDIA_SM100A in lowerings,
         lowering=lowering,
+        b_transposed=b_transposed,
     )
     return contract, []

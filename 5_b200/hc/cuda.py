@@ -59,6 +59,7 @@ class _GemmArgs(ctypes.Structure):
         ("a", ctypes.c_void_p), ("lda", ctypes.c_int64),
         ("b", ctypes.c_void_p), ("ldb", ctypes.c_int64),
         ("c", ctypes.c_void_p), ("ldc", ctypes.c_int64),
+        ("b_layout", ctypes.c_int32), ("reserved", ctypes.c_int32),
     ]
 
 
@@ -194,21 +195,27 @@ class GemmPlan:
                 f"launches={self.kernel_launches}, scratch={self.scratch_bytes})")
 
 
+B_KN, B_NK = 0, 1  # B stored [k, n] (default) or transposed, [n, k]
+
+
 def _gemm_args(m: int, n: int, k: int, dtype: Any, a: int | None, lda: int, b: int | None, ldb: int,
-               c: int | None, ldc: int, variant: int) -> _GemmArgs:
-    return _GemmArgs(m, n, k, dtype_code(dtype), variant, a, lda, b, ldb, c, ldc)
+               c: int | None, ldc: int, variant: int, b_transposed: bool = False) -> _GemmArgs:
+    return _GemmArgs(m, n, k, dtype_code(dtype), variant, a, lda, b, ldb, c, ldc,
+                     B_NK if b_transposed else B_KN, 0)
 
 
 def plan_gemm(m: int, n: int, k: int, dtype: Any, *, a: int = 0x1000, lda: int | None = None,
               b: int = 0x40000000, ldb: int | None = None, c: int = 0x80000000,
-              ldc: int | None = None, variant: int = VARIANT_AUTO, sm_count: int = 148) -> GemmPlan:
+              ldc: int | None = None, variant: int = VARIANT_AUTO, sm_count: int = 148,
+              b_transposed: bool = False) -> GemmPlan:
     """Validates a problem and returns its launch plan without touching a device.
 
     The pointer arguments are plain integers that are only inspected (null, alignment,
     overlap); the defaults are well-aligned, far-apart placeholders.
     """
-    args = _gemm_args(m, n, k, dtype, a, k if lda is None else lda, b, n if ldb is None else ldb,
-                      c, n if ldc is None else ldc, variant)
+    args = _gemm_args(m, n, k, dtype, a, k if lda is None else lda, b,
+                      (k if b_transposed else n) if ldb is None else ldb, c, n if ldc is None else ldc, variant,
+                      b_transposed)
     info = _PlanInfo()
     status = library().hcCudaGemmPlan(ctypes.byref(args), sm_count, ctypes.byref(info))
     if status:
@@ -284,15 +291,17 @@ class Context:
 
     # -- the hot path -------------------------------------------------------------------
     def gemm(self, a: "DeviceBuffer", b: "DeviceBuffer", c: "DeviceBuffer", *,
-             variant: int = VARIANT_AUTO, push: "list[DeviceBuffer] | None" = None) -> None:
+             variant: int = VARIANT_AUTO, push: "list[DeviceBuffer] | None" = None,
+             b_transposed: bool = False) -> None:
         """Enqueues C = A @ B on device buffers (asynchronous; see `synchronize`).
 
+        `b_transposed`: `b` holds B transposed, shape (n, k).
         `push`: up to 7 more buffers shaped and pitched like `c` (typically windows of peer
         GPUs' copies of C, see `ipc_open`) that receive every tile of C as well.
         """
         m, k = a.shape
-        n = b.shape[1]
-        args = _gemm_args(m, n, k, a.dtype, a.ptr, a.ld, b.ptr, b.ld, c.ptr, c.ld, variant)
+        n = b.shape[0] if b_transposed else b.shape[1]
+        args = _gemm_args(m, n, k, a.dtype, a.ptr, a.ld, b.ptr, b.ld, c.ptr, c.ld, variant, b_transposed)
         if not push:
             self._check(self._lib.hcCudaGemm(self._handle, ctypes.byref(args)))
             return
@@ -321,13 +330,16 @@ class Context:
             self._check(self._lib.hcCudaIpcClose(self._handle, ptr))
 
     def gemm_host(self, a: np.ndarray, b: np.ndarray, c: np.ndarray, *,
-                  variant: int = VARIANT_AUTO) -> None:
-        """C = A @ B on host arrays: copies in, multiplies on the GPU, copies C back in place."""
+                  variant: int = VARIANT_AUTO, b_transposed: bool = False) -> None:
+        """C = A @ B on host arrays: copies in, multiplies on the GPU, copies C back in place.
+        With `b_transposed`, `b` holds B transposed, shape (n, k)."""
         m, k = a.shape
-        n = b.shape[1]
+        n = b.shape[0] if b_transposed else b.shape[1]
+        b_rows, b_cols = b.shape
         args = _gemm_args(m, n, k, a.dtype, a.ctypes.data, a.strides[0] // a.itemsize if m > 1 else max(k, 1),
-                          b.ctypes.data, b.strides[0] // b.itemsize if k > 1 else max(n, 1),
-                          c.ctypes.data, c.strides[0] // c.itemsize if m > 1 else max(n, 1), variant)
+                          b.ctypes.data, b.strides[0] // b.itemsize if b_rows > 1 else max(b_cols, 1),
+                          c.ctypes.data, c.strides[0] // c.itemsize if m > 1 else max(n, 1), variant,
+                          b_transposed)
         self._check(self._lib.hcCudaGemmHost(self._handle, ctypes.byref(args)))
 
     def selftest_device_timeout(self, budget_cycles: int = 2_000_000) -> None:

@@ -196,13 +196,20 @@ int plan_gemm(const HcCudaContext *ctx, const HcCudaGemmArgs *args, int sm_count
   if (args->lda < k || args->lda > kMaxPitch)
     return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "lda (%lld) must be at least k (%lld)",
                 (long long)args->lda, (long long)k);
-  if (args->ldb < n || args->ldb > kMaxPitch)
-    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "ldb (%lld) must be at least n (%lld)",
-                (long long)args->ldb, (long long)n);
+  if (args->b_layout != HC_CUDA_B_KN && args->b_layout != HC_CUDA_B_NK)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "b_layout must be HC_CUDA_B_KN or HC_CUDA_B_NK (got %d)",
+                args->b_layout);
+  if (args->reserved != 0)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "reserved must be 0");
+  const bool b_nk = args->b_layout == HC_CUDA_B_NK;
+  const int64_t b_rows = b_nk ? n : k, b_cols = b_nk ? k : n;  // as stored
+  if (args->ldb < b_cols || args->ldb > kMaxPitch)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "ldb (%lld) must be at least %s (%lld)",
+                (long long)args->ldb, b_nk ? "k" : "n", (long long)b_cols);
   if ((reinterpret_cast<uintptr_t>(args->a) & 1) != 0 || (reinterpret_cast<uintptr_t>(args->b) & 1) != 0)
     return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "a and b must be 2-byte aligned");
   const size_t a_bytes = (static_cast<size_t>(m - 1) * args->lda + k) * 2;
-  const size_t b_bytes = (static_cast<size_t>(k - 1) * args->ldb + n) * 2;
+  const size_t b_bytes = (static_cast<size_t>(b_rows - 1) * args->ldb + b_cols) * 2;
   const size_t c_bytes = (static_cast<size_t>(m - 1) * args->ldc + n) * 4;
   if (ranges_overlap(args->c, c_bytes, args->a, a_bytes) ||
       ranges_overlap(args->c, c_bytes, args->b, b_bytes))
@@ -225,7 +232,7 @@ int plan_gemm(const HcCudaContext *ctx, const HcCudaGemmArgs *args, int sm_count
   if (plan->repack_a)
     scratch += round_up(m * round_up(k, kRepackPitchElems) * 2, 1024);
   if (plan->repack_b)
-    scratch += round_up(k * round_up(n, kRepackPitchElems) * 2, 1024);
+    scratch += round_up(b_rows * round_up(b_cols, kRepackPitchElems) * 2, 1024);
   plan->kernel_launches = 1 + ((plan->repack_a || plan->repack_b) ? 1 : 0);
 
   if (variant == HC_CUDA_GEMM_DENSE) {
@@ -348,6 +355,8 @@ int enqueue_gemm(HcCudaContext *ctx, const HcCudaGemmArgs *args, const HcCudaGem
   const void *a = args->a;
   const void *b = args->b;
   int64_t lda = args->lda, ldb = args->ldb;
+  const bool b_nk = args->b_layout == HC_CUDA_B_NK;
+  const int b_rows = b_nk ? n : k, b_cols = b_nk ? k : n;  // B as stored
   char *cursor = static_cast<char *>(ctx->scratch);
   if (plan.repack_a || plan.repack_b) {
     // One launch copies whichever operands need it into scratch with 128-byte-aligned pitches.
@@ -361,14 +370,14 @@ int enqueue_gemm(HcCudaContext *ctx, const HcCudaGemmArgs *args, const HcCudaGem
       cursor += round_up(static_cast<int64_t>(m) * pitch_a * 2, 1024);
     }
     if (plan.repack_b) {
-      pitch_b = round_up(n, kRepackPitchElems);
+      pitch_b = round_up(b_cols, kRepackPitchElems);
       src_b = b;
       dst_b = cursor;
-      cursor += round_up(static_cast<int64_t>(k) * pitch_b * 2, 1024);
+      cursor += round_up(static_cast<int64_t>(b_rows) * pitch_b * 2, 1024);
     }
     HC_TRY_CUDA(ctx, hc::sm100::launch_repack_pitch_two(src_a, lda, dst_a, pitch_a, plan.repack_a ? m : 0, k,
-                                                        src_b, ldb, dst_b, pitch_b, plan.repack_b ? k : 0, n,
-                                                        ctx->stream));
+                                                        src_b, ldb, dst_b, pitch_b, plan.repack_b ? b_rows : 0,
+                                                        b_cols, ctx->stream));
     if (plan.repack_a) {
       a = dst_a;
       lda = pitch_a;
@@ -380,21 +389,27 @@ int enqueue_gemm(HcCudaContext *ctx, const HcCudaGemmArgs *args, const HcCudaGem
   }
 
   CUtensorMap tmap_a, tmap_b;
+  const int b_layout = b_nk ? hc::sm100::kBLayoutNK : hc::sm100::kBLayoutKN;
   if (plan.variant == HC_CUDA_GEMM_DENSE) {
     const hc::sm100::DenseTileShape t = hc::sm100::dense_tile_shape();
+    const bool pairs = hc::sm100::dense_uses_pairs(m, n, k, ctx->prop.multiProcessorCount);
     if (int rc = encode_map(ctx, &tmap_a, args->dtype, a, k, m, static_cast<uint64_t>(lda) * 2,
                             t.block_k, t.block_m))
       return rc;
-    if (int rc = encode_map(ctx, &tmap_b, args->dtype, b, n, k, static_cast<uint64_t>(ldb) * 2, 64,
-                            t.block_k))
+    // B stored [K, N]: 64 (n) x 64 (k) boxes. Stored [N, K]: one box of 64 (k) x the CTA's rows
+    // of n (256 on single CTAs, 128 per CTA of a pair).
+    if (int rc = b_nk ? encode_map(ctx, &tmap_b, args->dtype, b, k, n, static_cast<uint64_t>(ldb) * 2, t.block_k,
+                                   pairs ? t.block_n / 2 : t.block_n)
+                      : encode_map(ctx, &tmap_b, args->dtype, b, n, k, static_cast<uint64_t>(ldb) * 2, 64,
+                                   t.block_k))
       return rc;
-    if (hc::sm100::dense_uses_pairs(m, n, k, ctx->prop.multiProcessorCount)) {
+    if (pairs) {
       HC_TRY_CUDA(ctx, hc::sm100::launch_gemm_dense_pair(tmap_a, tmap_b, args->c, m, n, k, args->ldc,
-                                                         args->dtype, ctx->group_n, plan.grid, push,
+                                                         args->dtype, ctx->group_n, plan.grid, b_layout, push,
                                                          ctx->status_dev, ctx->stream));
     } else {
       HC_TRY_CUDA(ctx, hc::sm100::launch_gemm_dense(tmap_a, tmap_b, args->c, m, n, k, args->ldc,
-                                                    args->dtype, ctx->group_n, plan.grid, push,
+                                                    args->dtype, ctx->group_n, plan.grid, b_layout, push,
                                                     ctx->status_dev, ctx->stream));
     }
     return HC_CUDA_OK;
@@ -405,8 +420,10 @@ int enqueue_gemm(HcCudaContext *ctx, const HcCudaGemmArgs *args, const HcCudaGem
   if (int rc = encode_map(ctx, &tmap_a, args->dtype, a, k, m, static_cast<uint64_t>(lda) * 2,
                           s.block_k, padded_m))
     return rc;
-  if (int rc = encode_map(ctx, &tmap_b, args->dtype, b, n, k, static_cast<uint64_t>(ldb) * 2, 64,
-                          s.block_k))
+  if (int rc = b_nk ? encode_map(ctx, &tmap_b, args->dtype, b, k, n, static_cast<uint64_t>(ldb) * 2, s.block_k,
+                                 s.block_n)
+                    : encode_map(ctx, &tmap_b, args->dtype, b, n, k, static_cast<uint64_t>(ldb) * 2, 64,
+                                 s.block_k))
     return rc;
   float *partials = nullptr;
   if (plan.splits > 1) {
@@ -416,7 +433,7 @@ int enqueue_gemm(HcCudaContext *ctx, const HcCudaGemmArgs *args, const HcCudaGem
   }
   HC_TRY_CUDA(ctx, hc::sm100::launch_gemm_skinny(tmap_a, tmap_b, args->c, m, n, k, args->ldc,
                                                  args->dtype, plan.splits, partials, ctx->counters,
-                                                 plan.grid, ctx->status_dev, ctx->stream));
+                                                 plan.grid, b_layout, ctx->status_dev, ctx->stream));
   return HC_CUDA_OK;
 }
 
@@ -841,11 +858,13 @@ int hcCudaGemmHost(HcCudaContext *ctx, const HcCudaGemmArgs *args) {
   HC_TRY_CUDA(ctx, cudaSetDevice(ctx->device));
   // Device copies get pitches that satisfy TMA (16 bytes), so no repack pass is needed.
   const size_t lda = static_cast<size_t>(round_up(args->k, kRepackPitchElems));
-  const size_t ldb = static_cast<size_t>(round_up(args->n, kRepackPitchElems));
+  const bool b_nk = args->b_layout == HC_CUDA_B_NK;
+  const size_t b_rows = b_nk ? n : k, b_cols = b_nk ? k : n;  // B as stored
+  const size_t ldb = static_cast<size_t>(round_up(static_cast<int64_t>(b_cols), kRepackPitchElems));
   const size_t ldc = static_cast<size_t>(round_up(args->n, 4));
   if (int rc = ensure_stage(ctx, 0, m * lda * 2))
     return rc;
-  if (int rc = ensure_stage(ctx, 1, k * ldb * 2))
+  if (int rc = ensure_stage(ctx, 1, b_rows * ldb * 2))
     return rc;
   if (int rc = ensure_stage(ctx, 2, m * ldc * 4))
     return rc;
@@ -864,7 +883,7 @@ int hcCudaGemmHost(HcCudaContext *ctx, const HcCudaGemmArgs *args) {
     HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(ctx->stage[0], lda * 2, args->a, static_cast<size_t>(args->lda) * 2,
                                        k * 2, m, cudaMemcpyHostToDevice, ctx->stream));
     HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(ctx->stage[1], ldb * 2, args->b, static_cast<size_t>(args->ldb) * 2,
-                                       n * 2, k, cudaMemcpyHostToDevice, ctx->stream));
+                                       b_cols * 2, b_rows, cudaMemcpyHostToDevice, ctx->stream));
     if (int rc = plan_gemm(ctx, &dev, ctx->prop.multiProcessorCount, false, &plan))
       return rc;
     if (int rc = enqueue_gemm(ctx, &dev, plan))
@@ -887,7 +906,7 @@ int hcCudaGemmHost(HcCudaContext *ctx, const HcCudaGemmArgs *args) {
   HC_TRY_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_in, ctx->fence_event, 0));
   HC_TRY_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_out, ctx->fence_event, 0));
   HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(ctx->stage[1], ldb * 2, args->b, static_cast<size_t>(args->ldb) * 2,
-                                     n * 2, k, cudaMemcpyHostToDevice, ctx->copy_in));
+                                     b_cols * 2, b_rows, cudaMemcpyHostToDevice, ctx->copy_in));
   for (int p = 0; p < panels; ++p) {
     const size_t row0 = static_cast<size_t>(p) * panel_rows;
     const size_t rows = row0 + panel_rows <= m ? panel_rows : m - row0;

@@ -81,7 +81,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
 gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                        const __grid_constant__ CUtensorMap tmap_b, float *__restrict__ c, int m, int n,
                        int k, long long ldc, uint32_t idesc, int tiles_m, int tiles_n, int group_n,
-                       int l2_hints, PushTargets push, int *status) {
+                       int l2_hints, int b_layout, PushTargets push, int *status) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t smem_base = (raw_addr + 1023u) & ~1023u;
@@ -161,10 +161,15 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
           for (int sub = 0; sub < kKSub; ++sub) {
             const int k0 = kb * kBlockK + sub * 64;
             tma_load_2d_pair_hint(a_dst + sub * kASubBytes, &tmap_a, leader_full, k0, m0, pol_a);
+            if (b_layout == kBLayoutKN) {
 #pragma unroll
-            for (int j = 0; j < kCtaN / 64; ++j)
-              tma_load_2d_pair_hint(b_dst + j * kBChunkBytes + sub * kBBoxBytes, &tmap_b, leader_full,
-                                    n0 + j * 64, k0, pol_b);
+              for (int j = 0; j < kCtaN / 64; ++j)
+                tma_load_2d_pair_hint(b_dst + j * kBChunkBytes + sub * kBBoxBytes, &tmap_b, leader_full,
+                                      n0 + j * 64, k0, pol_b);
+            } else {
+              // B stored [N, K]: this CTA's 128 rows (n) x 64 k, K-major like A, one box per sub-block.
+              tma_load_2d_pair_hint(b_dst + sub * kASubBytes, &tmap_b, leader_full, k0, n0, pol_b);
+            }
           }
           if (++stage == kStages) {
             stage = 0;
@@ -194,14 +199,19 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
           tcgen05_fence_after_sync();
           const uint32_t a_addr = smem_base + stage * kStageBytes;
           const uint32_t b_addr = a_addr + kATileBytes;
-          const uint64_t b_desc = make_smem_desc_sw128(b_addr, kBChunkBytes, 1024);
+          const bool b_kn = b_layout == kBLayoutKN;
 #pragma unroll
           for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
             // A: one 16 KiB sub-block per 64 k, +32 bytes per 16-wide k-step inside its swizzle
-            // row. B: k-rows are contiguous across the stage, +2 KiB per k-step.
-            const uint64_t a_desc = make_smem_desc_sw128(a_addr + (kk / 4) * kASubBytes, 16, 1024);
-            umma_f16_ss_pair(d_tmem, a_desc + static_cast<uint64_t>((kk % 4) * 2),
-                             b_desc + static_cast<uint64_t>(kk * 128), idesc, (kb | kk) != 0 ? 1u : 0u);
+            // row. B stored [K, N]: k-rows are contiguous across the stage, +2 KiB per k-step;
+            // B stored [N, K]: laid out and advanced exactly like A.
+            const uint64_t a_desc = make_smem_desc_sw128(a_addr + (kk / 4) * kASubBytes, 16, 1024) +
+                                    static_cast<uint64_t>((kk % 4) * 2);
+            const uint64_t b_desc =
+                b_kn ? make_smem_desc_sw128(b_addr, kBChunkBytes, 1024) + static_cast<uint64_t>(kk * 128)
+                     : make_smem_desc_sw128(b_addr + (kk / 4) * kASubBytes, 16, 1024) +
+                           static_cast<uint64_t>((kk % 4) * 2);
+            umma_f16_ss_pair(d_tmem, a_desc, b_desc, idesc, (kb | kk) != 0 ? 1u : 0u);
           }
           // Hand ring slot `stage` back to both producers.
           umma_commit_pair(map_to_cta(empty_bar(stage), 0));
@@ -261,8 +271,8 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
 cudaError_t launch_gemm_dense_pair(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, float *c,
                                    int m, int n, int k, long long ldc, int dtype, int group_n,
-                                   int max_ctas, const PushTargets &push, int *status,
-    cudaStream_t stream) {
+                                   int max_ctas, int b_layout, const PushTargets &push, int *status,
+                                   cudaStream_t stream) {
   using namespace dense_pair;
   static thread_local int configured_device = -1;
   int device = 0;
@@ -287,14 +297,14 @@ cudaError_t launch_gemm_dense_pair(const CUtensorMap &tmap_a, const CUtensorMap 
   if (num_tiles < clusters)
     clusters = num_tiles;
   const uint32_t idesc = make_idesc_f16(dtype == kDTypeBF16 ? 1u : 0u, /*a_mn_major=*/false,
-                                        /*b_mn_major=*/true, kTileM, kTileN);
+                                        /*b_mn_major=*/b_layout == kBLayoutKN, kTileM, kTileN);
   if (group_n < 1)
     group_n = 1;
   int l2_hints = 3;
   if (const char *h = std::getenv("HC_CUDA_L2_HINTS"))  // tuning aid
     l2_hints = std::atoi(h);
   gemm_dense_pair_kernel<<<static_cast<unsigned>(clusters * 2), kNumThreads, kSmemBytes, stream>>>(
-      tmap_a, tmap_b, c, m, n, k, ldc, idesc, tiles_m, tiles_n, group_n, l2_hints, push, status);
+      tmap_a, tmap_b, c, m, n, k, ldc, idesc, tiles_m, tiles_n, group_n, l2_hints, b_layout, push, status);
   return cudaGetLastError();
 }
 

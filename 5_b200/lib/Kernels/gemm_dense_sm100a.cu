@@ -70,7 +70,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_dense_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   const __grid_constant__ CUtensorMap tmap_b, float *__restrict__ c, int m, int n,
                   int k, long long ldc, uint32_t idesc, int tiles_m, int tiles_n, int group_n,
-                  PushTargets push, int *status) {
+                  int b_layout, PushTargets push, int *status) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t smem_base = (raw_addr + 1023u) & ~1023u;  // swizzled tiles need 1 KiB alignment
@@ -133,10 +133,14 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint32_t b_dst = a_dst + kATileBytes;
           mbar_arrive_expect_tx(full_bar(stage), kStageBytes);
           tma_load_2d(a_dst, &tmap_a, full_bar(stage), kb * kBlockK, m0);
+          if (b_layout == kBLayoutKN) {
 #pragma unroll
-          for (int j = 0; j < kBlockN / 64; ++j)
-            tma_load_2d(b_dst + j * kBChunkBytes, &tmap_b, full_bar(stage), n0 + j * 64,
-                        kb * kBlockK);
+            for (int j = 0; j < kBlockN / 64; ++j)
+              tma_load_2d(b_dst + j * kBChunkBytes, &tmap_b, full_bar(stage), n0 + j * 64, kb * kBlockK);
+          } else {
+            // B stored [N, K]: one box of 256 rows (n) x 64 k, K-major like A.
+            tma_load_2d(b_dst, &tmap_b, full_bar(stage), kb * kBlockK, n0);
+          }
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
@@ -167,14 +171,18 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint32_t b_addr = a_addr + kATileBytes;
           // A: K-major, groups of 8 rows are 1024 bytes apart.
           const uint64_t a_desc = make_smem_desc_sw128(a_addr, 16, 1024);
-          // B: N-major, 64-column chunks are kBChunkBytes apart, groups of 8 k-rows 1024.
-          const uint64_t b_desc = make_smem_desc_sw128(b_addr, kBChunkBytes, 1024);
+          // B stored [K, N]: N-major, 64-column chunks are kBChunkBytes apart, groups of 8 k-rows
+          // 1024. B stored [N, K]: K-major exactly like A.
+          const bool b_kn = b_layout == kBLayoutKN;
+          const uint64_t b_desc = b_kn ? make_smem_desc_sw128(b_addr, kBChunkBytes, 1024)
+                                       : make_smem_desc_sw128(b_addr, 16, 1024);
+          const uint64_t b_step = b_kn ? 128 : 2;  // descriptor units (16 bytes) per 16-wide k-step
 #pragma unroll
           for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
             // Per 16-wide k-step: A advances 32 bytes inside the swizzle row, B advances
             // two groups of 8 k-rows (2048 bytes); both in 16-byte descriptor units.
             umma_f16_ss(d_tmem, a_desc + static_cast<uint64_t>(kk * 2),
-                        b_desc + static_cast<uint64_t>(kk * 128), idesc,
+                        b_desc + static_cast<uint64_t>(kk) * b_step, idesc,
                         (kb | kk) != 0 ? 1u : 0u);
           }
           umma_commit(empty_bar(stage));
@@ -231,8 +239,8 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
 cudaError_t launch_gemm_dense(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, float *c,
                               int m, int n, int k, long long ldc, int dtype, int group_n,
-                              int max_ctas, const PushTargets &push, int *status,
-    cudaStream_t stream) {
+                              int max_ctas, int b_layout, const PushTargets &push, int *status,
+                              cudaStream_t stream) {
   using namespace dense;
   static thread_local int configured_device = -1;
   int device = 0;
@@ -253,12 +261,12 @@ cudaError_t launch_gemm_dense(const CUtensorMap &tmap_a, const CUtensorMap &tmap
     return cudaErrorInvalidValue;
   const int grid = static_cast<int>(num_tiles < max_ctas ? num_tiles : max_ctas);
   const uint32_t idesc = make_idesc_f16(dtype == kDTypeBF16 ? 1u : 0u, /*a_mn_major=*/false,
-                                        /*b_mn_major=*/true, kBlockM, kBlockN);
+                                        /*b_mn_major=*/b_layout == kBLayoutKN, kBlockM, kBlockN);
   if (group_n < 1)
     group_n = 1;
   gemm_dense_kernel<<<grid, kNumThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, c, m, n, k, ldc,
                                                                idesc, tiles_m, tiles_n, group_n,
-                                                               push, status);
+                                                               b_layout, push, status);
   return cudaGetLastError();
 }
 

@@ -10,6 +10,12 @@
 namespace hc {
 namespace sm100 {
 
+// How B is stored: [K, N] row-major (the hc kernel's Buffer[K, N]) or [N, K] row-major (B
+// transposed, Buffer[N, K]). The matching tensor map is {n inner, k} with 64x64 boxes, or
+// {k inner, n} with a 64 x (CTA's rows of n) box.
+constexpr int kBLayoutKN = 0;
+constexpr int kBLayoutNK = 1;
+
 constexpr int kDTypeF16 = 0;
 constexpr int kDTypeBF16 = 1;
 
@@ -37,14 +43,15 @@ DenseTileShape dense_tile_shape();
 //   tmap_b: B as a 2-D tensor {n (inner), k}, box {64, 64},  128-byte swizzle.
 cudaError_t launch_gemm_dense(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, float *c,
                               int m, int n, int k, long long ldc, int dtype, int group_n,
-                              int max_ctas, const PushTargets &push, int *status, cudaStream_t stream);
+                              int max_ctas, int b_layout, const PushTargets &push, int *status,
+                              cudaStream_t stream);
 
 // Same product on CTA pairs: clusters of two CTAs own 256x256 tiles and issue
 // tcgen05.mma.cta_group::2. Takes the same tensor maps as launch_gemm_dense. `max_ctas` is
 // rounded down to an even number of CTAs.
 cudaError_t launch_gemm_dense_pair(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, float *c,
                                    int m, int n, int k, long long ldc, int dtype, int group_n,
-                                   int max_ctas, const PushTargets &push, int *status,
+                                   int max_ctas, int b_layout, const PushTargets &push, int *status,
                                    cudaStream_t stream);
 
 // Whether the dense variant runs on CTA pairs for this problem.
@@ -73,8 +80,8 @@ size_t skinny_counters_bytes(int n);
 //   entry and are zero again on exit.
 cudaError_t launch_gemm_skinny(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, float *c,
                                int m, int n, int k, long long ldc, int dtype, int splits,
-                               float *partials, unsigned *counters, int max_ctas, int *status,
-                               cudaStream_t stream);
+                               float *partials, unsigned *counters, int max_ctas, int b_layout,
+                               int *status, cudaStream_t stream);
 
 // Copies a rows x cols matrix of 16-bit elements into a buffer whose row pitch is a
 // multiple of 8 elements (16 bytes), as TMA requires. Columns [cols, round_up(cols, 8))

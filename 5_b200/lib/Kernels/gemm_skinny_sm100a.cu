@@ -58,6 +58,7 @@ __global__ void __launch_bounds__(kNumThreads, kCtasPerSm)
 gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a,
                    const __grid_constant__ CUtensorMap tmap_b, float *__restrict__ c, int m, int n,
                    int k, long long ldc, uint32_t idesc, int n_tiles, int splits, int num_stages,
+                   int b_layout,
                    float *__restrict__ partials, unsigned *__restrict__ counters, int *status) {
   using Cfg = Config<kMp>;
   const uint32_t kStages = static_cast<uint32_t>(num_stages);  // ring depth of this launch
@@ -126,10 +127,15 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint32_t b_dst = smem_base + stage * Cfg::kStageBytes;
           const uint32_t a_dst = b_dst + kBTileBytes;
           mbar_arrive_expect_tx(full_bar(stage), Cfg::kStageBytes);
+          if (b_layout == kBLayoutKN) {
 #pragma unroll
-          for (int j = 0; j < kBlockN / 64; ++j)
-            tma_load_2d_hint(b_dst + j * kBChunkBytes, &tmap_b, full_bar(stage), n0 + j * 64,
-                             kb * kBlockK, stream_policy);
+            for (int j = 0; j < kBlockN / 64; ++j)
+              tma_load_2d_hint(b_dst + j * kBChunkBytes, &tmap_b, full_bar(stage), n0 + j * 64,
+                               kb * kBlockK, stream_policy);
+          } else {
+            // B stored [N, K]: 128 rows (n) x 64 k in one box, K-major.
+            tma_load_2d_hint(b_dst, &tmap_b, full_bar(stage), kb * kBlockK, n0, stream_policy);
+          }
           tma_load_2d_hint(a_dst, &tmap_a, full_bar(stage), kb * kBlockK, 0, keep_policy);
           if (++stage == kStages) {
             stage = 0;
@@ -162,13 +168,17 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a,
           tcgen05_fence_after_sync();
           const uint32_t bt_addr = smem_base + stage * Cfg::kStageBytes;
           const uint32_t a_addr = bt_addr + kBTileBytes;
-          // UMMA "A" operand = B^T tile (128 n x 64 k), n contiguous: MN-major.
-          const uint64_t bt_desc = make_smem_desc_sw128(bt_addr, kBChunkBytes, 1024);
+          // UMMA "A" operand = B^T tile (128 n x 64 k): MN-major when B is stored [K, N] (n
+          // contiguous), K-major when it is stored [N, K].
+          const bool b_kn = b_layout == kBLayoutKN;
+          const uint64_t bt_desc = b_kn ? make_smem_desc_sw128(bt_addr, kBChunkBytes, 1024)
+                                        : make_smem_desc_sw128(bt_addr, 16, 1024);
+          const uint64_t bt_step = b_kn ? 128 : 2;
           // UMMA "B" operand = A tile (kMp rows x 64 k), k contiguous: K-major.
           const uint64_t a_desc = make_smem_desc_sw128(a_addr, 16, 1024);
 #pragma unroll
           for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
-            umma_f16_ss(d_tmem, bt_desc + static_cast<uint64_t>(kk * 128),
+            umma_f16_ss(d_tmem, bt_desc + static_cast<uint64_t>(kk) * bt_step,
                         a_desc + static_cast<uint64_t>(kk * 2), idesc,
                         (kb != kb_begin || kk != 0) ? 1u : 0u);
           }
@@ -282,7 +292,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a,
 template <int kMp>
 cudaError_t launch(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, float *c, int m, int n,
                    int k, long long ldc, int dtype, int splits, float *partials,
-                   unsigned *counters, int max_ctas, int *status, cudaStream_t stream) {
+                   unsigned *counters, int max_ctas, int b_layout, int *status, cudaStream_t stream) {
   using Cfg = Config<kMp>;
   static thread_local int configured_device = -1;
   int device = 0;
@@ -301,10 +311,11 @@ cudaError_t launch(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, float *
   const int grid = static_cast<int>(units < max_ctas ? units : max_ctas);
   // max_ctas is two per SM; a grid of at most half of that leaves one CTA per SM.
   const int num_stages = grid * 2 <= max_ctas ? Cfg::kStagesAlone : Cfg::kStagesShared;
-  const uint32_t idesc = make_idesc_f16(dtype == kDTypeBF16 ? 1u : 0u, /*a_mn_major=*/true,
+  const uint32_t idesc = make_idesc_f16(dtype == kDTypeBF16 ? 1u : 0u, /*a_mn_major=*/b_layout == kBLayoutKN,
                                         /*b_mn_major=*/false, kBlockN, kMp);
+  // (The first flag describes the UMMA "A" operand, which is B^T here.)
   gemm_skinny_kernel<kMp><<<grid, kNumThreads, Cfg::smem_bytes(num_stages), stream>>>(
-      tmap_a, tmap_b, c, m, n, k, ldc, idesc, n_tiles, splits, num_stages, partials, counters, status);
+      tmap_a, tmap_b, c, m, n, k, ldc, idesc, n_tiles, splits, num_stages, b_layout, partials, counters, status);
   return cudaGetLastError();
 }
 
@@ -366,19 +377,19 @@ size_t skinny_counters_bytes(int n) {
 
 cudaError_t launch_gemm_skinny(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, float *c,
                                int m, int n, int k, long long ldc, int dtype, int splits,
-                               float *partials, unsigned *counters, int max_ctas, int *status,
-                               cudaStream_t stream) {
+                               float *partials, unsigned *counters, int max_ctas, int b_layout,
+                               int *status, cudaStream_t stream) {
   if (m < 1 || m > 64 || splits < 1)
     return cudaErrorInvalidValue;
   const int mp = skinny::padded_m(m);
   if (mp == 16)
     return skinny::launch<16>(tmap_a, tmap_b, c, m, n, k, ldc, dtype, splits, partials, counters,
-                              max_ctas, status, stream);
+                              max_ctas, b_layout, status, stream);
   if (mp == 32)
     return skinny::launch<32>(tmap_a, tmap_b, c, m, n, k, ldc, dtype, splits, partials, counters,
-                              max_ctas, status, stream);
+                              max_ctas, b_layout, status, stream);
   return skinny::launch<64>(tmap_a, tmap_b, c, m, n, k, ldc, dtype, splits, partials, counters,
-                            max_ctas, status, stream);
+                            max_ctas, b_layout, status, stream);
 }
 
 } // namespace sm100

@@ -39,7 +39,7 @@
 extern "C" {
 #endif
 
-#define HC_CUDA_API_VERSION 1
+#define HC_CUDA_API_VERSION 2
 
 typedef enum HcCudaStatus {
   HC_CUDA_OK = 0,
@@ -67,6 +67,13 @@ typedef enum HcCudaGemmVariant {
   HC_CUDA_GEMM_ZERO_FILL = 4 /* k == 0: C is set to zero, no kernel */
 } HcCudaGemmVariant;
 
+/* How B is laid out in memory. */
+typedef enum HcCudaBLayout {
+  HC_CUDA_B_KN = 0, /* B stored [k, n] row-major, pitch ldb >= n: the reference kernel's Buffer[K, N] */
+  HC_CUDA_B_NK = 1  /* B stored transposed, [n, k] row-major, pitch ldb >= k: a kernel whose b is
+                       Buffer[N, K] and whose k-loop loads b[col0:col0+16, k0:k0+16] */
+} HcCudaBLayout;
+
 /* C[m,n] = A[m,k] * B[k,n]; all three row-major with element pitches lda/ldb/ldc.
  * Mirrors the launch arguments of the reference kernel, `(a, b, c)` with
  * a: Buffer[M, K], b: Buffer[K, N], c: Buffer[M, N] (examples/...:306-311), the symbols
@@ -85,6 +92,8 @@ typedef struct HcCudaGemmArgs {
   int64_t ldb;
   float *c;
   int64_t ldc;
+  int32_t b_layout; /* HcCudaBLayout */
+  int32_t reserved; /* must be 0 */
 } HcCudaGemmArgs;
 
 /* What a GEMM call will do; computed on the host without touching a device. */

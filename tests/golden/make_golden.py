@@ -20,6 +20,9 @@ Fixtures (all produced by `hc.simulator.launch` on the example kernel):
   sim_bf16_m33_n17_k40_seed5
       a bfloat16 twin of the kernel: the example's source with its element type replaced,
       executed in memory by the same simulator
+  simbt_f16_m17_n19_k18_seed9
+      the transposed-B member of the family defined in 5_b200/examples/b200_wmma_matmul.py
+      (b stored [N, K]); `b_bits` holds B as stored
 The file blocked_reference.npz holds `reference_blocked_matmul` of the first four (the
 reference test's own comparison value, atol 2e-6).
 """
@@ -100,6 +103,23 @@ def main() -> int:
     c = np.zeros((33, 17), np.float32)
     twin.sim.launch(twin.tiled_gfx11_wmma_matmul, a, b, c)
     _save("sim_bf16_m33_n17_k40_seed5", a, b, c)
+
+    # This repository's transposed-B member of the kernel family (b: Buffer[N, K]), executed by the
+    # reference simulator: the file is loaded against the reference's `hc` package.
+    import importlib.util
+
+    path = REPO / "5_b200" / "examples" / "b200_wmma_matmul.py"
+    spec = importlib.util.spec_from_file_location("b200_example_under_reference", path)
+    mod = importlib.util.module_from_spec(spec)
+    mod.__package__ = "loaded_by_make_golden"  # keeps the script-mode sys.path insertion off
+    sys.modules[spec.name] = mod
+    spec.loader.exec_module(mod)
+    rng = np.random.default_rng(9)
+    a = rng.uniform(-1.0, 1.0, size=(17, 18)).astype(np.float16)
+    bt = rng.uniform(-1.0, 1.0, size=(19, 18)).astype(np.float16)
+    c = np.zeros((17, 19), np.float32)
+    mod.hc.simulator.launch(mod.tiled_wmma_matmul_for("float16", True), a, bt, c)
+    _save("simbt_f16_m17_n19_k18_seed9", a, bt, c)
     return 0
 
 

@@ -27,7 +27,7 @@ def test_library_exports_every_declared_symbol() -> None:
     for name in declared:
         assert hasattr(lib, name), f"{name} is declared in hc-c/Cuda.h but not exported"
     assert set(declared) == set(cuda.EXPORTS)
-    assert lib.hcCudaApiVersion() == 1
+    assert lib.hcCudaApiVersion() == 2
 
 
 def test_every_declaration_cites_or_describes_its_reference_counterpart() -> None:
@@ -81,6 +81,24 @@ def test_plan_flags_pitches_that_need_a_repack() -> None:
     assert not padded.repack_a and not padded.repack_b and padded.kernel_launches == 1
     misaligned_base = cuda.plan_gemm(128, 256, 64, "float16", a=0x1002)
     assert misaligned_base.repack_a and not misaligned_base.repack_b
+
+
+def test_plan_with_b_stored_transposed() -> None:
+    plan = cuda.plan_gemm(4095, 3073, 1031, "bfloat16", b_transposed=True)
+    assert plan.variant == "dense" and plan.repack_a and plan.repack_b and plan.kernel_launches == 2
+    assert plan.scratch_bytes >= 4095 * 1088 * 2 + 3073 * 1088 * 2  # B is n rows of k as stored
+    aligned = cuda.plan_gemm(512, 1000, 1024, "float16", b_transposed=True)
+    assert not aligned.repack_b  # pitch k = 1024 is TMA-legal although n is not a multiple of 8
+    with pytest.raises(DeviceError, match="ldb \\(63\\) must be at least k \\(64\\)"):
+        cuda.plan_gemm(128, 256, 64, "float16", ldb=63, b_transposed=True)
+    lib = cuda.library()
+    args = cuda._GemmArgs(8, 8, 8, 0, 0, 0x1000, 8, 0x2000, 8, 0x3000, 8, 5, 0)
+    info = cuda._PlanInfo()
+    assert lib.hcCudaGemmPlan(ctypes.byref(args), 148, ctypes.byref(info)) == 1
+    assert b"b_layout" in lib.hcCudaContextLastError(None)
+    args = cuda._GemmArgs(8, 8, 8, 0, 0, 0x1000, 8, 0x2000, 8, 0x3000, 8, 0, 1)
+    assert lib.hcCudaGemmPlan(ctypes.byref(args), 148, ctypes.byref(info)) == 1
+    assert b"reserved" in lib.hcCudaContextLastError(None)
 
 
 def test_plan_degenerate_shapes() -> None:

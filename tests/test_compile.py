@@ -148,6 +148,19 @@ def test_lowering_hook_is_called_and_steers_the_variant() -> None:
     assert hc.compile(other, target=NVIDIA_SM100A).plan.lowering is None  # no hook registered
 
 
+def test_transposed_b_member_is_recognised() -> None:
+    handle = compiled_for("float16", None, True)
+    plan = handle.plan
+    assert plan is not None and plan.b_transposed and plan.intrinsic_name == "wmma_16x16x16_bt"
+    assert (plan.m_dim, plan.n_dim, plan.k_dim) == ("M", "N", "K") and plan.tile == (16, 16, 16)
+    launch = handle.prepare(np.zeros((17, 18), np.float16), np.zeros((19, 18), np.float16),
+                            np.zeros((17, 19), np.float32))
+    assert launch.symbols == {"M": 17, "K": 18, "N": 19} and launch.work_shape == (64, 2)
+    with pytest.raises(hc.LaunchError, match="conflicting binding for K: 18 from 'a.shape\\[1\\]' vs 19 from 'b.shape\\[1\\]'"):
+        handle(np.zeros((17, 18), np.float16), np.zeros((18, 19), np.float16), np.zeros((17, 19), np.float32))
+    assert not compiled_for("float16").plan.b_transposed
+
+
 def test_family_members_are_recognised() -> None:
     for kwargs in ({}, {"in_dtype": __import__("ml_dtypes").bfloat16}, {"tile": (32, 16, 16), "acc": 16},
                    {"tile": (16, 16, 32)}, {"wave": 64, "acc": 4}):
@@ -161,7 +174,7 @@ def test_family_members_are_recognised() -> None:
     [
         ({"in_dtype": np.float32}, "are not a\\[M,K\\], b\\[K,N\\]"),
         ({"out_dtype": np.float16}, "c\\[M,N\\] float32"),
-        ({"b_dims": (N, K)}, "are not a\\[M,K\\], b\\[K,N\\]"),
+        ({"b_dims": (N, K)}, "axis 1 of the `b` window must advance with the k-loop variable"),
         ({"effects": "write"}, "expected 'pure'"),
         ({"acc": 4}, "accumulator values per lane"),
         ({"k_step": 8}, "k-loop must be"),

@@ -98,6 +98,38 @@ def test_skinny_ladder(shape: tuple[int, int, int], dtype: str) -> None:
     assert_close_to_oracle(gpu_wmma_matmul(a, b), a, b)
 
 
+TRANSPOSED_SHAPES = [
+    (17, 19, 18), (128, 256, 64), (129, 257, 65), (300, 520, 1000), (1024, 96, 130), (513, 1000, 264),
+    (2048, 2048, 512), (8, 129, 65), (7, 1000, 777), (33, 512, 2048), (64, 3000, 520), (8, 4096, 8192),
+]
+
+
+@pytest.mark.parametrize("shape", TRANSPOSED_SHAPES)
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+def test_b_stored_transposed(shape: tuple[int, int, int], dtype: str) -> None:
+    """The Buffer[N, K] member of the kernel family (B handed over as stored, [n, k]): dense
+    single-CTA, CTA-pair and skinny shapes, aligned and odd pitches."""
+    m, n, k = shape
+    a, b = random_inputs(m, n, k, dtype, scale=0.25)
+    bt = np.ascontiguousarray(b.T)
+    c = gpu_wmma_matmul(a, bt, b_transposed=True)
+    assert_close_to_oracle(c, a, b)
+
+
+def test_transposed_b_fixture_and_device_buffers(gpu_ctx) -> None:
+    a, bt, c_sim = load_golden("simbt_f16_m17_n19_k18_seed9")
+    assert_close_to_oracle(gpu_wmma_matmul(a, bt, b_transposed=True), a, np.ascontiguousarray(bt.T), expect=c_sim)
+    a, b = random_inputs(384, 1100, 520, "float16")
+    bt = np.ascontiguousarray(b.T)
+    da, dbt = gpu_ctx.to_device(a), gpu_ctx.to_device(bt)
+    dc = gpu_ctx.empty((384, 1100), np.float32)
+    compiled_for("float16", None, True)(da, dbt, dc)
+    expect = gpu_wmma_matmul(a, b)
+    assert_close_to_oracle(dc.to_numpy(), a, b)
+    # Same tiles and k order as the [K, N] kernel: the tensor cores see the same operands.
+    assert np.array_equal(dc.to_numpy(), expect)
+
+
 def test_skinny_split_k_is_deterministic(gpu_ctx) -> None:
     a, b = random_inputs(8, 2048, 8192, "float16", scale=0.1)
     assert gpu_ctx.plan(8, 2048, 8192, "float16").splits > 1

@@ -15,6 +15,7 @@ from oracle import cpu_ref
 
 def test_fixtures_are_present() -> None:
     assert len(GOLDEN_NAMES) == 6
+    assert (GOLDEN / "simbt_f16_m17_n19_k18_seed9.npz").exists()
     assert (GOLDEN / "blocked_reference.npz").exists()
 
 
@@ -25,6 +26,15 @@ def test_oracle_is_bit_identical_to_the_reference_simulator(name: str) -> None:
         out = fn(a, b)
         assert out.dtype == np.float32
         assert np.array_equal(out.view(np.uint32), c_sim.view(np.uint32)), fn.__name__
+
+
+def test_transposed_b_kernel_fixture() -> None:
+    """The Buffer[N, K] member of the kernel family, as the reference simulator executed it:
+    the oracle on the un-transposed B reproduces its output bit for bit."""
+    a, bt, c_sim = load_golden("simbt_f16_m17_n19_k18_seed9")
+    assert bt.shape == (19, 18)
+    out = cpu_ref.matmul_k_ascending(a, np.ascontiguousarray(bt.T))
+    assert np.array_equal(out.view(np.uint32), c_sim.view(np.uint32))
 
 
 def test_oracle_meets_the_reference_tests_own_tolerance() -> None:
