@@ -352,15 +352,18 @@ def run_gpu_arm(args, ranks: Ranks) -> None:
         a, b = workloads.make_inputs(name)
         local_n = w.n
     m, k = w.m, w.k
-    da, db = ctx.to_device(a), ctx.to_device(b)
+    bt = np.ascontiguousarray(b.T) if args.b_transposed else None
+    da, db = ctx.to_device(a), ctx.to_device(bt if args.b_transposed else b)
+    handle = compiled_for(w.dtype, ranks.local_rank, args.b_transposed)
+    gemm_kwargs = {"b_transposed": True} if args.b_transposed else {}
     dc = ctx.empty((m, local_n), np.float32)
-    plan = ctx.plan(m, local_n, k, w.dtype)
+    plan = ctx.plan(m, local_n, k, w.dtype, b_transposed=args.b_transposed)
     local_flops = workloads.flops(m, local_n, k)
     total_flops = workloads.flops(w.m, w.n, w.k)
 
     # ---- warm-up, then the timed region (device time, max over ranks) ----------------------
     for _ in range(max(args.warmup, 3)):
-        ctx.gemm(da, db, dc)
+        ctx.gemm(da, db, dc, **gemm_kwargs)
     ctx.synchronize()
     sampler = ClockSampler(ranks.local_rank)
     sampler.start()
@@ -371,7 +374,7 @@ def run_gpu_arm(args, ranks: Ranks) -> None:
     t_begin = time.perf_counter()
     start_ev.record()
     for _ in range(args.steps):
-        ctx.gemm(da, db, dc)
+        ctx.gemm(da, db, dc, **gemm_kwargs)
     stop_ev.record()
     elapsed_ms = stop_ev.elapsed_ms_since(start_ev)
     ctx.synchronize()
@@ -385,7 +388,7 @@ def run_gpu_arm(args, ranks: Ranks) -> None:
         c_begin = time.perf_counter()
         while time.perf_counter() - c_begin < 0.5:
             for _ in range(8):
-                ctx.gemm(da, db, dc)
+                ctx.gemm(da, db, dc, **gemm_kwargs)
             ctx.synchronize()
         clocks = sampler.summary(c_begin, time.perf_counter())
         clocks["note"] = "sampled over a 0.5 s continuation of the timed launches"
@@ -412,10 +415,11 @@ def run_gpu_arm(args, ranks: Ranks) -> None:
         return
     e2e_steps = max(1, min(args.steps, args.e2e_steps))
     pa = cuda.pinned_empty(a.shape, a.dtype)
-    pb = cuda.pinned_empty(b.shape, b.dtype)
+    host_b = bt if args.b_transposed else b
+    pb = cuda.pinned_empty(host_b.shape, host_b.dtype)
     pc = cuda.pinned_empty((m, local_n), np.float32)
     pa[...] = a
-    pb[...] = b
+    pb[...] = host_b
     handle(pa, pb, pc)  # warm-up: allocates the context's staging buffers
     default_ctx = cuda.default_context(ranks.local_rank)
     e0, e1 = default_ctx.event(), default_ctx.event()
@@ -536,6 +540,7 @@ def run_gpu_arm(args, ranks: Ranks) -> None:
         "data": "synthetic",
         "config": {"workload": name, "m": w.m, "n": w.n, "k": w.k, "input_dtype": w.dtype,
                    "accumulate": "fp32", "variant": plan.variant, "per_gpu_n": local_n,
+                   "b_layout": "[N, K] (transposed)" if args.b_transposed else "[K, N]",
                    "parallelism": f"n-sharded x{ranks.world}" if ranks.world > 1 else "single GPU",
                    "l2": "inputs larger than L2 (A+B+C per GPU exceed 126 MB)"
                    if a.nbytes + b.nbytes + c.nbytes > 126e6 else "working set fits L2",
@@ -574,6 +579,8 @@ def main() -> int:
     parser.add_argument("--e2e-steps", type=int, default=5)
     parser.add_argument("--no-gather", action="store_true")
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--b-transposed", action="store_true",
+                        help="hand B over stored [N, K] and use the Buffer[N, K] member of the kernel family")
     parser.add_argument("--cublas", action="store_true",
                         help="also time cuBLAS (torch.mm) on the same inputs with the same loop, for context")
     parser.add_argument("--quick", action="store_true",
@@ -581,6 +588,8 @@ def main() -> int:
     args = parser.parse_args()
     if args.steps < 1:
         parser.error("--steps must be at least 1")
+    if args.b_transposed and args.gpus > 1:
+        parser.error("--b-transposed is a single-GPU measurement")
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.gpus > 1 and world == 1 and args.impl != "reference":
