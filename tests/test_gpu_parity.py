@@ -130,6 +130,44 @@ def test_transposed_b_fixture_and_device_buffers(gpu_ctx) -> None:
     assert np.array_equal(dc.to_numpy(), expect)
 
 
+@pytest.mark.parametrize("seed", range(6))
+def test_random_shapes(seed: int, gpu_ctx) -> None:
+    """Seeded random shapes, small and awkward ones included, in both element types and both B
+    layouts, on device buffers with random extra pitch: every result against float64 and the
+    oracle's bound. Catches tile-scheduling and edge-predication corner cases the fixed ladders
+    do not name."""
+    rng = np.random.default_rng(1000 + seed)
+    for _ in range(12):
+        kind = rng.integers(0, 4)
+        if kind == 0:
+            m, n, k = (int(rng.integers(1, 65)), int(rng.integers(1, 2000)), int(rng.integers(1, 3000)))
+        elif kind == 1:
+            m, n, k = (int(rng.integers(65, 700)), int(rng.integers(1, 1500)), int(rng.integers(1, 600)))
+        elif kind == 2:
+            m, n, k = (int(rng.integers(1, 300)), int(rng.integers(1, 300)), int(rng.integers(1, 300)))
+        else:
+            m, n, k = (int(rng.integers(700, 2600)), int(rng.integers(1500, 4200)), int(rng.integers(16, 200)))
+        dtype = "bfloat16" if rng.integers(0, 2) else "float16"
+        transposed = bool(rng.integers(0, 2))
+        a = (rng.standard_normal((m, k)) * 0.5).astype(np_dtype(dtype))
+        b = (rng.standard_normal((k, n)) * 0.5).astype(np_dtype(dtype))
+        b_stored = np.ascontiguousarray(b.T) if transposed else b
+        pads = [int(x) for x in rng.choice([0, 0, 1, 3, 8, 64], size=3)]
+        da = cuda.DeviceBuffer(gpu_ctx, a.shape, a.dtype, ld=a.shape[1] + pads[0])
+        db = cuda.DeviceBuffer(gpu_ctx, b_stored.shape, b.dtype, ld=b_stored.shape[1] + pads[1])
+        dc = cuda.DeviceBuffer(gpu_ctx, (m, n), np.float32, ld=n + pads[2])
+        da.copy_from_host(a)
+        db.copy_from_host(b_stored)
+        dc.fill_bytes(0xFF)
+        gpu_ctx.gemm(da, db, dc, b_transposed=transposed)
+        gpu_ctx.synchronize()
+        c = dc.to_numpy()
+        report = workloads.check_against_float64(c, a, b)
+        assert report["ok"], (m, n, k, dtype, transposed, pads, report)
+        for buf in (da, db, dc):
+            buf.free()
+
+
 def test_skinny_split_k_is_deterministic(gpu_ctx) -> None:
     a, b = random_inputs(8, 2048, 8192, "float16", scale=0.1)
     assert gpu_ctx.plan(8, 2048, 8192, "float16").splits > 1
