@@ -48,16 +48,15 @@ def _tile_origin(tile_row, tile_col):
     return tile_row * TILE_M, tile_col * TILE_N
 
 
-def build_tiled_wmma_matmul(element_type, b_transposed=False):
-    """Returns the `@kernel` function for A, B of `element_type` (np.float16 or bfloat16).
+MEMBERS = ("plain", "accumulate", "fused")
+FUSED_SCALE = 0.125  # the constant the "fused" member multiplies its accumulators by
 
-    With `b_transposed` the kernel takes B stored transposed, `b: Buffer[N, K]` (the usual layout
-    of a weight matrix): its k-loop loads `b[col0:col0+16, k0:k0+16]` windows and the intrinsic's
-    B tile is (n, k). The arithmetic is the same, C = A @ B^T-as-stored.
-    """
-    element_type = np.dtype(element_type).type
-    if b_transposed:
-        return _build_transposed_b(element_type)
+
+def _helpers(element_type, b_transposed):
+    """The pieces every member of the family shares: the 16x16x16 intrinsic with its NVIDIA
+    lowering hook, and the workgroup functions around it. With `b_transposed` the B tile is
+    indexed (n, k)."""
+    b_tile_shape = (TILE_N, TILE_K) if b_transposed else (TILE_K, TILE_N)
 
     @kernel.intrinsic(
         scope=WorkItem,
@@ -66,7 +65,7 @@ def build_tiled_wmma_matmul(element_type, b_transposed=False):
         operand_types=(
             undef_type(),
             tensor_type((TILE_M, TILE_K), element_type),
-            tensor_type((TILE_K, TILE_N), element_type),
+            tensor_type(b_tile_shape, element_type),
             vector_type((TILE_K,), element_type),
             vector_type((TILE_K,), element_type),
             vector_type((ACC_PER_LANE,), np.float32),
@@ -90,7 +89,8 @@ def build_tiled_wmma_matmul(element_type, b_transposed=False):
             row = lane // TILE_N + slot * row_step
             total = np.float32(acc_frag[slot])
             for kk in range(TILE_K):
-                total += np.float32(a_vals[row, kk]) * np.float32(b_vals[kk, col])
+                b_value = b_vals[col, kk] if b_transposed else b_vals[kk, col]
+                total += np.float32(a_vals[row, kk]) * np.float32(b_value)
             out[slot] = total
         return group.vload(out, shape=(ACC_PER_LANE,))
 
@@ -105,6 +105,7 @@ def build_tiled_wmma_matmul(element_type, b_transposed=False):
             "instruction": getattr(ctx, "instruction", "tcgen05.mma.kind::f16"),
             "accumulator": "tensor memory, fp32",
             "cta_tiles": getattr(ctx, "cta_tiles", ()),
+            "b_operand": "K-major" if b_transposed else "MN-major",
             "input_dtype": np.dtype(element_type).name,
         }
 
@@ -114,7 +115,9 @@ def build_tiled_wmma_matmul(element_type, b_transposed=False):
 
     @kernel.func(scope=WorkItem)
     def b_fragment(wi, b_tile):
-        return b_tile[:, wi.local_id()[0] % TILE_N].vec().with_inactive(value=element_type(0))
+        lane_col = wi.local_id()[0] % TILE_N
+        column = b_tile[lane_col, :] if b_transposed else b_tile[:, lane_col]
+        return column.vec().with_inactive(value=element_type(0))
 
     @kernel.func(scope=WorkGroup)
     def zero_accumulators(group):
@@ -122,6 +125,19 @@ def build_tiled_wmma_matmul(element_type, b_transposed=False):
         def per_lane(wi):
             del wi
             return group.vzeros(shape=(ACC_PER_LANE,), dtype=np.float32)
+
+        return per_lane()
+
+    @kernel.func(scope=WorkGroup)
+    def load_accumulators(group, c, row0, col0):
+        """The lanes' accumulators start from the C tile (elements outside C read as 0)."""
+        c_tile = group.load(c[row0 : row0 + TILE_M, col0 : col0 + TILE_N], shape=(TILE_M, TILE_N))
+
+        @group.workitems
+        def per_lane(wi):
+            lane = wi.local_id()[0]
+            rows = c_tile[lane // TILE_N :: WAVE_LANES // TILE_N, lane % TILE_N]
+            return rows.vec().with_inactive(value=np.float32(0))
 
         return per_lane()
 
@@ -145,6 +161,19 @@ def build_tiled_wmma_matmul(element_type, b_transposed=False):
         return per_lane()
 
     @kernel.func(scope=WorkGroup)
+    def add_column_bias(group, bias, col0, acc):
+        """Adds bias[column] to every accumulator of that column."""
+        bias_tile = group.load(bias[col0 : col0 + TILE_N], shape=(TILE_N,))
+
+        @group.workitems
+        def per_lane(wi):
+            lane = wi.local_id()[0]
+            value = bias_tile[lane % TILE_N : lane % TILE_N + 1].vec().with_inactive(value=np.float32(0))
+            return acc[:, lane, 0] + value
+
+        return per_lane()
+
+    @kernel.func(scope=WorkGroup)
     def store_accumulators(group, c, row0, col0, acc):
         @group.workitems
         def per_lane(wi):
@@ -156,11 +185,104 @@ def build_tiled_wmma_matmul(element_type, b_transposed=False):
 
         per_lane()
 
-    @kernel(
-        work_shape=(ceil_div(M, TILE_M) * WAVE_LANES, ceil_div(N, TILE_N)),
-        group_shape=(WAVE_LANES, 1),
-        subgroup_size=WAVE_LANES,
-    )
+    return (zero_accumulators, load_accumulators, multiply_accumulate, add_column_bias, store_accumulators)
+
+
+_LAUNCH = dict(
+    work_shape=(ceil_div(M, TILE_M) * WAVE_LANES, ceil_div(N, TILE_N)),
+    group_shape=(WAVE_LANES, 1),
+    subgroup_size=WAVE_LANES,
+)
+
+
+def build_tiled_wmma_matmul(element_type, b_transposed=False, member="plain"):
+    """Returns the `@kernel` function for A, B of `element_type` (np.float16 or bfloat16).
+
+    With `b_transposed` the kernel takes B stored transposed, `b: Buffer[N, K]` (the usual layout
+    of a weight matrix): its k-loop loads `b[col0:col0+16, k0:k0+16]` windows and the intrinsic's
+    B tile is (n, k). The arithmetic is the same, C = A @ B^T-as-stored.
+
+    `member` selects what surrounds the k-loop:
+      "plain"       C = A @ B, the reference example itself;
+      "accumulate"  C = C + A @ B: the accumulators are loaded from `c` instead of zeroed;
+      "fused"       C = maximum(FUSED_SCALE * (A @ B) + bias, 0) with a fourth buffer
+                    `bias: Buffer[N, float32]`: element-wise statements between the k-loop and
+                    the store, which the NVIDIA target folds into the store of C.
+    """
+    element_type = np.dtype(element_type).type
+    if member not in MEMBERS:
+        raise ValueError(f"member must be one of {MEMBERS}")
+    if b_transposed and member != "plain":
+        raise ValueError("the transposed-B example is built as the plain member only")
+    (zero_accumulators, load_accumulators, multiply_accumulate, add_column_bias,
+     store_accumulators) = _helpers(element_type, b_transposed)
+    suffix = np.dtype(element_type).name
+
+    if b_transposed:
+
+        @kernel(**_LAUNCH)
+        def tiled_wmma_matmul_bt(
+            group,
+            a: Buffer[M, K, element_type],
+            b: Buffer[N, K, element_type],
+            c: Buffer[M, N, np.float32],
+        ) -> None:
+            row0, col0 = _tile_origin(group.group_id[0], group.group_id[1])
+            acc = zero_accumulators(group)
+            for k0 in range(0, a.shape[1], TILE_K):
+                a_tile = group.load(a[row0 : row0 + TILE_M, k0 : k0 + TILE_K], shape=(TILE_M, TILE_K))
+                bt_tile = group.load(b[col0 : col0 + TILE_N, k0 : k0 + TILE_K], shape=(TILE_N, TILE_K))
+                acc = multiply_accumulate(group, a_tile, bt_tile, acc)
+            store_accumulators(group, c, row0, col0, acc)
+
+        tiled_wmma_matmul_bt.__name__ = f"tiled_wmma_matmul_bt_{suffix}"
+        return tiled_wmma_matmul_bt
+
+    if member == "accumulate":
+
+        @kernel(**_LAUNCH)
+        def tiled_wmma_matmul_acc(
+            group,
+            a: Buffer[M, K, element_type],
+            b: Buffer[K, N, element_type],
+            c: Buffer[M, N, np.float32],
+        ) -> None:
+            row0, col0 = _tile_origin(group.group_id[0], group.group_id[1])
+            acc = load_accumulators(group, c, row0, col0)
+            for k0 in range(0, a.shape[1], TILE_K):
+                a_tile = group.load(a[row0 : row0 + TILE_M, k0 : k0 + TILE_K], shape=(TILE_M, TILE_K))
+                b_tile = group.load(b[k0 : k0 + TILE_K, col0 : col0 + TILE_N], shape=(TILE_K, TILE_N))
+                acc = multiply_accumulate(group, a_tile, b_tile, acc)
+            store_accumulators(group, c, row0, col0, acc)
+
+        tiled_wmma_matmul_acc.__name__ = f"tiled_wmma_matmul_acc_{suffix}"
+        return tiled_wmma_matmul_acc
+
+    if member == "fused":
+
+        @kernel(**_LAUNCH)
+        def tiled_wmma_matmul_fused(
+            group,
+            a: Buffer[M, K, element_type],
+            b: Buffer[K, N, element_type],
+            c: Buffer[M, N, np.float32],
+            bias: Buffer[N, np.float32],
+        ) -> None:
+            row0, col0 = _tile_origin(group.group_id[0], group.group_id[1])
+            acc = zero_accumulators(group)
+            for k0 in range(0, a.shape[1], TILE_K):
+                a_tile = group.load(a[row0 : row0 + TILE_M, k0 : k0 + TILE_K], shape=(TILE_M, TILE_K))
+                b_tile = group.load(b[k0 : k0 + TILE_K, col0 : col0 + TILE_N], shape=(TILE_K, TILE_N))
+                acc = multiply_accumulate(group, a_tile, b_tile, acc)
+            acc = acc * np.float32(FUSED_SCALE)
+            acc = add_column_bias(group, bias, col0, acc)
+            acc = np.maximum(acc, np.float32(0))
+            store_accumulators(group, c, row0, col0, acc)
+
+        tiled_wmma_matmul_fused.__name__ = f"tiled_wmma_matmul_fused_{suffix}"
+        return tiled_wmma_matmul_fused
+
+    @kernel(**_LAUNCH)
     def tiled_wmma_matmul(
         group,
         a: Buffer[M, K, element_type],
@@ -175,136 +297,27 @@ def build_tiled_wmma_matmul(element_type, b_transposed=False):
             acc = multiply_accumulate(group, a_tile, b_tile, acc)
         store_accumulators(group, c, row0, col0, acc)
 
-    tiled_wmma_matmul.__name__ = f"tiled_wmma_matmul_{np.dtype(element_type).name}"
+    tiled_wmma_matmul.__name__ = f"tiled_wmma_matmul_{suffix}"
     return tiled_wmma_matmul
 
 
-def _build_transposed_b(element_type):
-    """The kernel for B stored [N, K]; same structure as above with the B tile indexed (n, k)."""
-
-    @kernel.intrinsic(
-        scope=WorkItem,
-        effects="pure",
-        const_attrs={"wave_size", "arch"},
-        operand_types=(
-            undef_type(),
-            tensor_type((TILE_M, TILE_K), element_type),
-            tensor_type((TILE_N, TILE_K), element_type),
-            vector_type((TILE_K,), element_type),
-            vector_type((TILE_K,), element_type),
-            vector_type((ACC_PER_LANE,), np.float32),
-            idx_type(),
-        ),
-        result_types=(vector_type((ACC_PER_LANE,), np.float32),),
-    )
-    def wmma_16x16x16_bt(group, a_tile, bt_tile, a_frag, b_frag, acc_frag, *, lane, wave_size, arch):
-        """Host-simulator body: D = A.B^T + C for one 16x16x16 step, B tile given as (n, k)."""
-        del a_frag, b_frag, arch
-        a_vals = a_tile.with_inactive(value=element_type(0))
-        b_vals = bt_tile.with_inactive(value=element_type(0))
-        col = lane % TILE_N
-        row_step = wave_size // TILE_N
-        out = np.empty((ACC_PER_LANE,), dtype=np.float32)
-        for slot in range(ACC_PER_LANE):
-            row = lane // TILE_N + slot * row_step
-            total = np.float32(acc_frag[slot])
-            for kk in range(TILE_K):
-                total += np.float32(a_vals[row, kk]) * np.float32(b_vals[col, kk])
-            out[slot] = total
-        return group.vload(out, shape=(ACC_PER_LANE,))
-
-    @wmma_16x16x16_bt.lower(target=NVIDIA_TARGET)
-    def _lower_to_umma(ctx, *operands, **attrs):
-        del operands, attrs
-        return {"variant": "auto", "b_operand": "K-major", "input_dtype": np.dtype(element_type).name,
-                "instruction": getattr(ctx, "instruction", "tcgen05.mma.kind::f16")}
-
-    @kernel.func(scope=WorkItem)
-    def a_fragment(wi, a_tile):
-        return a_tile[wi.local_id()[0] % TILE_M, :].vec().with_inactive(value=element_type(0))
-
-    @kernel.func(scope=WorkItem)
-    def b_fragment(wi, bt_tile):
-        return bt_tile[wi.local_id()[0] % TILE_N, :].vec().with_inactive(value=element_type(0))
-
-    @kernel.func(scope=WorkGroup)
-    def zero_accumulators(group):
-        @group.workitems
-        def per_lane(wi):
-            del wi
-            return group.vzeros(shape=(ACC_PER_LANE,), dtype=np.float32)
-
-        return per_lane()
-
-    @kernel.func(scope=WorkGroup)
-    def multiply_accumulate(group, a_tile, bt_tile, acc):
-        @group.workitems
-        def per_lane(wi):
-            lane = wi.local_id()[0]
-            return wmma_16x16x16_bt(
-                group,
-                a_tile,
-                bt_tile,
-                a_fragment(wi, a_tile),
-                b_fragment(wi, bt_tile),
-                acc[:, lane, 0],
-                lane=lane,
-                wave_size=WAVE_LANES,
-                arch=ARCH,
-            )
-
-        return per_lane()
-
-    @kernel.func(scope=WorkGroup)
-    def store_accumulators(group, c, row0, col0, acc):
-        @group.workitems
-        def per_lane(wi):
-            lane = wi.local_id()[0]
-            col = col0 + lane % TILE_N
-            first = row0 + lane // TILE_N
-            group.store(c[first : row0 + TILE_M : WAVE_LANES // TILE_N, col : col + 1], acc[:, lane, :])
-
-        per_lane()
-
-    @kernel(
-        work_shape=(ceil_div(M, TILE_M) * WAVE_LANES, ceil_div(N, TILE_N)),
-        group_shape=(WAVE_LANES, 1),
-        subgroup_size=WAVE_LANES,
-    )
-    def tiled_wmma_matmul_bt(
-        group,
-        a: Buffer[M, K, element_type],
-        b: Buffer[N, K, element_type],
-        c: Buffer[M, N, np.float32],
-    ) -> None:
-        row0, col0 = _tile_origin(group.group_id[0], group.group_id[1])
-        acc = zero_accumulators(group)
-        for k0 in range(0, a.shape[1], TILE_K):
-            a_tile = group.load(a[row0 : row0 + TILE_M, k0 : k0 + TILE_K], shape=(TILE_M, TILE_K))
-            bt_tile = group.load(b[col0 : col0 + TILE_N, k0 : k0 + TILE_K], shape=(TILE_N, TILE_K))
-            acc = multiply_accumulate(group, a_tile, bt_tile, acc)
-        store_accumulators(group, c, row0, col0, acc)
-
-    tiled_wmma_matmul_bt.__name__ = f"tiled_wmma_matmul_bt_{np.dtype(element_type).name}"
-    return tiled_wmma_matmul_bt
-
-
 @functools.lru_cache(maxsize=None)
-def tiled_wmma_matmul_for(dtype_name, b_transposed=False):
+def tiled_wmma_matmul_for(dtype_name, b_transposed=False, member="plain"):
     """The kernel for "float16" or "bfloat16" (built once per process)."""
     if dtype_name == "bfloat16":
         import ml_dtypes
 
-        return build_tiled_wmma_matmul(ml_dtypes.bfloat16, b_transposed)
+        return build_tiled_wmma_matmul(ml_dtypes.bfloat16, b_transposed, member)
     if dtype_name == "float16":
-        return build_tiled_wmma_matmul(np.float16, b_transposed)
+        return build_tiled_wmma_matmul(np.float16, b_transposed, member)
     raise ValueError(f"unsupported element type {dtype_name!r}")
 
 
 @functools.lru_cache(maxsize=None)
-def compiled_for(dtype_name, device=None, b_transposed=False):
+def compiled_for(dtype_name, device=None, b_transposed=False, member="plain"):
     """`hc.compile(..., target="nvidia-sm100a")` of the kernel for one element type."""
-    return hc.compile(tiled_wmma_matmul_for(dtype_name, b_transposed), target=NVIDIA_TARGET, device=device)
+    return hc.compile(tiled_wmma_matmul_for(dtype_name, b_transposed, member), target=NVIDIA_TARGET,
+                      device=device)
 
 
 def gpu_wmma_matmul(a, b, *, device=None, b_transposed=False):

@@ -79,26 +79,32 @@ class CompiledKernel:
         a, b, c = (launch.arguments[p] for p in (plan.a_param, plan.b_param, plan.c_param))
         variant = {"auto": cuda.VARIANT_AUTO, "dense": cuda.VARIANT_DENSE, "skinny": cuda.VARIANT_SKINNY}[
             (plan.lowering or {}).get("variant", "auto")]
-        on_device = [type(x).__name__ == "DeviceBuffer" for x in (a, b, c)]
+        bias = launch.arguments[plan.bias_param] if plan.bias_param is not None else None
+        buffers = (a, b, c) if bias is None else (a, b, c, bias)
+        on_device = [type(x).__name__ == "DeviceBuffer" for x in buffers]
         if any(on_device) and not all(on_device):
             raise LaunchError("buffers must be all numpy.ndarray or all DeviceBuffer")
+        options = dict(variant=variant, b_transposed=plan.b_transposed, accumulate=plan.accumulate,
+                       epilogue=plan.epilogue)
         if all(on_device):
             ctx = a.ctx
-            if b.ctx is not ctx or c.ctx is not ctx:
+            if any(x.ctx is not ctx for x in buffers):
                 raise LaunchError("device buffers must belong to one context")
-            ctx.gemm(a, b, c, variant=variant, b_transposed=plan.b_transposed)
+            ctx.gemm(a, b, c, bias=bias, **options)
             ctx.synchronize()
             return
         ctx = cuda.default_context(self.device)
         a_host = _row_major(a)
         b_host = _row_major(b)
+        bias_host = None if bias is None else np.ascontiguousarray(bias)
         if _is_row_major(c) and c.flags.writeable:
-            ctx.gemm_host(a_host, b_host, c, variant=variant, b_transposed=plan.b_transposed)
+            ctx.gemm_host(a_host, b_host, c, bias=bias_host, **options)
             return
         if not c.flags.writeable:
             raise LaunchError(f"{plan.c_param} must be writeable")
-        staged = np.empty(c.shape, np.float32)
-        ctx.gemm_host(a_host, b_host, staged, variant=variant, b_transposed=plan.b_transposed)
+        # C's previous contents start the sums of an accumulating kernel.
+        staged = np.array(c, dtype=np.float32, order="C") if plan.accumulate else np.empty(c.shape, np.float32)
+        ctx.gemm_host(a_host, b_host, staged, bias=bias_host, **options)
         c[...] = staged
 
     # -- text ---------------------------------------------------------------------------

@@ -33,6 +33,8 @@ from pathlib import Path
 from types import FunctionType
 from typing import Any
 
+import numpy as np
+
 from ._intrinsic_contracts import serialize_intrinsic_type_spec
 
 __all__ = [
@@ -77,6 +79,13 @@ class GemmContract:
     # True when the kernel's b is Buffer[N, K] (B stored transposed) and its k-loop loads
     # b[cols, k0:k0+tk] windows, with the intrinsic's B tile shaped (tn, tk).
     b_transposed: bool = False
+    # True when the accumulators are loaded from `c` before the k-loop: C = C + A.B.
+    accumulate: bool = False
+    # Element-wise statements between the k-loop and the store, in order, as the launcher takes
+    # them: ("scale", x), ("add", x), ("max", x), ("min", x), ("bias",).
+    epilogue: tuple[tuple, ...] = ()
+    # The rank-1 `Buffer[N, float32]` parameter that ("bias",) adds per column, if any.
+    bias_param: str | None = None
 
 
 @dataclass(frozen=True)
@@ -302,11 +311,19 @@ def _names_in(node: ast.AST | None) -> set[str]:
     return {n.id for n in ast.walk(node) if isinstance(n, ast.Name)} if node is not None else set()
 
 
+_MAX_EPILOGUE_OPS = 4
+
+
 def _check_body(kernel_fn: Any, params: list[str], a: str, b: str, c: str, tile: tuple[int, int, int],
-                k_dim: Any, b_transposed: bool = False) -> list[str]:
+                k_dim: Any, b_transposed: bool = False, bias: str | None = None,
+                facts: dict[str, Any] | None = None) -> list[str]:
     """Structural check of the k-loop: `for k0 in range(0, K, tk)` with one masked load of an
     A window `a[rows, k0:k0+tk]` and one of a B window `b[k0:k0+tk, cols]`, then a store
-    that receives `c`. Returns problems (empty when the body has the expected shape)."""
+    that receives `c`. Returns problems (empty when the body has the expected shape).
+
+    `facts`, when given, receives what surrounds the loop: "accumulate" (the accumulators come
+    from a call that is given `c` before the loop) and "epilogue" (the element-wise statements on
+    the accumulators between the loop and the store)."""
     try:
         tree = ast.parse(textwrap.dedent(inspect.getsource(kernel_fn)))
     except (OSError, TypeError, SyntaxError):
@@ -367,7 +384,134 @@ def _check_body(kernel_fn: Any, params: list[str], a: str, b: str, c: str, tile:
             problems.append(f"axis {1 - axis} of the `{name}` window must not depend on the k-loop variable")
     if shape.c_uses_after_loop < 1:
         problems.append(f"`{c}` must be passed to a store after the k-loop")
+    surroundings = _loop_surroundings(fn_node, loop, c, bias, const_value, problems)
+    if facts is not None:
+        facts.update(surroundings)
     return problems
+
+
+def _number(node: ast.AST | None, const_value: Any) -> float | None:
+    """A numeric constant as the kernel spells it: a literal, a module-level or closure name,
+    `np.float32(<that>)`, or a negation of one. The statement runs in fp32, so the value is
+    rounded to fp32."""
+    if isinstance(node, ast.UnaryOp) and isinstance(node.op, (ast.USub, ast.UAdd)):
+        inner = _number(node.operand, const_value)
+        if inner is None:
+            return None
+        return -inner if isinstance(node.op, ast.USub) else inner
+    if isinstance(node, ast.Call) and len(node.args) == 1 and not node.keywords:
+        func = node.func
+        name = func.attr if isinstance(func, ast.Attribute) else (func.id if isinstance(func, ast.Name) else None)
+        if name in ("float32", "float64", "float16", "float"):
+            return _number(node.args[0], const_value)
+        return None
+    value = const_value(node)
+    if isinstance(value, bool) or not isinstance(value, (int, float, np.integer, np.floating)):
+        return None
+    value = float(np.float32(value))
+    return value if np.isfinite(value) else None
+
+
+def _loop_surroundings(fn_node: ast.AST, loop: ast.For, c: str, bias: str | None, const_value: Any,
+                       problems: list[str]) -> dict[str, Any]:
+    """Reads the top-level statements before and after the k-loop (see `_check_body`)."""
+    body = list(fn_node.body)
+    if loop not in body:
+        problems.append("the k-loop must be a top-level statement of the kernel body")
+        return {"accumulate": False, "epilogue": ()}
+    at = body.index(loop)
+
+    def call_names(node: ast.AST) -> set[str]:
+        return {arg.id for arg in getattr(node, "args", ()) if isinstance(arg, ast.Name)}
+
+    # The accumulator variable: assigned in the loop from a call that also receives it.
+    acc = None
+    for stmt in loop.body:
+        if (isinstance(stmt, ast.Assign) and len(stmt.targets) == 1 and isinstance(stmt.targets[0], ast.Name)
+                and isinstance(stmt.value, ast.Call) and stmt.targets[0].id in call_names(stmt.value)):
+            acc = stmt.targets[0].id
+    if acc is None:
+        problems.append("the k-loop must update the accumulators as `acc = f(..., acc)`")
+        return {"accumulate": False, "epilogue": ()}
+
+    accumulate = False
+    initialised = False
+    for stmt in body[:at]:
+        if (isinstance(stmt, ast.Assign) and len(stmt.targets) == 1 and isinstance(stmt.targets[0], ast.Name)
+                and stmt.targets[0].id == acc):
+            initialised = True
+            accumulate = isinstance(stmt.value, ast.Call) and c in call_names(stmt.value)
+        elif c in _names_in(stmt):
+            problems.append(f"`{c}` may only be read before the k-loop to initialise `{acc}`")
+    if not initialised:
+        problems.append(f"`{acc}` must be initialised before the k-loop")
+
+    ops: list[tuple] = []
+    stored = False
+    for stmt in body[at + 1:]:
+        text = ast.unparse(stmt)
+        if isinstance(stmt, ast.Expr) and isinstance(stmt.value, ast.Call) and c in call_names(stmt.value):
+            if acc not in call_names(stmt.value):
+                problems.append(f"the store `{text}` must receive `{acc}`")
+            stored = True
+            continue
+        if acc not in _names_in(stmt):
+            continue
+        if stored:
+            problems.append(f"`{text}` uses `{acc}` after the store")
+            continue
+        ok_target = (isinstance(stmt, ast.Assign) and len(stmt.targets) == 1
+                     and isinstance(stmt.targets[0], ast.Name) and stmt.targets[0].id == acc)
+        op = _elementwise_op(stmt.value, acc, bias, const_value) if ok_target else None
+        if op is None:
+            problems.append(
+                f"`{text}` is not an element-wise statement this target folds into the store "
+                f"(`{acc} = {acc} * x`, `+ x`, `- x`, `np.maximum({acc}, x)`, `np.minimum({acc}, x)` with a "
+                f"numeric constant x, `{acc} = f(..., bias, ..., {acc})`, `{acc}.astype(np.float32)`)")
+        elif op:
+            ops.append(op)
+    if len(ops) > _MAX_EPILOGUE_OPS:
+        problems.append(f"at most {_MAX_EPILOGUE_OPS} element-wise statements can be folded into the store, "
+                        f"found {len(ops)}")
+    bias_ops = sum(1 for op in ops if op[0] == "bias")
+    if bias is not None and bias_ops != 1:
+        problems.append(f"`{bias}` must be added to `{acc}` exactly once between the k-loop and the store")
+    return {"accumulate": accumulate, "epilogue": tuple(ops)}
+
+
+def _elementwise_op(value: ast.AST, acc: str, bias: str | None, const_value: Any) -> tuple | None:
+    """One statement `acc = <value>` as a fused operation; () for a no-op; None if unsupported."""
+    def is_acc(node: ast.AST) -> bool:
+        return isinstance(node, ast.Name) and node.id == acc
+
+    if isinstance(value, ast.BinOp):
+        left, right = value.left, value.right
+        if isinstance(value.op, (ast.Mult, ast.Add)) and (is_acc(left) or is_acc(right)):
+            x = _number(right if is_acc(left) else left, const_value)
+            if x is not None:
+                return ("scale" if isinstance(value.op, ast.Mult) else "add", x)
+        if isinstance(value.op, ast.Sub) and is_acc(left):
+            x = _number(right, const_value)
+            if x is not None:
+                return ("add", -x)
+        return None
+    if isinstance(value, ast.Call):
+        func = value.func
+        name = func.attr if isinstance(func, ast.Attribute) else (func.id if isinstance(func, ast.Name) else None)
+        if name in ("maximum", "minimum") and len(value.args) == 2 and not value.keywords:
+            first, second = value.args
+            if is_acc(first) or is_acc(second):
+                x = _number(second if is_acc(first) else first, const_value)
+                if x is not None:
+                    return ("max" if name == "maximum" else "min", x)
+            return None
+        if (name == "astype" and isinstance(func, ast.Attribute) and is_acc(func.value) and len(value.args) == 1
+                and ast.unparse(value.args[0]).split(".")[-1] == "float32"):
+            return ()
+        names = {arg.id for arg in value.args if isinstance(arg, ast.Name)}
+        if bias is not None and bias in names and acc in names:
+            return ("bias",)
+    return None
 
 
 @dataclass(frozen=True)
@@ -430,18 +574,26 @@ def recognise_tiled_matmul(kernel_fn: Any) -> tuple[GemmContract | None, list[st
         params = list(inspect.signature(kernel_fn).parameters)
     except (TypeError, ValueError):
         return None, [f"{name}: signature is not inspectable"]
-    if len(params) != 4:
-        return None, [f"{name}: expected (group, a, b, c) parameters, found {len(params)} parameters"]
+    if len(params) not in (4, 5):
+        return None, [f"{name}: expected (group, a, b, c) or (group, a, b, c, bias) parameters, "
+                      f"found {len(params)} parameters"]
     annotations = resolved_annotations(kernel_fn)
     specs = []
+    vectors = []
     for param in params[1:]:
         spec = annotations.get(param)
-        if type(spec).__name__ != "BufferSpec" or len(getattr(spec, "dimensions", ())) != 2:
-            return None, [f"{name}: parameter `{param}` must be annotated as a rank-2 Buffer"]
+        rank = len(getattr(spec, "dimensions", ()))
+        if type(spec).__name__ != "BufferSpec" or rank not in (1, 2):
+            return None, [f"{name}: parameter `{param}` must be annotated as a rank-2 Buffer"
+                          + (" (or the rank-1 bias)" if len(params) == 5 else "")]
         keys = tuple(_dim_key(d) for d in spec.dimensions)
         if None in keys:
             return None, [f"{name}: extents of `{param}` must be symbols or integers"]
-        specs.append((param, keys, spec.dtype))
+        (specs if rank == 2 else vectors).append((param, keys, spec.dtype))
+    if len(specs) != 3 or len(vectors) != len(params) - 4:
+        return None, [f"{name}: expected three rank-2 buffers (a, b, c)"
+                      + (" and one rank-1 bias" if len(params) == 5 else "")
+                      + f", found {len(specs)} rank-2 and {len(vectors)} rank-1"]
 
     # Operand roles from how the extents chain: a[M,K] b[K,N] c[M,N] in any parameter order.
     roles = None
@@ -465,6 +617,11 @@ def recognise_tiled_matmul(kernel_fn: Any) -> tuple[GemmContract | None, list[st
             f"{list(_SUPPORTED_INPUT_DTYPES)} and c[M,N] float32"
         ]
     a, b, c, m_dim, n_dim, k_dim, input_dtype = roles
+    bias = None
+    if vectors:
+        bias, (bias_dim,), bias_dtype = vectors[0]
+        if bias_dim != n_dim or bias_dtype != "float32":
+            return None, [f"{name}: `{bias}` must be Buffer[{n_dim}, float32], one value per column of `{c}`"]
 
     intrinsics = [fn for fn in _reachable_callables(kernel_fn) if hasattr(fn, "__hc_intrinsic__")]
     matches = []
@@ -485,7 +642,8 @@ def recognise_tiled_matmul(kernel_fn: Any) -> tuple[GemmContract | None, list[st
 
     wave, geometry_problems = _check_geometry(meta, {"m": m_dim, "n": n_dim, "k": k_dim}, tile, acc_len)
     problems.extend(geometry_problems)
-    problems.extend(_check_body(kernel_fn, params, a, b, c, tile, k_dim, b_transposed))
+    facts: dict[str, Any] = {}
+    problems.extend(_check_body(kernel_fn, params, a, b, c, tile, k_dim, b_transposed, bias, facts))
     if problems:
         return None, [f"{name}: {p}" for p in problems]
 
@@ -501,5 +659,8 @@ def recognise_tiled_matmul(kernel_fn: Any) -> tuple[GemmContract | None, list[st
         has_target_lowering=NVIDIA_SM100A in lowerings,
         lowering=lowering,
         b_transposed=b_transposed,
+        accumulate=bool(facts.get("accumulate", False)),
+        epilogue=tuple(facts.get("epilogue", ())),
+        bias_param=bias,
     )
     return contract, []

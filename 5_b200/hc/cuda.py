@@ -15,6 +15,7 @@ import ctypes
 import os
 import threading
 from pathlib import Path
+from collections.abc import Sequence
 from typing import Any
 
 import numpy as np
@@ -34,8 +35,13 @@ __all__ = [
 ]
 
 F16, BF16 = 0, 1
-VARIANT_AUTO, VARIANT_DENSE, VARIANT_SKINNY, VARIANT_NOOP, VARIANT_ZERO_FILL = 0, 1, 2, 3, 4
-VARIANT_NAMES = {0: "auto", 1: "dense", 2: "skinny", 3: "noop", 4: "zero_fill"}
+VARIANT_AUTO, VARIANT_DENSE, VARIANT_SKINNY, VARIANT_NOOP, VARIANT_ZERO_FILL, VARIANT_ELEMENTWISE = 0, 1, 2, 3, 4, 5
+VARIANT_NAMES = {0: "auto", 1: "dense", 2: "skinny", 3: "noop", 4: "zero_fill", 5: "elementwise"}
+API_VERSION = 3
+# Element-wise operations fused into the store of C: ("scale", x), ("add", x), ("max", x),
+# ("min", x) and ("bias",) -- the last adds bias[column].
+EPILOGUE_KINDS = {"scale": 1, "add": 2, "max": 3, "min": 4, "bias": 5}
+MAX_EPILOGUE_OPS = 4
 COMM_ID_BYTES = 128
 IPC_HANDLE_BYTES = 64
 MAX_PUSH_TARGETS = 7
@@ -59,7 +65,10 @@ class _GemmArgs(ctypes.Structure):
         ("a", ctypes.c_void_p), ("lda", ctypes.c_int64),
         ("b", ctypes.c_void_p), ("ldb", ctypes.c_int64),
         ("c", ctypes.c_void_p), ("ldc", ctypes.c_int64),
-        ("b_layout", ctypes.c_int32), ("reserved", ctypes.c_int32),
+        ("b_layout", ctypes.c_int32), ("accumulate", ctypes.c_int32),
+        ("epilogue_count", ctypes.c_int32), ("epilogue_kind", ctypes.c_int32 * 4),
+        ("epilogue_value", ctypes.c_float * 4), ("reserved", ctypes.c_int32),
+        ("bias", ctypes.c_void_p),
     ]
 
 
@@ -199,15 +208,29 @@ B_KN, B_NK = 0, 1  # B stored [k, n] (default) or transposed, [n, k]
 
 
 def _gemm_args(m: int, n: int, k: int, dtype: Any, a: int | None, lda: int, b: int | None, ldb: int,
-               c: int | None, ldc: int, variant: int, b_transposed: bool = False) -> _GemmArgs:
+               c: int | None, ldc: int, variant: int, b_transposed: bool = False, accumulate: bool = False,
+               epilogue: Sequence[tuple] = (), bias: int | None = None) -> _GemmArgs:
+    epilogue = tuple(epilogue)
+    if len(epilogue) > MAX_EPILOGUE_OPS:
+        raise ValueError(f"at most {MAX_EPILOGUE_OPS} fused element-wise operations are supported")
+    kinds = (ctypes.c_int32 * 4)()
+    values = (ctypes.c_float * 4)()
+    for i, op in enumerate(epilogue):
+        name = op[0]
+        if name not in EPILOGUE_KINDS:
+            raise ValueError(f"unknown fused operation {name!r}; expected one of {sorted(EPILOGUE_KINDS)}")
+        kinds[i] = EPILOGUE_KINDS[name]
+        values[i] = float(op[1]) if len(op) > 1 else 0.0
     return _GemmArgs(m, n, k, dtype_code(dtype), variant, a, lda, b, ldb, c, ldc,
-                     B_NK if b_transposed else B_KN, 0)
+                     B_NK if b_transposed else B_KN, 1 if accumulate else 0, len(epilogue), kinds, values, 0,
+                     bias)
 
 
 def plan_gemm(m: int, n: int, k: int, dtype: Any, *, a: int = 0x1000, lda: int | None = None,
               b: int = 0x40000000, ldb: int | None = None, c: int = 0x80000000,
               ldc: int | None = None, variant: int = VARIANT_AUTO, sm_count: int = 148,
-              b_transposed: bool = False) -> GemmPlan:
+              b_transposed: bool = False, accumulate: bool = False, epilogue: Sequence[tuple] = (),
+              bias: int | None = 0xC0000000) -> GemmPlan:
     """Validates a problem and returns its launch plan without touching a device.
 
     The pointer arguments are plain integers that are only inspected (null, alignment,
@@ -215,7 +238,7 @@ def plan_gemm(m: int, n: int, k: int, dtype: Any, *, a: int = 0x1000, lda: int |
     """
     args = _gemm_args(m, n, k, dtype, a, k if lda is None else lda, b,
                       (k if b_transposed else n) if ldb is None else ldb, c, n if ldc is None else ldc, variant,
-                      b_transposed)
+                      b_transposed, accumulate, epilogue, bias)
     info = _PlanInfo()
     status = library().hcCudaGemmPlan(ctypes.byref(args), sm_count, ctypes.byref(info))
     if status:
@@ -292,16 +315,24 @@ class Context:
     # -- the hot path -------------------------------------------------------------------
     def gemm(self, a: "DeviceBuffer", b: "DeviceBuffer", c: "DeviceBuffer", *,
              variant: int = VARIANT_AUTO, push: "list[DeviceBuffer] | None" = None,
-             b_transposed: bool = False) -> None:
+             b_transposed: bool = False, accumulate: bool = False, epilogue: Sequence[tuple] = (),
+             bias: "DeviceBuffer | None" = None) -> None:
         """Enqueues C = A @ B on device buffers (asynchronous; see `synchronize`).
 
         `b_transposed`: `b` holds B transposed, shape (n, k).
+        `accumulate`: C = C + A @ B (the previous contents of C start the sums).
+        `epilogue`: element-wise operations applied in order before the store, e.g.
+        `(("scale", 0.5), ("bias",), ("max", 0.0))`; `bias` is the float32 vector of n values
+        that ("bias",) adds to every row.
         `push`: up to 7 more buffers shaped and pitched like `c` (typically windows of peer
         GPUs' copies of C, see `ipc_open`) that receive every tile of C as well.
         """
         m, k = a.shape
         n = b.shape[0] if b_transposed else b.shape[1]
-        args = _gemm_args(m, n, k, a.dtype, a.ptr, a.ld, b.ptr, b.ld, c.ptr, c.ld, variant, b_transposed)
+        if bias is not None and (bias.dtype != np.float32 or bias.shape != (n,)):
+            raise ValueError("bias must be a float32 buffer of n values")
+        args = _gemm_args(m, n, k, a.dtype, a.ptr, a.ld, b.ptr, b.ld, c.ptr, c.ld, variant, b_transposed,
+                          accumulate, epilogue, None if bias is None else bias.ptr)
         if not push:
             self._check(self._lib.hcCudaGemm(self._handle, ctypes.byref(args)))
             return
@@ -330,16 +361,20 @@ class Context:
             self._check(self._lib.hcCudaIpcClose(self._handle, ptr))
 
     def gemm_host(self, a: np.ndarray, b: np.ndarray, c: np.ndarray, *,
-                  variant: int = VARIANT_AUTO, b_transposed: bool = False) -> None:
+                  variant: int = VARIANT_AUTO, b_transposed: bool = False, accumulate: bool = False,
+                  epilogue: Sequence[tuple] = (), bias: np.ndarray | None = None) -> None:
         """C = A @ B on host arrays: copies in, multiplies on the GPU, copies C back in place.
-        With `b_transposed`, `b` holds B transposed, shape (n, k)."""
+        With `b_transposed`, `b` holds B transposed, shape (n, k). `accumulate`, `epilogue` and
+        `bias` (a contiguous float32 host vector) as for `gemm`."""
         m, k = a.shape
         n = b.shape[0] if b_transposed else b.shape[1]
         b_rows, b_cols = b.shape
         args = _gemm_args(m, n, k, a.dtype, a.ctypes.data, a.strides[0] // a.itemsize if m > 1 else max(k, 1),
                           b.ctypes.data, b.strides[0] // b.itemsize if b_rows > 1 else max(b_cols, 1),
                           c.ctypes.data, c.strides[0] // c.itemsize if m > 1 else max(n, 1), variant,
-                          b_transposed)
+                          b_transposed, accumulate, epilogue, None if bias is None else bias.ctypes.data)
+        if bias is not None and (bias.dtype != np.float32 or bias.shape != (n,) or not bias.flags.c_contiguous):
+            raise ValueError("bias must be a contiguous float32 vector of n values")
         self._check(self._lib.hcCudaGemmHost(self._handle, ctypes.byref(args)))
 
     def selftest_device_timeout(self, budget_cycles: int = 2_000_000) -> None:

@@ -173,12 +173,32 @@ int plan_gemm(const HcCudaContext *ctx, const HcCudaGemmArgs *args, int sm_count
       args->variant != HC_CUDA_GEMM_SKINNY)
     return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "variant must be AUTO, DENSE or SKINNY (got %d)",
                 args->variant);
+  if (args->accumulate != 0 && args->accumulate != 1)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "accumulate must be 0 or 1 (got %d)", args->accumulate);
+  if (args->epilogue_count < 0 || args->epilogue_count > HC_CUDA_MAX_EPILOGUE_OPS)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "epilogue_count must be 0..%d (got %d)",
+                HC_CUDA_MAX_EPILOGUE_OPS, args->epilogue_count);
+  int bias_ops = 0;
+  for (int i = 0; i < args->epilogue_count; ++i) {
+    const int kind = args->epilogue_kind[i];
+    if (kind < HC_CUDA_EPILOGUE_SCALE || kind > HC_CUDA_EPILOGUE_BIAS_COLUMN)
+      return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "epilogue_kind[%d] is not an HcCudaEpilogueOp (got %d)", i, kind);
+    bias_ops += kind == HC_CUDA_EPILOGUE_BIAS_COLUMN ? 1 : 0;
+  }
+  if (bias_ops > 1)
+    return fail(ctx, HC_CUDA_ERR_UNSUPPORTED, "at most one HC_CUDA_EPILOGUE_BIAS_COLUMN operation is supported");
+  if (args->reserved != 0)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "reserved must be 0");
   if (sm_count <= 0)
     sm_count = kDefaultSmCount;
 
   if (m == 0 || n == 0) {
     plan->variant = HC_CUDA_GEMM_NOOP;
     return HC_CUDA_OK;
+  }
+  if (bias_ops != 0) {
+    if (args->bias == nullptr || (reinterpret_cast<uintptr_t>(args->bias) & 3) != 0)
+      return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "bias must be a 4-byte-aligned pointer to n floats");
   }
   if (args->c == nullptr)
     return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "c must not be null");
@@ -187,8 +207,17 @@ int plan_gemm(const HcCudaContext *ctx, const HcCudaGemmArgs *args, int sm_count
                 (long long)args->ldc, (long long)n);
   if ((reinterpret_cast<uintptr_t>(args->c) & 3) != 0)
     return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "c must be 4-byte aligned");
+  const size_t c_bytes = (static_cast<size_t>(m - 1) * args->ldc + n) * 4;
+  if (bias_ops != 0 && ranges_overlap(args->c, c_bytes, args->bias, static_cast<size_t>(n) * 4))
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "c must not overlap bias");
   if (k == 0) {
-    plan->variant = HC_CUDA_GEMM_ZERO_FILL;
+    // No product to add: C becomes zero, stays as it is, or only receives the element-wise work.
+    if (args->epilogue_count != 0) {
+      plan->variant = HC_CUDA_GEMM_ELEMENTWISE;
+      plan->kernel_launches = 1;
+    } else {
+      plan->variant = args->accumulate ? HC_CUDA_GEMM_NOOP : HC_CUDA_GEMM_ZERO_FILL;
+    }
     return HC_CUDA_OK;
   }
   if (args->a == nullptr || args->b == nullptr)
@@ -199,8 +228,6 @@ int plan_gemm(const HcCudaContext *ctx, const HcCudaGemmArgs *args, int sm_count
   if (args->b_layout != HC_CUDA_B_KN && args->b_layout != HC_CUDA_B_NK)
     return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "b_layout must be HC_CUDA_B_KN or HC_CUDA_B_NK (got %d)",
                 args->b_layout);
-  if (args->reserved != 0)
-    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "reserved must be 0");
   const bool b_nk = args->b_layout == HC_CUDA_B_NK;
   const int64_t b_rows = b_nk ? n : k, b_cols = b_nk ? k : n;  // as stored
   if (args->ldb < b_cols || args->ldb > kMaxPitch)
@@ -210,7 +237,6 @@ int plan_gemm(const HcCudaContext *ctx, const HcCudaGemmArgs *args, int sm_count
     return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "a and b must be 2-byte aligned");
   const size_t a_bytes = (static_cast<size_t>(m - 1) * args->lda + k) * 2;
   const size_t b_bytes = (static_cast<size_t>(b_rows - 1) * args->ldb + b_cols) * 2;
-  const size_t c_bytes = (static_cast<size_t>(m - 1) * args->ldc + n) * 4;
   if (ranges_overlap(args->c, c_bytes, args->a, a_bytes) ||
       ranges_overlap(args->c, c_bytes, args->b, b_bytes))
     return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "c must not overlap a or b");
@@ -340,10 +366,22 @@ int encode_map(HcCudaContext *ctx, CUtensorMap *map, int dtype, const void *base
 // Enqueues the GEMM on device-resident buffers. The caller holds ctx->mu and has made the
 // context's device current.
 int enqueue_gemm(HcCudaContext *ctx, const HcCudaGemmArgs *args, const HcCudaGemmPlanInfo &plan,
-                 const hc::sm100::PushTargets &push = hc::sm100::PushTargets{}) {
+                 const hc::sm100::Epilogue &push = hc::sm100::Epilogue{}) {
   if (plan.variant == HC_CUDA_GEMM_NOOP)
     return HC_CUDA_OK;
   const int m = static_cast<int>(args->m), n = static_cast<int>(args->n), k = static_cast<int>(args->k);
+  hc::sm100::Epilogue ep = push;  // the push targets, if any; the fused work comes from args
+  ep.accumulate = args->accumulate;
+  ep.op_count = args->epilogue_count;
+  for (int i = 0; i < args->epilogue_count; ++i) {
+    ep.op_kind[i] = args->epilogue_kind[i];
+    ep.op_value[i] = args->epilogue_value[i];
+  }
+  ep.bias = args->bias;
+  if (plan.variant == HC_CUDA_GEMM_ELEMENTWISE) {
+    HC_TRY_CUDA(ctx, hc::sm100::launch_epilogue_only(args->c, m, n, args->ldc, ep, ctx->stream));
+    return HC_CUDA_OK;
+  }
   if (plan.variant == HC_CUDA_GEMM_ZERO_FILL) {
     HC_TRY_CUDA(ctx, cudaMemset2DAsync(args->c, static_cast<size_t>(args->ldc) * 4, 0,
                                        static_cast<size_t>(n) * 4, static_cast<size_t>(m), ctx->stream));
@@ -405,11 +443,11 @@ int enqueue_gemm(HcCudaContext *ctx, const HcCudaGemmArgs *args, const HcCudaGem
       return rc;
     if (pairs) {
       HC_TRY_CUDA(ctx, hc::sm100::launch_gemm_dense_pair(tmap_a, tmap_b, args->c, m, n, k, args->ldc,
-                                                         args->dtype, ctx->group_n, plan.grid, b_layout, push,
+                                                         args->dtype, ctx->group_n, plan.grid, b_layout, ep,
                                                          ctx->status_dev, ctx->stream));
     } else {
       HC_TRY_CUDA(ctx, hc::sm100::launch_gemm_dense(tmap_a, tmap_b, args->c, m, n, k, args->ldc,
-                                                    args->dtype, ctx->group_n, plan.grid, b_layout, push,
+                                                    args->dtype, ctx->group_n, plan.grid, b_layout, ep,
                                                     ctx->status_dev, ctx->stream));
     }
     return HC_CUDA_OK;
@@ -433,7 +471,7 @@ int enqueue_gemm(HcCudaContext *ctx, const HcCudaGemmArgs *args, const HcCudaGem
   }
   HC_TRY_CUDA(ctx, hc::sm100::launch_gemm_skinny(tmap_a, tmap_b, args->c, m, n, k, args->ldc,
                                                  args->dtype, plan.splits, partials, ctx->counters,
-                                                 plan.grid, b_layout, ctx->status_dev, ctx->stream));
+                                                 plan.grid, b_layout, ep, ctx->status_dev, ctx->stream));
   return HC_CUDA_OK;
 }
 
@@ -776,7 +814,7 @@ int hcCudaGemmPush(HcCudaContext *ctx, const HcCudaGemmArgs *args, float *const 
   HcCudaGemmPlanInfo plan;
   if (int rc = plan_gemm(ctx, &dense, ctx->prop.multiProcessorCount, false, &plan))
     return rc;
-  hc::sm100::PushTargets push{};
+  hc::sm100::Epilogue push{};
   if (plan.variant == HC_CUDA_GEMM_DENSE && n_targets > 0) {
     if ((dense.ldc & 3) != 0 || (reinterpret_cast<uintptr_t>(dense.c) & 15) != 0)
       return fail(ctx, HC_CUDA_ERR_UNSUPPORTED, "pushing needs c 16-byte aligned and ldc a multiple of 4");
@@ -786,10 +824,10 @@ int hcCudaGemmPush(HcCudaContext *ctx, const HcCudaGemmArgs *args, float *const 
         return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "push target %d must be a 16-byte-aligned device pointer", i);
       if (ranges_overlap(targets[i], c_bytes, dense.c, c_bytes))
         return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "push target %d overlaps c", i);
-      push.c[i] = targets[i];
+      push.push[i] = targets[i];
     }
-    push.count = n_targets;
-  } else if (n_targets > 0 && plan.variant == HC_CUDA_GEMM_ZERO_FILL) {
+    push.push_count = n_targets;
+  } else if (n_targets > 0 && dense.k == 0 && dense.m > 0 && dense.n > 0) {
     return fail(ctx, HC_CUDA_ERR_UNSUPPORTED, "k == 0 with push targets is not supported");
   }
   HC_TRY_CUDA(ctx, cudaSetDevice(ctx->device));
@@ -856,6 +894,9 @@ int hcCudaGemmHost(HcCudaContext *ctx, const HcCudaGemmArgs *args) {
     return HC_CUDA_OK;
   }
   HC_TRY_CUDA(ctx, cudaSetDevice(ctx->device));
+  bool has_bias = false;
+  for (int i = 0; i < args->epilogue_count; ++i)
+    has_bias = has_bias || args->epilogue_kind[i] == HC_CUDA_EPILOGUE_BIAS_COLUMN;
   // Device copies get pitches that satisfy TMA (16 bytes), so no repack pass is needed.
   const size_t lda = static_cast<size_t>(round_up(args->k, kRepackPitchElems));
   const bool b_nk = args->b_layout == HC_CUDA_B_NK;
@@ -866,9 +907,15 @@ int hcCudaGemmHost(HcCudaContext *ctx, const HcCudaGemmArgs *args) {
     return rc;
   if (int rc = ensure_stage(ctx, 1, b_rows * ldb * 2))
     return rc;
-  if (int rc = ensure_stage(ctx, 2, m * ldc * 4))
+  // C's staging buffer also holds the bias vector, after the last row.
+  if (int rc = ensure_stage(ctx, 2, m * ldc * 4 + (has_bias ? n * 4 : 0)))
     return rc;
   HcCudaGemmArgs dev = *args;
+  float *bias_dev = reinterpret_cast<float *>(static_cast<char *>(ctx->stage[2]) + m * ldc * 4);
+  if (has_bias) {
+    dev.bias = bias_dev;
+    HC_TRY_CUDA(ctx, cudaMemcpyAsync(bias_dev, args->bias, n * 4, cudaMemcpyHostToDevice, ctx->stream));
+  }
   dev.a = ctx->stage[0];
   dev.lda = static_cast<int64_t>(lda);
   dev.b = ctx->stage[1];
@@ -877,6 +924,18 @@ int hcCudaGemmHost(HcCudaContext *ctx, const HcCudaGemmArgs *args) {
   dev.ldc = static_cast<int64_t>(ldc);
 
   const size_t total_bytes = (m * k + k * n) * 2 + m * n * 4;
+  if (plan.variant == HC_CUDA_GEMM_ELEMENTWISE) {
+    if (args->accumulate)
+      HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(ctx->stage[2], ldc * 4, args->c, static_cast<size_t>(args->ldc) * 4,
+                                         n * 4, m, cudaMemcpyHostToDevice, ctx->stream));
+    if (int rc = plan_gemm(ctx, &dev, ctx->prop.multiProcessorCount, false, &plan))
+      return rc;
+    if (int rc = enqueue_gemm(ctx, &dev, plan))
+      return rc;
+    HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(args->c, static_cast<size_t>(args->ldc) * 4, ctx->stage[2], ldc * 4,
+                                       n * 4, m, cudaMemcpyDeviceToHost, ctx->stream));
+    return synchronize_locked(ctx);
+  }
   const bool pipelined = plan.variant == HC_CUDA_GEMM_DENSE && m >= 1024 && total_bytes >= (size_t(32) << 20) &&
                          std::getenv("HC_CUDA_NO_COPY_OVERLAP") == nullptr;
   if (!pipelined) {
@@ -884,6 +943,9 @@ int hcCudaGemmHost(HcCudaContext *ctx, const HcCudaGemmArgs *args) {
                                        k * 2, m, cudaMemcpyHostToDevice, ctx->stream));
     HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(ctx->stage[1], ldb * 2, args->b, static_cast<size_t>(args->ldb) * 2,
                                        b_cols * 2, b_rows, cudaMemcpyHostToDevice, ctx->stream));
+    if (args->accumulate)
+      HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(ctx->stage[2], ldc * 4, args->c, static_cast<size_t>(args->ldc) * 4,
+                                         n * 4, m, cudaMemcpyHostToDevice, ctx->stream));
     if (int rc = plan_gemm(ctx, &dev, ctx->prop.multiProcessorCount, false, &plan))
       return rc;
     if (int rc = enqueue_gemm(ctx, &dev, plan))
@@ -914,6 +976,11 @@ int hcCudaGemmHost(HcCudaContext *ctx, const HcCudaGemmArgs *args) {
     char *a_dst = static_cast<char *>(ctx->stage[0]) + row0 * lda * 2;
     HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(a_dst, lda * 2, a_src, static_cast<size_t>(args->lda) * 2, k * 2, rows,
                                        cudaMemcpyHostToDevice, ctx->copy_in));
+    if (args->accumulate)  // this panel's rows of C are the starting values of its sums
+      HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(static_cast<float *>(ctx->stage[2]) + row0 * ldc, ldc * 4,
+                                         args->c + row0 * static_cast<size_t>(args->ldc),
+                                         static_cast<size_t>(args->ldc) * 4, n * 4, rows,
+                                         cudaMemcpyHostToDevice, ctx->copy_in));
     HC_TRY_CUDA(ctx, cudaEventRecord(ctx->panel_in[p], ctx->copy_in));
     HC_TRY_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->panel_in[p], 0));
     HcCudaGemmArgs part = dev;

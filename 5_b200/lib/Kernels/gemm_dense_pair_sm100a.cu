@@ -81,7 +81,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
 gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                        const __grid_constant__ CUtensorMap tmap_b, float *__restrict__ c, int m, int n,
                        int k, long long ldc, uint32_t idesc, int tiles_m, int tiles_n, int group_n,
-                       int l2_hints, int b_layout, PushTargets push, int *status) {
+                       int l2_hints, int b_layout, Epilogue ep, int *status) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t smem_base = (raw_addr + 1023u) & ~1023u;
@@ -246,7 +246,7 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int col_base = tc.n_blk * kTileN;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kTileN;
       drain_accumulator_rows<kTileN>(taddr, stage_gen, c, ldc, m, n, row_base, col_base, vec_ok, lane,
-                                     map_to_cta(tmem_empty_bar(acc), 0), /*release_remote=*/true, push);
+                                     map_to_cta(tmem_empty_bar(acc), 0), /*release_remote=*/true, ep);
     }
   }
 
@@ -271,7 +271,7 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
 cudaError_t launch_gemm_dense_pair(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, float *c,
                                    int m, int n, int k, long long ldc, int dtype, int group_n,
-                                   int max_ctas, int b_layout, const PushTargets &push, int *status,
+                                   int max_ctas, int b_layout, const Epilogue &ep, int *status,
                                    cudaStream_t stream) {
   using namespace dense_pair;
   static thread_local int configured_device = -1;
@@ -304,7 +304,7 @@ cudaError_t launch_gemm_dense_pair(const CUtensorMap &tmap_a, const CUtensorMap 
   if (const char *h = std::getenv("HC_CUDA_L2_HINTS"))  // tuning aid
     l2_hints = std::atoi(h);
   gemm_dense_pair_kernel<<<static_cast<unsigned>(clusters * 2), kNumThreads, kSmemBytes, stream>>>(
-      tmap_a, tmap_b, c, m, n, k, ldc, idesc, tiles_m, tiles_n, group_n, l2_hints, b_layout, push, status);
+      tmap_a, tmap_b, c, m, n, k, ldc, idesc, tiles_m, tiles_n, group_n, l2_hints, b_layout, ep, status);
   return cudaGetLastError();
 }
 

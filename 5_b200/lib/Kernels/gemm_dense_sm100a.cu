@@ -70,7 +70,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_dense_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   const __grid_constant__ CUtensorMap tmap_b, float *__restrict__ c, int m, int n,
                   int k, long long ldc, uint32_t idesc, int tiles_m, int tiles_n, int group_n,
-                  int b_layout, PushTargets push, int *status) {
+                  int b_layout, Epilogue ep, int *status) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t smem_base = (raw_addr + 1023u) & ~1023u;  // swizzled tiles need 1 KiB alignment
@@ -214,7 +214,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int col_base = tc.n_blk * kBlockN;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kBlockN;
       drain_accumulator_rows<kBlockN>(taddr, stage_gen, c, ldc, m, n, row_base, col_base, vec_ok, lane,
-                                      tmem_empty_bar(acc), /*release_remote=*/false, push);
+                                      tmem_empty_bar(acc), /*release_remote=*/false, ep);
     }
   }
 
@@ -239,7 +239,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
 cudaError_t launch_gemm_dense(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, float *c,
                               int m, int n, int k, long long ldc, int dtype, int group_n,
-                              int max_ctas, int b_layout, const PushTargets &push, int *status,
+                              int max_ctas, int b_layout, const Epilogue &ep, int *status,
                               cudaStream_t stream) {
   using namespace dense;
   static thread_local int configured_device = -1;
@@ -266,7 +266,7 @@ cudaError_t launch_gemm_dense(const CUtensorMap &tmap_a, const CUtensorMap &tmap
     group_n = 1;
   gemm_dense_kernel<<<grid, kNumThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, c, m, n, k, ldc,
                                                                idesc, tiles_m, tiles_n, group_n,
-                                                               b_layout, push, status);
+                                                               b_layout, ep, status);
   return cudaGetLastError();
 }
 

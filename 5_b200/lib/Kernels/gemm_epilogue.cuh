@@ -16,7 +16,56 @@
 namespace hc {
 namespace sm100 {
 
-// Writes one 32-column chunk (already in registers, lane = row) of this warp's 32 rows to C.
+// The fused element-wise work on one value that is about to be stored at `dst` (column `col`).
+__device__ __forceinline__ float finish_value(float v, const float *dst, int col, const Epilogue &ep) {
+  if (ep.accumulate)
+    v += __ldcs(dst);
+#pragma unroll
+  for (int i = 0; i < kMaxEpilogueOps; ++i) {
+    if (i < ep.op_count) {
+      const int kind = ep.op_kind[i];
+      const float x = kind == kEpilogueBiasColumn ? __ldg(ep.bias + col) : ep.op_value[i];
+      v = kind == kEpilogueScale ? v * x
+        : kind == kEpilogueMax   ? fmaxf(v, x)
+        : kind == kEpilogueMin   ? fminf(v, x)
+                                 : v + x;
+    }
+  }
+  return v;
+}
+
+// Four consecutive values of one row, all inside C, `dst` 16-byte aligned.
+__device__ __forceinline__ float4 finish_group(float4 v, const float *dst, int col, const Epilogue &ep) {
+  if (ep.accumulate) {
+    const float4 old = __ldcs(reinterpret_cast<const float4 *>(dst));
+    v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
+  }
+#pragma unroll
+  for (int i = 0; i < kMaxEpilogueOps; ++i) {
+    if (i < ep.op_count) {
+      const int kind = ep.op_kind[i];
+      float4 x;
+      if (kind == kEpilogueBiasColumn) {
+        x = make_float4(__ldg(ep.bias + col), __ldg(ep.bias + col + 1), __ldg(ep.bias + col + 2),
+                        __ldg(ep.bias + col + 3));
+      } else {
+        const float s = ep.op_value[i];
+        x = make_float4(s, s, s, s);
+      }
+      if (kind == kEpilogueScale) {
+        v.x *= x.x; v.y *= x.y; v.z *= x.z; v.w *= x.w;
+      } else if (kind == kEpilogueMax) {
+        v.x = fmaxf(v.x, x.x); v.y = fmaxf(v.y, x.y); v.z = fmaxf(v.z, x.z); v.w = fmaxf(v.w, x.w);
+      } else if (kind == kEpilogueMin) {
+        v.x = fminf(v.x, x.x); v.y = fminf(v.y, x.y); v.z = fminf(v.z, x.z); v.w = fminf(v.w, x.w);
+      } else {
+        v.x += x.x; v.y += x.y; v.z += x.z; v.w += x.w;
+      }
+    }
+  }
+  return v;
+}
+
 // Stages this lane's 32 values with the row rotated left by kShift elements, so that the
 // 16-byte groups of the row *in memory* (which start kShift elements into the chunk) land on
 // 16-byte pieces of the staging block.
@@ -36,11 +85,12 @@ __device__ __forceinline__ void stage_row_shifted(const uint32_t (&r)[32], float
 __device__ __forceinline__ void write_chunk(const uint32_t (&r)[32], int chunk, bool last_chunk, float *buf,
                                             float *__restrict__ c, long long ldc, int m, int n,
                                             int row_base, int col_base, bool vec_ok, int lane,
-                                            float (&carry)[3], const PushTargets &push) {
+                                            float (&carry)[3], const Epilogue &ep) {
   const int col0 = col_base + chunk * 32;
   if (col0 >= n)
     return;  // warp-uniform
   const int piece = lane & 7;
+  const bool fused = ep.accumulate != 0 || ep.op_count != 0;  // grid-uniform
   if (vec_ok) {
     stage_row_shifted<0>(r, buf, lane);
     __syncwarp();
@@ -49,18 +99,25 @@ __device__ __forceinline__ void write_chunk(const uint32_t (&r)[32], int chunk, 
     for (int i = 0; i < 8; ++i) {
       const int rr = i * 4 + (lane >> 3);
       const int row = row_base + rr;
-      const float4 v = *reinterpret_cast<const float4 *>(buf + rr * 32 + ((piece ^ (rr & 7)) << 2));
+      float4 v = *reinterpret_cast<const float4 *>(buf + rr * 32 + ((piece ^ (rr & 7)) << 2));
       if (row < m) {
         const long long offset = static_cast<long long>(row) * ldc + col;
         float *dst = c + offset;
         if (col + 3 < n) {
+          if (fused)
+            v = finish_group(v, dst, col, ep);
           __stcs(reinterpret_cast<float4 *>(dst), v);
           // The same 128-byte row segments go to every push target (peer GPUs' copies of C).
-          for (int t = 0; t < push.count; ++t)
-            __stcs(reinterpret_cast<float4 *>(push.c[t] + offset), v);
+          for (int t = 0; t < ep.push_count; ++t)
+            __stcs(reinterpret_cast<float4 *>(ep.push[t] + offset), v);
         } else {
-          for (int t = -1; t < push.count; ++t) {
-            float *edge = t < 0 ? dst : push.c[t] + offset;
+          if (fused) {
+            if (col < n) v.x = finish_value(v.x, dst, col, ep);
+            if (col + 1 < n) v.y = finish_value(v.y, dst + 1, col + 1, ep);
+            if (col + 2 < n) v.z = finish_value(v.z, dst + 2, col + 2, ep);
+          }
+          for (int t = -1; t < ep.push_count; ++t) {
+            float *edge = t < 0 ? dst : ep.push[t] + offset;
             if (col < n) __stcs(edge, v.x);
             if (col + 1 < n) __stcs(edge + 1, v.y);
             if (col + 2 < n) __stcs(edge + 2, v.z);
@@ -84,6 +141,12 @@ __device__ __forceinline__ void write_chunk(const uint32_t (&r)[32], int chunk, 
       return static_cast<int>((4u - ((phase0 + static_cast<unsigned>(rr) * phase_step) & 3u)) & 3u);
     };
     float *tile_dst = c + static_cast<long long>(row_base) * ldc + col0;
+    auto store_value = [&](float *dst, float v, int col) {
+      __stcs(dst, fused ? finish_value(v, dst, col, ep) : v);
+    };
+    auto store_group = [&](float *dst, float4 v, int col) {
+      __stcs(reinterpret_cast<float4 *>(dst), fused ? finish_group(v, dst, col, ep) : v);
+    };
     {
       const int shift = shift_of(lane);
       float *dst = tile_dst + static_cast<long long>(lane) * ldc;
@@ -100,9 +163,9 @@ __device__ __forceinline__ void write_chunk(const uint32_t (&r)[32], int chunk, 
         const float f0 = __uint_as_float(r[0]), f1 = __uint_as_float(r[1]), f2 = __uint_as_float(r[2]);
         if (chunk == 0) {
           // Elements before the first aligned group of the tile row.
-          if (col0 < n) __stcs(dst, f0);
-          if (shift >= 2 && col0 + 1 < n) __stcs(dst + 1, f1);
-          if (shift == 3 && col0 + 2 < n) __stcs(dst + 2, f2);
+          if (col0 < n) store_value(dst, f0, col0);
+          if (shift >= 2 && col0 + 1 < n) store_value(dst + 1, f1, col0 + 1);
+          if (shift == 3 && col0 + 2 < n) store_value(dst + 2, f2, col0 + 2);
         } else {
           // The group that straddles the previous chunk and this one: its first 4 - shift
           // elements were kept from the previous chunk in `carry`.
@@ -110,20 +173,21 @@ __device__ __forceinline__ void write_chunk(const uint32_t (&r)[32], int chunk, 
                          : shift == 2 ? make_float4(carry[1], carry[2], f0, f1)
                                       : make_float4(carry[2], f0, f1, f2);
           float *group = dst + shift - 4;
-          if (col0 + shift - 1 < n) {
-            __stcs(reinterpret_cast<float4 *>(group), v);
+          const int group_col = col0 + shift - 4;
+          if (group_col + 3 < n) {
+            store_group(group, v, group_col);
           } else {
             // Only the elements left of column n exist (the previous chunk's are always inside).
-            __stcs(group, v.x);
-            if (col0 + shift - 3 < n) __stcs(group + 1, v.y);
-            if (col0 + shift - 2 < n) __stcs(group + 2, v.z);
+            store_value(group, v.x, group_col);
+            if (group_col + 1 < n) store_value(group + 1, v.y, group_col + 1);
+            if (group_col + 2 < n) store_value(group + 2, v.z, group_col + 2);
           }
         }
         if (last_chunk || col0 + 32 >= n) {
           // No next chunk will complete the trailing group: write its elements singly.
           for (int e = 28 + shift; e < 32; ++e)
             if (col0 + e < n)
-              __stcs(dst + e, __uint_as_float(e == 29 ? r[29] : (e == 30 ? r[30] : r[31])));
+              store_value(dst + e, __uint_as_float(e == 29 ? r[29] : (e == 30 ? r[30] : r[31])), col0 + e);
         }
       }
       carry[0] = __uint_as_float(r[29]);
@@ -140,11 +204,11 @@ __device__ __forceinline__ void write_chunk(const uint32_t (&r)[32], int chunk, 
       if (row_base + rr < m && e0 + 3 < 32) {
         float *dst = tile_dst + static_cast<long long>(rr) * ldc + e0;
         if (col0 + e0 + 3 < n) {
-          __stcs(reinterpret_cast<float4 *>(dst), v);
+          store_group(dst, v, col0 + e0);
         } else {
-          if (col0 + e0 < n) __stcs(dst, v.x);
-          if (col0 + e0 + 1 < n) __stcs(dst + 1, v.y);
-          if (col0 + e0 + 2 < n) __stcs(dst + 2, v.z);
+          if (col0 + e0 < n) store_value(dst, v.x, col0 + e0);
+          if (col0 + e0 + 1 < n) store_value(dst + 1, v.y, col0 + e0 + 1);
+          if (col0 + e0 + 2 < n) store_value(dst + 2, v.z, col0 + e0 + 2);
         }
       }
     }
@@ -162,7 +226,7 @@ __device__ __forceinline__ void drain_accumulator_rows(uint32_t taddr, float *st
                                                        long long ldc, int m, int n, int row_base,
                                                        int col_base, bool vec_ok, int lane,
                                                        uint32_t release_bar, bool release_remote,
-                                                       const PushTargets &push) {
+                                                       const Epilogue &ep) {
   constexpr int kChunks = kColumns / 32;
   static_assert(kChunks % 2 == 0, "chunks are processed in pairs");
   uint32_t ra[32], rb[32];
@@ -172,7 +236,7 @@ __device__ __forceinline__ void drain_accumulator_rows(uint32_t taddr, float *st
   for (int chunk = 0; chunk < kChunks; chunk += 2) {
     tmem_load_wait_for(ra);
     tmem_load_32x32b_x32(taddr + (chunk + 1) * 32, rb);
-    write_chunk(ra, chunk, false, stage, c, ldc, m, n, row_base, col_base, vec_ok, lane, carry, push);
+    write_chunk(ra, chunk, false, stage, c, ldc, m, n, row_base, col_base, vec_ok, lane, carry, ep);
     tmem_load_wait_for(rb);
     if (chunk + 2 < kChunks) {
       tmem_load_32x32b_x32(taddr + (chunk + 2) * 32, ra);
@@ -187,7 +251,7 @@ __device__ __forceinline__ void drain_accumulator_rows(uint32_t taddr, float *st
           mbar_arrive(release_bar);
       }
     }
-    write_chunk(rb, chunk + 1, chunk + 2 >= kChunks, stage, c, ldc, m, n, row_base, col_base, vec_ok, lane, carry, push);
+    write_chunk(rb, chunk + 1, chunk + 2 >= kChunks, stage, c, ldc, m, n, row_base, col_base, vec_ok, lane, carry, ep);
   }
 }
 

@@ -27,9 +27,26 @@ constexpr int kStatusDeviceWaitTimeout = 5;
 // column slab of C straight into its peers' memory over NVLink while later tiles are still being
 // computed (plain peer stores; nothing is ever loaded from a peer).
 constexpr int kMaxPushTargets = 7;
-struct PushTargets {
-  float *c[kMaxPushTargets];
-  int count;
+
+// Element-wise work fused into the store of C. With `accumulate` the previous contents of C are
+// the starting value of the sum (the hc kernel that loads its accumulators from `c` before the
+// k-loop); `ops` then run in order on every element, mirroring the element-wise statements an
+// hc kernel applies to its accumulators between the k-loop and the store. The value that
+// reaches C is also what goes to the push targets.
+constexpr int kMaxEpilogueOps = 4;
+constexpr int kEpilogueScale = 1;       // v = v * value
+constexpr int kEpilogueAdd = 2;         // v = v + value
+constexpr int kEpilogueMax = 3;         // v = max(v, value)
+constexpr int kEpilogueMin = 4;         // v = min(v, value)
+constexpr int kEpilogueBiasColumn = 5;  // v = v + bias[column]
+struct Epilogue {
+  float *push[kMaxPushTargets];
+  int push_count;
+  int accumulate;
+  int op_count;
+  int op_kind[kMaxEpilogueOps];
+  float op_value[kMaxEpilogueOps];
+  const float *bias;
 };
 
 struct DenseTileShape {
@@ -43,7 +60,7 @@ DenseTileShape dense_tile_shape();
 //   tmap_b: B as a 2-D tensor {n (inner), k}, box {64, 64},  128-byte swizzle.
 cudaError_t launch_gemm_dense(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, float *c,
                               int m, int n, int k, long long ldc, int dtype, int group_n,
-                              int max_ctas, int b_layout, const PushTargets &push, int *status,
+                              int max_ctas, int b_layout, const Epilogue &ep, int *status,
                               cudaStream_t stream);
 
 // Same product on CTA pairs: clusters of two CTAs own 256x256 tiles and issue
@@ -51,7 +68,7 @@ cudaError_t launch_gemm_dense(const CUtensorMap &tmap_a, const CUtensorMap &tmap
 // rounded down to an even number of CTAs.
 cudaError_t launch_gemm_dense_pair(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, float *c,
                                    int m, int n, int k, long long ldc, int dtype, int group_n,
-                                   int max_ctas, int b_layout, const PushTargets &push, int *status,
+                                   int max_ctas, int b_layout, const Epilogue &ep, int *status,
                                    cudaStream_t stream);
 
 // Whether the dense variant runs on CTA pairs for this problem.
@@ -81,7 +98,11 @@ size_t skinny_counters_bytes(int n);
 cudaError_t launch_gemm_skinny(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, float *c,
                                int m, int n, int k, long long ldc, int dtype, int splits,
                                float *partials, unsigned *counters, int max_ctas, int b_layout,
-                               int *status, cudaStream_t stream);
+                               const Epilogue &ep, int *status, cudaStream_t stream);
+
+// k == 0 with fused element-wise work: C = ops(accumulate ? C : 0), no product to add.
+cudaError_t launch_epilogue_only(float *c, int m, int n, long long ldc, const Epilogue &ep,
+                                 cudaStream_t stream);
 
 // Copies a rows x cols matrix of 16-bit elements into a buffer whose row pitch is a
 // multiple of 8 elements (16 bytes), as TMA requires. Columns [cols, round_up(cols, 8))

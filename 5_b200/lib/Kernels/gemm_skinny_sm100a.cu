@@ -18,6 +18,7 @@
 //
 // Warp roles: warp 0 TMA producer, warp 1 TMEM owner + tcgen05.mma issuer, warps 2-5
 // epilogue (TMEM -> registers -> partials / C).
+#include "gemm_epilogue.cuh"
 #include "gemm_launch.h"
 #include "sm100_ptx.cuh"
 
@@ -58,7 +59,7 @@ __global__ void __launch_bounds__(kNumThreads, kCtasPerSm)
 gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a,
                    const __grid_constant__ CUtensorMap tmap_b, float *__restrict__ c, int m, int n,
                    int k, long long ldc, uint32_t idesc, int n_tiles, int splits, int num_stages,
-                   int b_layout,
+                   int b_layout, Epilogue ep,
                    float *__restrict__ partials, unsigned *__restrict__ counters, int *status) {
   using Cfg = Config<kMp>;
   const uint32_t kStages = static_cast<uint32_t>(num_stages);  // ring depth of this launch
@@ -224,11 +225,15 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a,
         mbar_arrive(tmem_empty_bar(acc));
 
       const int col = n_tile * kBlockN + quarter * 32 + lane;
+      const bool fused = ep.accumulate != 0 || ep.op_count != 0;
       if (splits == 1) {
 #pragma unroll
         for (int mm = 0; mm < kMp; ++mm)
-          if (mm < m && col < n)
-            __stcs(c + static_cast<long long>(mm) * ldc + col, __uint_as_float(r[mm]));
+          if (mm < m && col < n) {
+            float *dst = c + static_cast<long long>(mm) * ldc + col;
+            const float v = __uint_as_float(r[mm]);
+            __stcs(dst, fused ? finish_value(v, dst, col, ep) : v);
+          }
         continue;
       }
       float *my_partial = partials + static_cast<size_t>(split) * m * n_pad + col;
@@ -264,8 +269,10 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if (col < n) {
 #pragma unroll
             for (int j = 0; j < 8; ++j)
-              if (mm0 + j < m)
-                __stcs(c + static_cast<long long>(mm0 + j) * ldc + col, sums[j]);
+              if (mm0 + j < m) {
+                float *dst = c + static_cast<long long>(mm0 + j) * ldc + col;
+                __stcs(dst, fused ? finish_value(sums[j], dst, col, ep) : sums[j]);
+              }
           }
         }
         if (lane == 0)
@@ -292,7 +299,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a,
 template <int kMp>
 cudaError_t launch(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, float *c, int m, int n,
                    int k, long long ldc, int dtype, int splits, float *partials,
-                   unsigned *counters, int max_ctas, int b_layout, int *status, cudaStream_t stream) {
+                   unsigned *counters, int max_ctas, int b_layout, const Epilogue &ep, int *status,
+                   cudaStream_t stream) {
   using Cfg = Config<kMp>;
   static thread_local int configured_device = -1;
   int device = 0;
@@ -315,7 +323,7 @@ cudaError_t launch(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, float *
                                         /*b_mn_major=*/false, kBlockN, kMp);
   // (The first flag describes the UMMA "A" operand, which is B^T here.)
   gemm_skinny_kernel<kMp><<<grid, kNumThreads, Cfg::smem_bytes(num_stages), stream>>>(
-      tmap_a, tmap_b, c, m, n, k, ldc, idesc, n_tiles, splits, num_stages, b_layout, partials, counters, status);
+      tmap_a, tmap_b, c, m, n, k, ldc, idesc, n_tiles, splits, num_stages, b_layout, ep, partials, counters, status);
   return cudaGetLastError();
 }
 
@@ -378,18 +386,18 @@ size_t skinny_counters_bytes(int n) {
 cudaError_t launch_gemm_skinny(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, float *c,
                                int m, int n, int k, long long ldc, int dtype, int splits,
                                float *partials, unsigned *counters, int max_ctas, int b_layout,
-                               int *status, cudaStream_t stream) {
+                               const Epilogue &ep, int *status, cudaStream_t stream) {
   if (m < 1 || m > 64 || splits < 1)
     return cudaErrorInvalidValue;
   const int mp = skinny::padded_m(m);
   if (mp == 16)
     return skinny::launch<16>(tmap_a, tmap_b, c, m, n, k, ldc, dtype, splits, partials, counters,
-                              max_ctas, b_layout, status, stream);
+                              max_ctas, b_layout, ep, status, stream);
   if (mp == 32)
     return skinny::launch<32>(tmap_a, tmap_b, c, m, n, k, ldc, dtype, splits, partials, counters,
-                              max_ctas, b_layout, status, stream);
+                              max_ctas, b_layout, ep, status, stream);
   return skinny::launch<64>(tmap_a, tmap_b, c, m, n, k, ldc, dtype, splits, partials, counters,
-                            max_ctas, b_layout, status, stream);
+                            max_ctas, b_layout, ep, status, stream);
 }
 
 } // namespace sm100

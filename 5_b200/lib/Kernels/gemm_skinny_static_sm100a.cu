@@ -133,6 +133,9 @@ int hcCudaGemmSkinnyStatic(const HcCudaGemmArgs *args, void *stream, int synchro
   if (int rc = setup_current_device(device, &setup))
     return report(rc);
 
+  if (args->accumulate != 0 || args->epilogue_count != 0)
+    return report(fail(HC_CUDA_ERR_UNSUPPORTED,
+                       "the static-scratch entry point computes C = A*B only (no accumulate, no fused operations)"));
   // Same validation and split choice as the regular path.
   HcCudaGemmArgs forced = *args;
   forced.variant = HC_CUDA_GEMM_SKINNY;
@@ -151,6 +154,7 @@ int hcCudaGemmSkinnyStatic(const HcCudaGemmArgs *args, void *stream, int synchro
   } else {
     if (args->b_layout != HC_CUDA_B_KN)
       return report(fail(HC_CUDA_ERR_UNSUPPORTED, "the static-scratch entry point takes B stored [k, n] only"));
+
     if (plan.repack_a || plan.repack_b)
       return report(fail(HC_CUDA_ERR_UNSUPPORTED,
                          "the static-scratch entry point needs a and b 16-byte aligned with lda and ldb "
@@ -182,7 +186,8 @@ int hcCudaGemmSkinnyStatic(const HcCudaGemmArgs *args, void *stream, int synchro
                         shape.block_k))
       return report(rc);
     err = hc::sm100::launch_gemm_skinny(tmap_a, tmap_b, args->c, m, n, k, args->ldc, args->dtype, plan.splits,
-                                        partials, counters, plan.grid, hc::sm100::kBLayoutKN, status_word, cuda_stream);
+                                        partials, counters, plan.grid, hc::sm100::kBLayoutKN, hc::sm100::Epilogue{},
+                                        status_word, cuda_stream);
     if (err != cudaSuccess)
       return report(fail(HC_CUDA_ERR_CUDA, std::string("launching the skinny kernel: ") + cudaGetErrorString(err)));
   }

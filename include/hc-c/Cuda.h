@@ -39,7 +39,7 @@
 extern "C" {
 #endif
 
-#define HC_CUDA_API_VERSION 2
+#define HC_CUDA_API_VERSION 3
 
 typedef enum HcCudaStatus {
   HC_CUDA_OK = 0,
@@ -64,7 +64,9 @@ typedef enum HcCudaGemmVariant {
                               when there are too few column blocks to fill the GPU */
   /* Reported by hcCudaGemmPlan only: */
   HC_CUDA_GEMM_NOOP = 3,     /* m == 0 or n == 0: nothing to write */
-  HC_CUDA_GEMM_ZERO_FILL = 4 /* k == 0: C is set to zero, no kernel */
+  HC_CUDA_GEMM_ZERO_FILL = 4,    /* k == 0: C is set to zero, no kernel */
+  HC_CUDA_GEMM_ELEMENTWISE = 5   /* k == 0 with fused element-wise work: one small kernel that
+                                    applies it to C (accumulate) or to zeros */
 } HcCudaGemmVariant;
 
 /* How B is laid out in memory. */
@@ -73,6 +75,19 @@ typedef enum HcCudaBLayout {
   HC_CUDA_B_NK = 1  /* B stored transposed, [n, k] row-major, pitch ldb >= k: a kernel whose b is
                        Buffer[N, K] and whose k-loop loads b[col0:col0+16, k0:k0+16] */
 } HcCudaBLayout;
+
+/* Element-wise operations fused into the store of C, applied in the order given. They mirror
+ * the element-wise statements an hc kernel may apply to its accumulators between the k-loop and
+ * the store (the v1 tensor operations of doc/langref.md:405-414: `*`, `+`, `-`, `maximum`,
+ * `minimum` with a scalar, and the addition of a per-column vector). */
+typedef enum HcCudaEpilogueOp {
+  HC_CUDA_EPILOGUE_SCALE = 1,      /* v = v * value */
+  HC_CUDA_EPILOGUE_ADD = 2,        /* v = v + value */
+  HC_CUDA_EPILOGUE_MAX = 3,        /* v = max(v, value) */
+  HC_CUDA_EPILOGUE_MIN = 4,        /* v = min(v, value) */
+  HC_CUDA_EPILOGUE_BIAS_COLUMN = 5 /* v = v + bias[column]; value is ignored */
+} HcCudaEpilogueOp;
+#define HC_CUDA_MAX_EPILOGUE_OPS 4
 
 /* C[m,n] = A[m,k] * B[k,n]; all three row-major with element pitches lda/ldb/ldc.
  * Mirrors the launch arguments of the reference kernel, `(a, b, c)` with
@@ -92,8 +107,18 @@ typedef struct HcCudaGemmArgs {
   int64_t ldb;
   float *c;
   int64_t ldc;
-  int32_t b_layout; /* HcCudaBLayout */
-  int32_t reserved; /* must be 0 */
+  int32_t b_layout;   /* HcCudaBLayout */
+  int32_t accumulate; /* 0: C = A*B. 1: C = C + A*B, the kernel that loads its accumulators from
+                         `c` before the k-loop instead of zeroing them; every in-range element of
+                         C is then read once and written once */
+  int32_t epilogue_count;                          /* 0..HC_CUDA_MAX_EPILOGUE_OPS */
+  int32_t epilogue_kind[HC_CUDA_MAX_EPILOGUE_OPS]; /* HcCudaEpilogueOp, applied in order to
+                                                      (C +) A*B before it is stored */
+  float epilogue_value[HC_CUDA_MAX_EPILOGUE_OPS];
+  int32_t reserved;  /* must be 0 */
+  const float *bias; /* n floats, 4-byte aligned; read by HC_CUDA_EPILOGUE_BIAS_COLUMN (at most
+                        one such operation), NULL otherwise. Host memory for hcCudaGemmHost,
+                        device memory elsewhere */
 } HcCudaGemmArgs;
 
 /* What a GEMM call will do; computed on the host without touching a device. */

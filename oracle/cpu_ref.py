@@ -47,14 +47,16 @@ def build(force: bool = False) -> Path:
 def load() -> ctypes.CDLL:
     global _LIB
     if _LIB is None:
-        if not _LIB_PATH.exists():
-            build()
-        lib = ctypes.CDLL(str(_LIB_PATH))
+        lib = ctypes.CDLL(str(build()))  # rebuilt when the source is newer than the library
+        if not hasattr(lib, "hc_oracle_matmul_fused"):  # a stale library with a fresh timestamp
+            lib = ctypes.CDLL(str(build(force=True)))
         i64, vp, ci = ctypes.c_int64, ctypes.c_void_p, ctypes.c_int
         lib.hc_oracle_matmul.argtypes = [vp, i64, vp, i64, vp, i64, i64, i64, i64, ci, ci]
         lib.hc_oracle_matmul.restype = ci
         lib.hc_oracle_matmul_rows.argtypes = [vp, i64, vp, i64, vp, i64, i64, i64, i64, ci, i64, i64, ci]
         lib.hc_oracle_matmul_rows.restype = ci
+        lib.hc_oracle_matmul_fused.argtypes = [vp, i64, vp, i64, vp, i64, i64, i64, i64, ci, ci, ci, vp, vp, vp, ci]
+        lib.hc_oracle_matmul_fused.restype = ci
         lib.hc_oracle_matmul_tiled.argtypes = [vp, i64, vp, i64, vp, i64, i64, i64, i64, ci]
         lib.hc_oracle_matmul_tiled.restype = ci
         lib.hc_oracle_max_threads.restype = ci
@@ -102,6 +104,29 @@ def matmul_k_ascending(a: np.ndarray, b: np.ndarray, *, threads: int = 0,
     r0, r1 = (0, m) if rows is None else rows
     rc = load().hc_oracle_matmul_rows(abits.ctypes.data, max(k, 1), bbits.ctypes.data, max(n, 1),
                                       c.ctypes.data, max(n, 1), m, n, k, code, r0, r1, threads)
+    if rc != 0:
+        raise MemoryError("the oracle could not allocate its widened copy of B")
+    return c
+
+
+EPILOGUE_KINDS = {"scale": 1, "add": 2, "max": 3, "min": 4, "bias": 5}
+
+
+def matmul_fused(a: np.ndarray, b: np.ndarray, *, c0: np.ndarray | None = None, epilogue=(),
+                 bias: np.ndarray | None = None, threads: int = 0) -> np.ndarray:
+    """Members of the kernel family around the example: accumulators that start from `c0`
+    (C += A.B) and element-wise statements after the k-loop, e.g.
+    `(("scale", 0.5), ("bias",), ("max", 0.0))`, in the reference simulator's fp32 order."""
+    m, n, k, code = _check(a, b)
+    abits, bbits = _as_bits(a), _as_bits(b)
+    c = np.zeros((m, n), np.float32) if c0 is None else np.array(c0, dtype=np.float32, order="C", copy=True)
+    kinds = np.array([EPILOGUE_KINDS[op[0]] for op in epilogue], dtype=np.int32)
+    values = np.array([float(op[1]) if len(op) > 1 else 0.0 for op in epilogue], dtype=np.float32)
+    bias32 = None if bias is None else np.ascontiguousarray(bias, dtype=np.float32)
+    rc = load().hc_oracle_matmul_fused(abits.ctypes.data, max(k, 1), bbits.ctypes.data, max(n, 1),
+                                       c.ctypes.data, max(n, 1), m, n, k, code, 0 if c0 is None else 1,
+                                       len(kinds), kinds.ctypes.data, values.ctypes.data,
+                                       None if bias32 is None else bias32.ctypes.data, threads)
     if rc != 0:
         raise MemoryError("the oracle could not allocate its widened copy of B")
     return c

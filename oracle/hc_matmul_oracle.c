@@ -146,6 +146,12 @@ typedef struct {
   int dtype;
   int64_t next_widen_row;
   int64_t next_row;
+  /* Family members beyond the reference example (all zero for the example itself): */
+  int accumulate;          /* accumulators start from C instead of +0.0f */
+  int op_count;            /* element-wise statements between the k-loop and the store */
+  const int *op_kind;      /* 1: v*x  2: v+x  3: max(v,x)  4: min(v,x)  5: v+bias[col] */
+  const float *op_value;
+  const float *bias;
 } RowsJob;
 
 static void *widen_worker(void *arg) {
@@ -167,14 +173,27 @@ static void *rows_worker(void *arg) {
     if (r >= job->row_end)
       return NULL;
     float *out = job->c + r * job->ldc;
-    for (int64_t j = 0; j < n; ++j)
-      out[j] = 0.0f;
+    if (!job->accumulate)
+      for (int64_t j = 0; j < n; ++j)
+        out[j] = 0.0f;
     for (int64_t kk = 0; kk < job->k; ++kk) {
       const float av = to_float(job->a[r * job->lda + kk], job->dtype);
       const float *brow = job->bf + kk * n;
       for (int64_t j = 0; j < n; ++j) {
         const float prod = av * brow[j];
         out[j] = out[j] + prod;
+      }
+    }
+    for (int i = 0; i < job->op_count; ++i) {
+      const int kind = job->op_kind[i];
+      const float x = job->op_value[i];
+      for (int64_t j = 0; j < n; ++j) {
+        const float v = out[j];
+        out[j] = kind == 1 ? v * x
+               : kind == 2 ? v + x
+               : kind == 3 ? (v > x ? v : x)
+               : kind == 4 ? (v < x ? v : x)
+                           : v + job->bias[j];
       }
     }
   }
@@ -195,9 +214,9 @@ static void run_threads(void *(*fn)(void *), RowsJob *job, int threads) {
  * accumulator per column. Rows [row_begin, row_end) of C are computed, so callers can time
  * or check a bounded sample of a large problem. `threads` <= 0 means one per online CPU.
  * Returns 0, or -1 if memory for the widened copy of B could not be obtained. */
-int hc_oracle_matmul_rows(const uint16_t *a, int64_t lda, const uint16_t *b, int64_t ldb, float *c,
-                          int64_t ldc, int64_t m, int64_t n, int64_t k, int dtype,
-                          int64_t row_begin, int64_t row_end, int threads) {
+static int matmul_rows_job(const uint16_t *a, int64_t lda, const uint16_t *b, int64_t ldb, float *c,
+                           int64_t ldc, int64_t m, int64_t n, int64_t k, int dtype,
+                           int64_t row_begin, int64_t row_end, int threads, const RowsJob *extra) {
   if (row_begin < 0)
     row_begin = 0;
   if (row_end > m)
@@ -208,6 +227,8 @@ int hc_oracle_matmul_rows(const uint16_t *a, int64_t lda, const uint16_t *b, int
     threads = hc_oracle_max_threads();
   RowsJob job;
   memset(&job, 0, sizeof job);
+  if (extra != NULL)
+    job = *extra;
   job.a = a;
   job.b = b;
   job.c = c;
@@ -228,6 +249,31 @@ int hc_oracle_matmul_rows(const uint16_t *a, int64_t lda, const uint16_t *b, int
   run_threads(rows_worker, &job, threads);
   free(job.bf);
   return 0;
+}
+
+int hc_oracle_matmul_rows(const uint16_t *a, int64_t lda, const uint16_t *b, int64_t ldb, float *c,
+                          int64_t ldc, int64_t m, int64_t n, int64_t k, int dtype,
+                          int64_t row_begin, int64_t row_end, int threads) {
+  return matmul_rows_job(a, lda, b, ldb, c, ldc, m, n, k, dtype, row_begin, row_end, threads, NULL);
+}
+
+/* The kernel family around the example, as the reference simulator executes its members:
+ * with `accumulate` the accumulators are loaded from C before the k-loop (out-of-range
+ * elements read as 0 and are never stored), so each sum starts from C[i,j] and then takes
+ * the products k ascending; after the k-loop `op_count` element-wise fp32 statements run in
+ * order on every accumulator value (kinds as in RowsJob; kind 5 adds bias[column]). */
+int hc_oracle_matmul_fused(const uint16_t *a, int64_t lda, const uint16_t *b, int64_t ldb, float *c,
+                           int64_t ldc, int64_t m, int64_t n, int64_t k, int dtype, int accumulate,
+                           int op_count, const int *op_kind, const float *op_value, const float *bias,
+                           int threads) {
+  RowsJob extra;
+  memset(&extra, 0, sizeof extra);
+  extra.accumulate = accumulate;
+  extra.op_count = op_count;
+  extra.op_kind = op_kind;
+  extra.op_value = op_value;
+  extra.bias = bias;
+  return matmul_rows_job(a, lda, b, ldb, c, ldc, m, n, k, dtype, 0, m, threads, &extra);
 }
 
 int hc_oracle_matmul(const uint16_t *a, int64_t lda, const uint16_t *b, int64_t ldb, float *c,

@@ -23,6 +23,10 @@ Fixtures (all produced by `hc.simulator.launch` on the example kernel):
   simbt_f16_m17_n19_k18_seed9
       the transposed-B member of the family defined in 5_b200/examples/b200_wmma_matmul.py
       (b stored [N, K]); `b_bits` holds B as stored
+  simacc_f16_m17_n19_k18_seed11
+      the accumulating member of that family (C = C + A.B); `c0` holds C before the launch
+  simfused_bf16_m33_n17_k40_seed12
+      the fused member (C = maximum(0.125 * (A.B) + bias, 0)); `bias` holds the fourth buffer
 The file blocked_reference.npz holds `reference_blocked_matmul` of the first four (the
 reference test's own comparison value, atol 2e-6).
 """
@@ -63,13 +67,14 @@ def _bf16_twin(example_module):
     return twin
 
 
-def _save(name: str, a: np.ndarray, b: np.ndarray, c: np.ndarray) -> None:
+def _save(name: str, a: np.ndarray, b: np.ndarray, c: np.ndarray, **extra: np.ndarray) -> None:
     np.savez_compressed(
         HERE / f"{name}.npz",
         a_bits=a.view(np.uint16),
         b_bits=b.view(np.uint16),
         c=c,
         dtype=np.array(a.dtype.name),
+        **extra,
     )
     print(f"{name}: A{a.shape} B{b.shape} -> C{c.shape}", flush=True)
 
@@ -120,6 +125,22 @@ def main() -> int:
     c = np.zeros((17, 19), np.float32)
     mod.hc.simulator.launch(mod.tiled_wmma_matmul_for("float16", True), a, bt, c)
     _save("simbt_f16_m17_n19_k18_seed9", a, bt, c)
+
+    rng = np.random.default_rng(11)
+    a = rng.uniform(-1.0, 1.0, size=(17, 18)).astype(np.float16)
+    b = rng.uniform(-1.0, 1.0, size=(18, 19)).astype(np.float16)
+    c0 = rng.uniform(-2.0, 2.0, size=(17, 19)).astype(np.float32)
+    c = c0.copy()
+    mod.hc.simulator.launch(mod.tiled_wmma_matmul_for("float16", False, "accumulate"), a, b, c)
+    _save("simacc_f16_m17_n19_k18_seed11", a, b, c, c0=c0)
+
+    rng = np.random.default_rng(12)
+    a = rng.uniform(-1.0, 1.0, size=(33, 40)).astype(ml_dtypes.bfloat16)
+    b = rng.uniform(-1.0, 1.0, size=(40, 17)).astype(ml_dtypes.bfloat16)
+    bias = rng.uniform(-0.5, 0.5, size=(17,)).astype(np.float32)
+    c = np.full((33, 17), np.float32(-7.0))  # every element must be overwritten
+    mod.hc.simulator.launch(mod.tiled_wmma_matmul_for("bfloat16", False, "fused"), a, b, c, bias)
+    _save("simfused_bf16_m33_n17_k40_seed12", a, b, c, bias=bias)
     return 0
 
 

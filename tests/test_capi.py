@@ -27,7 +27,7 @@ def test_library_exports_every_declared_symbol() -> None:
     for name in declared:
         assert hasattr(lib, name), f"{name} is declared in hc-c/Cuda.h but not exported"
     assert set(declared) == set(cuda.EXPORTS)
-    assert lib.hcCudaApiVersion() == 2
+    assert lib.hcCudaApiVersion() == cuda.API_VERSION
 
 
 def test_every_declaration_cites_or_describes_its_reference_counterpart() -> None:
@@ -96,9 +96,49 @@ def test_plan_with_b_stored_transposed() -> None:
     info = cuda._PlanInfo()
     assert lib.hcCudaGemmPlan(ctypes.byref(args), 148, ctypes.byref(info)) == 1
     assert b"b_layout" in lib.hcCudaContextLastError(None)
-    args = cuda._GemmArgs(8, 8, 8, 0, 0, 0x1000, 8, 0x2000, 8, 0x3000, 8, 0, 1)
+    args = cuda._GemmArgs(8, 8, 8, 0, 0, 0x1000, 8, 0x2000, 8, 0x3000, 8, 0, 0)
+    args.reserved = 1
     assert lib.hcCudaGemmPlan(ctypes.byref(args), 148, ctypes.byref(info)) == 1
     assert b"reserved" in lib.hcCudaContextLastError(None)
+
+
+def test_plan_with_accumulate_and_fused_operations() -> None:
+    """The C += A.B member and the element-wise operations folded into the store."""
+    assert ctypes.sizeof(cuda._GemmArgs) == 136  # the layout include/hc-c/Cuda.h declares
+    plain = cuda.plan_gemm(4095, 3073, 1031, "bfloat16", lda=1031, ldb=3073, ldc=3073)
+    fused = cuda.plan_gemm(4095, 3073, 1031, "bfloat16", lda=1031, ldb=3073, ldc=3073, accumulate=True,
+                           epilogue=(("scale", 0.5), ("bias",), ("max", 0.0), ("min", 6.0)))
+    assert (fused.variant, fused.grid, fused.kernel_launches) == (plain.variant, plain.grid, plain.kernel_launches)
+    # k == 0: nothing to add. C stays (accumulate), is zeroed, or only gets the element-wise work.
+    assert cuda.plan_gemm(64, 64, 0, "float16", accumulate=True).variant == "noop"
+    assert cuda.plan_gemm(64, 64, 0, "float16").variant == "zero_fill"
+    only = cuda.plan_gemm(64, 64, 0, "float16", accumulate=True, epilogue=(("add", 1.0),))
+    assert only.variant == "elementwise" and only.kernel_launches == 1
+    with pytest.raises(DeviceError, match="at most one HC_CUDA_EPILOGUE_BIAS_COLUMN"):
+        cuda.plan_gemm(64, 64, 64, "float16", epilogue=(("bias",), ("bias",)))
+    with pytest.raises(DeviceError, match="bias must be a 4-byte-aligned pointer"):
+        cuda.plan_gemm(64, 64, 64, "float16", epilogue=(("bias",),), bias=None)
+    with pytest.raises(DeviceError, match="bias must be a 4-byte-aligned pointer"):
+        cuda.plan_gemm(64, 64, 64, "float16", epilogue=(("bias",),), bias=0xC0000002)
+    with pytest.raises(DeviceError, match="c must not overlap bias"):
+        cuda.plan_gemm(64, 64, 64, "float16", epilogue=(("bias",),), bias=0x80000000 + 64)
+    with pytest.raises(ValueError, match="at most 4 fused"):
+        cuda.plan_gemm(64, 64, 64, "float16", epilogue=(("add", 1.0),) * 5)
+    with pytest.raises(ValueError, match="unknown fused operation"):
+        cuda.plan_gemm(64, 64, 64, "float16", epilogue=(("divide", 2.0),))
+    lib = cuda.library()
+    info = cuda._PlanInfo()
+    args = cuda._gemm_args(8, 8, 8, "float16", 0x1000, 8, 0x2000, 8, 0x3000, 8, 0)
+    args.accumulate = 2
+    assert lib.hcCudaGemmPlan(ctypes.byref(args), 148, ctypes.byref(info)) == 1
+    assert b"accumulate" in lib.hcCudaContextLastError(None)
+    args.accumulate, args.epilogue_count = 0, 5
+    assert lib.hcCudaGemmPlan(ctypes.byref(args), 148, ctypes.byref(info)) == 1
+    assert b"epilogue_count" in lib.hcCudaContextLastError(None)
+    args.epilogue_count = 1
+    args.epilogue_kind[0] = 9
+    assert lib.hcCudaGemmPlan(ctypes.byref(args), 148, ctypes.byref(info)) == 1
+    assert b"epilogue_kind[0]" in lib.hcCudaContextLastError(None)
 
 
 def test_plan_degenerate_shapes() -> None:

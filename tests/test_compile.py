@@ -151,7 +151,7 @@ def test_lowering_hook_is_called_and_steers_the_variant() -> None:
 def test_transposed_b_member_is_recognised() -> None:
     handle = compiled_for("float16", None, True)
     plan = handle.plan
-    assert plan is not None and plan.b_transposed and plan.intrinsic_name == "wmma_16x16x16_bt"
+    assert plan is not None and plan.b_transposed and plan.intrinsic_name == "wmma_16x16x16"
     assert (plan.m_dim, plan.n_dim, plan.k_dim) == ("M", "N", "K") and plan.tile == (16, 16, 16)
     launch = handle.prepare(np.zeros((17, 18), np.float16), np.zeros((19, 18), np.float16),
                             np.zeros((17, 19), np.float32))
@@ -159,6 +159,126 @@ def test_transposed_b_member_is_recognised() -> None:
     with pytest.raises(hc.LaunchError, match="conflicting binding for K: 18 from 'a.shape\\[1\\]' vs 19 from 'b.shape\\[1\\]'"):
         handle(np.zeros((17, 18), np.float16), np.zeros((18, 19), np.float16), np.zeros((17, 19), np.float32))
     assert not compiled_for("float16").plan.b_transposed
+
+
+def test_accumulating_and_fused_members_are_recognised() -> None:
+    acc = compiled_for("float16", None, False, "accumulate").plan
+    assert acc is not None and acc.accumulate and acc.epilogue == () and acc.bias_param is None
+    fused_handle = compiled_for("bfloat16", None, False, "fused")
+    fused = fused_handle.plan
+    assert fused is not None and not fused.accumulate and fused.bias_param == "bias"
+    assert fused.epilogue == (("scale", 0.125), ("bias",), ("max", 0.0))
+    plain = compiled_for("float16").plan
+    assert not plain.accumulate and plain.epilogue == () and plain.bias_param is None
+    bf16 = np_bf16()
+    launch = fused_handle.prepare(np.zeros((33, 40), bf16), np.zeros((40, 17), bf16), np.zeros((33, 17), np.float32),
+                                  np.zeros((17,), np.float32))
+    assert launch.symbols == {"M": 33, "K": 40, "N": 17}
+    with pytest.raises(hc.LaunchError, match="conflicting binding for N: 17 from .* vs 16 from 'bias.shape\\[0\\]'"):
+        fused_handle(np.zeros((33, 40), bf16), np.zeros((40, 17), bf16), np.zeros((33, 17), np.float32),
+                     np.zeros((16,), np.float32))
+    with pytest.raises(hc.LaunchError, match="bias dtype expected float32, got float64"):
+        fused_handle(np.zeros((33, 40), bf16), np.zeros((40, 17), bf16), np.zeros((33, 17), np.float32),
+                     np.zeros((17,), np.float64))
+
+
+_VARIANT_SOURCE = """
+import numpy as np
+from hc import Buffer, WorkGroup, WorkItem, idx_type, kernel, sym, tensor_type, undef_type, vector_type
+from hc.symbols import ceil_div
+
+M, N, K = sym.M, sym.N, sym.K
+SIX = 6.0
+
+@kernel.intrinsic(
+    scope=WorkItem, effects="pure", const_attrs={{"wave_size", "arch"}},
+    operand_types=(undef_type(), tensor_type((16, 16), np.float16), tensor_type((16, 16), np.float16),
+                   vector_type((16,), np.float16), vector_type((16,), np.float16),
+                   vector_type((8,), np.float32), idx_type()),
+    result_types=(vector_type((8,), np.float32),))
+def mma(group, a_tile, b_tile, a_frag, b_frag, acc_frag, *, lane, wave_size, arch):
+    return acc_frag
+
+@kernel.func(scope=WorkGroup)
+def step_fn(group, a_tile, b_tile, acc):
+    return mma(group, a_tile, b_tile, None, None, acc, lane=0, wave_size=32, arch="x")
+
+@kernel.func(scope=WorkGroup)
+def from_c(group, c):
+    return group.load(c[0:16, 0:16], shape=(16, 16))
+
+@kernel.func(scope=WorkGroup)
+def plus_bias(group, bias, acc):
+    return acc
+
+@kernel.func(scope=WorkGroup)
+def store(group, c, acc):
+    group.store(c, acc)
+
+@kernel(work_shape=(ceil_div(M, 16) * 32, ceil_div(N, 16)), group_shape=(32, 1), subgroup_size=32)
+def matmul(group, a: Buffer[M, K, np.float16], b: Buffer[K, N, np.float16], c: Buffer[M, N, np.float32]{extra_param}) -> None:
+    acc = {init}
+    for k0 in range(0, a.shape[1], 16):
+        a_tile = group.load(a[0:16, k0 : k0 + 16], shape=(16, 16))
+        b_tile = group.load(b[k0 : k0 + 16, 0:16], shape=(16, 16))
+        acc = step_fn(group, a_tile, b_tile, acc)
+{after}
+    store(group, c, acc)
+{tail}
+"""
+
+
+def _variant(tmp_path, name, *, init="0", after=(), extra_param="", tail=""):
+    import importlib.util
+
+    text = _VARIANT_SOURCE.format(init=init, after="\n".join("    " + line for line in after),
+                                  extra_param=extra_param, tail="    " + tail if tail else "")
+    path = tmp_path / f"{name}.py"
+    path.write_text(text, encoding="utf-8")
+    spec = importlib.util.spec_from_file_location(name, path)
+    module = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(module)
+    return module.matmul
+
+
+def test_statements_around_the_k_loop(tmp_path) -> None:
+    """What the recogniser reads before the k-loop (accumulators loaded from c) and between the
+    loop and the store (element-wise statements in their spellings)."""
+    plan, why = recognise_tiled_matmul(_variant(tmp_path, "v_acc", init="from_c(group, c)"))
+    assert plan is not None and plan.accumulate and plan.epilogue == (), why
+    plan, why = recognise_tiled_matmul(_variant(
+        tmp_path, "v_ops", after=["acc = 2 * acc", "acc = acc - np.float32(1.5)", "acc = acc.astype(np.float32)",
+                                  "acc = np.minimum(SIX, acc)", "acc = np.maximum(acc, -0.5)"]))
+    assert plan is not None and not plan.accumulate, why
+    assert plan.epilogue == (("scale", 2.0), ("add", -1.5), ("min", 6.0), ("max", -0.5))
+    plan, why = recognise_tiled_matmul(_variant(
+        tmp_path, "v_bias", init="from_c(group, c)", extra_param=", bias: Buffer[N, np.float32]",
+        after=["acc = plus_bias(group, bias, acc)", "acc = acc * 0.1"]))
+    assert plan is not None and plan.accumulate and plan.bias_param == "bias", why
+    assert plan.epilogue == (("bias",), ("scale", float(np.float32(0.1))))
+
+    def rejected(name, message, **kwargs):
+        plan, why = recognise_tiled_matmul(_variant(tmp_path, name, **kwargs))
+        assert plan is None and any(message in line for line in why), why
+
+    rejected("r_div", "is not an element-wise statement this target folds", after=["acc = acc / 2"])
+    rejected("r_square", "is not an element-wise statement this target folds", after=["acc = acc * acc"])
+    rejected("r_exp", "is not an element-wise statement this target folds", after=["acc = np.exp(acc)"])
+    rejected("r_other", "is not an element-wise statement this target folds", after=["other = acc * 2"])
+    rejected("r_many", "at most 4 element-wise statements", after=["acc = acc + 1"] * 5)
+    rejected("r_after", "after the store", tail="acc = acc * 2")
+    rejected("r_unused", "must be added to `acc` exactly once", extra_param=", bias: Buffer[N, np.float32]")
+    rejected("r_dtype", "must be Buffer[N, float32]", extra_param=", bias: Buffer[N, np.float16]",
+             after=["acc = plus_bias(group, bias, acc)"])
+    rejected("r_extent", "must be Buffer[N, float32]", extra_param=", bias: Buffer[M, np.float32]",
+             after=["acc = plus_bias(group, bias, acc)"])
+    rejected("r_early", "may only be read before the k-loop to initialise", init="0\n    peek = from_c(group, c)")
+
+
+def np_bf16():
+    import ml_dtypes
+
+    return ml_dtypes.bfloat16
 
 
 def test_family_members_are_recognised() -> None:

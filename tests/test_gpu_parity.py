@@ -130,6 +130,147 @@ def test_transposed_b_fixture_and_device_buffers(gpu_ctx) -> None:
     assert np.array_equal(dc.to_numpy(), expect)
 
 
+# ---------------------------------------------------------------- around the k-loop -----
+
+
+def assert_fused_close(out, a, b, *, c0=None, epilogue=(), bias=None, use_oracle=True) -> None:
+    """`out` against ops(C0 + A.B) in float64, with the benchmark's element bound carried through
+    the element-wise operations (each is 1-Lipschitz up to its scale factor), and against the
+    oracle's fp32 restatement under the same bound."""
+    a64, b64 = a.astype(np.float64), b.astype(np.float64)
+    ref = a64 @ b64
+    bound = np.abs(a64) @ np.abs(b64)
+    if c0 is not None:
+        ref = ref + c0
+        bound = bound + np.abs(c0)
+    for op in epilogue:
+        if op[0] == "scale":
+            ref, bound = ref * np.float32(op[1]), bound * abs(op[1])
+        elif op[0] == "add":
+            ref, bound = ref + np.float32(op[1]), bound + abs(op[1])
+        elif op[0] == "bias":
+            ref, bound = ref + bias[None, :], bound + np.abs(bias)[None, :]
+        elif op[0] == "max":
+            ref = np.maximum(ref, np.float32(op[1]))
+        else:
+            ref = np.minimum(ref, np.float32(op[1]))
+    assert out.shape == ref.shape and out.dtype == np.float32 and np.isfinite(out).all()
+    diff = np.abs(out - ref)
+    assert (diff <= ELEMENT_RATIO * bound + 1e-30).all(), float((diff / np.maximum(bound, 1e-30)).max())
+    assert np.linalg.norm(diff) <= REL_FROBENIUS * max(np.linalg.norm(ref), 1e-30)
+    if use_oracle:
+        expect = cpu_ref.matmul_fused(a, b, c0=c0, epilogue=epilogue, bias=bias)
+        assert (np.abs(out.astype(np.float64) - expect) <= ELEMENT_RATIO * bound + 1e-30).all()
+
+
+def test_accumulating_and_fused_fixtures() -> None:
+    """The members the reference simulator executed (host arrays through the compiled handles)."""
+    golden = load_golden.__globals__["GOLDEN"]
+    a, b, c_sim = load_golden("simacc_f16_m17_n19_k18_seed11")
+    with np.load(golden / "simacc_f16_m17_n19_k18_seed11.npz") as data:
+        c0 = data["c0"]
+    c = c0.copy()
+    compiled_for("float16", None, False, "accumulate")(a, b, c)
+    assert_fused_close(c, a, b, c0=c0)
+    np.testing.assert_allclose(c, c_sim, rtol=0, atol=2e-6)  # the reference test's own tolerance
+    strided = np.zeros((17, 40), np.float32)[:, ::2][:, :19]  # not row-major: staged through a copy
+    strided[...] = c0
+    compiled_for("float16", None, False, "accumulate")(a, b, strided)
+    assert np.array_equal(strided, c)
+
+    a, b, c_sim = load_golden("simfused_bf16_m33_n17_k40_seed12")
+    with np.load(golden / "simfused_bf16_m33_n17_k40_seed12.npz") as data:
+        bias = data["bias"]
+    c = np.full((33, 17), np.float32(-7.0))
+    compiled_for("bfloat16", None, False, "fused")(a, b, c, bias)
+    assert_fused_close(c, a, b, epilogue=(("scale", 0.125), ("bias",), ("max", 0.0)), bias=bias)
+    np.testing.assert_allclose(c, c_sim, rtol=0, atol=2e-6)
+    assert np.array_equal(c == 0, c_sim == 0)  # clipped in the same places
+
+
+FUSED_SHAPES = [
+    # dense on single CTAs / CTA pairs, aligned and odd pitches; skinny with and without split-k
+    (128, 256, 64, 0), (300, 520, 136, 0), (513, 1001, 264, 3), (1024, 1024, 256, 0), (2050, 2051, 130, 1),
+    (8, 4096, 512, 0), (8, 129, 2048, 0), (33, 515, 1024, 5), (64, 16384, 256, 0),
+]
+
+
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+@pytest.mark.parametrize("shape", FUSED_SHAPES)
+def test_accumulate_and_fused_operations_on_device_buffers(shape, dtype: str, gpu_ctx) -> None:
+    m, n, k, pad = shape
+    a, b = random_inputs(m, n, k, dtype, scale=0.25)
+    rng = np.random.default_rng([m, n, k, 77])
+    c0 = rng.standard_normal((m, n)).astype(np.float32)
+    bias = rng.standard_normal((n,)).astype(np.float32)
+    da, db = gpu_ctx.to_device(a), gpu_ctx.to_device(b)
+    dbias = gpu_ctx.to_device(bias)
+    dc = cuda.DeviceBuffer(gpu_ctx, (m, n), np.float32, ld=n + pad)
+    cases = [
+        dict(accumulate=True),
+        dict(epilogue=(("scale", 0.5), ("bias",), ("max", 0.0))),
+        dict(accumulate=True, epilogue=(("bias",), ("scale", -2.0), ("min", 1.0), ("add", 0.25))),
+    ]
+    for case in cases:
+        dc.copy_from_host(c0)
+        gpu_ctx.gemm(da, db, dc, bias=dbias if any(op[0] == "bias" for op in case.get("epilogue", ())) else None,
+                     **case)
+        gpu_ctx.synchronize()
+        assert_fused_close(dc.to_numpy(), a, b, c0=c0 if case.get("accumulate") else None,
+                           epilogue=case.get("epilogue", ()), bias=bias, use_oracle=m * n * k <= 1 << 28)
+    # Two accumulating launches in a row add the product twice.
+    dc.copy_from_host(c0)
+    gpu_ctx.gemm(da, db, dc, accumulate=True)
+    gpu_ctx.gemm(da, db, dc, accumulate=True)
+    gpu_ctx.synchronize()
+    twice = dc.to_numpy()
+    gpu_ctx.gemm(da, db, dc)
+    gpu_ctx.synchronize()
+    product = dc.to_numpy()
+    np.testing.assert_allclose(twice, c0 + 2 * product, rtol=1e-5, atol=1e-5)
+    for buf in (da, db, dc, dbias):
+        buf.free()
+
+
+def test_fused_operations_on_host_arrays(gpu_ctx) -> None:
+    """Host buffers: C and the bias travel to the device first; the large case takes the
+    pipelined row-panel path, where each panel's rows of C arrive before its product."""
+    for m, n, k in ((200, 300, 264), (2048, 2304, 2048), (16, 5000, 1024)):
+        a, b = random_inputs(m, n, k, "float16", scale=0.25)
+        rng = np.random.default_rng([m, n, k, 78])
+        c0 = rng.standard_normal((m, n)).astype(np.float32)
+        bias = rng.standard_normal((n,)).astype(np.float32)
+        ops = (("scale", 0.5), ("bias",), ("max", -0.25))
+        c = c0.copy()
+        gpu_ctx.gemm_host(a, b, c, accumulate=True, epilogue=ops, bias=bias)
+        assert_fused_close(c, a, b, c0=c0, epilogue=ops, bias=bias, use_oracle=m * n * k <= 1 << 28)
+
+
+def test_fused_operations_with_k_zero(gpu_ctx) -> None:
+    """No product: the launch whose k-loop runs zero times still applies what surrounds it."""
+    rng = np.random.default_rng(5)
+    m, n = 37, 129
+    c0 = rng.standard_normal((m, n)).astype(np.float32)
+    bias = rng.standard_normal((n,)).astype(np.float32)
+    a = np.zeros((m, 0), np.float16)
+    b = np.zeros((0, n), np.float16)
+    c = c0.copy()
+    gpu_ctx.gemm_host(a, b, c, accumulate=True)
+    assert np.array_equal(c, c0)
+    gpu_ctx.gemm_host(a, b, c, accumulate=True, epilogue=(("scale", 2.0), ("bias",)), bias=bias)
+    assert np.array_equal(c, c0 * np.float32(2.0) + bias[None, :])
+    gpu_ctx.gemm_host(a, b, c, epilogue=(("add", 3.0), ("min", 1.0)))
+    assert np.array_equal(c, np.full((m, n), np.float32(1.0)))
+    dc = cuda.DeviceBuffer(gpu_ctx, (m, n), np.float32, ld=n + 3)
+    dc.copy_from_host(c0)
+    da, db = cuda.DeviceBuffer(gpu_ctx, (m, 0), np.float16, ld=8), cuda.DeviceBuffer(gpu_ctx, (0, n), np.float16, ld=n)
+    gpu_ctx.gemm(da, db, dc, accumulate=True, epilogue=(("max", 0.0),))
+    gpu_ctx.synchronize()
+    assert np.array_equal(dc.to_numpy(), np.maximum(c0, np.float32(0)))
+    assert compiled_for("float16", None, False, "fused")(a, b, c, bias) is None
+    assert np.array_equal(c, np.maximum(np.zeros((m, n), np.float32) * np.float32(0.125) + bias[None, :], 0))
+
+
 @pytest.mark.parametrize("seed", range(6))
 def test_random_shapes(seed: int, gpu_ctx) -> None:
     """Seeded random shapes, small and awkward ones included, in both element types and both B

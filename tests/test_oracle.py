@@ -16,6 +16,8 @@ from oracle import cpu_ref
 def test_fixtures_are_present() -> None:
     assert len(GOLDEN_NAMES) == 6
     assert (GOLDEN / "simbt_f16_m17_n19_k18_seed9.npz").exists()
+    assert (GOLDEN / "simacc_f16_m17_n19_k18_seed11.npz").exists()
+    assert (GOLDEN / "simfused_bf16_m33_n17_k40_seed12.npz").exists()
     assert (GOLDEN / "blocked_reference.npz").exists()
 
 
@@ -35,6 +37,35 @@ def test_transposed_b_kernel_fixture() -> None:
     assert bt.shape == (19, 18)
     out = cpu_ref.matmul_k_ascending(a, np.ascontiguousarray(bt.T))
     assert np.array_equal(out.view(np.uint32), c_sim.view(np.uint32))
+
+
+def test_accumulating_and_fused_kernel_fixtures() -> None:
+    """The C += A.B member and the member with element-wise statements after the k-loop, as the
+    reference simulator executed them: the oracle's restatement is bit-identical."""
+    a, b, c_sim = load_golden("simacc_f16_m17_n19_k18_seed11")
+    with np.load(GOLDEN / "simacc_f16_m17_n19_k18_seed11.npz") as data:
+        c0 = data["c0"]
+    out = cpu_ref.matmul_fused(a, b, c0=c0)
+    assert np.array_equal(out.view(np.uint32), c_sim.view(np.uint32))
+    assert not np.array_equal(out, cpu_ref.matmul_k_ascending(a, b))  # C's old contents matter
+    # Starting from C is not the same rounding as adding C at the end.
+    late = cpu_ref.matmul_k_ascending(a, b) + c0
+    assert np.abs(late - c_sim).max() < 1e-5
+
+    a, b, c_sim = load_golden("simfused_bf16_m33_n17_k40_seed12")
+    with np.load(GOLDEN / "simfused_bf16_m33_n17_k40_seed12.npz") as data:
+        bias = data["bias"]
+    ops = (("scale", 0.125), ("bias",), ("max", 0.0))
+    out = cpu_ref.matmul_fused(a, b, epilogue=ops, bias=bias)
+    assert np.array_equal(out.view(np.uint32), c_sim.view(np.uint32))
+    assert (c_sim == 0).any() and (c_sim > 0).any()  # the maximum clips some elements, not all
+    by_hand = np.maximum(cpu_ref.matmul_numpy(a, b) * np.float32(0.125) + bias[None, :], np.float32(0))
+    assert np.array_equal(by_hand.view(np.uint32), c_sim.view(np.uint32))
+    # Order matters: the statements are applied as written.
+    swapped = cpu_ref.matmul_fused(a, b, epilogue=(("bias",), ("scale", 0.125), ("max", 0.0)), bias=bias)
+    assert not np.array_equal(swapped, c_sim)
+    for op, fn in ((("add", 1.5), lambda x: x + np.float32(1.5)), (("min", 0.25), lambda x: np.minimum(x, np.float32(0.25)))):
+        assert np.array_equal(cpu_ref.matmul_fused(a, b, epilogue=(op,)), fn(cpu_ref.matmul_numpy(a, b)))
 
 
 def test_oracle_meets_the_reference_tests_own_tolerance() -> None:
