@@ -377,7 +377,10 @@ int enqueue_gemm(HcCudaContext *ctx, const HcCudaGemmArgs *args, const HcCudaGem
     ep.op_kind[i] = args->epilogue_kind[i];
     ep.op_value[i] = args->epilogue_value[i];
   }
-  ep.bias = args->bias;
+  ep.bias = nullptr;  // non-null only when an operation reads it
+  for (int i = 0; i < args->epilogue_count; ++i)
+    if (args->epilogue_kind[i] == HC_CUDA_EPILOGUE_BIAS_COLUMN)
+      ep.bias = args->bias;
   if (plan.variant == HC_CUDA_GEMM_ELEMENTWISE) {
     HC_TRY_CUDA(ctx, hc::sm100::launch_epilogue_only(args->c, m, n, args->ldc, ep, ctx->stream));
     return HC_CUDA_OK;

@@ -77,6 +77,10 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int tiles_m, int tiles
   return tc;
 }
 
+// kFused: the launch has work folded into the store (accumulate, element-wise operations); the
+// plain instantiation is the reference example's C = A.B and compiles to the same code as before
+// that work existed.
+template <bool kFused>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
 gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                        const __grid_constant__ CUtensorMap tmap_b, float *__restrict__ c, int m, int n,
@@ -238,14 +242,16 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const TileCoord tc = tile_coord(tile, tiles_m, tiles_n, group_n);
       const uint32_t acc = iter & 1u;
       const uint32_t acc_phase = (iter >> 1) & 1u;
+      const int row_base = tc.m_blk * kTileM + static_cast<int>(cta_rank) * kCtaM + quarter * 32;
+      const int col_base = tc.n_blk * kTileN;
+      if (kFused && ep.accumulate)
+        prefetch_c_tile_row(c, ldc, m, n, row_base + lane, col_base, kTileN);
       const bool ready = mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag);
       if (!__all_sync(0xffffffffu, ready))
         break;
       tcgen05_fence_after_sync();
-      const int row_base = tc.m_blk * kTileM + static_cast<int>(cta_rank) * kCtaM + quarter * 32;
-      const int col_base = tc.n_blk * kTileN;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kTileN;
-      drain_accumulator_rows<kTileN>(taddr, stage_gen, c, ldc, m, n, row_base, col_base, vec_ok, lane,
+      drain_accumulator_rows<kTileN, kFused>(taddr, stage_gen, c, ldc, m, n, row_base, col_base, vec_ok, lane,
                                      map_to_cta(tmem_empty_bar(acc), 0), /*release_remote=*/true, ep);
     }
   }
@@ -280,8 +286,11 @@ cudaError_t launch_gemm_dense_pair(const CUtensorMap &tmap_a, const CUtensorMap 
   if (err != cudaSuccess)
     return err;
   if (configured_device != device) {
-    err = cudaFuncSetAttribute(gemm_dense_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    err = cudaFuncSetAttribute(gemm_dense_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                static_cast<int>(kSmemBytes));
+    if (err == cudaSuccess)
+      err = cudaFuncSetAttribute(gemm_dense_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(kSmemBytes));
     if (err != cudaSuccess)
       return err;
     configured_device = device;
@@ -303,8 +312,13 @@ cudaError_t launch_gemm_dense_pair(const CUtensorMap &tmap_a, const CUtensorMap 
   int l2_hints = 3;
   if (const char *h = std::getenv("HC_CUDA_L2_HINTS"))  // tuning aid
     l2_hints = std::atoi(h);
-  gemm_dense_pair_kernel<<<static_cast<unsigned>(clusters * 2), kNumThreads, kSmemBytes, stream>>>(
-      tmap_a, tmap_b, c, m, n, k, ldc, idesc, tiles_m, tiles_n, group_n, l2_hints, b_layout, ep, status);
+  const unsigned grid = static_cast<unsigned>(clusters * 2);
+  if (ep.accumulate != 0 || ep.op_count != 0)
+    gemm_dense_pair_kernel<true><<<grid, kNumThreads, kSmemBytes, stream>>>(
+        tmap_a, tmap_b, c, m, n, k, ldc, idesc, tiles_m, tiles_n, group_n, l2_hints, b_layout, ep, status);
+  else
+    gemm_dense_pair_kernel<false><<<grid, kNumThreads, kSmemBytes, stream>>>(
+        tmap_a, tmap_b, c, m, n, k, ldc, idesc, tiles_m, tiles_n, group_n, l2_hints, b_layout, ep, status);
   return cudaGetLastError();
 }
 

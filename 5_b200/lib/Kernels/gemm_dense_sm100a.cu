@@ -66,6 +66,8 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int tiles_m, int tiles
   return tc;
 }
 
+// kFused: the launch has work folded into the store (accumulate, element-wise operations).
+template <bool kFused>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_dense_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   const __grid_constant__ CUtensorMap tmap_b, float *__restrict__ c, int m, int n,
@@ -206,14 +208,16 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const TileCoord tc = tile_coord(tile, tiles_m, tiles_n, group_n);
       const uint32_t acc = iter & 1u;
       const uint32_t acc_phase = (iter >> 1) & 1u;
+      const int row_base = tc.m_blk * kBlockM + quarter * 32;
+      const int col_base = tc.n_blk * kBlockN;
+      if (kFused && ep.accumulate)
+        prefetch_c_tile_row(c, ldc, m, n, row_base + lane, col_base, kBlockN);
       const bool ready = mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag);
       if (!__all_sync(0xffffffffu, ready))
         break;
       tcgen05_fence_after_sync();
-      const int row_base = tc.m_blk * kBlockM + quarter * 32;
-      const int col_base = tc.n_blk * kBlockN;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kBlockN;
-      drain_accumulator_rows<kBlockN>(taddr, stage_gen, c, ldc, m, n, row_base, col_base, vec_ok, lane,
+      drain_accumulator_rows<kBlockN, kFused>(taddr, stage_gen, c, ldc, m, n, row_base, col_base, vec_ok, lane,
                                       tmem_empty_bar(acc), /*release_remote=*/false, ep);
     }
   }
@@ -248,8 +252,11 @@ cudaError_t launch_gemm_dense(const CUtensorMap &tmap_a, const CUtensorMap &tmap
   if (err != cudaSuccess)
     return err;
   if (configured_device != device) {
-    err = cudaFuncSetAttribute(gemm_dense_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    err = cudaFuncSetAttribute(gemm_dense_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                static_cast<int>(kSmemBytes));
+    if (err == cudaSuccess)
+      err = cudaFuncSetAttribute(gemm_dense_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(kSmemBytes));
     if (err != cudaSuccess)
       return err;
     configured_device = device;
@@ -264,9 +271,14 @@ cudaError_t launch_gemm_dense(const CUtensorMap &tmap_a, const CUtensorMap &tmap
                                         /*b_mn_major=*/b_layout == kBLayoutKN, kBlockM, kBlockN);
   if (group_n < 1)
     group_n = 1;
-  gemm_dense_kernel<<<grid, kNumThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, c, m, n, k, ldc,
-                                                               idesc, tiles_m, tiles_n, group_n,
-                                                               b_layout, ep, status);
+  if (ep.accumulate != 0 || ep.op_count != 0)
+    gemm_dense_kernel<true><<<grid, kNumThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, c, m, n, k, ldc, idesc,
+                                                                       tiles_m, tiles_n, group_n, b_layout, ep,
+                                                                       status);
+  else
+    gemm_dense_kernel<false><<<grid, kNumThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, c, m, n, k, ldc, idesc,
+                                                                        tiles_m, tiles_n, group_n, b_layout, ep,
+                                                                        status);
   return cudaGetLastError();
 }
 

@@ -66,6 +66,94 @@ __device__ __forceinline__ float4 finish_group(float4 v, const float *dst, int c
   return v;
 }
 
+// The operations alone, on four values whose bias (if any) has already been fetched.
+__device__ __forceinline__ float4 apply_ops(float4 v, float4 bias, const Epilogue &ep) {
+#pragma unroll
+  for (int i = 0; i < kMaxEpilogueOps; ++i) {
+    if (i < ep.op_count) {
+      const int kind = ep.op_kind[i];
+      const float s = ep.op_value[i];
+      const float4 x = kind == kEpilogueBiasColumn ? bias : make_float4(s, s, s, s);
+      if (kind == kEpilogueScale) {
+        v.x *= x.x; v.y *= x.y; v.z *= x.z; v.w *= x.w;
+      } else if (kind == kEpilogueMax) {
+        v.x = fmaxf(v.x, x.x); v.y = fmaxf(v.y, x.y); v.z = fmaxf(v.z, x.z); v.w = fmaxf(v.w, x.w);
+      } else if (kind == kEpilogueMin) {
+        v.x = fminf(v.x, x.x); v.y = fminf(v.y, x.y); v.z = fminf(v.z, x.z); v.w = fminf(v.w, x.w);
+      } else {
+        v.x += x.x; v.y += x.y; v.z += x.z; v.w += x.w;
+      }
+    }
+  }
+  return v;
+}
+
+// The operations on the eight groups a lane stores per chunk. The kind of each operation is the
+// same for the whole grid, so it is branched on once per chunk and the work inside is one
+// instruction per value. `bias_of(i)` gives the four bias values of group i.
+template <typename BiasFn>
+__device__ __forceinline__ void apply_ops_to_groups(float4 (&v)[8], const Epilogue &ep, BiasFn bias_of) {
+#pragma unroll
+  for (int op = 0; op < kMaxEpilogueOps; ++op) {
+    if (op >= ep.op_count)
+      break;
+    const int kind = ep.op_kind[op];
+    const float x = ep.op_value[op];
+    if (kind == kEpilogueScale) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        v[i].x *= x; v[i].y *= x; v[i].z *= x; v[i].w *= x;
+      }
+    } else if (kind == kEpilogueAdd) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        v[i].x += x; v[i].y += x; v[i].z += x; v[i].w += x;
+      }
+    } else if (kind == kEpilogueMax) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        v[i].x = fmaxf(v[i].x, x); v[i].y = fmaxf(v[i].y, x); v[i].z = fmaxf(v[i].z, x); v[i].w = fmaxf(v[i].w, x);
+      }
+    } else if (kind == kEpilogueMin) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        v[i].x = fminf(v[i].x, x); v[i].y = fminf(v[i].y, x); v[i].z = fminf(v[i].z, x); v[i].w = fminf(v[i].w, x);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float4 b = bias_of(i);
+        v[i].x += b.x; v[i].y += b.y; v[i].z += b.z; v[i].w += b.w;
+      }
+    }
+  }
+}
+
+// Previous contents of four consecutive elements of C starting at column `col` (zeros past n).
+// `aligned`: dst is 16-byte aligned, so a full group is one 128-bit load.
+__device__ __forceinline__ float4 load_previous(const float *dst, int col, int n, bool aligned) {
+  if (aligned && col + 3 < n)
+    return __ldcs(reinterpret_cast<const float4 *>(dst));
+  float4 old = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  if (col < n) old.x = __ldcs(dst);
+  if (col + 1 < n) old.y = __ldcs(dst + 1);
+  if (col + 2 < n) old.z = __ldcs(dst + 2);
+  if (col + 3 < n) old.w = __ldcs(dst + 3);
+  return old;
+}
+
+// With an accumulating kernel the epilogue reads C before it writes it. Each lane asks for the
+// lines of its row of the tile to be brought into L2 while the tile's products are still being
+// accumulated, so that those reads do not wait on DRAM.
+__device__ __forceinline__ void prefetch_c_tile_row(const float *c, long long ldc, int m, int n, int row,
+                                                    int col_base, int columns) {
+  if (row >= m)
+    return;
+  const float *p = c + static_cast<long long>(row) * ldc;
+  for (int col = col_base; col < col_base + columns && col < n; col += 32)
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(p + col));
+}
+
 // Stages this lane's 32 values with the row rotated left by kShift elements, so that the
 // 16-byte groups of the row *in memory* (which start kShift elements into the chunk) land on
 // 16-byte pieces of the staging block.
@@ -82,6 +170,7 @@ __device__ __forceinline__ void stage_row_shifted(const uint32_t (&r)[32], float
 // Writes one 32-column chunk (already in registers, lane = row) of this warp's 32 rows to C.
 // `carry` holds the last three values of this lane's row from the previous chunk (odd-pitch
 // path only); `last_chunk` says that no further chunk of the tile follows.
+template <bool kFused>
 __device__ __forceinline__ void write_chunk(const uint32_t (&r)[32], int chunk, bool last_chunk, float *buf,
                                             float *__restrict__ c, long long ldc, int m, int n,
                                             int row_base, int col_base, bool vec_ok, int lane,
@@ -90,40 +179,71 @@ __device__ __forceinline__ void write_chunk(const uint32_t (&r)[32], int chunk, 
   if (col0 >= n)
     return;  // warp-uniform
   const int piece = lane & 7;
-  const bool fused = ep.accumulate != 0 || ep.op_count != 0;  // grid-uniform
+  constexpr bool fused = kFused;  // the plain kernel carries none of the fused work
+  // One bias value per lane (column col0 + lane); groups fetch theirs by shuffle.
+  float bias_lane = 0.0f;
+  if (fused && ep.bias != nullptr && col0 + lane < n)
+    bias_lane = __ldg(ep.bias + col0 + lane);
   if (vec_ok) {
+    const int col = col0 + piece * 4;
+    // Everything that has to be read comes first, so that the reads of all eight row groups are
+    // in flight together instead of one after each store.
+    float4 previous[8];
+    float4 bias = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (fused) {
+      bias = make_float4(__shfl_sync(0xffffffffu, bias_lane, piece * 4), __shfl_sync(0xffffffffu, bias_lane, piece * 4 + 1),
+                         __shfl_sync(0xffffffffu, bias_lane, piece * 4 + 2), __shfl_sync(0xffffffffu, bias_lane, piece * 4 + 3));
+      if (ep.accumulate) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int row = row_base + i * 4 + (lane >> 3);
+          previous[i] = row < m ? load_previous(c + static_cast<long long>(row) * ldc + col, col, n, true)
+                                : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        }
+      }
+    }
     stage_row_shifted<0>(r, buf, lane);
     __syncwarp();
-    const int col = col0 + piece * 4;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int rr = i * 4 + (lane >> 3);
-      const int row = row_base + rr;
-      float4 v = *reinterpret_cast<const float4 *>(buf + rr * 32 + ((piece ^ (rr & 7)) << 2));
+    auto store_group_of_row = [&](int i, const float4 &value) {
+      const int row = row_base + i * 4 + (lane >> 3);
       if (row < m) {
         const long long offset = static_cast<long long>(row) * ldc + col;
         float *dst = c + offset;
         if (col + 3 < n) {
-          if (fused)
-            v = finish_group(v, dst, col, ep);
-          __stcs(reinterpret_cast<float4 *>(dst), v);
+          __stcs(reinterpret_cast<float4 *>(dst), value);
           // The same 128-byte row segments go to every push target (peer GPUs' copies of C).
           for (int t = 0; t < ep.push_count; ++t)
-            __stcs(reinterpret_cast<float4 *>(ep.push[t] + offset), v);
+            __stcs(reinterpret_cast<float4 *>(ep.push[t] + offset), value);
         } else {
-          if (fused) {
-            if (col < n) v.x = finish_value(v.x, dst, col, ep);
-            if (col + 1 < n) v.y = finish_value(v.y, dst + 1, col + 1, ep);
-            if (col + 2 < n) v.z = finish_value(v.z, dst + 2, col + 2, ep);
-          }
           for (int t = -1; t < ep.push_count; ++t) {
             float *edge = t < 0 ? dst : ep.push[t] + offset;
-            if (col < n) __stcs(edge, v.x);
-            if (col + 1 < n) __stcs(edge + 1, v.y);
-            if (col + 2 < n) __stcs(edge + 2, v.z);
+            if (col < n) __stcs(edge, value.x);
+            if (col + 1 < n) __stcs(edge + 1, value.y);
+            if (col + 2 < n) __stcs(edge + 2, value.z);
           }
         }
       }
+    };
+    if constexpr (!kFused) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int rr = i * 4 + (lane >> 3);
+        store_group_of_row(i, *reinterpret_cast<const float4 *>(buf + rr * 32 + ((piece ^ (rr & 7)) << 2)));
+      }
+    } else {
+      float4 v[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int rr = i * 4 + (lane >> 3);
+        v[i] = *reinterpret_cast<const float4 *>(buf + rr * 32 + ((piece ^ (rr & 7)) << 2));
+        if (ep.accumulate) {
+          v[i].x += previous[i].x; v[i].y += previous[i].y; v[i].z += previous[i].z; v[i].w += previous[i].w;
+        }
+      }
+      apply_ops_to_groups(v, ep, [&](int) { return bias; });
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        store_group_of_row(i, v[i]);
     }
   } else {
     // C's rows do not start on 16-byte boundaries (odd pitch or base). For row r, `shift(r)`
@@ -195,22 +315,57 @@ __device__ __forceinline__ void write_chunk(const uint32_t (&r)[32], int chunk, 
       carry[2] = __uint_as_float(r[31]);
     }
     __syncwarp();
+    // The staged groups: reads of all eight row groups first, then the stores.
+    float4 previous[8];
+    if (fused && ep.accumulate) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+      for (int i = 0; i < 8; ++i) {
+        const int rr = i * 4 + (lane >> 3);
+        const int e0 = shift_of(rr) + piece * 4;
+        previous[i] = (row_base + rr < m && e0 + 3 < 32)
+                          ? load_previous(tile_dst + static_cast<long long>(rr) * ldc + e0, col0 + e0, n, true)
+                          : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      }
+    }
+    auto store_staged_group = [&](int i, const float4 &value) {
       const int rr = i * 4 + (lane >> 3);
-      const int shift = shift_of(rr);
-      const float4 v = *reinterpret_cast<const float4 *>(buf + rr * 32 + ((piece ^ (rr & 7)) << 2));
-      const int e0 = shift + piece * 4;
+      const int e0 = shift_of(rr) + piece * 4;
       if (row_base + rr < m && e0 + 3 < 32) {
         float *dst = tile_dst + static_cast<long long>(rr) * ldc + e0;
         if (col0 + e0 + 3 < n) {
-          store_group(dst, v, col0 + e0);
+          __stcs(reinterpret_cast<float4 *>(dst), value);
         } else {
-          if (col0 + e0 < n) store_value(dst, v.x, col0 + e0);
-          if (col0 + e0 + 1 < n) store_value(dst + 1, v.y, col0 + e0 + 1);
-          if (col0 + e0 + 2 < n) store_value(dst + 2, v.z, col0 + e0 + 2);
+          if (col0 + e0 < n) __stcs(dst, value.x);
+          if (col0 + e0 + 1 < n) __stcs(dst + 1, value.y);
+          if (col0 + e0 + 2 < n) __stcs(dst + 2, value.z);
         }
       }
+    };
+    if constexpr (!kFused) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int rr = i * 4 + (lane >> 3);
+        store_staged_group(i, *reinterpret_cast<const float4 *>(buf + rr * 32 + ((piece ^ (rr & 7)) << 2)));
+      }
+    } else {
+      float4 v[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int rr = i * 4 + (lane >> 3);
+        v[i] = *reinterpret_cast<const float4 *>(buf + rr * 32 + ((piece ^ (rr & 7)) << 2));
+        if (ep.accumulate) {
+          v[i].x += previous[i].x; v[i].y += previous[i].y; v[i].z += previous[i].z; v[i].w += previous[i].w;
+        }
+      }
+      apply_ops_to_groups(v, ep, [&](int i) {
+        // (e0 + j) & 31: lanes whose group is skipped below still take part in the shuffles.
+        const int e0 = shift_of(i * 4 + (lane >> 3)) + piece * 4;
+        return make_float4(__shfl_sync(0xffffffffu, bias_lane, e0 & 31), __shfl_sync(0xffffffffu, bias_lane, (e0 + 1) & 31),
+                           __shfl_sync(0xffffffffu, bias_lane, (e0 + 2) & 31), __shfl_sync(0xffffffffu, bias_lane, (e0 + 3) & 31));
+      });
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        store_staged_group(i, v[i]);
     }
   }
   __syncwarp();
@@ -221,7 +376,7 @@ __device__ __forceinline__ void write_chunk(const uint32_t (&r)[32], int chunk, 
 //
 // The TMEM load of the next chunk is in flight while the current chunk is transposed and
 // stored (two register sets alternate), so the TMEM latency is hidden behind the stores.
-template <int kColumns>
+template <int kColumns, bool kFused>
 __device__ __forceinline__ void drain_accumulator_rows(uint32_t taddr, float *stage, float *__restrict__ c,
                                                        long long ldc, int m, int n, int row_base,
                                                        int col_base, bool vec_ok, int lane,
@@ -236,7 +391,7 @@ __device__ __forceinline__ void drain_accumulator_rows(uint32_t taddr, float *st
   for (int chunk = 0; chunk < kChunks; chunk += 2) {
     tmem_load_wait_for(ra);
     tmem_load_32x32b_x32(taddr + (chunk + 1) * 32, rb);
-    write_chunk(ra, chunk, false, stage, c, ldc, m, n, row_base, col_base, vec_ok, lane, carry, ep);
+    write_chunk<kFused>(ra, chunk, false, stage, c, ldc, m, n, row_base, col_base, vec_ok, lane, carry, ep);
     tmem_load_wait_for(rb);
     if (chunk + 2 < kChunks) {
       tmem_load_32x32b_x32(taddr + (chunk + 2) * 32, ra);
@@ -251,7 +406,7 @@ __device__ __forceinline__ void drain_accumulator_rows(uint32_t taddr, float *st
           mbar_arrive(release_bar);
       }
     }
-    write_chunk(rb, chunk + 1, chunk + 2 >= kChunks, stage, c, ldc, m, n, row_base, col_base, vec_ok, lane, carry, ep);
+    write_chunk<kFused>(rb, chunk + 1, chunk + 2 >= kChunks, stage, c, ldc, m, n, row_base, col_base, vec_ok, lane, carry, ep);
   }
 }
 

@@ -202,6 +202,14 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int split = unit / n_tiles;
       const uint32_t acc = iter & 1u;
       const uint32_t acc_phase = (iter >> 1) & 1u;
+      if (ep.accumulate && splits == 1) {
+        // C is read before it is written: fetch this warp's 128-byte piece of every row into L2
+        // while B is still streaming (one lane per row).
+        const int first_col = n_tile * kBlockN + quarter * 32;
+        for (int mm = lane; mm < m; mm += 32)
+          if (first_col < n)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(c + static_cast<long long>(mm) * ldc + first_col));
+      }
       const bool ready = mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag);
       if (!__all_sync(0xffffffffu, ready))
         break;
@@ -227,13 +235,30 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int col = n_tile * kBlockN + quarter * 32 + lane;
       const bool fused = ep.accumulate != 0 || ep.op_count != 0;
       if (splits == 1) {
+        if (!fused) {
 #pragma unroll
-        for (int mm = 0; mm < kMp; ++mm)
-          if (mm < m && col < n) {
-            float *dst = c + static_cast<long long>(mm) * ldc + col;
-            const float v = __uint_as_float(r[mm]);
-            __stcs(dst, fused ? finish_value(v, dst, col, ep) : v);
-          }
+          for (int mm = 0; mm < kMp; ++mm)
+            if (mm < m && col < n)
+              __stcs(c + static_cast<long long>(mm) * ldc + col, __uint_as_float(r[mm]));
+          continue;
+        }
+        // Reads first (the previous contents of eight rows, the bias once), then the stores.
+        const float bias = (ep.bias != nullptr && col < n) ? __ldg(ep.bias + col) : 0.0f;
+#pragma unroll
+        for (int mm0 = 0; mm0 < kMp; mm0 += 8) {
+          float previous[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            previous[j] = (ep.accumulate && mm0 + j < m && col < n)
+                              ? __ldcs(c + static_cast<long long>(mm0 + j) * ldc + col) : 0.0f;
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            if (mm0 + j < m && col < n) {
+              const float4 v = apply_ops(make_float4(__uint_as_float(r[mm0 + j]) + previous[j], 0.0f, 0.0f, 0.0f),
+                                         make_float4(bias, 0.0f, 0.0f, 0.0f), ep);
+              __stcs(c + static_cast<long long>(mm0 + j) * ldc + col, v.x);
+            }
+        }
         continue;
       }
       float *my_partial = partials + static_cast<size_t>(split) * m * n_pad + col;
@@ -252,10 +277,15 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a,
         // Every split of this 32-column block has published its partial sums.
         __threadfence();
         const float *col_partials = partials + col;
+        const float bias = (fused && ep.bias != nullptr && col < n) ? __ldg(ep.bias + col) : 0.0f;
         // Eight rows at a time, their loads issued together: the additions of one row stay in
         // split order, but the L2 round trips of different rows and splits overlap.
         for (int mm0 = 0; mm0 < m; mm0 += 8) {
-          float sums[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+          float sums[8];  // an accumulating kernel's sums start from C
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            sums[j] = (ep.accumulate && mm0 + j < m && col < n)
+                          ? __ldcs(c + static_cast<long long>(mm0 + j) * ldc + col) : 0.0f;
 #pragma unroll 4
           for (int s = 0; s < splits; ++s) {
             float part[8];
@@ -270,8 +300,9 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
             for (int j = 0; j < 8; ++j)
               if (mm0 + j < m) {
-                float *dst = c + static_cast<long long>(mm0 + j) * ldc + col;
-                __stcs(dst, fused ? finish_value(sums[j], dst, col, ep) : sums[j]);
+                const float4 v = apply_ops(make_float4(sums[j], 0.0f, 0.0f, 0.0f),
+                                           make_float4(bias, 0.0f, 0.0f, 0.0f), ep);
+                __stcs(c + static_cast<long long>(mm0 + j) * ldc + col, fused ? v.x : sums[j]);
               }
           }
         }

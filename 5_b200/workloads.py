@@ -121,21 +121,46 @@ def make_sharded_inputs(col_begin: int, col_end: int, *, m: int | None = None, k
 
 
 def check_against_float64(c: np.ndarray, a: np.ndarray, b: np.ndarray, *,
-                          rows: np.ndarray | None = None) -> dict[str, float | bool]:
+                          rows: np.ndarray | None = None, c0: np.ndarray | None = None,
+                          epilogue: tuple = (), bias: np.ndarray | None = None) -> dict[str, float | bool]:
     """The benchmark's parity rule, versus a float64 product of the same low-precision inputs:
     relative Frobenius error <= 1e-3 and, element-wise, |C - ref| <= 1e-2 * (|A| |B|).
 
     `rows` restricts the check to a sample of rows (the reference product of a large problem
     is computed on the CPU, so the sample bounds host time); the result says how many rows
     were checked.
+
+    For the other members of the kernel family the reference value is ops(C0 + A.B): `c0` is C
+    before the launch (accumulating member), `epilogue` the element-wise operations in order
+    (("scale", x), ("add", x), ("max", x), ("min", x), ("bias",)) and `bias` the per-column
+    vector. The element bound is carried through them (|C0| and the added constants join it,
+    a scale multiplies it, max/min leave it).
     """
     if rows is not None:
         a = a[rows]
         c = c[rows]
+        c0 = None if c0 is None else c0[rows]
     a64 = a.astype(np.float64)
     b64 = b.astype(np.float64)
     ref = a64 @ b64
     bound = np.abs(a64) @ np.abs(b64)
+    if c0 is not None:
+        ref = ref + c0
+        bound = bound + np.abs(c0)
+    for op in epilogue:
+        x = float(np.float32(op[1])) if len(op) > 1 else 0.0
+        if op[0] == "scale":
+            ref, bound = ref * x, bound * abs(x)
+        elif op[0] == "add":
+            ref, bound = ref + x, bound + abs(x)
+        elif op[0] == "bias":
+            ref, bound = ref + bias[None, :], bound + np.abs(bias)[None, :]
+        elif op[0] == "max":
+            ref = np.maximum(ref, x)
+        elif op[0] == "min":
+            ref = np.minimum(ref, x)
+        else:
+            raise ValueError(f"unknown operation {op[0]!r}")
     diff = np.abs(c.astype(np.float64) - ref)
     rel_fro = float(np.linalg.norm(diff) / max(np.linalg.norm(ref), 1e-300))
     with np.errstate(divide="ignore", invalid="ignore"):

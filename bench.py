@@ -337,10 +337,6 @@ def run_gpu_arm(args, ranks: Ranks) -> None:
     name = choose_workload(args, ranks.world)
     w = workloads.CONFIGS[name]
     ctx = cuda.Context(ranks.local_rank)
-    handle = compiled_for(w.dtype, ranks.local_rank)
-    if handle.plan is None:
-        raise SystemExit(f"kernel not recognised: {handle.pipeline_diagnostics}")
-
     # ---- inputs -------------------------------------------------------------------------
     if name == "sharded":
         slab = column_slab(w.n, ranks.world, ranks.rank, align=workloads.SHARDED_BLOCK_COLUMNS)
@@ -354,10 +350,21 @@ def run_gpu_arm(args, ranks: Ranks) -> None:
     m, k = w.m, w.k
     bt = np.ascontiguousarray(b.T) if args.b_transposed else None
     da, db = ctx.to_device(a), ctx.to_device(bt if args.b_transposed else b)
-    handle = compiled_for(w.dtype, ranks.local_rank, args.b_transposed)
-    gemm_kwargs = {"b_transposed": True} if args.b_transposed else {}
+    handle = compiled_for(w.dtype, ranks.local_rank, args.b_transposed, args.member)
+    if handle.plan is None:
+        raise SystemExit(f"kernel not recognised: {handle.pipeline_diagnostics}")
+    contract = handle.plan
+    bias = dbias = None
+    if contract.bias_param is not None:
+        bias = np.random.default_rng(99).standard_normal(local_n).astype(np.float32)
+        dbias = ctx.to_device(bias)
+    gemm_kwargs = {"b_transposed": args.b_transposed, "accumulate": contract.accumulate,
+                   "epilogue": contract.epilogue, "bias": dbias}
+    member_check = {"epilogue": contract.epilogue, "bias": bias}
     dc = ctx.empty((m, local_n), np.float32)
-    plan = ctx.plan(m, local_n, k, w.dtype, b_transposed=args.b_transposed)
+    dc.fill_bytes(0)
+    plan = ctx.plan(m, local_n, k, w.dtype, b_transposed=args.b_transposed, accumulate=contract.accumulate,
+                    epilogue=contract.epilogue)
     local_flops = workloads.flops(m, local_n, k)
     total_flops = workloads.flops(w.m, w.n, w.k)
 
@@ -398,9 +405,14 @@ def run_gpu_arm(args, ranks: Ranks) -> None:
     kernel_tflops = local_flops / (ms_per_step * 1e-3) / 1e12
 
     # ---- correctness of what was timed (sampled rows, float64 rule) ------------------------
+    if contract.accumulate:
+        # The timed launches kept adding to C; check one launch on top of zeros.
+        dc.fill_bytes(0)
+        ctx.gemm(da, db, dc, **gemm_kwargs)
+        ctx.synchronize()
     c = dc.to_numpy()
     rows = np.unique(np.linspace(0, m - 1, 16).astype(np.int64))
-    parity = workloads.check_against_float64(c, a, b, rows=rows)
+    parity = workloads.check_against_float64(c, a, b, rows=rows, **member_check)
     parity_all = ranks.gather_objects(parity)
 
     # ---- end to end through the public handle on pinned host buffers ---------------------
@@ -420,19 +432,25 @@ def run_gpu_arm(args, ranks: Ranks) -> None:
     pc = cuda.pinned_empty((m, local_n), np.float32)
     pa[...] = a
     pb[...] = host_b
-    handle(pa, pb, pc)  # warm-up: allocates the context's staging buffers
+    pc[...] = 0
+    call_args = (pa, pb, pc) if bias is None else (pa, pb, pc, bias)
+    handle(*call_args)  # warm-up: allocates the context's staging buffers
     default_ctx = cuda.default_context(ranks.local_rank)
     e0, e1 = default_ctx.event(), default_ctx.event()
     ranks.barrier()
     default_ctx.synchronize()
     e0.record()
     for _ in range(e2e_steps):
-        handle(pa, pb, pc)
+        handle(*call_args)
     e1.record()
     e2e_ms = ranks.max(e1.elapsed_ms_since(e0)) / e2e_steps
-    e2e_ok = bool(np.array_equal(pc[rows], c[rows]))
+    if contract.accumulate:  # the host C has taken the product 1 + e2e_steps times
+        e2e_ok = bool(np.allclose(pc[rows], (1 + e2e_steps) * c[rows], rtol=1e-4, atol=1e-5))
+    else:
+        e2e_ok = bool(np.array_equal(pc[rows], c[rows]))
+    h2d_bytes = a.nbytes + b.nbytes + (pc.nbytes if contract.accumulate else 0) + (0 if bias is None else bias.nbytes)
     e2e = {"value": total_flops / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_ms,
-           "steps": e2e_steps, "h2d_bytes_per_step": int(a.nbytes + b.nbytes),
+           "steps": e2e_steps, "h2d_bytes_per_step": int(h2d_bytes),
            "d2h_bytes_per_step": int(pc.nbytes), "matches_device_path": e2e_ok,
            "api": "hc.compile(kernel, target='nvidia-sm100a')(a, b, c) on pinned NumPy arrays"}
     sampler.stop()
@@ -511,6 +529,7 @@ def run_gpu_arm(args, ranks: Ranks) -> None:
     peaks, peaks_source = measured_peaks()
     if plan.variant == "skinny":
         algo_bytes = workloads.algorithmic_bytes(m, local_n, k)
+        algo_bytes += (4 * m * local_n if contract.accumulate else 0) + (0 if bias is None else bias.nbytes)
         achieved = algo_bytes / (ms_per_step * 1e-3) / 1e9
         peak = float(peaks["hbm_gbs"])
         roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
@@ -541,6 +560,7 @@ def run_gpu_arm(args, ranks: Ranks) -> None:
         "config": {"workload": name, "m": w.m, "n": w.n, "k": w.k, "input_dtype": w.dtype,
                    "accumulate": "fp32", "variant": plan.variant, "per_gpu_n": local_n,
                    "b_layout": "[N, K] (transposed)" if args.b_transposed else "[K, N]",
+                   "member": args.member,
                    "parallelism": f"n-sharded x{ranks.world}" if ranks.world > 1 else "single GPU",
                    "l2": "inputs larger than L2 (A+B+C per GPU exceed 126 MB)"
                    if a.nbytes + b.nbytes + c.nbytes > 126e6 else "working set fits L2",
@@ -581,6 +601,9 @@ def main() -> int:
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--b-transposed", action="store_true",
                         help="hand B over stored [N, K] and use the Buffer[N, K] member of the kernel family")
+    parser.add_argument("--member", choices=("plain", "accumulate", "fused"), default="plain",
+                        help="kernel family member: C = A.B (the reference example, default), C += A.B, or "
+                             "C = maximum(0.125 * A.B + bias, 0) folded into the store")
     parser.add_argument("--cublas", action="store_true",
                         help="also time cuBLAS (torch.mm) on the same inputs with the same loop, for context")
     parser.add_argument("--quick", action="store_true",
@@ -588,8 +611,10 @@ def main() -> int:
     args = parser.parse_args()
     if args.steps < 1:
         parser.error("--steps must be at least 1")
-    if args.b_transposed and args.gpus > 1:
-        parser.error("--b-transposed is a single-GPU measurement")
+    if (args.b_transposed or args.member != "plain") and args.gpus > 1:
+        parser.error("--b-transposed and --member are single-GPU measurements")
+    if args.b_transposed and args.member != "plain":
+        parser.error("the transposed-B example is built as the plain member only")
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.gpus > 1 and world == 1 and args.impl != "reference":
