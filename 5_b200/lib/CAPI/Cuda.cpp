@@ -110,6 +110,7 @@ struct HcCudaContext {
   cudaEvent_t fence_event = nullptr;
   EncodeTiledFn encode = nullptr;
   int group_n = 8;
+  bool c_tma_store = true;  // HC_CUDA_C_TMA_STORE=0 keeps ordinary stores (tuning aid)
   ncclComm_t comm = nullptr;
   int nranks = 0;
   int rank = -1;
@@ -343,14 +344,17 @@ int ensure_stage(HcCudaContext *ctx, int which, size_t bytes) {
   return HC_CUDA_OK;
 }
 
+constexpr int kMapFloat32 = -1;  // encode_map's dtype for C; otherwise an HcCudaDType
+
 int encode_map(HcCudaContext *ctx, CUtensorMap *map, int dtype, const void *base, uint64_t inner,
                uint64_t outer, uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_outer) {
   const cuuint64_t dims[2] = {inner, outer};
   const cuuint64_t strides[1] = {pitch_bytes};
   const cuuint32_t box[2] = {box_inner, box_outer};
   const cuuint32_t elem_strides[2] = {1, 1};
-  const CUtensorMapDataType type =
-      dtype == HC_CUDA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const CUtensorMapDataType type = dtype == kMapFloat32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                   : dtype == HC_CUDA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                           : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   const CUresult res = ctx->encode(map, type, 2, const_cast<void *>(base), dims, strides, box,
                                    elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
                                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -444,14 +448,23 @@ int enqueue_gemm(HcCudaContext *ctx, const HcCudaGemmArgs *args, const HcCudaGem
                       : encode_map(ctx, &tmap_b, args->dtype, b, n, k, static_cast<uint64_t>(ldb) * 2, 64,
                                    t.block_k))
       return rc;
+    // C leaves through TMA stores when its rows start on 16-byte boundaries (the launcher falls
+    // back to ordinary stores for fused work and push targets).
+    CUtensorMap tmap_c;
+    const CUtensorMap *c_map = nullptr;
+    if ((args->ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(args->c) & 15) == 0 && ctx->c_tma_store) {
+      if (int rc = encode_map(ctx, &tmap_c, kMapFloat32, args->c, n, m, static_cast<uint64_t>(args->ldc) * 4, 32, 32))
+        return rc;
+      c_map = &tmap_c;
+    }
     if (pairs) {
       HC_TRY_CUDA(ctx, hc::sm100::launch_gemm_dense_pair(tmap_a, tmap_b, args->c, m, n, k, args->ldc,
                                                          args->dtype, ctx->group_n, plan.grid, b_layout, ep,
-                                                         ctx->status_dev, ctx->stream));
+                                                         c_map, ctx->status_dev, ctx->stream));
     } else {
       HC_TRY_CUDA(ctx, hc::sm100::launch_gemm_dense(tmap_a, tmap_b, args->c, m, n, k, args->ldc,
                                                     args->dtype, ctx->group_n, plan.grid, b_layout, ep,
-                                                    ctx->status_dev, ctx->stream));
+                                                    c_map, ctx->status_dev, ctx->stream));
     }
     return HC_CUDA_OK;
   }
@@ -595,6 +608,8 @@ int hcCudaContextCreate(int device, HcCudaContext **out) {
     if (v >= 1)
       ctx->group_n = v;
   }
+  if (const char *t = std::getenv("HC_CUDA_C_TMA_STORE"))
+    ctx->c_tma_store = std::atoi(t) != 0;
   *out = ctx;
   return HC_CUDA_OK;
 }

@@ -45,8 +45,17 @@ constexpr int kBlockK = HC_PAIR_BLOCK_K;  // k extent of one ring stage: 64 or 1
 constexpr int kKSub = kBlockK / 64;       // 64-wide (one swizzle row) sub-blocks per stage
 constexpr int kUmmaK = 16;
 constexpr int kStages = 6 / kKSub;
-constexpr int kNumThreads = 192;
-constexpr int kNumEpilogueWarps = 4;
+// Warp 0 loads, warp 1 issues the MMAs, the rest drain accumulators. The plain kernel has eight
+// epilogue warps: two per 32-lane quarter of tensor memory, each taking half of the tile's columns,
+// so that every scheduler has two of them to interleave (a lone warp per scheduler exposes every
+// latency of its chunk loop, which is what bounds shapes with a short k-loop). The fused kernel
+// needs more registers per thread and keeps four.
+constexpr int kMaxEpilogueWarps = 8;
+template <bool kFused>
+struct Roles {
+  static constexpr int kEpilogueWarps = kFused ? 4 : 8;
+  static constexpr int kThreads = 64 + 32 * kEpilogueWarps;
+};
 constexpr int kTmemColumns = 512;  // two accumulators of kTileN fp32 columns
 
 constexpr uint32_t kASubBytes = kCtaM * 64 * 2;                   // 128 rows x 64 k: 16 KiB
@@ -57,8 +66,9 @@ constexpr uint32_t kBTileBytes = kBChunkBytes * (kCtaN / 64);
 constexpr uint32_t kStageBytes = kATileBytes + kBTileBytes;       // 32 KiB per CTA at kBlockK = 64
 constexpr uint32_t kEpilogueWarpBytes = 32 * 32 * 4;
 constexpr uint32_t kBarrierBytes = 256;
-constexpr uint32_t kSmemBytes = kStages * kStageBytes + kNumEpilogueWarps * kEpilogueWarpBytes +
+constexpr uint32_t kSmemBytes = kStages * kStageBytes + kMaxEpilogueWarps * kEpilogueWarpBytes +
                                 kBarrierBytes + 1024;
+static_assert(kSmemBytes <= 227 * 1024, "dynamic shared memory of one CTA");
 
 struct TileCoord {
   int m_blk;
@@ -81,9 +91,10 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int tiles_m, int tiles
 // plain instantiation is the reference example's C = A.B and compiles to the same code as before
 // that work existed.
 template <bool kFused>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Roles<kFused>::kThreads, 1)
 gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                       const __grid_constant__ CUtensorMap tmap_b, float *__restrict__ c, int m, int n,
+                       const __grid_constant__ CUtensorMap tmap_b,
+                       const __grid_constant__ CUtensorMap tmap_c, int c_tma, float *__restrict__ c, int m, int n,
                        int k, long long ldc, uint32_t idesc, int tiles_m, int tiles_n, int group_n,
                        int l2_hints, int b_layout, Epilogue ep, int *status) {
   extern __shared__ uint8_t smem_raw[];
@@ -92,7 +103,9 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
   uint8_t *smem_gen = smem_raw + (smem_base - raw_addr);
 
   const uint32_t epi_base = smem_base + kStages * kStageBytes;
-  const uint32_t bar_base = epi_base + kNumEpilogueWarps * kEpilogueWarpBytes;
+  constexpr int kEpilogueWarps = Roles<kFused>::kEpilogueWarps;
+  constexpr int kColumnsPerWarp = kTileN * 4 / kEpilogueWarps;  // 4 quarters of lanes share the warps
+  const uint32_t bar_base = epi_base + kMaxEpilogueWarps * kEpilogueWarpBytes;
   auto full_bar = [&](uint32_t s) { return bar_base + 8u * s; };
   auto empty_bar = [&](uint32_t s) { return bar_base + 8u * (kStages + s); };
   auto tmem_full_bar = [&](uint32_t a) { return bar_base + 8u * (2 * kStages + a); };
@@ -112,7 +125,7 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     for (uint32_t a = 0; a < 2; ++a) {
       mbar_init(tmem_full_bar(a), 1);
-      mbar_init(tmem_empty_bar(a), 2 * kNumEpilogueWarps);
+      mbar_init(tmem_empty_bar(a), 2 * kEpilogueWarps);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -233,7 +246,8 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
   } else {
     // ------------------------------------------------------------ epilogue ----------
-    const int quarter = warp & 3;
+    const int quarter = warp & 3;                // the TMEM lanes a warp may read follow warp % 4
+    const int column_part = (warp - 2) >> 2;     // which share of the tile's columns it drains
     float *stage_gen = reinterpret_cast<float *>(smem_gen + (epi_base - smem_base) +
                                                  (warp - 2) * kEpilogueWarpBytes);
     const bool vec_ok = ((ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(c) & 15) == 0);
@@ -243,17 +257,21 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const uint32_t acc = iter & 1u;
       const uint32_t acc_phase = (iter >> 1) & 1u;
       const int row_base = tc.m_blk * kTileM + static_cast<int>(cta_rank) * kCtaM + quarter * 32;
-      const int col_base = tc.n_blk * kTileN;
+      const int col_base = tc.n_blk * kTileN + column_part * kColumnsPerWarp;
       if (kFused && ep.accumulate)
-        prefetch_c_tile_row(c, ldc, m, n, row_base + lane, col_base, kTileN);
+        prefetch_c_tile_row(c, ldc, m, n, row_base + lane, col_base, kColumnsPerWarp);
       const bool ready = mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag);
       if (!__all_sync(0xffffffffu, ready))
         break;
       tcgen05_fence_after_sync();
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kTileN;
-      drain_accumulator_rows<kTileN, kFused>(taddr, stage_gen, c, ldc, m, n, row_base, col_base, vec_ok, lane,
-                                     map_to_cta(tmem_empty_bar(acc), 0), /*release_remote=*/true, ep);
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kTileN +
+                             column_part * kColumnsPerWarp;
+      drain_accumulator_rows<kColumnsPerWarp, kFused>(taddr, stage_gen, c, ldc, m, n, row_base, col_base, vec_ok, lane,
+                                     map_to_cta(tmem_empty_bar(acc), 0), /*release_remote=*/true, ep,
+                                     c_tma ? &tmap_c : nullptr);
     }
+    if (c_tma && lane == 0)
+      tma_store_wait_all();  // shared memory must outlive the stores that read it
   }
 
   // Neither CTA may leave (or free TMEM) while its partner can still read its shared memory,
@@ -277,8 +295,8 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
 cudaError_t launch_gemm_dense_pair(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, float *c,
                                    int m, int n, int k, long long ldc, int dtype, int group_n,
-                                   int max_ctas, int b_layout, const Epilogue &ep, int *status,
-                                   cudaStream_t stream) {
+                                   int max_ctas, int b_layout, const Epilogue &ep, const CUtensorMap *tmap_c,
+                                   int *status, cudaStream_t stream) {
   using namespace dense_pair;
   static thread_local int configured_device = -1;
   int device = 0;
@@ -309,16 +327,20 @@ cudaError_t launch_gemm_dense_pair(const CUtensorMap &tmap_a, const CUtensorMap 
                                         /*b_mn_major=*/b_layout == kBLayoutKN, kTileM, kTileN);
   if (group_n < 1)
     group_n = 1;
+  // TMA stores of C only for the plain product of an aligned C that goes nowhere else.
+  const bool fused_store = ep.accumulate != 0 || ep.op_count != 0;
+  const int c_tma = (tmap_c != nullptr && !fused_store && ep.push_count == 0) ? 1 : 0;
+  const CUtensorMap c_map = c_tma ? *tmap_c : tmap_a;  // unused unless c_tma
   int l2_hints = 3;
   if (const char *h = std::getenv("HC_CUDA_L2_HINTS"))  // tuning aid
     l2_hints = std::atoi(h);
   const unsigned grid = static_cast<unsigned>(clusters * 2);
   if (ep.accumulate != 0 || ep.op_count != 0)
-    gemm_dense_pair_kernel<true><<<grid, kNumThreads, kSmemBytes, stream>>>(
-        tmap_a, tmap_b, c, m, n, k, ldc, idesc, tiles_m, tiles_n, group_n, l2_hints, b_layout, ep, status);
+    gemm_dense_pair_kernel<true><<<grid, Roles<true>::kThreads, kSmemBytes, stream>>>(
+        tmap_a, tmap_b, c_map, c_tma, c, m, n, k, ldc, idesc, tiles_m, tiles_n, group_n, l2_hints, b_layout, ep, status);
   else
-    gemm_dense_pair_kernel<false><<<grid, kNumThreads, kSmemBytes, stream>>>(
-        tmap_a, tmap_b, c, m, n, k, ldc, idesc, tiles_m, tiles_n, group_n, l2_hints, b_layout, ep, status);
+    gemm_dense_pair_kernel<false><<<grid, Roles<false>::kThreads, kSmemBytes, stream>>>(
+        tmap_a, tmap_b, c_map, c_tma, c, m, n, k, ldc, idesc, tiles_m, tiles_n, group_n, l2_hints, b_layout, ep, status);
   return cudaGetLastError();
 }
 

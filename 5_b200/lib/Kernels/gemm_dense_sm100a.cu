@@ -34,8 +34,15 @@ constexpr int kBlockN = 256;
 constexpr int kBlockK = 64;  // 64 x 2 bytes = one 128-byte swizzle row
 constexpr int kUmmaK = 16;
 constexpr int kStages = 4;
-constexpr int kNumThreads = 192;
-constexpr int kNumEpilogueWarps = 4;
+// Warp 0 loads, warp 1 issues the MMAs, the rest drain accumulators: eight warps in the plain
+// kernel (two per quarter of tensor-memory lanes, each half of the tile's columns), four in the
+// fused one, which needs more registers per thread.
+constexpr int kMaxEpilogueWarps = 8;
+template <bool kFused>
+struct Roles {
+  static constexpr int kEpilogueWarps = kFused ? 4 : 8;
+  static constexpr int kThreads = 64 + 32 * kEpilogueWarps;
+};
 constexpr int kTmemColumns = 512;  // two fp32 accumulators of kBlockN columns
 
 constexpr uint32_t kATileBytes = kBlockM * kBlockK * 2;            // 16 KiB
@@ -44,7 +51,7 @@ constexpr uint32_t kBTileBytes = kBChunkBytes * (kBlockN / 64);    // 32 KiB
 constexpr uint32_t kStageBytes = kATileBytes + kBTileBytes;        // 48 KiB
 constexpr uint32_t kEpilogueWarpBytes = 32 * 32 * 4;               // one 32x32 fp32 block
 constexpr uint32_t kBarrierBytes = 256;
-constexpr uint32_t kSmemBytes = kStages * kStageBytes + kNumEpilogueWarps * kEpilogueWarpBytes +
+constexpr uint32_t kSmemBytes = kStages * kStageBytes + kMaxEpilogueWarps * kEpilogueWarpBytes +
                                 kBarrierBytes + 1024 /* alignment slack */;
 
 struct TileCoord {
@@ -68,9 +75,10 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int tiles_m, int tiles
 
 // kFused: the launch has work folded into the store (accumulate, element-wise operations).
 template <bool kFused>
-__global__ void __launch_bounds__(kNumThreads, 1)
+__global__ void __launch_bounds__(Roles<kFused>::kThreads, 1)
 gemm_dense_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                  const __grid_constant__ CUtensorMap tmap_b, float *__restrict__ c, int m, int n,
+                  const __grid_constant__ CUtensorMap tmap_b,
+                       const __grid_constant__ CUtensorMap tmap_c, int c_tma, float *__restrict__ c, int m, int n,
                   int k, long long ldc, uint32_t idesc, int tiles_m, int tiles_n, int group_n,
                   int b_layout, Epilogue ep, int *status) {
   extern __shared__ uint8_t smem_raw[];
@@ -79,7 +87,9 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tmap_a,
   uint8_t *smem_gen = smem_raw + (smem_base - raw_addr);
 
   const uint32_t epi_base = smem_base + kStages * kStageBytes;
-  const uint32_t bar_base = epi_base + kNumEpilogueWarps * kEpilogueWarpBytes;
+  constexpr int kEpilogueWarps = Roles<kFused>::kEpilogueWarps;
+  constexpr int kColumnsPerWarp = kBlockN * 4 / kEpilogueWarps;
+  const uint32_t bar_base = epi_base + kMaxEpilogueWarps * kEpilogueWarpBytes;
   auto full_bar = [&](uint32_t s) { return bar_base + 8u * s; };
   auto empty_bar = [&](uint32_t s) { return bar_base + 8u * (kStages + s); };
   auto tmem_full_bar = [&](uint32_t a) { return bar_base + 8u * (2 * kStages + a); };
@@ -98,7 +108,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     for (uint32_t a = 0; a < 2; ++a) {
       mbar_init(tmem_full_bar(a), 1);
-      mbar_init(tmem_empty_bar(a), kNumEpilogueWarps);
+      mbar_init(tmem_empty_bar(a), kEpilogueWarps);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -200,6 +210,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tmap_a,
   } else {
     // ------------------------------------------------------------ epilogue ----------
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
+    const int column_part = (warp - 2) >> 2;  // which share of the tile's columns this warp drains
     const uint32_t stage_smem = epi_base + (warp - 2) * kEpilogueWarpBytes;
     float *stage_gen = reinterpret_cast<float *>(smem_gen + (stage_smem - smem_base));
     const bool vec_ok = ((ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(c) & 15) == 0);
@@ -209,17 +220,21 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const uint32_t acc = iter & 1u;
       const uint32_t acc_phase = (iter >> 1) & 1u;
       const int row_base = tc.m_blk * kBlockM + quarter * 32;
-      const int col_base = tc.n_blk * kBlockN;
+      const int col_base = tc.n_blk * kBlockN + column_part * kColumnsPerWarp;
       if (kFused && ep.accumulate)
-        prefetch_c_tile_row(c, ldc, m, n, row_base + lane, col_base, kBlockN);
+        prefetch_c_tile_row(c, ldc, m, n, row_base + lane, col_base, kColumnsPerWarp);
       const bool ready = mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag);
       if (!__all_sync(0xffffffffu, ready))
         break;
       tcgen05_fence_after_sync();
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kBlockN;
-      drain_accumulator_rows<kBlockN, kFused>(taddr, stage_gen, c, ldc, m, n, row_base, col_base, vec_ok, lane,
-                                      tmem_empty_bar(acc), /*release_remote=*/false, ep);
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kBlockN +
+                             column_part * kColumnsPerWarp;
+      drain_accumulator_rows<kColumnsPerWarp, kFused>(taddr, stage_gen, c, ldc, m, n, row_base, col_base, vec_ok, lane,
+                                      tmem_empty_bar(acc), /*release_remote=*/false, ep,
+                                     c_tma ? &tmap_c : nullptr);
     }
+    if (c_tma && lane == 0)
+      tma_store_wait_all();  // shared memory must outlive the stores that read it
   }
 
   tcgen05_fence_before_sync();
@@ -243,8 +258,8 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
 cudaError_t launch_gemm_dense(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, float *c,
                               int m, int n, int k, long long ldc, int dtype, int group_n,
-                              int max_ctas, int b_layout, const Epilogue &ep, int *status,
-                              cudaStream_t stream) {
+                              int max_ctas, int b_layout, const Epilogue &ep, const CUtensorMap *tmap_c,
+                              int *status, cudaStream_t stream) {
   using namespace dense;
   static thread_local int configured_device = -1;
   int device = 0;
@@ -271,12 +286,16 @@ cudaError_t launch_gemm_dense(const CUtensorMap &tmap_a, const CUtensorMap &tmap
                                         /*b_mn_major=*/b_layout == kBLayoutKN, kBlockM, kBlockN);
   if (group_n < 1)
     group_n = 1;
+  // TMA stores of C only for the plain product of an aligned C that goes nowhere else.
+  const bool fused_store = ep.accumulate != 0 || ep.op_count != 0;
+  const int c_tma = (tmap_c != nullptr && !fused_store && ep.push_count == 0) ? 1 : 0;
+  const CUtensorMap c_map = c_tma ? *tmap_c : tmap_a;  // unused unless c_tma
   if (ep.accumulate != 0 || ep.op_count != 0)
-    gemm_dense_kernel<true><<<grid, kNumThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, c, m, n, k, ldc, idesc,
+    gemm_dense_kernel<true><<<grid, Roles<true>::kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, c_map, c_tma, c, m, n, k, ldc, idesc,
                                                                        tiles_m, tiles_n, group_n, b_layout, ep,
                                                                        status);
   else
-    gemm_dense_kernel<false><<<grid, kNumThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, c, m, n, k, ldc, idesc,
+    gemm_dense_kernel<false><<<grid, Roles<false>::kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, c_map, c_tma, c, m, n, k, ldc, idesc,
                                                                         tiles_m, tiles_n, group_n, b_layout, ep,
                                                                         status);
   return cudaGetLastError();

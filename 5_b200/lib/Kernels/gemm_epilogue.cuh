@@ -371,6 +371,28 @@ __device__ __forceinline__ void write_chunk(const uint32_t (&r)[32], int chunk, 
   __syncwarp();
 }
 
+// The chunk leaves through the TMA store engine: staged exactly as for the coalesced stores (the
+// XOR of the 16-byte piece with the row is the 128-byte swizzle of the tensor map), then one
+// elected lane issues a 32x32 box store. Rows >= m and columns >= n are clipped by the tensor map.
+// Needs C's base and pitch 16-byte aligned; `buf` is 1024-byte aligned.
+__device__ __forceinline__ void store_chunk_tma(const uint32_t (&r)[32], int chunk, float *buf,
+                                                const CUtensorMap *tmap_c, int m, int n, int row_base,
+                                                int col_base, int lane) {
+  const int col0 = col_base + chunk * 32;
+  if (col0 >= n || row_base >= m)
+    return;  // warp-uniform
+  if (lane == 0)
+    tma_store_wait_read();  // the previous chunk's store has read the buffer
+  __syncwarp();
+  stage_row_shifted<0>(r, buf, lane);
+  fence_proxy_async_smem();
+  __syncwarp();
+  if (lane == 0) {
+    tma_store_2d(tmap_c, smem_u32(buf), col0, row_base);
+    tma_store_commit();
+  }
+}
+
 // `release_bar`: mbarrier (cluster-window address when `release_remote`) that receives one
 // arrival from this warp as soon as the accumulator has been read completely.
 //
@@ -381,17 +403,22 @@ __device__ __forceinline__ void drain_accumulator_rows(uint32_t taddr, float *st
                                                        long long ldc, int m, int n, int row_base,
                                                        int col_base, bool vec_ok, int lane,
                                                        uint32_t release_bar, bool release_remote,
-                                                       const Epilogue &ep) {
+                                                       const Epilogue &ep, const CUtensorMap *tmap_c) {
   constexpr int kChunks = kColumns / 32;
   static_assert(kChunks % 2 == 0, "chunks are processed in pairs");
   uint32_t ra[32], rb[32];
   float carry[3] = {0.0f, 0.0f, 0.0f};
+  // Plain stores of an aligned C go through TMA (`tmap_c` is null otherwise).
+  const bool tma = !kFused && tmap_c != nullptr;
   tmem_load_32x32b_x32(taddr, ra);
 #pragma unroll 1
   for (int chunk = 0; chunk < kChunks; chunk += 2) {
     tmem_load_wait_for(ra);
     tmem_load_32x32b_x32(taddr + (chunk + 1) * 32, rb);
-    write_chunk<kFused>(ra, chunk, false, stage, c, ldc, m, n, row_base, col_base, vec_ok, lane, carry, ep);
+    if (tma)
+      store_chunk_tma(ra, chunk, stage, tmap_c, m, n, row_base, col_base, lane);
+    else
+      write_chunk<kFused>(ra, chunk, false, stage, c, ldc, m, n, row_base, col_base, vec_ok, lane, carry, ep);
     tmem_load_wait_for(rb);
     if (chunk + 2 < kChunks) {
       tmem_load_32x32b_x32(taddr + (chunk + 2) * 32, ra);
@@ -406,7 +433,11 @@ __device__ __forceinline__ void drain_accumulator_rows(uint32_t taddr, float *st
           mbar_arrive(release_bar);
       }
     }
-    write_chunk<kFused>(rb, chunk + 1, chunk + 2 >= kChunks, stage, c, ldc, m, n, row_base, col_base, vec_ok, lane, carry, ep);
+    if (tma)
+      store_chunk_tma(rb, chunk + 1, stage, tmap_c, m, n, row_base, col_base, lane);
+    else
+      write_chunk<kFused>(rb, chunk + 1, chunk + 2 >= kChunks, stage, c, ldc, m, n, row_base, col_base, vec_ok, lane,
+                          carry, ep);
   }
 }
 

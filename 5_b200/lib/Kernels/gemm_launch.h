@@ -58,18 +58,21 @@ DenseTileShape dense_tile_shape();
 // C[m,n] = A * B through the TMA + tcgen05 persistent kernel.
 //   tmap_a: A as a 2-D tensor {k (inner), m}, box {64, 128}, 128-byte swizzle.
 //   tmap_b: B as a 2-D tensor {n (inner), k}, box {64, 64},  128-byte swizzle.
+//   tmap_c: C as a 2-D fp32 tensor {n (inner), m}, box {32, 32}, 128-byte swizzle, or null. When
+//           given (C's base and pitch are 16-byte aligned) and the launch is the plain product
+//           without push targets, the tiles of C leave through TMA stores.
 cudaError_t launch_gemm_dense(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, float *c,
                               int m, int n, int k, long long ldc, int dtype, int group_n,
-                              int max_ctas, int b_layout, const Epilogue &ep, int *status,
-                              cudaStream_t stream);
+                              int max_ctas, int b_layout, const Epilogue &ep, const CUtensorMap *tmap_c,
+                              int *status, cudaStream_t stream);
 
 // Same product on CTA pairs: clusters of two CTAs own 256x256 tiles and issue
 // tcgen05.mma.cta_group::2. Takes the same tensor maps as launch_gemm_dense. `max_ctas` is
 // rounded down to an even number of CTAs.
 cudaError_t launch_gemm_dense_pair(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, float *c,
                                    int m, int n, int k, long long ldc, int dtype, int group_n,
-                                   int max_ctas, int b_layout, const Epilogue &ep, int *status,
-                                   cudaStream_t stream);
+                                   int max_ctas, int b_layout, const Epilogue &ep, const CUtensorMap *tmap_c,
+                                   int *status, cudaStream_t stream);
 
 // Whether the dense variant runs on CTA pairs for this problem.
 bool dense_uses_pairs(long long m, long long n, long long k, int sm_count);

@@ -112,6 +112,31 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap
       : "memory");
 }
 
+// Tile store, shared memory -> global, through the same tensor-map machinery: elements of the box
+// that fall outside the tensor are not written. Belongs to the issuing thread's bulk group.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t src_smem, int32_t x, int32_t y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               :
+               : "l"(reinterpret_cast<uint64_t>(map)), "r"(src_smem), "r"(x), "r"(y)
+               : "memory");
+}
+
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+
+// Until the stores this thread committed have finished *reading* shared memory (the source may
+// then be overwritten) ...
+__device__ __forceinline__ void tma_store_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+
+// ... or have completed altogether.
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+// Makes this thread's ordinary shared-memory writes visible to the async proxy (TMA).
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
 __device__ __forceinline__ void tma_load_2d_hint(uint32_t dst_smem, const CUtensorMap *map,
                                                  uint32_t bar, int32_t x, int32_t y,
                                                  uint64_t policy) {
