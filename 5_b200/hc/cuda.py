@@ -77,7 +77,7 @@ class _PlanInfo(ctypes.Structure):
         ("variant", ctypes.c_int32), ("tiles_m", ctypes.c_int32), ("tiles_n", ctypes.c_int32),
         ("splits", ctypes.c_int32), ("grid", ctypes.c_int32), ("repack_a", ctypes.c_int32),
         ("repack_b", ctypes.c_int32), ("kernel_launches", ctypes.c_int32),
-        ("scratch_bytes", ctypes.c_int64),
+        ("scratch_bytes", ctypes.c_int64), ("first_split_tile", ctypes.c_int32), ("reserved", ctypes.c_int32),
     ]
 
 
@@ -197,9 +197,11 @@ class GemmPlan:
         self.repack_b = bool(info.repack_b)
         self.kernel_launches = info.kernel_launches
         self.scratch_bytes = info.scratch_bytes
+        self.first_split_tile = info.first_split_tile
 
     def __repr__(self) -> str:
-        return (f"GemmPlan({self.variant}, tiles={self.tiles_m}x{self.tiles_n}, splits={self.splits}, "
+        splits = f"{self.splits}" + (f" from tile {self.first_split_tile}" if self.first_split_tile else "")
+        return (f"GemmPlan({self.variant}, tiles={self.tiles_m}x{self.tiles_n}, splits={splits}, "
                 f"grid={self.grid}, repack=({self.repack_a}, {self.repack_b}), "
                 f"launches={self.kernel_launches}, scratch={self.scratch_bytes})")
 

@@ -271,12 +271,25 @@ int plan_gemm(const HcCudaContext *ctx, const HcCudaGemmArgs *args, int sm_count
     const int64_t tiles = static_cast<int64_t>(plan->tiles_m) * plan->tiles_n;
     if (tiles > 0x3fffffffLL)
       return fail(ctx, HC_CUDA_ERR_UNSUPPORTED, "too many tiles");
-    if (pairs) {
-      const int64_t clusters = sm_count / 2;
-      plan->grid = static_cast<int32_t>(2 * (tiles < clusters ? tiles : clusters));
-    } else {
-      plan->grid = static_cast<int32_t>(tiles < sm_count ? tiles : sm_count);
+    // Tiles that do not fill a round of the persistent CTAs (all of them, or the last round's) are
+    // split over k when k is long enough.
+    const int block_k = hc::sm100::dense_block_k(pairs);
+    const int num_kb = static_cast<int>((k + block_k - 1) / block_k);
+    const int slots = pairs ? sm_count / 2 : sm_count;
+    long long first_split_tile = 0;
+    plan->splits = hc::sm100::dense_choose_splits(tiles, slots, num_kb, &first_split_tile);
+    if (const char *forced = std::getenv("HC_CUDA_DENSE_SPLITS")) {  // tuning aid: split every tile
+      const int v = std::atoi(forced);
+      if (v >= 1 && v <= num_kb && v <= 64) {
+        plan->splits = v;
+        first_split_tile = 0;
+      }
     }
+    const int64_t split_tiles = plan->splits > 1 ? tiles - first_split_tile : 0;
+    const int64_t units = tiles + split_tiles * (plan->splits - 1);
+    plan->grid = static_cast<int32_t>((pairs ? 2 : 1) * (units < slots ? units : slots));
+    scratch += static_cast<int64_t>(hc::sm100::dense_partials_bytes(split_tiles, plan->splits, pairs));
+    plan->first_split_tile = static_cast<int32_t>(first_split_tile);
   } else {
     const hc::sm100::SkinnyShape s = hc::sm100::skinny_shape(static_cast<int>(m));
     plan->tiles_m = 1;
@@ -457,14 +470,28 @@ int enqueue_gemm(HcCudaContext *ctx, const HcCudaGemmArgs *args, const HcCudaGem
         return rc;
       c_map = &tmap_c;
     }
+    hc::sm100::SplitK split{plan.splits, plan.first_split_tile, nullptr, nullptr};
+    CUtensorMap tmap_p;
+    if (plan.splits > 1) {
+      const long long split_tiles = static_cast<long long>(plan.tiles_m) * plan.tiles_n - plan.first_split_tile;
+      if (int rc = ensure_counters(ctx, hc::sm100::dense_counters_bytes(split_tiles)))
+        return rc;
+      split.partials = reinterpret_cast<float *>(cursor);  // after the repacked operands, 1 KiB aligned
+      split.counters = ctx->counters;
+      const uint64_t tile_rows = static_cast<uint64_t>(pairs ? 2 * t.block_m : t.block_m);
+      if (int rc = encode_map(ctx, &tmap_p, kMapFloat32, split.partials, static_cast<uint64_t>(t.block_n),
+                              static_cast<uint64_t>(split_tiles) * plan.splits * tile_rows,
+                              static_cast<uint64_t>(t.block_n) * 4, 32, 32))
+        return rc;
+    }
     if (pairs) {
       HC_TRY_CUDA(ctx, hc::sm100::launch_gemm_dense_pair(tmap_a, tmap_b, args->c, m, n, k, args->ldc,
                                                          args->dtype, ctx->group_n, plan.grid, b_layout, ep,
-                                                         c_map, ctx->status_dev, ctx->stream));
+                                                         c_map, split, &tmap_p, ctx->status_dev, ctx->stream));
     } else {
       HC_TRY_CUDA(ctx, hc::sm100::launch_gemm_dense(tmap_a, tmap_b, args->c, m, n, k, args->ldc,
                                                     args->dtype, ctx->group_n, plan.grid, b_layout, ep,
-                                                    c_map, ctx->status_dev, ctx->stream));
+                                                    c_map, split, &tmap_p, ctx->status_dev, ctx->stream));
     }
     return HC_CUDA_OK;
   }

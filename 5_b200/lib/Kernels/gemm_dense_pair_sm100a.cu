@@ -94,9 +94,10 @@ template <bool kFused>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Roles<kFused>::kThreads, 1)
 gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                        const __grid_constant__ CUtensorMap tmap_b,
-                       const __grid_constant__ CUtensorMap tmap_c, int c_tma, float *__restrict__ c, int m, int n,
+                       const __grid_constant__ CUtensorMap tmap_c, int c_tma,
+                       const __grid_constant__ CUtensorMap tmap_partials, float *__restrict__ c, int m, int n,
                        int k, long long ldc, uint32_t idesc, int tiles_m, int tiles_n, int group_n,
-                       int l2_hints, int b_layout, Epilogue ep, int *status) {
+                       int l2_hints, int b_layout, Epilogue ep, SplitK split, int *status) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t smem_base = (raw_addr + 1023u) & ~1023u;
@@ -147,6 +148,11 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int num_kb = (k + kBlockK - 1) / kBlockK;
   const int cluster_id = static_cast<int>(blockIdx.x >> 1);
   const int num_clusters = static_cast<int>(gridDim.x >> 1);
+  // A unit is one tile, or with split-k one range of a tile's k-blocks; the splits of a tile are
+  // consecutive units, so they run on neighbouring clusters at the same time.
+  const int num_units = split.splits == 1 ? num_tiles
+                                          : split.first_split_tile + (num_tiles - split.first_split_tile) * split.splits;
+  auto first_kb = [&](int part, int parts) { return static_cast<int>(static_cast<long long>(part) * num_kb / parts); };
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer ------
@@ -160,11 +166,13 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const uint64_t pol_b = l2_hints == 0 ? l2_policy_evict_normal() : l2_policy_evict_last();
       uint32_t stage = 0, phase = 0;
       bool ok = true;
-      for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters) {
-        const TileCoord tc = tile_coord(tile, tiles_m, tiles_n, group_n);
+      for (int unit = cluster_id; ok && unit < num_units; unit += num_clusters) {
+        const DenseUnit u = decode_unit(unit, split);
+        const TileCoord tc = tile_coord(u.tile, tiles_m, tiles_n, group_n);
         const int m0 = tc.m_blk * kTileM + static_cast<int>(cta_rank) * kCtaM;
         const int n0 = tc.n_blk * kTileN + static_cast<int>(cta_rank) * kCtaN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int kb_end = first_kb(u.part + 1, u.parts);
+        for (int kb = first_kb(u.part, u.parts); kb < kb_end; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
             ok = false;
             break;
@@ -201,14 +209,16 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       uint32_t stage = 0, phase = 0;
       uint32_t iter = 0;
       bool ok = true;
-      for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters, ++iter) {
+      for (int unit = cluster_id; ok && unit < num_units; unit += num_clusters, ++iter) {
+        const DenseUnit u = decode_unit(unit, split);
         const uint32_t acc = iter & 1u;
         const uint32_t acc_phase = (iter >> 1) & 1u;
         if (!mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, abort_flag))
           break;
         tcgen05_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * kTileN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int kb_begin = first_kb(u.part, u.parts), kb_end = first_kb(u.part + 1, u.parts);
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
           if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
             ok = false;
             break;
@@ -228,7 +238,7 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 b_kn ? make_smem_desc_sw128(b_addr, kBChunkBytes, 1024) + static_cast<uint64_t>(kk * 128)
                      : make_smem_desc_sw128(b_addr + (kk / 4) * kASubBytes, 16, 1024) +
                            static_cast<uint64_t>((kk % 4) * 2);
-            umma_f16_ss_pair(d_tmem, a_desc, b_desc, idesc, (kb | kk) != 0 ? 1u : 0u);
+            umma_f16_ss_pair(d_tmem, a_desc, b_desc, idesc, (kb != kb_begin || kk != 0) ? 1u : 0u);
           }
           // Hand ring slot `stage` back to both producers.
           umma_commit_pair(map_to_cta(empty_bar(stage), 0));
@@ -252,8 +262,9 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                                  (warp - 2) * kEpilogueWarpBytes);
     const bool vec_ok = ((ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(c) & 15) == 0);
     uint32_t iter = 0;
-    for (int tile = cluster_id; tile < num_tiles; tile += num_clusters, ++iter) {
-      const TileCoord tc = tile_coord(tile, tiles_m, tiles_n, group_n);
+    for (int unit = cluster_id; unit < num_units; unit += num_clusters, ++iter) {
+      const DenseUnit u = decode_unit(unit, split);
+      const TileCoord tc = tile_coord(u.tile, tiles_m, tiles_n, group_n);
       const uint32_t acc = iter & 1u;
       const uint32_t acc_phase = (iter >> 1) & 1u;
       const int row_base = tc.m_blk * kTileM + static_cast<int>(cta_rank) * kCtaM + quarter * 32;
@@ -266,11 +277,36 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       tcgen05_fence_after_sync();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kTileN +
                              column_part * kColumnsPerWarp;
-      drain_accumulator_rows<kColumnsPerWarp, kFused>(taddr, stage_gen, c, ldc, m, n, row_base, col_base, vec_ok, lane,
-                                     map_to_cta(tmem_empty_bar(acc), 0), /*release_remote=*/true, ep,
-                                     c_tma ? &tmap_c : nullptr);
+      if (u.parts == 1) {
+        drain_accumulator_rows<kColumnsPerWarp, kFused>(taddr, stage_gen, c, ldc, m, n, row_base, col_base, vec_ok,
+                                                        lane, map_to_cta(tmem_empty_bar(acc), 0),
+                                                        /*release_remote=*/true, ep, c_tma ? &tmap_c : nullptr);
+        continue;
+      }
+      // Split-k: the partial rows go to this unit's tile of the partials buffer (TMA stores, like
+      // C); the warp whose unit completes the tile adds the tiles up.
+      constexpr size_t kTileFloats = static_cast<size_t>(kTileM) * kTileN;
+      const int tile_row = static_cast<int>(cta_rank) * kCtaM + quarter * 32, tile_col = column_part * kColumnsPerWarp;
+      drain_accumulator_rows<kColumnsPerWarp, false>(taddr, stage_gen, nullptr, 0, 0x7fffffff, kTileN,
+                                                     u.split_index * kTileM + tile_row, tile_col, true, lane,
+                                                     map_to_cta(tmem_empty_bar(acc), 0), /*release_remote=*/true,
+                                                     Epilogue{}, &tmap_partials);
+      if (lane == 0) {
+        tma_store_wait_all();  // the partial rows are in memory before the unit counts itself in
+        fence_proxy_async_all();
+      }
+      unsigned *counter =
+          split.counters + (static_cast<size_t>(u.split_tile) * 2 + cta_rank) * kMaxEpilogueWarps + (warp - 2);
+      if (split_arrive_is_last(counter, u.parts, lane)) {
+        reduce_partials_rows<kColumnsPerWarp, kFused>(
+            split.partials + static_cast<size_t>(u.split_tile) * u.parts * kTileFloats +
+                static_cast<size_t>(tile_row) * kTileN + tile_col,
+            kTileN, kTileFloats, u.parts, stage_gen, c, ldc, m, n, row_base, col_base, vec_ok, lane, ep, c_tma ? &tmap_c : nullptr);
+        if (lane == 0)
+          *counter = 0u;
+      }
     }
-    if (c_tma && lane == 0)
+    if ((c_tma || split.splits > 1) && lane == 0)
       tma_store_wait_all();  // shared memory must outlive the stores that read it
   }
 
@@ -296,7 +332,8 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
 cudaError_t launch_gemm_dense_pair(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, float *c,
                                    int m, int n, int k, long long ldc, int dtype, int group_n,
                                    int max_ctas, int b_layout, const Epilogue &ep, const CUtensorMap *tmap_c,
-                                   int *status, cudaStream_t stream) {
+                                   const SplitK &split, const CUtensorMap *tmap_partials, int *status,
+                                   cudaStream_t stream) {
   using namespace dense_pair;
   static thread_local int configured_device = -1;
   int device = 0;
@@ -318,11 +355,18 @@ cudaError_t launch_gemm_dense_pair(const CUtensorMap &tmap_a, const CUtensorMap 
   const long long num_tiles = static_cast<long long>(tiles_m) * tiles_n;
   if (num_tiles <= 0 || num_tiles > 0x3fffffffLL)
     return cudaErrorInvalidValue;
+  if (split.splits < 1 ||
+      (split.splits > 1 && (split.partials == nullptr || split.counters == nullptr || tmap_partials == nullptr)))
+    return cudaErrorInvalidValue;
+  if (split.splits > 1 && (split.first_split_tile < 0 || split.first_split_tile >= num_tiles))
+    return cudaErrorInvalidValue;
+  const long long num_units =
+      split.splits == 1 ? num_tiles : split.first_split_tile + (num_tiles - split.first_split_tile) * split.splits;
   long long clusters = max_ctas / 2;
   if (clusters < 1)
     clusters = 1;
-  if (num_tiles < clusters)
-    clusters = num_tiles;
+  if (num_units < clusters)
+    clusters = num_units;
   const uint32_t idesc = make_idesc_f16(dtype == kDTypeBF16 ? 1u : 0u, /*a_mn_major=*/false,
                                         /*b_mn_major=*/b_layout == kBLayoutKN, kTileM, kTileN);
   if (group_n < 1)
@@ -331,18 +375,21 @@ cudaError_t launch_gemm_dense_pair(const CUtensorMap &tmap_a, const CUtensorMap 
   const bool fused_store = ep.accumulate != 0 || ep.op_count != 0;
   const int c_tma = (tmap_c != nullptr && !fused_store && ep.push_count == 0) ? 1 : 0;
   const CUtensorMap c_map = c_tma ? *tmap_c : tmap_a;  // unused unless c_tma
+  const CUtensorMap p_map = split.splits > 1 ? *tmap_partials : tmap_a;  // unused unless split
   int l2_hints = 3;
   if (const char *h = std::getenv("HC_CUDA_L2_HINTS"))  // tuning aid
     l2_hints = std::atoi(h);
   const unsigned grid = static_cast<unsigned>(clusters * 2);
   if (ep.accumulate != 0 || ep.op_count != 0)
     gemm_dense_pair_kernel<true><<<grid, Roles<true>::kThreads, kSmemBytes, stream>>>(
-        tmap_a, tmap_b, c_map, c_tma, c, m, n, k, ldc, idesc, tiles_m, tiles_n, group_n, l2_hints, b_layout, ep, status);
+        tmap_a, tmap_b, c_map, c_tma, p_map, c, m, n, k, ldc, idesc, tiles_m, tiles_n, group_n, l2_hints, b_layout, ep, split, status);
   else
     gemm_dense_pair_kernel<false><<<grid, Roles<false>::kThreads, kSmemBytes, stream>>>(
-        tmap_a, tmap_b, c_map, c_tma, c, m, n, k, ldc, idesc, tiles_m, tiles_n, group_n, l2_hints, b_layout, ep, status);
+        tmap_a, tmap_b, c_map, c_tma, p_map, c, m, n, k, ldc, idesc, tiles_m, tiles_n, group_n, l2_hints, b_layout, ep, split, status);
   return cudaGetLastError();
 }
+
+int dense_block_k(bool pairs) { return pairs ? dense_pair::kBlockK : dense_tile_shape().block_k; }
 
 bool dense_uses_pairs(long long m, long long n, long long k, int sm_count) {
   (void)k;

@@ -78,9 +78,10 @@ template <bool kFused>
 __global__ void __launch_bounds__(Roles<kFused>::kThreads, 1)
 gemm_dense_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   const __grid_constant__ CUtensorMap tmap_b,
-                       const __grid_constant__ CUtensorMap tmap_c, int c_tma, float *__restrict__ c, int m, int n,
+                       const __grid_constant__ CUtensorMap tmap_c, int c_tma,
+                       const __grid_constant__ CUtensorMap tmap_partials, float *__restrict__ c, int m, int n,
                   int k, long long ldc, uint32_t idesc, int tiles_m, int tiles_n, int group_n,
-                  int b_layout, Epilogue ep, int *status) {
+                  int b_layout, Epilogue ep, SplitK split, int *status) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t smem_base = (raw_addr + 1023u) & ~1023u;  // swizzled tiles need 1 KiB alignment
@@ -126,17 +127,24 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
   const int num_tiles = tiles_m * tiles_n;
   const int num_kb = (k + kBlockK - 1) / kBlockK;
+  // A unit is one tile, or with split-k one range of a tile's k-blocks; the splits of a tile are
+  // consecutive units, so they run on neighbouring CTAs at the same time.
+  const int num_units = split.splits == 1 ? num_tiles
+                                          : split.first_split_tile + (num_tiles - split.first_split_tile) * split.splits;
+  auto first_kb = [&](int part, int parts) { return static_cast<int>(static_cast<long long>(part) * num_kb / parts); };
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer ------
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-        const TileCoord tc = tile_coord(tile, tiles_m, tiles_n, group_n);
+      for (int unit = blockIdx.x; ok && unit < num_units; unit += gridDim.x) {
+        const DenseUnit u = decode_unit(unit, split);
+        const TileCoord tc = tile_coord(u.tile, tiles_m, tiles_n, group_n);
         const int m0 = tc.m_blk * kBlockM;
         const int n0 = tc.n_blk * kBlockN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int kb_end = first_kb(u.part + 1, u.parts);
+        for (int kb = first_kb(u.part, u.parts); kb < kb_end; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
             ok = false;
             break;
@@ -166,14 +174,16 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tmap_a,
       uint32_t stage = 0, phase = 0;
       uint32_t iter = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++iter) {
+      for (int unit = blockIdx.x; ok && unit < num_units; unit += gridDim.x, ++iter) {
+        const DenseUnit u = decode_unit(unit, split);
         const uint32_t acc = iter & 1u;
         const uint32_t acc_phase = (iter >> 1) & 1u;
         if (!mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, abort_flag))
           break;
         tcgen05_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * kBlockN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int kb_begin = first_kb(u.part, u.parts), kb_end = first_kb(u.part + 1, u.parts);
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
           if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
             ok = false;
             break;
@@ -195,7 +205,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tmap_a,
             // two groups of 8 k-rows (2048 bytes); both in 16-byte descriptor units.
             umma_f16_ss(d_tmem, a_desc + static_cast<uint64_t>(kk * 2),
                         b_desc + static_cast<uint64_t>(kk) * b_step, idesc,
-                        (kb | kk) != 0 ? 1u : 0u);
+                        (kb != kb_begin || kk != 0) ? 1u : 0u);
           }
           umma_commit(empty_bar(stage));
           if (++stage == kStages) {
@@ -215,8 +225,9 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tmap_a,
     float *stage_gen = reinterpret_cast<float *>(smem_gen + (stage_smem - smem_base));
     const bool vec_ok = ((ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(c) & 15) == 0);
     uint32_t iter = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++iter) {
-      const TileCoord tc = tile_coord(tile, tiles_m, tiles_n, group_n);
+    for (int unit = blockIdx.x; unit < num_units; unit += gridDim.x, ++iter) {
+      const DenseUnit u = decode_unit(unit, split);
+      const TileCoord tc = tile_coord(u.tile, tiles_m, tiles_n, group_n);
       const uint32_t acc = iter & 1u;
       const uint32_t acc_phase = (iter >> 1) & 1u;
       const int row_base = tc.m_blk * kBlockM + quarter * 32;
@@ -229,11 +240,35 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tmap_a,
       tcgen05_fence_after_sync();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kBlockN +
                              column_part * kColumnsPerWarp;
-      drain_accumulator_rows<kColumnsPerWarp, kFused>(taddr, stage_gen, c, ldc, m, n, row_base, col_base, vec_ok, lane,
-                                      tmem_empty_bar(acc), /*release_remote=*/false, ep,
-                                     c_tma ? &tmap_c : nullptr);
+      if (u.parts == 1) {
+        drain_accumulator_rows<kColumnsPerWarp, kFused>(taddr, stage_gen, c, ldc, m, n, row_base, col_base, vec_ok,
+                                                        lane, tmem_empty_bar(acc), /*release_remote=*/false, ep,
+                                                        c_tma ? &tmap_c : nullptr);
+        continue;
+      }
+      // Split-k: the partial rows go to this unit's tile of the partials buffer (TMA stores, like
+      // C); the warp whose unit completes the tile adds the tiles up.
+      constexpr size_t kTileFloats = static_cast<size_t>(kBlockM) * kBlockN;
+      const int tile_row = quarter * 32, tile_col = column_part * kColumnsPerWarp;
+      drain_accumulator_rows<kColumnsPerWarp, false>(taddr, stage_gen, nullptr, 0, 0x7fffffff, kBlockN,
+                                                     u.split_index * kBlockM + tile_row, tile_col, true, lane,
+                                                     tmem_empty_bar(acc), /*release_remote=*/false, Epilogue{},
+                                                     &tmap_partials);
+      if (lane == 0) {
+        tma_store_wait_all();  // the partial rows are in memory before the unit counts itself in
+        fence_proxy_async_all();
+      }
+      unsigned *counter = split.counters + static_cast<size_t>(u.split_tile) * (2 * kMaxEpilogueWarps) + (warp - 2);
+      if (split_arrive_is_last(counter, u.parts, lane)) {
+        reduce_partials_rows<kColumnsPerWarp, kFused>(
+            split.partials + static_cast<size_t>(u.split_tile) * u.parts * kTileFloats +
+                static_cast<size_t>(tile_row) * kBlockN + tile_col,
+            kBlockN, kTileFloats, u.parts, stage_gen, c, ldc, m, n, row_base, col_base, vec_ok, lane, ep, c_tma ? &tmap_c : nullptr);
+        if (lane == 0)
+          *counter = 0u;
+      }
     }
-    if (c_tma && lane == 0)
+    if ((c_tma || split.splits > 1) && lane == 0)
       tma_store_wait_all();  // shared memory must outlive the stores that read it
   }
 
@@ -259,7 +294,8 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tmap_a,
 cudaError_t launch_gemm_dense(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, float *c,
                               int m, int n, int k, long long ldc, int dtype, int group_n,
                               int max_ctas, int b_layout, const Epilogue &ep, const CUtensorMap *tmap_c,
-                              int *status, cudaStream_t stream) {
+                              const SplitK &split, const CUtensorMap *tmap_partials, int *status,
+                                   cudaStream_t stream) {
   using namespace dense;
   static thread_local int configured_device = -1;
   int device = 0;
@@ -281,7 +317,14 @@ cudaError_t launch_gemm_dense(const CUtensorMap &tmap_a, const CUtensorMap &tmap
   const long long num_tiles = static_cast<long long>(tiles_m) * tiles_n;
   if (num_tiles <= 0 || num_tiles > 0x7fffffffLL)
     return cudaErrorInvalidValue;
-  const int grid = static_cast<int>(num_tiles < max_ctas ? num_tiles : max_ctas);
+  if (split.splits < 1 ||
+      (split.splits > 1 && (split.partials == nullptr || split.counters == nullptr || tmap_partials == nullptr)))
+    return cudaErrorInvalidValue;
+  if (split.splits > 1 && (split.first_split_tile < 0 || split.first_split_tile >= num_tiles))
+    return cudaErrorInvalidValue;
+  const long long num_units =
+      split.splits == 1 ? num_tiles : split.first_split_tile + (num_tiles - split.first_split_tile) * split.splits;
+  const int grid = static_cast<int>(num_units < max_ctas ? num_units : max_ctas);
   const uint32_t idesc = make_idesc_f16(dtype == kDTypeBF16 ? 1u : 0u, /*a_mn_major=*/false,
                                         /*b_mn_major=*/b_layout == kBLayoutKN, kBlockM, kBlockN);
   if (group_n < 1)
@@ -290,15 +333,54 @@ cudaError_t launch_gemm_dense(const CUtensorMap &tmap_a, const CUtensorMap &tmap
   const bool fused_store = ep.accumulate != 0 || ep.op_count != 0;
   const int c_tma = (tmap_c != nullptr && !fused_store && ep.push_count == 0) ? 1 : 0;
   const CUtensorMap c_map = c_tma ? *tmap_c : tmap_a;  // unused unless c_tma
+  const CUtensorMap p_map = split.splits > 1 ? *tmap_partials : tmap_a;  // unused unless split
   if (ep.accumulate != 0 || ep.op_count != 0)
-    gemm_dense_kernel<true><<<grid, Roles<true>::kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, c_map, c_tma, c, m, n, k, ldc, idesc,
+    gemm_dense_kernel<true><<<grid, Roles<true>::kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, c_map, c_tma, p_map, c, m, n, k, ldc, idesc,
                                                                        tiles_m, tiles_n, group_n, b_layout, ep,
-                                                                       status);
+                                                                       split, status);
   else
-    gemm_dense_kernel<false><<<grid, Roles<false>::kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, c_map, c_tma, c, m, n, k, ldc, idesc,
+    gemm_dense_kernel<false><<<grid, Roles<false>::kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, c_map, c_tma, p_map, c, m, n, k, ldc, idesc,
                                                                         tiles_m, tiles_n, group_n, b_layout, ep,
-                                                                        status);
+                                                                        split, status);
   return cudaGetLastError();
+}
+
+int dense_choose_splits(long long tiles, int slots, int num_kb, long long *first_split_tile) {
+  *first_split_tile = 0;
+  if (tiles < 1 || slots < 1 || num_kb < 16)
+    return 1;
+  // The tiles that do not fill a round of the persistent CTAs: all of them when there are fewer
+  // tiles than CTAs, else the remainder after the full rounds. Splitting them is worth it only when
+  // at least half of the CTAs (or pairs) would idle meanwhile; every split keeps at least eight
+  // k-blocks, so that the k-loop it shortens outweighs the partial tile it adds.
+  const long long full_rounds = tiles / slots;
+  const long long rest = tiles - full_rounds * slots;
+  if (rest == 0 || rest * 2 > slots)
+    return 1;
+  // After full rounds the split only shortens the last round, by at most half a tile's k-loop,
+  // while its partial tiles cost about 10-15 us (measured): it pays from k of about 8192 on.
+  if (full_rounds > 0 && num_kb < 64)
+    return 1;
+  long long splits = slots / rest;
+  if (splits > num_kb / 8)
+    splits = num_kb / 8;
+  if (splits > 32)
+    splits = 32;
+  if (splits < 2)
+    return 1;
+  *first_split_tile = full_rounds * slots;
+  return static_cast<int>(splits);
+}
+
+size_t dense_partials_bytes(long long split_tiles, int splits, bool pairs) {
+  if (splits <= 1)
+    return 0;
+  const size_t tile_floats = static_cast<size_t>(pairs ? 2 * dense::kBlockM : dense::kBlockM) * dense::kBlockN;
+  return static_cast<size_t>(split_tiles) * splits * tile_floats * sizeof(float);
+}
+
+size_t dense_counters_bytes(long long split_tiles) {
+  return static_cast<size_t>(split_tiles) * 2 * dense::kMaxEpilogueWarps * sizeof(unsigned);
 }
 
 DenseTileShape dense_tile_shape() {

@@ -443,3 +443,126 @@ __device__ __forceinline__ void drain_accumulator_rows(uint32_t taddr, float *st
 
 } // namespace sm100
 } // namespace hc
+
+namespace hc {
+namespace sm100 {
+
+// Split-k, second half, run by the warp whose unit arrived last: the partial tiles of all splits
+// are added in split order and the sums leave through the same chunk writers as an unsplit tile.
+// `partial_rows`: this warp's first row of split 0's partial tile, at the warp's first column
+// (rows are `partial_ld` floats apart, consecutive splits `split_stride` floats). The partial
+// tiles are read the way C is written -- 8 lanes per 128-byte row segment -- so every load
+// instruction fetches four full lines.
+// (Not inlined: it runs once per tile, and kept apart it cannot raise the register demand of the
+// chunk loop that every tile goes through.)
+template <int kColumns, bool kFused>
+__device__ __noinline__ void reduce_partials_rows(const float *partial_rows, int partial_ld, size_t split_stride,
+                                                  int splits, float *stage, float *__restrict__ c, long long ldc,
+                                                  int m, int n, int row_base, int col_base, bool vec_ok, int lane,
+                                                  const Epilogue &ep, const CUtensorMap *tmap_c) {
+  constexpr int kChunks = kColumns / 32;
+  float carry[3] = {0.0f, 0.0f, 0.0f};
+  const bool tma = !kFused && tmap_c != nullptr;
+  const int piece = lane & 7;
+  const float *lane_base = partial_rows + static_cast<size_t>(lane >> 3) * partial_ld + piece * 4;
+#pragma unroll 1
+  for (int chunk = 0; chunk < kChunks; ++chunk) {
+    if (col_base + chunk * 32 >= n || row_base >= m)
+      break;  // warp-uniform: nothing of this or any later chunk is inside C
+    float4 sum[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      sum[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll 2
+    for (int s = 0; s < splits; ++s) {
+      const float *src = lane_base + s * split_stride + chunk * 32;
+      float4 part[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        part[i] = __ldcg(reinterpret_cast<const float4 *>(src + static_cast<size_t>(i * 4) * partial_ld));
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        sum[i].x += part[i].x; sum[i].y += part[i].y; sum[i].z += part[i].z; sum[i].w += part[i].w;
+      }
+    }
+    if (tma) {
+      if (lane == 0)
+        tma_store_wait_read();  // the previous chunk's store has read the buffer
+      __syncwarp();
+    }
+    // The sums go into the staging block where the coalesced writers would read them ...
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int rr = i * 4 + (lane >> 3);
+      *reinterpret_cast<float4 *>(stage + rr * 32 + ((piece ^ (rr & 7)) << 2)) = sum[i];
+    }
+    if (tma) {
+      // ... which is already the layout of a TMA box.
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_2d(tmap_c, smem_u32(stage), col_base + chunk * 32, row_base);
+        tma_store_commit();
+      }
+      continue;
+    }
+    // Otherwise each lane takes its row back into registers and the chunk goes through the
+    // ordinary writer (odd pitches, fused work, push targets).
+    __syncwarp();
+    uint32_t r[32];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const float4 v = *reinterpret_cast<const float4 *>(stage + lane * 32 + ((q ^ (lane & 7)) << 2));
+      r[4 * q] = __float_as_uint(v.x);
+      r[4 * q + 1] = __float_as_uint(v.y);
+      r[4 * q + 2] = __float_as_uint(v.z);
+      r[4 * q + 3] = __float_as_uint(v.w);
+    }
+    write_chunk<kFused>(r, chunk, chunk == kChunks - 1, stage, c, ldc, m, n, row_base, col_base, vec_ok, lane,
+                        carry, ep);
+  }
+}
+
+// One unit of a dense launch: a whole tile (parts == 1) or one k range of a split tile.
+struct DenseUnit {
+  int tile;
+  int part, parts;
+  int split_index;  // of a split unit: its number among the split units (partial tile index)
+  int split_tile;   // of a split unit: its tile's number among the split tiles (counter index)
+};
+
+__device__ __forceinline__ DenseUnit decode_unit(int unit, const SplitK &split) {
+  DenseUnit u;
+  if (unit < split.first_split_tile || split.splits == 1) {
+    u.tile = unit;
+    u.part = 0;
+    u.parts = 1;
+    u.split_index = 0;
+    u.split_tile = 0;
+    return u;
+  }
+  u.split_index = unit - split.first_split_tile;
+  u.split_tile = u.split_index / split.splits;
+  u.part = u.split_index - u.split_tile * split.splits;
+  u.parts = split.splits;
+  u.tile = split.first_split_tile + u.split_tile;
+  return u;
+}
+
+// Counts this warp's partial rows in; true for the warp whose unit completes the tile. The
+// partial rows written before the call are visible to that warp after it.
+__device__ __forceinline__ bool split_arrive_is_last(unsigned *counter, int splits, int lane) {
+  __threadfence();
+  __syncwarp();
+  unsigned arrived = 0;
+  if (lane == 0)
+    arrived = atomicAdd(counter, 1u);
+  arrived = __shfl_sync(0xffffffffu, arrived, 0);
+  if (arrived != static_cast<unsigned>(splits - 1))
+    return false;
+  __threadfence();
+  return true;
+}
+
+} // namespace sm100
+} // namespace hc

@@ -49,6 +49,31 @@ struct Epilogue {
   const float *bias;
 };
 
+// Splitting dense tiles over k. Tiles [0, first_split_tile) are computed whole; each later tile
+// is computed by `splits` units, each over its own range of k-blocks. That covers both a product
+// with too few tiles for the GPU (first_split_tile = 0) and the last, partly filled round of a
+// larger one (first_split_tile = the tiles of the full rounds), whose tiles would otherwise keep
+// most CTAs waiting for a few. A split unit writes its fp32 partial tile to `partials`
+// ([split tile][split][tile rows][tile columns]) and counts itself in on `counters` (one word per
+// split tile, CTA of the pair and epilogue warp; zero on entry, zero again on exit). The unit that
+// arrives last adds the partial tiles in split order -- so the result does not depend on which
+// unit that is -- and stores C through the usual epilogue. No unit waits for another.
+// The units write their partial tiles with TMA stores: `tmap_partials` (launch argument) is the
+// partials buffer as a 2-D fp32 tensor {256 (inner), split units x tile rows}, box {32, 32},
+// 128-byte swizzle.
+struct SplitK {
+  int splits;            // 1: nothing is split
+  int first_split_tile;  // tiles before this one are whole
+  float *partials;
+  unsigned *counters;
+};
+// What to split for `tiles` tiles on `slots` CTAs (or CTA pairs) and `num_kb` k-blocks: returns the
+// number of splits and sets *first_split_tile.
+int dense_choose_splits(long long tiles, int slots, int num_kb, long long *first_split_tile);
+size_t dense_partials_bytes(long long split_tiles, int splits, bool pairs);
+size_t dense_counters_bytes(long long split_tiles);
+int dense_block_k(bool pairs);  // k extent of one ring stage of the chosen dense kernel
+
 struct DenseTileShape {
   int block_m, block_n, block_k, stages;
   unsigned smem_bytes;
@@ -64,7 +89,8 @@ DenseTileShape dense_tile_shape();
 cudaError_t launch_gemm_dense(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, float *c,
                               int m, int n, int k, long long ldc, int dtype, int group_n,
                               int max_ctas, int b_layout, const Epilogue &ep, const CUtensorMap *tmap_c,
-                              int *status, cudaStream_t stream);
+                              const SplitK &split, const CUtensorMap *tmap_partials, int *status,
+                                   cudaStream_t stream);
 
 // Same product on CTA pairs: clusters of two CTAs own 256x256 tiles and issue
 // tcgen05.mma.cta_group::2. Takes the same tensor maps as launch_gemm_dense. `max_ctas` is
@@ -72,7 +98,8 @@ cudaError_t launch_gemm_dense(const CUtensorMap &tmap_a, const CUtensorMap &tmap
 cudaError_t launch_gemm_dense_pair(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, float *c,
                                    int m, int n, int k, long long ldc, int dtype, int group_n,
                                    int max_ctas, int b_layout, const Epilogue &ep, const CUtensorMap *tmap_c,
-                                   int *status, cudaStream_t stream);
+                                   const SplitK &split, const CUtensorMap *tmap_partials, int *status,
+                                   cudaStream_t stream);
 
 // Whether the dense variant runs on CTA pairs for this problem.
 bool dense_uses_pairs(long long m, long long n, long long k, int sm_count);

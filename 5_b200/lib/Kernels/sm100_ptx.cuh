@@ -132,6 +132,10 @@ __device__ __forceinline__ void tma_store_wait_read() {
 // ... or have completed altogether.
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
+// Orders this thread's async-proxy operations (completed TMA stores) and generic-proxy
+// operations on all memory against each other.
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
 // Makes this thread's ordinary shared-memory writes visible to the async proxy (TMA).
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

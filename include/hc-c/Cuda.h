@@ -126,12 +126,16 @@ typedef struct HcCudaGemmPlanInfo {
   int32_t variant;         /* DENSE, SKINNY, NOOP or ZERO_FILL */
   int32_t tiles_m;         /* C tiles along m (dense) or 1 (skinny) */
   int32_t tiles_n;         /* C tiles along n */
-  int32_t splits;          /* k-splits (skinny), 1 otherwise */
+  int32_t splits;          /* k-splits: of every column block (skinny), or of the dense tiles from
+                              first_split_tile on; 1 when nothing is split */
   int32_t grid;            /* CTAs of the GEMM kernel */
   int32_t repack_a;        /* 1: A is first copied to a 128-byte-aligned pitch */
   int32_t repack_b;        /* 1: B likewise */
   int32_t kernel_launches; /* kernels this call enqueues (the GEMM, plus one repack if needed) */
   int64_t scratch_bytes;   /* context scratch the call needs */
+  int32_t first_split_tile; /* dense with splits > 1: tiles before this one are computed whole (the
+                               full rounds of the persistent CTAs); 0 when every tile is split */
+  int32_t reserved;
 } HcCudaGemmPlanInfo;
 
 typedef struct HcCudaDeviceInfo {

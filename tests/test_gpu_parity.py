@@ -271,6 +271,107 @@ def test_fused_operations_with_k_zero(gpu_ctx) -> None:
     assert np.array_equal(c, np.maximum(np.zeros((m, n), np.float32) * np.float32(0.125) + bias[None, :], 0))
 
 
+DENSE_SPLIT_SHAPES = [
+    # few tiles, long k: the plan splits k over the idle CTAs (single CTAs, CTA pairs, odd pitches)
+    (128, 2048, 4096, 0), (96, 1000, 8192, 3), (256, 1024, 8192, 0), (300, 700, 6000, 1), (512, 512, 16384, 0),
+    (256, 256, 32768, 0), (1024, 1024, 4096, 0), (130, 258, 2050, 5),
+]
+
+
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+@pytest.mark.parametrize("shape", DENSE_SPLIT_SHAPES)
+def test_dense_split_k(shape, dtype: str, gpu_ctx) -> None:
+    """Dense shapes with few tiles: partial tiles per k range, added in split order by whichever
+    unit finishes last. Checked against the oracle, for determinism, and with the fused members."""
+    m, n, k, pad = shape
+    plan = gpu_ctx.plan(m, n, k, dtype, ldc=n + pad)
+    assert plan.variant == "dense" and plan.splits > 1, plan
+    a, b = random_inputs(m, n, k, dtype, scale=0.25)
+    da, db = gpu_ctx.to_device(a), gpu_ctx.to_device(b)
+    dc = cuda.DeviceBuffer(gpu_ctx, (m, n), np.float32, ld=n + pad)
+    dc.fill_bytes(0xFF)
+    gpu_ctx.gemm(da, db, dc)
+    gpu_ctx.synchronize()
+    first = dc.to_numpy()
+    assert_close_to_oracle(first, a, b)
+    for _ in range(3):  # the counters are back at zero and the order of arrival does not matter
+        dc.fill_bytes(0xFF)
+        gpu_ctx.gemm(da, db, dc)
+        gpu_ctx.synchronize()
+        assert np.array_equal(dc.to_numpy(), first)
+    rng = np.random.default_rng([m, n, k, 5])
+    c0 = rng.standard_normal((m, n)).astype(np.float32)
+    bias = rng.standard_normal((n,)).astype(np.float32)
+    dbias = gpu_ctx.to_device(bias)
+    ops = (("scale", 0.5), ("bias",), ("max", -0.5))
+    dc.copy_from_host(c0)
+    gpu_ctx.gemm(da, db, dc, accumulate=True, epilogue=ops, bias=dbias)
+    gpu_ctx.synchronize()
+    assert_fused_close(dc.to_numpy(), a, b, c0=c0, epilogue=ops, bias=bias, use_oracle=m * n * k <= 1 << 28)
+    bt = gpu_ctx.to_device(np.ascontiguousarray(b.T))
+    dc.fill_bytes(0xFF)
+    gpu_ctx.gemm(da, bt, dc, b_transposed=True)
+    gpu_ctx.synchronize()
+    assert np.array_equal(dc.to_numpy(), first)
+    for buf in (da, db, dc, dbias, bt):
+        buf.free()
+
+
+def test_dense_split_k_forced(gpu_ctx, monkeypatch) -> None:
+    """Split counts the plan would not choose, on a shape with many tiles per CTA (units of one tile
+    land on different CTAs in different rounds)."""
+    m, n, k = 1100, 2300, 1536
+    a, b = random_inputs(m, n, k, "float16", scale=0.25)
+    da, db = gpu_ctx.to_device(a), gpu_ctx.to_device(b)
+    dc = gpu_ctx.empty((m, n), np.float32)
+    gpu_ctx.gemm(da, db, dc)
+    gpu_ctx.synchronize()
+    unsplit = dc.to_numpy()
+    for mode in ("single", "pair"):
+        monkeypatch.setenv("HC_CUDA_DENSE_MODE", mode)
+        for splits in (2, 3, 5):
+            monkeypatch.setenv("HC_CUDA_DENSE_SPLITS", str(splits))
+            assert gpu_ctx.plan(m, n, k, "float16").splits == splits
+            dc.fill_bytes(0xFF)
+            gpu_ctx.gemm(da, db, dc)
+            gpu_ctx.synchronize()
+            out = dc.to_numpy()
+            assert_close_to_oracle(out, a, b)
+            np.testing.assert_allclose(out, unsplit, rtol=0, atol=1e-4)
+
+
+@pytest.mark.parametrize("shape", [(4864, 1024, 8192), (2432, 2048, 8200), (9600, 512, 8192)])
+def test_dense_split_of_the_last_round(shape, gpu_ctx, monkeypatch) -> None:
+    """More tiles than CTAs with a small remainder: the tiles of the last, partly filled round
+    are split over k, the earlier ones are not."""
+    m, n, k = shape
+    plan = gpu_ctx.plan(m, n, k, "float16")
+    tiles = plan.tiles_m * plan.tiles_n
+    assert plan.splits > 1 and 0 < plan.first_split_tile < tiles, plan
+    a, b = random_inputs(m, n, k, "float16", scale=0.25)
+    da, db = gpu_ctx.to_device(a), gpu_ctx.to_device(b)
+    dc = gpu_ctx.empty((m, n), np.float32)
+    dc.fill_bytes(0xFF)
+    gpu_ctx.gemm(da, db, dc)
+    gpu_ctx.synchronize()
+    out = dc.to_numpy()
+    rows = _sample_rows(m)
+    assert workloads.check_against_float64(out, a, b, rows=rows)["ok"]
+    dc.fill_bytes(0xFF)
+    gpu_ctx.gemm(da, db, dc)
+    gpu_ctx.synchronize()
+    assert np.array_equal(dc.to_numpy(), out)
+    monkeypatch.setenv("HC_CUDA_DENSE_SPLITS", "1")
+    assert gpu_ctx.plan(m, n, k, "float16").splits == 1
+    gpu_ctx.gemm(da, db, dc)
+    gpu_ctx.synchronize()
+    whole = dc.to_numpy()
+    np.testing.assert_allclose(out, whole, rtol=0, atol=1e-4)
+    assert (out != whole).any()  # the split tiles were added in a different order
+    for buf in (da, db, dc):
+        buf.free()
+
+
 @pytest.mark.parametrize("seed", range(6))
 def test_random_shapes(seed: int, gpu_ctx) -> None:
     """Seeded random shapes, small and awkward ones included, in both element types and both B
