@@ -51,9 +51,9 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum),
 # from the ncu captures summarised under profiles/. None = not captured for that workload.
 NCU_DRAM_TRAFFIC_BYTES = {
-    "gemm_8192": 1.300e9,  # profiles/gemm_dense_pair_kernel__gemm_8192.md
+    "gemm_8192": 1.317e9,  # profiles/gemm_dense_pair_kernel__gemm_8192.md
     "skinny": 272.4e6,     # profiles/gemm_skinny_kernel__skinny_8x16384x8192.md
-    "ragged": 18.4e6,      # profiles/ragged_4095x3073x1031__launches.md (GEMM kernel only)
+    "ragged": 21.1e6,      # profiles/ragged_4095x3073x1031__launches.md (GEMM kernel only)
 }
 
 
