@@ -366,7 +366,7 @@ def test_dense_split_of_the_last_round(shape, gpu_ctx, monkeypatch) -> None:
     gpu_ctx.gemm(da, db, dc)
     gpu_ctx.synchronize()
     whole = dc.to_numpy()
-    np.testing.assert_allclose(out, whole, rtol=0, atol=1e-4)
+    np.testing.assert_allclose(out, whole, rtol=0, atol=2e-3)  # fp32 reassociation over k = 8192
     assert (out != whole).any()  # the split tiles were added in a different order
     for buf in (da, db, dc):
         buf.free()
