@@ -26,6 +26,7 @@ __all__ = [
     "Context",
     "DeviceBuffer",
     "GemmPlan",
+    "BoundGemm",
     "default_context",
     "device_count",
     "library",
@@ -344,6 +345,20 @@ class Context:
         pointers = (ctypes.c_void_p * len(push))(*[t.ptr for t in push])
         self._check(self._lib.hcCudaGemmPush(self._handle, ctypes.byref(args), pointers, len(push)))
 
+    def bind_gemm(self, a: "DeviceBuffer", b: "DeviceBuffer", c: "DeviceBuffer", *,
+                  variant: int = VARIANT_AUTO, b_transposed: bool = False, accumulate: bool = False,
+                  epilogue: Sequence[tuple] = (), bias: "DeviceBuffer | None" = None) -> "BoundGemm":
+        """The same call as `gemm` with its arguments marshalled once: `launch()` on the result only
+        crosses the C ABI, for loops in which the Python side of `gemm` (a few microseconds per call)
+        would otherwise pace the GPU. The buffers must stay allocated while it is used."""
+        m, k = a.shape
+        n = b.shape[0] if b_transposed else b.shape[1]
+        if bias is not None and (bias.dtype != np.float32 or bias.shape != (n,)):
+            raise ValueError("bias must be a float32 buffer of n values")
+        args = _gemm_args(m, n, k, a.dtype, a.ptr, a.ld, b.ptr, b.ld, c.ptr, c.ld, variant, b_transposed,
+                          accumulate, epilogue, None if bias is None else bias.ptr)
+        return BoundGemm(self, args, (a, b, c, bias))
+
     # -- sharing device memory between the processes of one node ----------------------------
     def ipc_export(self, buf: "DeviceBuffer") -> bytes:
         """Handle (64 bytes) of the allocation behind `buf`, for `ipc_open` in another process."""
@@ -440,6 +455,26 @@ class Event:
             self.close()
         except Exception:
             pass
+
+
+class BoundGemm:
+    """A GEMM on device buffers with its C-ABI arguments already built (`Context.bind_gemm`)."""
+
+    __slots__ = ("_ctx", "_args", "_ref", "_buffers", "_call", "_handle")
+
+    def __init__(self, ctx: Context, args: _GemmArgs, buffers: tuple) -> None:
+        self._ctx = ctx
+        self._args = args
+        self._ref = ctypes.byref(args)
+        self._buffers = buffers  # kept alive with the call
+        self._call = ctx._lib.hcCudaGemm
+        self._handle = ctx._handle
+
+    def launch(self) -> None:
+        """Enqueues the product (asynchronous, like `Context.gemm`)."""
+        status = self._call(self._handle, self._ref)
+        if status:
+            self._ctx._check(status)
 
 
 class DeviceBuffer:

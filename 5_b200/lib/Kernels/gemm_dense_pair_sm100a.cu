@@ -48,12 +48,12 @@ constexpr int kStages = 6 / kKSub;
 // Warp 0 loads, warp 1 issues the MMAs, the rest drain accumulators. The plain kernel has eight
 // epilogue warps: two per 32-lane quarter of tensor memory, each taking half of the tile's columns,
 // so that every scheduler has two of them to interleave (a lone warp per scheduler exposes every
-// latency of its chunk loop, which is what bounds shapes with a short k-loop). The fused kernel
-// needs more registers per thread and keeps four.
+// latency of its chunk loop, which is what bounds shapes with a short k-loop). The kernel that
+// reads C in its epilogue needs more registers per thread and keeps four.
 constexpr int kMaxEpilogueWarps = 8;
-template <bool kFused>
+template <bool kReadsC>
 struct Roles {
-  static constexpr int kEpilogueWarps = kFused ? 4 : 8;
+  static constexpr int kEpilogueWarps = kReadsC ? 4 : 8;
   static constexpr int kThreads = 64 + 32 * kEpilogueWarps;
 };
 constexpr int kTmemColumns = 512;  // two accumulators of kTileN fp32 columns
@@ -87,11 +87,12 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int tiles_m, int tiles
   return tc;
 }
 
-// kFused: the launch has work folded into the store (accumulate, element-wise operations); the
-// plain instantiation is the reference example's C = A.B and compiles to the same code as before
-// that work existed.
-template <bool kFused>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Roles<kFused>::kThreads, 1)
+// kReadsC: the epilogue has to read C's previous contents (an accumulating launch whose stores
+// cannot do the addition themselves: operations follow it, C's pitch rules out TMA, or there are
+// push targets). Every other launch -- the plain product, element-wise operations, accumulation
+// by TMA additions -- runs the other instantiation, which never reads C.
+template <bool kReadsC>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Roles<kReadsC>::kThreads, 1)
 gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                        const __grid_constant__ CUtensorMap tmap_b,
                        const __grid_constant__ CUtensorMap tmap_c, int c_tma,
@@ -104,7 +105,7 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
   uint8_t *smem_gen = smem_raw + (smem_base - raw_addr);
 
   const uint32_t epi_base = smem_base + kStages * kStageBytes;
-  constexpr int kEpilogueWarps = Roles<kFused>::kEpilogueWarps;
+  constexpr int kEpilogueWarps = Roles<kReadsC>::kEpilogueWarps;
   constexpr int kColumnsPerWarp = kTileN * 4 / kEpilogueWarps;  // 4 quarters of lanes share the warps
   const uint32_t bar_base = epi_base + kMaxEpilogueWarps * kEpilogueWarpBytes;
   auto full_bar = [&](uint32_t s) { return bar_base + 8u * s; };
@@ -269,7 +270,7 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const uint32_t acc_phase = (iter >> 1) & 1u;
       const int row_base = tc.m_blk * kTileM + static_cast<int>(cta_rank) * kCtaM + quarter * 32;
       const int col_base = tc.n_blk * kTileN + column_part * kColumnsPerWarp;
-      if (kFused && ep.accumulate)
+      if (kReadsC)
         prefetch_c_tile_row(c, ldc, m, n, row_base + lane, col_base, kColumnsPerWarp);
       const bool ready = mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag);
       if (!__all_sync(0xffffffffu, ready))
@@ -278,7 +279,7 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kTileN +
                              column_part * kColumnsPerWarp;
       if (u.parts == 1) {
-        drain_accumulator_rows<kColumnsPerWarp, kFused>(taddr, stage_gen, c, ldc, m, n, row_base, col_base, vec_ok,
+        drain_accumulator_rows<kColumnsPerWarp, kReadsC>(taddr, stage_gen, c, ldc, m, n, row_base, col_base, vec_ok,
                                                         lane, map_to_cta(tmem_empty_bar(acc), 0),
                                                         /*release_remote=*/true, ep, c_tma ? &tmap_c : nullptr);
         continue;
@@ -298,7 +299,7 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       unsigned *counter =
           split.counters + (static_cast<size_t>(u.split_tile) * 2 + cta_rank) * kMaxEpilogueWarps + (warp - 2);
       if (split_arrive_is_last(counter, u.parts, lane)) {
-        reduce_partials_rows<kColumnsPerWarp, kFused>(
+        reduce_partials_rows<kColumnsPerWarp, kReadsC>(
             split.partials + static_cast<size_t>(u.split_tile) * u.parts * kTileFloats +
                 static_cast<size_t>(tile_row) * kTileN + tile_col,
             kTileN, kTileFloats, u.parts, stage_gen, c, ldc, m, n, row_base, col_base, vec_ok, lane, ep, c_tma ? &tmap_c : nullptr);
@@ -371,21 +372,26 @@ cudaError_t launch_gemm_dense_pair(const CUtensorMap &tmap_a, const CUtensorMap 
                                         /*b_mn_major=*/b_layout == kBLayoutKN, kTileM, kTileN);
   if (group_n < 1)
     group_n = 1;
-  // TMA stores of C only for the plain product of an aligned C that goes nowhere else.
-  const bool fused_store = ep.accumulate != 0 || ep.op_count != 0;
-  const int c_tma = (tmap_c != nullptr && !fused_store && ep.push_count == 0) ? 1 : 0;
+  // C leaves through TMA stores when it is aligned (tmap_c), goes nowhere else, and any element-wise
+  // work can run before the store: no accumulation, or an accumulation that nothing follows, which
+  // the stores themselves perform as additions. Only the remaining case reads C in the epilogue.
+  Epilogue launch_ep = ep;
+  const bool tma_possible = tmap_c != nullptr && ep.push_count == 0;
+  launch_ep.accumulate_by_tma = (tma_possible && ep.accumulate != 0 && ep.op_count == 0) ? 1 : 0;
+  const bool reads_c = ep.accumulate != 0 && launch_ep.accumulate_by_tma == 0;
+  const int c_tma = (tma_possible && !reads_c) ? 1 : 0;
   const CUtensorMap c_map = c_tma ? *tmap_c : tmap_a;  // unused unless c_tma
   const CUtensorMap p_map = split.splits > 1 ? *tmap_partials : tmap_a;  // unused unless split
   int l2_hints = 3;
   if (const char *h = std::getenv("HC_CUDA_L2_HINTS"))  // tuning aid
     l2_hints = std::atoi(h);
   const unsigned grid = static_cast<unsigned>(clusters * 2);
-  if (ep.accumulate != 0 || ep.op_count != 0)
+  if (reads_c)
     gemm_dense_pair_kernel<true><<<grid, Roles<true>::kThreads, kSmemBytes, stream>>>(
-        tmap_a, tmap_b, c_map, c_tma, p_map, c, m, n, k, ldc, idesc, tiles_m, tiles_n, group_n, l2_hints, b_layout, ep, split, status);
+        tmap_a, tmap_b, c_map, c_tma, p_map, c, m, n, k, ldc, idesc, tiles_m, tiles_n, group_n, l2_hints, b_layout, launch_ep, split, status);
   else
     gemm_dense_pair_kernel<false><<<grid, Roles<false>::kThreads, kSmemBytes, stream>>>(
-        tmap_a, tmap_b, c_map, c_tma, p_map, c, m, n, k, ldc, idesc, tiles_m, tiles_n, group_n, l2_hints, b_layout, ep, split, status);
+        tmap_a, tmap_b, c_map, c_tma, p_map, c, m, n, k, ldc, idesc, tiles_m, tiles_n, group_n, l2_hints, b_layout, launch_ep, split, status);
   return cudaGetLastError();
 }
 

@@ -36,11 +36,11 @@ constexpr int kUmmaK = 16;
 constexpr int kStages = 4;
 // Warp 0 loads, warp 1 issues the MMAs, the rest drain accumulators: eight warps in the plain
 // kernel (two per quarter of tensor-memory lanes, each half of the tile's columns), four in the
-// fused one, which needs more registers per thread.
+// one that reads C in its epilogue, which needs more registers per thread.
 constexpr int kMaxEpilogueWarps = 8;
-template <bool kFused>
+template <bool kReadsC>
 struct Roles {
-  static constexpr int kEpilogueWarps = kFused ? 4 : 8;
+  static constexpr int kEpilogueWarps = kReadsC ? 4 : 8;
   static constexpr int kThreads = 64 + 32 * kEpilogueWarps;
 };
 constexpr int kTmemColumns = 512;  // two fp32 accumulators of kBlockN columns
@@ -73,9 +73,9 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int tiles_m, int tiles
   return tc;
 }
 
-// kFused: the launch has work folded into the store (accumulate, element-wise operations).
-template <bool kFused>
-__global__ void __launch_bounds__(Roles<kFused>::kThreads, 1)
+// kReadsC: the epilogue has to read C's previous contents (see gemm_dense_pair_kernel).
+template <bool kReadsC>
+__global__ void __launch_bounds__(Roles<kReadsC>::kThreads, 1)
 gemm_dense_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   const __grid_constant__ CUtensorMap tmap_b,
                        const __grid_constant__ CUtensorMap tmap_c, int c_tma,
@@ -88,7 +88,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tmap_a,
   uint8_t *smem_gen = smem_raw + (smem_base - raw_addr);
 
   const uint32_t epi_base = smem_base + kStages * kStageBytes;
-  constexpr int kEpilogueWarps = Roles<kFused>::kEpilogueWarps;
+  constexpr int kEpilogueWarps = Roles<kReadsC>::kEpilogueWarps;
   constexpr int kColumnsPerWarp = kBlockN * 4 / kEpilogueWarps;
   const uint32_t bar_base = epi_base + kMaxEpilogueWarps * kEpilogueWarpBytes;
   auto full_bar = [&](uint32_t s) { return bar_base + 8u * s; };
@@ -232,7 +232,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const uint32_t acc_phase = (iter >> 1) & 1u;
       const int row_base = tc.m_blk * kBlockM + quarter * 32;
       const int col_base = tc.n_blk * kBlockN + column_part * kColumnsPerWarp;
-      if (kFused && ep.accumulate)
+      if (kReadsC)
         prefetch_c_tile_row(c, ldc, m, n, row_base + lane, col_base, kColumnsPerWarp);
       const bool ready = mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag);
       if (!__all_sync(0xffffffffu, ready))
@@ -241,7 +241,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kBlockN +
                              column_part * kColumnsPerWarp;
       if (u.parts == 1) {
-        drain_accumulator_rows<kColumnsPerWarp, kFused>(taddr, stage_gen, c, ldc, m, n, row_base, col_base, vec_ok,
+        drain_accumulator_rows<kColumnsPerWarp, kReadsC>(taddr, stage_gen, c, ldc, m, n, row_base, col_base, vec_ok,
                                                         lane, tmem_empty_bar(acc), /*release_remote=*/false, ep,
                                                         c_tma ? &tmap_c : nullptr);
         continue;
@@ -260,7 +260,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
       unsigned *counter = split.counters + static_cast<size_t>(u.split_tile) * (2 * kMaxEpilogueWarps) + (warp - 2);
       if (split_arrive_is_last(counter, u.parts, lane)) {
-        reduce_partials_rows<kColumnsPerWarp, kFused>(
+        reduce_partials_rows<kColumnsPerWarp, kReadsC>(
             split.partials + static_cast<size_t>(u.split_tile) * u.parts * kTileFloats +
                 static_cast<size_t>(tile_row) * kBlockN + tile_col,
             kBlockN, kTileFloats, u.parts, stage_gen, c, ldc, m, n, row_base, col_base, vec_ok, lane, ep, c_tma ? &tmap_c : nullptr);
@@ -329,18 +329,23 @@ cudaError_t launch_gemm_dense(const CUtensorMap &tmap_a, const CUtensorMap &tmap
                                         /*b_mn_major=*/b_layout == kBLayoutKN, kBlockM, kBlockN);
   if (group_n < 1)
     group_n = 1;
-  // TMA stores of C only for the plain product of an aligned C that goes nowhere else.
-  const bool fused_store = ep.accumulate != 0 || ep.op_count != 0;
-  const int c_tma = (tmap_c != nullptr && !fused_store && ep.push_count == 0) ? 1 : 0;
+  // C leaves through TMA stores when it is aligned (tmap_c), goes nowhere else, and any element-wise
+  // work can run before the store: no accumulation, or an accumulation that nothing follows, which
+  // the stores themselves perform as additions. Only the remaining case reads C in the epilogue.
+  Epilogue launch_ep = ep;
+  const bool tma_possible = tmap_c != nullptr && ep.push_count == 0;
+  launch_ep.accumulate_by_tma = (tma_possible && ep.accumulate != 0 && ep.op_count == 0) ? 1 : 0;
+  const bool reads_c = ep.accumulate != 0 && launch_ep.accumulate_by_tma == 0;
+  const int c_tma = (tma_possible && !reads_c) ? 1 : 0;
   const CUtensorMap c_map = c_tma ? *tmap_c : tmap_a;  // unused unless c_tma
   const CUtensorMap p_map = split.splits > 1 ? *tmap_partials : tmap_a;  // unused unless split
-  if (ep.accumulate != 0 || ep.op_count != 0)
+  if (reads_c)
     gemm_dense_kernel<true><<<grid, Roles<true>::kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, c_map, c_tma, p_map, c, m, n, k, ldc, idesc,
-                                                                       tiles_m, tiles_n, group_n, b_layout, ep,
+                                                                       tiles_m, tiles_n, group_n, b_layout, launch_ep,
                                                                        split, status);
   else
     gemm_dense_kernel<false><<<grid, Roles<false>::kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, c_map, c_tma, p_map, c, m, n, k, ldc, idesc,
-                                                                        tiles_m, tiles_n, group_n, b_layout, ep,
+                                                                        tiles_m, tiles_n, group_n, b_layout, launch_ep,
                                                                         split, status);
   return cudaGetLastError();
 }

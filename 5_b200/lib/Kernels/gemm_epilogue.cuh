@@ -154,6 +154,44 @@ __device__ __forceinline__ void prefetch_c_tile_row(const float *c, long long ld
     asm volatile("prefetch.global.L2 [%0];" ::"l"(p + col));
 }
 
+// The operations on a chunk that is still in its tensor-memory layout (lane = row, r[j] = column
+// col0 + j): one instruction per value and operation, the kind branched on once per chunk. Used
+// whenever C's previous contents are not needed, so that the chunk can then leave like a plain one
+// (TMA store, or the coalesced writers for an odd pitch).
+__device__ __forceinline__ void apply_ops_lane_row(uint32_t (&r)[32], int col0, int n, int lane, const Epilogue &ep) {
+  float bias_lane = 0.0f;
+  if (ep.bias != nullptr && col0 + lane < n)
+    bias_lane = __ldg(ep.bias + col0 + lane);
+#pragma unroll
+  for (int op = 0; op < kMaxEpilogueOps; ++op) {
+    if (op >= ep.op_count)
+      break;
+    const int kind = ep.op_kind[op];
+    const float x = ep.op_value[op];
+    if (kind == kEpilogueScale) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        r[j] = __float_as_uint(__uint_as_float(r[j]) * x);
+    } else if (kind == kEpilogueAdd) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        r[j] = __float_as_uint(__uint_as_float(r[j]) + x);
+    } else if (kind == kEpilogueMax) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        r[j] = __float_as_uint(fmaxf(__uint_as_float(r[j]), x));
+    } else if (kind == kEpilogueMin) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        r[j] = __float_as_uint(fminf(__uint_as_float(r[j]), x));
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        r[j] = __float_as_uint(__uint_as_float(r[j]) + __shfl_sync(0xffffffffu, bias_lane, j));
+    }
+  }
+}
+
 // Stages this lane's 32 values with the row rotated left by kShift elements, so that the
 // 16-byte groups of the row *in memory* (which start kShift elements into the chunk) land on
 // 16-byte pieces of the staging block.
@@ -170,7 +208,10 @@ __device__ __forceinline__ void stage_row_shifted(const uint32_t (&r)[32], float
 // Writes one 32-column chunk (already in registers, lane = row) of this warp's 32 rows to C.
 // `carry` holds the last three values of this lane's row from the previous chunk (odd-pitch
 // path only); `last_chunk` says that no further chunk of the tile follows.
-template <bool kFused>
+// kReadsC: the launch adds to C's previous contents and has to read them here (an accumulating
+// kernel whose stores cannot do the addition); the operations then run here too, after that
+// addition. Otherwise the operations have already been applied to `r` and this is a plain store.
+template <bool kReadsC>
 __device__ __forceinline__ void write_chunk(const uint32_t (&r)[32], int chunk, bool last_chunk, float *buf,
                                             float *__restrict__ c, long long ldc, int m, int n,
                                             int row_base, int col_base, bool vec_ok, int lane,
@@ -179,7 +220,7 @@ __device__ __forceinline__ void write_chunk(const uint32_t (&r)[32], int chunk, 
   if (col0 >= n)
     return;  // warp-uniform
   const int piece = lane & 7;
-  constexpr bool fused = kFused;  // the plain kernel carries none of the fused work
+  constexpr bool fused = kReadsC;
   // One bias value per lane (column col0 + lane); groups fetch theirs by shuffle.
   float bias_lane = 0.0f;
   if (fused && ep.bias != nullptr && col0 + lane < n)
@@ -224,7 +265,7 @@ __device__ __forceinline__ void write_chunk(const uint32_t (&r)[32], int chunk, 
         }
       }
     };
-    if constexpr (!kFused) {
+    if constexpr (!kReadsC) {
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const int rr = i * 4 + (lane >> 3);
@@ -341,7 +382,7 @@ __device__ __forceinline__ void write_chunk(const uint32_t (&r)[32], int chunk, 
         }
       }
     };
-    if constexpr (!kFused) {
+    if constexpr (!kReadsC) {
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const int rr = i * 4 + (lane >> 3);
@@ -375,9 +416,10 @@ __device__ __forceinline__ void write_chunk(const uint32_t (&r)[32], int chunk, 
 // XOR of the 16-byte piece with the row is the 128-byte swizzle of the tensor map), then one
 // elected lane issues a 32x32 box store. Rows >= m and columns >= n are clipped by the tensor map.
 // Needs C's base and pitch 16-byte aligned; `buf` is 1024-byte aligned.
+// `add`: the box is added to C (TMA reduction) instead of replacing it.
 __device__ __forceinline__ void store_chunk_tma(const uint32_t (&r)[32], int chunk, float *buf,
                                                 const CUtensorMap *tmap_c, int m, int n, int row_base,
-                                                int col_base, int lane) {
+                                                int col_base, int lane, bool add = false) {
   const int col0 = col_base + chunk * 32;
   if (col0 >= n || row_base >= m)
     return;  // warp-uniform
@@ -388,7 +430,10 @@ __device__ __forceinline__ void store_chunk_tma(const uint32_t (&r)[32], int chu
   fence_proxy_async_smem();
   __syncwarp();
   if (lane == 0) {
-    tma_store_2d(tmap_c, smem_u32(buf), col0, row_base);
+    if (add)
+      tma_reduce_add_2d(tmap_c, smem_u32(buf), col0, row_base);
+    else
+      tma_store_2d(tmap_c, smem_u32(buf), col0, row_base);
     tma_store_commit();
   }
 }
@@ -398,7 +443,7 @@ __device__ __forceinline__ void store_chunk_tma(const uint32_t (&r)[32], int chu
 //
 // The TMEM load of the next chunk is in flight while the current chunk is transposed and
 // stored (two register sets alternate), so the TMEM latency is hidden behind the stores.
-template <int kColumns, bool kFused>
+template <int kColumns, bool kReadsC>
 __device__ __forceinline__ void drain_accumulator_rows(uint32_t taddr, float *stage, float *__restrict__ c,
                                                        long long ldc, int m, int n, int row_base,
                                                        int col_base, bool vec_ok, int lane,
@@ -408,17 +453,21 @@ __device__ __forceinline__ void drain_accumulator_rows(uint32_t taddr, float *st
   static_assert(kChunks % 2 == 0, "chunks are processed in pairs");
   uint32_t ra[32], rb[32];
   float carry[3] = {0.0f, 0.0f, 0.0f};
-  // Plain stores of an aligned C go through TMA (`tmap_c` is null otherwise).
-  const bool tma = !kFused && tmap_c != nullptr;
+  // Stores of an aligned C go through TMA (`tmap_c` is null otherwise).
+  const bool tma = !kReadsC && tmap_c != nullptr;
+  const bool tma_add = ep.accumulate_by_tma != 0;
+  const bool ops_first = !kReadsC && ep.op_count != 0;  // element-wise work done in registers
   tmem_load_32x32b_x32(taddr, ra);
 #pragma unroll 1
   for (int chunk = 0; chunk < kChunks; chunk += 2) {
     tmem_load_wait_for(ra);
     tmem_load_32x32b_x32(taddr + (chunk + 1) * 32, rb);
+    if (ops_first && col_base + chunk * 32 < n)
+      apply_ops_lane_row(ra, col_base + chunk * 32, n, lane, ep);
     if (tma)
-      store_chunk_tma(ra, chunk, stage, tmap_c, m, n, row_base, col_base, lane);
+      store_chunk_tma(ra, chunk, stage, tmap_c, m, n, row_base, col_base, lane, tma_add);
     else
-      write_chunk<kFused>(ra, chunk, false, stage, c, ldc, m, n, row_base, col_base, vec_ok, lane, carry, ep);
+      write_chunk<kReadsC>(ra, chunk, false, stage, c, ldc, m, n, row_base, col_base, vec_ok, lane, carry, ep);
     tmem_load_wait_for(rb);
     if (chunk + 2 < kChunks) {
       tmem_load_32x32b_x32(taddr + (chunk + 2) * 32, ra);
@@ -433,10 +482,12 @@ __device__ __forceinline__ void drain_accumulator_rows(uint32_t taddr, float *st
           mbar_arrive(release_bar);
       }
     }
+    if (ops_first && col_base + (chunk + 1) * 32 < n)
+      apply_ops_lane_row(rb, col_base + (chunk + 1) * 32, n, lane, ep);
     if (tma)
-      store_chunk_tma(rb, chunk + 1, stage, tmap_c, m, n, row_base, col_base, lane);
+      store_chunk_tma(rb, chunk + 1, stage, tmap_c, m, n, row_base, col_base, lane, tma_add);
     else
-      write_chunk<kFused>(rb, chunk + 1, chunk + 2 >= kChunks, stage, c, ldc, m, n, row_base, col_base, vec_ok, lane,
+      write_chunk<kReadsC>(rb, chunk + 1, chunk + 2 >= kChunks, stage, c, ldc, m, n, row_base, col_base, vec_ok, lane,
                           carry, ep);
   }
 }
@@ -455,14 +506,15 @@ namespace sm100 {
 // instruction fetches four full lines.
 // (Not inlined: it runs once per tile, and kept apart it cannot raise the register demand of the
 // chunk loop that every tile goes through.)
-template <int kColumns, bool kFused>
+template <int kColumns, bool kReadsC>
 __device__ __noinline__ void reduce_partials_rows(const float *partial_rows, int partial_ld, size_t split_stride,
                                                   int splits, float *stage, float *__restrict__ c, long long ldc,
                                                   int m, int n, int row_base, int col_base, bool vec_ok, int lane,
                                                   const Epilogue &ep, const CUtensorMap *tmap_c) {
   constexpr int kChunks = kColumns / 32;
   float carry[3] = {0.0f, 0.0f, 0.0f};
-  const bool tma = !kFused && tmap_c != nullptr;
+  const bool tma = !kReadsC && tmap_c != nullptr;
+  const bool ops_first = !kReadsC && ep.op_count != 0;
   const int piece = lane & 7;
   const float *lane_base = partial_rows + static_cast<size_t>(lane >> 3) * partial_ld + piece * 4;
 #pragma unroll 1
@@ -486,6 +538,18 @@ __device__ __noinline__ void reduce_partials_rows(const float *partial_rows, int
       }
     }
     if (tma) {
+      if (ops_first) {
+        // Each lane's groups start at column piece * 4 of the chunk: its four bias values.
+        const int col0 = col_base + chunk * 32;
+        float bias_lane = 0.0f;
+        if (ep.bias != nullptr && col0 + lane < n)
+          bias_lane = __ldg(ep.bias + col0 + lane);
+        const float4 bias = make_float4(__shfl_sync(0xffffffffu, bias_lane, piece * 4),
+                                        __shfl_sync(0xffffffffu, bias_lane, piece * 4 + 1),
+                                        __shfl_sync(0xffffffffu, bias_lane, piece * 4 + 2),
+                                        __shfl_sync(0xffffffffu, bias_lane, piece * 4 + 3));
+        apply_ops_to_groups(sum, ep, [&](int) { return bias; });
+      }
       if (lane == 0)
         tma_store_wait_read();  // the previous chunk's store has read the buffer
       __syncwarp();
@@ -501,7 +565,10 @@ __device__ __noinline__ void reduce_partials_rows(const float *partial_rows, int
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) {
-        tma_store_2d(tmap_c, smem_u32(stage), col_base + chunk * 32, row_base);
+        if (ep.accumulate_by_tma != 0)
+          tma_reduce_add_2d(tmap_c, smem_u32(stage), col_base + chunk * 32, row_base);
+        else
+          tma_store_2d(tmap_c, smem_u32(stage), col_base + chunk * 32, row_base);
         tma_store_commit();
       }
       continue;
@@ -518,7 +585,9 @@ __device__ __noinline__ void reduce_partials_rows(const float *partial_rows, int
       r[4 * q + 2] = __float_as_uint(v.z);
       r[4 * q + 3] = __float_as_uint(v.w);
     }
-    write_chunk<kFused>(r, chunk, chunk == kChunks - 1, stage, c, ldc, m, n, row_base, col_base, vec_ok, lane,
+    if (ops_first)
+      apply_ops_lane_row(r, col_base + chunk * 32, n, lane, ep);
+    write_chunk<kReadsC>(r, chunk, chunk == kChunks - 1, stage, c, ldc, m, n, row_base, col_base, vec_ok, lane,
                         carry, ep);
   }
 }

@@ -47,6 +47,9 @@ struct Epilogue {
   int op_kind[kMaxEpilogueOps];
   float op_value[kMaxEpilogueOps];
   const float *bias;
+  // Set by the dense launchers: accumulate by letting the TMA stores add to C (possible when the
+  // stores go through TMA and no operation follows the accumulation), so C is never read.
+  int accumulate_by_tma;
 };
 
 // Splitting dense tiles over k. Tiles [0, first_split_tile) are computed whole; each later tile

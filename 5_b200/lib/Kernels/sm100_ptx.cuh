@@ -121,6 +121,15 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t sr
                : "memory");
 }
 
+// Same box, added to what global memory holds (fp32 add performed at the memory side): C += tile
+// without the kernel ever reading C.
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap *map, uint32_t src_smem, int32_t x, int32_t y) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+               :
+               : "l"(reinterpret_cast<uint64_t>(map)), "r"(src_smem), "r"(x), "r"(y)
+               : "memory");
+}
+
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 
 // Until the stores this thread committed have finished *reading* shared memory (the source may

@@ -369,8 +369,9 @@ def run_gpu_arm(args, ranks: Ranks) -> None:
     total_flops = workloads.flops(w.m, w.n, w.k)
 
     # ---- warm-up, then the timed region (device time, max over ranks) ----------------------
+    bound = ctx.bind_gemm(da, db, dc, **gemm_kwargs)  # arguments marshalled once; launch() is one C call
     for _ in range(max(args.warmup, 3)):
-        ctx.gemm(da, db, dc, **gemm_kwargs)
+        bound.launch()
     ctx.synchronize()
     sampler = ClockSampler(ranks.local_rank)
     sampler.start()
@@ -381,7 +382,7 @@ def run_gpu_arm(args, ranks: Ranks) -> None:
     t_begin = time.perf_counter()
     start_ev.record()
     for _ in range(args.steps):
-        ctx.gemm(da, db, dc, **gemm_kwargs)
+        bound.launch()
     stop_ev.record()
     elapsed_ms = stop_ev.elapsed_ms_since(start_ev)
     ctx.synchronize()
@@ -395,7 +396,7 @@ def run_gpu_arm(args, ranks: Ranks) -> None:
         c_begin = time.perf_counter()
         while time.perf_counter() - c_begin < 0.5:
             for _ in range(8):
-                ctx.gemm(da, db, dc, **gemm_kwargs)
+                bound.launch()
             ctx.synchronize()
         clocks = sampler.summary(c_begin, time.perf_counter())
         clocks["note"] = "sampled over a 0.5 s continuation of the timed launches"

@@ -372,6 +372,23 @@ def test_dense_split_of_the_last_round(shape, gpu_ctx, monkeypatch) -> None:
         buf.free()
 
 
+def test_bound_gemm_launches_like_gemm(gpu_ctx) -> None:
+    a, b = random_inputs(300, 520, 136, "float16", scale=0.25)
+    bias = np.linspace(-1, 1, 520).astype(np.float32)
+    da, db, dbias = gpu_ctx.to_device(a), gpu_ctx.to_device(b), gpu_ctx.to_device(bias)
+    dc, dd = gpu_ctx.empty((300, 520), np.float32), gpu_ctx.empty((300, 520), np.float32)
+    ops = (("bias",), ("max", 0.0))
+    gpu_ctx.gemm(da, db, dc, epilogue=ops, bias=dbias)
+    bound = gpu_ctx.bind_gemm(da, db, dd, epilogue=ops, bias=dbias)
+    for _ in range(3):
+        dd.fill_bytes(0xFF)
+        bound.launch()
+        gpu_ctx.synchronize()
+        assert np.array_equal(dd.to_numpy(), dc.to_numpy())
+    with pytest.raises(ValueError, match="bias must be a float32 buffer of n values"):
+        gpu_ctx.bind_gemm(da, db, dd, epilogue=ops, bias=da)
+
+
 @pytest.mark.parametrize("seed", range(6))
 def test_random_shapes(seed: int, gpu_ctx) -> None:
     """Seeded random shapes, small and awkward ones included, in both element types and both B
