@@ -66,28 +66,6 @@ __device__ __forceinline__ float4 finish_group(float4 v, const float *dst, int c
   return v;
 }
 
-// The operations alone, on four values whose bias (if any) has already been fetched.
-__device__ __forceinline__ float4 apply_ops(float4 v, float4 bias, const Epilogue &ep) {
-#pragma unroll
-  for (int i = 0; i < kMaxEpilogueOps; ++i) {
-    if (i < ep.op_count) {
-      const int kind = ep.op_kind[i];
-      const float s = ep.op_value[i];
-      const float4 x = kind == kEpilogueBiasColumn ? bias : make_float4(s, s, s, s);
-      if (kind == kEpilogueScale) {
-        v.x *= x.x; v.y *= x.y; v.z *= x.z; v.w *= x.w;
-      } else if (kind == kEpilogueMax) {
-        v.x = fmaxf(v.x, x.x); v.y = fmaxf(v.y, x.y); v.z = fmaxf(v.z, x.z); v.w = fmaxf(v.w, x.w);
-      } else if (kind == kEpilogueMin) {
-        v.x = fminf(v.x, x.x); v.y = fminf(v.y, x.y); v.z = fminf(v.z, x.z); v.w = fminf(v.w, x.w);
-      } else {
-        v.x += x.x; v.y += x.y; v.z += x.z; v.w += x.w;
-      }
-    }
-  }
-  return v;
-}
-
 // The operations on the eight groups a lane stores per chunk. The kind of each operation is the
 // same for the whole grid, so it is branched on once per chunk and the work inside is one
 // instruction per value. `bias_of(i)` gives the four bias values of group i.
@@ -152,6 +130,36 @@ __device__ __forceinline__ void prefetch_c_tile_row(const float *c, long long ld
   const float *p = c + static_cast<long long>(row) * ldc;
   for (int col = col_base; col < col_base + columns && col < n; col += 32)
     asm volatile("prefetch.global.L2 [%0];" ::"l"(p + col));
+}
+
+// The operations on N values of one column (all take the same bias), the kind of each operation
+// branched on once for the lot.
+template <int N>
+__device__ __forceinline__ void apply_ops_to_column(float (&v)[N], float bias, const Epilogue &ep) {
+#pragma unroll
+  for (int op = 0; op < kMaxEpilogueOps; ++op) {
+    if (op >= ep.op_count)
+      break;
+    const int kind = ep.op_kind[op];
+    const float x = kind == kEpilogueBiasColumn ? bias : ep.op_value[op];
+    if (kind == kEpilogueScale) {
+#pragma unroll
+      for (int j = 0; j < N; ++j)
+        v[j] *= x;
+    } else if (kind == kEpilogueMax) {
+#pragma unroll
+      for (int j = 0; j < N; ++j)
+        v[j] = fmaxf(v[j], x);
+    } else if (kind == kEpilogueMin) {
+#pragma unroll
+      for (int j = 0; j < N; ++j)
+        v[j] = fminf(v[j], x);
+    } else {
+#pragma unroll
+      for (int j = 0; j < N; ++j)
+        v[j] += x;
+    }
+  }
 }
 
 // The operations on a chunk that is still in its tensor-memory layout (lane = row, r[j] = column

@@ -251,13 +251,15 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a,
           for (int j = 0; j < 8; ++j)
             previous[j] = (ep.accumulate && mm0 + j < m && col < n)
                               ? __ldcs(c + static_cast<long long>(mm0 + j) * ldc + col) : 0.0f;
+          float v[8];
 #pragma unroll
           for (int j = 0; j < 8; ++j)
-            if (mm0 + j < m && col < n) {
-              const float4 v = apply_ops(make_float4(__uint_as_float(r[mm0 + j]) + previous[j], 0.0f, 0.0f, 0.0f),
-                                         make_float4(bias, 0.0f, 0.0f, 0.0f), ep);
-              __stcs(c + static_cast<long long>(mm0 + j) * ldc + col, v.x);
-            }
+            v[j] = __uint_as_float(r[mm0 + j]) + previous[j];
+          apply_ops_to_column(v, bias, ep);
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            if (mm0 + j < m && col < n)
+              __stcs(c + static_cast<long long>(mm0 + j) * ldc + col, v[j]);
         }
         continue;
       }
@@ -296,14 +298,13 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a,
             for (int j = 0; j < 8; ++j)
               sums[j] += part[j];
           }
+          if (fused)
+            apply_ops_to_column(sums, bias, ep);
           if (col < n) {
 #pragma unroll
             for (int j = 0; j < 8; ++j)
-              if (mm0 + j < m) {
-                const float4 v = apply_ops(make_float4(sums[j], 0.0f, 0.0f, 0.0f),
-                                           make_float4(bias, 0.0f, 0.0f, 0.0f), ep);
-                __stcs(c + static_cast<long long>(mm0 + j) * ldc + col, fused ? v.x : sums[j]);
-              }
+              if (mm0 + j < m)
+                __stcs(c + static_cast<long long>(mm0 + j) * ldc + col, sums[j]);
           }
         }
         if (lane == 0)
