@@ -141,6 +141,26 @@ def test_plan_with_accumulate_and_fused_operations() -> None:
     assert b"epilogue_kind[0]" in lib.hcCudaContextLastError(None)
 
 
+def test_plan_splits_dense_tiles_that_do_not_fill_a_round() -> None:
+    """Few tiles and a long k: every tile is split. More tiles than CTAs with a small remainder and
+    k >= 8192: only the last round's tiles. Otherwise nothing is split."""
+    few = cuda.plan_gemm(128, 8192, 8192, "float16")
+    assert (few.variant, few.tiles_m, few.tiles_n, few.splits, few.first_split_tile, few.grid) == ("dense", 1, 32, 4, 0, 128)
+    assert few.scratch_bytes == 32 * 4 * 128 * 256 * 4 and few.kernel_launches == 1
+    one_tile = cuda.plan_gemm(256, 256, 32768, "bfloat16")
+    assert one_tile.splits == 32 and one_tile.grid == 64  # 32 CTA pairs
+    tail = cuda.plan_gemm(4864, 1024, 8192, "float16")  # 19 x 4 pair tiles = one round of 74 + 2
+    assert (tail.splits, tail.first_split_tile, tail.grid) == (8, 74, 148)
+    assert tail.scratch_bytes == 2 * 8 * 256 * 256 * 4
+    for shape in ((8192, 8192, 8192), (4096, 4096, 4096), (4095, 3073, 1031), (512, 8192, 8192), (1024, 1024, 1024)):
+        plan = cuda.plan_gemm(*shape, "float16")
+        assert plan.splits == 1 and plan.first_split_tile == 0 and plan.scratch_bytes % (1 << 10) == 0, (shape, plan)
+    # Short k: the k-loop a split would shorten is not worth its partial tiles.
+    assert cuda.plan_gemm(128, 8192, 512, "float16").splits == 1
+    # Fewer SMs, more rounds.
+    assert cuda.plan_gemm(128, 8192, 8192, "float16", sm_count=32).splits == 1
+
+
 def test_plan_degenerate_shapes() -> None:
     assert cuda.plan_gemm(0, 5, 7, "float16").variant == "noop"
     assert cuda.plan_gemm(5, 0, 7, "float16").kernel_launches == 0
