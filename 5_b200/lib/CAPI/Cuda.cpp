@@ -88,6 +88,17 @@ struct HcCudaEvent {
   cudaEvent_t event = nullptr;
 };
 
+// One remembered cuTensorMapEncodeTiled result (see encode_map).
+constexpr unsigned kMapCacheEntries = 16;
+struct MapCacheEntry {
+  bool valid = false;
+  int dtype = 0;
+  const void *base = nullptr;
+  uint64_t inner = 0, outer = 0, pitch_bytes = 0;
+  uint32_t box_inner = 0, box_outer = 0;
+  CUtensorMap map;
+};
+
 struct HcCudaContext {
   int device = -1;
   cudaStream_t stream = nullptr;
@@ -111,6 +122,8 @@ struct HcCudaContext {
   EncodeTiledFn encode = nullptr;
   int group_n = 8;
   bool c_tma_store = true;  // HC_CUDA_C_TMA_STORE=0 keeps ordinary stores (tuning aid)
+  MapCacheEntry map_cache[kMapCacheEntries];  // recently encoded tensor maps, see encode_map
+  unsigned map_cache_next = 0;
   ncclComm_t comm = nullptr;
   int nranks = 0;
   int rank = -1;
@@ -361,6 +374,15 @@ constexpr int kMapFloat32 = -1;  // encode_map's dtype for C; otherwise an HcCud
 
 int encode_map(HcCudaContext *ctx, CUtensorMap *map, int dtype, const void *base, uint64_t inner,
                uint64_t outer, uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_outer) {
+  // A tensor map is a pure function of these arguments, and callers launch the same product on
+  // the same buffers over and over: keep the last few (the caller holds ctx->mu).
+  for (MapCacheEntry &e : ctx->map_cache) {
+    if (e.valid && e.base == base && e.inner == inner && e.outer == outer && e.pitch_bytes == pitch_bytes &&
+        e.box_inner == box_inner && e.box_outer == box_outer && e.dtype == dtype) {
+      *map = e.map;
+      return HC_CUDA_OK;
+    }
+  }
   const cuuint64_t dims[2] = {inner, outer};
   const cuuint64_t strides[1] = {pitch_bytes};
   const cuuint32_t box[2] = {box_inner, box_outer};
@@ -377,6 +399,9 @@ int encode_map(HcCudaContext *ctx, CUtensorMap *map, int dtype, const void *base
                 "cuTensorMapEncodeTiled failed with CUresult %d (base %p, dims %llu x %llu, pitch %llu)",
                 static_cast<int>(res), base, (unsigned long long)inner, (unsigned long long)outer,
                 (unsigned long long)pitch_bytes);
+  MapCacheEntry &slot = ctx->map_cache[ctx->map_cache_next];
+  ctx->map_cache_next = (ctx->map_cache_next + 1) % kMapCacheEntries;
+  slot = MapCacheEntry{true, dtype, base, inner, outer, pitch_bytes, box_inner, box_outer, *map};
   return HC_CUDA_OK;
 }
 
