@@ -116,8 +116,10 @@ struct HcCudaContext {
   static constexpr int kMaxPanels = 8;
   cudaStream_t copy_in = nullptr;
   cudaStream_t copy_out = nullptr;
-  cudaEvent_t panel_in[kMaxPanels] = {};
-  cudaEvent_t panel_done[kMaxPanels] = {};
+  static constexpr int kMaxSteps = 2 * kMaxPanels;  // a panel of A and one of B per step
+  cudaEvent_t panel_in[kMaxSteps] = {};
+  cudaEvent_t panel_done[kMaxSteps] = {};
+  bool planning_host_panels = false;  // plan_gemm then never splits k: see hcCudaGemmHost
   cudaEvent_t fence_event = nullptr;
   EncodeTiledFn encode = nullptr;
   int group_n = 8;
@@ -291,7 +293,11 @@ int plan_gemm(const HcCudaContext *ctx, const HcCudaGemmArgs *args, int sm_count
     const int slots = pairs ? sm_count / 2 : sm_count;
     long long first_split_tile = 0;
     plan->splits = hc::sm100::dense_choose_splits(tiles, slots, num_kb, &first_split_tile);
-    if (const char *forced = std::getenv("HC_CUDA_DENSE_SPLITS")) {  // tuning aid: split every tile
+    if (ctx != nullptr && ctx->planning_host_panels) {
+      // The panels of one host-buffer product must give the bits of the unsplit product.
+      plan->splits = 1;
+      first_split_tile = 0;
+    } else if (const char *forced = std::getenv("HC_CUDA_DENSE_SPLITS")) {  // tuning aid: split every tile
       const int v = std::atoi(forced);
       if (v >= 1 && v <= num_kb && v <= 64) {
         plan->splits = v;
@@ -548,7 +554,7 @@ int ensure_copy_streams(HcCudaContext *ctx) {
     return HC_CUDA_OK;
   HC_TRY_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->copy_in, cudaStreamNonBlocking));
   HC_TRY_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->copy_out, cudaStreamNonBlocking));
-  for (int i = 0; i < HcCudaContext::kMaxPanels; ++i) {
+  for (int i = 0; i < HcCudaContext::kMaxSteps; ++i) {
     HC_TRY_CUDA(ctx, cudaEventCreateWithFlags(&ctx->panel_in[i], cudaEventDisableTiming));
     HC_TRY_CUDA(ctx, cudaEventCreateWithFlags(&ctx->panel_done[i], cudaEventDisableTiming));
   }
@@ -677,7 +683,7 @@ int hcCudaContextDestroy(HcCudaContext *ctx) {
     for (void *p : ctx->stage)
       if (p != nullptr)
         cudaFree(p);
-    for (int i = 0; i < HcCudaContext::kMaxPanels; ++i) {
+    for (int i = 0; i < HcCudaContext::kMaxSteps; ++i) {
       if (ctx->panel_in[i] != nullptr)
         cudaEventDestroy(ctx->panel_in[i]);
       if (ctx->panel_done[i] != nullptr)
@@ -1025,52 +1031,148 @@ int hcCudaGemmHost(HcCudaContext *ctx, const HcCudaGemmArgs *args) {
     return synchronize_locked(ctx);
   }
 
-  // Pipelined form. PCIe carries both directions at once, so the rows of C of one panel travel
-  // back while the next panels of A are still arriving and being multiplied; the call then takes
-  // about (time to send B) + max(time to send A, time to fetch C) instead of the sum of all four.
   if (int rc = ensure_copy_streams(ctx))
     return rc;
-  size_t panel_rows = (m + HcCudaContext::kMaxPanels - 1) / HcCudaContext::kMaxPanels;
-  panel_rows = static_cast<size_t>(round_up(static_cast<int64_t>(panel_rows), 256));
-  const int panels = static_cast<int>((m + panel_rows - 1) / panel_rows);
   // Everything already queued on the main stream comes first.
   HC_TRY_CUDA(ctx, cudaEventRecord(ctx->fence_event, ctx->stream));
   HC_TRY_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_in, ctx->fence_event, 0));
   HC_TRY_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_out, ctx->fence_event, 0));
-  HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(ctx->stage[1], ldb * 2, args->b, static_cast<size_t>(args->ldb) * 2,
-                                     b_cols * 2, b_rows, cudaMemcpyHostToDevice, ctx->copy_in));
-  for (int p = 0; p < panels; ++p) {
-    const size_t row0 = static_cast<size_t>(p) * panel_rows;
-    const size_t rows = row0 + panel_rows <= m ? panel_rows : m - row0;
-    const char *a_src = static_cast<const char *>(args->a) + row0 * static_cast<size_t>(args->lda) * 2;
-    char *a_dst = static_cast<char *>(ctx->stage[0]) + row0 * lda * 2;
-    HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(a_dst, lda * 2, a_src, static_cast<size_t>(args->lda) * 2, k * 2, rows,
-                                       cudaMemcpyHostToDevice, ctx->copy_in));
-    if (args->accumulate)  // this panel's rows of C are the starting values of its sums
-      HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(static_cast<float *>(ctx->stage[2]) + row0 * ldc, ldc * 4,
-                                         args->c + row0 * static_cast<size_t>(args->ldc),
-                                         static_cast<size_t>(args->ldc) * 4, n * 4, rows,
-                                         cudaMemcpyHostToDevice, ctx->copy_in));
-    HC_TRY_CUDA(ctx, cudaEventRecord(ctx->panel_in[p], ctx->copy_in));
-    HC_TRY_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->panel_in[p], 0));
+  struct PanelsPlanning {  // the sub-products below are planned without k-splits
+    HcCudaContext *ctx;
+    explicit PanelsPlanning(HcCudaContext *c) : ctx(c) { ctx->planning_host_panels = true; }
+    ~PanelsPlanning() { ctx->planning_host_panels = false; }
+  } planning_guard(ctx);
+
+  // One sub-product C[row0:row0+rows, col0:col0+cols] on the staged operands, then its way home.
+  int done_events = 0;
+  auto multiply_and_fetch = [&](size_t row0, size_t rows, size_t col0, size_t cols, cudaEvent_t inputs_ready) -> int {
+    HC_TRY_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, inputs_ready, 0));
     HcCudaGemmArgs part = dev;
     part.m = static_cast<int64_t>(rows);
-    part.a = a_dst;
-    part.c = static_cast<float *>(ctx->stage[2]) + row0 * ldc;
+    part.n = static_cast<int64_t>(cols);
+    part.a = static_cast<const char *>(dev.a) + row0 * lda * 2;
+    part.b = static_cast<const char *>(dev.b) + (b_nk ? col0 * ldb : col0) * 2;
+    part.c = dev.c + row0 * ldc + col0;
+    if (has_bias)
+      part.bias = dev.bias + col0;
     HcCudaGemmPlanInfo part_plan;
     if (int rc = plan_gemm(ctx, &part, ctx->prop.multiProcessorCount, false, &part_plan))
       return rc;
     if (int rc = enqueue_gemm(ctx, &part, part_plan))
       return rc;
-    HC_TRY_CUDA(ctx, cudaEventRecord(ctx->panel_done[p], ctx->stream));
-    HC_TRY_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_out, ctx->panel_done[p], 0));
-    HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(args->c + row0 * static_cast<size_t>(args->ldc),
-                                       static_cast<size_t>(args->ldc) * 4, part.c, ldc * 4, n * 4, rows,
+    cudaEvent_t done = ctx->panel_done[done_events++];
+    HC_TRY_CUDA(ctx, cudaEventRecord(done, ctx->stream));
+    HC_TRY_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_out, done, 0));
+    HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(args->c + row0 * static_cast<size_t>(args->ldc) + col0,
+                                       static_cast<size_t>(args->ldc) * 4, part.c, ldc * 4, cols * 4, rows,
                                        cudaMemcpyDeviceToHost, ctx->copy_out));
+    return HC_CUDA_OK;
+  };
+  auto finish = [&]() -> int {
+    HC_TRY_CUDA(ctx, cudaEventRecord(ctx->fence_event, ctx->copy_out));
+    HC_TRY_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->fence_event, 0));
+    return synchronize_locked(ctx);
+  };
+  // Panels are multiples of 256 rows (or columns); a remainder shorter than that joins the last one.
+  auto panel_size = [](size_t total) {
+    const size_t size = (total + HcCudaContext::kMaxPanels - 1) / HcCudaContext::kMaxPanels;
+    return static_cast<size_t>(round_up(static_cast<int64_t>(size), 256));
+  };
+  auto panel_count = [](size_t total, size_t size) {
+    const size_t count = total / size;
+    return static_cast<int>(count == 0 || total - count * size >= 256 ? count + 1 : count);
+  };
+  auto panel_extent = [](size_t start, size_t total, size_t size) {
+    return total - start < size + 256 ? total - start : size;
+  };
+  const size_t panel_rows = panel_size(m);
+  const int row_panels = panel_count(m, panel_rows);
+
+  // Pinned host memory can be copied in strided pieces at full rate; with it, and a C that does
+  // not have to travel to the device first, A and B are sent in alternating panels (below).
+  auto is_pinned = [](const void *p) {
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) {
+      cudaGetLastError();
+      return false;
+    }
+    return attr.type == cudaMemoryTypeHost;
+  };
+  const bool square = n >= 2048 && !args->accumulate && is_pinned(args->a) && is_pinned(args->b) &&
+                      is_pinned(args->c) && std::getenv("HC_CUDA_ROW_PANELS_ONLY") == nullptr;
+  if (!square) {
+    // Row panels. PCIe carries both directions at once, so the rows of C of one panel travel back
+    // while the next panels of A are still arriving and being multiplied; the call then takes
+    // about (time to send B) + max(time to send A, time to fetch C) instead of the sum of all four.
+    HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(ctx->stage[1], ldb * 2, args->b, static_cast<size_t>(args->ldb) * 2,
+                                       b_cols * 2, b_rows, cudaMemcpyHostToDevice, ctx->copy_in));
+    for (int p = 0; p < row_panels; ++p) {
+      const size_t row0 = static_cast<size_t>(p) * panel_rows;
+      const size_t rows = panel_extent(row0, m, panel_rows);
+      HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(static_cast<char *>(ctx->stage[0]) + row0 * lda * 2, lda * 2,
+                                         static_cast<const char *>(args->a) + row0 * static_cast<size_t>(args->lda) * 2,
+                                         static_cast<size_t>(args->lda) * 2, k * 2, rows, cudaMemcpyHostToDevice,
+                                         ctx->copy_in));
+      if (args->accumulate)  // this panel's rows of C are the starting values of its sums
+        HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(static_cast<float *>(ctx->stage[2]) + row0 * ldc, ldc * 4,
+                                           args->c + row0 * static_cast<size_t>(args->ldc),
+                                           static_cast<size_t>(args->ldc) * 4, n * 4, rows,
+                                           cudaMemcpyHostToDevice, ctx->copy_in));
+      HC_TRY_CUDA(ctx, cudaEventRecord(ctx->panel_in[p], ctx->copy_in));
+      if (int rc = multiply_and_fetch(row0, rows, 0, n, ctx->panel_in[p]))
+        return rc;
+    }
+    return finish();
   }
-  HC_TRY_CUDA(ctx, cudaEventRecord(ctx->fence_event, ctx->copy_out));
-  HC_TRY_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->fence_event, 0));
-  return synchronize_locked(ctx);
+
+  // Alternating panels. Waiting for all of B before the first product leaves the return path idle
+  // for the time B takes. Instead row panels of A and column panels of B are sent in turn, and
+  // after each arrival everything that has become computable is multiplied and sent back: A_s
+  // gives C[rows s, columns of B_0..B_{s-1}], B_s gives C[rows of A_0..A_s, columns s]. The
+  // computable part of C grows with the square of what has arrived, so the return path starts after
+  // one panel of each instead of after a whole operand, and both directions stay busy to the end.
+  const size_t panel_cols = panel_size(n);
+  const int col_panels = panel_count(n, panel_cols);
+  int in_events = 0;
+  size_t rows_sent = 0, cols_sent = 0;
+  for (int step = 0; step < (row_panels > col_panels ? row_panels : col_panels); ++step) {
+    if (step < row_panels) {
+      const size_t row0 = rows_sent;
+      const size_t rows = panel_extent(row0, m, panel_rows);
+      HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(static_cast<char *>(ctx->stage[0]) + row0 * lda * 2, lda * 2,
+                                         static_cast<const char *>(args->a) + row0 * static_cast<size_t>(args->lda) * 2,
+                                         static_cast<size_t>(args->lda) * 2, k * 2, rows, cudaMemcpyHostToDevice,
+                                         ctx->copy_in));
+      cudaEvent_t arrived = ctx->panel_in[in_events++];
+      HC_TRY_CUDA(ctx, cudaEventRecord(arrived, ctx->copy_in));
+      rows_sent += rows;
+      if (cols_sent > 0)
+        if (int rc = multiply_and_fetch(row0, rows, 0, cols_sent, arrived))
+          return rc;
+    }
+    if (step < col_panels) {
+      const size_t col0 = cols_sent;
+      const size_t cols = panel_extent(col0, n, panel_cols);
+      if (b_nk) {  // stored [n, k]: the panel is a block of rows
+        HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(static_cast<char *>(ctx->stage[1]) + col0 * ldb * 2, ldb * 2,
+                                           static_cast<const char *>(args->b) + col0 * static_cast<size_t>(args->ldb) * 2,
+                                           static_cast<size_t>(args->ldb) * 2, k * 2, cols, cudaMemcpyHostToDevice,
+                                           ctx->copy_in));
+      } else {     // stored [k, n]: a block of columns, k pieces of `cols` elements
+        HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(static_cast<char *>(ctx->stage[1]) + col0 * 2, ldb * 2,
+                                           static_cast<const char *>(args->b) + col0 * 2,
+                                           static_cast<size_t>(args->ldb) * 2, cols * 2, k, cudaMemcpyHostToDevice,
+                                           ctx->copy_in));
+      }
+      cudaEvent_t arrived = ctx->panel_in[in_events++];
+      HC_TRY_CUDA(ctx, cudaEventRecord(arrived, ctx->copy_in));
+      cols_sent += cols;
+      if (rows_sent > 0)
+        if (int rc = multiply_and_fetch(0, rows_sent, col0, cols, arrived))
+          return rc;
+    }
+  }
+  return finish();
 }
 
 int hcCudaSelfTestDeviceTimeout(HcCudaContext *ctx, int64_t budget_cycles) {

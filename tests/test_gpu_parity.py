@@ -542,6 +542,48 @@ def test_numpy_views_and_strides() -> None:
     assert np.array_equal(c3, c2)
 
 
+@pytest.mark.parametrize("b_transposed", [False, True])
+def test_large_product_on_pinned_buffers_in_alternating_panels(gpu_ctx, b_transposed: bool) -> None:
+    """Pinned host arrays: A and B travel in alternating panels and C returns block by block. The
+    result must equal the device-buffer path bit for bit, with and without fused operations, and
+    leave the surroundings of a strided C alone."""
+    m, n, k = 3000, 4100, 1100
+    a, b = random_inputs(m, n, k, "float16", scale=0.25)
+    b_host = np.ascontiguousarray(b.T) if b_transposed else b
+    pa, pb = cuda.pinned_empty(a.shape, a.dtype), cuda.pinned_empty(b_host.shape, b_host.dtype)
+    pc_store = cuda.pinned_empty((m + 2, n + 6), np.float32)
+    pa[...] = a
+    pb[...] = b_host
+    pc_store[...] = np.nan
+    pc = pc_store[1:-1, 3:-3]
+    gpu_ctx.gemm_host(pa, pb, pc, b_transposed=b_transposed)
+    da, db = gpu_ctx.to_device(a), gpu_ctx.to_device(b_host)
+    dc = gpu_ctx.empty((m, n), np.float32)
+    gpu_ctx.gemm(da, db, dc, b_transposed=b_transposed)
+    gpu_ctx.synchronize()
+    assert np.array_equal(np.ascontiguousarray(pc), dc.to_numpy())
+    assert np.isnan(pc_store[0]).all() and np.isnan(pc_store[-1]).all()
+    assert np.isnan(pc_store[:, :3]).all() and np.isnan(pc_store[:, -3:]).all()
+    assert workloads.check_against_float64(np.ascontiguousarray(pc), a, b, rows=_sample_rows(m))["ok"]
+    bias = np.linspace(-2, 2, n).astype(np.float32)
+    ops = (("scale", 0.5), ("bias",), ("max", 0.0))
+    gpu_ctx.gemm_host(pa, pb, pc, b_transposed=b_transposed, epilogue=ops, bias=bias)
+    dbias = gpu_ctx.to_device(bias)
+    gpu_ctx.gemm(da, db, dc, b_transposed=b_transposed, epilogue=ops, bias=dbias)
+    gpu_ctx.synchronize()
+    assert np.array_equal(np.ascontiguousarray(pc), dc.to_numpy())
+    # Accumulation needs C on the device first: the row-panel schedule, same bits as one launch.
+    c0 = np.random.default_rng(3).standard_normal((m, n)).astype(np.float32)
+    pc[...] = c0
+    gpu_ctx.gemm_host(pa, pb, pc, b_transposed=b_transposed, accumulate=True)
+    dc.copy_from_host(c0)
+    gpu_ctx.gemm(da, db, dc, b_transposed=b_transposed, accumulate=True)
+    gpu_ctx.synchronize()
+    assert np.array_equal(np.ascontiguousarray(pc), dc.to_numpy())
+    for buf in (da, db, dc, dbias):
+        buf.free()
+
+
 def test_large_ragged_product_on_pageable_numpy_buffers(gpu_ctx) -> None:
     """Config 3 through the handle on ordinary (pageable) NumPy arrays: large enough for the
     host call to pipeline its copies in row panels. The result must equal the device-buffer
