@@ -48,7 +48,7 @@ def _tile_origin(tile_row, tile_col):
     return tile_row * TILE_M, tile_col * TILE_N
 
 
-MEMBERS = ("plain", "accumulate", "fused")
+MEMBERS = ("plain", "accumulate", "fused", "narrow")
 FUSED_SCALE = 0.125  # the constant the "fused" member multiplies its accumulators by
 
 
@@ -207,7 +207,9 @@ def build_tiled_wmma_matmul(element_type, b_transposed=False, member="plain"):
       "accumulate"  C = C + A @ B: the accumulators are loaded from `c` instead of zeroed;
       "fused"       C = maximum(FUSED_SCALE * (A @ B) + bias, 0) with a fourth buffer
                     `bias: Buffer[N, float32]`: element-wise statements between the k-loop and
-                    the store, which the NVIDIA target folds into the store of C.
+                    the store, which the NVIDIA target folds into the store of C;
+      "narrow"      C = (A @ B).astype(element_type) with `c: Buffer[M, N, element_type]`: fp32
+                    accumulation, 16-bit output.
     """
     element_type = np.dtype(element_type).type
     if member not in MEMBERS:
@@ -281,6 +283,27 @@ def build_tiled_wmma_matmul(element_type, b_transposed=False, member="plain"):
 
         tiled_wmma_matmul_fused.__name__ = f"tiled_wmma_matmul_fused_{suffix}"
         return tiled_wmma_matmul_fused
+
+    if member == "narrow":
+
+        @kernel(**_LAUNCH)
+        def tiled_wmma_matmul_narrow(
+            group,
+            a: Buffer[M, K, element_type],
+            b: Buffer[K, N, element_type],
+            c: Buffer[M, N, element_type],
+        ) -> None:
+            row0, col0 = _tile_origin(group.group_id[0], group.group_id[1])
+            acc = zero_accumulators(group)
+            for k0 in range(0, a.shape[1], TILE_K):
+                a_tile = group.load(a[row0 : row0 + TILE_M, k0 : k0 + TILE_K], shape=(TILE_M, TILE_K))
+                b_tile = group.load(b[k0 : k0 + TILE_K, col0 : col0 + TILE_N], shape=(TILE_K, TILE_N))
+                acc = multiply_accumulate(group, a_tile, b_tile, acc)
+            acc = acc.astype(element_type)
+            store_accumulators(group, c, row0, col0, acc)
+
+        tiled_wmma_matmul_narrow.__name__ = f"tiled_wmma_matmul_narrow_{suffix}"
+        return tiled_wmma_matmul_narrow
 
     @kernel(**_LAUNCH)
     def tiled_wmma_matmul(

@@ -103,7 +103,7 @@ class CompiledKernel:
         if not c.flags.writeable:
             raise LaunchError(f"{plan.c_param} must be writeable")
         # C's previous contents start the sums of an accumulating kernel.
-        staged = np.array(c, dtype=np.float32, order="C") if plan.accumulate else np.empty(c.shape, np.float32)
+        staged = np.array(c, order="C") if plan.accumulate else np.empty(c.shape, c.dtype)
         ctx.gemm_host(a_host, b_host, staged, bias=bias_host, **options)
         c[...] = staged
 

@@ -52,6 +52,7 @@ ScheduleSource = Path | str | None
 
 NVIDIA_SM100A = "nvidia-sm100a"
 _SUPPORTED_INPUT_DTYPES = ("float16", "bfloat16")
+_SUPPORTED_OUTPUT_DTYPES = ("float32", "float16", "bfloat16")
 _PROBE_SHAPES = ((1, 1, 1), (16, 16, 16), (17, 19, 18), (64, 48, 80), (4095, 3073, 1031))
 
 
@@ -67,7 +68,7 @@ class GemmContract:
     n_dim: Any
     k_dim: Any
     input_dtype: str  # "float16" | "bfloat16"
-    output_dtype: str  # "float32"
+    output_dtype: str  # "float32", or "float16" / "bfloat16": the float32 result rounded on store
     tile: tuple[int, int, int]  # WMMA tile (m, n, k) of the kernel as written
     wave_size: int
     accumulators_per_lane: int
@@ -316,7 +317,7 @@ _MAX_EPILOGUE_OPS = 4
 
 def _check_body(kernel_fn: Any, params: list[str], a: str, b: str, c: str, tile: tuple[int, int, int],
                 k_dim: Any, b_transposed: bool = False, bias: str | None = None,
-                facts: dict[str, Any] | None = None) -> list[str]:
+                facts: dict[str, Any] | None = None, output_dtype: str = "float32") -> list[str]:
     """Structural check of the k-loop: `for k0 in range(0, K, tk)` with one masked load of an
     A window `a[rows, k0:k0+tk]` and one of a B window `b[k0:k0+tk, cols]`, then a store
     that receives `c`. Returns problems (empty when the body has the expected shape).
@@ -384,7 +385,7 @@ def _check_body(kernel_fn: Any, params: list[str], a: str, b: str, c: str, tile:
             problems.append(f"axis {1 - axis} of the `{name}` window must not depend on the k-loop variable")
     if shape.c_uses_after_loop < 1:
         problems.append(f"`{c}` must be passed to a store after the k-loop")
-    surroundings = _loop_surroundings(fn_node, loop, c, bias, const_value, problems)
+    surroundings = _loop_surroundings(fn_node, loop, c, bias, const_value, problems, output_dtype, consts)
     if facts is not None:
         facts.update(surroundings)
     return problems
@@ -412,8 +413,26 @@ def _number(node: ast.AST | None, const_value: Any) -> float | None:
     return value if np.isfinite(value) else None
 
 
+def _dtype_name_of(node: ast.AST, consts: dict[str, Any]) -> str | None:
+    """The NumPy dtype name an expression such as `np.float16`, `ml_dtypes.bfloat16` or a closure
+    variable holding a scalar type denotes, or None."""
+    try:
+        if isinstance(node, ast.Name):
+            value = consts[node.id]
+        elif isinstance(node, ast.Attribute) and isinstance(node.value, ast.Name):
+            value = getattr(consts[node.value.id], node.attr)
+        elif isinstance(node, ast.Constant) and isinstance(node.value, str):
+            value = node.value
+        else:
+            return None
+        return np.dtype(value).name
+    except (KeyError, AttributeError, TypeError):
+        return None
+
+
 def _loop_surroundings(fn_node: ast.AST, loop: ast.For, c: str, bias: str | None, const_value: Any,
-                       problems: list[str]) -> dict[str, Any]:
+                       problems: list[str], output_dtype: str = "float32",
+                       consts: dict[str, Any] | None = None) -> dict[str, Any]:
     """Reads the top-level statements before and after the k-loop (see `_check_body`)."""
     body = list(fn_node.body)
     if loop not in body:
@@ -446,8 +465,11 @@ def _loop_surroundings(fn_node: ast.AST, loop: ast.For, c: str, bias: str | None
     if not initialised:
         problems.append(f"`{acc}` must be initialised before the k-loop")
 
+    if accumulate and output_dtype != "float32":
+        problems.append(f"a kernel that loads its accumulators from `{c}` needs a float32 `{c}` (got {output_dtype})")
     ops: list[tuple] = []
     stored = False
+    narrowed = False  # the accumulators have been converted to the 16-bit type of `c`
     for stmt in body[at + 1:]:
         text = ast.unparse(stmt)
         if isinstance(stmt, ast.Expr) and isinstance(stmt.value, ast.Call) and c in call_names(stmt.value):
@@ -463,11 +485,23 @@ def _loop_surroundings(fn_node: ast.AST, loop: ast.For, c: str, bias: str | None
         ok_target = (isinstance(stmt, ast.Assign) and len(stmt.targets) == 1
                      and isinstance(stmt.targets[0], ast.Name) and stmt.targets[0].id == acc)
         op = _elementwise_op(stmt.value, acc, bias, const_value) if ok_target else None
+        if op is not None and op and op[0] == "astype":
+            target = _dtype_name_of(op[1], consts or {})
+            if target == "float32" and not narrowed:
+                continue
+            if target == output_dtype and target != "float32" and not narrowed:
+                narrowed = True
+                continue
+            op = None
+        elif op and narrowed:
+            problems.append(f"`{text}` runs on the 16-bit values: element-wise statements must come before "
+                            f"`{acc}.astype({output_dtype})`")
+            continue
         if op is None:
             problems.append(
                 f"`{text}` is not an element-wise statement this target folds into the store "
                 f"(`{acc} = {acc} * x`, `+ x`, `- x`, `np.maximum({acc}, x)`, `np.minimum({acc}, x)` with a "
-                f"numeric constant x, `{acc} = f(..., bias, ..., {acc})`, `{acc}.astype(np.float32)`)")
+                f"numeric constant x, `{acc} = f(..., bias, ..., {acc})`, `{acc}.astype(<float32 or the dtype of {c}>)`)")
         elif op:
             ops.append(op)
     if len(ops) > _MAX_EPILOGUE_OPS:
@@ -505,9 +539,8 @@ def _elementwise_op(value: ast.AST, acc: str, bias: str | None, const_value: Any
                 if x is not None:
                     return ("max" if name == "maximum" else "min", x)
             return None
-        if (name == "astype" and isinstance(func, ast.Attribute) and is_acc(func.value) and len(value.args) == 1
-                and ast.unparse(value.args[0]).split(".")[-1] == "float32"):
-            return ()
+        if name == "astype" and isinstance(func, ast.Attribute) and is_acc(func.value) and len(value.args) == 1:
+            return ("astype", value.args[0])  # resolved by the caller against the dtype of c
         names = {arg.id for arg in value.args if isinstance(arg, ast.Name)}
         if bias is not None and bias in names and acc in names:
             return ("bias",)
@@ -600,13 +633,13 @@ def recognise_tiled_matmul(kernel_fn: Any) -> tuple[GemmContract | None, list[st
     b_transposed = False
     for ia, ib, ic in ((0, 1, 2), (0, 2, 1), (1, 0, 2), (1, 2, 0), (2, 0, 1), (2, 1, 0)):
         (pa, (am, ak), da), (pb, b_dims, db), (pc, (cm, cn), dc) = specs[ia], specs[ib], specs[ic]
-        if not (am == cm and dc == "float32" and da == db and da in _SUPPORTED_INPUT_DTYPES):
+        if not (am == cm and dc in _SUPPORTED_OUTPUT_DTYPES and da == db and da in _SUPPORTED_INPUT_DTYPES):
             continue
         for transposed in (False, True):
             bk, bn = (b_dims[1], b_dims[0]) if transposed else b_dims
             # With m == n == k as fixed equal extents the untransposed reading wins.
             if ak == bk and bn == cn and roles is None:
-                roles = (pa, pb, pc, am, bn, ak, da)
+                roles = (pa, pb, pc, am, bn, ak, da, dc)
                 b_transposed = transposed
         if roles is not None and (ia, ib, ic) == (0, 1, 2):
             break
@@ -614,9 +647,9 @@ def recognise_tiled_matmul(kernel_fn: Any) -> tuple[GemmContract | None, list[st
         described = ", ".join(f"{p}: Buffer{list(k)} {d}" for p, k, d in specs)
         return None, [
             f"{name}: buffers ({described}) are not a[M,K], b[K,N] (or b[N,K]) of one of "
-            f"{list(_SUPPORTED_INPUT_DTYPES)} and c[M,N] float32"
+            f"{list(_SUPPORTED_INPUT_DTYPES)} and c[M,N] of one of {list(_SUPPORTED_OUTPUT_DTYPES)}"
         ]
-    a, b, c, m_dim, n_dim, k_dim, input_dtype = roles
+    a, b, c, m_dim, n_dim, k_dim, input_dtype, output_dtype = roles
     bias = None
     if vectors:
         bias, (bias_dim,), bias_dtype = vectors[0]
@@ -643,7 +676,7 @@ def recognise_tiled_matmul(kernel_fn: Any) -> tuple[GemmContract | None, list[st
     wave, geometry_problems = _check_geometry(meta, {"m": m_dim, "n": n_dim, "k": k_dim}, tile, acc_len)
     problems.extend(geometry_problems)
     facts: dict[str, Any] = {}
-    problems.extend(_check_body(kernel_fn, params, a, b, c, tile, k_dim, b_transposed, bias, facts))
+    problems.extend(_check_body(kernel_fn, params, a, b, c, tile, k_dim, b_transposed, bias, facts, output_dtype))
     if problems:
         return None, [f"{name}: {p}" for p in problems]
 
@@ -653,7 +686,7 @@ def recognise_tiled_matmul(kernel_fn: Any) -> tuple[GemmContract | None, list[st
         return None, [f"{name}: {p}" for p in hook_problems]
     contract = GemmContract(
         kernel_name=name, a_param=a, b_param=b, c_param=c, m_dim=m_dim, n_dim=n_dim, k_dim=k_dim,
-        input_dtype=input_dtype, output_dtype="float32", tile=tile, wave_size=wave,
+        input_dtype=input_dtype, output_dtype=output_dtype, tile=tile, wave_size=wave,
         accumulators_per_lane=acc_len, intrinsic_name=intrinsic.__name__,
         intrinsic_const_attrs=tuple(sorted(intrinsic.__hc_intrinsic__.const_attrs)),
         has_target_lowering=NVIDIA_SM100A in lowerings,

@@ -38,7 +38,7 @@ __all__ = [
 F16, BF16 = 0, 1
 VARIANT_AUTO, VARIANT_DENSE, VARIANT_SKINNY, VARIANT_NOOP, VARIANT_ZERO_FILL, VARIANT_ELEMENTWISE = 0, 1, 2, 3, 4, 5
 VARIANT_NAMES = {0: "auto", 1: "dense", 2: "skinny", 3: "noop", 4: "zero_fill", 5: "elementwise"}
-API_VERSION = 3
+API_VERSION = 4
 # Element-wise operations fused into the store of C: ("scale", x), ("add", x), ("max", x),
 # ("min", x) and ("bias",) -- the last adds bias[column].
 EPILOGUE_KINDS = {"scale": 1, "add": 2, "max": 3, "min": 4, "bias": 5}
@@ -68,7 +68,7 @@ class _GemmArgs(ctypes.Structure):
         ("c", ctypes.c_void_p), ("ldc", ctypes.c_int64),
         ("b_layout", ctypes.c_int32), ("accumulate", ctypes.c_int32),
         ("epilogue_count", ctypes.c_int32), ("epilogue_kind", ctypes.c_int32 * 4),
-        ("epilogue_value", ctypes.c_float * 4), ("reserved", ctypes.c_int32),
+        ("epilogue_value", ctypes.c_float * 4), ("c_dtype", ctypes.c_int32),
         ("bias", ctypes.c_void_p),
     ]
 
@@ -185,6 +185,17 @@ def dtype_code(dtype: Any) -> int:
     raise ValueError(f"the CUDA backend multiplies float16 or bfloat16 matrices, got {name}")
 
 
+C_F32, C_F16, C_BF16 = 0, 1, 2  # element type of C (HcCudaCType)
+
+
+def c_dtype_code(dtype: Any) -> int:
+    name = dtype if isinstance(dtype, str) else np.dtype(dtype).name
+    codes = {"float32": C_F32, "float16": C_F16, "bfloat16": C_BF16}
+    if name not in codes:
+        raise ValueError(f"C must be float32, float16 or bfloat16, got {name}")
+    return codes[name]
+
+
 class GemmPlan:
     """What one GEMM call does on the device (`hcCudaGemmPlan`)."""
 
@@ -212,7 +223,7 @@ B_KN, B_NK = 0, 1  # B stored [k, n] (default) or transposed, [n, k]
 
 def _gemm_args(m: int, n: int, k: int, dtype: Any, a: int | None, lda: int, b: int | None, ldb: int,
                c: int | None, ldc: int, variant: int, b_transposed: bool = False, accumulate: bool = False,
-               epilogue: Sequence[tuple] = (), bias: int | None = None) -> _GemmArgs:
+               epilogue: Sequence[tuple] = (), bias: int | None = None, c_dtype: Any = "float32") -> _GemmArgs:
     epilogue = tuple(epilogue)
     if len(epilogue) > MAX_EPILOGUE_OPS:
         raise ValueError(f"at most {MAX_EPILOGUE_OPS} fused element-wise operations are supported")
@@ -225,15 +236,15 @@ def _gemm_args(m: int, n: int, k: int, dtype: Any, a: int | None, lda: int, b: i
         kinds[i] = EPILOGUE_KINDS[name]
         values[i] = float(op[1]) if len(op) > 1 else 0.0
     return _GemmArgs(m, n, k, dtype_code(dtype), variant, a, lda, b, ldb, c, ldc,
-                     B_NK if b_transposed else B_KN, 1 if accumulate else 0, len(epilogue), kinds, values, 0,
-                     bias)
+                     B_NK if b_transposed else B_KN, 1 if accumulate else 0, len(epilogue), kinds, values,
+                     c_dtype_code(c_dtype), bias)
 
 
 def plan_gemm(m: int, n: int, k: int, dtype: Any, *, a: int = 0x1000, lda: int | None = None,
               b: int = 0x40000000, ldb: int | None = None, c: int = 0x80000000,
               ldc: int | None = None, variant: int = VARIANT_AUTO, sm_count: int = 148,
               b_transposed: bool = False, accumulate: bool = False, epilogue: Sequence[tuple] = (),
-              bias: int | None = 0xC0000000) -> GemmPlan:
+              bias: int | None = 0xC0000000, c_dtype: Any = "float32") -> GemmPlan:
     """Validates a problem and returns its launch plan without touching a device.
 
     The pointer arguments are plain integers that are only inspected (null, alignment,
@@ -241,7 +252,7 @@ def plan_gemm(m: int, n: int, k: int, dtype: Any, *, a: int = 0x1000, lda: int |
     """
     args = _gemm_args(m, n, k, dtype, a, k if lda is None else lda, b,
                       (k if b_transposed else n) if ldb is None else ldb, c, n if ldc is None else ldc, variant,
-                      b_transposed, accumulate, epilogue, bias)
+                      b_transposed, accumulate, epilogue, bias, c_dtype)
     info = _PlanInfo()
     status = library().hcCudaGemmPlan(ctypes.byref(args), sm_count, ctypes.byref(info))
     if status:
@@ -322,6 +333,7 @@ class Context:
              bias: "DeviceBuffer | None" = None) -> None:
         """Enqueues C = A @ B on device buffers (asynchronous; see `synchronize`).
 
+        `c` is float32, or float16 / bfloat16 (the float32 result rounded to nearest even).
         `b_transposed`: `b` holds B transposed, shape (n, k).
         `accumulate`: C = C + A @ B (the previous contents of C start the sums).
         `epilogue`: element-wise operations applied in order before the store, e.g.
@@ -335,7 +347,7 @@ class Context:
         if bias is not None and (bias.dtype != np.float32 or bias.shape != (n,)):
             raise ValueError("bias must be a float32 buffer of n values")
         args = _gemm_args(m, n, k, a.dtype, a.ptr, a.ld, b.ptr, b.ld, c.ptr, c.ld, variant, b_transposed,
-                          accumulate, epilogue, None if bias is None else bias.ptr)
+                          accumulate, epilogue, None if bias is None else bias.ptr, c.dtype)
         if not push:
             self._check(self._lib.hcCudaGemm(self._handle, ctypes.byref(args)))
             return
@@ -356,7 +368,7 @@ class Context:
         if bias is not None and (bias.dtype != np.float32 or bias.shape != (n,)):
             raise ValueError("bias must be a float32 buffer of n values")
         args = _gemm_args(m, n, k, a.dtype, a.ptr, a.ld, b.ptr, b.ld, c.ptr, c.ld, variant, b_transposed,
-                          accumulate, epilogue, None if bias is None else bias.ptr)
+                          accumulate, epilogue, None if bias is None else bias.ptr, c.dtype)
         return BoundGemm(self, args, (a, b, c, bias))
 
     # -- sharing device memory between the processes of one node ----------------------------
@@ -389,7 +401,7 @@ class Context:
         args = _gemm_args(m, n, k, a.dtype, a.ctypes.data, a.strides[0] // a.itemsize if m > 1 else max(k, 1),
                           b.ctypes.data, b.strides[0] // b.itemsize if b_rows > 1 else max(b_cols, 1),
                           c.ctypes.data, c.strides[0] // c.itemsize if m > 1 else max(n, 1), variant,
-                          b_transposed, accumulate, epilogue, None if bias is None else bias.ctypes.data)
+                          b_transposed, accumulate, epilogue, None if bias is None else bias.ctypes.data, c.dtype)
         if bias is not None and (bias.dtype != np.float32 or bias.shape != (n,) or not bias.flags.c_contiguous):
             raise ValueError("bias must be a contiguous float32 vector of n values")
         self._check(self._lib.hcCudaGemmHost(self._handle, ctypes.byref(args)))

@@ -203,8 +203,11 @@ int plan_gemm(const HcCudaContext *ctx, const HcCudaGemmArgs *args, int sm_count
   }
   if (bias_ops > 1)
     return fail(ctx, HC_CUDA_ERR_UNSUPPORTED, "at most one HC_CUDA_EPILOGUE_BIAS_COLUMN operation is supported");
-  if (args->reserved != 0)
-    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "reserved must be 0");
+  if (args->c_dtype != HC_CUDA_C_F32 && args->c_dtype != HC_CUDA_C_F16 && args->c_dtype != HC_CUDA_C_BF16)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "c_dtype must be an HcCudaCType (got %d)", args->c_dtype);
+  if (args->c_dtype != HC_CUDA_C_F32 && args->accumulate != 0)
+    return fail(ctx, HC_CUDA_ERR_UNSUPPORTED, "accumulate needs a float32 C");
+  const size_t c_elem = args->c_dtype == HC_CUDA_C_F32 ? 4 : 2;
   if (sm_count <= 0)
     sm_count = kDefaultSmCount;
 
@@ -221,9 +224,9 @@ int plan_gemm(const HcCudaContext *ctx, const HcCudaGemmArgs *args, int sm_count
   if (args->ldc < n || args->ldc > kMaxPitch)
     return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "ldc (%lld) must be at least n (%lld)",
                 (long long)args->ldc, (long long)n);
-  if ((reinterpret_cast<uintptr_t>(args->c) & 3) != 0)
-    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "c must be 4-byte aligned");
-  const size_t c_bytes = (static_cast<size_t>(m - 1) * args->ldc + n) * 4;
+  if ((reinterpret_cast<uintptr_t>(args->c) & (c_elem - 1)) != 0)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "c must be %zu-byte aligned", c_elem);
+  const size_t c_bytes = (static_cast<size_t>(m - 1) * args->ldc + n) * c_elem;
   if (bias_ops != 0 && ranges_overlap(args->c, c_bytes, args->bias, static_cast<size_t>(n) * 4))
     return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "c must not overlap bias");
   if (k == 0) {
@@ -429,13 +432,15 @@ int enqueue_gemm(HcCudaContext *ctx, const HcCudaGemmArgs *args, const HcCudaGem
   for (int i = 0; i < args->epilogue_count; ++i)
     if (args->epilogue_kind[i] == HC_CUDA_EPILOGUE_BIAS_COLUMN)
       ep.bias = args->bias;
+  ep.c_dtype = args->c_dtype;
+  const size_t c_elem = args->c_dtype == HC_CUDA_C_F32 ? 4 : 2;
   if (plan.variant == HC_CUDA_GEMM_ELEMENTWISE) {
     HC_TRY_CUDA(ctx, hc::sm100::launch_epilogue_only(args->c, m, n, args->ldc, ep, ctx->stream));
     return HC_CUDA_OK;
   }
   if (plan.variant == HC_CUDA_GEMM_ZERO_FILL) {
-    HC_TRY_CUDA(ctx, cudaMemset2DAsync(args->c, static_cast<size_t>(args->ldc) * 4, 0,
-                                       static_cast<size_t>(n) * 4, static_cast<size_t>(m), ctx->stream));
+    HC_TRY_CUDA(ctx, cudaMemset2DAsync(args->c, static_cast<size_t>(args->ldc) * c_elem, 0,
+                                       static_cast<size_t>(n) * c_elem, static_cast<size_t>(m), ctx->stream));
     return HC_CUDA_OK;
   }
   if (int rc = ensure_scratch(ctx, static_cast<size_t>(plan.scratch_bytes)))
@@ -496,8 +501,14 @@ int enqueue_gemm(HcCudaContext *ctx, const HcCudaGemmArgs *args, const HcCudaGem
     // back to ordinary stores for fused work and push targets).
     CUtensorMap tmap_c;
     const CUtensorMap *c_map = nullptr;
-    if ((args->ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(args->c) & 15) == 0 && ctx->c_tma_store) {
-      if (int rc = encode_map(ctx, &tmap_c, kMapFloat32, args->c, n, m, static_cast<uint64_t>(args->ldc) * 4, 32, 32))
+    const bool c_rows_aligned = (static_cast<size_t>(args->ldc) * c_elem) % 16 == 0 &&
+                                (reinterpret_cast<uintptr_t>(args->c) & 15) == 0;
+    if (c_rows_aligned && ctx->c_tma_store) {
+      // float32: 32 x 32 boxes; 16-bit: 64 columns x 32 rows (128-byte rows either way).
+      const int map_type = args->c_dtype == HC_CUDA_C_F32 ? kMapFloat32
+                           : args->c_dtype == HC_CUDA_C_BF16 ? HC_CUDA_BF16 : HC_CUDA_F16;
+      if (int rc = encode_map(ctx, &tmap_c, map_type, args->c, n, m, static_cast<uint64_t>(args->ldc) * c_elem,
+                              args->c_dtype == HC_CUDA_C_F32 ? 32 : 64, 32))
         return rc;
       c_map = &tmap_c;
     }
@@ -887,12 +898,14 @@ int hcCudaGemmPush(HcCudaContext *ctx, const HcCudaGemmArgs *args, float *const 
     dense.variant = HC_CUDA_GEMM_DENSE;
   if (dense.variant != HC_CUDA_GEMM_DENSE)
     return fail(ctx, HC_CUDA_ERR_UNSUPPORTED, "pushing C to other buffers is implemented by the dense kernels only");
+  if (dense.c_dtype != HC_CUDA_C_F32 && n_targets > 0)
+    return fail(ctx, HC_CUDA_ERR_UNSUPPORTED, "pushing C to other buffers needs a float32 C");
   HcCudaGemmPlanInfo plan;
   if (int rc = plan_gemm(ctx, &dense, ctx->prop.multiProcessorCount, false, &plan))
     return rc;
   hc::sm100::Epilogue push{};
   if (plan.variant == HC_CUDA_GEMM_DENSE && n_targets > 0) {
-    if ((dense.ldc & 3) != 0 || (reinterpret_cast<uintptr_t>(dense.c) & 15) != 0)
+    if ((dense.ldc & 3) != 0 || (reinterpret_cast<uintptr_t>(dense.c) & 15) != 0)  // (float32 C here)
       return fail(ctx, HC_CUDA_ERR_UNSUPPORTED, "pushing needs c 16-byte aligned and ldc a multiple of 4");
     const size_t c_bytes = (static_cast<size_t>(dense.m - 1) * dense.ldc + dense.n) * 4;
     for (int i = 0; i < n_targets; ++i) {
@@ -964,9 +977,12 @@ int hcCudaGemmHost(HcCudaContext *ctx, const HcCudaGemmArgs *args) {
     return HC_CUDA_OK;
   const size_t m = static_cast<size_t>(args->m), n = static_cast<size_t>(args->n),
                k = static_cast<size_t>(args->k);
+  const size_t ce = args->c_dtype == HC_CUDA_C_F32 ? 4 : 2;  // bytes per element of C
+  char *const host_c = static_cast<char *>(args->c);
+  const size_t host_c_pitch = static_cast<size_t>(args->ldc) * ce;
   if (plan.variant == HC_CUDA_GEMM_ZERO_FILL) {
     for (size_t i = 0; i < m; ++i)
-      std::memset(args->c + i * static_cast<size_t>(args->ldc), 0, n * sizeof(float));
+      std::memset(host_c + i * host_c_pitch, 0, n * ce);
     return HC_CUDA_OK;
   }
   HC_TRY_CUDA(ctx, cudaSetDevice(ctx->device));
@@ -978,16 +994,17 @@ int hcCudaGemmHost(HcCudaContext *ctx, const HcCudaGemmArgs *args) {
   const bool b_nk = args->b_layout == HC_CUDA_B_NK;
   const size_t b_rows = b_nk ? n : k, b_cols = b_nk ? k : n;  // B as stored
   const size_t ldb = static_cast<size_t>(round_up(static_cast<int64_t>(b_cols), kRepackPitchElems));
-  const size_t ldc = static_cast<size_t>(round_up(args->n, 4));
+  const size_t ldc = static_cast<size_t>(round_up(args->n, 16 / static_cast<int64_t>(ce)));  // 16-byte rows: TMA stores
   if (int rc = ensure_stage(ctx, 0, m * lda * 2))
     return rc;
   if (int rc = ensure_stage(ctx, 1, b_rows * ldb * 2))
     return rc;
   // C's staging buffer also holds the bias vector, after the last row.
-  if (int rc = ensure_stage(ctx, 2, m * ldc * 4 + (has_bias ? n * 4 : 0)))
+  if (int rc = ensure_stage(ctx, 2, round_up(static_cast<int64_t>(m * ldc * ce), 16) + (has_bias ? n * 4 : 0)))
     return rc;
   HcCudaGemmArgs dev = *args;
-  float *bias_dev = reinterpret_cast<float *>(static_cast<char *>(ctx->stage[2]) + m * ldc * 4);
+  char *const dev_c = static_cast<char *>(ctx->stage[2]);
+  float *bias_dev = reinterpret_cast<float *>(dev_c + round_up(static_cast<int64_t>(m * ldc * ce), 16));
   if (has_bias) {
     dev.bias = bias_dev;
     HC_TRY_CUDA(ctx, cudaMemcpyAsync(bias_dev, args->bias, n * 4, cudaMemcpyHostToDevice, ctx->stream));
@@ -996,20 +1013,20 @@ int hcCudaGemmHost(HcCudaContext *ctx, const HcCudaGemmArgs *args) {
   dev.lda = static_cast<int64_t>(lda);
   dev.b = ctx->stage[1];
   dev.ldb = static_cast<int64_t>(ldb);
-  dev.c = static_cast<float *>(ctx->stage[2]);
+  dev.c = dev_c;
   dev.ldc = static_cast<int64_t>(ldc);
 
-  const size_t total_bytes = (m * k + k * n) * 2 + m * n * 4;
+  const size_t total_bytes = (m * k + k * n) * 2 + m * n * ce;
   if (plan.variant == HC_CUDA_GEMM_ELEMENTWISE) {
     if (args->accumulate)
-      HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(ctx->stage[2], ldc * 4, args->c, static_cast<size_t>(args->ldc) * 4,
-                                         n * 4, m, cudaMemcpyHostToDevice, ctx->stream));
+      HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(dev_c, ldc * ce, host_c, host_c_pitch, n * ce, m, cudaMemcpyHostToDevice,
+                                         ctx->stream));
     if (int rc = plan_gemm(ctx, &dev, ctx->prop.multiProcessorCount, false, &plan))
       return rc;
     if (int rc = enqueue_gemm(ctx, &dev, plan))
       return rc;
-    HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(args->c, static_cast<size_t>(args->ldc) * 4, ctx->stage[2], ldc * 4,
-                                       n * 4, m, cudaMemcpyDeviceToHost, ctx->stream));
+    HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(host_c, host_c_pitch, dev_c, ldc * ce, n * ce, m, cudaMemcpyDeviceToHost,
+                                       ctx->stream));
     return synchronize_locked(ctx);
   }
   const bool pipelined = plan.variant == HC_CUDA_GEMM_DENSE && m >= 1024 && total_bytes >= (size_t(32) << 20) &&
@@ -1020,14 +1037,14 @@ int hcCudaGemmHost(HcCudaContext *ctx, const HcCudaGemmArgs *args) {
     HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(ctx->stage[1], ldb * 2, args->b, static_cast<size_t>(args->ldb) * 2,
                                        b_cols * 2, b_rows, cudaMemcpyHostToDevice, ctx->stream));
     if (args->accumulate)
-      HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(ctx->stage[2], ldc * 4, args->c, static_cast<size_t>(args->ldc) * 4,
-                                         n * 4, m, cudaMemcpyHostToDevice, ctx->stream));
+      HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(dev_c, ldc * ce, host_c, host_c_pitch, n * ce, m, cudaMemcpyHostToDevice,
+                                         ctx->stream));
     if (int rc = plan_gemm(ctx, &dev, ctx->prop.multiProcessorCount, false, &plan))
       return rc;
     if (int rc = enqueue_gemm(ctx, &dev, plan))
       return rc;
-    HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(args->c, static_cast<size_t>(args->ldc) * 4, ctx->stage[2], ldc * 4,
-                                       n * 4, m, cudaMemcpyDeviceToHost, ctx->stream));
+    HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(host_c, host_c_pitch, dev_c, ldc * ce, n * ce, m, cudaMemcpyDeviceToHost,
+                                       ctx->stream));
     return synchronize_locked(ctx);
   }
 
@@ -1052,7 +1069,7 @@ int hcCudaGemmHost(HcCudaContext *ctx, const HcCudaGemmArgs *args) {
     part.n = static_cast<int64_t>(cols);
     part.a = static_cast<const char *>(dev.a) + row0 * lda * 2;
     part.b = static_cast<const char *>(dev.b) + (b_nk ? col0 * ldb : col0) * 2;
-    part.c = dev.c + row0 * ldc + col0;
+    part.c = dev_c + (row0 * ldc + col0) * ce;
     if (has_bias)
       part.bias = dev.bias + col0;
     HcCudaGemmPlanInfo part_plan;
@@ -1063,9 +1080,8 @@ int hcCudaGemmHost(HcCudaContext *ctx, const HcCudaGemmArgs *args) {
     cudaEvent_t done = ctx->panel_done[done_events++];
     HC_TRY_CUDA(ctx, cudaEventRecord(done, ctx->stream));
     HC_TRY_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_out, done, 0));
-    HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(args->c + row0 * static_cast<size_t>(args->ldc) + col0,
-                                       static_cast<size_t>(args->ldc) * 4, part.c, ldc * 4, cols * 4, rows,
-                                       cudaMemcpyDeviceToHost, ctx->copy_out));
+    HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(host_c + row0 * host_c_pitch + col0 * ce, host_c_pitch, part.c, ldc * ce,
+                                       cols * ce, rows, cudaMemcpyDeviceToHost, ctx->copy_out));
     return HC_CUDA_OK;
   };
   auto finish = [&]() -> int {
@@ -1114,10 +1130,8 @@ int hcCudaGemmHost(HcCudaContext *ctx, const HcCudaGemmArgs *args) {
                                          static_cast<size_t>(args->lda) * 2, k * 2, rows, cudaMemcpyHostToDevice,
                                          ctx->copy_in));
       if (args->accumulate)  // this panel's rows of C are the starting values of its sums
-        HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(static_cast<float *>(ctx->stage[2]) + row0 * ldc, ldc * 4,
-                                           args->c + row0 * static_cast<size_t>(args->ldc),
-                                           static_cast<size_t>(args->ldc) * 4, n * 4, rows,
-                                           cudaMemcpyHostToDevice, ctx->copy_in));
+        HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(dev_c + row0 * ldc * ce, ldc * ce, host_c + row0 * host_c_pitch, host_c_pitch,
+                                           n * ce, rows, cudaMemcpyHostToDevice, ctx->copy_in));
       HC_TRY_CUDA(ctx, cudaEventRecord(ctx->panel_in[p], ctx->copy_in));
       if (int rc = multiply_and_fetch(row0, rows, 0, n, ctx->panel_in[p]))
         return rc;

@@ -11,20 +11,22 @@ namespace sm100 {
 namespace {
 
 __global__ void __launch_bounds__(256)
-epilogue_only_kernel(float *__restrict__ c, int m, int n, long long ldc, Epilogue ep) {
+epilogue_only_kernel(void *c, int m, int n, long long ldc, Epilogue ep) {
   const long long total = static_cast<long long>(m) * n;
   for (long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
        idx += static_cast<long long>(gridDim.x) * blockDim.x) {
     const int row = static_cast<int>(idx / n);
     const int col = static_cast<int>(idx - static_cast<long long>(row) * n);
-    float *dst = c + row * ldc + col;
-    *dst = finish_value(0.0f, dst, col, ep);
+    const long long index = row * ldc + col;
+    // (Accumulation is only offered for a float32 C.)
+    const float v = finish_value(0.0f, static_cast<const float *>(c) + index, col, ep);
+    store_c_element(c, index, v, ep.c_dtype);
   }
 }
 
 } // namespace
 
-cudaError_t launch_epilogue_only(float *c, int m, int n, long long ldc, const Epilogue &ep,
+cudaError_t launch_epilogue_only(void *c, int m, int n, long long ldc, const Epilogue &ep,
                                  cudaStream_t stream) {
   if (m <= 0 || n <= 0)
     return cudaSuccess;

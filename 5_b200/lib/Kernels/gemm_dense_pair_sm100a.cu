@@ -96,7 +96,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Roles<kReadsC>::kThr
 gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                        const __grid_constant__ CUtensorMap tmap_b,
                        const __grid_constant__ CUtensorMap tmap_c, int c_tma,
-                       const __grid_constant__ CUtensorMap tmap_partials, float *__restrict__ c, int m, int n,
+                       const __grid_constant__ CUtensorMap tmap_partials, void *c, int m, int n,
                        int k, long long ldc, uint32_t idesc, int tiles_m, int tiles_n, int group_n,
                        int l2_hints, int b_layout, Epilogue ep, SplitK split, int *status) {
   extern __shared__ uint8_t smem_raw[];
@@ -271,7 +271,7 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int row_base = tc.m_blk * kTileM + static_cast<int>(cta_rank) * kCtaM + quarter * 32;
       const int col_base = tc.n_blk * kTileN + column_part * kColumnsPerWarp;
       if (kReadsC)
-        prefetch_c_tile_row(c, ldc, m, n, row_base + lane, col_base, kColumnsPerWarp);
+        prefetch_c_tile_row(static_cast<const float *>(c), ldc, m, n, row_base + lane, col_base, kColumnsPerWarp);
       const bool ready = mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag);
       if (!__all_sync(0xffffffffu, ready))
         break;
@@ -330,7 +330,7 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
 } // namespace dense_pair
 
-cudaError_t launch_gemm_dense_pair(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, float *c,
+cudaError_t launch_gemm_dense_pair(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, void *c,
                                    int m, int n, int k, long long ldc, int dtype, int group_n,
                                    int max_ctas, int b_layout, const Epilogue &ep, const CUtensorMap *tmap_c,
                                    const SplitK &split, const CUtensorMap *tmap_partials, int *status,
@@ -375,6 +375,8 @@ cudaError_t launch_gemm_dense_pair(const CUtensorMap &tmap_a, const CUtensorMap 
   // C leaves through TMA stores when it is aligned (tmap_c), goes nowhere else, and any element-wise
   // work can run before the store: no accumulation, or an accumulation that nothing follows, which
   // the stores themselves perform as additions. Only the remaining case reads C in the epilogue.
+  if (ep.c_dtype != kCTypeF32 && (ep.accumulate != 0 || ep.push_count != 0))
+    return cudaErrorInvalidValue;  // rejected with a message by the caller's validation
   Epilogue launch_ep = ep;
   const bool tma_possible = tmap_c != nullptr && ep.push_count == 0;
   launch_ep.accumulate_by_tma = (tma_possible && ep.accumulate != 0 && ep.op_count == 0) ? 1 : 0;

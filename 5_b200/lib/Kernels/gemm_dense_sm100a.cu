@@ -79,7 +79,7 @@ __global__ void __launch_bounds__(Roles<kReadsC>::kThreads, 1)
 gemm_dense_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   const __grid_constant__ CUtensorMap tmap_b,
                        const __grid_constant__ CUtensorMap tmap_c, int c_tma,
-                       const __grid_constant__ CUtensorMap tmap_partials, float *__restrict__ c, int m, int n,
+                       const __grid_constant__ CUtensorMap tmap_partials, void *c, int m, int n,
                   int k, long long ldc, uint32_t idesc, int tiles_m, int tiles_n, int group_n,
                   int b_layout, Epilogue ep, SplitK split, int *status) {
   extern __shared__ uint8_t smem_raw[];
@@ -233,7 +233,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int row_base = tc.m_blk * kBlockM + quarter * 32;
       const int col_base = tc.n_blk * kBlockN + column_part * kColumnsPerWarp;
       if (kReadsC)
-        prefetch_c_tile_row(c, ldc, m, n, row_base + lane, col_base, kColumnsPerWarp);
+        prefetch_c_tile_row(static_cast<const float *>(c), ldc, m, n, row_base + lane, col_base, kColumnsPerWarp);
       const bool ready = mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag);
       if (!__all_sync(0xffffffffu, ready))
         break;
@@ -291,7 +291,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
 } // namespace dense
 
-cudaError_t launch_gemm_dense(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, float *c,
+cudaError_t launch_gemm_dense(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, void *c,
                               int m, int n, int k, long long ldc, int dtype, int group_n,
                               int max_ctas, int b_layout, const Epilogue &ep, const CUtensorMap *tmap_c,
                               const SplitK &split, const CUtensorMap *tmap_partials, int *status,
@@ -332,6 +332,8 @@ cudaError_t launch_gemm_dense(const CUtensorMap &tmap_a, const CUtensorMap &tmap
   // C leaves through TMA stores when it is aligned (tmap_c), goes nowhere else, and any element-wise
   // work can run before the store: no accumulation, or an accumulation that nothing follows, which
   // the stores themselves perform as additions. Only the remaining case reads C in the epilogue.
+  if (ep.c_dtype != kCTypeF32 && (ep.accumulate != 0 || ep.push_count != 0))
+    return cudaErrorInvalidValue;  // rejected with a message by the caller's validation
   Epilogue launch_ep = ep;
   const bool tma_possible = tmap_c != nullptr && ep.push_count == 0;
   launch_ep.accumulate_by_tma = (tma_possible && ep.accumulate != 0 && ep.op_count == 0) ? 1 : 0;

@@ -10,11 +10,39 @@
 // each row is rotated to its own 16-byte phase while it is staged.
 #pragma once
 
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
 #include "gemm_launch.h"
 #include "sm100_ptx.cuh"
 
 namespace hc {
 namespace sm100 {
+
+// ---------------------------------------------------------------- 16-bit C ----------
+// Two float32 values rounded to nearest even and packed (first value in the low half).
+__device__ __forceinline__ uint32_t pack_pair(float lo, float hi, int c_dtype) {
+  if (c_dtype == kCTypeF16) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t *>(&h);
+  }
+  const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t *>(&h);
+}
+
+__device__ __forceinline__ uint16_t round_to_16(float v, int c_dtype) {
+  if (c_dtype == kCTypeF16)
+    return __half_as_ushort(__float2half_rn(v));
+  return __bfloat16_as_ushort(__float2bfloat16_rn(v));
+}
+
+// One element of C of whatever type, at element index `index`.
+__device__ __forceinline__ void store_c_element(void *c, long long index, float v, int c_dtype) {
+  if (c_dtype == kCTypeF32)
+    __stcs(static_cast<float *>(c) + index, v);
+  else
+    static_cast<uint16_t *>(c)[index] = round_to_16(v, c_dtype);
+}
 
 // The fused element-wise work on one value that is about to be stored at `dst` (column `col`).
 __device__ __forceinline__ float finish_value(float v, const float *dst, int col, const Epilogue &ep) {
@@ -446,19 +474,119 @@ __device__ __forceinline__ void store_chunk_tma(const uint32_t (&r)[32], int chu
   }
 }
 
+// 16-bit C, 64 columns at a time: `w` holds this lane's row as 32 packed pairs (columns col0 ..
+// col0 + 63). Staged like a float32 chunk (the rows are 128 bytes either way) and stored by TMA
+// through a 16-bit tensor map with a 64 x 32 box.
+__device__ __forceinline__ void store_block16_tma(const uint32_t (&w)[32], int col0, float *buf,
+                                                  const CUtensorMap *tmap_c, int m, int n, int row_base, int lane) {
+  if (col0 >= n || row_base >= m)
+    return;  // warp-uniform
+  if (lane == 0)
+    tma_store_wait_read();
+  __syncwarp();
+  stage_row_shifted<0>(w, buf, lane);
+  fence_proxy_async_smem();
+  __syncwarp();
+  if (lane == 0) {
+    tma_store_2d(tmap_c, smem_u32(buf), col0, row_base);
+    tma_store_commit();
+  }
+}
+
+// 16-bit C whose base or pitch rules out TMA: the block is staged the same way and written row by
+// row, each lane storing elements `lane` and `lane + 32` of the row (64 contiguous bytes per
+// instruction), predicated at the edges. `columns`: 64, or 32 when only the low half of `w` is set.
+__device__ __forceinline__ void store_block16_plain(const uint32_t (&w)[32], int col0, int columns, float *buf,
+                                                    uint16_t *__restrict__ c, long long ldc, int m, int n,
+                                                    int row_base, int lane) {
+  if (col0 >= n || row_base >= m)
+    return;  // warp-uniform
+  stage_row_shifted<0>(w, buf, lane);
+  __syncwarp();
+  const uint16_t *halves = reinterpret_cast<const uint16_t *>(buf);
+#pragma unroll 4
+  for (int rr = 0; rr < 32; ++rr) {
+    if (row_base + rr >= m)
+      break;
+    uint16_t *dst = c + static_cast<long long>(row_base + rr) * ldc + col0;
+    for (int e = lane; e < columns; e += 32) {
+      // Element e of the row sits in 16-byte piece e / 8, which was stored at piece ^ (row & 7).
+      const int piece = (e >> 3) ^ (rr & 7);
+      if (col0 + e < n)
+        dst[e] = halves[rr * 64 + piece * 8 + (e & 7)];
+    }
+  }
+  __syncwarp();
+}
+
+// The accumulator drain for a 16-bit C: two 32-column chunks make one 64-column block of packed
+// pairs; element-wise operations run on the float32 values first.
+template <int kColumns>
+__device__ __forceinline__ void drain_accumulator_rows16(uint32_t taddr, float *stage, void *c, long long ldc, int m,
+                                                         int n, int row_base, int col_base, int lane,
+                                                         uint32_t release_bar, bool release_remote,
+                                                         const Epilogue &ep, const CUtensorMap *tmap_c) {
+  constexpr int kChunks = kColumns / 32;
+  static_assert(kChunks % 2 == 0, "chunks are processed in pairs");
+  uint32_t ra[32], rb[32], w[32];
+  const bool ops = ep.op_count != 0;
+  tmem_load_32x32b_x32(taddr, ra);
+#pragma unroll 1
+  for (int chunk = 0; chunk < kChunks; chunk += 2) {
+    const int col0 = col_base + chunk * 32;
+    tmem_load_wait_for(ra);
+    tmem_load_32x32b_x32(taddr + (chunk + 1) * 32, rb);
+    if (ops && col0 < n)
+      apply_ops_lane_row(ra, col0, n, lane, ep);
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+      w[j] = pack_pair(__uint_as_float(ra[2 * j]), __uint_as_float(ra[2 * j + 1]), ep.c_dtype);
+    tmem_load_wait_for(rb);
+    if (chunk + 2 < kChunks) {
+      tmem_load_32x32b_x32(taddr + (chunk + 2) * 32, ra);
+    } else {
+      tcgen05_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) {
+        if (release_remote)
+          mbar_arrive_cluster(release_bar);
+        else
+          mbar_arrive(release_bar);
+      }
+    }
+    if (ops && col0 + 32 < n)
+      apply_ops_lane_row(rb, col0 + 32, n, lane, ep);
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+      w[16 + j] = pack_pair(__uint_as_float(rb[2 * j]), __uint_as_float(rb[2 * j + 1]), ep.c_dtype);
+    if (tmap_c != nullptr)
+      store_block16_tma(w, col0, stage, tmap_c, m, n, row_base, lane);
+    else
+      store_block16_plain(w, col0, 64, stage, static_cast<uint16_t *>(c), ldc, m, n, row_base, lane);
+  }
+}
+
 // `release_bar`: mbarrier (cluster-window address when `release_remote`) that receives one
 // arrival from this warp as soon as the accumulator has been read completely.
 //
 // The TMEM load of the next chunk is in flight while the current chunk is transposed and
 // stored (two register sets alternate), so the TMEM latency is hidden behind the stores.
 template <int kColumns, bool kReadsC>
-__device__ __forceinline__ void drain_accumulator_rows(uint32_t taddr, float *stage, float *__restrict__ c,
+__device__ __forceinline__ void drain_accumulator_rows(uint32_t taddr, float *stage, void *c_any,
                                                        long long ldc, int m, int n, int row_base,
                                                        int col_base, bool vec_ok, int lane,
                                                        uint32_t release_bar, bool release_remote,
                                                        const Epilogue &ep, const CUtensorMap *tmap_c) {
   constexpr int kChunks = kColumns / 32;
   static_assert(kChunks % 2 == 0, "chunks are processed in pairs");
+  if constexpr (!kReadsC) {
+    if (ep.c_dtype != kCTypeF32) {  // grid-uniform
+      drain_accumulator_rows16<kColumns>(taddr, stage, c_any, ldc, m, n, row_base, col_base, lane, release_bar,
+                                         release_remote, ep, tmap_c);
+      return;
+    }
+  }
+  float *__restrict__ c = static_cast<float *>(c_any);
   uint32_t ra[32], rb[32];
   float carry[3] = {0.0f, 0.0f, 0.0f};
   // Stores of an aligned C go through TMA (`tmap_c` is null otherwise).
@@ -516,12 +644,14 @@ namespace sm100 {
 // chunk loop that every tile goes through.)
 template <int kColumns, bool kReadsC>
 __device__ __noinline__ void reduce_partials_rows(const float *partial_rows, int partial_ld, size_t split_stride,
-                                                  int splits, float *stage, float *__restrict__ c, long long ldc,
+                                                  int splits, float *stage, void *c_any, long long ldc,
                                                   int m, int n, int row_base, int col_base, bool vec_ok, int lane,
                                                   const Epilogue &ep, const CUtensorMap *tmap_c) {
   constexpr int kChunks = kColumns / 32;
   float carry[3] = {0.0f, 0.0f, 0.0f};
-  const bool tma = !kReadsC && tmap_c != nullptr;
+  float *__restrict__ c = static_cast<float *>(c_any);
+  const bool half_out = !kReadsC && ep.c_dtype != kCTypeF32;  // then `tmap_c` (64-column boxes) is not used here
+  const bool tma = !kReadsC && tmap_c != nullptr && !half_out;
   const bool ops_first = !kReadsC && ep.op_count != 0;
   const int piece = lane & 7;
   const float *lane_base = partial_rows + static_cast<size_t>(lane >> 3) * partial_ld + piece * 4;
@@ -595,6 +725,17 @@ __device__ __noinline__ void reduce_partials_rows(const float *partial_rows, int
     }
     if (ops_first)
       apply_ops_lane_row(r, col_base + chunk * 32, n, lane, ep);
+    if (half_out) {
+      uint32_t w[32];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        w[j] = pack_pair(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]), ep.c_dtype);
+        w[16 + j] = 0u;
+      }
+      store_block16_plain(w, col_base + chunk * 32, 32, stage, static_cast<uint16_t *>(c_any), ldc, m, n, row_base,
+                          lane);
+      continue;
+    }
     write_chunk<kReadsC>(r, chunk, chunk == kChunks - 1, stage, c, ldc, m, n, row_base, col_base, vec_ok, lane,
                         carry, ep);
   }

@@ -18,6 +18,9 @@ constexpr int kBLayoutNK = 1;
 
 constexpr int kDTypeF16 = 0;
 constexpr int kDTypeBF16 = 1;
+constexpr int kCTypeF32 = 0;
+constexpr int kCTypeF16 = 1;
+constexpr int kCTypeBF16 = 2;
 
 // Value a kernel writes to the status word when one of its bounded waits ran out.
 constexpr int kStatusDeviceWaitTimeout = 5;
@@ -47,6 +50,9 @@ struct Epilogue {
   int op_kind[kMaxEpilogueOps];
   float op_value[kMaxEpilogueOps];
   const float *bias;
+  // Element type of C: 0 float32, 1 float16, 2 bfloat16 (the float32 value rounded to nearest
+  // even). 16-bit output is written by the kernels that do not read C.
+  int c_dtype;
   // Set by the dense launchers: accumulate by letting the TMA stores add to C (possible when the
   // stores go through TMA and no operation follows the accumulation), so C is never read.
   int accumulate_by_tma;
@@ -86,10 +92,11 @@ DenseTileShape dense_tile_shape();
 // C[m,n] = A * B through the TMA + tcgen05 persistent kernel.
 //   tmap_a: A as a 2-D tensor {k (inner), m}, box {64, 128}, 128-byte swizzle.
 //   tmap_b: B as a 2-D tensor {n (inner), k}, box {64, 64},  128-byte swizzle.
-//   tmap_c: C as a 2-D fp32 tensor {n (inner), m}, box {32, 32}, 128-byte swizzle, or null. When
+//   tmap_c: C as a 2-D tensor {n (inner), m}, 128-byte swizzle -- float32 with box {32, 32}, or for
+//           a 16-bit C (ep.c_dtype) its element type with box {64, 32} -- or null. When
 //           given (C's base and pitch are 16-byte aligned) and the launch is the plain product
 //           without push targets, the tiles of C leave through TMA stores.
-cudaError_t launch_gemm_dense(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, float *c,
+cudaError_t launch_gemm_dense(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, void *c,
                               int m, int n, int k, long long ldc, int dtype, int group_n,
                               int max_ctas, int b_layout, const Epilogue &ep, const CUtensorMap *tmap_c,
                               const SplitK &split, const CUtensorMap *tmap_partials, int *status,
@@ -98,7 +105,7 @@ cudaError_t launch_gemm_dense(const CUtensorMap &tmap_a, const CUtensorMap &tmap
 // Same product on CTA pairs: clusters of two CTAs own 256x256 tiles and issue
 // tcgen05.mma.cta_group::2. Takes the same tensor maps as launch_gemm_dense. `max_ctas` is
 // rounded down to an even number of CTAs.
-cudaError_t launch_gemm_dense_pair(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, float *c,
+cudaError_t launch_gemm_dense_pair(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, void *c,
                                    int m, int n, int k, long long ldc, int dtype, int group_n,
                                    int max_ctas, int b_layout, const Epilogue &ep, const CUtensorMap *tmap_c,
                                    const SplitK &split, const CUtensorMap *tmap_partials, int *status,
@@ -128,13 +135,13 @@ size_t skinny_counters_bytes(int n);
 //   tmap_a: A as {k (inner), m}, box {64, padded m}; tmap_b as for the dense kernel.
 //   partials / counters: scratch (ignored when splits == 1); counters must be zero on
 //   entry and are zero again on exit.
-cudaError_t launch_gemm_skinny(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, float *c,
+cudaError_t launch_gemm_skinny(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, void *c,
                                int m, int n, int k, long long ldc, int dtype, int splits,
                                float *partials, unsigned *counters, int max_ctas, int b_layout,
                                const Epilogue &ep, int *status, cudaStream_t stream);
 
 // k == 0 with fused element-wise work: C = ops(accumulate ? C : 0), no product to add.
-cudaError_t launch_epilogue_only(float *c, int m, int n, long long ldc, const Epilogue &ep,
+cudaError_t launch_epilogue_only(void *c, int m, int n, long long ldc, const Epilogue &ep,
                                  cudaStream_t stream);
 
 // Copies a rows x cols matrix of 16-bit elements into a buffer whose row pitch is a

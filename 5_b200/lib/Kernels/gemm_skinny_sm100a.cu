@@ -57,11 +57,12 @@ struct Config {
 template <int kMp>
 __global__ void __launch_bounds__(kNumThreads, kCtasPerSm)
 gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                   const __grid_constant__ CUtensorMap tmap_b, float *__restrict__ c, int m, int n,
+                   const __grid_constant__ CUtensorMap tmap_b, void *c_any, int m, int n,
                    int k, long long ldc, uint32_t idesc, int n_tiles, int splits, int num_stages,
                    int b_layout, Epilogue ep,
                    float *__restrict__ partials, unsigned *__restrict__ counters, int *status) {
   using Cfg = Config<kMp>;
+  float *__restrict__ c = static_cast<float *>(c_any);  // the float32 view (accumulation reads it)
   const uint32_t kStages = static_cast<uint32_t>(num_stages);  // ring depth of this launch
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -239,7 +240,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
           for (int mm = 0; mm < kMp; ++mm)
             if (mm < m && col < n)
-              __stcs(c + static_cast<long long>(mm) * ldc + col, __uint_as_float(r[mm]));
+              store_c_element(c_any, static_cast<long long>(mm) * ldc + col, __uint_as_float(r[mm]), ep.c_dtype);
           continue;
         }
         // Reads first (the previous contents of eight rows, the bias once), then the stores.
@@ -259,7 +260,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
           for (int j = 0; j < 8; ++j)
             if (mm0 + j < m && col < n)
-              __stcs(c + static_cast<long long>(mm0 + j) * ldc + col, v[j]);
+              store_c_element(c_any, static_cast<long long>(mm0 + j) * ldc + col, v[j], ep.c_dtype);
         }
         continue;
       }
@@ -304,7 +305,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
             for (int j = 0; j < 8; ++j)
               if (mm0 + j < m)
-                __stcs(c + static_cast<long long>(mm0 + j) * ldc + col, sums[j]);
+                store_c_element(c_any, static_cast<long long>(mm0 + j) * ldc + col, sums[j], ep.c_dtype);
           }
         }
         if (lane == 0)
@@ -329,7 +330,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a,
 }
 
 template <int kMp>
-cudaError_t launch(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, float *c, int m, int n,
+cudaError_t launch(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, void *c, int m, int n,
                    int k, long long ldc, int dtype, int splits, float *partials,
                    unsigned *counters, int max_ctas, int b_layout, const Epilogue &ep, int *status,
                    cudaStream_t stream) {
@@ -415,7 +416,7 @@ size_t skinny_counters_bytes(int n) {
   return n_tiles * 4 * sizeof(unsigned);
 }
 
-cudaError_t launch_gemm_skinny(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, float *c,
+cudaError_t launch_gemm_skinny(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, void *c,
                                int m, int n, int k, long long ldc, int dtype, int splits,
                                float *partials, unsigned *counters, int max_ctas, int b_layout,
                                const Epilogue &ep, int *status, cudaStream_t stream) {

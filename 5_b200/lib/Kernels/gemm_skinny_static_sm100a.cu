@@ -133,9 +133,9 @@ int hcCudaGemmSkinnyStatic(const HcCudaGemmArgs *args, void *stream, int synchro
   if (int rc = setup_current_device(device, &setup))
     return report(rc);
 
-  if (args->accumulate != 0 || args->epilogue_count != 0)
-    return report(fail(HC_CUDA_ERR_UNSUPPORTED,
-                       "the static-scratch entry point computes C = A*B only (no accumulate, no fused operations)"));
+  if (args->accumulate != 0 || args->epilogue_count != 0 || args->c_dtype != HC_CUDA_C_F32)
+    return report(fail(HC_CUDA_ERR_UNSUPPORTED, "the static-scratch entry point computes a float32 C = A*B only "
+                                                "(no accumulate, no fused operations, no 16-bit C)"));
   // Same validation and split choice as the regular path.
   HcCudaGemmArgs forced = *args;
   forced.variant = HC_CUDA_GEMM_SKINNY;

@@ -361,10 +361,11 @@ def run_gpu_arm(args, ranks: Ranks) -> None:
     gemm_kwargs = {"b_transposed": args.b_transposed, "accumulate": contract.accumulate,
                    "epilogue": contract.epilogue, "bias": dbias}
     member_check = {"epilogue": contract.epilogue, "bias": bias}
-    dc = ctx.empty((m, local_n), np.float32)
+    c_type = a.dtype if contract.output_dtype != "float32" else np.dtype(np.float32)
+    dc = ctx.empty((m, local_n), c_type)
     dc.fill_bytes(0)
     plan = ctx.plan(m, local_n, k, w.dtype, b_transposed=args.b_transposed, accumulate=contract.accumulate,
-                    epilogue=contract.epilogue)
+                    epilogue=contract.epilogue, c_dtype=contract.output_dtype)
     local_flops = workloads.flops(m, local_n, k)
     total_flops = workloads.flops(w.m, w.n, w.k)
 
@@ -414,6 +415,14 @@ def run_gpu_arm(args, ranks: Ranks) -> None:
     c = dc.to_numpy()
     rows = np.unique(np.linspace(0, m - 1, 16).astype(np.int64))
     parity = workloads.check_against_float64(c, a, b, rows=rows, **member_check)
+    if contract.output_dtype != "float32":
+        # A 16-bit C carries half a unit in its last place on top of the float32 bound.
+        ulp = 2.0 ** -11 if contract.output_dtype == "float16" else 2.0 ** -8
+        exact = a[rows].astype(np.float64) @ b.astype(np.float64)
+        bound = np.abs(a[rows].astype(np.float64)) @ np.abs(b.astype(np.float64))
+        diff = np.abs(c[rows].astype(np.float64) - exact)
+        parity["ok"] = bool(parity["finite"] and (diff <= 1e-2 * bound + ulp * np.abs(exact)).all())
+        parity["output_rounding"] = f"{contract.output_dtype}: half a unit in the last place added to the element bound"
     parity_all = ranks.gather_objects(parity)
 
     # ---- end to end through the public handle on pinned host buffers ---------------------
@@ -430,7 +439,7 @@ def run_gpu_arm(args, ranks: Ranks) -> None:
     pa = cuda.pinned_empty(a.shape, a.dtype)
     host_b = bt if args.b_transposed else b
     pb = cuda.pinned_empty(host_b.shape, host_b.dtype)
-    pc = cuda.pinned_empty((m, local_n), np.float32)
+    pc = cuda.pinned_empty((m, local_n), c_type)
     pa[...] = a
     pb[...] = host_b
     pc[...] = 0
@@ -529,7 +538,7 @@ def run_gpu_arm(args, ranks: Ranks) -> None:
     # ---- roofline of the dominant kernel ----------------------------------------------------
     peaks, peaks_source = measured_peaks()
     if plan.variant == "skinny":
-        algo_bytes = workloads.algorithmic_bytes(m, local_n, k)
+        algo_bytes = workloads.algorithmic_bytes(m, local_n, k) - (4 - c_type.itemsize) * m * local_n
         algo_bytes += (4 * m * local_n if contract.accumulate else 0) + (0 if bias is None else bias.nbytes)
         achieved = algo_bytes / (ms_per_step * 1e-3) / 1e9
         peak = float(peaks["hbm_gbs"])
@@ -602,9 +611,9 @@ def main() -> int:
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--b-transposed", action="store_true",
                         help="hand B over stored [N, K] and use the Buffer[N, K] member of the kernel family")
-    parser.add_argument("--member", choices=("plain", "accumulate", "fused"), default="plain",
-                        help="kernel family member: C = A.B (the reference example, default), C += A.B, or "
-                             "C = maximum(0.125 * A.B + bias, 0) folded into the store")
+    parser.add_argument("--member", choices=("plain", "accumulate", "fused", "narrow"), default="plain",
+                        help="kernel family member: C = A.B (the reference example, default), C += A.B, "
+                             "C = maximum(0.125 * A.B + bias, 0) folded into the store, or C in the input type")
     parser.add_argument("--cublas", action="store_true",
                         help="also time cuBLAS (torch.mm) on the same inputs with the same loop, for context")
     parser.add_argument("--quick", action="store_true",

@@ -39,7 +39,7 @@
 extern "C" {
 #endif
 
-#define HC_CUDA_API_VERSION 3
+#define HC_CUDA_API_VERSION 4
 
 typedef enum HcCudaStatus {
   HC_CUDA_OK = 0,
@@ -52,8 +52,9 @@ typedef enum HcCudaStatus {
   HC_CUDA_ERR_OUT_OF_MEMORY = 7
 } HcCudaStatus;
 
-/* Element type of A and B. C is always float32 (fp32 accumulate and output), as in the
- * reference kernel's `Buffer[M, N, np.float32]` (examples/amdgpu_gfx11_wmma_matmul.py:310). */
+/* Element type of A and B. Accumulation is always float32 and C is float32 unless c_dtype says
+ * otherwise, as in the reference kernel's `Buffer[M, N, np.float32]`
+ * (examples/amdgpu_gfx11_wmma_matmul.py:310). */
 typedef enum HcCudaDType { HC_CUDA_F16 = 0, HC_CUDA_BF16 = 1 } HcCudaDType;
 
 typedef enum HcCudaGemmVariant {
@@ -68,6 +69,12 @@ typedef enum HcCudaGemmVariant {
   HC_CUDA_GEMM_ELEMENTWISE = 5   /* k == 0 with fused element-wise work: one small kernel that
                                     applies it to C (accumulate) or to zeros */
 } HcCudaGemmVariant;
+
+/* Element type of C. The products are always accumulated in float32; a 16-bit C receives the
+ * float32 value (after any fused operations) rounded to nearest even, which is what the
+ * reference simulator's store does for a kernel whose `c` is `Buffer[M, N, np.float16]`
+ * (with or without an explicit `acc.astype(np.float16)` before the store). */
+typedef enum HcCudaCType { HC_CUDA_C_F32 = 0, HC_CUDA_C_F16 = 1, HC_CUDA_C_BF16 = 2 } HcCudaCType;
 
 /* How B is laid out in memory. */
 typedef enum HcCudaBLayout {
@@ -94,7 +101,7 @@ typedef enum HcCudaEpilogueOp {
  * a: Buffer[M, K], b: Buffer[K, N], c: Buffer[M, N] (examples/...:306-311), the symbols
  * M, N, K being what `_bind_buffer` derives from the array shapes (hc/simulator.py:752-768).
  * Every in-range element of C is overwritten; nothing outside C is written; A and B are
- * read only. A, B 2-byte aligned, C 4-byte aligned; other alignments and pitches are
+ * read only. A, B 2-byte aligned, C aligned to its element size; other alignments and pitches are
  * accepted (a or b not 16-byte aligned, or lda/ldb not a multiple of 8 elements, costs one
  * repack launch through context scratch memory). */
 typedef struct HcCudaGemmArgs {
@@ -105,7 +112,7 @@ typedef struct HcCudaGemmArgs {
   int64_t lda;
   const void *b;
   int64_t ldb;
-  float *c;
+  void *c;         /* float32 unless c_dtype says otherwise */
   int64_t ldc;
   int32_t b_layout;   /* HcCudaBLayout */
   int32_t accumulate; /* 0: C = A*B. 1: C = C + A*B, the kernel that loads its accumulators from
@@ -115,7 +122,8 @@ typedef struct HcCudaGemmArgs {
   int32_t epilogue_kind[HC_CUDA_MAX_EPILOGUE_OPS]; /* HcCudaEpilogueOp, applied in order to
                                                       (C +) A*B before it is stored */
   float epilogue_value[HC_CUDA_MAX_EPILOGUE_OPS];
-  int32_t reserved;  /* must be 0 */
+  int32_t c_dtype;   /* HcCudaCType; 16-bit C is not available together with accumulate or with
+                        push targets (HC_CUDA_ERR_UNSUPPORTED) */
   const float *bias; /* n floats, 4-byte aligned; read by HC_CUDA_EPILOGUE_BIAS_COLUMN (at most
                         one such operation), NULL otherwise. Host memory for hcCudaGemmHost,
                         device memory elsewhere */

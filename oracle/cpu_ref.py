@@ -113,10 +113,12 @@ EPILOGUE_KINDS = {"scale": 1, "add": 2, "max": 3, "min": 4, "bias": 5}
 
 
 def matmul_fused(a: np.ndarray, b: np.ndarray, *, c0: np.ndarray | None = None, epilogue=(),
-                 bias: np.ndarray | None = None, threads: int = 0) -> np.ndarray:
+                 bias: np.ndarray | None = None, threads: int = 0, out_dtype=None) -> np.ndarray:
     """Members of the kernel family around the example: accumulators that start from `c0`
     (C += A.B) and element-wise statements after the k-loop, e.g.
-    `(("scale", 0.5), ("bias",), ("max", 0.0))`, in the reference simulator's fp32 order."""
+    `(("scale", 0.5), ("bias",), ("max", 0.0))`, in the reference simulator's fp32 order. With
+    `out_dtype` (float16 / bfloat16, a kernel whose `c` is a 16-bit buffer) the fp32 values are
+    rounded to nearest even at the end, as the simulator's `astype` / store does."""
     m, n, k, code = _check(a, b)
     abits, bbits = _as_bits(a), _as_bits(b)
     c = np.zeros((m, n), np.float32) if c0 is None else np.array(c0, dtype=np.float32, order="C", copy=True)
@@ -129,7 +131,7 @@ def matmul_fused(a: np.ndarray, b: np.ndarray, *, c0: np.ndarray | None = None, 
                                        None if bias32 is None else bias32.ctypes.data, threads)
     if rc != 0:
         raise MemoryError("the oracle could not allocate its widened copy of B")
-    return c
+    return c if out_dtype is None else c.astype(out_dtype)
 
 
 def matmul_tiled(a: np.ndarray, b: np.ndarray) -> np.ndarray:

@@ -27,6 +27,8 @@ Fixtures (all produced by `hc.simulator.launch` on the example kernel):
       the accumulating member of that family (C = C + A.B); `c0` holds C before the launch
   simfused_bf16_m33_n17_k40_seed12
       the fused member (C = maximum(0.125 * (A.B) + bias, 0)); `bias` holds the fourth buffer
+  simnarrow_bf16_m33_n17_k40_seed13
+      the narrow member (c: Buffer[M, N, bfloat16]); `c_bits` holds the 16-bit output
 The file blocked_reference.npz holds `reference_blocked_matmul` of the first four (the
 reference test's own comparison value, atol 2e-6).
 """
@@ -141,6 +143,13 @@ def main() -> int:
     c = np.full((33, 17), np.float32(-7.0))  # every element must be overwritten
     mod.hc.simulator.launch(mod.tiled_wmma_matmul_for("bfloat16", False, "fused"), a, b, c, bias)
     _save("simfused_bf16_m33_n17_k40_seed12", a, b, c, bias=bias)
+
+    rng = np.random.default_rng(13)
+    a = rng.uniform(-1.0, 1.0, size=(33, 40)).astype(ml_dtypes.bfloat16)
+    b = rng.uniform(-1.0, 1.0, size=(40, 17)).astype(ml_dtypes.bfloat16)
+    c = np.full((33, 17), 7.0).astype(ml_dtypes.bfloat16)
+    mod.hc.simulator.launch(mod.tiled_wmma_matmul_for("bfloat16", False, "narrow"), a, b, c)
+    _save("simnarrow_bf16_m33_n17_k40_seed13", a, b, c.astype(np.float32), c_bits=c.view(np.uint16))
     return 0
 
 

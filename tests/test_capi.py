@@ -97,9 +97,28 @@ def test_plan_with_b_stored_transposed() -> None:
     assert lib.hcCudaGemmPlan(ctypes.byref(args), 148, ctypes.byref(info)) == 1
     assert b"b_layout" in lib.hcCudaContextLastError(None)
     args = cuda._GemmArgs(8, 8, 8, 0, 0, 0x1000, 8, 0x2000, 8, 0x3000, 8, 0, 0)
-    args.reserved = 1
+    args.c_dtype = 3
     assert lib.hcCudaGemmPlan(ctypes.byref(args), 148, ctypes.byref(info)) == 1
-    assert b"reserved" in lib.hcCudaContextLastError(None)
+    assert b"c_dtype" in lib.hcCudaContextLastError(None)
+
+
+def test_plan_with_a_16_bit_c() -> None:
+    """C may be float16 or bfloat16 (the float32 result rounded on store); it then needs only 2-byte
+    alignment, and is not offered together with accumulation."""
+    plan = cuda.plan_gemm(4095, 3073, 1031, "bfloat16", lda=1031, ldb=3073, ldc=3073, c_dtype="bfloat16")
+    plain = cuda.plan_gemm(4095, 3073, 1031, "bfloat16", lda=1031, ldb=3073, ldc=3073)
+    assert (plan.variant, plan.grid, plan.kernel_launches) == (plain.variant, plain.grid, plain.kernel_launches)
+    assert cuda.plan_gemm(8, 512, 1024, "float16", c=0x80000002, c_dtype="float16").variant == "skinny"
+    with pytest.raises(DeviceError, match="c must be 4-byte aligned"):
+        cuda.plan_gemm(8, 512, 1024, "float16", c=0x80000002)
+    with pytest.raises(DeviceError, match="c must be 2-byte aligned"):
+        cuda.plan_gemm(8, 512, 1024, "float16", c=0x80000001, c_dtype="float16")
+    with pytest.raises(DeviceError, match="HC_CUDA_ERR_UNSUPPORTED: accumulate needs a float32 C"):
+        cuda.plan_gemm(64, 64, 64, "float16", accumulate=True, c_dtype="float16")
+    assert cuda.plan_gemm(64, 64, 0, "float16", c_dtype="bfloat16").variant == "zero_fill"
+    assert cuda.plan_gemm(64, 64, 0, "float16", c_dtype="bfloat16", epilogue=(("add", 1.0),)).variant == "elementwise"
+    with pytest.raises(ValueError, match="C must be float32, float16 or bfloat16"):
+        cuda.plan_gemm(64, 64, 64, "float16", c_dtype="float64")
 
 
 def test_plan_with_accumulate_and_fused_operations() -> None:

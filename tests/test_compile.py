@@ -275,6 +275,40 @@ def test_statements_around_the_k_loop(tmp_path) -> None:
     rejected("r_early", "may only be read before the k-loop to initialise", init="0\n    peek = from_c(group, c)")
 
 
+def test_narrow_member_and_astype_placement(tmp_path) -> None:
+    narrow = compiled_for("bfloat16", None, False, "narrow")
+    assert narrow.plan is not None and narrow.plan.output_dtype == "bfloat16" and narrow.plan.epilogue == ()
+    bf16 = np_bf16()
+    with pytest.raises(hc.LaunchError, match="c dtype expected bfloat16, got float32"):
+        narrow(np.zeros((33, 40), bf16), np.zeros((40, 17), bf16), np.zeros((33, 17), np.float32))
+    half_c = ", c: Buffer[M, N, np.float32]"
+    source = _VARIANT_SOURCE.replace(half_c, ", c: Buffer[M, N, np.float16]")
+    assert source != _VARIANT_SOURCE
+
+    def variant(name, **kwargs):
+        import importlib.util
+
+        text = source.format(init=kwargs.get("init", "0"), extra_param="", tail="",
+                             after="\n".join("    " + line for line in kwargs.get("after", ())))
+        path = tmp_path / f"{name}.py"
+        path.write_text(text, encoding="utf-8")
+        spec = importlib.util.spec_from_file_location(name, path)
+        module = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(module)
+        return recognise_tiled_matmul(module.matmul)
+
+    plan, why = variant("n_implicit")  # the store itself narrows, as in the simulator
+    assert plan is not None and plan.output_dtype == "float16", why
+    plan, why = variant("n_ops", after=["acc = acc * 0.5", "acc = acc.astype(np.float32)", "acc = acc.astype(np.float16)"])
+    assert plan is not None and plan.epilogue == (("scale", 0.5),), why
+    plan, why = variant("n_late", after=["acc = acc.astype(np.float16)", "acc = acc * 0.5"])
+    assert plan is None and any("runs on the 16-bit values" in line for line in why), why
+    plan, why = variant("n_other", after=["acc = acc.astype(np.float64)"])
+    assert plan is None and any("is not an element-wise statement" in line for line in why), why
+    plan, why = variant("n_acc", init="from_c(group, c)")
+    assert plan is None and any("needs a float32 `c`" in line for line in why), why
+
+
 def np_bf16():
     import ml_dtypes
 
@@ -293,7 +327,7 @@ def test_family_members_are_recognised() -> None:
     ("kwargs", "message"),
     [
         ({"in_dtype": np.float32}, "are not a\\[M,K\\], b\\[K,N\\]"),
-        ({"out_dtype": np.float16}, "c\\[M,N\\] float32"),
+        ({"out_dtype": np.float64}, "c\\[M,N\\] of one of \\['float32', 'float16', 'bfloat16'\\]"),
         ({"b_dims": (N, K)}, "axis 1 of the `b` window must advance with the k-loop variable"),
         ({"effects": "write"}, "expected 'pure'"),
         ({"acc": 4}, "accumulator values per lane"),

@@ -18,6 +18,7 @@ import workloads
 from conftest import GOLDEN_NAMES, load_golden, np_dtype
 from examples.b200_wmma_matmul import compiled_for, gpu_wmma_matmul
 from hc import cuda
+from hc.errors import DeviceError
 from oracle import cpu_ref
 
 pytestmark = pytest.mark.gpu
@@ -370,6 +371,94 @@ def test_dense_split_of_the_last_round(shape, gpu_ctx, monkeypatch) -> None:
     assert (out != whole).any()  # the split tiles were added in a different order
     for buf in (da, db, dc):
         buf.free()
+
+
+def assert_narrow_close(out, a, b, *, epilogue=(), bias=None) -> None:
+    """A 16-bit C against the float64 reference: the benchmark's element bound plus half a unit in
+    the last place of the output type."""
+    eps = 2.0 ** -11 if out.dtype == np.float16 else 2.0 ** -8
+    a64, b64 = a.astype(np.float64), b.astype(np.float64)
+    ref = a64 @ b64
+    bound = np.abs(a64) @ np.abs(b64)
+    for op in epilogue:
+        if op[0] == "scale":
+            ref, bound = ref * np.float32(op[1]), bound * abs(op[1])
+        elif op[0] == "add":
+            ref, bound = ref + np.float32(op[1]), bound + abs(op[1])
+        elif op[0] == "bias":
+            ref, bound = ref + bias[None, :], bound + np.abs(bias)[None, :]
+        elif op[0] == "max":
+            ref = np.maximum(ref, np.float32(op[1]))
+        else:
+            ref = np.minimum(ref, np.float32(op[1]))
+    got = out.astype(np.float64)
+    assert np.isfinite(got).all()
+    diff = np.abs(got - ref)
+    assert (diff <= ELEMENT_RATIO * bound + eps * np.abs(ref) + 1e-30).all(), float(diff.max())
+
+
+NARROW_SHAPES = [
+    # TMA path (pitch a multiple of 8 elements), plain path (odd pitch), skinny, split-k, edges
+    (128, 256, 64, 0), (300, 520, 136, 0), (513, 1001, 264, 3), (1024, 1024, 256, 0), (2050, 2051, 130, 1),
+    (8, 4096, 512, 0), (33, 515, 1024, 5), (64, 16384, 256, 0), (128, 2048, 4096, 0), (300, 700, 6000, 1),
+]
+
+
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+@pytest.mark.parametrize("shape", NARROW_SHAPES)
+def test_16_bit_c(shape, dtype: str, gpu_ctx) -> None:
+    m, n, k, pad = shape
+    a, b = random_inputs(m, n, k, dtype, scale=0.25)
+    out_type = np_dtype(dtype)
+    da, db = gpu_ctx.to_device(a), gpu_ctx.to_device(b)
+    dc = cuda.DeviceBuffer(gpu_ctx, (m, n), out_type, ld=n + pad)
+    d32 = gpu_ctx.empty((m, n), np.float32)
+    gpu_ctx.gemm(da, db, d32)
+    dc.fill_bytes(0x7F)
+    gpu_ctx.gemm(da, db, dc)
+    gpu_ctx.synchronize()
+    out = dc.to_numpy()
+    assert out.dtype == np.dtype(out_type)
+    assert_narrow_close(out, a, b)
+    # Exactly the float32 result rounded to nearest even (same plan, so the same float32 bits).
+    assert np.array_equal(out.view(np.uint16), d32.to_numpy().astype(out_type).view(np.uint16))
+    bias = np.linspace(-1, 1, n).astype(np.float32)
+    dbias = gpu_ctx.to_device(bias)
+    ops = (("scale", 0.5), ("bias",), ("max", 0.0))
+    gpu_ctx.gemm(da, db, dc, epilogue=ops, bias=dbias)
+    gpu_ctx.synchronize()
+    assert_narrow_close(dc.to_numpy(), a, b, epilogue=ops, bias=bias)
+    with pytest.raises(DeviceError, match="accumulate needs a float32 C"):
+        gpu_ctx.gemm(da, db, dc, accumulate=True)
+    for buf in (da, db, dc, d32, dbias):
+        buf.free()
+
+
+def test_narrow_member_fixture_and_host_arrays(gpu_ctx) -> None:
+    import ml_dtypes
+
+    a, b, c_sim32 = load_golden("simnarrow_bf16_m33_n17_k40_seed13")
+    c = np.full((33, 17), 7.0).astype(ml_dtypes.bfloat16)
+    compiled_for("bfloat16", None, False, "narrow")(a, b, c)
+    assert_narrow_close(c, a, b)
+    # One unit in the last place of bfloat16 at most, where the float32 sums straddle a rounding point.
+    assert np.abs(c.astype(np.float32) - c_sim32).max() <= 2.0 ** -7 * np.abs(c_sim32).max()
+    assert (c.astype(np.float32) == c_sim32).mean() > 0.98
+    # k == 0 and the large host paths (pageable: row panels; pinned: alternating panels).
+    z = np.full((5, 9), 3.0).astype(np.float16)
+    gpu_ctx.gemm_host(np.zeros((5, 0), np.float16), np.zeros((0, 9), np.float16), z, epilogue=(("add", 1.5),))
+    assert np.array_equal(z, np.full((5, 9), 1.5, np.float16))
+    m, n, k = 3000, 4100, 1100
+    a, b = random_inputs(m, n, k, "float16", scale=0.25)
+    c_store = np.full((m + 2, n + 4), np.float16(9.0))
+    gpu_ctx.gemm_host(a, b, c_store[1:-1, 2:-2])
+    pa, pb = cuda.pinned_empty(a.shape, a.dtype), cuda.pinned_empty(b.shape, b.dtype)
+    pc = cuda.pinned_empty((m, n), np.float16)
+    pa[...], pb[...] = a, b
+    gpu_ctx.gemm_host(pa, pb, pc)
+    assert np.array_equal(pc, c_store[1:-1, 2:-2])
+    assert (c_store[0] == 9).all() and (c_store[-1] == 9).all() and (c_store[:, :2] == 9).all() and (c_store[:, -2:] == 9).all()
+    assert_narrow_close(np.ascontiguousarray(pc[:64]), a[:64], b)
 
 
 def test_bound_gemm_launches_like_gemm(gpu_ctx) -> None:

@@ -18,6 +18,7 @@ def test_fixtures_are_present() -> None:
     assert (GOLDEN / "simbt_f16_m17_n19_k18_seed9.npz").exists()
     assert (GOLDEN / "simacc_f16_m17_n19_k18_seed11.npz").exists()
     assert (GOLDEN / "simfused_bf16_m33_n17_k40_seed12.npz").exists()
+    assert (GOLDEN / "simnarrow_bf16_m33_n17_k40_seed13.npz").exists()
     assert (GOLDEN / "blocked_reference.npz").exists()
 
 
@@ -66,6 +67,20 @@ def test_accumulating_and_fused_kernel_fixtures() -> None:
     assert not np.array_equal(swapped, c_sim)
     for op, fn in ((("add", 1.5), lambda x: x + np.float32(1.5)), (("min", 0.25), lambda x: np.minimum(x, np.float32(0.25)))):
         assert np.array_equal(cpu_ref.matmul_fused(a, b, epilogue=(op,)), fn(cpu_ref.matmul_numpy(a, b)))
+
+
+def test_narrow_kernel_fixture() -> None:
+    """The member whose c is a bfloat16 buffer, as the reference simulator executed it: fp32
+    accumulation, rounded to nearest even on the way out."""
+    import ml_dtypes
+
+    a, b, c_sim32 = load_golden("simnarrow_bf16_m33_n17_k40_seed13")
+    with np.load(GOLDEN / "simnarrow_bf16_m33_n17_k40_seed13.npz") as data:
+        c_bits = data["c_bits"]
+    out = cpu_ref.matmul_fused(a, b, out_dtype=ml_dtypes.bfloat16)
+    assert out.dtype == ml_dtypes.bfloat16 and np.array_equal(out.view(np.uint16), c_bits)
+    assert np.array_equal(out.astype(np.float32), c_sim32)
+    assert not np.array_equal(cpu_ref.matmul_k_ascending(a, b), c_sim32)  # the rounding is visible
 
 
 def test_oracle_meets_the_reference_tests_own_tolerance() -> None:
