@@ -458,6 +458,12 @@ def run_gpu_arm(args, ranks: Ranks) -> None:
         e2e_ok = bool(np.allclose(pc[rows], (1 + e2e_steps) * c[rows], rtol=1e-4, atol=1e-5))
     else:
         e2e_ok = bool(np.array_equal(pc[rows], c[rows]))
+        if not e2e_ok and plan.splits > 1:
+            # The device launch split some tiles over k; the host call's panels never do, so the two
+            # differ by fp32 reassociation in those tiles.
+            scale = float(np.abs(c[rows].astype(np.float64)).max())
+            e2e_ok = bool(np.allclose(pc[rows].astype(np.float64), c[rows].astype(np.float64), rtol=1e-4,
+                                      atol=1e-5 * max(scale, 1.0)))
     h2d_bytes = a.nbytes + b.nbytes + (pc.nbytes if contract.accumulate else 0) + (0 if bias is None else bias.nbytes)
     e2e = {"value": total_flops / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_ms,
            "steps": e2e_steps, "h2d_bytes_per_step": int(h2d_bytes),
