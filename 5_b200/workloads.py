@@ -22,7 +22,7 @@ from dataclasses import dataclass
 
 import numpy as np
 
-__all__ = ["CONFIGS", "Workload", "check_against_float64", "flops", "algorithmic_bytes", "make_inputs",
+__all__ = ["CONFIGS", "Workload", "register_custom", "check_against_float64", "flops", "algorithmic_bytes", "make_inputs",
            "make_sharded_inputs", "SHARDED_BLOCK_COLUMNS"]
 
 SHARDED_BLOCK_COLUMNS = 2048
@@ -45,6 +45,13 @@ CONFIGS = {
     "skinny": Workload("skinny", 8, 16384, 8192, "float16", 3),
     "sharded": Workload("sharded", 16384, 32768, 16384, "float16", 4),
 }
+
+
+def register_custom(m: int, n: int, k: int, dtype: str = "float16") -> str:
+    """Adds workload "custom": an arbitrary shape with the distribution of configuration 2
+    (N(0,1)/sqrt(K), default_rng(5)), for profiling other members of the kernel family."""
+    CONFIGS["custom"] = Workload("custom", int(m), int(n), int(k), dtype, 5)
+    return "custom"
 
 
 def flops(m: int, n: int, k: int) -> float:
@@ -81,7 +88,7 @@ def make_inputs(name: str) -> tuple[np.ndarray, np.ndarray]:
     if name == "sim_64":
         a = rng.standard_normal((w.m, w.k)).astype(dtype)
         b = rng.standard_normal((w.k, w.n)).astype(dtype)
-    elif name == "gemm_8192":
+    elif name in ("gemm_8192", "custom"):
         scale = 1.0 / np.sqrt(w.k)
         a = _normal(rng, (w.m, w.k), scale, dtype)
         b = _normal(rng, (w.k, w.n), scale, dtype)

@@ -612,6 +612,8 @@ def main() -> int:
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", choices=("b200", "reference"), default="b200")
     parser.add_argument("--workload", choices=sorted(workloads.CONFIGS), default=None)
+    parser.add_argument("--shape", default=None, metavar="MxNxK",
+                        help="an arbitrary float16 shape instead of a named workload (single GPU), e.g. 8192x8192x512")
     parser.add_argument("--e2e-steps", type=int, default=5)
     parser.add_argument("--no-gather", action="store_true")
     parser.add_argument("--no-cpu-baseline", action="store_true")
@@ -627,6 +629,15 @@ def main() -> int:
     args = parser.parse_args()
     if args.steps < 1:
         parser.error("--steps must be at least 1")
+    if args.shape is not None:
+        try:
+            dims = [int(x) for x in args.shape.lower().split("x")]
+            assert len(dims) == 3 and min(dims) >= 1
+        except (ValueError, AssertionError):
+            parser.error("--shape takes MxNxK, e.g. 8192x8192x512")
+        if args.gpus > 1 or args.workload is not None:
+            parser.error("--shape is a single-GPU measurement and excludes --workload")
+        args.workload = workloads.register_custom(*dims)
     if (args.b_transposed or args.member != "plain") and args.gpus > 1:
         parser.error("--b-transposed and --member are single-GPU measurements")
     if args.b_transposed and args.member != "plain":
