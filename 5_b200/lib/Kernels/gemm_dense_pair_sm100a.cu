@@ -20,8 +20,13 @@
 //   empty[s]      one per CTA. CTA 0's MMA thread commits to its own and to its partner's when the
 //                 MMAs that read ring slot s have finished.
 //   tmem_full[a]  one per CTA, committed by CTA 0 after the last k-block of a tile.
-//   tmem_empty[a] CTA 0 only, 8 arrivals: the four epilogue warps of each CTA.
+//   tmem_empty[a] CTA 0 only; one arrival per epilogue warp of either CTA (8 warps per CTA in the
+//                 plain instantiation, 4 in the one that reads C).
 // No load uses multicast; every CTA fetches its own operand halves.
+//
+// The epilogue (gemm_epilogue.cuh) stores C by TMA when its base and pitch allow, applies fused
+// element-wise operations, writes a float32 or 16-bit C, and, when tiles are split over k, parks
+// partial tiles and lets the last unit of a tile add them up.
 #include "gemm_epilogue.cuh"
 #include "gemm_launch.h"
 #include "sm100_ptx.cuh"

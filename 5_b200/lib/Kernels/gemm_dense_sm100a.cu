@@ -12,10 +12,11 @@
 //              shared-memory stages; out-of-range rows/columns/k are zero-filled by TMA.
 //   warp 1   : allocates TMEM and issues tcgen05.mma (128x256x16, fp32 accumulate in
 //              TMEM); tcgen05.commit hands each ring slot back to the producer.
-//   warps 2-5: epilogue. tcgen05.ld the finished accumulator (two accumulators of 256
-//              columns alternate, so this overlaps the next tile's main loop), transpose
-//              through shared memory and write C with coalesced 128-bit stores,
-//              predicated on the matrix edge.
+//   warps 2..: epilogue (eight warps, two per quarter of the TMEM lanes; four in the
+//              instantiation that reads C). tcgen05.ld the finished accumulator (two
+//              accumulators of 256 columns alternate, so this overlaps the next tile's main
+//              loop), stage it in shared memory and store C by TMA, or, when C's pitch rules
+//              that out, with coalesced 128-bit stores predicated on the matrix edge.
 //
 // The kernel is persistent: CTA b processes tiles b, b+grid, ... in an order that walks
 // groups of `group_n` tile columns so that concurrently running CTAs share A and B
