@@ -180,6 +180,33 @@ def test_plan_splits_dense_tiles_that_do_not_fill_a_round() -> None:
     assert cuda.plan_gemm(128, 8192, 8192, "float16", sm_count=32).splits == 1
 
 
+def test_library_calls_from_threads() -> None:
+    """Loading the library and planning are safe from several threads at once (one-time
+    initialisation, thread-local error text)."""
+    import threading
+
+    seen: list = []
+
+    def work(i: int) -> None:
+        for _ in range(200):
+            plan = cuda.plan_gemm(128 + i, 256, 512, "float16")
+            assert plan.variant == "dense"
+            try:
+                cuda.plan_gemm(8, 8, 8, "float16", lda=4 + i % 3)
+            except DeviceError as exc:
+                assert f"lda ({4 + i % 3}) must be at least k (8)" in str(exc)  # this thread's own message
+            else:  # pragma: no cover
+                raise AssertionError("expected a DeviceError")
+        seen.append(i)
+
+    threads = [threading.Thread(target=work, args=(i,)) for i in range(8)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(timeout=60)
+    assert sorted(seen) == list(range(8))
+
+
 def test_plan_degenerate_shapes() -> None:
     assert cuda.plan_gemm(0, 5, 7, "float16").variant == "noop"
     assert cuda.plan_gemm(5, 0, 7, "float16").kernel_launches == 0

@@ -461,6 +461,54 @@ def test_narrow_member_fixture_and_host_arrays(gpu_ctx) -> None:
     assert_narrow_close(np.ascontiguousarray(pc[:64]), a[:64], b)
 
 
+def test_concurrent_calls_from_threads(gpu_ctx) -> None:
+    """Launches from several host threads at once, as the reference tests its simulator
+    (tests/test_simulator.py:1113-1125): calls on one context are serialised inside the library,
+    contexts of their own run side by side; every thread gets its own product."""
+    import threading
+
+    handle = compiled_for("float16")
+    shapes = [(200 + 37 * i, 300 + 11 * i, 136 + 64 * i) for i in range(6)]
+    problems = [random_inputs(m, n, k, "float16", seed=i, scale=0.25) for i, (m, n, k) in enumerate(shapes)]
+    results: list = [None] * len(shapes)
+    errors: list = []
+
+    def through_the_handle(i: int) -> None:
+        try:
+            a, b = problems[i]
+            for _ in range(5):
+                c = np.full((a.shape[0], b.shape[1]), np.nan, np.float32)
+                handle(a, b, c)
+                results[i] = c
+        except Exception as exc:  # noqa: BLE001 - reported below
+            errors.append((i, exc))
+
+    def through_an_own_context(i: int) -> None:
+        try:
+            ctx = cuda.Context(0)
+            a, b = problems[i]
+            da, db = ctx.to_device(a), ctx.to_device(b)
+            dc = ctx.empty((a.shape[0], b.shape[1]), np.float32)
+            for _ in range(5):
+                ctx.gemm(da, db, dc)
+                ctx.synchronize()
+            results[i] = dc.to_numpy()
+            ctx.close()
+        except Exception as exc:  # noqa: BLE001
+            errors.append((i, exc))
+
+    threads = [threading.Thread(target=through_the_handle if i % 2 == 0 else through_an_own_context, args=(i,))
+               for i in range(len(shapes))]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(timeout=120)
+    assert not errors, errors
+    for (a, b), c in zip(problems, results):
+        assert c is not None
+        assert_close_to_oracle(c, a, b)
+
+
 def test_bound_gemm_launches_like_gemm(gpu_ctx) -> None:
     a, b = random_inputs(300, 520, 136, "float16", scale=0.25)
     bias = np.linspace(-1, 1, 520).astype(np.float32)
