@@ -134,6 +134,8 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       mbar_init(tmem_full_bar(a), 1);
       mbar_init(tmem_empty_bar(a), 2 * kEpilogueWarps);
     }
+    for (uint32_t w = 0; w < kMaxEpilogueWarps; ++w)
+      mbar_init(bar_base + 128u + 8u * w, 1);  // per epilogue warp: arrival of a chunk of C loaded by TMA
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_descriptor(&tmap_a);
@@ -267,6 +269,8 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
     float *stage_gen = reinterpret_cast<float *>(smem_gen + (epi_base - smem_base) +
                                                  (warp - 2) * kEpilogueWarpBytes);
     const bool vec_ok = ((ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(c) & 15) == 0);
+    const uint32_t c_load_bar = bar_base + 128u + 8u * static_cast<uint32_t>(warp - 2);
+    uint32_t c_load_phase = 0;
     uint32_t iter = 0;
     for (int unit = cluster_id; unit < num_units; unit += num_clusters, ++iter) {
       const DenseUnit u = decode_unit(unit, split);
@@ -275,7 +279,7 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const uint32_t acc_phase = (iter >> 1) & 1u;
       const int row_base = tc.m_blk * kTileM + static_cast<int>(cta_rank) * kCtaM + quarter * 32;
       const int col_base = tc.n_blk * kTileN + column_part * kColumnsPerWarp;
-      if (kReadsC)
+      if (kReadsC || ep.accumulate_by_tma_load)
         prefetch_c_tile_row(static_cast<const float *>(c), ldc, m, n, row_base + lane, col_base, kColumnsPerWarp);
       const bool ready = mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag);
       if (!__all_sync(0xffffffffu, ready))
@@ -286,7 +290,8 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       if (u.parts == 1) {
         drain_accumulator_rows<kColumnsPerWarp, kReadsC>(taddr, stage_gen, c, ldc, m, n, row_base, col_base, vec_ok,
                                                         lane, map_to_cta(tmem_empty_bar(acc), 0),
-                                                        /*release_remote=*/true, ep, c_tma ? &tmap_c : nullptr);
+                                                        /*release_remote=*/true, ep, c_tma ? &tmap_c : nullptr,
+                                                        c_load_bar, &c_load_phase, abort_flag);
         continue;
       }
       // Split-k: the partial rows go to this unit's tile of the partials buffer (TMA stores, like
@@ -377,15 +382,20 @@ cudaError_t launch_gemm_dense_pair(const CUtensorMap &tmap_a, const CUtensorMap 
                                         /*b_mn_major=*/b_layout == kBLayoutKN, kTileM, kTileN);
   if (group_n < 1)
     group_n = 1;
-  // C leaves through TMA stores when it is aligned (tmap_c), goes nowhere else, and any element-wise
-  // work can run before the store: no accumulation, or an accumulation that nothing follows, which
-  // the stores themselves perform as additions. Only the remaining case reads C in the epilogue.
+  // C leaves through TMA stores when it is aligned (tmap_c) and goes nowhere else. Element-wise work
+  // runs in registers before the store; an accumulation that nothing follows is performed by the
+  // stores themselves as additions; one that operations follow loads its chunks of C by TMA. Only
+  // what is left (odd pitch, push targets, accumulation with operations in a launch split over k)
+  // reads C with ordinary loads, in the other instantiation.
   if (ep.c_dtype != kCTypeF32 && (ep.accumulate != 0 || ep.push_count != 0))
     return cudaErrorInvalidValue;  // rejected with a message by the caller's validation
   Epilogue launch_ep = ep;
   const bool tma_possible = tmap_c != nullptr && ep.push_count == 0;
   launch_ep.accumulate_by_tma = (tma_possible && ep.accumulate != 0 && ep.op_count == 0) ? 1 : 0;
-  const bool reads_c = ep.accumulate != 0 && launch_ep.accumulate_by_tma == 0;
+  launch_ep.accumulate_by_tma_load =
+      (tma_possible && ep.accumulate != 0 && ep.op_count != 0 && split.splits == 1) ? 1 : 0;
+  const bool reads_c =
+      ep.accumulate != 0 && launch_ep.accumulate_by_tma == 0 && launch_ep.accumulate_by_tma_load == 0;
   const int c_tma = (tma_possible && !reads_c) ? 1 : 0;
   const CUtensorMap c_map = c_tma ? *tmap_c : tmap_a;  // unused unless c_tma
   const CUtensorMap p_map = split.splits > 1 ? *tmap_partials : tmap_a;  // unused unless split

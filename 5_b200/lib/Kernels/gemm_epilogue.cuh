@@ -474,6 +474,46 @@ __device__ __forceinline__ void store_chunk_tma(const uint32_t (&r)[32], int chu
   }
 }
 
+// An accumulating launch with operations after the sum, C addressable by TMA: the chunk's previous
+// contents are loaded into the staging block by TMA (`bar`: this warp's mbarrier, `phase` its
+// parity, kept across chunks), each lane adds its row to its registers, the operations run, and
+// the chunk is staged again and stored by TMA. Returns false when the wait for the load gave up.
+__device__ __forceinline__ bool accumulate_chunk_tma(uint32_t (&r)[32], int chunk, float *buf,
+                                                     const CUtensorMap *tmap_c, int m, int n, int row_base,
+                                                     int col_base, int lane, uint32_t bar, uint32_t &phase,
+                                                     volatile uint32_t *abort_flag, const Epilogue &ep) {
+  const int col0 = col_base + chunk * 32;
+  if (col0 >= n || row_base >= m)
+    return true;  // warp-uniform
+  if (lane == 0) {
+    tma_store_wait_read();  // the previous chunk's store has read the block
+    mbar_arrive_expect_tx(bar, 32 * 32 * 4);
+    tma_load_2d(smem_u32(buf), tmap_c, bar, col0, row_base);  // rows >= m, columns >= n arrive as zeros
+  }
+  const bool arrived = mbar_wait(bar, phase, abort_flag);
+  phase ^= 1u;
+  if (!__all_sync(0xffffffffu, arrived))
+    return false;
+#pragma unroll
+  for (int q = 0; q < 8; ++q) {
+    const float4 old = *reinterpret_cast<const float4 *>(buf + lane * 32 + ((q ^ (lane & 7)) << 2));
+    r[4 * q] = __float_as_uint(__uint_as_float(r[4 * q]) + old.x);
+    r[4 * q + 1] = __float_as_uint(__uint_as_float(r[4 * q + 1]) + old.y);
+    r[4 * q + 2] = __float_as_uint(__uint_as_float(r[4 * q + 2]) + old.z);
+    r[4 * q + 3] = __float_as_uint(__uint_as_float(r[4 * q + 3]) + old.w);
+  }
+  apply_ops_lane_row(r, col0, n, lane, ep);
+  __syncwarp();  // every lane has read its row before any lane overwrites the block
+  stage_row_shifted<0>(r, buf, lane);
+  fence_proxy_async_smem();
+  __syncwarp();
+  if (lane == 0) {
+    tma_store_2d(tmap_c, smem_u32(buf), col0, row_base);
+    tma_store_commit();
+  }
+  return true;
+}
+
 // 16-bit C, 64 columns at a time: `w` holds this lane's row as 32 packed pairs (columns col0 ..
 // col0 + 63). Staged like a float32 chunk (the rows are 128 bytes either way) and stored by TMA
 // through a 16-bit tensor map with a 64 x 32 box.
@@ -576,7 +616,9 @@ __device__ __forceinline__ void drain_accumulator_rows(uint32_t taddr, float *st
                                                        long long ldc, int m, int n, int row_base,
                                                        int col_base, bool vec_ok, int lane,
                                                        uint32_t release_bar, bool release_remote,
-                                                       const Epilogue &ep, const CUtensorMap *tmap_c) {
+                                                       const Epilogue &ep, const CUtensorMap *tmap_c,
+                                                       uint32_t c_load_bar = 0, uint32_t *c_load_phase = nullptr,
+                                                       volatile uint32_t *abort_flag = nullptr) {
   constexpr int kChunks = kColumns / 32;
   static_assert(kChunks % 2 == 0, "chunks are processed in pairs");
   if constexpr (!kReadsC) {
@@ -592,7 +634,8 @@ __device__ __forceinline__ void drain_accumulator_rows(uint32_t taddr, float *st
   // Stores of an aligned C go through TMA (`tmap_c` is null otherwise).
   const bool tma = !kReadsC && tmap_c != nullptr;
   const bool tma_add = ep.accumulate_by_tma != 0;
-  const bool ops_first = !kReadsC && ep.op_count != 0;  // element-wise work done in registers
+  const bool tma_load_add = !kReadsC && ep.accumulate_by_tma_load != 0 && c_load_phase != nullptr;
+  const bool ops_first = !kReadsC && ep.op_count != 0 && !tma_load_add;  // element-wise work done in registers
   tmem_load_32x32b_x32(taddr, ra);
 #pragma unroll 1
   for (int chunk = 0; chunk < kChunks; chunk += 2) {
@@ -600,7 +643,10 @@ __device__ __forceinline__ void drain_accumulator_rows(uint32_t taddr, float *st
     tmem_load_32x32b_x32(taddr + (chunk + 1) * 32, rb);
     if (ops_first && col_base + chunk * 32 < n)
       apply_ops_lane_row(ra, col_base + chunk * 32, n, lane, ep);
-    if (tma)
+    if (tma_load_add)
+      accumulate_chunk_tma(ra, chunk, stage, tmap_c, m, n, row_base, col_base, lane, c_load_bar, *c_load_phase,
+                           abort_flag, ep);
+    else if (tma)
       store_chunk_tma(ra, chunk, stage, tmap_c, m, n, row_base, col_base, lane, tma_add);
     else
       write_chunk<kReadsC>(ra, chunk, false, stage, c, ldc, m, n, row_base, col_base, vec_ok, lane, carry, ep);
@@ -620,7 +666,10 @@ __device__ __forceinline__ void drain_accumulator_rows(uint32_t taddr, float *st
     }
     if (ops_first && col_base + (chunk + 1) * 32 < n)
       apply_ops_lane_row(rb, col_base + (chunk + 1) * 32, n, lane, ep);
-    if (tma)
+    if (tma_load_add)
+      accumulate_chunk_tma(rb, chunk + 1, stage, tmap_c, m, n, row_base, col_base, lane, c_load_bar, *c_load_phase,
+                           abort_flag, ep);
+    else if (tma)
       store_chunk_tma(rb, chunk + 1, stage, tmap_c, m, n, row_base, col_base, lane, tma_add);
     else
       write_chunk<kReadsC>(rb, chunk + 1, chunk + 2 >= kChunks, stage, c, ldc, m, n, row_base, col_base, vec_ok, lane,

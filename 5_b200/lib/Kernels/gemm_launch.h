@@ -56,6 +56,10 @@ struct Epilogue {
   // Set by the dense launchers: accumulate by letting the TMA stores add to C (possible when the
   // stores go through TMA and no operation follows the accumulation), so C is never read.
   int accumulate_by_tma;
+  // Set by the dense launchers: an accumulation that operations follow, into a C that TMA can
+  // address: each chunk of C's previous contents comes in by a TMA load, is added in registers,
+  // the operations run, and the chunk leaves by a TMA store.
+  int accumulate_by_tma_load;
 };
 
 // Splitting dense tiles over k. Tiles [0, first_split_tile) are computed whole; each later tile
