@@ -148,18 +148,14 @@ cudaError_t launch_gemm_skinny(const CUtensorMap &tmap_a, const CUtensorMap &tma
 cudaError_t launch_epilogue_only(void *c, int m, int n, long long ldc, const Epilogue &ep,
                                  cudaStream_t stream);
 
-// Copies a rows x cols matrix of 16-bit elements into a buffer whose row pitch is a
-// multiple of 8 elements (16 bytes), as TMA requires. Columns [cols, round_up(cols, 8))
-// of the destination are zeroed.
-cudaError_t launch_repack_pitch(const void *src, long long src_ld, void *dst, long long dst_ld,
-                                int rows, int cols, cudaStream_t stream);
-
 // Launches one thread that waits `budget_cycles` (clamped to [1e3, 2e8]) on a barrier nobody
 // signals and then reports kStatusDeviceWaitTimeout through `status`, like a GEMM kernel whose
 // wait ran out.
 cudaError_t launch_wait_selftest(long long budget_cycles, int *status, cudaStream_t stream);
 
-// Two such copies in one launch (either may be empty: rows or cols 0).
+// Copies rows x cols matrices of 16-bit elements into buffers whose row pitch is a multiple of 8
+// elements (16 bytes), as TMA requires; columns [cols, round_up(cols, 8)) of a destination are
+// zeroed. Two copies in one launch (either may be empty: rows or cols 0).
 cudaError_t launch_repack_pitch_two(const void *src0, long long src0_ld, void *dst0, long long dst0_ld,
                                     int rows0, int cols0, const void *src1, long long src1_ld, void *dst1,
                                     long long dst1_ld, int rows1, int cols1, cudaStream_t stream);

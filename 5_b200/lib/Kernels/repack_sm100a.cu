@@ -68,11 +68,6 @@ bool valid_destination(const RepackJob &job) {
 
 } // namespace
 
-cudaError_t launch_repack_pitch(const void *src, long long src_ld, void *dst, long long dst_ld,
-                                int rows, int cols, cudaStream_t stream) {
-  return launch_repack_pitch_two(src, src_ld, dst, dst_ld, rows, cols, nullptr, 0, nullptr, 0, 0, 0, stream);
-}
-
 cudaError_t launch_repack_pitch_two(const void *src0, long long src0_ld, void *dst0, long long dst0_ld,
                                     int rows0, int cols0, const void *src1, long long src1_ld, void *dst1,
                                     long long dst1_ld, int rows1, int cols1, cudaStream_t stream) {
