@@ -444,6 +444,13 @@ def test_narrow_member_fixture_and_host_arrays(gpu_ctx) -> None:
     # One unit in the last place of bfloat16 at most, where the float32 sums straddle a rounding point.
     assert np.abs(c.astype(np.float32) - c_sim32).max() <= 2.0 ** -7 * np.abs(c_sim32).max()
     assert (c.astype(np.float32) == c_sim32).mean() > 0.98
+    # The type of C is independent of the operands' type.
+    a, b = random_inputs(200, 264, 136, "bfloat16", scale=0.25)
+    da, db = gpu_ctx.to_device(a), gpu_ctx.to_device(b)
+    dc = gpu_ctx.empty((200, 264), np.float16)
+    gpu_ctx.gemm(da, db, dc)
+    gpu_ctx.synchronize()
+    assert_narrow_close(dc.to_numpy(), a, b)
     # k == 0 and the large host paths (pageable: row panels; pinned: alternating panels).
     z = np.full((5, 9), 3.0).astype(np.float16)
     gpu_ctx.gemm_host(np.zeros((5, 0), np.float16), np.zeros((0, 9), np.float16), z, epilogue=(("add", 1.5),))
