@@ -276,67 +276,211 @@ def _check_geometry(meta: Any, dims: dict[str, Any], tile: tuple[int, int, int],
     return wave, problems
 
 
-class _BodyShape(ast.NodeVisitor):
-    """Collects the facts of the kernel body the recogniser relies on."""
-
-    def __init__(self, group: str, a: str, b: str, c: str) -> None:
-        self.group, self.a, self.b, self.c = group, a, b, c
-        self.k_loops: list[ast.For] = []
-        self.loads_in_loop: dict[str, list[ast.Subscript]] = {a: [], b: []}
-        self.c_uses_after_loop = 0
-        self._loop_depth = 0
-        self._after_loop = False
-
-    def visit_For(self, node: ast.For) -> None:
-        self.k_loops.append(node)
-        self._loop_depth += 1
-        for stmt in node.body:
-            self.visit(stmt)
-        self._loop_depth -= 1
-        self._after_loop = True
-
-    def visit_Call(self, node: ast.Call) -> None:
-        func = node.func
-        is_group_load = (isinstance(func, ast.Attribute) and func.attr == "load"
-                         and isinstance(func.value, ast.Name) and func.value.id == self.group)
-        if is_group_load and self._loop_depth == 1 and node.args:
-            src = node.args[0]
-            if isinstance(src, ast.Subscript) and isinstance(src.value, ast.Name) and src.value.id in self.loads_in_loop:
-                self.loads_in_loop[src.value.id].append(src)
-        if self._after_loop and any(isinstance(arg, ast.Name) and arg.id == self.c for arg in node.args):
-            self.c_uses_after_loop += 1
-        self.generic_visit(node)
-
-
 def _names_in(node: ast.AST | None) -> set[str]:
     return {n.id for n in ast.walk(node) if isinstance(n, ast.Name)} if node is not None else set()
 
 
 _MAX_EPILOGUE_OPS = 4
 
+# ---- integer index expressions as affine forms ------------------------------------------------
+#
+# Tile origins and window bounds are integer expressions over `group.group_id[0]`,
+# `group.group_id[1]` and the k-loop variable. They are evaluated to affine forms
+# {symbol: coefficient} ("1" is the constant term), so that `row0 : row0 + 16` with
+# `row0, col0 = _tile_origin(group.group_id[0], group.group_id[1])` can be compared with what a
+# matmul tile needs, whatever the spelling (a helper returning a tuple, two assignments, the
+# products written inline).
+
+_GID0, _GID1, _KVAR, _ONE = "group_id[0]", "group_id[1]", "k", "1"
+Affine = dict
+
+
+def _affine_const(value: int) -> Affine:
+    return {_ONE: int(value)} if value else {}
+
+
+def _affine_add(x: Affine, y: Affine, sign: int = 1) -> Affine:
+    out = dict(x)
+    for key, coeff in y.items():
+        out[key] = out.get(key, 0) + sign * coeff
+    return {key: coeff for key, coeff in out.items() if coeff}
+
+
+def _affine_mul(x: Affine, y: Affine) -> Affine | None:
+    for scalar, other in ((x, y), (y, x)):
+        if set(scalar) <= {_ONE}:
+            factor = scalar.get(_ONE, 0)
+            return {key: coeff * factor for key, coeff in other.items() if coeff * factor}
+    return None
+
+
+def _affine_text(x: Affine) -> str:
+    if not x:
+        return "0"
+    parts = []
+    for key, coeff in sorted(x.items(), key=lambda item: item[0] == _ONE):
+        parts.append(str(coeff) if key == _ONE else (key if coeff == 1 else f"{coeff}*{key}"))
+    return " + ".join(parts)
+
+
+def _function_consts(fn: Any) -> dict[str, Any]:
+    consts = dict(getattr(fn, "__globals__", {}))
+    try:
+        consts.update(inspect.getclosurevars(fn).nonlocals)
+    except (TypeError, ValueError):
+        pass
+    return consts
+
+
+def _function_node(fn: Any) -> ast.FunctionDef | None:
+    try:
+        tree = ast.parse(textwrap.dedent(inspect.getsource(fn)))
+    except (OSError, TypeError, SyntaxError, IndentationError):
+        return None
+    return next((n for n in tree.body if isinstance(n, (ast.FunctionDef, ast.AsyncFunctionDef))), None)
+
+
+def _without_docstring(body: list[ast.stmt]) -> list[ast.stmt]:
+    if body and isinstance(body[0], ast.Expr) and isinstance(body[0].value, ast.Constant) \
+            and isinstance(body[0].value.value, str):
+        return body[1:]
+    return body
+
+
+class _IndexEvaluator:
+    """Evaluates integer index expressions of one function body to affine forms."""
+
+    def __init__(self, group: str, consts: dict[str, Any], depth: int = 0) -> None:
+        self.group, self.consts, self.depth = group, consts, depth
+        self.env: dict[str, Any] = {}  # name -> Affine | tuple of Affine
+
+    def eval(self, node: ast.AST | None) -> Any:
+        if isinstance(node, ast.Constant):
+            value = node.value
+            return _affine_const(value) if isinstance(value, int) and not isinstance(value, bool) else None
+        if isinstance(node, ast.Name):
+            if node.id in self.env:
+                return self.env[node.id]
+            value = self.consts.get(node.id)
+            if isinstance(value, (int, np.integer)) and not isinstance(value, bool):
+                return _affine_const(int(value))
+            return None
+        if isinstance(node, ast.Tuple):
+            parts = tuple(self.eval(elt) for elt in node.elts)
+            return None if any(part is None or isinstance(part, tuple) for part in parts) else parts
+        if isinstance(node, ast.UnaryOp) and isinstance(node.op, (ast.USub, ast.UAdd)):
+            inner = self.eval(node.operand)
+            if not isinstance(inner, dict):
+                return None
+            return _affine_add({}, inner, -1) if isinstance(node.op, ast.USub) else inner
+        if isinstance(node, ast.BinOp):
+            left, right = self.eval(node.left), self.eval(node.right)
+            if not isinstance(left, dict) or not isinstance(right, dict):
+                return None
+            if isinstance(node.op, ast.Add):
+                return _affine_add(left, right)
+            if isinstance(node.op, ast.Sub):
+                return _affine_add(left, right, -1)
+            if isinstance(node.op, ast.Mult):
+                return _affine_mul(left, right)
+            return None
+        if isinstance(node, ast.Subscript):
+            index = node.slice
+            if not (isinstance(index, ast.Constant) and isinstance(index.value, int)):
+                return None
+            base = node.value
+            if (isinstance(base, ast.Attribute) and base.attr == "group_id" and isinstance(base.value, ast.Name)
+                    and base.value.id == self.group and self.group and index.value in (0, 1)):
+                return {(_GID0, _GID1)[index.value]: 1}
+            whole = self.eval(base)
+            if isinstance(whole, tuple) and 0 <= index.value < len(whole):
+                return whole[index.value]
+            return None
+        if isinstance(node, ast.Call):
+            return self._inline(node)
+        return None
+
+    def _inline(self, node: ast.Call) -> Any:
+        """A call of a plain Python helper whose body is one `return <index expression>`."""
+        if node.keywords or not isinstance(node.func, ast.Name) or self.depth >= 4:
+            return None
+        fn = self.consts.get(node.func.id)
+        if not isinstance(fn, FunctionType):
+            return None
+        args = [self.eval(arg) for arg in node.args]
+        if any(not isinstance(arg, dict) for arg in args):
+            return None
+        fn_node = _function_node(fn)
+        if fn_node is None:
+            return None
+        spec = fn_node.args
+        if spec.vararg or spec.kwarg or spec.kwonlyargs or spec.defaults or len(spec.args) != len(args):
+            return None
+        body = _without_docstring(list(fn_node.body))
+        if len(body) != 1 or not isinstance(body[0], ast.Return):
+            return None
+        inner = _IndexEvaluator("", _function_consts(fn), self.depth + 1)
+        inner.env = {param.arg: arg for param, arg in zip(spec.args, args)}
+        return inner.eval(body[0].value)
+
+    def assign(self, stmt: ast.Assign) -> bool:
+        """Binds the targets of an index assignment; False if it is not one."""
+        if len(stmt.targets) != 1:
+            return False
+        target, value = stmt.targets[0], self.eval(stmt.value)
+        if isinstance(target, ast.Name) and isinstance(value, dict):
+            self.env[target.id] = value
+            return True
+        if (isinstance(target, ast.Tuple) and isinstance(value, tuple) and len(target.elts) == len(value)
+                and all(isinstance(elt, ast.Name) for elt in target.elts)):
+            for elt, part in zip(target.elts, value):
+                self.env[elt.id] = part
+            return True
+        return False
+
+
+_FORBIDDEN_IN_HELPERS = (ast.If, ast.While, ast.For, ast.Try, ast.With, ast.IfExp, ast.Lambda, ast.Global,
+                         ast.Nonlocal, ast.Match, ast.ListComp, ast.SetComp, ast.DictComp, ast.GeneratorExp)
+
+
+def _helper_is_straight_line(fn: Any) -> str | None:
+    """The workgroup helpers are validated by running them on probe workgroups (`hc._tile_probe`);
+    that only means something for code without branches or loops of its own."""
+    fn_node = _function_node(fn)
+    if fn_node is None:
+        return f"source of helper `{getattr(fn, '__name__', fn)}` is unavailable"
+    for node in ast.walk(fn_node):
+        if isinstance(node, _FORBIDDEN_IN_HELPERS):
+            return (f"helper `{fn.__name__}` contains a `{type(node).__name__}` statement or expression; helpers "
+                    f"around the intrinsic must be straight-line code")
+    return None
+
 
 def _check_body(kernel_fn: Any, params: list[str], a: str, b: str, c: str, tile: tuple[int, int, int],
                 k_dim: Any, b_transposed: bool = False, bias: str | None = None,
                 facts: dict[str, Any] | None = None, output_dtype: str = "float32") -> list[str]:
-    """Structural check of the k-loop: `for k0 in range(0, K, tk)` with one masked load of an
-    A window `a[rows, k0:k0+tk]` and one of a B window `b[k0:k0+tk, cols]`, then a store
-    that receives `c`. Returns problems (empty when the body has the expected shape).
+    """Checks that the kernel body is, statement for statement, the tiled matmul of
+    examples/amdgpu_gfx11_wmma_matmul.py:312-326 (or a member of its family):
 
-    `facts`, when given, receives what surrounds the loop: "accumulate" (the accumulators come
-    from a call that is given `c` before the loop) and "epilogue" (the element-wise statements on
-    the accumulators between the loop and the store)."""
-    try:
-        tree = ast.parse(textwrap.dedent(inspect.getsource(kernel_fn)))
-    except (OSError, TypeError, SyntaxError):
-        return ["kernel source is unavailable, so its k-loop cannot be checked"]
-    fn_node = next((n for n in tree.body if isinstance(n, (ast.FunctionDef, ast.AsyncFunctionDef))), None)
+        row0, col0 = <index expressions equal to group.group_id[0] * tm, group.group_id[1] * tn>
+        acc = <init helper>(group[, c, row0, col0])
+        for k0 in range(0, K, tk):
+            a_tile = group.load(a[row0 : row0 + tm, k0 : k0 + tk], shape=(tm, tk))
+            b_tile = group.load(b[k0 : k0 + tk, col0 : col0 + tn], shape=(tk, tn))   # or b[cols, ks]
+            acc = <step helper>(group, a_tile, b_tile, acc)
+        acc = <element-wise statement>            # zero or more
+        <store helper>(group, c, row0, col0, acc)
+
+    and nothing else. Returns problems (empty when the body has that form).
+
+    `facts` receives "accumulate", "epilogue" and "calls": the helper calls with their arguments
+    classified, for the probe that validates what the helpers do (`hc._tile_probe`)."""
+    fn_node = _function_node(kernel_fn)
     if fn_node is None:
-        return ["kernel source does not define a function"]
-    consts = dict(getattr(kernel_fn, "__globals__", {}))
-    try:
-        consts.update(inspect.getclosurevars(kernel_fn).nonlocals)
-    except (TypeError, ValueError):
-        pass
+        return ["kernel source is unavailable, so its body cannot be checked"]
+    consts = _function_consts(kernel_fn)
+    group = params[0]
+    tm, tn, tk = tile
 
     def const_value(node: ast.AST | None) -> Any:
         if isinstance(node, ast.Constant):
@@ -345,49 +489,258 @@ def _check_body(kernel_fn: Any, params: list[str], a: str, b: str, c: str, tile:
             return consts.get(node.id)
         return None
 
-    shape = _BodyShape(params[0], a, b, c)
-    for stmt in fn_node.body:
-        shape.visit(stmt)
+    body = _without_docstring(list(fn_node.body))
+    loops = [stmt for stmt in body if isinstance(stmt, ast.For)]
+    nested = [n for stmt in body for n in ast.walk(stmt) if isinstance(n, (ast.For, ast.While)) and n not in loops]
+    if len(loops) != 1 or nested:
+        return [f"expected exactly one k-loop in the kernel body, found {len(loops) + len(nested)}"
+                if len(loops) + len(nested) != 1 else "the k-loop must be a top-level statement of the kernel body"]
+    loop = loops[0]
+    at = body.index(loop)
     problems: list[str] = []
-    if len(shape.k_loops) != 1:
-        return [f"expected exactly one k-loop in the kernel body, found {len(shape.k_loops)}"]
-    loop = shape.k_loops[0]
-    tk = tile[2]
+
+    # -- the loop header ---------------------------------------------------------------------
     it = loop.iter
     ok_range = (isinstance(it, ast.Call) and isinstance(it.func, ast.Name) and it.func.id == "range"
-                and len(it.args) == 3 and const_value(it.args[0]) == 0 and const_value(it.args[2]) == tk)
-    if ok_range:
-        stop = it.args[1]
-        # K may be spelled `a.shape[1]`, `b.shape[0]` or as the K symbol / literal itself.
-        spelled = ast.unparse(stop).replace(" ", "")
-        k_names = {f"{a}.shape[1]", f"{b}.shape[1]" if b_transposed else f"{b}.shape[0]"}
-        if isinstance(k_dim, str):
-            k_names.add(k_dim)
-        if spelled not in k_names and const_value(stop) != k_dim:
-            problems.append(f"k-loop bound `{ast.unparse(stop)}` is not the shared extent of {a} and {b}")
-    else:
-        problems.append(f"k-loop must be `for k0 in range(0, K, {tk})`")
-    k_var = loop.target.id if isinstance(loop.target, ast.Name) else None
-    for name, axis in ((a, 1), (b, 1 if b_transposed else 0)):
-        loads = shape.loads_in_loop[name]
-        if len(loads) != 1:
-            problems.append(f"expected one group.load of a window of `{name}` per k-step, found {len(loads)}")
+                and not it.keywords and len(it.args) == 3 and const_value(it.args[0]) == 0
+                and const_value(it.args[2]) == tk and isinstance(loop.target, ast.Name) and not loop.orelse)
+    if not ok_range:
+        return [f"k-loop must be `for k0 in range(0, K, {tk})`"]
+    stop = it.args[1]
+    # K may be spelled `a.shape[1]`, `b.shape[0]` or as the K symbol / literal itself.
+    spelled = ast.unparse(stop).replace(" ", "")
+    k_names = {f"{a}.shape[1]", f"{b}.shape[1]" if b_transposed else f"{b}.shape[0]"}
+    if isinstance(k_dim, str):
+        k_names.add(k_dim)
+    if spelled not in k_names and const_value(stop) != k_dim:
+        problems.append(f"k-loop bound `{ast.unparse(stop)}` is not the shared extent of {a} and {b}")
+    k_var = loop.target.id
+
+    # -- the accumulator variable: `acc = f(..., acc)` closes the loop body --------------------
+    def plain_call(node: ast.AST | None) -> ast.Call | None:
+        ok = (isinstance(node, ast.Call) and isinstance(node.func, ast.Name) and not node.keywords
+              and not any(isinstance(arg, ast.Starred) for arg in node.args))
+        return node if ok else None
+
+    def single_name_target(stmt: ast.stmt) -> str | None:
+        if isinstance(stmt, ast.Assign) and len(stmt.targets) == 1 and isinstance(stmt.targets[0], ast.Name):
+            return stmt.targets[0].id
+        return None
+
+    acc = None
+    for stmt in loop.body:
+        name = single_name_target(stmt)
+        call = plain_call(stmt.value) if name else None
+        if call is not None and any(isinstance(arg, ast.Name) and arg.id == name for arg in call.args):
+            acc = name
+    if acc is None:
+        return problems + ["the k-loop must update the accumulators as `acc = f(group, a_tile, b_tile, acc)`"]
+
+    # -- before the loop: tile origins, then the accumulator initialiser -----------------------
+    index = _IndexEvaluator(group, consts)
+    row_origin, col_origin = {_GID0: tm}, {_GID1: tn}
+    calls: dict[str, Any] = {}
+
+    def classify(call: ast.Call, what: str, tiles: dict[str, str]) -> tuple[tuple, ...] | None:
+        """The arguments of a helper call as the probe takes them, or None (problem recorded)."""
+        kinds: list[tuple] = []
+        for arg in call.args:
+            if isinstance(arg, ast.Name) and arg.id == group:
+                kinds.append(("group",))
+            elif isinstance(arg, ast.Name) and arg.id == c:
+                kinds.append(("c",))
+            elif isinstance(arg, ast.Name) and arg.id == acc:
+                kinds.append(("acc",))
+            elif isinstance(arg, ast.Name) and bias is not None and arg.id == bias:
+                kinds.append(("bias",))
+            elif isinstance(arg, ast.Name) and arg.id in tiles:
+                kinds.append((tiles[arg.id],))
+            else:
+                value = index.eval(arg)
+                if value == row_origin:
+                    kinds.append(("origin", lambda g0, g1: g0 * tm))
+                elif value == col_origin:
+                    kinds.append(("origin", lambda g0, g1: g1 * tn))
+                else:
+                    found = _affine_text(value) if isinstance(value, dict) else "not an index expression"
+                    problems.append(
+                        f"argument `{ast.unparse(arg)}` of the {what} `{ast.unparse(call)}` must be the group, a "
+                        f"buffer, the accumulators, or the tile's row origin ({_affine_text(row_origin)}) or "
+                        f"column origin ({_affine_text(col_origin)}); it is {found}")
+                    return None
+        return tuple(kinds)
+
+    def helper_of(call: ast.Call, what: str) -> Any:
+        fn = consts.get(call.func.id)
+        if not isinstance(fn, FunctionType):
+            problems.append(f"the {what} `{ast.unparse(call)}` must call a helper function defined in Python")
+            return None
+        why = _helper_is_straight_line(fn)
+        if why:
+            problems.append(why)
+            return None
+        return fn
+
+    def helper_call(call: ast.Call, what: str, tiles: dict[str, str] | None = None) -> Any:
+        from ._tile_probe import HelperCall
+
+        fn = helper_of(call, what)
+        kinds = classify(call, what, tiles or {}) if fn is not None else None
+        return None if fn is None or kinds is None else HelperCall(fn, kinds, ast.unparse(call))
+
+    accumulate = False
+    initialised = False
+    for stmt in body[:at]:
+        text = ast.unparse(stmt)
+        if single_name_target(stmt) == acc:
+            call = plain_call(stmt.value)
+            if call is None or initialised:
+                problems.append(f"`{text}`: the accumulators must be initialised once, by a call such as "
+                                f"`{acc} = zero_accumulators({group})` or `{acc} = load_accumulators({group}, {c}, "
+                                f"row0, col0)`")
+                continue
+            initialised = True
+            calls["init"] = helper_call(call, "accumulator initialiser")
+            kinds = calls["init"].args if calls["init"] is not None else ()
+            accumulate = ("c",) in kinds
+            if ("acc",) in kinds or ("bias",) in kinds:
+                problems.append(f"`{text}`: the accumulator initialiser may only receive the group, `{c}` and "
+                                f"the tile origin")
+        elif initialised or not (isinstance(stmt, ast.Assign) and index.assign(stmt)):
+            problems.append(f"`{text}` before the k-loop is neither a tile-origin assignment (an integer "
+                            f"expression over {group}.group_id) nor the accumulator initialiser")
+    if not initialised:
+        problems.append(f"`{acc}` must be initialised before the k-loop")
+    if accumulate and output_dtype != "float32":
+        problems.append(f"a kernel that loads its accumulators from `{c}` needs a float32 `{c}` (got {output_dtype})")
+
+    # -- the loop body: one window of a, one of b, one step -----------------------------------
+    index.env[k_var] = {_KVAR: 1}
+    tiles: dict[str, str] = {}
+    b_axes = (1, 0) if b_transposed else (0, 1)  # (k axis, n axis) of b as stored
+    wanted = {
+        a: ("a_tile", ((row_origin, tm, "rows", f"{group}.group_id[0] * {tm}"), ({_KVAR: 1}, tk, "columns", k_var))),
+        b: ("b_tile", tuple(
+            ({_KVAR: 1}, tk, "rows" if axis == 0 else "columns", k_var) if axis == b_axes[0]
+            else (col_origin, tn, "rows" if axis == 0 else "columns", f"{group}.group_id[1] * {tn}")
+            for axis in (0, 1))),
+    }
+    step_stmt = None
+    for stmt in loop.body:
+        text = ast.unparse(stmt)
+        name = single_name_target(stmt)
+        if name == acc and step_stmt is None and plain_call(stmt.value) is not None:
+            step_stmt = stmt
             continue
-        index = loads[0].slice
-        parts = list(index.elts) if isinstance(index, ast.Tuple) else [index]
-        if len(parts) != 2 or not all(isinstance(p, ast.Slice) for p in parts):
-            problems.append(f"the load of `{name}` must slice both axes")
+        load = stmt.value if name and isinstance(stmt.value, ast.Call) else None
+        func = load.func if load is not None else None
+        is_load = (isinstance(func, ast.Attribute) and func.attr == "load" and isinstance(func.value, ast.Name)
+                   and func.value.id == group and len(load.args) == 1
+                   and isinstance(load.args[0], ast.Subscript) and isinstance(load.args[0].value, ast.Name)
+                   and load.args[0].value.id in wanted)
+        if not is_load or step_stmt is not None:
+            problems.append(f"`{text}` in the k-loop is not one of: a `{group}.load` of a window of `{a}`, one of "
+                            f"`{b}`, then `{acc} = f({group}, a_tile, b_tile, {acc})`")
             continue
-        k_slice, other = parts[axis], parts[1 - axis]
-        if k_var is None or k_var not in _names_in(k_slice.lower) or k_var not in _names_in(k_slice.upper):
-            problems.append(f"axis {axis} of the `{name}` window must advance with the k-loop variable")
-        if k_var is not None and k_var in (_names_in(other.lower) | _names_in(other.upper)):
-            problems.append(f"axis {1 - axis} of the `{name}` window must not depend on the k-loop variable")
-    if shape.c_uses_after_loop < 1:
+        source = load.args[0]
+        buffer = source.value.id
+        role, axes = wanted[buffer]
+        if role in tiles.values():
+            problems.append(f"expected one group.load of a window of `{buffer}` per k-step, found another: `{text}`")
+            continue
+        tiles[name] = role
+        parts = list(source.slice.elts) if isinstance(source.slice, ast.Tuple) else [source.slice]
+        if len(parts) != 2 or not all(isinstance(p, ast.Slice) and p.step is None for p in parts):
+            problems.append(f"the load of `{buffer}` must slice both axes as `lo:hi`")
+            continue
+        extents = []
+        for axis, (part, (origin, extent, axis_name, origin_text)) in enumerate(zip(parts, axes)):
+            lo, hi = index.eval(part.lower), index.eval(part.upper)
+            extents.append(extent)
+            if lo != origin or not isinstance(hi, dict) or _affine_add(hi, origin, -1) != _affine_const(extent):
+                k_axis = origin == {_KVAR: 1}
+                found = ast.unparse(part)
+                problems.append(
+                    f"axis {axis} of the `{buffer}` window must "
+                    + (f"advance with the k-loop variable as `{k_var} : {k_var} + {extent}`" if k_axis
+                       else f"be the tile's {axis_name} `o : o + {extent}` with o = {origin_text}")
+                    + f" (found `{found}`)")
+        keywords = {kw.arg: kw.value for kw in load.keywords}
+        shape_node = keywords.get("shape")
+        shape_ok = (set(keywords) == {"shape"} and isinstance(shape_node, ast.Tuple)
+                    and [const_value(elt) for elt in shape_node.elts] == extents)
+        if not shape_ok:
+            problems.append(f"the load of `{buffer}` must be `{group}.load(<window>, shape={tuple(extents)})` with "
+                            f"no other keyword")
+    for buffer, (role, _) in wanted.items():
+        if role not in tiles.values():
+            problems.append(f"expected one group.load of a window of `{buffer}` per k-step, found 0")
+    if step_stmt is None:
+        problems.append(f"the k-loop must end with `{acc} = f({group}, a_tile, b_tile, {acc})`")
+    elif not problems or all(role in tiles.values() for role in ("a_tile", "b_tile")):
+        call = plain_call(step_stmt.value)
+        calls["step"] = helper_call(call, "multiply-accumulate step", tiles)
+        kinds = calls["step"].args if calls["step"] is not None else None
+        if kinds is not None and (sorted(k[0] for k in kinds if k[0] != "group") != ["a_tile", "acc", "b_tile"]):
+            problems.append(f"`{ast.unparse(step_stmt)}` must receive the two tiles loaded in this k-step and "
+                            f"`{acc}`, each once, and nothing else but the group")
+
+    # -- after the loop: element-wise statements, then the store -------------------------------
+    ops: list[tuple] = []
+    stored = False
+    narrowed = False  # the accumulators have been converted to the 16-bit type of `c`
+    for stmt in body[at + 1:]:
+        text = ast.unparse(stmt)
+        if stored:
+            problems.append(f"`{text}` follows the store" + (f" and uses `{acc}` after the store"
+                                                             if acc in _names_in(stmt) else ""))
+            continue
+        call = plain_call(stmt.value) if isinstance(stmt, ast.Expr) else None
+        if call is not None and any(isinstance(arg, ast.Name) and arg.id == c for arg in call.args):
+            stored = True
+            calls["store"] = helper_call(call, "store")
+            kinds = calls["store"].args if calls["store"] is not None else None
+            if kinds is not None and (kinds.count(("c",)) != 1 or kinds.count(("acc",)) != 1 or ("bias",) in kinds):
+                problems.append(f"the store `{text}` must receive `{c}` and `{acc}`, each once")
+            continue
+        ok_target = single_name_target(stmt) == acc
+        op = _elementwise_op(stmt.value, acc, bias, const_value) if ok_target else None
+        if op is not None and op and op[0] == "astype":
+            target = _dtype_name_of(op[1], consts)
+            if target == "float32" and not narrowed:
+                continue
+            if target == output_dtype and target != "float32" and not narrowed:
+                narrowed = True
+                continue
+            op = None
+        elif op and narrowed:
+            problems.append(f"`{text}` runs on the 16-bit values: element-wise statements must come before "
+                            f"`{acc}.astype({output_dtype})`")
+            continue
+        if op is None:
+            problems.append(
+                f"`{text}` is not an element-wise statement this target folds into the store "
+                f"(`{acc} = {acc} * x`, `+ x`, `- x`, `np.maximum({acc}, x)`, `np.minimum({acc}, x)` with a "
+                f"numeric constant x, `{acc} = f(..., bias, ..., {acc})`, `{acc}.astype(<float32 or the dtype of {c}>)`)")
+            continue
+        if op[0] == "bias":
+            if "bias" in calls:
+                problems.append(f"`{bias}` must be added to `{acc}` exactly once between the k-loop and the store")
+                continue
+            calls["bias"] = helper_call(plain_call(stmt.value), "bias addition") if plain_call(stmt.value) else None
+            if plain_call(stmt.value) is None:
+                problems.append(f"`{text}` must be a plain call `{acc} = f({group}, {bias}, col0, {acc})`")
+        ops.append(op)
+    if not stored:
         problems.append(f"`{c}` must be passed to a store after the k-loop")
-    surroundings = _loop_surroundings(fn_node, loop, c, bias, const_value, problems, output_dtype, consts)
+    if len(ops) > _MAX_EPILOGUE_OPS:
+        problems.append(f"at most {_MAX_EPILOGUE_OPS} element-wise statements can be folded into the store, "
+                        f"found {len(ops)}")
+    bias_ops = sum(1 for op in ops if op[0] == "bias")
+    if bias is not None and bias_ops != 1 and not any("exactly once" in p for p in problems):
+        problems.append(f"`{bias}` must be added to `{acc}` exactly once between the k-loop and the store")
     if facts is not None:
-        facts.update(surroundings)
+        facts.update({"accumulate": accumulate, "epilogue": tuple(ops), "calls": calls})
     return problems
 
 
@@ -428,89 +781,6 @@ def _dtype_name_of(node: ast.AST, consts: dict[str, Any]) -> str | None:
         return np.dtype(value).name
     except (KeyError, AttributeError, TypeError):
         return None
-
-
-def _loop_surroundings(fn_node: ast.AST, loop: ast.For, c: str, bias: str | None, const_value: Any,
-                       problems: list[str], output_dtype: str = "float32",
-                       consts: dict[str, Any] | None = None) -> dict[str, Any]:
-    """Reads the top-level statements before and after the k-loop (see `_check_body`)."""
-    body = list(fn_node.body)
-    if loop not in body:
-        problems.append("the k-loop must be a top-level statement of the kernel body")
-        return {"accumulate": False, "epilogue": ()}
-    at = body.index(loop)
-
-    def call_names(node: ast.AST) -> set[str]:
-        return {arg.id for arg in getattr(node, "args", ()) if isinstance(arg, ast.Name)}
-
-    # The accumulator variable: assigned in the loop from a call that also receives it.
-    acc = None
-    for stmt in loop.body:
-        if (isinstance(stmt, ast.Assign) and len(stmt.targets) == 1 and isinstance(stmt.targets[0], ast.Name)
-                and isinstance(stmt.value, ast.Call) and stmt.targets[0].id in call_names(stmt.value)):
-            acc = stmt.targets[0].id
-    if acc is None:
-        problems.append("the k-loop must update the accumulators as `acc = f(..., acc)`")
-        return {"accumulate": False, "epilogue": ()}
-
-    accumulate = False
-    initialised = False
-    for stmt in body[:at]:
-        if (isinstance(stmt, ast.Assign) and len(stmt.targets) == 1 and isinstance(stmt.targets[0], ast.Name)
-                and stmt.targets[0].id == acc):
-            initialised = True
-            accumulate = isinstance(stmt.value, ast.Call) and c in call_names(stmt.value)
-        elif c in _names_in(stmt):
-            problems.append(f"`{c}` may only be read before the k-loop to initialise `{acc}`")
-    if not initialised:
-        problems.append(f"`{acc}` must be initialised before the k-loop")
-
-    if accumulate and output_dtype != "float32":
-        problems.append(f"a kernel that loads its accumulators from `{c}` needs a float32 `{c}` (got {output_dtype})")
-    ops: list[tuple] = []
-    stored = False
-    narrowed = False  # the accumulators have been converted to the 16-bit type of `c`
-    for stmt in body[at + 1:]:
-        text = ast.unparse(stmt)
-        if isinstance(stmt, ast.Expr) and isinstance(stmt.value, ast.Call) and c in call_names(stmt.value):
-            if acc not in call_names(stmt.value):
-                problems.append(f"the store `{text}` must receive `{acc}`")
-            stored = True
-            continue
-        if acc not in _names_in(stmt):
-            continue
-        if stored:
-            problems.append(f"`{text}` uses `{acc}` after the store")
-            continue
-        ok_target = (isinstance(stmt, ast.Assign) and len(stmt.targets) == 1
-                     and isinstance(stmt.targets[0], ast.Name) and stmt.targets[0].id == acc)
-        op = _elementwise_op(stmt.value, acc, bias, const_value) if ok_target else None
-        if op is not None and op and op[0] == "astype":
-            target = _dtype_name_of(op[1], consts or {})
-            if target == "float32" and not narrowed:
-                continue
-            if target == output_dtype and target != "float32" and not narrowed:
-                narrowed = True
-                continue
-            op = None
-        elif op and narrowed:
-            problems.append(f"`{text}` runs on the 16-bit values: element-wise statements must come before "
-                            f"`{acc}.astype({output_dtype})`")
-            continue
-        if op is None:
-            problems.append(
-                f"`{text}` is not an element-wise statement this target folds into the store "
-                f"(`{acc} = {acc} * x`, `+ x`, `- x`, `np.maximum({acc}, x)`, `np.minimum({acc}, x)` with a "
-                f"numeric constant x, `{acc} = f(..., bias, ..., {acc})`, `{acc}.astype(<float32 or the dtype of {c}>)`)")
-        elif op:
-            ops.append(op)
-    if len(ops) > _MAX_EPILOGUE_OPS:
-        problems.append(f"at most {_MAX_EPILOGUE_OPS} element-wise statements can be folded into the store, "
-                        f"found {len(ops)}")
-    bias_ops = sum(1 for op in ops if op[0] == "bias")
-    if bias is not None and bias_ops != 1:
-        problems.append(f"`{bias}` must be added to `{acc}` exactly once between the k-loop and the store")
-    return {"accumulate": accumulate, "epilogue": tuple(ops)}
 
 
 def _elementwise_op(value: ast.AST, acc: str, bias: str | None, const_value: Any) -> tuple | None:
@@ -586,6 +856,28 @@ def _run_lowering_hook(intrinsic: Any, tile: tuple[int, int, int], wave: int, dt
     if variant not in _VARIANTS:
         return None, [f"lowering hook of {intrinsic.__name__}: variant must be one of {list(_VARIANTS)}"]
     return dict(result), []
+
+
+def _probe_helpers(facts: dict[str, Any], tile: tuple[int, int, int], wave: int, acc_len: int,
+                   input_dtype: str, b_transposed: bool) -> list[str]:
+    """Runs the helper calls `_check_body` classified on probe workgroups (`hc._tile_probe`): the
+    initialiser, the step with its intrinsic, the bias addition and the store must together leave
+    `(c +) a @ b (+ bias)` in exactly the workgroup's tile of `c`, at interior, edge and corner tiles."""
+    from ._tile_probe import probe_helper_chain
+
+    calls = facts.get("calls", {})
+    if any(calls.get(key) is None for key in ("init", "step", "store")):
+        return ["the kernel's helper calls could not be resolved"]
+    if input_dtype == "bfloat16":
+        import ml_dtypes
+
+        element_type: Any = ml_dtypes.bfloat16
+    else:
+        element_type = np.dtype(input_dtype).type
+    return probe_helper_chain(init=calls["init"], step=calls["step"], store=calls["store"],
+                              bias=calls.get("bias"), tile=tile, wave=wave, acc_len=acc_len,
+                              input_dtype=element_type, accumulate=bool(facts.get("accumulate")),
+                              b_transposed=b_transposed)
 
 
 # ------------------------------------------------------------------ recogniser ----------
@@ -677,6 +969,9 @@ def recognise_tiled_matmul(kernel_fn: Any) -> tuple[GemmContract | None, list[st
     problems.extend(geometry_problems)
     facts: dict[str, Any] = {}
     problems.extend(_check_body(kernel_fn, params, a, b, c, tile, k_dim, b_transposed, bias, facts, output_dtype))
+    if problems:
+        return None, [f"{name}: {p}" for p in problems]
+    problems.extend(_probe_helpers(facts, tile, wave, acc_len, input_dtype, b_transposed))
     if problems:
         return None, [f"{name}: {p}" for p in problems]
 

@@ -78,7 +78,7 @@ class _PlanInfo(ctypes.Structure):
         ("variant", ctypes.c_int32), ("tiles_m", ctypes.c_int32), ("tiles_n", ctypes.c_int32),
         ("splits", ctypes.c_int32), ("grid", ctypes.c_int32), ("repack_a", ctypes.c_int32),
         ("repack_b", ctypes.c_int32), ("kernel_launches", ctypes.c_int32),
-        ("scratch_bytes", ctypes.c_int64), ("first_split_tile", ctypes.c_int32), ("reserved", ctypes.c_int32),
+        ("scratch_bytes", ctypes.c_int64), ("first_split_tile", ctypes.c_int32), ("ring_stages", ctypes.c_int32),
     ]
 
 
@@ -210,6 +210,7 @@ class GemmPlan:
         self.kernel_launches = info.kernel_launches
         self.scratch_bytes = info.scratch_bytes
         self.first_split_tile = info.first_split_tile
+        self.ring_stages = info.ring_stages  # skinny: shared-memory ring depth of this grid; else 0
 
     def __repr__(self) -> str:
         splits = f"{self.splits}" + (f" from tile {self.first_split_tile}" if self.first_split_tile else "")

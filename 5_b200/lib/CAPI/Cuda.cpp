@@ -326,6 +326,7 @@ int plan_gemm(const HcCudaContext *ctx, const HcCudaGemmArgs *args, int sm_count
     const int64_t units = static_cast<int64_t>(plan->tiles_n) * plan->splits;
     const int64_t slots = static_cast<int64_t>(sm_count) * 2;
     plan->grid = static_cast<int32_t>(units < slots ? units : slots);
+    plan->ring_stages = hc::sm100::skinny_ring_stages(static_cast<int>(m), plan->grid, sm_count);
     scratch += static_cast<int64_t>(
         hc::sm100::skinny_partials_bytes(static_cast<int>(m), static_cast<int>(n), plan->splits));
   }
@@ -556,7 +557,8 @@ int enqueue_gemm(HcCudaContext *ctx, const HcCudaGemmArgs *args, const HcCudaGem
   }
   HC_TRY_CUDA(ctx, hc::sm100::launch_gemm_skinny(tmap_a, tmap_b, args->c, m, n, k, args->ldc,
                                                  args->dtype, plan.splits, partials, ctx->counters,
-                                                 plan.grid, b_layout, ep, ctx->status_dev, ctx->stream));
+                                                 plan.grid, ctx->prop.multiProcessorCount, b_layout, ep,
+                                                 ctx->status_dev, ctx->stream));
   return HC_CUDA_OK;
 }
 

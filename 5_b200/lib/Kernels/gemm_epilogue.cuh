@@ -36,6 +36,19 @@ __device__ __forceinline__ uint16_t round_to_16(float v, int c_dtype) {
   return __bfloat16_as_ushort(__float2bfloat16_rn(v));
 }
 
+// maximum / minimum as NumPy (and so the reference simulator) define them: a NaN operand gives
+// NaN, where fmaxf/fminf would return the other operand.
+__device__ __forceinline__ float max_nan(float a, float b) {
+  float d;
+  asm("max.NaN.f32 %0, %1, %2;" : "=f"(d) : "f"(a), "f"(b));
+  return d;
+}
+__device__ __forceinline__ float min_nan(float a, float b) {
+  float d;
+  asm("min.NaN.f32 %0, %1, %2;" : "=f"(d) : "f"(a), "f"(b));
+  return d;
+}
+
 // One element of C of whatever type, at element index `index`.
 __device__ __forceinline__ void store_c_element(void *c, long long index, float v, int c_dtype) {
   if (c_dtype == kCTypeF32)
@@ -54,8 +67,8 @@ __device__ __forceinline__ float finish_value(float v, const float *dst, int col
       const int kind = ep.op_kind[i];
       const float x = kind == kEpilogueBiasColumn ? __ldg(ep.bias + col) : ep.op_value[i];
       v = kind == kEpilogueScale ? v * x
-        : kind == kEpilogueMax   ? fmaxf(v, x)
-        : kind == kEpilogueMin   ? fminf(v, x)
+        : kind == kEpilogueMax   ? max_nan(v, x)
+        : kind == kEpilogueMin   ? min_nan(v, x)
                                  : v + x;
     }
   }
@@ -83,9 +96,9 @@ __device__ __forceinline__ float4 finish_group(float4 v, const float *dst, int c
       if (kind == kEpilogueScale) {
         v.x *= x.x; v.y *= x.y; v.z *= x.z; v.w *= x.w;
       } else if (kind == kEpilogueMax) {
-        v.x = fmaxf(v.x, x.x); v.y = fmaxf(v.y, x.y); v.z = fmaxf(v.z, x.z); v.w = fmaxf(v.w, x.w);
+        v.x = max_nan(v.x, x.x); v.y = max_nan(v.y, x.y); v.z = max_nan(v.z, x.z); v.w = max_nan(v.w, x.w);
       } else if (kind == kEpilogueMin) {
-        v.x = fminf(v.x, x.x); v.y = fminf(v.y, x.y); v.z = fminf(v.z, x.z); v.w = fminf(v.w, x.w);
+        v.x = min_nan(v.x, x.x); v.y = min_nan(v.y, x.y); v.z = min_nan(v.z, x.z); v.w = min_nan(v.w, x.w);
       } else {
         v.x += x.x; v.y += x.y; v.z += x.z; v.w += x.w;
       }
@@ -118,12 +131,12 @@ __device__ __forceinline__ void apply_ops_to_groups(float4 (&v)[8], const Epilog
     } else if (kind == kEpilogueMax) {
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        v[i].x = fmaxf(v[i].x, x); v[i].y = fmaxf(v[i].y, x); v[i].z = fmaxf(v[i].z, x); v[i].w = fmaxf(v[i].w, x);
+        v[i].x = max_nan(v[i].x, x); v[i].y = max_nan(v[i].y, x); v[i].z = max_nan(v[i].z, x); v[i].w = max_nan(v[i].w, x);
       }
     } else if (kind == kEpilogueMin) {
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        v[i].x = fminf(v[i].x, x); v[i].y = fminf(v[i].y, x); v[i].z = fminf(v[i].z, x); v[i].w = fminf(v[i].w, x);
+        v[i].x = min_nan(v[i].x, x); v[i].y = min_nan(v[i].y, x); v[i].z = min_nan(v[i].z, x); v[i].w = min_nan(v[i].w, x);
       }
     } else {
 #pragma unroll
@@ -177,11 +190,11 @@ __device__ __forceinline__ void apply_ops_to_column(float (&v)[N], float bias, c
     } else if (kind == kEpilogueMax) {
 #pragma unroll
       for (int j = 0; j < N; ++j)
-        v[j] = fmaxf(v[j], x);
+        v[j] = max_nan(v[j], x);
     } else if (kind == kEpilogueMin) {
 #pragma unroll
       for (int j = 0; j < N; ++j)
-        v[j] = fminf(v[j], x);
+        v[j] = min_nan(v[j], x);
     } else {
 #pragma unroll
       for (int j = 0; j < N; ++j)
@@ -215,11 +228,11 @@ __device__ __forceinline__ void apply_ops_lane_row(uint32_t (&r)[32], int col0, 
     } else if (kind == kEpilogueMax) {
 #pragma unroll
       for (int j = 0; j < 32; ++j)
-        r[j] = __float_as_uint(fmaxf(__uint_as_float(r[j]), x));
+        r[j] = __float_as_uint(max_nan(__uint_as_float(r[j]), x));
     } else if (kind == kEpilogueMin) {
 #pragma unroll
       for (int j = 0; j < 32; ++j)
-        r[j] = __float_as_uint(fminf(__uint_as_float(r[j]), x));
+        r[j] = __float_as_uint(min_nan(__uint_as_float(r[j]), x));
     } else {
 #pragma unroll
       for (int j = 0; j < 32; ++j)

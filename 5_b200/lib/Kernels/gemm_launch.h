@@ -130,6 +130,10 @@ SkinnyShape skinny_shape(int m);
 // Number of k-splits the skinny kernel would use for this problem on `sm_count` SMs.
 int skinny_choose_splits(int n, int k, int sm_count);
 
+// Ring stages a skinny launch of `grid` CTAs uses on a device with `sm_count` SMs: the deep ring
+// (all of an SM's shared memory) when no two CTAs share an SM, the shallow one otherwise.
+int skinny_ring_stages(int m, int grid, int sm_count);
+
 // Scratch the skinny kernel needs for `splits` > 1: partial sums then arrival counters.
 size_t skinny_partials_bytes(int m, int n, int splits);
 size_t skinny_counters_bytes(int n);
@@ -138,11 +142,12 @@ size_t skinny_counters_bytes(int n);
 // fixed order by the last work unit to finish each block of columns.
 //   tmap_a: A as {k (inner), m}, box {64, padded m}; tmap_b as for the dense kernel.
 //   partials / counters: scratch (ignored when splits == 1); counters must be zero on
-//   entry and are zero again on exit.
+//   entry and are zero again on exit. `max_ctas` caps the grid (two per SM); `sm_count` decides
+//   the ring depth (skinny_ring_stages).
 cudaError_t launch_gemm_skinny(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, void *c,
                                int m, int n, int k, long long ldc, int dtype, int splits,
-                               float *partials, unsigned *counters, int max_ctas, int b_layout,
-                               const Epilogue &ep, int *status, cudaStream_t stream);
+                               float *partials, unsigned *counters, int max_ctas, int sm_count,
+                               int b_layout, const Epilogue &ep, int *status, cudaStream_t stream);
 
 // k == 0 with fused element-wise work: C = ops(accumulate ? C : 0), no product to add.
 cudaError_t launch_epilogue_only(void *c, int m, int n, long long ldc, const Epilogue &ep,

@@ -332,8 +332,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a,
 template <int kMp>
 cudaError_t launch(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, void *c, int m, int n,
                    int k, long long ldc, int dtype, int splits, float *partials,
-                   unsigned *counters, int max_ctas, int b_layout, const Epilogue &ep, int *status,
-                   cudaStream_t stream) {
+                   unsigned *counters, int max_ctas, int sm_count, int b_layout, const Epilogue &ep,
+                   int *status, cudaStream_t stream) {
   using Cfg = Config<kMp>;
   static thread_local int configured_device = -1;
   int device = 0;
@@ -350,8 +350,7 @@ cudaError_t launch(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, void *c
   const int n_tiles = (n + kBlockN - 1) / kBlockN;
   const long long units = static_cast<long long>(n_tiles) * splits;
   const int grid = static_cast<int>(units < max_ctas ? units : max_ctas);
-  // max_ctas is two per SM; a grid of at most half of that leaves one CTA per SM.
-  const int num_stages = grid * 2 <= max_ctas ? Cfg::kStagesAlone : Cfg::kStagesShared;
+  const int num_stages = skinny_ring_stages(m, grid, sm_count);
   const uint32_t idesc = make_idesc_f16(dtype == kDTypeBF16 ? 1u : 0u, /*a_mn_major=*/b_layout == kBLayoutKN,
                                         /*b_mn_major=*/false, kBlockN, kMp);
   // (The first flag describes the UMMA "A" operand, which is B^T here.)
@@ -403,6 +402,18 @@ int skinny_choose_splits(int n, int k, int sm_count) {
   return splits < 1 ? 1 : splits;
 }
 
+int skinny_ring_stages(int m, int grid, int sm_count) {
+  // A grid with no more CTAs than SMs leaves every CTA alone on its SM, so each may take all of
+  // the shared memory (twice the bytes in flight); a larger grid shares an SM between two.
+  const bool alone = grid <= sm_count;
+  const int mp = skinny::padded_m(m);
+  if (mp == 16)
+    return alone ? skinny::Config<16>::kStagesAlone : skinny::Config<16>::kStagesShared;
+  if (mp == 32)
+    return alone ? skinny::Config<32>::kStagesAlone : skinny::Config<32>::kStagesShared;
+  return alone ? skinny::Config<64>::kStagesAlone : skinny::Config<64>::kStagesShared;
+}
+
 size_t skinny_partials_bytes(int m, int n, int splits) {
   if (splits <= 1)
     return 0;
@@ -418,19 +429,19 @@ size_t skinny_counters_bytes(int n) {
 
 cudaError_t launch_gemm_skinny(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, void *c,
                                int m, int n, int k, long long ldc, int dtype, int splits,
-                               float *partials, unsigned *counters, int max_ctas, int b_layout,
-                               const Epilogue &ep, int *status, cudaStream_t stream) {
-  if (m < 1 || m > 64 || splits < 1)
+                               float *partials, unsigned *counters, int max_ctas, int sm_count,
+                               int b_layout, const Epilogue &ep, int *status, cudaStream_t stream) {
+  if (m < 1 || m > 64 || splits < 1 || sm_count < 1)
     return cudaErrorInvalidValue;
   const int mp = skinny::padded_m(m);
   if (mp == 16)
     return skinny::launch<16>(tmap_a, tmap_b, c, m, n, k, ldc, dtype, splits, partials, counters,
-                              max_ctas, b_layout, ep, status, stream);
+                              max_ctas, sm_count, b_layout, ep, status, stream);
   if (mp == 32)
     return skinny::launch<32>(tmap_a, tmap_b, c, m, n, k, ldc, dtype, splits, partials, counters,
-                              max_ctas, b_layout, ep, status, stream);
+                              max_ctas, sm_count, b_layout, ep, status, stream);
   return skinny::launch<64>(tmap_a, tmap_b, c, m, n, k, ldc, dtype, splits, partials, counters,
-                            max_ctas, b_layout, ep, status, stream);
+                            max_ctas, sm_count, b_layout, ep, status, stream);
 }
 
 } // namespace sm100

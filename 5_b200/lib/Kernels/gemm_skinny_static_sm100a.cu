@@ -146,6 +146,7 @@ int hcCudaGemmSkinnyStatic(const HcCudaGemmArgs *args, void *stream, int synchro
   const int m = static_cast<int>(args->m), n = static_cast<int>(args->n), k = static_cast<int>(args->k);
   if (plan.variant == HC_CUDA_GEMM_NOOP)
     return HC_CUDA_OK;
+  bool launched_kernel = false;
   if (plan.variant == HC_CUDA_GEMM_ZERO_FILL) {
     err = cudaMemset2DAsync(args->c, static_cast<size_t>(args->ldc) * 4, 0, static_cast<size_t>(n) * 4,
                             static_cast<size_t>(m), cuda_stream);
@@ -186,21 +187,33 @@ int hcCudaGemmSkinnyStatic(const HcCudaGemmArgs *args, void *stream, int synchro
                         shape.block_k))
       return report(rc);
     err = hc::sm100::launch_gemm_skinny(tmap_a, tmap_b, args->c, m, n, k, args->ldc, args->dtype, plan.splits,
-                                        partials, counters, plan.grid, hc::sm100::kBLayoutKN, hc::sm100::Epilogue{},
-                                        status_word, cuda_stream);
+                                        partials, counters, plan.grid, setup->sm_count, hc::sm100::kBLayoutKN,
+                                        hc::sm100::Epilogue{}, status_word, cuda_stream);
     if (err != cudaSuccess)
       return report(fail(HC_CUDA_ERR_CUDA, std::string("launching the skinny kernel: ") + cudaGetErrorString(err)));
+    launched_kernel = true;
   }
   if (synchronize) {
+    // A zero fill launches no kernel, so there is no status to read: the word may still hold
+    // what an earlier asynchronous call left there.
     int device_status = 0;
-    err = cudaMemcpyAsync(&device_status, setup->scratch, sizeof(int), cudaMemcpyDeviceToHost, cuda_stream);
+    err = launched_kernel ? cudaMemcpyAsync(&device_status, setup->scratch, sizeof(int), cudaMemcpyDeviceToHost,
+                                            cuda_stream)
+                          : cudaSuccess;
     if (err == cudaSuccess)
       err = cudaStreamSynchronize(cuda_stream);
     if (err != cudaSuccess)
       return report(fail(HC_CUDA_ERR_CUDA, std::string("waiting for the stream: ") + cudaGetErrorString(err)));
-    if (device_status != 0)
+    if (device_status != 0) {
+      // Reported once: the word starts at zero for whoever reads it next.
+      err = cudaMemsetAsync(setup->scratch, 0, sizeof(int), cuda_stream);
+      if (err == cudaSuccess)
+        err = cudaStreamSynchronize(cuda_stream);
+      if (err != cudaSuccess)
+        cudaGetLastError();
       return report(fail(HC_CUDA_ERR_DEVICE_TIMEOUT,
                          "the kernel reported that a bounded device-side wait ran out; C is invalid"));
+    }
   }
   return HC_CUDA_OK;
 }

@@ -143,7 +143,9 @@ typedef struct HcCudaGemmPlanInfo {
   int64_t scratch_bytes;   /* context scratch the call needs */
   int32_t first_split_tile; /* dense with splits > 1: tiles before this one are computed whole (the
                                full rounds of the persistent CTAs); 0 when every tile is split */
-  int32_t reserved;
+  int32_t ring_stages;      /* skinny: stages of the CTA's shared-memory ring for this grid on
+                               `sm_count` SMs -- the deep ring (all of an SM's shared memory) when
+                               no two CTAs share an SM, else the shallow one; 0 for other variants */
 } HcCudaGemmPlanInfo;
 
 typedef struct HcCudaDeviceInfo {
@@ -284,8 +286,12 @@ HC_CUDA_CAPI_EXPORTED int hcCudaIpcClose(HcCudaContext *ctx, void *device_ptr);
  * multiples of 8 elements (no repack is possible without scratch). The split-k partial sums
  * must fit: splits * m * round_up(n, 128) * 4 <= 8 MiB and n <= 131072, otherwise
  * HC_CUDA_ERR_UNSUPPORTED. `synchronize` != 0 waits for the result and reports a device-side
- * timeout; with 0 the call returns once the work is enqueued. On failure a message is copied
- * into `error_text` (may be NULL).
+ * timeout (once: the status word is cleared after it has been reported); with 0 the call returns
+ * once the work is enqueued. A device-side timeout is observable ONLY through a call with
+ * `synchronize` != 0: the status word lives in the shared array and every launch clears it, so
+ * after an asynchronous call whose result matters, either make the last call of the batch a
+ * synchronising one or check the result by other means. On failure a message is copied into
+ * `error_text` (may be NULL).
  *
  * The first call on each device looks up the array's device address and the driver's tensor-map
  * encoder; make that first call outside any stream capture. All calls on a device share the one

@@ -191,8 +191,8 @@ static void *rows_worker(void *arg) {
         const float v = out[j];
         out[j] = kind == 1 ? v * x
                : kind == 2 ? v + x
-               : kind == 3 ? (v > x ? v : x)
-               : kind == 4 ? (v < x ? v : x)
+               : kind == 3 ? ((v > x || v != v) ? v : x) /* np.maximum: a NaN stays a NaN */
+               : kind == 4 ? ((v < x || v != v) ? v : x) /* np.minimum likewise */
                            : v + job->bias[j];
       }
     }

@@ -25,6 +25,8 @@ Fixtures (all produced by `hc.simulator.launch` on the example kernel):
       (b stored [N, K]); `b_bits` holds B as stored
   simacc_f16_m17_n19_k18_seed11
       the accumulating member of that family (C = C + A.B); `c0` holds C before the launch
+  simfusednan_bf16_m33_n17_k40_seed14
+      the fused member on inputs with infinities and a NaN (NaN must survive np.maximum)
   simfused_bf16_m33_n17_k40_seed12
       the fused member (C = maximum(0.125 * (A.B) + bias, 0)); `bias` holds the fourth buffer
   simnarrow_bf16_m33_n17_k40_seed13
@@ -83,7 +85,8 @@ def _save(name: str, a: np.ndarray, b: np.ndarray, c: np.ndarray, **extra: np.nd
 
 def main() -> int:
     parser = argparse.ArgumentParser()
-    parser.add_argument("--reference", default="/root/reference")
+    parser.add_argument("--reference", default=os.environ.get("HC_REFERENCE_DIR", "/root/reference"),
+                        help="checkout of the reference project (default: $HC_REFERENCE_DIR)")
     args = parser.parse_args()
     ex = _import_reference(Path(args.reference))
 
@@ -143,6 +146,23 @@ def main() -> int:
     c = np.full((33, 17), np.float32(-7.0))  # every element must be overwritten
     mod.hc.simulator.launch(mod.tiled_wmma_matmul_for("bfloat16", False, "fused"), a, b, c, bias)
     _save("simfused_bf16_m33_n17_k40_seed12", a, b, c, bias=bias)
+
+    # The same member on inputs that hold infinities and a NaN: np.maximum propagates NaN (inf * 0
+    # and inf - inf inside the k-sum), -inf becomes 0, +inf stays.
+    rng = np.random.default_rng(14)
+    a = rng.uniform(-1.0, 1.0, size=(33, 40)).astype(ml_dtypes.bfloat16)
+    b = rng.uniform(-1.0, 1.0, size=(40, 17)).astype(ml_dtypes.bfloat16)
+    a[3, 5] = np.inf
+    b[5, 2] = 0.0
+    a[7, 1] = np.nan
+    a[11, 0], a[11, 39] = np.inf, -np.inf
+    b[0, :], b[39, :] = 1.0, 1.0
+    a[20, 8] = -np.inf
+    bias = rng.uniform(-0.5, 0.5, size=(17,)).astype(np.float32)
+    c = np.full((33, 17), np.float32(-7.0))
+    with np.errstate(invalid="ignore"):
+        mod.hc.simulator.launch(mod.tiled_wmma_matmul_for("bfloat16", False, "fused"), a, b, c, bias)
+    _save("simfusednan_bf16_m33_n17_k40_seed14", a, b, c, bias=bias)
 
     rng = np.random.default_rng(13)
     a = rng.uniform(-1.0, 1.0, size=(33, 40)).astype(ml_dtypes.bfloat16)

@@ -18,11 +18,10 @@ from examples.b200_wmma_matmul import compiled_for, tiled_wmma_matmul_for
 M, N, K = sym.M, sym.N, sym.K
 
 
-def _family(*, tile=(16, 16, 16), wave=32, acc=8, in_dtype=np.float16, out_dtype=np.float32,
-            effects="pure", k_step=None, work_shape=None, loop=True, b_dims=None):
-    """A matmul kernel of the example's family with one aspect varied."""
-    tm, tn, tk = tile
-    step = tk if k_step is None else k_step
+def _helpers(tm, tn, tk, wave, acc, in_dtype, effects="pure", mma_body="matmul"):
+    """Real helpers of a (tm, tn, tk) tile on `wave` lanes: lane l owns column l % tn and rows
+    l // tn, l // tn + wave // tn, ... of the tile (`acc` values per lane)."""
+    step_rows = max(wave // tn, 1)
 
     @kernel.intrinsic(
         scope=WorkItem, effects=effects, const_attrs={"wave_size", "arch"},
@@ -31,36 +30,166 @@ def _family(*, tile=(16, 16, 16), wave=32, acc=8, in_dtype=np.float16, out_dtype
                        vector_type((acc,), np.float32), idx_type()),
         result_types=(vector_type((acc,), np.float32),))
     def mma(group, a_tile, b_tile, a_frag, b_frag, acc_frag, *, lane, wave_size, arch):
-        return acc_frag
+        if mma_body == "identity":
+            return acc_frag
+        a_vals = a_tile.with_inactive(value=in_dtype(0))
+        b_vals = b_tile.with_inactive(value=in_dtype(0))
+        out = np.empty((acc,), dtype=np.float32)
+        for slot in range(acc):
+            total = np.float32(acc_frag[slot])
+            for kk in range(tk):
+                total += np.float32(a_vals[lane // tn + slot * step_rows, kk]) * np.float32(b_vals[kk, lane % tn])
+            out[slot] = total
+        return group.vload(out, shape=(acc,))
 
     @kernel.func(scope=WorkGroup)
-    def step_fn(group, a_tile, b_tile, acc):
-        return mma(group, a_tile, b_tile, None, None, acc, lane=0, wave_size=wave, arch="x")
+    def zeros(group):
+        @group.workitems
+        def per_lane(wi):
+            return group.vzeros(shape=(acc,), dtype=np.float32)
+
+        return per_lane()
 
     @kernel.func(scope=WorkGroup)
-    def store(group, c, acc):
-        group.store(c, acc)
+    def ones(group):
+        @group.workitems
+        def per_lane(wi):
+            return group.vones(shape=(acc,), dtype=np.float32)
+
+        return per_lane()
+
+    @kernel.func(scope=WorkGroup)
+    def from_c(group, c, row0, col0):
+        c_tile = group.load(c[row0 : row0 + tm, col0 : col0 + tn], shape=(tm, tn))
+
+        @group.workitems
+        def per_lane(wi):
+            lane = wi.local_id()[0]
+            return c_tile[lane // tn :: step_rows, lane % tn].vec().with_inactive(value=np.float32(0))
+
+        return per_lane()
+
+    @kernel.func(scope=WorkGroup)
+    def step_fn(group, a_tile, b_tile, acc_values):
+        @group.workitems
+        def per_lane(wi):
+            lane = wi.local_id()[0]
+            return mma(group, a_tile, b_tile, a_tile[lane % tm, :].vec(), b_tile[:, lane % tn].vec(),
+                       acc_values[:, lane, 0], lane=lane, wave_size=wave, arch="x")
+
+        return per_lane()
+
+    @kernel.func(scope=WorkGroup)
+    def plus_bias(group, bias, col0, acc_values):
+        bias_tile = group.load(bias[col0 : col0 + tn], shape=(tn,))
+
+        @group.workitems
+        def per_lane(wi):
+            lane = wi.local_id()[0]
+            return acc_values[:, lane, 0] + bias_tile[lane % tn : lane % tn + 1].vec().with_inactive(value=np.float32(0))
+
+        return per_lane()
+
+    @kernel.func(scope=WorkGroup)
+    def store(group, c, row0, col0, acc_values):
+        @group.workitems
+        def per_lane(wi):
+            lane = wi.local_id()[0]
+            col = col0 + lane % tn
+            group.store(c[row0 + lane // tn : row0 + tm : step_rows, col : col + 1], acc_values[:, lane, :])
+
+        per_lane()
+
+    return mma, zeros, ones, from_c, step_fn, plus_bias, store
+
+
+def _family(*, tile=(16, 16, 16), wave=32, acc=8, in_dtype=np.float16, out_dtype=np.float32,
+            effects="pure", k_step=None, work_shape=None, loop=True, b_dims=None, mma_body="matmul",
+            windows="tile", store_at="tile", init="zeros"):
+    """A matmul kernel of the example's family with one aspect varied (or broken)."""
+    tm, tn, tk = tile
+    step = tk if k_step is None else k_step
+    mma, zeros, ones, from_c, step_fn, plus_bias, store = _helpers(tm, tn, tk, wave, acc, in_dtype, effects, mma_body)
+    start = {"zeros": zeros, "ones": ones}[init]
 
     shape = work_shape if work_shape is not None else (ceil_div(M, tm) * wave, ceil_div(N, tn))
     bd = b_dims if b_dims is not None else (K, N)
+    launch = dict(work_shape=shape, group_shape=(wave, 1), subgroup_size=wave)
 
-    if loop:
-        @kernel(work_shape=shape, group_shape=(wave, 1), subgroup_size=wave)
+    if not loop:
+        @kernel(**launch)
         def matmul(group, a: Buffer[M, K, in_dtype], b: Buffer[bd[0], bd[1], in_dtype],
                    c: Buffer[M, N, out_dtype]) -> None:
-            acc = 0
+            row0, col0 = group.group_id[0] * tm, group.group_id[1] * tn
+            a_tile = group.load(a[row0 : row0 + tm, 0:tk], shape=(tm, tk))
+            b_tile = group.load(b[0:tk, col0 : col0 + tn], shape=(tk, tn))
+            store(group, c, row0, col0, step_fn(group, a_tile, b_tile, start(group)))
+    elif windows == "constant":  # every workgroup reads the first tile row / column
+        @kernel(**launch)
+        def matmul(group, a: Buffer[M, K, in_dtype], b: Buffer[bd[0], bd[1], in_dtype],
+                   c: Buffer[M, N, out_dtype]) -> None:
+            row0, col0 = group.group_id[0] * tm, group.group_id[1] * tn
+            acc_values = start(group)
             for k0 in range(0, a.shape[1], step):
                 a_tile = group.load(a[0:tm, k0 : k0 + tk], shape=(tm, tk))
                 b_tile = group.load(b[k0 : k0 + tk, 0:tn], shape=(tk, tn))
-                acc = step_fn(group, a_tile, b_tile, acc)
-            store(group, c, acc)
-    else:
-        @kernel(work_shape=shape, group_shape=(wave, 1), subgroup_size=wave)
+                acc_values = step_fn(group, a_tile, b_tile, acc_values)
+            store(group, c, row0, col0, acc_values)
+    elif windows == "swapped":  # rows from group_id[1], columns from group_id[0]
+        @kernel(**launch)
         def matmul(group, a: Buffer[M, K, in_dtype], b: Buffer[bd[0], bd[1], in_dtype],
                    c: Buffer[M, N, out_dtype]) -> None:
-            a_tile = group.load(a[0:tm, 0:tk], shape=(tm, tk))
-            b_tile = group.load(b[0:tk, 0:tn], shape=(tk, tn))
-            store(group, c, step_fn(group, a_tile, b_tile, 0))
+            row0, col0 = group.group_id[1] * tm, group.group_id[0] * tn
+            acc_values = start(group)
+            for k0 in range(0, a.shape[1], step):
+                a_tile = group.load(a[row0 : row0 + tm, k0 : k0 + tk], shape=(tm, tk))
+                b_tile = group.load(b[k0 : k0 + tk, col0 : col0 + tn], shape=(tk, tn))
+                acc_values = step_fn(group, a_tile, b_tile, acc_values)
+            store(group, c, row0, col0, acc_values)
+    elif windows == "wide":  # the k window is wider than the k step
+        @kernel(**launch)
+        def matmul(group, a: Buffer[M, K, in_dtype], b: Buffer[bd[0], bd[1], in_dtype],
+                   c: Buffer[M, N, out_dtype]) -> None:
+            row0, col0 = group.group_id[0] * tm, group.group_id[1] * tn
+            acc_values = start(group)
+            for k0 in range(0, a.shape[1], step):
+                a_tile = group.load(a[row0 : row0 + tm, k0 : k0 + 2 * tk], shape=(tm, tk))
+                b_tile = group.load(b[k0 : k0 + tk, col0 : col0 + tn], shape=(tk, tn))
+                acc_values = step_fn(group, a_tile, b_tile, acc_values)
+            store(group, c, row0, col0, acc_values)
+    elif store_at == "shifted":  # the tile is stored one row lower than it was computed for
+        @kernel(**launch)
+        def matmul(group, a: Buffer[M, K, in_dtype], b: Buffer[bd[0], bd[1], in_dtype],
+                   c: Buffer[M, N, out_dtype]) -> None:
+            row0, col0 = group.group_id[0] * tm, group.group_id[1] * tn
+            acc_values = start(group)
+            for k0 in range(0, a.shape[1], step):
+                a_tile = group.load(a[row0 : row0 + tm, k0 : k0 + tk], shape=(tm, tk))
+                b_tile = group.load(b[k0 : k0 + tk, col0 : col0 + tn], shape=(tk, tn))
+                acc_values = step_fn(group, a_tile, b_tile, acc_values)
+            store(group, c, row0 + 1, col0, acc_values)
+    elif store_at == "transposed":  # row and column origin exchanged in the store
+        @kernel(**launch)
+        def matmul(group, a: Buffer[M, K, in_dtype], b: Buffer[bd[0], bd[1], in_dtype],
+                   c: Buffer[M, N, out_dtype]) -> None:
+            row0, col0 = group.group_id[0] * tm, group.group_id[1] * tn
+            acc_values = start(group)
+            for k0 in range(0, a.shape[1], step):
+                a_tile = group.load(a[row0 : row0 + tm, k0 : k0 + tk], shape=(tm, tk))
+                b_tile = group.load(b[k0 : k0 + tk, col0 : col0 + tn], shape=(tk, tn))
+                acc_values = step_fn(group, a_tile, b_tile, acc_values)
+            store(group, c, col0, row0, acc_values)
+    else:
+        @kernel(**launch)
+        def matmul(group, a: Buffer[M, K, in_dtype], b: Buffer[bd[0], bd[1], in_dtype],
+                   c: Buffer[M, N, out_dtype]) -> None:
+            row0, col0 = group.group_id[0] * tm, group.group_id[1] * tn
+            acc_values = start(group)
+            for k0 in range(0, a.shape[1], step):
+                a_tile = group.load(a[row0 : row0 + tm, k0 : k0 + tk], shape=(tm, tk))
+                b_tile = group.load(b[k0 : k0 + tk, col0 : col0 + tn], shape=(tk, tn))
+                acc_values = step_fn(group, a_tile, b_tile, acc_values)
+            store(group, c, row0, col0, acc_values)
 
     return matmul
 
@@ -197,42 +326,99 @@ SIX = 6.0
                    vector_type((8,), np.float32), idx_type()),
     result_types=(vector_type((8,), np.float32),))
 def mma(group, a_tile, b_tile, a_frag, b_frag, acc_frag, *, lane, wave_size, arch):
-    return acc_frag
+    a_vals = a_tile.with_inactive(value=np.float16(0))
+    b_vals = b_tile.with_inactive(value=np.float16(0))
+    out = np.empty((8,), dtype=np.float32)
+    for slot in range(8):
+        total = np.float32(acc_frag[slot])
+        for kk in range(16):
+            total += np.float32(a_vals[lane // 16 + 2 * slot, kk]) * np.float32(b_vals[kk, lane % 16])
+        out[slot] = total
+    return group.vload(out, shape=(8,))
+
+@kernel.func(scope=WorkGroup)
+def zeros(group):
+    @group.workitems
+    def per_lane(wi):
+        return group.vzeros(shape=(8,), dtype=np.float32)
+    return per_lane()
 
 @kernel.func(scope=WorkGroup)
 def step_fn(group, a_tile, b_tile, acc):
-    return mma(group, a_tile, b_tile, None, None, acc, lane=0, wave_size=32, arch="x")
+    @group.workitems
+    def per_lane(wi):
+        lane = wi.local_id()[0]
+        return mma(group, a_tile, b_tile, a_tile[lane % 16, :].vec(), b_tile[:, lane % 16].vec(),
+                   acc[:, lane, 0], lane=lane, wave_size=32, arch="x")
+    return per_lane()
 
 @kernel.func(scope=WorkGroup)
-def from_c(group, c):
-    return group.load(c[0:16, 0:16], shape=(16, 16))
+def from_c(group, c, row0, col0):
+    c_tile = group.load(c[row0 : row0 + 16, col0 : col0 + 16], shape=(16, 16))
+    @group.workitems
+    def per_lane(wi):
+        lane = wi.local_id()[0]
+        return c_tile[lane // 16 :: 2, lane % 16].vec().with_inactive(value=np.float32(0))
+    return per_lane()
 
 @kernel.func(scope=WorkGroup)
-def plus_bias(group, bias, acc):
-    return acc
+def plus_bias(group, bias, col0, acc):
+    bias_tile = group.load(bias[col0 : col0 + 16], shape=(16,))
+    @group.workitems
+    def per_lane(wi):
+        lane = wi.local_id()[0]
+        return acc[:, lane, 0] + bias_tile[lane % 16 : lane % 16 + 1].vec().with_inactive(value=np.float32(0))
+    return per_lane()
 
 @kernel.func(scope=WorkGroup)
-def store(group, c, acc):
-    group.store(c, acc)
+def minus_bias(group, bias, col0, acc):
+    bias_tile = group.load(bias[col0 : col0 + 16], shape=(16,))
+    @group.workitems
+    def per_lane(wi):
+        lane = wi.local_id()[0]
+        return acc[:, lane, 0] - bias_tile[lane % 16 : lane % 16 + 1].vec().with_inactive(value=np.float32(0))
+    return per_lane()
+
+@kernel.func(scope=WorkGroup)
+def store(group, c, row0, col0, acc):
+    @group.workitems
+    def per_lane(wi):
+        lane = wi.local_id()[0]
+        col = col0 + lane % 16
+        group.store(c[row0 + lane // 16 : row0 + 16 : 2, col : col + 1], acc[:, lane, :])
+    per_lane()
+
+@kernel.func(scope=WorkGroup)
+def store_some(group, c, row0, col0, acc):
+    @group.workitems
+    def per_lane(wi):
+        lane = wi.local_id()[0]
+        col = col0 + lane % 16
+        if lane != 7:
+            group.store(c[row0 + lane // 16 : row0 + 16 : 2, col : col + 1], acc[:, lane, :])
+    per_lane()
 
 @kernel(work_shape=(ceil_div(M, 16) * 32, ceil_div(N, 16)), group_shape=(32, 1), subgroup_size=32)
 def matmul(group, a: Buffer[M, K, np.float16], b: Buffer[K, N, np.float16], c: Buffer[M, N, np.float32]{extra_param}) -> None:
+    row0 = group.group_id[0] * 16
+    col0 = 16 * group.group_id[1]
     acc = {init}
     for k0 in range(0, a.shape[1], 16):
-        a_tile = group.load(a[0:16, k0 : k0 + 16], shape=(16, 16))
-        b_tile = group.load(b[k0 : k0 + 16, 0:16], shape=(16, 16))
-        acc = step_fn(group, a_tile, b_tile, acc)
+        a_tile = group.load(a[row0 : row0 + 16, k0 : k0 + 16], shape=(16, 16))
+        b_tile = group.load(b[k0 : k0 + 16, col0 : col0 + 16], shape=(16, 16))
+        acc = step_fn(group, a_tile, b_tile, acc){in_loop}
 {after}
-    store(group, c, acc)
+    {store}(group, c, row0, col0, acc)
 {tail}
 """
 
 
-def _variant(tmp_path, name, *, init="0", after=(), extra_param="", tail=""):
+def _variant(tmp_path, name, *, init="zeros(group)", after=(), extra_param="", tail="", in_loop="", store="store"):
     import importlib.util
 
     text = _VARIANT_SOURCE.format(init=init, after="\n".join("    " + line for line in after),
-                                  extra_param=extra_param, tail="    " + tail if tail else "")
+                                  extra_param=extra_param, tail="    " + tail if tail else "", store=store,
+                                  in_loop=("\n        " + in_loop) if in_loop else "")
     path = tmp_path / f"{name}.py"
     path.write_text(text, encoding="utf-8")
     spec = importlib.util.spec_from_file_location(name, path)
@@ -244,7 +430,7 @@ def _variant(tmp_path, name, *, init="0", after=(), extra_param="", tail=""):
 def test_statements_around_the_k_loop(tmp_path) -> None:
     """What the recogniser reads before the k-loop (accumulators loaded from c) and between the
     loop and the store (element-wise statements in their spellings)."""
-    plan, why = recognise_tiled_matmul(_variant(tmp_path, "v_acc", init="from_c(group, c)"))
+    plan, why = recognise_tiled_matmul(_variant(tmp_path, "v_acc", init="from_c(group, c, row0, col0)"))
     assert plan is not None and plan.accumulate and plan.epilogue == (), why
     plan, why = recognise_tiled_matmul(_variant(
         tmp_path, "v_ops", after=["acc = 2 * acc", "acc = acc - np.float32(1.5)", "acc = acc.astype(np.float32)",
@@ -252,8 +438,8 @@ def test_statements_around_the_k_loop(tmp_path) -> None:
     assert plan is not None and not plan.accumulate, why
     assert plan.epilogue == (("scale", 2.0), ("add", -1.5), ("min", 6.0), ("max", -0.5))
     plan, why = recognise_tiled_matmul(_variant(
-        tmp_path, "v_bias", init="from_c(group, c)", extra_param=", bias: Buffer[N, np.float32]",
-        after=["acc = plus_bias(group, bias, acc)", "acc = acc * 0.1"]))
+        tmp_path, "v_bias", init="from_c(group, c, row0, col0)", extra_param=", bias: Buffer[N, np.float32]",
+        after=["acc = plus_bias(group, bias, col0, acc)", "acc = acc * 0.1"]))
     assert plan is not None and plan.accumulate and plan.bias_param == "bias", why
     assert plan.epilogue == (("bias",), ("scale", float(np.float32(0.1))))
 
@@ -269,10 +455,20 @@ def test_statements_around_the_k_loop(tmp_path) -> None:
     rejected("r_after", "after the store", tail="acc = acc * 2")
     rejected("r_unused", "must be added to `acc` exactly once", extra_param=", bias: Buffer[N, np.float32]")
     rejected("r_dtype", "must be Buffer[N, float32]", extra_param=", bias: Buffer[N, np.float16]",
-             after=["acc = plus_bias(group, bias, acc)"])
+             after=["acc = plus_bias(group, bias, col0, acc)"])
     rejected("r_extent", "must be Buffer[N, float32]", extra_param=", bias: Buffer[M, np.float32]",
-             after=["acc = plus_bias(group, bias, acc)"])
-    rejected("r_early", "may only be read before the k-loop to initialise", init="0\n    peek = from_c(group, c)")
+             after=["acc = plus_bias(group, bias, col0, acc)"])
+    rejected("r_early", "is neither a tile-origin assignment", init="zeros(group)\n    peek = from_c(group, c, row0, col0)")
+    # What the statements do, not only how they look:
+    rejected("r_literal", "the accumulators must be initialised once, by a call", init="0")
+    rejected("r_loop_extra", "in the k-loop is not one of", in_loop="acc = acc * 2")
+    rejected("r_loop_if", "in the k-loop is not one of", in_loop="if k0 > 16: acc = zeros(group)")
+    rejected("r_bias_sign", "that are not a @ b + bias", extra_param=", bias: Buffer[N, np.float32]",
+             after=["acc = minus_bias(group, bias, col0, acc)"])
+    rejected("r_bias_origin", "that are not a @ b + bias",
+             extra_param=", bias: Buffer[N, np.float32]", after=["acc = plus_bias(group, bias, row0, acc)"])
+    rejected("r_branchy_store", "helpers around the intrinsic must be straight-line code", store="store_some")
+    rejected("r_acc_origin", "or column origin", init="from_c(group, c, row0, col0 + 16)")
 
 
 def test_narrow_member_and_astype_placement(tmp_path) -> None:
@@ -288,7 +484,7 @@ def test_narrow_member_and_astype_placement(tmp_path) -> None:
     def variant(name, **kwargs):
         import importlib.util
 
-        text = source.format(init=kwargs.get("init", "0"), extra_param="", tail="",
+        text = source.format(init=kwargs.get("init", "zeros(group)"), extra_param="", tail="", store="store", in_loop="",
                              after="\n".join("    " + line for line in kwargs.get("after", ())))
         path = tmp_path / f"{name}.py"
         path.write_text(text, encoding="utf-8")
@@ -305,7 +501,7 @@ def test_narrow_member_and_astype_placement(tmp_path) -> None:
     assert plan is None and any("runs on the 16-bit values" in line for line in why), why
     plan, why = variant("n_other", after=["acc = acc.astype(np.float64)"])
     assert plan is None and any("is not an element-wise statement" in line for line in why), why
-    plan, why = variant("n_acc", init="from_c(group, c)")
+    plan, why = variant("n_acc", init="from_c(group, c, row0, col0)")
     assert plan is None and any("needs a float32 `c`" in line for line in why), why
 
 
@@ -335,6 +531,16 @@ def test_family_members_are_recognised() -> None:
         ({"loop": False}, "exactly one k-loop"),
         ({"work_shape": (ceil_div(M, 16) * 32, ceil_div(N, 32))}, "work_shape evaluates to"),
         ({"work_shape": (M, N, K)}, "work_shape must be a pair"),
+        # Kernels with the right shape that compute something else: the reference simulator would run
+        # them as written, so launching them as C = A.B would give different results.
+        ({"windows": "constant"}, "axis 0 of the `a` window must be the tile's rows .* \\(found `0:tm`\\)"),
+        ({"windows": "constant"}, "axis 1 of the `b` window must be the tile's columns"),
+        ({"windows": "swapped"}, "axis 0 of the `a` window must be the tile's rows .* o = group.group_id\\[0\\] \\* 16"),
+        ({"windows": "wide"}, "axis 1 of the `a` window must advance with the k-loop variable as `k0 : k0 \\+ 16`"),
+        ({"store_at": "shifted"}, "argument `row0 \\+ 1` of the store .* it is 16\\*group_id\\[0\\] \\+ 1"),
+        ({"store_at": "transposed"}, "writes outside its tile of `c`"),
+        ({"init": "ones"}, "does not start the accumulators at zero"),
+        ({"mma_body": "identity"}, "leaves values in its tile of `c` that are not a @ b"),
     ],
 )
 def test_other_kernels_are_refused_with_a_reason(kwargs: dict, message: str) -> None:

@@ -189,6 +189,38 @@ def test_accumulating_and_fused_fixtures() -> None:
     assert np.array_equal(c == 0, c_sim == 0)  # clipped in the same places
 
 
+def test_fused_fixture_with_infinities_and_nan(gpu_ctx) -> None:
+    """NaN and infinities go through the fused maximum / minimum as in NumPy (and so in the
+    reference simulator): NaN stays NaN, -inf is clipped, +inf stays. Host arrays through the
+    handle (dense kernel) and device buffers through the skinny and dense kernels."""
+    golden = load_golden.__globals__["GOLDEN"]
+    a, b, c_sim = load_golden("simfusednan_bf16_m33_n17_k40_seed14")
+    with np.load(golden / "simfusednan_bf16_m33_n17_k40_seed14.npz") as data:
+        bias = data["bias"]
+    ops = (("scale", 0.125), ("bias",), ("max", 0.0))
+
+    def check(c: np.ndarray) -> None:
+        assert np.array_equal(np.isnan(c), np.isnan(c_sim))
+        assert np.array_equal(np.isposinf(c), np.isposinf(c_sim)) and not np.isneginf(c).any()
+        finite = np.isfinite(c_sim)
+        np.testing.assert_allclose(c[finite], c_sim[finite], rtol=0, atol=2e-6)
+        assert np.array_equal(c[finite] == 0, c_sim[finite] == 0)
+
+    c = np.full((33, 17), np.float32(-7.0))
+    compiled_for("bfloat16", None, False, "fused")(a, b, c, bias)
+    check(c)
+    da, db, dbias = gpu_ctx.to_device(a), gpu_ctx.to_device(b), gpu_ctx.to_device(bias)
+    for variant in (cuda.VARIANT_SKINNY, cuda.VARIANT_DENSE):
+        dc = gpu_ctx.empty((33, 17), np.float32)
+        gpu_ctx.gemm(da, db, dc, variant=variant, epilogue=ops, bias=dbias)
+        check(dc.to_numpy())
+        gpu_ctx.gemm(da, db, dc, variant=variant, epilogue=(("min", 1.0),))
+        assert np.array_equal(np.isnan(dc.to_numpy()), np.isnan(c_sim))
+        dc.free()
+    for buf in (da, db, dbias):
+        buf.free()
+
+
 FUSED_SHAPES = [
     # dense on single CTAs / CTA pairs, aligned and odd pitches; skinny with and without split-k
     (128, 256, 64, 0), (300, 520, 136, 0), (513, 1001, 264, 3), (1024, 1024, 256, 0), (2050, 2051, 130, 1),

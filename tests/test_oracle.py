@@ -18,6 +18,7 @@ def test_fixtures_are_present() -> None:
     assert (GOLDEN / "simbt_f16_m17_n19_k18_seed9.npz").exists()
     assert (GOLDEN / "simacc_f16_m17_n19_k18_seed11.npz").exists()
     assert (GOLDEN / "simfused_bf16_m33_n17_k40_seed12.npz").exists()
+    assert (GOLDEN / "simfusednan_bf16_m33_n17_k40_seed14.npz").exists()
     assert (GOLDEN / "simnarrow_bf16_m33_n17_k40_seed13.npz").exists()
     assert (GOLDEN / "blocked_reference.npz").exists()
 
@@ -67,6 +68,24 @@ def test_accumulating_and_fused_kernel_fixtures() -> None:
     assert not np.array_equal(swapped, c_sim)
     for op, fn in ((("add", 1.5), lambda x: x + np.float32(1.5)), (("min", 0.25), lambda x: np.minimum(x, np.float32(0.25)))):
         assert np.array_equal(cpu_ref.matmul_fused(a, b, epilogue=(op,)), fn(cpu_ref.matmul_numpy(a, b)))
+
+
+def test_fused_kernel_fixture_with_infinities_and_nan() -> None:
+    """np.maximum keeps a NaN (inf * 0 or inf - inf inside the k-sum); -inf is clipped to 0, +inf
+    stays. The reference simulator's output on such inputs is reproduced bit for bit, NaN
+    positions included."""
+    a, b, c_sim = load_golden("simfusednan_bf16_m33_n17_k40_seed14")
+    with np.load(GOLDEN / "simfusednan_bf16_m33_n17_k40_seed14.npz") as data:
+        bias = data["bias"]
+    assert np.isnan(c_sim).any() and np.isposinf(c_sim).any() and not np.isneginf(c_sim).any()
+    assert np.isnan(c_sim[7]).all() and np.isnan(c_sim[3, 2]) and np.isnan(c_sim[11]).all()
+    assert (c_sim[20] == 0).any()  # -inf * positive b, clipped by the maximum
+    out = cpu_ref.matmul_fused(a, b, epilogue=(("scale", 0.125), ("bias",), ("max", 0.0)), bias=bias)
+    assert np.array_equal(np.isnan(out), np.isnan(c_sim))
+    finite = ~np.isnan(c_sim)
+    assert np.array_equal(out[finite].view(np.uint32), c_sim[finite].view(np.uint32))
+    low = cpu_ref.matmul_fused(a, b, epilogue=(("min", 1.0),))
+    assert np.array_equal(np.isnan(low), np.isnan(c_sim))
 
 
 def test_narrow_kernel_fixture() -> None:
