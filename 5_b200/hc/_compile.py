@@ -24,6 +24,7 @@ from typing import Any
 import numpy as np
 
 from ._launch import PreparedLaunch, prepare_launch
+from ._map_kernels import MapContract
 from ._pipeline import GemmContract, ScheduleSource, lower_for_target
 from .errors import LaunchError
 
@@ -47,7 +48,7 @@ class CompiledKernel:
     pipeline_diagnostics: tuple[str, ...] = field(default=())
     # Extensions of the NVIDIA path.
     target: str | None = field(default=None)
-    plan: GemmContract | None = field(default=None)
+    plan: GemmContract | MapContract | None = field(default=None)
     schedule: ScheduleSource = field(default=None)
     device: int | None = field(default=None)
 
@@ -64,7 +65,10 @@ class CompiledKernel:
         launch = prepare_launch(self.kernel, args, kwargs, dict(self.bindings))
         if launch.is_empty:
             return None
-        self._launch_gemm(launch)
+        if isinstance(self.plan, MapContract):
+            self._launch_map(launch)
+        else:
+            self._launch_gemm(launch)
         return None
 
     def prepare(self, *args: Any, **kwargs: Any) -> PreparedLaunch:
@@ -106,6 +110,49 @@ class CompiledKernel:
         staged = np.array(c, order="C") if plan.accumulate else np.empty(c.shape, c.dtype)
         ctx.gemm_host(a_host, b_host, staged, bias=bias_host, **options)
         c[...] = staged
+
+    def _launch_map(self, launch: PreparedLaunch) -> None:
+        """out[i] = ops(x[i] [, y[i]]) for a recognised element-wise kernel."""
+        from . import cuda
+
+        plan = self.plan
+        assert isinstance(plan, MapContract)
+        names = [plan.x_param] + ([plan.other_param] if plan.other_param else []) + [plan.out_param]
+        buffers = [launch.arguments[name] for name in names]
+        for name, buf in zip(names, buffers):
+            if buf.dtype != np.float32:
+                raise LaunchError(f"{name} dtype expected float32, got {buf.dtype.name}: target {self.target!r} runs "
+                                  f"element-wise kernels on float32 buffers")
+        x, out = buffers[0], buffers[-1]
+        other = buffers[1] if plan.other_param else None
+        on_device = [type(buf).__name__ == "DeviceBuffer" for buf in buffers]
+        if any(on_device) and not all(on_device):
+            raise LaunchError("buffers must be all numpy.ndarray or all DeviceBuffer")
+        if all(on_device):
+            ctx = x.ctx
+            if any(buf.ctx is not ctx for buf in buffers):
+                raise LaunchError("device buffers must belong to one context")
+            ctx.map(x, out, plan.ops, other=other)
+            ctx.synchronize()
+            return
+        if not out.flags.writeable:
+            raise LaunchError(f"{plan.out_param} must be writeable")
+        ctx = cuda.default_context(self.device)
+        # Inputs that are the output array itself (in place) stay that array; everything else that
+        # is not contiguous is staged through a contiguous copy.
+        direct = out.flags.c_contiguous
+        staged = out if direct else np.empty(out.shape, np.float32)
+
+        def host(arr: np.ndarray) -> np.ndarray:
+            if arr is out:
+                if not direct:
+                    staged[...] = out
+                return staged
+            return np.ascontiguousarray(arr)
+
+        ctx.map_host(host(x), staged, plan.ops, other=None if other is None else host(other))
+        if not direct:
+            out[...] = staged
 
     # -- text ---------------------------------------------------------------------------
     def _name(self) -> str:

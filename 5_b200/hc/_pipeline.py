@@ -5,8 +5,9 @@ frontend IR to the `hc` dialect and stops there (run_front_to_hc, hc/_pipeline.p
 no target can execute anything. Here the module keeps that role -- "turn a decorated kernel
 into something a handle can carry" -- for targets that need no MLIR. One target exists:
 
-    "nvidia-sm100a"   maps the tiled WMMA matmul kernel family onto the hand-written B200
-                      kernels behind include/hc-c/Cuda.h.
+    "nvidia-sm100a"   maps the tiled WMMA matmul kernel family (this module) and the masked
+                      element-wise map (hc._map_kernels) onto the hand-written B200 kernels
+                      behind include/hc-c/Cuda.h.
 
 The target does not translate Python to device code. It recognises the kernel: from the
 `@kernel` metadata (launch geometry), the `Buffer` annotations (operand roles, extents,
@@ -92,7 +93,7 @@ class GemmContract:
 @dataclass(frozen=True)
 class TargetResult:
     target: str
-    plan: GemmContract | None
+    plan: Any  # GemmContract, hc._map_kernels.MapContract, or None
     diagnostics: tuple[str, ...]
 
 
@@ -101,10 +102,26 @@ def known_targets() -> tuple[str, ...]:
 
 
 def lower_for_target(kernel_fn: Any, target: str) -> TargetResult:
+    """Tries the kernel classes the target runs: the tiled matmul family, then the masked
+    element-wise map (`hc._map_kernels`). The diagnostics of the class the kernel's signature
+    points at are reported when neither matches."""
     if target != NVIDIA_SM100A:
         raise ValueError(f"unknown hc.compile target {target!r}; known targets: {list(known_targets())}")
+    from ._map_kernels import recognise_elementwise_map
+
     plan, diagnostics = recognise_tiled_matmul(kernel_fn)
+    if plan is None:
+        map_plan, map_diagnostics = recognise_elementwise_map(kernel_fn)
+        if map_plan is not None:
+            return TargetResult(target, map_plan, ())
+        if _looks_one_dimensional(kernel_fn):
+            diagnostics = map_diagnostics
     return TargetResult(target, plan, tuple(diagnostics))
+
+
+def _looks_one_dimensional(kernel_fn: Any) -> bool:
+    work = getattr(getattr(kernel_fn, "__hc_kernel__", None), "work_shape", None)
+    return not isinstance(work, tuple) or len(work) == 1
 
 
 # ------------------------------------------------------------------ helpers -------------

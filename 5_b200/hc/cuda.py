@@ -38,7 +38,7 @@ __all__ = [
 F16, BF16 = 0, 1
 VARIANT_AUTO, VARIANT_DENSE, VARIANT_SKINNY, VARIANT_NOOP, VARIANT_ZERO_FILL, VARIANT_ELEMENTWISE = 0, 1, 2, 3, 4, 5
 VARIANT_NAMES = {0: "auto", 1: "dense", 2: "skinny", 3: "noop", 4: "zero_fill", 5: "elementwise"}
-API_VERSION = 4
+API_VERSION = 5
 # Element-wise operations fused into the store of C: ("scale", x), ("add", x), ("max", x),
 # ("min", x) and ("bias",) -- the last adds bias[column].
 EPILOGUE_KINDS = {"scale": 1, "add": 2, "max": 3, "min": 4, "bias": 5}
@@ -55,7 +55,7 @@ EXPORTS = (
     "hcCudaMemset", "hcCudaGemmPlan", "hcCudaGemm", "hcCudaGemmHost", "hcCudaEventCreate",
     "hcCudaEventDestroy", "hcCudaEventRecord", "hcCudaEventElapsedMs", "hcCudaCommGetUniqueId",
     "hcCudaCommInitRank", "hcCudaCommAllGather", "hcCudaCommDestroy", "hcCudaGemmSkinnyStatic", "hcCudaSelfTestDeviceTimeout", "hcCudaGemmPush", "hcCudaIpcExport",
-    "hcCudaIpcOpen", "hcCudaIpcClose",
+    "hcCudaIpcOpen", "hcCudaIpcClose", "hcCudaMap", "hcCudaMapHost",
 )
 
 
@@ -71,6 +71,33 @@ class _GemmArgs(ctypes.Structure):
         ("epilogue_value", ctypes.c_float * 4), ("c_dtype", ctypes.c_int32),
         ("bias", ctypes.c_void_p),
     ]
+
+
+# Operations of the element-wise map (HcCudaMapOp): with a float32 constant, or with the element of
+# the second input ("..._other").
+MAP_KINDS = {"scale": 1, "add": 2, "max": 3, "min": 4, "rsub": 5, "add_other": 6, "sub_other": 7,
+             "rsub_other": 8, "mul_other": 9, "max_other": 10, "min_other": 11}
+MAX_MAP_OPS = 8
+
+
+class _MapArgs(ctypes.Structure):
+    _fields_ = [
+        ("n", ctypes.c_int64), ("x", ctypes.c_void_p), ("y", ctypes.c_void_p), ("out", ctypes.c_void_p),
+        ("op_count", ctypes.c_int32), ("op_kind", ctypes.c_int32 * 8), ("op_value", ctypes.c_float * 8),
+    ]
+
+
+def _map_args(n: int, x: int | None, y: int | None, out: int | None, ops: Sequence[tuple]) -> _MapArgs:
+    ops = tuple(ops)
+    if len(ops) > MAX_MAP_OPS:
+        raise ValueError(f"at most {MAX_MAP_OPS} element-wise operations are supported")
+    args = _MapArgs(n=n, x=x, y=y, out=out, op_count=len(ops))
+    for i, op in enumerate(ops):
+        if op[0] not in MAP_KINDS:
+            raise ValueError(f"unknown element-wise operation {op[0]!r}; known: {sorted(MAP_KINDS)}")
+        args.op_kind[i] = MAP_KINDS[op[0]]
+        args.op_value[i] = float(op[1]) if len(op) > 1 else 0.0
+    return args
 
 
 class _PlanInfo(ctypes.Structure):
@@ -155,6 +182,8 @@ def library() -> ctypes.CDLL:
         lib.hcCudaIpcOpen.argtypes = [vp, vp, sz, pvp]
         lib.hcCudaIpcClose.argtypes = [vp, vp]
         lib.hcCudaGemmSkinnyStatic.argtypes = [ctypes.POINTER(_GemmArgs), vp, i, ctypes.c_char_p, sz]
+        lib.hcCudaMap.argtypes = [vp, ctypes.POINTER(_MapArgs)]
+        lib.hcCudaMapHost.argtypes = [vp, ctypes.POINTER(_MapArgs)]
         for name in EXPORTS:
             getattr(lib, name)  # AttributeError here means a stale or foreign library
         _LIB = lib
@@ -389,6 +418,27 @@ class Context:
     def ipc_close(self, ptr: int) -> None:
         if ptr:
             self._check(self._lib.hcCudaIpcClose(self._handle, ptr))
+
+    def map(self, x: "DeviceBuffer", out: "DeviceBuffer", ops: Sequence[tuple], *,
+            other: "DeviceBuffer | None" = None) -> None:
+        """Enqueues out[i] = ops(x[i] [, other[i]]) on one-dimensional float32 device buffers
+        (asynchronous). `ops` in order, e.g. `(("scale", 2.0), ("add_other",), ("max", 0.0))`."""
+        for buf in (x, out) + (() if other is None else (other,)):
+            if buf.dtype != np.float32 or buf.ndim != 1 or buf.shape != x.shape:
+                raise ValueError("map() takes one-dimensional float32 buffers of one length")
+        args = _map_args(x.shape[0], x.ptr, None if other is None else other.ptr, out.ptr, ops)
+        self._check(self._lib.hcCudaMap(self._handle, ctypes.byref(args)))
+
+    def map_host(self, x: np.ndarray, out: np.ndarray, ops: Sequence[tuple], *,
+                 other: np.ndarray | None = None) -> None:
+        """The same on contiguous one-dimensional float32 host arrays: copies in, runs, copies `out`
+        back in place; returns when `out` is complete."""
+        for arr in (x, out) + (() if other is None else (other,)):
+            if arr.dtype != np.float32 or arr.ndim != 1 or arr.shape != x.shape or not arr.flags.c_contiguous:
+                raise ValueError("map_host() takes contiguous one-dimensional float32 arrays of one length")
+        args = _map_args(x.shape[0], x.ctypes.data, None if other is None else other.ctypes.data,
+                         out.ctypes.data, ops)
+        self._check(self._lib.hcCudaMapHost(self._handle, ctypes.byref(args)))
 
     def gemm_host(self, a: np.ndarray, b: np.ndarray, c: np.ndarray, *,
                   variant: int = VARIANT_AUTO, b_transposed: bool = False, accumulate: bool = False,

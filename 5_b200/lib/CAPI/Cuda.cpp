@@ -18,6 +18,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <initializer_list>
 #include <mutex>
 #include <new>
 #include <string>
@@ -1056,6 +1057,20 @@ int hcCudaGemmHost(HcCudaContext *ctx, const HcCudaGemmArgs *args) {
   HC_TRY_CUDA(ctx, cudaEventRecord(ctx->fence_event, ctx->stream));
   HC_TRY_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_in, ctx->fence_event, 0));
   HC_TRY_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_out, ctx->fence_event, 0));
+  // Whatever way this call ends, no copy may still be running into the caller's arrays or the
+  // staging buffers when it returns: an error return in the middle of the panel loop waits for
+  // all three streams first (the success path waits in finish()).
+  struct DrainOnExit {
+    HcCudaContext *ctx;
+    bool armed = true;
+    ~DrainOnExit() {
+      if (!armed)
+        return;
+      for (cudaStream_t s : {ctx->copy_in, ctx->copy_out, ctx->stream})
+        if (cudaStreamSynchronize(s) != cudaSuccess)
+          cudaGetLastError();
+    }
+  } drain_guard{ctx};
   struct PanelsPlanning {  // the sub-products below are planned without k-splits
     HcCudaContext *ctx;
     explicit PanelsPlanning(HcCudaContext *c) : ctx(c) { ctx->planning_host_panels = true; }
@@ -1089,7 +1104,9 @@ int hcCudaGemmHost(HcCudaContext *ctx, const HcCudaGemmArgs *args) {
   auto finish = [&]() -> int {
     HC_TRY_CUDA(ctx, cudaEventRecord(ctx->fence_event, ctx->copy_out));
     HC_TRY_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->fence_event, 0));
-    return synchronize_locked(ctx);
+    const int rc = synchronize_locked(ctx);  // waits for the main stream, which waits for copy_out
+    drain_guard.armed = rc != HC_CUDA_OK && rc != HC_CUDA_ERR_DEVICE_TIMEOUT;
+    return rc;
   };
   // Panels are multiples of 256 rows (or columns); a remainder shorter than that joins the last one.
   auto panel_size = [](size_t total) {
@@ -1189,6 +1206,136 @@ int hcCudaGemmHost(HcCudaContext *ctx, const HcCudaGemmArgs *args) {
     }
   }
   return finish();
+}
+
+namespace {
+
+// Validation shared by hcCudaMap and hcCudaMapHost; fills `ops`.
+int check_map_args(const HcCudaContext *ctx, const HcCudaMapArgs *args, hc::sm100::MapOps *ops) {
+  if (args == nullptr)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "args must not be null");
+  if (args->n < 0)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "n must be non-negative (got %lld)", (long long)args->n);
+  if (args->n > (int64_t(1) << 40))
+    return fail(ctx, HC_CUDA_ERR_UNSUPPORTED, "n must be at most 2^40");
+  if (args->op_count < 0 || args->op_count > HC_CUDA_MAX_MAP_OPS)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "op_count must be 0..%d (got %d)", HC_CUDA_MAX_MAP_OPS,
+                args->op_count);
+  bool uses_other = false;
+  ops->count = args->op_count;
+  for (int i = 0; i < args->op_count; ++i) {
+    const int kind = args->op_kind[i];
+    if (kind < HC_CUDA_MAP_SCALE || kind > HC_CUDA_MAP_MIN_OTHER)
+      return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "op_kind[%d] is not an HcCudaMapOp (got %d)", i, kind);
+    uses_other = uses_other || kind >= HC_CUDA_MAP_ADD_OTHER;
+    ops->kind[i] = kind;
+    ops->value[i] = args->op_value[i];
+  }
+  if (args->n == 0)
+    return HC_CUDA_OK;
+  if (args->x == nullptr || args->out == nullptr || (uses_other && args->y == nullptr))
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "x and out (and y, when an ..._OTHER operation is used) must "
+                                                   "not be null");
+  const size_t bytes = static_cast<size_t>(args->n) * 4;
+  const void *inputs[2] = {args->x, uses_other ? args->y : nullptr};
+  for (const void *in : inputs) {
+    if (in == nullptr)
+      continue;
+    if ((reinterpret_cast<uintptr_t>(in) & 3) != 0 || (reinterpret_cast<uintptr_t>(args->out) & 3) != 0)
+      return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "x, y and out must be 4-byte aligned");
+    if (in != args->out && ranges_overlap(in, bytes, args->out, bytes))
+      return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "out may be the same buffer as an input, but must not "
+                                                     "partially overlap one");
+  }
+  return HC_CUDA_OK;
+}
+
+} // namespace
+
+int hcCudaMap(HcCudaContext *ctx, const HcCudaMapArgs *args) {
+  if (ctx == nullptr)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "ctx must not be null");
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  hc::sm100::MapOps ops{};
+  if (int rc = check_map_args(ctx, args, &ops))
+    return rc;
+  if (args->n == 0)
+    return HC_CUDA_OK;
+  HC_TRY_CUDA(ctx, cudaSetDevice(ctx->device));
+  HC_TRY_CUDA(ctx, hc::sm100::launch_map_f32(args->x, args->y, args->out, args->n, ops,
+                                             ctx->prop.multiProcessorCount, ctx->stream));
+  return HC_CUDA_OK;
+}
+
+int hcCudaMapHost(HcCudaContext *ctx, const HcCudaMapArgs *args) {
+  if (ctx == nullptr)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "ctx must not be null");
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  hc::sm100::MapOps ops{};
+  if (int rc = check_map_args(ctx, args, &ops))
+    return rc;
+  if (args->n == 0)
+    return HC_CUDA_OK;
+  HC_TRY_CUDA(ctx, cudaSetDevice(ctx->device));
+  bool two = false;
+  for (int i = 0; i < ops.count; ++i)
+    two = two || ops.kind[i] >= HC_CUDA_MAP_ADD_OTHER;
+  const size_t n = static_cast<size_t>(args->n);
+  // Chunks of 4 Mi elements (16 MiB per array): a ring of kMaxSteps device chunks per array, so
+  // that chunk i + 1 arrives and chunk i - 1 leaves while chunk i is computed.
+  constexpr size_t kChunk = size_t(4) << 20;
+  constexpr int kRing = HcCudaContext::kMaxSteps;
+  const size_t chunks = (n + kChunk - 1) / kChunk;
+  const size_t ring = chunks < static_cast<size_t>(kRing) ? chunks : static_cast<size_t>(kRing);
+  const size_t slot = (n < kChunk ? n : kChunk) * 4;
+  if (int rc = ensure_stage(ctx, 0, ring * slot))
+    return rc;
+  if (two)
+    if (int rc = ensure_stage(ctx, 1, ring * slot))
+      return rc;
+  if (int rc = ensure_stage(ctx, 2, ring * slot))
+    return rc;
+  if (int rc = ensure_copy_streams(ctx))
+    return rc;
+  HC_TRY_CUDA(ctx, cudaEventRecord(ctx->fence_event, ctx->stream));
+  HC_TRY_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_in, ctx->fence_event, 0));
+  HC_TRY_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_out, ctx->fence_event, 0));
+  struct Drain {  // no copy may still touch the caller's arrays when the call returns
+    HcCudaContext *ctx;
+    ~Drain() {
+      for (cudaStream_t s : {ctx->copy_in, ctx->copy_out, ctx->stream})
+        if (cudaStreamSynchronize(s) != cudaSuccess)
+          cudaGetLastError();
+    }
+  } drain{ctx};
+  for (size_t chunk = 0; chunk < chunks; ++chunk) {
+    const size_t begin = chunk * kChunk;
+    const size_t count = n - begin < kChunk ? n - begin : kChunk;
+    const int s = static_cast<int>(chunk % ring);
+    float *dx = reinterpret_cast<float *>(static_cast<char *>(ctx->stage[0]) + s * slot);
+    float *dy = two ? reinterpret_cast<float *>(static_cast<char *>(ctx->stage[1]) + s * slot) : nullptr;
+    float *dout = reinterpret_cast<float *>(static_cast<char *>(ctx->stage[2]) + s * slot);
+    // Ring slot s is free for new input once the kernel of its previous user has run, and its
+    // output slot once that chunk's copy out has finished.
+    if (chunk >= ring) {
+      HC_TRY_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_in, ctx->panel_done[s], 0));
+      HC_TRY_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->panel_in[s], 0));  // re-recorded below, after use
+    }
+    HC_TRY_CUDA(ctx, cudaMemcpyAsync(dx, args->x + begin, count * 4, cudaMemcpyHostToDevice, ctx->copy_in));
+    if (two)
+      HC_TRY_CUDA(ctx, cudaMemcpyAsync(dy, args->y + begin, count * 4, cudaMemcpyHostToDevice, ctx->copy_in));
+    HC_TRY_CUDA(ctx, cudaEventRecord(ctx->fence_event, ctx->copy_in));
+    HC_TRY_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->fence_event, 0));
+    HC_TRY_CUDA(ctx, hc::sm100::launch_map_f32(dx, dy, dout, static_cast<long long>(count), ops,
+                                               ctx->prop.multiProcessorCount, ctx->stream));
+    HC_TRY_CUDA(ctx, cudaEventRecord(ctx->panel_done[s], ctx->stream));
+    HC_TRY_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_out, ctx->panel_done[s], 0));
+    HC_TRY_CUDA(ctx, cudaMemcpyAsync(args->out + begin, dout, count * 4, cudaMemcpyDeviceToHost, ctx->copy_out));
+    HC_TRY_CUDA(ctx, cudaEventRecord(ctx->panel_in[s], ctx->copy_out));  // "output slot s has left"
+  }
+  HC_TRY_CUDA(ctx, cudaEventRecord(ctx->fence_event, ctx->copy_out));
+  HC_TRY_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->fence_event, 0));
+  return synchronize_locked(ctx);
 }
 
 int hcCudaSelfTestDeviceTimeout(HcCudaContext *ctx, int64_t budget_cycles) {

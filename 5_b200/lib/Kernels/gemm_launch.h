@@ -165,5 +165,32 @@ cudaError_t launch_repack_pitch_two(const void *src0, long long src0_ld, void *d
                                     int rows0, int cols0, const void *src1, long long src1_ld, void *dst1,
                                     long long dst1_ld, int rows1, int cols1, cudaStream_t stream);
 
+// ---- the masked element-wise map (one-dimensional load / compute / store kernels) --------------
+// out[i] = ops(x[i] [, y[i]]) for i in [0, n), float32: at most kMaxMapOps operations applied in
+// order, each with a float32 constant or with the element of the second input.
+constexpr int kMaxMapOps = 8;
+constexpr int kMapScale = 1;            // v = v * value
+constexpr int kMapAdd = 2;              // v = v + value
+constexpr int kMapMax = 3;              // v = maximum(v, value)   (NaN propagates, as in NumPy)
+constexpr int kMapMin = 4;              // v = minimum(v, value)
+constexpr int kMapReverseSub = 5;       // v = value - v
+constexpr int kMapAddOther = 6;         // v = v + y[i]
+constexpr int kMapSubOther = 7;         // v = v - y[i]
+constexpr int kMapReverseSubOther = 8;  // v = y[i] - v
+constexpr int kMapMulOther = 9;         // v = v * y[i]
+constexpr int kMapMaxOther = 10;        // v = maximum(v, y[i])
+constexpr int kMapMinOther = 11;        // v = minimum(v, y[i])
+struct MapOps {
+  int count;
+  int kind[kMaxMapOps];
+  float value[kMaxMapOps];
+};
+// CTAs of the map kernel for n elements on `sm_count` SMs (a persistent grid, eight CTAs per SM).
+int map_grid(long long n, int sm_count);
+// y may be null when no operation uses the second input. x, y, out: 4-byte aligned; 16-byte
+// alignment of all of them selects the 128-bit path.
+cudaError_t launch_map_f32(const float *x, const float *y, float *out, long long n, const MapOps &ops,
+                           int sm_count, cudaStream_t stream);
+
 } // namespace sm100
 } // namespace hc

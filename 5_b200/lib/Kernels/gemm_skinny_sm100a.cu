@@ -22,6 +22,9 @@
 #include "gemm_launch.h"
 #include "sm100_ptx.cuh"
 
+#include <cstdlib>
+#include <cstring>
+
 namespace hc {
 namespace sm100 {
 
@@ -405,7 +408,13 @@ int skinny_choose_splits(int n, int k, int sm_count) {
 int skinny_ring_stages(int m, int grid, int sm_count) {
   // A grid with no more CTAs than SMs leaves every CTA alone on its SM, so each may take all of
   // the shared memory (twice the bytes in flight); a larger grid shares an SM between two.
-  const bool alone = grid <= sm_count;
+  bool alone = grid <= sm_count;
+  if (const char *forced = std::getenv("HC_CUDA_SKINNY_RING")) {  // tuning aid: "shallow" or "deep"
+    if (std::strcmp(forced, "shallow") == 0)
+      alone = false;
+    else if (std::strcmp(forced, "deep") == 0 && grid <= sm_count)
+      alone = true;
+  }
   const int mp = skinny::padded_m(m);
   if (mp == 16)
     return alone ? skinny::Config<16>::kStagesAlone : skinny::Config<16>::kStagesShared;

@@ -48,12 +48,13 @@ NOMINAL_PEAK_TFLOPS = 2250.0  # dense fp16/bf16, for context
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
-# DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum),
-# from the ncu captures summarised under profiles/. None = not captured for that workload.
-NCU_DRAM_TRAFFIC_BYTES = {
-    "gemm_8192": 1.317e9,  # profiles/gemm_dense_pair_kernel__gemm_8192.md
-    "skinny": 272.4e6,     # profiles/gemm_skinny_kernel__skinny_8x16384x8192.md
-    "ragged": 21.1e6,      # profiles/ragged_4095x3073x1031__launches.md (GEMM kernel only)
+# DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum) as
+# (bytes, where the figure comes from): ncu captures summarised under profiles/, NOT measured by
+# the run that prints them. Workloads without a capture carry no figure.
+NCU_DRAM_TRAFFIC = {
+    "gemm_8192": (1.317e9, "ncu capture, profiles/gemm_dense_pair_kernel__gemm_8192.md"),
+    "skinny": (272.4e6, "ncu capture, profiles/gemm_skinny_kernel__skinny_8x16384x8192.md"),
+    "ragged": (21.1e6, "ncu capture, profiles/ragged_4095x3073x1031__launches.md (GEMM kernel only)"),
 }
 
 
@@ -85,7 +86,7 @@ class ClockSampler:
         0x0000000000000080: "hw_power_brake_slowdown",
     }
 
-    def __init__(self, device_index: int, period_s: float = 0.01) -> None:
+    def __init__(self, device_index: int, period_s: float = 0.002) -> None:
         self.device_index = device_index
         self.period_s = period_s
         self.samples: list[tuple[float, int, int]] = []  # (time, sm_mhz, reasons bitmask)
@@ -231,6 +232,45 @@ def time_cpu_oracle(a: np.ndarray, b: np.ndarray, target_seconds: float = 12.0) 
     }
 
 
+_SIMULATOR_SCRIPT = r"""
+import importlib, json, os, sys, time
+import numpy as np
+sys.path.insert(0, sys.argv[2]); sys.path.insert(0, sys.argv[1])
+ex = importlib.import_module("examples.amdgpu_gfx11_wmma_matmul")
+rng = np.random.default_rng(0)
+a = rng.standard_normal((64, 64)).astype(np.float16)
+b = rng.standard_normal((64, 64)).astype(np.float16)
+start = time.perf_counter()
+c = ex.simulate_gfx11_wmma_matmul(a, b)
+print(json.dumps({"seconds": time.perf_counter() - start, "checksum": float(np.abs(c).sum())}))
+"""
+
+
+def time_reference_simulator() -> dict:
+    """The reference's own executor, `hc.simulator`, on benchmark configuration 1 (64^3, float16,
+    seed 0): the unmodified Python package from the checkout that $HC_REFERENCE_DIR names, with
+    oracle/standins/ in place of its two absent third-party dependencies (neither carries
+    arithmetic). One core: the simulator is a Python interpreter loop. Without a checkout the
+    record says so; the C restatement above is then the only CPU figure."""
+    reference = os.environ.get("HC_REFERENCE_DIR", "")
+    if not reference or not (Path(reference) / "hc" / "simulator.py").exists():
+        return {"unavailable": "unavailable on this box: no reference checkout ($HC_REFERENCE_DIR is not set "
+                               "or has no hc/simulator.py)"}
+    env = dict(os.environ)
+    env["HC_IXSIMPL_VENDOR_DIR"] = str(REPO / "oracle" / "standins" / "ixsimpl_vendor")
+    try:
+        result = subprocess.run([sys.executable, "-c", _SIMULATOR_SCRIPT, reference, str(REPO / "oracle" / "standins")],
+                                capture_output=True, text=True, timeout=300, env=env)
+        if result.returncode != 0:
+            return {"unavailable": f"the reference simulator did not run: {result.stderr.strip()[-200:]}"}
+        out = json.loads(result.stdout.strip().splitlines()[-1])
+    except Exception as exc:
+        return {"unavailable": f"the reference simulator did not run: {type(exc).__name__}: {exc}"}
+    flops = workloads.flops(64, 64, 64)
+    return {"seconds": out["seconds"], "value": flops / out["seconds"] / 1e12, "unit": UNIT, "cores": 1,
+            "kind": "reference", "sample": "hc.simulator on the whole of configuration 1 (64x64x64, float16, seed 0)"}
+
+
 def time_numpy_matmul(a: np.ndarray, b: np.ndarray, budget_rows: int = 8192) -> dict:
     """NumPy/BLAS float32 matmul of the same shape (inputs widened first), for context."""
     rows = min(a.shape[0], budget_rows)
@@ -314,13 +354,14 @@ def run_reference_arm(args, ranks: Ranks) -> None:
     value = sum(float(r["value"]) * r["seconds"] for r in timed) / seconds
     baseline = dict(timed[-1])
     baseline["value"] = value
+    baseline["simulator"] = time_reference_simulator()
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": ranks.world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": seconds / len(timed) * 1e3,
         "higher_is_better": True, "scaling": "strong" if ranks.world > 1 else "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": name, "m": w.m, "n": w.n, "k": w.k, "input_dtype": w.dtype,
-                   "note": "CPU restatement of the reference simulator's arithmetic on host cores; "
+        "config": {"workload": name, "m": w.m, "n": w.n, "k": w.k, "input_dtype": w.dtype},
+        "detail": {"note": "CPU restatement of the reference simulator's arithmetic on host cores; "
                            "each step is the bounded sample named in cpu_baseline.sample"},
         "cpu_baseline": baseline,
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -329,103 +370,291 @@ def run_reference_arm(args, ranks: Ranks) -> None:
     print(json.dumps(line), flush=True)
 
 
-def run_gpu_arm(args, ranks: Ranks) -> None:
-    from examples.b200_wmma_matmul import compiled_for
-    from hc import cuda
-    from hc.distributed import column_slab, init_communicator
+L2_BYTES = 126e6
 
-    name = choose_workload(args, ranks.world)
-    w = workloads.CONFIGS[name]
-    ctx = cuda.Context(ranks.local_rank)
-    # ---- inputs -------------------------------------------------------------------------
-    if name == "sharded":
-        slab = column_slab(w.n, ranks.world, ranks.rank, align=workloads.SHARDED_BLOCK_COLUMNS)
-        a, b = workloads.make_sharded_inputs(slab.begin, slab.end)
-        local_n = slab.width
-    else:
-        if ranks.world > 1:
-            raise SystemExit(f"workload {name} does not shard; run it with --gpus 1")
-        a, b = workloads.make_inputs(name)
-        local_n = w.n
-    m, k = w.m, w.k
-    bt = np.ascontiguousarray(b.T) if args.b_transposed else None
-    da, db = ctx.to_device(a), ctx.to_device(bt if args.b_transposed else b)
-    handle = compiled_for(w.dtype, ranks.local_rank, args.b_transposed, args.member)
-    if handle.plan is None:
-        raise SystemExit(f"kernel not recognised: {handle.pipeline_diagnostics}")
-    contract = handle.plan
-    bias = dbias = None
-    if contract.bias_param is not None:
-        bias = np.random.default_rng(99).standard_normal(local_n).astype(np.float32)
-        dbias = ctx.to_device(bias)
-    gemm_kwargs = {"b_transposed": args.b_transposed, "accumulate": contract.accumulate,
-                   "epilogue": contract.epilogue, "bias": dbias}
-    member_check = {"epilogue": contract.epilogue, "bias": bias}
-    c_type = a.dtype if contract.output_dtype != "float32" else np.dtype(np.float32)
-    dc = ctx.empty((m, local_n), c_type)
-    dc.fill_bytes(0)
-    plan = ctx.plan(m, local_n, k, w.dtype, b_transposed=args.b_transposed, accumulate=contract.accumulate,
-                    epilogue=contract.epilogue, c_dtype=contract.output_dtype)
-    local_flops = workloads.flops(m, local_n, k)
-    total_flops = workloads.flops(w.m, w.n, w.k)
 
-    # ---- warm-up, then the timed region (device time, max over ranks) ----------------------
-    bound = ctx.bind_gemm(da, db, dc, **gemm_kwargs)  # arguments marshalled once; launch() is one C call
-    for _ in range(max(args.warmup, 3)):
-        bound.launch()
-    ctx.synchronize()
-    sampler = ClockSampler(ranks.local_rank)
-    sampler.start()
+def timed_region(ctx, ranks: Ranks, sampler: ClockSampler, launch, steps: int) -> tuple[float, dict]:
+    """`steps` launches between two CUDA events on the context's stream, bracketed by a barrier and
+    a device synchronise on both sides. Returns (device milliseconds, max over ranks; clocks sampled
+    between the two host time stamps)."""
     start_ev, stop_ev = ctx.event(), ctx.event()
     ranks.barrier()
     ctx.synchronize()
     ranks.device_sync()
     t_begin = time.perf_counter()
     start_ev.record()
-    for _ in range(args.steps):
-        bound.launch()
+    for i in range(steps):
+        launch(i)
     stop_ev.record()
     elapsed_ms = stop_ev.elapsed_ms_since(start_ev)
     ctx.synchronize()
     ranks.device_sync()
     t_end = time.perf_counter()
     ranks.barrier()
-    clocks = sampler.summary(t_begin, t_end)
-    if clocks["samples"] < 3 and not args.quick:
-        # The timed region was shorter than the sampling period: keep the same launches
-        # running for half a second more and sample the clocks over that continuation.
-        c_begin = time.perf_counter()
-        while time.perf_counter() - c_begin < 0.5:
-            for _ in range(8):
-                bound.launch()
+    return ranks.max(elapsed_ms), sampler.summary(t_begin, t_end)
+
+
+class DeviceRun:
+    """One workload resident in HBM on this rank: buffers, the compiled handle's plan, the timed
+    launches, parity of what was timed, and the roofline of its dominant kernel."""
+
+    def __init__(self, ctx, ranks: Ranks, name: str, *, b_transposed: bool = False, member: str = "plain",
+                 rotate: bool = False) -> None:
+        from examples.b200_wmma_matmul import compiled_for
+        from hc.distributed import column_slab
+
+        self.ctx, self.ranks, self.name = ctx, ranks, name
+        w = self.w = workloads.CONFIGS[name]
+        if name == "sharded":
+            slab = column_slab(w.n, ranks.world, ranks.rank, align=workloads.SHARDED_BLOCK_COLUMNS)
+            self.a, self.b = workloads.make_sharded_inputs(slab.begin, slab.end)
+            self.local_n = slab.width
+        else:
+            self.a, self.b = workloads.make_inputs(name)
+            self.local_n = w.n
+        self.m, self.k = w.m, w.k
+        self.b_transposed = b_transposed
+        self.host_b = np.ascontiguousarray(self.b.T) if b_transposed else self.b
+        self.handle = compiled_for(w.dtype, ranks.local_rank, b_transposed, member)
+        if self.handle.plan is None:
+            raise SystemExit(f"kernel not recognised: {self.handle.pipeline_diagnostics}")
+        contract = self.contract = self.handle.plan
+        self.bias = self.dbias = None
+        if contract.bias_param is not None:
+            self.bias = np.random.default_rng(99).standard_normal(self.local_n).astype(np.float32)
+            self.dbias = ctx.to_device(self.bias)
+        self.gemm_kwargs = {"b_transposed": b_transposed, "accumulate": contract.accumulate,
+                            "epilogue": contract.epilogue, "bias": self.dbias}
+        self.c_type = self.a.dtype if contract.output_dtype != "float32" else np.dtype(np.float32)
+        # A working set smaller than L2 would be served from L2 on every launch after the first:
+        # such a workload is run on several copies of its buffers in turn, enough of them that a
+        # copy has left L2 by the time it is used again.
+        c_bytes = self.m * self.local_n * self.c_type.itemsize
+        self.working_set = self.a.nbytes + self.host_b.nbytes + c_bytes
+        copies = 1
+        if rotate and self.working_set < 1.5 * L2_BYTES and self.working_set >= 4e6:
+            copies = min(8, int(np.ceil(1.5 * L2_BYTES / self.working_set)))
+        self.sets = []
+        for _ in range(copies):
+            dc = ctx.empty((self.m, self.local_n), self.c_type)
+            dc.fill_bytes(0)
+            self.sets.append((ctx.to_device(self.a), ctx.to_device(self.host_b), dc))
+        self.da, self.db, self.dc = self.sets[0]
+        self.bound = [ctx.bind_gemm(da, db, dc, **self.gemm_kwargs) for da, db, dc in self.sets]
+        self.plan = ctx.plan(self.m, self.local_n, self.k, w.dtype, b_transposed=b_transposed,
+                             accumulate=contract.accumulate, epilogue=contract.epilogue,
+                             c_dtype=contract.output_dtype)
+        self.local_flops = workloads.flops(self.m, self.local_n, self.k)
+        self.total_flops = workloads.flops(w.m, w.n, w.k)
+        if self.working_set > L2_BYTES:
+            self.l2 = "inputs larger than L2 (A+B+C per GPU exceed 126 MB)"
+        elif copies > 1:
+            self.l2 = (f"{copies} copies of A, B, C used in turn ({copies * self.working_set / 1e6:.0f} MB in all, "
+                       f"larger than L2)")
+        else:
+            self.l2 = "working set fits L2: a launch-latency figure, not a bandwidth or tensor one"
+
+    def launch(self, i: int) -> None:
+        self.bound[i % len(self.bound)].launch()
+
+    def time(self, sampler: ClockSampler, steps: int, warmup: int, sustained_seconds: float = 0.0) -> None:
+        for i in range(max(warmup, 3) * len(self.bound)):
+            self.launch(i)
+        self.ctx.synchronize()
+        self.steps = steps
+        elapsed_ms, self.clocks = timed_region(self.ctx, self.ranks, sampler, self.launch, steps)
+        self.region_ms = elapsed_ms
+        self.ms_per_step = elapsed_ms / steps
+        self.sustained = None
+        if sustained_seconds > 0:
+            # The same launches for at least `sustained_seconds` of device time, so that every N and
+            # every workload is also seen in the power state a long job runs in.
+            count = int(max(steps, np.ceil(sustained_seconds * 1e3 / self.ms_per_step)))
+            long_ms, long_clocks = timed_region(self.ctx, self.ranks, sampler, self.launch, count)
+            self.sustained = {"launches": count, "seconds": long_ms / 1e3, "ms_per_step": long_ms / count,
+                              "clocks": long_clocks}
+
+    def check(self) -> dict:
+        """Parity of what was timed: sampled rows of C against the float64 rule."""
+        contract, ctx = self.contract, self.ctx
+        if contract.accumulate:
+            # The timed launches kept adding to C; check one launch on top of zeros.
+            self.dc.fill_bytes(0)
+            ctx.gemm(self.da, self.db, self.dc, **self.gemm_kwargs)
             ctx.synchronize()
-        clocks = sampler.summary(c_begin, time.perf_counter())
-        clocks["note"] = "sampled over a 0.5 s continuation of the timed launches"
-    elapsed_ms = ranks.max(elapsed_ms)
-    ms_per_step = elapsed_ms / args.steps
+        c = self.c = self.dc.to_numpy()
+        a, b = self.a, self.b
+        rows = self.rows = np.unique(np.linspace(0, self.m - 1, 16).astype(np.int64))
+        parity = workloads.check_against_float64(c, a, b, rows=rows, epilogue=contract.epilogue, bias=self.bias)
+        if contract.output_dtype != "float32":
+            # A 16-bit C carries half a unit in its last place on top of the float32 bound.
+            ulp = 2.0 ** -11 if contract.output_dtype == "float16" else 2.0 ** -8
+            exact = a[rows].astype(np.float64) @ b.astype(np.float64)
+            bound = np.abs(a[rows].astype(np.float64)) @ np.abs(b.astype(np.float64))
+            diff = np.abs(c[rows].astype(np.float64) - exact)
+            parity["ok"] = bool(parity["finite"] and (diff <= 1e-2 * bound + ulp * np.abs(exact)).all())
+            parity["output_rounding"] = (f"{contract.output_dtype}: half a unit in the last place added to the "
+                                         f"element bound")
+        self.parity_all = self.ranks.gather_objects(parity)
+        return self.parity_summary()
+
+    def parity_summary(self) -> dict:
+        return {"rule": "vs float64 product: rel Frobenius <= 1e-3, |err| <= 1e-2*(|A||B|)",
+                "rows_checked_per_rank": int(len(self.rows)), "ok": all(p["ok"] for p in self.parity_all),
+                "rel_frobenius": max(p["rel_frobenius"] for p in self.parity_all),
+                "max_element_ratio": max(p["max_element_ratio"] for p in self.parity_all)}
+
+    def kernel_name(self) -> str:
+        if self.plan.variant == "skinny":
+            return "gemm_skinny_kernel"
+        pairs = self.m > 128 and self.plan.tiles_m == -(-self.m // 256)
+        return "gemm_dense_pair_kernel" if pairs else "gemm_dense_kernel"
+
+    def roofline(self, peaks: dict, peaks_source: str) -> dict:
+        """Achieved rate of the dominant kernel over the timed region against the measured peak that
+        bounds it. `traffic` is only ever a figure from a committed ncu capture of the same kernel
+        and workload, named in `traffic_source`; nothing measured in this run stands behind it."""
+        traffic, source = NCU_DRAM_TRAFFIC.get(self.name, (None, None)) if self.ranks.world == 1 else (None, None)
+        seconds = self.ms_per_step * 1e-3
+        out: dict = {}
+        if self.plan.variant == "skinny":
+            algo = workloads.algorithmic_bytes(self.m, self.local_n, self.k) \
+                - (4 - self.c_type.itemsize) * self.m * self.local_n
+            algo += (4 * self.m * self.local_n if self.contract.accumulate else 0) \
+                + (0 if self.bias is None else self.bias.nbytes)
+            achieved, peak = algo / seconds / 1e9, float(peaks["hbm_gbs"])
+            out = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                   "algorithmic_bytes_per_launch": algo, "peak_source": f"{peaks_source} HBM copy bandwidth",
+                   "frac_of_nominal": achieved / NOMINAL_HBM_GBS}
+            if self.sustained:
+                rate = algo / (self.sustained["ms_per_step"] * 1e-3) / 1e9
+                out["sustained"] = {**self.sustained, "achieved": rate, "frac": rate / peak}
+        else:
+            achieved = self.local_flops / seconds / 1e12
+            burst, long_run = float(peaks["bf16_tflops"]), float(peaks["bf16_tflops_sustained"])
+            # A timed region shorter than a second is a burst (the clocks sampled inside it say so
+            # too); a longer one is compared with the figure cuBLAS sustains under the power cap.
+            is_burst = self.region_ms < 1000.0
+            peak = burst if is_burst else long_run
+            out = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                   "frac": achieved / peak, "flops_per_launch": self.local_flops,
+                   "peak_source": f"{peaks_source} cuBLAS bf16 8192^3 (16-bit output), "
+                                  + ("burst: the timed region lasted under a second" if is_burst
+                                     else "sustained: the timed region lasted over a second"),
+                   "timed_region_ms": self.region_ms,
+                   "frac_of_burst_peak": achieved / burst, "frac_of_sustained_peak": achieved / long_run,
+                   "frac_of_nominal": achieved / NOMINAL_PEAK_TFLOPS}
+            if self.sustained:
+                rate = self.local_flops / (self.sustained["ms_per_step"] * 1e-3) / 1e12
+                out["sustained"] = {**self.sustained, "achieved": rate, "peak": long_run, "frac": rate / long_run,
+                                    "peak_source": f"{peaks_source} cuBLAS bf16, back to back for seconds"}
+        out["kernel"] = self.kernel_name()
+        out["traffic"] = traffic
+        out["traffic_source"] = source if traffic is not None else "not captured for this workload"
+        return out
+
+    def free(self) -> None:
+        for bufs in self.sets:
+            for buf in bufs:
+                buf.free()
+        if self.dbias is not None:
+            self.dbias.free()
+        self.sets, self.bound = [], []
+
+
+def side_record(ctx, ranks: Ranks, sampler: ClockSampler, name: str, steps: int, peaks: dict, peaks_source: str,
+                sustained_seconds: float = 0.0) -> dict:
+    """One of the other benchmark configurations on this GPU: ms, achieved rate, roofline, parity,
+    clocks -- the same protocol as the headline workload, without the end-to-end and CPU legs."""
+    try:
+        run = DeviceRun(ctx, ranks, name, rotate=True)
+        run.time(sampler, steps, 5, sustained_seconds)
+        parity = run.check()
+        record = {
+            "m": run.m, "n": run.local_n, "k": run.k, "input_dtype": run.w.dtype, "steps": steps,
+            "ms_per_step": run.ms_per_step, "tflops": run.local_flops / (run.ms_per_step * 1e-3) / 1e12,
+            "gbs": workloads.algorithmic_bytes(run.m, run.local_n, run.k) / (run.ms_per_step * 1e-3) / 1e9,
+            "variant": run.plan.variant, "grid": run.plan.grid, "splits": run.plan.splits,
+            "launches_per_step": run.plan.kernel_launches, "l2": run.l2,
+            "roofline": run.roofline(peaks, peaks_source), "parity": parity, "clocks": run.clocks,
+        }
+        run.free()
+        return record
+    except Exception as exc:  # a side record must not take the headline number down with it
+        return {"error": f"{type(exc).__name__}: {exc}"}
+
+
+def map_record(ctx, ranks: Ranks, sampler: ClockSampler, steps: int, peaks: dict, peaks_source: str) -> dict:
+    """The masked element-wise kernel class (examples/b200_elementwise.py: scaled_clamp, seven float32
+    operations with a second input) on 2^27 elements per buffer: HBM-bound, 12 bytes per element
+    (two inputs read, one output written), checked bit for bit against the NumPy oracle."""
+    try:
+        from examples.b200_elementwise import compiled as compiled_map
+        from oracle import cpu_ref
+
+        n = 1 << 27
+        plan = compiled_map("scaled_clamp", ranks.local_rank).plan
+        rng = np.random.default_rng(16)
+        x = rng.standard_normal(n, dtype=np.float32)
+        y = rng.standard_normal(n, dtype=np.float32)
+        dx, dy, dout = ctx.to_device(x), ctx.to_device(y), ctx.empty((n,), np.float32)
+        launch = lambda i: ctx.map(dx, dout, plan.ops, other=dy)  # noqa: E731
+        for i in range(5):
+            launch(i)
+        ctx.synchronize()
+        elapsed_ms, clocks = timed_region(ctx, ranks, sampler, launch, steps)
+        ms = elapsed_ms / steps
+        sample = slice(0, 1 << 20)
+        got = dout.to_numpy()
+        want = cpu_ref.map_elementwise(x[sample], plan.ops, other=y[sample])
+        tail = cpu_ref.map_elementwise(x[-4099:], plan.ops, other=y[-4099:])
+        ok = bool(np.array_equal(got[sample].view(np.uint32), want.view(np.uint32))
+                  and np.array_equal(got[-4099:].view(np.uint32), tail.view(np.uint32)))
+        algo = 12.0 * n
+        achieved, peak = algo / (ms * 1e-3) / 1e9, float(peaks["hbm_gbs"])
+        for buf in (dx, dy, dout):
+            buf.free()
+        return {"kernel_class": "masked element-wise map (scaled_clamp: 7 float32 operations, 2 inputs)",
+                "n": n, "steps": steps, "ms_per_step": ms, "gbs": achieved,
+                "l2": "inputs larger than L2 (1.5 GiB per launch)",
+                "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                             "frac": achieved / peak, "algorithmic_bytes_per_launch": algo,
+                             "peak_source": f"{peaks_source} HBM copy bandwidth", "kernel": "map_f32_kernel",
+                             "frac_of_nominal": achieved / NOMINAL_HBM_GBS, "traffic": None,
+                             "traffic_source": "not captured for this workload"},
+                "parity": {"rule": "bit-identical to the NumPy oracle (first 2^20 and last 4099 elements)", "ok": ok},
+                "clocks": clocks}
+    except Exception as exc:
+        return {"error": f"{type(exc).__name__}: {exc}"}
+
+
+def run_gpu_arm(args, ranks: Ranks) -> None:
+    from hc import cuda
+    from hc.distributed import column_slab, init_communicator
+
+    name = choose_workload(args, ranks.world)
+    w = workloads.CONFIGS[name]
+    if name != "sharded" and ranks.world > 1:
+        raise SystemExit(f"workload {name} does not shard; run it with --gpus 1")
+    ctx = cuda.Context(ranks.local_rank)
+    peaks, peaks_source = measured_peaks()
+    run = DeviceRun(ctx, ranks, name, b_transposed=args.b_transposed, member=args.member)
+    a, b, m, k, local_n = run.a, run.b, run.m, run.k, run.local_n
+    da, db, dc = run.da, run.db, run.dc
+    contract, plan, handle, bias = run.contract, run.plan, run.handle, run.bias
+    c_type, total_flops = run.c_type, run.total_flops
+
+    # ---- warm-up, then the timed region (device time, max over ranks), then >= 2 s of the same ----
+    sampler = ClockSampler(ranks.local_rank)
+    sampler.start()
+    run.time(sampler, args.steps, args.warmup, 0.0 if args.quick else args.sustained_seconds)
+    ms_per_step, clocks = run.ms_per_step, run.clocks
     value = total_flops / (ms_per_step * 1e-3) / 1e12
-    kernel_tflops = local_flops / (ms_per_step * 1e-3) / 1e12
 
     # ---- correctness of what was timed (sampled rows, float64 rule) ------------------------
-    if contract.accumulate:
-        # The timed launches kept adding to C; check one launch on top of zeros.
-        dc.fill_bytes(0)
-        ctx.gemm(da, db, dc, **gemm_kwargs)
-        ctx.synchronize()
-    c = dc.to_numpy()
-    rows = np.unique(np.linspace(0, m - 1, 16).astype(np.int64))
-    parity = workloads.check_against_float64(c, a, b, rows=rows, **member_check)
-    if contract.output_dtype != "float32":
-        # A 16-bit C carries half a unit in its last place on top of the float32 bound.
-        ulp = 2.0 ** -11 if contract.output_dtype == "float16" else 2.0 ** -8
-        exact = a[rows].astype(np.float64) @ b.astype(np.float64)
-        bound = np.abs(a[rows].astype(np.float64)) @ np.abs(b.astype(np.float64))
-        diff = np.abs(c[rows].astype(np.float64) - exact)
-        parity["ok"] = bool(parity["finite"] and (diff <= 1e-2 * bound + ulp * np.abs(exact)).all())
-        parity["output_rounding"] = f"{contract.output_dtype}: half a unit in the last place added to the element bound"
-    parity_all = ranks.gather_objects(parity)
+    parity = run.check()
+    c, rows = run.c, run.rows
 
-    # ---- end to end through the public handle on pinned host buffers ---------------------
     if args.quick:
         sampler.stop()
         if ranks.rank == 0:
@@ -433,11 +662,13 @@ def run_gpu_arm(args, ranks: Ranks) -> None:
                               "steps": args.steps, "ms_per_step": ms_per_step, "quick": True,
                               "config": {"workload": name, "variant": plan.variant, "splits": plan.splits,
                                          "grid": plan.grid, "launches_per_step": plan.kernel_launches},
-                              "parity_ok": all(p["ok"] for p in parity_all), "clocks": clocks}), flush=True)
+                              "parity_ok": parity["ok"], "clocks": clocks}), flush=True)
         return
+
+    # ---- end to end through the public handle on pinned host buffers ---------------------
     e2e_steps = max(1, min(args.steps, args.e2e_steps))
     pa = cuda.pinned_empty(a.shape, a.dtype)
-    host_b = bt if args.b_transposed else b
+    host_b = run.host_b
     pb = cuda.pinned_empty(host_b.shape, host_b.dtype)
     pc = cuda.pinned_empty((m, local_n), c_type)
     pa[...] = a
@@ -469,7 +700,6 @@ def run_gpu_arm(args, ranks: Ranks) -> None:
            "steps": e2e_steps, "h2d_bytes_per_step": int(h2d_bytes),
            "d2h_bytes_per_step": int(pc.nbytes), "matches_device_path": e2e_ok,
            "api": "hc.compile(kernel, target='nvidia-sm100a')(a, b, c) on pinned NumPy arrays"}
-    sampler.stop()
 
     # ---- optional all-gather of the C slabs (N > 1), reported separately ---------------------
     gather = None
@@ -538,58 +768,49 @@ def run_gpu_arm(args, ranks: Ranks) -> None:
         except Exception as exc:
             fused = {"error": f"{type(exc).__name__}: {exc}"}
 
+    # ---- the other benchmark configurations on this GPU (single-GPU line only) --------------
+    side = {}
+    if ranks.world == 1 and name == "gemm_8192" and args.member == "plain" and not args.b_transposed \
+            and not args.no_side_workloads:
+        run.free()  # config 5 on one GPU needs 3.5 GiB of its own
+        side["skinny"] = side_record(ctx, ranks, sampler, "skinny", 400, peaks, peaks_source)
+        side["ragged"] = side_record(ctx, ranks, sampler, "ragged", 400, peaks, peaks_source)
+        side["sim_64"] = side_record(ctx, ranks, sampler, "sim_64", 1000, peaks, peaks_source)
+        side["elementwise_map"] = map_record(ctx, ranks, sampler, 50, peaks, peaks_source)
+        side["sharded_1gpu"] = side_record(ctx, ranks, sampler, "sharded", 10, peaks, peaks_source,
+                                           sustained_seconds=args.sustained_seconds)
+    sampler.stop()
+
     if ranks.rank != 0:
         return
 
-    # ---- roofline of the dominant kernel ----------------------------------------------------
-    peaks, peaks_source = measured_peaks()
-    if plan.variant == "skinny":
-        algo_bytes = workloads.algorithmic_bytes(m, local_n, k) - (4 - c_type.itemsize) * m * local_n
-        algo_bytes += (4 * m * local_n if contract.accumulate else 0) + (0 if bias is None else bias.nbytes)
-        achieved = algo_bytes / (ms_per_step * 1e-3) / 1e9
-        peak = float(peaks["hbm_gbs"])
-        roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                    "traffic": NCU_DRAM_TRAFFIC_BYTES.get(name), "kernel": "gemm_skinny_kernel",
-                    "algorithmic_bytes_per_launch": algo_bytes, "peak_source": f"{peaks_source} HBM copy bandwidth",
-                    "frac_of_nominal": achieved / NOMINAL_HBM_GBS}
-    else:
-        # Which measured cuBLAS figure the launch is compared with: the burst one for launches
-        # that ran at full clocks, the sustained one when the timed region ran under the power cap
-        # (sw_power_cap seen by NVML during it) or lasted longer than a second.
-        capped = "sw_power_cap" in clocks.get("reasons", []) or args.steps * ms_per_step > 1000.0
-        peak = float(peaks["bf16_tflops_sustained"] if capped else peaks["bf16_tflops"])
-        roofline = {"bound": "tensor", "achieved": kernel_tflops, "peak": peak, "unit": "TFLOP/s",
-                    "frac": kernel_tflops / peak, "traffic": NCU_DRAM_TRAFFIC_BYTES.get(name),
-                    "kernel": "gemm_dense_pair_kernel" if m > 128 and plan.tiles_m == -(-m // 256)
-                    else "gemm_dense_kernel", "flops_per_launch": local_flops,
-                    "peak_source": f"{peaks_source} cuBLAS bf16 8192^3 (16-bit output), "
-                                   f"{'sustained: the timed region ran under sw_power_cap' if capped else 'burst'}",
-                    "frac_of_burst_peak": kernel_tflops / float(peaks["bf16_tflops"]),
-                    "frac_of_sustained_peak": kernel_tflops / float(peaks["bf16_tflops_sustained"]),
-                    "frac_of_nominal": kernel_tflops / NOMINAL_PEAK_TFLOPS}
-
+    roofline = run.roofline(peaks, peaks_source)
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": ranks.world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "strong" if ranks.world > 1 else "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": {"workload": name, "m": w.m, "n": w.n, "k": w.k, "input_dtype": w.dtype,
-                   "accumulate": "fp32", "variant": plan.variant, "per_gpu_n": local_n,
+        "config": {"workload": name, "m": w.m, "n": w.n, "k": w.k, "input_dtype": w.dtype},
+        "detail": {"accumulate": "fp32", "variant": plan.variant, "per_gpu_n": local_n,
                    "b_layout": "[N, K] (transposed)" if args.b_transposed else "[K, N]",
                    "member": args.member,
                    "parallelism": f"n-sharded x{ranks.world}" if ranks.world > 1 else "single GPU",
-                   "l2": "inputs larger than L2 (A+B+C per GPU exceed 126 MB)"
-                   if a.nbytes + b.nbytes + c.nbytes > 126e6 else "working set fits L2",
-                   "device": ctx.name, "sm_count": ctx.sm_count},
+                   "l2": run.l2, "device": ctx.name, "sm_count": ctx.sm_count},
         "roofline": roofline,
         "e2e": e2e,
         "gpu_launches": args.steps * plan.kernel_launches,
         "clocks": clocks,
-        "parity": {"rule": "vs float64 product: rel Frobenius <= 1e-3, |err| <= 1e-2*(|A||B|)",
-                   "rows_checked_per_rank": int(len(rows)), "ok": all(p["ok"] for p in parity_all),
-                   "rel_frobenius": max(p["rel_frobenius"] for p in parity_all),
-                   "max_element_ratio": max(p["max_element_ratio"] for p in parity_all)},
+        "parity": parity,
     }
+    if run.sustained is not None:
+        per_step = run.sustained["ms_per_step"]
+        line["sustained"] = {"value": total_flops / (per_step * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": per_step,
+                             "launches": run.sustained["launches"], "seconds": run.sustained["seconds"],
+                             "clocks": run.sustained["clocks"],
+                             "note": "the timed launches repeated for at least this long, CUDA-event time, max "
+                                     "over ranks: the rate in the power state of a long job"}
+    if side:
+        line["workloads"] = side
     if gather is not None:
         line["all_gather"] = gather
     if fused is not None:
@@ -601,6 +822,7 @@ def run_gpu_arm(args, ranks: Ranks) -> None:
     if ranks.world == 1 and not args.no_cpu_baseline:
         baseline = time_cpu_oracle(a, b)
         baseline["numpy_f32_matmul"] = time_numpy_matmul(a, b)
+        baseline["simulator"] = time_reference_simulator()
         line["cpu_baseline"] = baseline
     print(json.dumps(line), flush=True)
 
@@ -615,6 +837,11 @@ def main() -> int:
     parser.add_argument("--shape", default=None, metavar="MxNxK",
                         help="an arbitrary float16 shape instead of a named workload (single GPU), e.g. 8192x8192x512")
     parser.add_argument("--e2e-steps", type=int, default=5)
+    parser.add_argument("--sustained-seconds", type=float, default=2.0,
+                        help="after the timed steps, repeat the same launches for at least this long and report "
+                             "that rate too (0 = skip)")
+    parser.add_argument("--no-side-workloads", action="store_true",
+                        help="single GPU: leave out the records of the other benchmark configurations")
     parser.add_argument("--no-gather", action="store_true")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--b-transposed", action="store_true",

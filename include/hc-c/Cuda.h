@@ -39,7 +39,7 @@
 extern "C" {
 #endif
 
-#define HC_CUDA_API_VERSION 4
+#define HC_CUDA_API_VERSION 5
 
 typedef enum HcCudaStatus {
   HC_CUDA_OK = 0,
@@ -240,6 +240,54 @@ HC_CUDA_CAPI_EXPORTED int hcCudaGemm(HcCudaContext *ctx, const HcCudaGemmArgs *a
  * copy of A in and the compute. Page-locked host buffers (hcCudaHostAlloc) make the copies
  * asynchronous and about twice as fast. */
 HC_CUDA_CAPI_EXPORTED int hcCudaGemmHost(HcCudaContext *ctx, const HcCudaGemmArgs *args);
+
+/* ---- the masked element-wise map ---------------------------------------------------------- */
+
+/* Operations of hcCudaMap, applied in order to every element: with a float32 constant, or with the
+ * element of the second input at the same index. They are the element-wise tensor operations of
+ * doc/langref.md:405-414 that a one-dimensional load / compute / store kernel spells out. */
+typedef enum HcCudaMapOp {
+  HC_CUDA_MAP_SCALE = 1,             /* v = v * value */
+  HC_CUDA_MAP_ADD = 2,               /* v = v + value */
+  HC_CUDA_MAP_MAX = 3,               /* v = maximum(v, value); NaN propagates, as in NumPy */
+  HC_CUDA_MAP_MIN = 4,               /* v = minimum(v, value) */
+  HC_CUDA_MAP_REVERSE_SUB = 5,       /* v = value - v */
+  HC_CUDA_MAP_ADD_OTHER = 6,         /* v = v + y[i] */
+  HC_CUDA_MAP_SUB_OTHER = 7,         /* v = v - y[i] */
+  HC_CUDA_MAP_REVERSE_SUB_OTHER = 8, /* v = y[i] - v */
+  HC_CUDA_MAP_MUL_OTHER = 9,         /* v = v * y[i] */
+  HC_CUDA_MAP_MAX_OTHER = 10,        /* v = maximum(v, y[i]) */
+  HC_CUDA_MAP_MIN_OTHER = 11         /* v = minimum(v, y[i]) */
+} HcCudaMapOp;
+#define HC_CUDA_MAX_MAP_OPS 8
+
+/* out[i] = ops(x[i] [, y[i]]) for i in [0, n): the kernel class of the reference simulator's masked
+ * vector test (tests/test_simulator.py:210-224) -- `vec = group.vload(x[gid:], shape=(G,))`,
+ * element-wise statements, `group.store(out[gid:], vec)` with work_shape=(W,) -- whose loads and
+ * stores are masked at the end of the buffers (hc/simulator.py:1338-1357, 1441-1458), so exactly
+ * the first n elements are read and written. float32 buffers, 4-byte aligned; `out` may be the very
+ * same buffer as x or y (in place) but must not partially overlap either. Every operation is one
+ * correctly rounded float32 operation, so the result is bit-identical to NumPy's. */
+typedef struct HcCudaMapArgs {
+  int64_t n;
+  const float *x;
+  const float *y; /* second input, or NULL when no ..._OTHER operation is used */
+  float *out;
+  int32_t op_count; /* 0..HC_CUDA_MAX_MAP_OPS; 0 copies x to out */
+  int32_t op_kind[HC_CUDA_MAX_MAP_OPS];
+  float op_value[HC_CUDA_MAX_MAP_OPS];
+} HcCudaMapArgs;
+
+/* Asynchronous; x, y, out are device pointers on the context's device. What
+ * `CompiledKernel.__call__` (hc/_compile.py:57-62) resolves to for a recognised element-wise
+ * kernel on device buffers. */
+HC_CUDA_CAPI_EXPORTED int hcCudaMap(HcCudaContext *ctx, const HcCudaMapArgs *args);
+
+/* Synchronous; x, y, out are host pointers (NumPy buffers). The arrays travel in chunks so that
+ * the copy in, the kernel and the copy out of successive chunks overlap; page-locked buffers make
+ * the copies asynchronous. The in-place, synchronous behaviour of `hc.simulator.launch`
+ * (hc/simulator.py:165-186). */
+HC_CUDA_CAPI_EXPORTED int hcCudaMapHost(HcCudaContext *ctx, const HcCudaMapArgs *args);
 
 /* ---- the product fused with its gather (N-sharded GEMM, one process per GPU) ------------- */
 

@@ -153,3 +153,35 @@ def matmul_numpy(a: np.ndarray, b: np.ndarray) -> np.ndarray:
     for kk in range(k):
         c += a32[:, kk : kk + 1] * b32[kk : kk + 1, :]
     return c
+
+
+def map_elementwise(x: np.ndarray, ops, other: np.ndarray | None = None) -> np.ndarray:
+    """The masked element-wise kernel class as the reference simulator executes it
+    (tests/test_simulator.py:210-224; loads hc/simulator.py:1338-1357, stores :1441-1458; value
+    arithmetic hc/_sim_types.py:373-420, which applies the NumPy ufunc to the payload): every
+    element below the buffers' extent goes through the statements once, each statement one
+    float32 NumPy operation. `ops` as the recogniser lists them: ("scale", c), ("add", c),
+    ("max", c), ("min", c), ("rsub", c), ("add_other",), ("sub_other",), ("rsub_other",),
+    ("mul_other",), ("max_other",), ("min_other",)."""
+    v = np.array(x, dtype=np.float32, copy=True)
+    w = None if other is None else np.asarray(other, dtype=np.float32)
+    with np.errstate(invalid="ignore", over="ignore"):
+        for op in ops:
+            kind = op[0]
+            operand = w if kind.endswith("_other") else np.float32(op[1])
+            base = kind[: -len("_other")] if kind.endswith("_other") else kind
+            if base in ("scale", "mul"):
+                v = v * operand
+            elif base == "add":
+                v = v + operand
+            elif base == "sub":
+                v = v - operand
+            elif base == "rsub":
+                v = operand - v
+            elif base == "max":
+                v = np.maximum(v, operand)
+            elif base == "min":
+                v = np.minimum(v, operand)
+            else:
+                raise ValueError(f"unknown operation {kind!r}")
+    return v.astype(np.float32, copy=False)

@@ -31,6 +31,10 @@ Fixtures (all produced by `hc.simulator.launch` on the example kernel):
       the fused member (C = maximum(0.125 * (A.B) + bias, 0)); `bias` holds the fourth buffer
   simnarrow_bf16_m33_n17_k40_seed13
       the narrow member (c: Buffer[M, N, bfloat16]); `c_bits` holds the 16-bit output
+  simmap_f32_seed15
+      the masked element-wise kernels of 5_b200/examples/b200_elementwise.py: `add_two_x/_y` the
+      reference's own vector test (tests/test_simulator.py:210-224), `x`, `y`, `out` the
+      scaled_clamp kernel on 1003 elements with NaN and infinities
 The file blocked_reference.npz holds `reference_blocked_matmul` of the first four (the
 reference test's own comparison value, atol 2e-6).
 """
@@ -170,6 +174,29 @@ def main() -> int:
     c = np.full((33, 17), 7.0).astype(ml_dtypes.bfloat16)
     mod.hc.simulator.launch(mod.tiled_wmma_matmul_for("bfloat16", False, "narrow"), a, b, c)
     _save("simnarrow_bf16_m33_n17_k40_seed13", a, b, c.astype(np.float32), c_bits=c.view(np.uint16))
+    # The masked element-wise kernels of 5_b200/examples/b200_elementwise.py under the reference
+    # simulator: the reference's own vector test (tests/test_simulator.py:210-224) and a chain of
+    # statements with a second input, on a length that no group size divides, with NaN and
+    # infinities among the values.
+    path = REPO / "5_b200" / "examples" / "b200_elementwise.py"
+    spec = importlib.util.spec_from_file_location("b200_elementwise_under_reference", path)
+    ew = importlib.util.module_from_spec(spec)
+    ew.__package__ = "loaded_by_make_golden"
+    sys.modules[spec.name] = ew
+    spec.loader.exec_module(ew)
+    x = np.arange(6, dtype=np.float32)
+    y = np.zeros((6,), dtype=np.float32)
+    ew.hc.simulator.launch(ew.add_two, x, y)
+    rng = np.random.default_rng(15)
+    x2 = rng.standard_normal(1003).astype(np.float32)
+    y2 = rng.standard_normal(1003).astype(np.float32)
+    x2[[5, 700]] = np.nan, -np.inf
+    y2[[64, 1002]] = np.inf, np.nan
+    out2 = np.full((1003,), np.float32(-7.0))
+    with np.errstate(invalid="ignore"):
+        ew.hc.simulator.launch(ew.scaled_clamp, x2, y2, out2)
+    np.savez_compressed(HERE / "simmap_f32_seed15.npz", add_two_x=x, add_two_y=y, x=x2, y=y2, out=out2)
+    print(f"simmap_f32_seed15: add_two{ x.shape } scaled_clamp{ x2.shape }", flush=True)
     return 0
 
 

@@ -191,3 +191,21 @@ print("ok")
         env=env, capture_output=True, text=True, timeout=120, cwd=str(REPO / "tests"))
     assert result.returncode == 0, result.stderr
     assert result.stdout.strip() == "ok"
+
+
+def test_elementwise_map_fixture() -> None:
+    """The masked element-wise kernels as the reference simulator executed them: the oracle's
+    statement-by-statement float32 restatement gives the same bits (NaN where it gave NaN), and
+    nothing was written past the operations the recogniser lists for these kernels."""
+    with np.load(GOLDEN / "simmap_f32_seed15.npz") as data:
+        fixture = {key: data[key] for key in data.files}
+    assert np.array_equal(fixture["add_two_y"], fixture["add_two_x"] + 2)  # the reference test's own assertion
+    assert np.array_equal(cpu_ref.map_elementwise(fixture["add_two_x"], (("add", 2.0),)), fixture["add_two_y"])
+    ops = (("scale", 0.5), ("add", -1.0), ("rsub_other",), ("max", 0.25), ("scale", -1.0), ("scale", 3.0),
+           ("add_other",))
+    out = cpu_ref.map_elementwise(fixture["x"], ops, other=fixture["y"])
+    want = fixture["out"]
+    assert np.isnan(want).sum() >= 3 and np.isinf(want).any() and not (want == -7.0).any()
+    assert np.array_equal(np.isnan(out), np.isnan(want))
+    keep = ~np.isnan(want)
+    assert np.array_equal(out[keep].view(np.uint32), want[keep].view(np.uint32))
