@@ -326,11 +326,11 @@ def build_tiled_wmma_matmul(element_type, b_transposed=False, member="plain"):
 
 @functools.lru_cache(maxsize=None)
 def tiled_wmma_matmul_for(dtype_name, b_transposed=False, member="plain"):
-    """The kernel for "float16" or "bfloat16" (built once per process)."""
-    if dtype_name == "bfloat16":
+    """The kernel for "float16", "bfloat16", "float8_e4m3fn" or "float8_e5m2" (built once per process)."""
+    if dtype_name in ("bfloat16", "float8_e4m3fn", "float8_e5m2"):
         import ml_dtypes
 
-        return build_tiled_wmma_matmul(ml_dtypes.bfloat16, b_transposed, member)
+        return build_tiled_wmma_matmul(getattr(ml_dtypes, dtype_name), b_transposed, member)
     if dtype_name == "float16":
         return build_tiled_wmma_matmul(np.float16, b_transposed, member)
     raise ValueError(f"unsupported element type {dtype_name!r}")
@@ -351,8 +351,8 @@ def gpu_wmma_matmul(a, b, *, device=None, b_transposed=False):
         raise ValueError("A and B must be rank-2 matrices")
     if a.shape[1] != (b.shape[1] if b_transposed else b.shape[0]):
         raise ValueError("A.shape[1] must match B.shape[0]")
-    if a.dtype != b.dtype or a.dtype.name not in ("float16", "bfloat16"):
-        raise ValueError("this example expects float16 or bfloat16 A and B operands of one type")
+    if a.dtype != b.dtype or a.dtype.name not in ("float16", "bfloat16", "float8_e4m3fn", "float8_e5m2"):
+        raise ValueError("this example expects float16, bfloat16 or float8 A and B operands of one type")
     c = np.zeros((a.shape[0], b.shape[0] if b_transposed else b.shape[1]), dtype=np.float32)
     compiled_for(a.dtype.name, device, b_transposed)(a, b, c)
     return c

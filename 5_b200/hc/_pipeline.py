@@ -52,7 +52,7 @@ __all__ = [
 ScheduleSource = Path | str | None
 
 NVIDIA_SM100A = "nvidia-sm100a"
-_SUPPORTED_INPUT_DTYPES = ("float16", "bfloat16")
+_SUPPORTED_INPUT_DTYPES = ("float16", "bfloat16", "float8_e4m3fn", "float8_e5m2")
 _SUPPORTED_OUTPUT_DTYPES = ("float32", "float16", "bfloat16")
 _PROBE_SHAPES = ((1, 1, 1), (16, 16, 16), (17, 19, 18), (64, 48, 80), (4095, 3073, 1031))
 
@@ -885,12 +885,12 @@ def _probe_helpers(facts: dict[str, Any], tile: tuple[int, int, int], wave: int,
     calls = facts.get("calls", {})
     if any(calls.get(key) is None for key in ("init", "step", "store")):
         return ["the kernel's helper calls could not be resolved"]
-    if input_dtype == "bfloat16":
+    if input_dtype == "float16":
+        element_type: Any = np.float16
+    else:
         import ml_dtypes
 
-        element_type: Any = ml_dtypes.bfloat16
-    else:
-        element_type = np.dtype(input_dtype).type
+        element_type = getattr(ml_dtypes, input_dtype)
     return probe_helper_chain(init=calls["init"], step=calls["step"], store=calls["store"],
                               bias=calls.get("bias"), tile=tile, wave=wave, acc_len=acc_len,
                               input_dtype=element_type, accumulate=bool(facts.get("accumulate")),

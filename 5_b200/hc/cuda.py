@@ -35,7 +35,7 @@ __all__ = [
     "plan_gemm",
 ]
 
-F16, BF16 = 0, 1
+F16, BF16, F8E4M3, F8E5M2 = 0, 1, 2, 3  # HcCudaDType
 VARIANT_AUTO, VARIANT_DENSE, VARIANT_SKINNY, VARIANT_NOOP, VARIANT_ZERO_FILL, VARIANT_ELEMENTWISE = 0, 1, 2, 3, 4, 5
 VARIANT_NAMES = {0: "auto", 1: "dense", 2: "skinny", 3: "noop", 4: "zero_fill", 5: "elementwise"}
 API_VERSION = 5
@@ -207,11 +207,10 @@ def device_count() -> int:
 
 def dtype_code(dtype: Any) -> int:
     name = dtype if isinstance(dtype, str) else np.dtype(dtype).name
-    if name == "float16":
-        return F16
-    if name == "bfloat16":
-        return BF16
-    raise ValueError(f"the CUDA backend multiplies float16 or bfloat16 matrices, got {name}")
+    codes = {"float16": F16, "bfloat16": BF16, "float8_e4m3fn": F8E4M3, "float8_e5m2": F8E5M2}
+    if name not in codes:
+        raise ValueError(f"the CUDA backend multiplies {sorted(codes)} matrices, got {name}")
+    return codes[name]
 
 
 C_F32, C_F16, C_BF16 = 0, 1, 2  # element type of C (HcCudaCType)

@@ -33,7 +33,7 @@ constexpr int64_t kMaxPitch = int64_t(1) << 38;
 // Pitch granularity of operands the library lays out itself (repacked or staged copies): 64
 // elements = 128 bytes, so that every 128-byte TMA box row is one aligned line. (TMA itself only
 // needs 16 bytes; rows that straddle lines cost about a third more time on the ragged config.)
-constexpr int64_t kRepackPitchElems = 64;
+constexpr int64_t kRepackPitchBytes = 128;  // pitch of repacked / staged operands: whole cache lines
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
                                    const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
@@ -183,9 +183,10 @@ int plan_gemm(const HcCudaContext *ctx, const HcCudaGemmArgs *args, int sm_count
                 (long long)m, (long long)n, (long long)k);
   if (m > kMaxDim || n > kMaxDim || k > kMaxDim)
     return fail(ctx, HC_CUDA_ERR_UNSUPPORTED, "m, n, k must each be at most 2^30");
-  if (args->dtype != HC_CUDA_F16 && args->dtype != HC_CUDA_BF16)
-    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "dtype must be HC_CUDA_F16 or HC_CUDA_BF16 (got %d)",
-                args->dtype);
+  if (args->dtype < HC_CUDA_F16 || args->dtype > HC_CUDA_F8E5M2)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "dtype must be an HcCudaDType (got %d)", args->dtype);
+  const bool f8 = hc::sm100::dtype_is_8bit(args->dtype);
+  const int64_t es = f8 ? 1 : 2;  // bytes per element of A and B
   if (args->variant != HC_CUDA_GEMM_AUTO && args->variant != HC_CUDA_GEMM_DENSE &&
       args->variant != HC_CUDA_GEMM_SKINNY)
     return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "variant must be AUTO, DENSE or SKINNY (got %d)",
@@ -253,10 +254,10 @@ int plan_gemm(const HcCudaContext *ctx, const HcCudaGemmArgs *args, int sm_count
   if (args->ldb < b_cols || args->ldb > kMaxPitch)
     return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "ldb (%lld) must be at least %s (%lld)",
                 (long long)args->ldb, b_nk ? "k" : "n", (long long)b_cols);
-  if ((reinterpret_cast<uintptr_t>(args->a) & 1) != 0 || (reinterpret_cast<uintptr_t>(args->b) & 1) != 0)
-    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "a and b must be 2-byte aligned");
-  const size_t a_bytes = (static_cast<size_t>(m - 1) * args->lda + k) * 2;
-  const size_t b_bytes = (static_cast<size_t>(b_rows - 1) * args->ldb + b_cols) * 2;
+  if ((reinterpret_cast<uintptr_t>(args->a) & (es - 1)) != 0 || (reinterpret_cast<uintptr_t>(args->b) & (es - 1)) != 0)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "a and b must be aligned to their element size");
+  const size_t a_bytes = (static_cast<size_t>(m - 1) * args->lda + k) * es;
+  const size_t b_bytes = (static_cast<size_t>(b_rows - 1) * args->ldb + b_cols) * es;
   if (ranges_overlap(args->c, c_bytes, args->a, a_bytes) ||
       ranges_overlap(args->c, c_bytes, args->b, b_bytes))
     return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "c must not overlap a or b");
@@ -271,15 +272,21 @@ int plan_gemm(const HcCudaContext *ctx, const HcCudaGemmArgs *args, int sm_count
   plan->variant = variant;
 
   if (!host_buffers) {
-    plan->repack_a = ((args->lda & 7) != 0 || (reinterpret_cast<uintptr_t>(args->a) & 15) != 0) ? 1 : 0;
-    plan->repack_b = ((args->ldb & 7) != 0 || (reinterpret_cast<uintptr_t>(args->b) & 15) != 0) ? 1 : 0;
+    plan->repack_a = ((args->lda * es) % 16 != 0 || (reinterpret_cast<uintptr_t>(args->a) & 15) != 0) ? 1 : 0;
+    plan->repack_b = ((args->ldb * es) % 16 != 0 || (reinterpret_cast<uintptr_t>(args->b) & 15) != 0) ? 1 : 0;
   }
+  // 8-bit operands reach the tensor cores K-major only: a float8 B stored [K, N] is transposed
+  // into scratch (one extra launch), whatever its pitch.
+  if (f8 && !b_nk)
+    plan->repack_b = 1;
   int64_t scratch = 0;
   if (plan->repack_a)
-    scratch += round_up(m * round_up(k, kRepackPitchElems) * 2, 1024);
+    scratch += round_up(m * round_up(k * es, kRepackPitchBytes), 1024);
   if (plan->repack_b)
-    scratch += round_up(b_rows * round_up(b_cols, kRepackPitchElems) * 2, 1024);
-  plan->kernel_launches = 1 + ((plan->repack_a || plan->repack_b) ? 1 : 0);
+    scratch += f8 && !b_nk ? round_up(n * round_up(k * es, kRepackPitchBytes), 1024)
+                           : round_up(b_rows * round_up(b_cols * es, kRepackPitchBytes), 1024);
+  // 16-bit operands share one repack launch; each 8-bit operand has its own.
+  plan->kernel_launches = 1 + (f8 ? plan->repack_a + plan->repack_b : ((plan->repack_a || plan->repack_b) ? 1 : 0));
 
   if (variant == HC_CUDA_GEMM_DENSE) {
     const hc::sm100::DenseTileShape t = hc::sm100::dense_tile_shape();
@@ -292,7 +299,7 @@ int plan_gemm(const HcCudaContext *ctx, const HcCudaGemmArgs *args, int sm_count
       return fail(ctx, HC_CUDA_ERR_UNSUPPORTED, "too many tiles");
     // Tiles that do not fill a round of the persistent CTAs (all of them, or the last round's) are
     // split over k when k is long enough.
-    const int block_k = hc::sm100::dense_block_k(pairs);
+    const int block_k = hc::sm100::dense_block_k(pairs) * static_cast<int>(2 / es);  // a stage holds the same bytes
     const int num_kb = static_cast<int>((k + block_k - 1) / block_k);
     const int slots = pairs ? sm_count / 2 : sm_count;
     long long first_split_tile = 0;
@@ -317,10 +324,12 @@ int plan_gemm(const HcCudaContext *ctx, const HcCudaGemmArgs *args, int sm_count
     const hc::sm100::SkinnyShape s = hc::sm100::skinny_shape(static_cast<int>(m));
     plan->tiles_m = 1;
     plan->tiles_n = static_cast<int32_t>((n + s.block_n - 1) / s.block_n);
-    plan->splits = hc::sm100::skinny_choose_splits(static_cast<int>(n), static_cast<int>(k), sm_count);
+    // (k counted in 16-bit equivalents: a k-block is 128 bytes of k whatever the element width.)
+    const int64_t k_units = (k * es + 1) / 2;
+    plan->splits = hc::sm100::skinny_choose_splits(static_cast<int>(n), static_cast<int>(k_units), sm_count);
     if (const char *forced = std::getenv("HC_CUDA_SKINNY_SPLITS")) {  // tuning aid
       const int v = std::atoi(forced);
-      const int64_t kb_total = (k + s.block_k - 1) / s.block_k;
+      const int64_t kb_total = (k_units + s.block_k - 1) / s.block_k;
       if (v >= 1 && v <= kb_total)
         plan->splits = v;
     }
@@ -400,7 +409,8 @@ int encode_map(HcCudaContext *ctx, CUtensorMap *map, int dtype, const void *base
   const cuuint32_t elem_strides[2] = {1, 1};
   const CUtensorMapDataType type = dtype == kMapFloat32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                                    : dtype == HC_CUDA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
-                                                           : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+                                   : hc::sm100::dtype_is_8bit(dtype) ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                                                     : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   const CUresult res = ctx->encode(map, type, 2, const_cast<void *>(base), dims, strides, box,
                                    elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
                                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -454,19 +464,40 @@ int enqueue_gemm(HcCudaContext *ctx, const HcCudaGemmArgs *args, const HcCudaGem
   const bool b_nk = args->b_layout == HC_CUDA_B_NK;
   const int b_rows = b_nk ? n : k, b_cols = b_nk ? k : n;  // B as stored
   char *cursor = static_cast<char *>(ctx->scratch);
-  if (plan.repack_a || plan.repack_b) {
+  const bool f8 = hc::sm100::dtype_is_8bit(args->dtype);
+  const int64_t es = f8 ? 1 : 2;  // bytes per element of A and B
+  bool b_nk_now = b_nk;           // how B is laid out where the GEMM kernel reads it
+  if (f8 && (plan.repack_a || plan.repack_b)) {
+    if (plan.repack_a) {
+      const int64_t pitch = round_up(static_cast<int64_t>(k), kRepackPitchBytes);
+      HC_TRY_CUDA(ctx, hc::sm100::launch_repack_bytes(a, lda, cursor, pitch, m, k, /*transpose=*/false, ctx->stream));
+      a = cursor;
+      lda = pitch;
+      cursor += round_up(static_cast<int64_t>(m) * pitch, 1024);
+    }
+    if (plan.repack_b) {
+      // Stored [K, N]: transposed to [N, K]. Stored [N, K] with an odd pitch: copied.
+      const int64_t pitch = round_up(static_cast<int64_t>(k), kRepackPitchBytes);
+      HC_TRY_CUDA(ctx, hc::sm100::launch_repack_bytes(b, ldb, cursor, pitch, b_rows, b_cols, /*transpose=*/!b_nk,
+                                                      ctx->stream));
+      b = cursor;
+      ldb = pitch;
+      b_nk_now = true;
+      cursor += round_up(static_cast<int64_t>(n) * pitch, 1024);
+    }
+  } else if (plan.repack_a || plan.repack_b) {
     // One launch copies whichever operands need it into scratch with 128-byte-aligned pitches.
     const void *src_a = nullptr, *src_b = nullptr;
     char *dst_a = nullptr, *dst_b = nullptr;
     int64_t pitch_a = 0, pitch_b = 0;
     if (plan.repack_a) {
-      pitch_a = round_up(k, kRepackPitchElems);
+      pitch_a = round_up(k, kRepackPitchBytes / 2);
       src_a = a;
       dst_a = cursor;
       cursor += round_up(static_cast<int64_t>(m) * pitch_a * 2, 1024);
     }
     if (plan.repack_b) {
-      pitch_b = round_up(b_cols, kRepackPitchElems);
+      pitch_b = round_up(b_cols, kRepackPitchBytes / 2);
       src_b = b;
       dst_b = cursor;
       cursor += round_up(static_cast<int64_t>(b_rows) * pitch_b * 2, 1024);
@@ -485,19 +516,20 @@ int enqueue_gemm(HcCudaContext *ctx, const HcCudaGemmArgs *args, const HcCudaGem
   }
 
   CUtensorMap tmap_a, tmap_b;
-  const int b_layout = b_nk ? hc::sm100::kBLayoutNK : hc::sm100::kBLayoutKN;
+  const int b_layout = b_nk_now ? hc::sm100::kBLayoutNK : hc::sm100::kBLayoutKN;
+  const uint32_t k_scale = static_cast<uint32_t>(2 / es);  // elements of k per 2 bytes: boxes are 128 bytes of k
   if (plan.variant == HC_CUDA_GEMM_DENSE) {
     const hc::sm100::DenseTileShape t = hc::sm100::dense_tile_shape();
     const bool pairs = hc::sm100::dense_uses_pairs(m, n, k, ctx->prop.multiProcessorCount);
-    if (int rc = encode_map(ctx, &tmap_a, args->dtype, a, k, m, static_cast<uint64_t>(lda) * 2,
-                            t.block_k, t.block_m))
+    if (int rc = encode_map(ctx, &tmap_a, args->dtype, a, k, m, static_cast<uint64_t>(lda) * es,
+                            t.block_k * k_scale, t.block_m))
       return rc;
     // B stored [K, N]: 64 (n) x 64 (k) boxes. Stored [N, K]: one box of 64 (k) x the CTA's rows
     // of n (256 on single CTAs, 128 per CTA of a pair).
-    if (int rc = b_nk ? encode_map(ctx, &tmap_b, args->dtype, b, k, n, static_cast<uint64_t>(ldb) * 2, t.block_k,
-                                   pairs ? t.block_n / 2 : t.block_n)
-                      : encode_map(ctx, &tmap_b, args->dtype, b, n, k, static_cast<uint64_t>(ldb) * 2, 64,
-                                   t.block_k))
+    if (int rc = b_nk_now ? encode_map(ctx, &tmap_b, args->dtype, b, k, n, static_cast<uint64_t>(ldb) * es,
+                                       t.block_k * k_scale, pairs ? t.block_n / 2 : t.block_n)
+                          : encode_map(ctx, &tmap_b, args->dtype, b, n, k, static_cast<uint64_t>(ldb) * 2, 64,
+                                       t.block_k))
       return rc;
     // C leaves through TMA stores when its rows start on 16-byte boundaries (the launcher falls
     // back to ordinary stores for fused work and push targets).
@@ -542,13 +574,13 @@ int enqueue_gemm(HcCudaContext *ctx, const HcCudaGemmArgs *args, const HcCudaGem
 
   const hc::sm100::SkinnyShape s = hc::sm100::skinny_shape(m);
   const uint32_t padded_m = m <= 16 ? 16 : (m <= 32 ? 32 : 64);
-  if (int rc = encode_map(ctx, &tmap_a, args->dtype, a, k, m, static_cast<uint64_t>(lda) * 2,
-                          s.block_k, padded_m))
+  if (int rc = encode_map(ctx, &tmap_a, args->dtype, a, k, m, static_cast<uint64_t>(lda) * es,
+                          s.block_k * k_scale, padded_m))
     return rc;
-  if (int rc = b_nk ? encode_map(ctx, &tmap_b, args->dtype, b, k, n, static_cast<uint64_t>(ldb) * 2, s.block_k,
-                                 s.block_n)
-                    : encode_map(ctx, &tmap_b, args->dtype, b, n, k, static_cast<uint64_t>(ldb) * 2, 64,
-                                 s.block_k))
+  if (int rc = b_nk_now ? encode_map(ctx, &tmap_b, args->dtype, b, k, n, static_cast<uint64_t>(ldb) * es,
+                                     s.block_k * k_scale, s.block_n)
+                        : encode_map(ctx, &tmap_b, args->dtype, b, n, k, static_cast<uint64_t>(ldb) * 2, 64,
+                                     s.block_k))
     return rc;
   float *partials = nullptr;
   if (plan.splits > 1) {
@@ -993,14 +1025,15 @@ int hcCudaGemmHost(HcCudaContext *ctx, const HcCudaGemmArgs *args) {
   for (int i = 0; i < args->epilogue_count; ++i)
     has_bias = has_bias || args->epilogue_kind[i] == HC_CUDA_EPILOGUE_BIAS_COLUMN;
   // Device copies get pitches that satisfy TMA (16 bytes), so no repack pass is needed.
-  const size_t lda = static_cast<size_t>(round_up(args->k, kRepackPitchElems));
+  const size_t es = hc::sm100::dtype_is_8bit(args->dtype) ? 1 : 2;  // bytes per element of A and B
+  const size_t lda = static_cast<size_t>(round_up(args->k, kRepackPitchBytes / static_cast<int64_t>(es)));
   const bool b_nk = args->b_layout == HC_CUDA_B_NK;
   const size_t b_rows = b_nk ? n : k, b_cols = b_nk ? k : n;  // B as stored
-  const size_t ldb = static_cast<size_t>(round_up(static_cast<int64_t>(b_cols), kRepackPitchElems));
+  const size_t ldb = static_cast<size_t>(round_up(static_cast<int64_t>(b_cols), kRepackPitchBytes / static_cast<int64_t>(es)));
   const size_t ldc = static_cast<size_t>(round_up(args->n, 16 / static_cast<int64_t>(ce)));  // 16-byte rows: TMA stores
-  if (int rc = ensure_stage(ctx, 0, m * lda * 2))
+  if (int rc = ensure_stage(ctx, 0, m * lda * es))
     return rc;
-  if (int rc = ensure_stage(ctx, 1, b_rows * ldb * 2))
+  if (int rc = ensure_stage(ctx, 1, b_rows * ldb * es))
     return rc;
   // C's staging buffer also holds the bias vector, after the last row.
   if (int rc = ensure_stage(ctx, 2, round_up(static_cast<int64_t>(m * ldc * ce), 16) + (has_bias ? n * 4 : 0)))
@@ -1019,7 +1052,7 @@ int hcCudaGemmHost(HcCudaContext *ctx, const HcCudaGemmArgs *args) {
   dev.c = dev_c;
   dev.ldc = static_cast<int64_t>(ldc);
 
-  const size_t total_bytes = (m * k + k * n) * 2 + m * n * ce;
+  const size_t total_bytes = (m * k + k * n) * es + m * n * ce;
   if (plan.variant == HC_CUDA_GEMM_ELEMENTWISE) {
     if (args->accumulate)
       HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(dev_c, ldc * ce, host_c, host_c_pitch, n * ce, m, cudaMemcpyHostToDevice,
@@ -1032,13 +1065,15 @@ int hcCudaGemmHost(HcCudaContext *ctx, const HcCudaGemmArgs *args) {
                                        ctx->stream));
     return synchronize_locked(ctx);
   }
+  // (8-bit operands take the sequential path: a float8 B stored [K, N] is transposed on the device as
+  // a whole before the product, which the panel pipeline below does not provide for.)
   const bool pipelined = plan.variant == HC_CUDA_GEMM_DENSE && m >= 1024 && total_bytes >= (size_t(32) << 20) &&
-                         std::getenv("HC_CUDA_NO_COPY_OVERLAP") == nullptr;
+                         es == 2 && std::getenv("HC_CUDA_NO_COPY_OVERLAP") == nullptr;
   if (!pipelined) {
-    HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(ctx->stage[0], lda * 2, args->a, static_cast<size_t>(args->lda) * 2,
-                                       k * 2, m, cudaMemcpyHostToDevice, ctx->stream));
-    HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(ctx->stage[1], ldb * 2, args->b, static_cast<size_t>(args->ldb) * 2,
-                                       b_cols * 2, b_rows, cudaMemcpyHostToDevice, ctx->stream));
+    HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(ctx->stage[0], lda * es, args->a, static_cast<size_t>(args->lda) * es,
+                                       k * es, m, cudaMemcpyHostToDevice, ctx->stream));
+    HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(ctx->stage[1], ldb * es, args->b, static_cast<size_t>(args->ldb) * es,
+                                       b_cols * es, b_rows, cudaMemcpyHostToDevice, ctx->stream));
     if (args->accumulate)
       HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(dev_c, ldc * ce, host_c, host_c_pitch, n * ce, m, cudaMemcpyHostToDevice,
                                          ctx->stream));

@@ -103,7 +103,7 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                        const __grid_constant__ CUtensorMap tmap_c, int c_tma,
                        const __grid_constant__ CUtensorMap tmap_partials, void *c, int m, int n,
                        int k, long long ldc, uint32_t idesc, int tiles_m, int tiles_n, int group_n,
-                       int l2_hints, int b_layout, Epilogue ep, SplitK split, int *status) {
+                       int l2_hints, int b_layout, int elem8, Epilogue ep, SplitK split, int *status) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t smem_base = (raw_addr + 1023u) & ~1023u;
@@ -153,7 +153,7 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const uint32_t tmem_base = *tmem_slot;
 
   const int num_tiles = tiles_m * tiles_n;
-  const int num_kb = (k + kBlockK - 1) / kBlockK;
+  const int num_kb = (k + (kBlockK << elem8) - 1) / (kBlockK << elem8);  // 8-bit: twice the k per stage
   const int cluster_id = static_cast<int>(blockIdx.x >> 1);
   const int num_clusters = static_cast<int>(gridDim.x >> 1);
   // A unit is one tile, or with split-k one range of a tile's k-blocks; the splits of a tile are
@@ -192,7 +192,7 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
             mbar_arrive_expect_tx(full_bar(stage), 2 * kStageBytes);
 #pragma unroll
           for (int sub = 0; sub < kKSub; ++sub) {
-            const int k0 = kb * kBlockK + sub * 64;
+            const int k0 = (kb * kBlockK + sub * 64) << elem8;
             tma_load_2d_pair_hint(a_dst + sub * kASubBytes, &tmap_a, leader_full, k0, m0, pol_a);
             if (b_layout == kBLayoutKN) {
 #pragma unroll
@@ -246,7 +246,7 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 b_kn ? make_smem_desc_sw128(b_addr, kBChunkBytes, 1024) + static_cast<uint64_t>(kk * 128)
                      : make_smem_desc_sw128(b_addr + (kk / 4) * kASubBytes, 16, 1024) +
                            static_cast<uint64_t>((kk % 4) * 2);
-            umma_f16_ss_pair(d_tmem, a_desc, b_desc, idesc, (kb != kb_begin || kk != 0) ? 1u : 0u);
+            umma_ss_pair(d_tmem, a_desc, b_desc, idesc, (kb != kb_begin || kk != 0) ? 1u : 0u, static_cast<uint32_t>(elem8));
           }
           // Hand ring slot `stage` back to both producers.
           umma_commit_pair(map_to_cta(empty_bar(stage), 0));
@@ -378,7 +378,10 @@ cudaError_t launch_gemm_dense_pair(const CUtensorMap &tmap_a, const CUtensorMap 
     clusters = 1;
   if (num_units < clusters)
     clusters = num_units;
-  const uint32_t idesc = make_idesc_f16(dtype == kDTypeBF16 ? 1u : 0u, /*a_mn_major=*/false,
+  const int elem8 = dtype_is_8bit(dtype) ? 1 : 0;
+  if (elem8 && b_layout != kBLayoutNK)
+    return cudaErrorInvalidValue;  // 8-bit operands are K-major: the caller transposes a [K, N] B first
+  const uint32_t idesc = make_idesc_f16(dtype_format(dtype), /*a_mn_major=*/false,
                                         /*b_mn_major=*/b_layout == kBLayoutKN, kTileM, kTileN);
   if (group_n < 1)
     group_n = 1;
@@ -405,10 +408,10 @@ cudaError_t launch_gemm_dense_pair(const CUtensorMap &tmap_a, const CUtensorMap 
   const unsigned grid = static_cast<unsigned>(clusters * 2);
   if (reads_c)
     gemm_dense_pair_kernel<true><<<grid, Roles<true>::kThreads, kSmemBytes, stream>>>(
-        tmap_a, tmap_b, c_map, c_tma, p_map, c, m, n, k, ldc, idesc, tiles_m, tiles_n, group_n, l2_hints, b_layout, launch_ep, split, status);
+        tmap_a, tmap_b, c_map, c_tma, p_map, c, m, n, k, ldc, idesc, tiles_m, tiles_n, group_n, l2_hints, b_layout, elem8, launch_ep, split, status);
   else
     gemm_dense_pair_kernel<false><<<grid, Roles<false>::kThreads, kSmemBytes, stream>>>(
-        tmap_a, tmap_b, c_map, c_tma, p_map, c, m, n, k, ldc, idesc, tiles_m, tiles_n, group_n, l2_hints, b_layout, launch_ep, split, status);
+        tmap_a, tmap_b, c_map, c_tma, p_map, c, m, n, k, ldc, idesc, tiles_m, tiles_n, group_n, l2_hints, b_layout, elem8, launch_ep, split, status);
   return cudaGetLastError();
 }
 

@@ -82,7 +82,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tmap_a,
                        const __grid_constant__ CUtensorMap tmap_c, int c_tma,
                        const __grid_constant__ CUtensorMap tmap_partials, void *c, int m, int n,
                   int k, long long ldc, uint32_t idesc, int tiles_m, int tiles_n, int group_n,
-                  int b_layout, Epilogue ep, SplitK split, int *status) {
+                  int b_layout, int elem8, Epilogue ep, SplitK split, int *status) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t smem_base = (raw_addr + 1023u) & ~1023u;  // swizzled tiles need 1 KiB alignment
@@ -129,7 +129,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const uint32_t tmem_base = *tmem_slot;
 
   const int num_tiles = tiles_m * tiles_n;
-  const int num_kb = (k + kBlockK - 1) / kBlockK;
+  const int num_kb = (k + (kBlockK << elem8) - 1) / (kBlockK << elem8);  // 8-bit: twice the k per stage
   // A unit is one tile, or with split-k one range of a tile's k-blocks; the splits of a tile are
   // consecutive units, so they run on neighbouring CTAs at the same time.
   const int num_units = split.splits == 1 ? num_tiles
@@ -155,14 +155,14 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint32_t a_dst = smem_base + stage * kStageBytes;
           const uint32_t b_dst = a_dst + kATileBytes;
           mbar_arrive_expect_tx(full_bar(stage), kStageBytes);
-          tma_load_2d(a_dst, &tmap_a, full_bar(stage), kb * kBlockK, m0);
+          tma_load_2d(a_dst, &tmap_a, full_bar(stage), (kb * kBlockK) << elem8, m0);
           if (b_layout == kBLayoutKN) {
 #pragma unroll
             for (int j = 0; j < kBlockN / 64; ++j)
               tma_load_2d(b_dst + j * kBChunkBytes, &tmap_b, full_bar(stage), n0 + j * 64, kb * kBlockK);
           } else {
             // B stored [N, K]: one box of 256 rows (n) x 64 k, K-major like A.
-            tma_load_2d(b_dst, &tmap_b, full_bar(stage), kb * kBlockK, n0);
+            tma_load_2d(b_dst, &tmap_b, full_bar(stage), (kb * kBlockK) << elem8, n0);
           }
           if (++stage == kStages) {
             stage = 0;
@@ -206,9 +206,9 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tmap_a,
           for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
             // Per 16-wide k-step: A advances 32 bytes inside the swizzle row, B advances
             // two groups of 8 k-rows (2048 bytes); both in 16-byte descriptor units.
-            umma_f16_ss(d_tmem, a_desc + static_cast<uint64_t>(kk * 2),
+            umma_ss(d_tmem, a_desc + static_cast<uint64_t>(kk * 2),
                         b_desc + static_cast<uint64_t>(kk) * b_step, idesc,
-                        (kb != kb_begin || kk != 0) ? 1u : 0u);
+                        (kb != kb_begin || kk != 0) ? 1u : 0u, static_cast<uint32_t>(elem8));
           }
           umma_commit(empty_bar(stage));
           if (++stage == kStages) {
@@ -331,7 +331,10 @@ cudaError_t launch_gemm_dense(const CUtensorMap &tmap_a, const CUtensorMap &tmap
   const long long num_units =
       split.splits == 1 ? num_tiles : split.first_split_tile + (num_tiles - split.first_split_tile) * split.splits;
   const int grid = static_cast<int>(num_units < max_ctas ? num_units : max_ctas);
-  const uint32_t idesc = make_idesc_f16(dtype == kDTypeBF16 ? 1u : 0u, /*a_mn_major=*/false,
+  const int elem8 = dtype_is_8bit(dtype) ? 1 : 0;
+  if (elem8 && b_layout != kBLayoutNK)
+    return cudaErrorInvalidValue;  // 8-bit operands are K-major: the caller transposes a [K, N] B first
+  const uint32_t idesc = make_idesc_f16(dtype_format(dtype), /*a_mn_major=*/false,
                                         /*b_mn_major=*/b_layout == kBLayoutKN, kBlockM, kBlockN);
   if (group_n < 1)
     group_n = 1;
@@ -354,11 +357,11 @@ cudaError_t launch_gemm_dense(const CUtensorMap &tmap_a, const CUtensorMap &tmap
   const CUtensorMap p_map = split.splits > 1 ? *tmap_partials : tmap_a;  // unused unless split
   if (reads_c)
     gemm_dense_kernel<true><<<grid, Roles<true>::kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, c_map, c_tma, p_map, c, m, n, k, ldc, idesc,
-                                                                       tiles_m, tiles_n, group_n, b_layout, launch_ep,
+                                                                       tiles_m, tiles_n, group_n, b_layout, elem8, launch_ep,
                                                                        split, status);
   else
     gemm_dense_kernel<false><<<grid, Roles<false>::kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, c_map, c_tma, p_map, c, m, n, k, ldc, idesc,
-                                                                        tiles_m, tiles_n, group_n, b_layout, launch_ep,
+                                                                        tiles_m, tiles_n, group_n, b_layout, elem8, launch_ep,
                                                                         split, status);
   return cudaGetLastError();
 }

@@ -18,6 +18,14 @@ constexpr int kBLayoutNK = 1;
 
 constexpr int kDTypeF16 = 0;
 constexpr int kDTypeBF16 = 1;
+constexpr int kDTypeF8E4M3 = 2;  // float8 e4m3fn
+constexpr int kDTypeF8E5M2 = 3;  // float8 e5m2
+// 8-bit operands run through tcgen05.mma.kind::f8f6f4 and must be K-major (A as [M, K], B as
+// [N, K]); the tiles are the same in bytes, so a ring stage holds twice as many k as for 16 bits.
+inline bool dtype_is_8bit(int dtype) { return dtype == kDTypeF8E4M3 || dtype == kDTypeF8E5M2; }
+inline int dtype_bytes(int dtype) { return dtype_is_8bit(dtype) ? 1 : 2; }
+// The A/B format field of the instruction descriptor (see make_idesc_f16).
+inline unsigned dtype_format(int dtype) { return (dtype == kDTypeBF16 || dtype == kDTypeF8E5M2) ? 1u : 0u; }
 constexpr int kCTypeF32 = 0;
 constexpr int kCTypeF16 = 1;
 constexpr int kCTypeBF16 = 2;
@@ -157,6 +165,12 @@ cudaError_t launch_epilogue_only(void *c, int m, int n, long long ldc, const Epi
 // signals and then reports kStatusDeviceWaitTimeout through `status`, like a GEMM kernel whose
 // wait ran out.
 cudaError_t launch_wait_selftest(long long budget_cycles, int *status, cudaStream_t stream);
+
+// 8-bit operands: copies a rows x cols matrix of bytes (pitch src_ld) to dst with pitch dst_ld
+// (a multiple of 16), transposed when `transpose` is set (dst is then cols x rows). This is how a
+// float8 B stored [K, N] becomes the K-major [N, K] operand, and how odd pitches are aligned.
+cudaError_t launch_repack_bytes(const void *src, long long src_ld, void *dst, long long dst_ld, int rows,
+                                int cols, bool transpose, cudaStream_t stream);
 
 // Copies rows x cols matrices of 16-bit elements into buffers whose row pitch is a multiple of 8
 // elements (16 bytes), as TMA requires; columns [cols, round_up(cols, 8)) of a destination are

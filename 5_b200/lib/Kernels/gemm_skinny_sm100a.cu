@@ -62,7 +62,7 @@ __global__ void __launch_bounds__(kNumThreads, kCtasPerSm)
 gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a,
                    const __grid_constant__ CUtensorMap tmap_b, void *c_any, int m, int n,
                    int k, long long ldc, uint32_t idesc, int n_tiles, int splits, int num_stages,
-                   int b_layout, Epilogue ep,
+                   int b_layout, int elem8, Epilogue ep,
                    float *__restrict__ partials, unsigned *__restrict__ counters, int *status) {
   using Cfg = Config<kMp>;
   float *__restrict__ c = static_cast<float *>(c_any);  // the float32 view (accumulation reads it)
@@ -107,7 +107,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a,
   tcgen05_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int kb_total = (k + kBlockK - 1) / kBlockK;
+  const int kb_total = (k + (kBlockK << elem8) - 1) / (kBlockK << elem8);  // 8-bit: twice the k per stage
   const int num_units = n_tiles * splits;
   const int n_pad = n_tiles * kBlockN;
 
@@ -139,9 +139,9 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                kb * kBlockK, stream_policy);
           } else {
             // B stored [N, K]: 128 rows (n) x 64 k in one box, K-major.
-            tma_load_2d_hint(b_dst, &tmap_b, full_bar(stage), kb * kBlockK, n0, stream_policy);
+            tma_load_2d_hint(b_dst, &tmap_b, full_bar(stage), (kb * kBlockK) << elem8, n0, stream_policy);
           }
-          tma_load_2d_hint(a_dst, &tmap_a, full_bar(stage), kb * kBlockK, 0, keep_policy);
+          tma_load_2d_hint(a_dst, &tmap_a, full_bar(stage), (kb * kBlockK) << elem8, 0, keep_policy);
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
@@ -183,9 +183,9 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint64_t a_desc = make_smem_desc_sw128(a_addr, 16, 1024);
 #pragma unroll
           for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
-            umma_f16_ss(d_tmem, bt_desc + static_cast<uint64_t>(kk) * bt_step,
-                        a_desc + static_cast<uint64_t>(kk * 2), idesc,
-                        (kb != kb_begin || kk != 0) ? 1u : 0u);
+            umma_ss(d_tmem, bt_desc + static_cast<uint64_t>(kk) * bt_step,
+                    a_desc + static_cast<uint64_t>(kk * 2), idesc,
+                    (kb != kb_begin || kk != 0) ? 1u : 0u, static_cast<uint32_t>(elem8));
           }
           umma_commit(empty_bar(stage));
           if (++stage == kStages) {
@@ -354,11 +354,14 @@ cudaError_t launch(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, void *c
   const long long units = static_cast<long long>(n_tiles) * splits;
   const int grid = static_cast<int>(units < max_ctas ? units : max_ctas);
   const int num_stages = skinny_ring_stages(m, grid, sm_count);
-  const uint32_t idesc = make_idesc_f16(dtype == kDTypeBF16 ? 1u : 0u, /*a_mn_major=*/b_layout == kBLayoutKN,
+  const int elem8 = dtype_is_8bit(dtype) ? 1 : 0;
+  if (elem8 && b_layout != kBLayoutNK)
+    return cudaErrorInvalidValue;  // 8-bit operands are K-major: the caller transposes a [K, N] B first
+  const uint32_t idesc = make_idesc_f16(dtype_format(dtype), /*a_mn_major=*/b_layout == kBLayoutKN,
                                         /*b_mn_major=*/false, kBlockN, kMp);
   // (The first flag describes the UMMA "A" operand, which is B^T here.)
   gemm_skinny_kernel<kMp><<<grid, kNumThreads, Cfg::smem_bytes(num_stages), stream>>>(
-      tmap_a, tmap_b, c, m, n, k, ldc, idesc, n_tiles, splits, num_stages, b_layout, ep, partials, counters, status);
+      tmap_a, tmap_b, c, m, n, k, ldc, idesc, n_tiles, splits, num_stages, b_layout, elem8, ep, partials, counters, status);
   return cudaGetLastError();
 }
 

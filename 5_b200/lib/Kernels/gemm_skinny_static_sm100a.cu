@@ -133,6 +133,9 @@ int hcCudaGemmSkinnyStatic(const HcCudaGemmArgs *args, void *stream, int synchro
   if (int rc = setup_current_device(device, &setup))
     return report(rc);
 
+  if (args->dtype != HC_CUDA_F16 && args->dtype != HC_CUDA_BF16)
+    return report(fail(HC_CUDA_ERR_UNSUPPORTED, "the static-scratch entry point multiplies float16 or bfloat16 "
+                                                "matrices (8-bit operands may need a transposing repack)"));
   if (args->accumulate != 0 || args->epilogue_count != 0 || args->c_dtype != HC_CUDA_C_F32)
     return report(fail(HC_CUDA_ERR_UNSUPPORTED, "the static-scratch entry point computes a float32 C = A*B only "
                                                 "(no accumulate, no fused operations, no 16-bit C)"));

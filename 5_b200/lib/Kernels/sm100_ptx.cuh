@@ -204,6 +204,24 @@ __device__ __forceinline__ void umma_f16_ss(uint32_t tmem_d, uint64_t desc_a, ui
       : "memory");
 }
 
+// The same with the element width chosen at run time: `elem8` != 0 issues kind::f8f6f4 (8-bit
+// floats, 32 of k per instruction), otherwise kind::f16 (16 of k). Both read 32 bytes of k per
+// operand row, so descriptors and their per-step advance are the same in bytes.
+__device__ __forceinline__ void umma_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                        uint32_t accumulate, uint32_t elem8) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p, q;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "setp.ne.b32 q, %5, 0;\n"
+      "@q tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n"
+      "@!q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n"
+      :
+      : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(elem8)
+      : "memory");
+}
+
 // Makes `bar` receive one arrival once every tcgen05.mma issued so far by this thread has
 // finished (implies tcgen05.fence::before_thread_sync).
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
@@ -343,6 +361,21 @@ __device__ __forceinline__ void umma_f16_ss_pair(uint32_t tmem_d, uint64_t desc_
       : "memory");
 }
 
+__device__ __forceinline__ void umma_ss_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                             uint32_t accumulate, uint32_t elem8) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p, q;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "setp.ne.b32 q, %5, 0;\n"
+      "@q tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n"
+      "@!q tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n"
+      :
+      : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(elem8)
+      : "memory");
+}
+
 // One arrival on `cluster_bar` (either CTA's) once all pair MMAs issued so far have finished.
 __device__ __forceinline__ void umma_commit_pair(uint32_t cluster_bar) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
@@ -369,8 +402,10 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr,
   return desc;
 }
 
-// Instruction descriptor for tcgen05.mma.kind::f16 with fp32 accumulation.
-//   in_format: 0 = fp16, 1 = bf16.  *_mn_major: operand is contiguous along M (or N).
+// Instruction descriptor for tcgen05.mma.kind::f16 and kind::f8f6f4 with fp32 accumulation (the
+// two kinds share the field layout).
+//   in_format: kind::f16: 0 = fp16, 1 = bf16; kind::f8f6f4: 0 = e4m3, 1 = e5m2.
+//   *_mn_major: operand is contiguous along M (or N).
 __host__ __device__ constexpr uint32_t make_idesc_f16(uint32_t in_format, bool a_mn_major,
                                                       bool b_mn_major, uint32_t umma_m,
                                                       uint32_t umma_n) {

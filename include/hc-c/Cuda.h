@@ -55,7 +55,17 @@ typedef enum HcCudaStatus {
 /* Element type of A and B. Accumulation is always float32 and C is float32 unless c_dtype says
  * otherwise, as in the reference kernel's `Buffer[M, N, np.float32]`
  * (examples/amdgpu_gfx11_wmma_matmul.py:310). */
-typedef enum HcCudaDType { HC_CUDA_F16 = 0, HC_CUDA_BF16 = 1 } HcCudaDType;
+typedef enum HcCudaDType {
+  HC_CUDA_F16 = 0,
+  HC_CUDA_BF16 = 1,
+  /* 8-bit floats in the ml_dtypes / OCP encodings (float8_e4m3fn: no infinities, NaN = S.1111.111;
+   * float8_e5m2: the upper byte of an fp16), multiplied by tcgen05.mma.kind::f8f6f4 with float32
+   * accumulation. Every product of two such values is exact in float32, as for the 16-bit types.
+   * The tensor cores take these operands with k contiguous, so a B stored [k, n] is transposed
+   * once into context scratch (one extra launch); B stored [n, k] is read where it stands. */
+  HC_CUDA_F8E4M3 = 2,
+  HC_CUDA_F8E5M2 = 3
+} HcCudaDType;
 
 typedef enum HcCudaGemmVariant {
   HC_CUDA_GEMM_AUTO = 0,   /* skinny when m <= 64, dense otherwise */
@@ -101,8 +111,8 @@ typedef enum HcCudaEpilogueOp {
  * a: Buffer[M, K], b: Buffer[K, N], c: Buffer[M, N] (examples/...:306-311), the symbols
  * M, N, K being what `_bind_buffer` derives from the array shapes (hc/simulator.py:752-768).
  * Every in-range element of C is overwritten; nothing outside C is written; A and B are
- * read only. A, B 2-byte aligned, C aligned to its element size; other alignments and pitches are
- * accepted (a or b not 16-byte aligned, or lda/ldb not a multiple of 8 elements, costs one
+ * read only. A, B, C aligned to their element sizes; other alignments and pitches are accepted
+ * (a or b not 16-byte aligned, or a pitch lda/ldb that is not a multiple of 16 bytes, costs one
  * repack launch through context scratch memory). */
 typedef struct HcCudaGemmArgs {
   int64_t m, n, k;

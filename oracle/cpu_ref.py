@@ -48,7 +48,7 @@ def load() -> ctypes.CDLL:
     global _LIB
     if _LIB is None:
         lib = ctypes.CDLL(str(build()))  # rebuilt when the source is newer than the library
-        if not hasattr(lib, "hc_oracle_matmul_fused"):  # a stale library with a fresh timestamp
+        if not hasattr(lib, "hc_oracle_matmul_fused") or not hasattr(lib, "hc_oracle_supports_f8"):  # a stale library with a fresh timestamp
             lib = ctypes.CDLL(str(build(force=True)))
         i64, vp, ci = ctypes.c_int64, ctypes.c_void_p, ctypes.c_int
         lib.hc_oracle_matmul.argtypes = [vp, i64, vp, i64, vp, i64, i64, i64, i64, ci, ci]
@@ -68,19 +68,22 @@ def max_threads() -> int:
     return int(load().hc_oracle_max_threads())
 
 
+F8E4M3FN = 2
+F8E5M2 = 3
+_DTYPE_CODES = {"float16": F16, "bfloat16": BF16, "float8_e4m3fn": F8E4M3FN, "float8_e5m2": F8E5M2}
+
+
 def dtype_code(dtype: np.dtype) -> int:
     name = np.dtype(dtype).name
-    if name == "float16":
-        return F16
-    if name == "bfloat16":
-        return BF16
-    raise ValueError(f"the oracle handles float16 and bfloat16 inputs, got {name}")
+    if name not in _DTYPE_CODES:
+        raise ValueError(f"the oracle handles {sorted(_DTYPE_CODES)} inputs, got {name}")
+    return _DTYPE_CODES[name]
 
 
 def _as_bits(x: np.ndarray) -> np.ndarray:
     if x.ndim != 2:
         raise ValueError("the oracle expects rank-2 matrices")
-    return np.ascontiguousarray(x).view(np.uint16)
+    return np.ascontiguousarray(x).view(np.uint8 if x.dtype.itemsize == 1 else np.uint16)
 
 
 def _check(a: np.ndarray, b: np.ndarray) -> tuple[int, int, int, int]:

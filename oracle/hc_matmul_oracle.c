@@ -30,7 +30,11 @@
  * fp32, so a fused multiply-add would give the same bits; the file is still compiled with
  * -ffp-contract=off so that the statement above does not depend on that argument.
  *
- * Inputs are passed as raw 16-bit patterns; `dtype` 0 = IEEE fp16, 1 = bfloat16.
+ * Inputs are passed as raw bit patterns; `dtype` 0 = IEEE fp16, 1 = bfloat16 (16-bit elements),
+ * 2 = float8 e4m3fn, 3 = float8 e5m2 (8-bit elements, the ml_dtypes / OCP encodings: e4m3fn has
+ * no infinities and one NaN pattern per sign, S.1111.111; e5m2 is the upper byte of an fp16).
+ * The simulator widens any NumPy element type with `np.float32(value)`, which is exact for all
+ * four, and products of two 8-bit floats are exact in fp32 like the 16-bit ones.
  */
 #include <stdint.h>
 #include <stdlib.h>
@@ -41,6 +45,8 @@
 
 #define HC_ORACLE_F16 0
 #define HC_ORACLE_BF16 1
+#define HC_ORACLE_F8E4M3FN 2
+#define HC_ORACLE_F8E5M2 3
 
 static float bits_to_float(uint32_t bits) {
   float f;
@@ -71,25 +77,54 @@ static float half_to_float(uint16_t h) {
 
 static float bf16_to_float(uint16_t h) { return bits_to_float((uint32_t)h << 16); }
 
-static float to_float(uint16_t v, int dtype) {
+static float f8e4m3fn_to_float(uint8_t v) {
+  const uint32_t sign = (uint32_t)(v & 0x80u) << 24;
+  const uint32_t exp = (v >> 3) & 0xfu;
+  uint32_t man = v & 0x7u;
+  if (exp == 15 && man == 7)
+    return bits_to_float(sign | 0x7fc00000u); /* the only NaN; there is no infinity */
+  if (exp == 0) {
+    if (man == 0)
+      return bits_to_float(sign);
+    int shift = 0; /* subnormal: man * 2^-9 */
+    while ((man & 0x8u) == 0) {
+      man <<= 1;
+      ++shift;
+    }
+    man &= 0x7u;
+    return bits_to_float(sign | ((uint32_t)(127 - 7 - shift + 1) << 23) | (man << 20));
+  }
+  return bits_to_float(sign | ((exp + 127 - 7) << 23) | (man << 20));
+}
+
+/* Element `index` of a matrix of `dtype` elements, widened to fp32 (exact). */
+static float to_float(const void *base, int64_t index, int dtype) {
+  if (dtype == HC_ORACLE_F8E4M3FN)
+    return f8e4m3fn_to_float(((const uint8_t *)base)[index]);
+  if (dtype == HC_ORACLE_F8E5M2)
+    return half_to_float((uint16_t)(((const uint8_t *)base)[index]) << 8);
+  const uint16_t v = ((const uint16_t *)base)[index];
   return dtype == HC_ORACLE_BF16 ? bf16_to_float(v) : half_to_float(v);
 }
+
+/* Marks a library that decodes the 8-bit element types (lets the loader spot a stale build). */
+int hc_oracle_supports_f8(void) { return 1; }
 
 int hc_oracle_max_threads(void) {
   const long online = sysconf(_SC_NPROCESSORS_ONLN);
   return online < 1 ? 1 : (online > 256 ? 256 : (int)online);
 }
 
-/* Widens a rows x cols matrix of 16-bit values to fp32 (exact). */
-void hc_oracle_widen(const uint16_t *src, int64_t ld, float *dst, int64_t rows, int64_t cols,
+/* Widens a rows x cols matrix of 16- or 8-bit values to fp32 (exact). */
+void hc_oracle_widen(const void *src, int64_t ld, float *dst, int64_t rows, int64_t cols,
                      int dtype) {
   for (int64_t r = 0; r < rows; ++r)
     for (int64_t c = 0; c < cols; ++c)
-      dst[r * cols + c] = to_float(src[r * ld + c], dtype);
+      dst[r * cols + c] = to_float(src, r * ld + c, dtype);
 }
 
 /* Literal restatement: workgroups, k-steps, lanes. Slow; for small shapes. Returns 0. */
-int hc_oracle_matmul_tiled(const uint16_t *a, int64_t lda, const uint16_t *b, int64_t ldb, float *c,
+int hc_oracle_matmul_tiled(const void *a, int64_t lda, const void *b, int64_t ldb, float *c,
                            int64_t ldc, int64_t m, int64_t n, int64_t k, int dtype) {
   enum { T = 16, LANES = 32, FRAG = 8 };
   const int64_t groups_m = (m + T - 1) / T, groups_n = (n + T - 1) / T;
@@ -105,9 +140,9 @@ int hc_oracle_matmul_tiled(const uint16_t *a, int64_t lda, const uint16_t *b, in
         for (int i = 0; i < T; ++i)
           for (int j = 0; j < T; ++j) {
             const int64_t ar = row0 + i, ak = k0 + j;
-            a_tile[i][j] = (ar < m && ak < k) ? to_float(a[ar * lda + ak], dtype) : 0.0f;
+            a_tile[i][j] = (ar < m && ak < k) ? to_float(a, ar * lda + ak, dtype) : 0.0f;
             const int64_t bk = k0 + i, bc = col0 + j;
-            b_tile[i][j] = (bk < k && bc < n) ? to_float(b[bk * ldb + bc], dtype) : 0.0f;
+            b_tile[i][j] = (bk < k && bc < n) ? to_float(b, bk * ldb + bc, dtype) : 0.0f;
           }
         for (int lane = 0; lane < LANES; ++lane) {
           const int col = lane % T;
@@ -138,8 +173,8 @@ int hc_oracle_matmul_tiled(const uint16_t *a, int64_t lda, const uint16_t *b, in
 /* Work shared by the threads of hc_oracle_matmul_rows: rows are handed out one at a time
  * through an atomic cursor; which thread computes a row does not affect its value. */
 typedef struct {
-  const uint16_t *a;
-  const uint16_t *b;
+  const void *a;
+  const void *b;
   float *bf;
   float *c;
   int64_t lda, ldb, ldc, n, k, row_end;
@@ -161,7 +196,7 @@ static void *widen_worker(void *arg) {
     if (r >= job->k)
       return NULL;
     for (int64_t j = 0; j < job->n; ++j)
-      job->bf[r * job->n + j] = to_float(job->b[r * job->ldb + j], job->dtype);
+      job->bf[r * job->n + j] = to_float(job->b, r * job->ldb + j, job->dtype);
   }
 }
 
@@ -177,7 +212,7 @@ static void *rows_worker(void *arg) {
       for (int64_t j = 0; j < n; ++j)
         out[j] = 0.0f;
     for (int64_t kk = 0; kk < job->k; ++kk) {
-      const float av = to_float(job->a[r * job->lda + kk], job->dtype);
+      const float av = to_float(job->a, r * job->lda + kk, job->dtype);
       const float *brow = job->bf + kk * n;
       for (int64_t j = 0; j < n; ++j) {
         const float prod = av * brow[j];
@@ -214,7 +249,7 @@ static void run_threads(void *(*fn)(void *), RowsJob *job, int threads) {
  * accumulator per column. Rows [row_begin, row_end) of C are computed, so callers can time
  * or check a bounded sample of a large problem. `threads` <= 0 means one per online CPU.
  * Returns 0, or -1 if memory for the widened copy of B could not be obtained. */
-static int matmul_rows_job(const uint16_t *a, int64_t lda, const uint16_t *b, int64_t ldb, float *c,
+static int matmul_rows_job(const void *a, int64_t lda, const void *b, int64_t ldb, float *c,
                            int64_t ldc, int64_t m, int64_t n, int64_t k, int dtype,
                            int64_t row_begin, int64_t row_end, int threads, const RowsJob *extra) {
   if (row_begin < 0)
@@ -251,7 +286,7 @@ static int matmul_rows_job(const uint16_t *a, int64_t lda, const uint16_t *b, in
   return 0;
 }
 
-int hc_oracle_matmul_rows(const uint16_t *a, int64_t lda, const uint16_t *b, int64_t ldb, float *c,
+int hc_oracle_matmul_rows(const void *a, int64_t lda, const void *b, int64_t ldb, float *c,
                           int64_t ldc, int64_t m, int64_t n, int64_t k, int dtype,
                           int64_t row_begin, int64_t row_end, int threads) {
   return matmul_rows_job(a, lda, b, ldb, c, ldc, m, n, k, dtype, row_begin, row_end, threads, NULL);
@@ -262,7 +297,7 @@ int hc_oracle_matmul_rows(const uint16_t *a, int64_t lda, const uint16_t *b, int
  * elements read as 0 and are never stored), so each sum starts from C[i,j] and then takes
  * the products k ascending; after the k-loop `op_count` element-wise fp32 statements run in
  * order on every accumulator value (kinds as in RowsJob; kind 5 adds bias[column]). */
-int hc_oracle_matmul_fused(const uint16_t *a, int64_t lda, const uint16_t *b, int64_t ldb, float *c,
+int hc_oracle_matmul_fused(const void *a, int64_t lda, const void *b, int64_t ldb, float *c,
                            int64_t ldc, int64_t m, int64_t n, int64_t k, int dtype, int accumulate,
                            int op_count, const int *op_kind, const float *op_value, const float *bias,
                            int threads) {
@@ -276,7 +311,7 @@ int hc_oracle_matmul_fused(const uint16_t *a, int64_t lda, const uint16_t *b, in
   return matmul_rows_job(a, lda, b, ldb, c, ldc, m, n, k, dtype, 0, m, threads, &extra);
 }
 
-int hc_oracle_matmul(const uint16_t *a, int64_t lda, const uint16_t *b, int64_t ldb, float *c,
+int hc_oracle_matmul(const void *a, int64_t lda, const void *b, int64_t ldb, float *c,
                      int64_t ldc, int64_t m, int64_t n, int64_t k, int dtype, int threads) {
   return hc_oracle_matmul_rows(a, lda, b, ldb, c, ldc, m, n, k, dtype, 0, m, threads);
 }

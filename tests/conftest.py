@@ -2,6 +2,7 @@
 
 from __future__ import annotations
 
+import os
 import sys
 from pathlib import Path
 
@@ -11,7 +12,8 @@ import pytest
 REPO = Path(__file__).resolve().parent.parent
 PACKAGE = REPO / "5_b200"
 GOLDEN = REPO / "tests" / "golden"
-REFERENCE = Path("/root/reference")
+# Checkout of the reference project, for the few tests that run its own code (skipped without it).
+REFERENCE = Path(os.environ.get("HC_REFERENCE_DIR", "/root/reference"))
 
 for entry in (str(REPO), str(PACKAGE)):
     if entry not in sys.path:
@@ -25,13 +27,7 @@ def pytest_configure(config: pytest.Config) -> None:
 def load_golden(name: str) -> tuple[np.ndarray, np.ndarray, np.ndarray]:
     """(A, B, C) of a fixture written by tests/golden/make_golden.py."""
     with np.load(GOLDEN / f"{name}.npz") as data:
-        dtype_name = str(data["dtype"])
-        if dtype_name == "bfloat16":
-            import ml_dtypes
-
-            dtype = ml_dtypes.bfloat16
-        else:
-            dtype = np.dtype(dtype_name).type
+        dtype = np_dtype(str(data["dtype"]))
         return data["a_bits"].view(dtype), data["b_bits"].view(dtype), data["c"]
 
 
@@ -48,8 +44,8 @@ def gpu_ctx():
 
 
 def np_dtype(name: str):
-    if name == "bfloat16":
+    if name in ("bfloat16", "float8_e4m3fn", "float8_e5m2"):
         import ml_dtypes
 
-        return ml_dtypes.bfloat16
+        return getattr(ml_dtypes, name)
     return np.dtype(name).type

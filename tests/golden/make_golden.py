@@ -31,6 +31,9 @@ Fixtures (all produced by `hc.simulator.launch` on the example kernel):
       the fused member (C = maximum(0.125 * (A.B) + bias, 0)); `bias` holds the fourth buffer
   simnarrow_bf16_m33_n17_k40_seed13
       the narrow member (c: Buffer[M, N, bfloat16]); `c_bits` holds the 16-bit output
+  simf8_e4m3fn_m33_n17_k40_seed16, simf8_e5m2_bt_m17_n19_k18_seed17
+      the float8 members of that family (8-bit raw patterns in `a_bits`, `b_bits`): e4m3fn with B
+      stored [K, N], e5m2 with B stored [N, K]
   simmap_f32_seed15
       the masked element-wise kernels of 5_b200/examples/b200_elementwise.py: `add_two_x/_y` the
       reference's own vector test (tests/test_simulator.py:210-224), `x`, `y`, `out` the
@@ -78,8 +81,8 @@ def _bf16_twin(example_module):
 def _save(name: str, a: np.ndarray, b: np.ndarray, c: np.ndarray, **extra: np.ndarray) -> None:
     np.savez_compressed(
         HERE / f"{name}.npz",
-        a_bits=a.view(np.uint16),
-        b_bits=b.view(np.uint16),
+        a_bits=a.view(np.uint8 if a.dtype.itemsize == 1 else np.uint16),
+        b_bits=b.view(np.uint8 if b.dtype.itemsize == 1 else np.uint16),
         c=c,
         dtype=np.array(a.dtype.name),
         **extra,
@@ -174,6 +177,22 @@ def main() -> int:
     c = np.full((33, 17), 7.0).astype(ml_dtypes.bfloat16)
     mod.hc.simulator.launch(mod.tiled_wmma_matmul_for("bfloat16", False, "narrow"), a, b, c)
     _save("simnarrow_bf16_m33_n17_k40_seed13", a, b, c.astype(np.float32), c_bits=c.view(np.uint16))
+    # 8-bit float members of the family (the simulator widens any NumPy element type with
+    # np.float32(...)): e4m3fn with B stored [K, N], e5m2 with B stored [N, K]. Values cover the
+    # formats' subnormals as well as their normal range.
+    rng = np.random.default_rng(16)
+    a = (rng.standard_normal((33, 40)) * rng.choice([0.01, 1.0, 8.0], size=(33, 40))).astype(ml_dtypes.float8_e4m3fn)
+    b = (rng.standard_normal((40, 17)) * rng.choice([0.01, 1.0, 8.0], size=(40, 17))).astype(ml_dtypes.float8_e4m3fn)
+    c = np.full((33, 17), np.float32(-7.0))
+    mod.hc.simulator.launch(mod.tiled_wmma_matmul_for("float8_e4m3fn"), a, b, c)
+    _save("simf8_e4m3fn_m33_n17_k40_seed16", a, b, c)
+    rng = np.random.default_rng(17)
+    a = (rng.standard_normal((17, 18)) * rng.choice([1e-4, 1.0, 100.0], size=(17, 18))).astype(ml_dtypes.float8_e5m2)
+    bt = (rng.standard_normal((19, 18)) * rng.choice([1e-4, 1.0, 100.0], size=(19, 18))).astype(ml_dtypes.float8_e5m2)
+    c = np.zeros((17, 19), np.float32)
+    mod.hc.simulator.launch(mod.tiled_wmma_matmul_for("float8_e5m2", True), a, bt, c)
+    _save("simf8_e5m2_bt_m17_n19_k18_seed17", a, bt, c)
+
     # The masked element-wise kernels of 5_b200/examples/b200_elementwise.py under the reference
     # simulator: the reference's own vector test (tests/test_simulator.py:210-224) and a chain of
     # statements with a second input, on a length that no group size divides, with NaN and

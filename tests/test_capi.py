@@ -222,7 +222,7 @@ def test_plan_degenerate_shapes() -> None:
         ({"a": 0}, "INVALID_ARGUMENT", "a and b must not be null"),
         ({"c": 0}, "INVALID_ARGUMENT", "c must not be null"),
         ({"c": 0x80000002}, "INVALID_ARGUMENT", "4-byte aligned"),
-        ({"b": 0x40000001}, "INVALID_ARGUMENT", "2-byte aligned"),
+        ({"b": 0x40000001}, "INVALID_ARGUMENT", "aligned to their element size"),
         ({"lda": 63}, "INVALID_ARGUMENT", "lda \\(63\\) must be at least k \\(64\\)"),
         ({"ldb": 10}, "INVALID_ARGUMENT", "ldb"),
         ({"ldc": 10}, "INVALID_ARGUMENT", "ldc"),

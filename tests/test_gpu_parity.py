@@ -117,6 +117,65 @@ def test_b_stored_transposed(shape: tuple[int, int, int], dtype: str) -> None:
     assert_close_to_oracle(c, a, b)
 
 
+FLOAT8_SHAPES = [
+    # dense on single CTAs and CTA pairs, skinny with and without split-k; k below, at and across the
+    # 128-element stage of the 8-bit kernels; odd pitches (repack) and aligned ones
+    (17, 19, 18), (128, 256, 128), (129, 257, 130), (300, 520, 1000), (1024, 96, 257), (513, 1000, 264),
+    (2048, 2048, 512), (8, 129, 65), (7, 1000, 777), (33, 512, 2048), (64, 3000, 520), (8, 4096, 8192),
+]
+
+
+def float8_inputs(m: int, n: int, k: int, dtype: str):
+    """Values spread over the format's range, subnormals included (products stay exact in fp32)."""
+    rng = np.random.default_rng([8, m, n, k])
+    scales = [0.01, 0.25, 2.0] if dtype == "float8_e4m3fn" else [1e-4, 0.25, 16.0]
+    a = (rng.standard_normal((m, k)) * rng.choice(scales, size=(m, k))).astype(np_dtype(dtype))
+    b = (rng.standard_normal((k, n)) * rng.choice(scales, size=(k, n))).astype(np_dtype(dtype))
+    return a, b
+
+
+@pytest.mark.parametrize("shape", FLOAT8_SHAPES)
+@pytest.mark.parametrize("dtype", ["float8_e4m3fn", "float8_e5m2"])
+def test_float8_members(shape: tuple[int, int, int], dtype: str) -> None:
+    """The float8 members of the kernel family, B stored [K, N] (transposed on the device before the
+    product) and [N, K] (read where it stands): same tolerance rule as the 16-bit members."""
+    m, n, k = shape
+    a, b = float8_inputs(m, n, k, dtype)
+    expect = cpu_ref.matmul_k_ascending(a, b)
+    assert_close_to_oracle(gpu_wmma_matmul(a, b), a, b, expect=expect)
+    c_t = gpu_wmma_matmul(a, np.ascontiguousarray(b.T), b_transposed=True)
+    assert_close_to_oracle(c_t, a, b, expect=expect)
+
+
+def test_float8_fixtures_and_device_buffers(gpu_ctx) -> None:
+    a, b, c_sim = load_golden("simf8_e4m3fn_m33_n17_k40_seed16")
+    assert_close_to_oracle(gpu_wmma_matmul(a, b), a, b, expect=c_sim)
+    a, bt, c_sim = load_golden("simf8_e5m2_bt_m17_n19_k18_seed17")
+    assert_close_to_oracle(gpu_wmma_matmul(a, bt, b_transposed=True), a, np.ascontiguousarray(bt.T), expect=c_sim)
+    # Device buffers: both layouts of B give the same bits (same tiles, same k order), and a launch
+    # with fused operations and a 16-bit C goes through the same epilogues as the 16-bit inputs.
+    a, b = float8_inputs(384, 1100, 520, "float8_e4m3fn")
+    da, db, dbt = gpu_ctx.to_device(a), gpu_ctx.to_device(b), gpu_ctx.to_device(np.ascontiguousarray(b.T))
+    dc, dct = gpu_ctx.empty((384, 1100), np.float32), gpu_ctx.empty((384, 1100), np.float32)
+    gpu_ctx.gemm(da, db, dc)
+    gpu_ctx.gemm(da, dbt, dct, b_transposed=True)
+    gpu_ctx.synchronize()
+    assert_close_to_oracle(dc.to_numpy(), a, b)
+    assert np.array_equal(dc.to_numpy(), dct.to_numpy())
+    bias = np.random.default_rng(3).standard_normal(1100).astype(np.float32)
+    dbias = gpu_ctx.to_device(bias)
+    ops = (("scale", 0.5), ("bias",), ("max", 0.0))
+    gpu_ctx.gemm(da, db, dc, epilogue=ops, bias=dbias)
+    gpu_ctx.synchronize()
+    assert_fused_close(dc.to_numpy(), a, b, epilogue=ops, bias=bias)
+    half = gpu_ctx.empty((384, 1100), np.float16)
+    gpu_ctx.gemm(da, dbt, half, b_transposed=True)
+    gpu_ctx.synchronize()
+    assert np.array_equal(half.to_numpy(), dct.to_numpy().astype(np.float16))
+    for buf in (da, db, dbt, dc, dct, dbias, half):
+        buf.free()
+
+
 def test_transposed_b_fixture_and_device_buffers(gpu_ctx) -> None:
     a, bt, c_sim = load_golden("simbt_f16_m17_n19_k18_seed9")
     assert_close_to_oracle(gpu_wmma_matmul(a, bt, b_transposed=True), a, np.ascontiguousarray(bt.T), expect=c_sim)

@@ -209,3 +209,32 @@ def test_elementwise_map_fixture() -> None:
     assert np.array_equal(np.isnan(out), np.isnan(want))
     keep = ~np.isnan(want)
     assert np.array_equal(out[keep].view(np.uint32), want[keep].view(np.uint32))
+
+
+def test_float8_kernel_fixtures() -> None:
+    """The float8 members as the reference simulator executed them (e4m3fn with B stored [K, N],
+    e5m2 with B stored [N, K]): every form of the oracle reproduces the outputs bit for bit, and the
+    8-bit decoders agree with ml_dtypes on all 256 patterns of each format."""
+    import ctypes
+
+    import ml_dtypes
+
+    a, b, c_sim = load_golden("simf8_e4m3fn_m33_n17_k40_seed16")
+    assert a.dtype == ml_dtypes.float8_e4m3fn and a.shape == (33, 40) and not (c_sim == -7.0).any()
+    for fn in (cpu_ref.matmul_k_ascending, cpu_ref.matmul_tiled, cpu_ref.matmul_numpy):
+        assert np.array_equal(fn(a, b).view(np.uint32), c_sim.view(np.uint32)), fn.__name__
+    a, bt, c_sim = load_golden("simf8_e5m2_bt_m17_n19_k18_seed17")
+    assert a.dtype == ml_dtypes.float8_e5m2 and bt.shape == (19, 18)
+    b = np.ascontiguousarray(bt.T)
+    for fn in (cpu_ref.matmul_k_ascending, cpu_ref.matmul_tiled, cpu_ref.matmul_numpy):
+        assert np.array_equal(fn(a, b).view(np.uint32), c_sim.view(np.uint32)), fn.__name__
+    lib = cpu_ref.load()
+    lib.hc_oracle_widen.argtypes = [ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64,
+                                    ctypes.c_int]
+    for dtype in (ml_dtypes.float8_e4m3fn, ml_dtypes.float8_e5m2):
+        every = np.arange(256, dtype=np.uint8).view(dtype).reshape(16, 16)
+        out = np.zeros((16, 16), np.float32)
+        lib.hc_oracle_widen(every.ctypes.data, 16, out.ctypes.data, 16, 16, cpu_ref.dtype_code(dtype))
+        want = every.astype(np.float32)
+        assert np.array_equal(np.isnan(out), np.isnan(want))
+        assert np.array_equal(out[~np.isnan(want)].view(np.uint32), want[~np.isnan(want)].view(np.uint32))
