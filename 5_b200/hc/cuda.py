@@ -56,6 +56,7 @@ EXPORTS = (
     "hcCudaEventDestroy", "hcCudaEventRecord", "hcCudaEventElapsedMs", "hcCudaCommGetUniqueId",
     "hcCudaCommInitRank", "hcCudaCommAllGather", "hcCudaCommDestroy", "hcCudaGemmSkinnyStatic", "hcCudaSelfTestDeviceTimeout", "hcCudaGemmPush", "hcCudaIpcExport",
     "hcCudaIpcOpen", "hcCudaIpcClose", "hcCudaMap", "hcCudaMapHost",
+    "hcCudaGemmHostDeviceA",
 )
 
 
@@ -168,6 +169,7 @@ def library() -> ctypes.CDLL:
         lib.hcCudaGemmPlan.argtypes = [ctypes.POINTER(_GemmArgs), i, ctypes.POINTER(_PlanInfo)]
         lib.hcCudaGemm.argtypes = [vp, ctypes.POINTER(_GemmArgs)]
         lib.hcCudaGemmHost.argtypes = [vp, ctypes.POINTER(_GemmArgs)]
+        lib.hcCudaGemmHostDeviceA.argtypes = [vp, ctypes.POINTER(_GemmArgs)]
         lib.hcCudaEventCreate.argtypes = [vp, pvp]
         lib.hcCudaEventDestroy.argtypes = [vp, vp]
         lib.hcCudaEventRecord.argtypes = [vp, vp]
@@ -417,6 +419,20 @@ class Context:
     def ipc_close(self, ptr: int) -> None:
         if ptr:
             self._check(self._lib.hcCudaIpcClose(self._handle, ptr))
+
+    def gemm_host_device_a(self, a: "DeviceBuffer", b: np.ndarray, c: np.ndarray, *,
+                           b_transposed: bool = False, epilogue: Sequence[tuple] = (),
+                           bias: np.ndarray | None = None) -> None:
+        """C = A @ B with A resident on the device and B, C host arrays (row-major): B travels in
+        column panels while earlier panels are multiplied and their columns of C travel back."""
+        m, k = a.shape
+        n = b.shape[0] if b_transposed else b.shape[1]
+        b_rows, b_cols = b.shape
+        args = _gemm_args(m, n, k, a.dtype, a.ptr, a.ld, b.ctypes.data,
+                          b.strides[0] // b.itemsize if b_rows > 1 else max(b_cols, 1), c.ctypes.data,
+                          c.strides[0] // c.itemsize if m > 1 else max(n, 1), VARIANT_AUTO, b_transposed, False,
+                          epilogue, None if bias is None else bias.ctypes.data, c.dtype)
+        self._check(self._lib.hcCudaGemmHostDeviceA(self._handle, ctypes.byref(args)))
 
     def map(self, x: "DeviceBuffer", out: "DeviceBuffer", ops: Sequence[tuple], *,
             other: "DeviceBuffer | None" = None) -> None:

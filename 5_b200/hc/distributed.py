@@ -18,7 +18,8 @@ from typing import Any
 
 import numpy as np
 
-__all__ = ["ColumnSlab", "PushedMatmul", "ShardedMatmul", "assemble_row_major", "column_slab", "init_communicator"]
+__all__ = ["ColumnSlab", "PushedMatmul", "ShardedMatmul", "assemble_row_major", "column_slab", "init_communicator",
+           "row_shard"]
 
 
 @dataclass(frozen=True)
@@ -54,6 +55,12 @@ def column_slab(n: int, world_size: int, rank: int, *, align: int = 1) -> Column
     return ColumnSlab(rank, world_size, begin, end)
 
 
+def row_shard(m: int, world_size: int, rank: int) -> ColumnSlab:
+    """Rows [begin, end) of A that rank `rank` uploads from the host when the ranks share that work
+    (`ShardedMatmul.host_product`): equal, contiguous shares when `world_size` divides `m`."""
+    return column_slab(m, world_size, rank, align=1)
+
+
 def init_communicator(ctx: Any, world_size: int, rank: int,
                       broadcast: Callable[[bytes | None], bytes]) -> None:
     """Joins `ctx` to a NCCL communicator of `world_size` ranks.
@@ -79,6 +86,7 @@ class ShardedMatmul:
         self.slab = column_slab(n, world_size, rank, align=align)
         self.world_size = world_size
         self.rank = rank
+        self._device_a: Any = None  # A gathered on the device, kept between host_product calls
 
     def upload(self, a: np.ndarray, b: np.ndarray) -> tuple[Any, Any, Any]:
         """Device copies of A (whole), this rank's slab of B, and an empty slab of C."""
@@ -94,6 +102,36 @@ class ShardedMatmul:
         """C slab = A @ B slab (asynchronous on the rank's stream)."""
         if self.slab.width:
             self.ctx.gemm(da, db_slab, dc_slab)
+
+    def host_product(self, a: np.ndarray, b_slab: np.ndarray, c_slab: np.ndarray) -> None:
+        """C slab = A @ B slab from host arrays, without sending A over PCIe once per rank.
+
+        `a` is the whole row-major A as this rank's host sees it; the rank uploads only its share
+        of the rows (`row_shard`), the ranks exchange the shares over NVLink with one in-place
+        all-gather (the context must have joined the communicator, `init_communicator`), and the
+        gathered A is multiplied with the rank's own slab of B, which travels in column panels
+        while earlier panels are multiplied and their columns of C travel back
+        (`hcCudaGemmHostDeviceA`). Collective: every rank calls it for every product. Returns when
+        this rank's `c_slab` is complete. Page-locked arrays make the copies asynchronous."""
+        m, k = a.shape
+        if b_slab.shape != (k, self.slab.width) or c_slab.shape != (m, self.slab.width):
+            raise ValueError("b_slab / c_slab do not match this rank's column slab")
+        if self._device_a is None or self._device_a.shape != (m, k) or self._device_a.dtype != a.dtype:
+            if self._device_a is not None:
+                self._device_a.free()
+            self._device_a = self.ctx.empty((m, k), a.dtype)
+        da = self._device_a
+        share = row_shard(m, self.world_size, self.rank)
+        if m % self.world_size == 0 and self.world_size > 1:
+            mine = da.window(share.begin, share.end, 0, k)
+            mine.copy_from_host(a[share.begin : share.end])
+            self.ctx.all_gather(mine, da)  # in place: the send buffer is this rank's part of `da`
+        else:
+            da.copy_from_host(a)  # shares of unequal size: every rank sends the whole of A
+        if self.slab.width:
+            self.ctx.gemm_host_device_a(da, b_slab, c_slab)
+        else:
+            self.ctx.synchronize()
 
     def all_gather(self, dc_slab: Any, gathered: Any) -> None:
         """Gathers equal-width C slabs into `gathered`, shape (world_size, M, slab width)."""

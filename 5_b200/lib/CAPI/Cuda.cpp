@@ -1243,6 +1243,108 @@ int hcCudaGemmHost(HcCudaContext *ctx, const HcCudaGemmArgs *args) {
   return finish();
 }
 
+int hcCudaGemmHostDeviceA(HcCudaContext *ctx, const HcCudaGemmArgs *args) {
+  if (ctx == nullptr)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "ctx must not be null");
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  HcCudaGemmPlanInfo plan;
+  if (int rc = plan_gemm(ctx, args, ctx->prop.multiProcessorCount, true, &plan))
+    return rc;
+  if (plan.variant == HC_CUDA_GEMM_NOOP)
+    return HC_CUDA_OK;
+  if (args->accumulate != 0 || hc::sm100::dtype_is_8bit(args->dtype) || args->k == 0)
+    return fail(ctx, HC_CUDA_ERR_UNSUPPORTED, "hcCudaGemmHostDeviceA computes C = ops(A*B) for float16 / bfloat16 "
+                                              "operands with k > 0 (no accumulate, no 8-bit operands)");
+  if ((reinterpret_cast<uintptr_t>(args->a) & 15) != 0 || (args->lda & 7) != 0)
+    return fail(ctx, HC_CUDA_ERR_UNSUPPORTED, "the device-resident a must be 16-byte aligned with lda a multiple of 8");
+  const size_t m = static_cast<size_t>(args->m), n = static_cast<size_t>(args->n), k = static_cast<size_t>(args->k);
+  const size_t ce = args->c_dtype == HC_CUDA_C_F32 ? 4 : 2;
+  char *const host_c = static_cast<char *>(args->c);
+  const size_t host_c_pitch = static_cast<size_t>(args->ldc) * ce;
+  HC_TRY_CUDA(ctx, cudaSetDevice(ctx->device));
+  bool has_bias = false;
+  for (int i = 0; i < args->epilogue_count; ++i)
+    has_bias = has_bias || args->epilogue_kind[i] == HC_CUDA_EPILOGUE_BIAS_COLUMN;
+  const bool b_nk = args->b_layout == HC_CUDA_B_NK;
+  const size_t b_rows = b_nk ? n : k, b_cols = b_nk ? k : n;  // B as stored
+  const size_t ldb = static_cast<size_t>(round_up(static_cast<int64_t>(b_cols), kRepackPitchBytes / 2));
+  const size_t ldc = static_cast<size_t>(round_up(args->n, 16 / static_cast<int64_t>(ce)));
+  if (int rc = ensure_stage(ctx, 1, b_rows * ldb * 2))
+    return rc;
+  if (int rc = ensure_stage(ctx, 2, round_up(static_cast<int64_t>(m * ldc * ce), 16) + (has_bias ? n * 4 : 0)))
+    return rc;
+  if (int rc = ensure_copy_streams(ctx))
+    return rc;
+  HcCudaGemmArgs dev = *args;
+  char *const dev_c = static_cast<char *>(ctx->stage[2]);
+  dev.b = ctx->stage[1];
+  dev.ldb = static_cast<int64_t>(ldb);
+  dev.c = dev_c;
+  dev.ldc = static_cast<int64_t>(ldc);
+  if (has_bias) {
+    float *bias_dev = reinterpret_cast<float *>(dev_c + round_up(static_cast<int64_t>(m * ldc * ce), 16));
+    dev.bias = bias_dev;
+    HC_TRY_CUDA(ctx, cudaMemcpyAsync(bias_dev, args->bias, n * 4, cudaMemcpyHostToDevice, ctx->stream));
+  }
+  HC_TRY_CUDA(ctx, cudaEventRecord(ctx->fence_event, ctx->stream));
+  HC_TRY_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_in, ctx->fence_event, 0));
+  HC_TRY_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_out, ctx->fence_event, 0));
+  struct Drain {  // no copy may still touch the caller's arrays when the call returns
+    HcCudaContext *ctx;
+    ~Drain() {
+      for (cudaStream_t s : {ctx->copy_in, ctx->copy_out, ctx->stream})
+        if (cudaStreamSynchronize(s) != cudaSuccess)
+          cudaGetLastError();
+    }
+  } drain{ctx};
+  struct PanelsPlanning {  // the sub-products are planned without k-splits: the bits of one launch
+    HcCudaContext *ctx;
+    explicit PanelsPlanning(HcCudaContext *c) : ctx(c) { ctx->planning_host_panels = true; }
+    ~PanelsPlanning() { ctx->planning_host_panels = false; }
+  } planning_guard(ctx);
+  // Column panels of B (multiples of 256 columns, at most kMaxPanels): panel p + 1 arrives while
+  // panel p is multiplied and the columns of C of panel p - 1 leave.
+  size_t panel_cols = (n + HcCudaContext::kMaxPanels - 1) / HcCudaContext::kMaxPanels;
+  panel_cols = static_cast<size_t>(round_up(static_cast<int64_t>(panel_cols), 256));
+  if (plan.variant != HC_CUDA_GEMM_DENSE || n < 1024)
+    panel_cols = n;
+  int panel = 0;
+  for (size_t col0 = 0; col0 < n; ++panel) {
+    size_t cols = n - col0 < panel_cols + 256 ? n - col0 : panel_cols;
+    if (b_nk)
+      HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(static_cast<char *>(ctx->stage[1]) + col0 * ldb * 2, ldb * 2,
+                                         static_cast<const char *>(args->b) + col0 * static_cast<size_t>(args->ldb) * 2,
+                                         static_cast<size_t>(args->ldb) * 2, k * 2, cols, cudaMemcpyHostToDevice,
+                                         ctx->copy_in));
+    else
+      HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(static_cast<char *>(ctx->stage[1]) + col0 * 2, ldb * 2,
+                                         static_cast<const char *>(args->b) + col0 * 2,
+                                         static_cast<size_t>(args->ldb) * 2, cols * 2, k, cudaMemcpyHostToDevice,
+                                         ctx->copy_in));
+    HC_TRY_CUDA(ctx, cudaEventRecord(ctx->panel_in[panel], ctx->copy_in));
+    HC_TRY_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->panel_in[panel], 0));
+    HcCudaGemmArgs part = dev;
+    part.n = static_cast<int64_t>(cols);
+    part.b = static_cast<const char *>(dev.b) + (b_nk ? col0 * ldb : col0) * 2;
+    part.c = dev_c + col0 * ce;
+    if (has_bias)
+      part.bias = dev.bias + col0;
+    HcCudaGemmPlanInfo part_plan;
+    if (int rc = plan_gemm(ctx, &part, ctx->prop.multiProcessorCount, false, &part_plan))
+      return rc;
+    if (int rc = enqueue_gemm(ctx, &part, part_plan))
+      return rc;
+    HC_TRY_CUDA(ctx, cudaEventRecord(ctx->panel_done[panel], ctx->stream));
+    HC_TRY_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_out, ctx->panel_done[panel], 0));
+    HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(host_c + col0 * ce, host_c_pitch, part.c, ldc * ce, cols * ce, m,
+                                       cudaMemcpyDeviceToHost, ctx->copy_out));
+    col0 += cols;
+  }
+  HC_TRY_CUDA(ctx, cudaEventRecord(ctx->fence_event, ctx->copy_out));
+  HC_TRY_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->fence_event, 0));
+  return synchronize_locked(ctx);
+}
+
 namespace {
 
 // Validation shared by hcCudaMap and hcCudaMapHost; fills `ops`.

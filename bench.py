@@ -675,14 +675,40 @@ def run_gpu_arm(args, ranks: Ranks) -> None:
     pb[...] = host_b
     pc[...] = 0
     call_args = (pa, pb, pc) if bias is None else (pa, pb, pc, bias)
-    handle(*call_args)  # warm-up: allocates the context's staging buffers
-    default_ctx = cuda.default_context(ranks.local_rank)
-    e0, e1 = default_ctx.event(), default_ctx.event()
+    e2e_api = "hc.compile(kernel, target='nvidia-sm100a')(a, b, c) on pinned NumPy arrays"
+    e2e_h2d_a = a.nbytes
+    comm_ready = False
+    if ranks.world > 1:
+        # The sharded product from host arrays: every rank holds A in host memory but uploads only
+        # its share of the rows; the shares are exchanged over NVLink instead of crossing PCIe once
+        # per rank. Needs the NCCL communicator the gather leg uses as well.
+        try:
+            from hc.distributed import ShardedMatmul
+
+            init_communicator(ctx, ranks.world, ranks.rank, ranks.broadcast_bytes)
+            comm_ready = True
+            sharded_host = ShardedMatmul(handle, ctx, w.n, ranks.world, ranks.rank,
+                                         align=workloads.SHARDED_BLOCK_COLUMNS)
+            e2e_call = lambda: sharded_host.host_product(pa, pb, pc)  # noqa: E731
+            e2e_ctx = ctx
+            e2e_api = ("hc.distributed.ShardedMatmul.host_product(a, b_slab, c_slab) on pinned NumPy arrays: each "
+                       "rank uploads 1/N of A's rows, the shares are exchanged over NVLink (NCCL all-gather), the "
+                       "B slab travels in column panels while earlier panels are multiplied and sent back")
+            e2e_h2d_a = a.nbytes // ranks.world if m % ranks.world == 0 else a.nbytes
+        except Exception as exc:
+            e2e_api += f" (sharded host path unavailable: {type(exc).__name__}: {exc})"
+            e2e_call = lambda: handle(*call_args)  # noqa: E731
+            e2e_ctx = cuda.default_context(ranks.local_rank)
+    else:
+        e2e_call = lambda: handle(*call_args)  # noqa: E731
+        e2e_ctx = cuda.default_context(ranks.local_rank)
+    e2e_call()  # warm-up: allocates the context's staging buffers
+    e0, e1 = e2e_ctx.event(), e2e_ctx.event()
     ranks.barrier()
-    default_ctx.synchronize()
+    e2e_ctx.synchronize()
     e0.record()
     for _ in range(e2e_steps):
-        handle(*call_args)
+        e2e_call()
     e1.record()
     e2e_ms = ranks.max(e1.elapsed_ms_since(e0)) / e2e_steps
     if contract.accumulate:  # the host C has taken the product 1 + e2e_steps times
@@ -695,17 +721,18 @@ def run_gpu_arm(args, ranks: Ranks) -> None:
             scale = float(np.abs(c[rows].astype(np.float64)).max())
             e2e_ok = bool(np.allclose(pc[rows].astype(np.float64), c[rows].astype(np.float64), rtol=1e-4,
                                       atol=1e-5 * max(scale, 1.0)))
-    h2d_bytes = a.nbytes + b.nbytes + (pc.nbytes if contract.accumulate else 0) + (0 if bias is None else bias.nbytes)
+    h2d_bytes = e2e_h2d_a + b.nbytes + (pc.nbytes if contract.accumulate else 0) + (0 if bias is None else bias.nbytes)
     e2e = {"value": total_flops / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_ms,
            "steps": e2e_steps, "h2d_bytes_per_step": int(h2d_bytes),
            "d2h_bytes_per_step": int(pc.nbytes), "matches_device_path": e2e_ok,
-           "api": "hc.compile(kernel, target='nvidia-sm100a')(a, b, c) on pinned NumPy arrays"}
+           "api": e2e_api}
 
     # ---- optional all-gather of the C slabs (N > 1), reported separately ---------------------
     gather = None
     if ranks.world > 1 and not args.no_gather:
         try:
-            init_communicator(ctx, ranks.world, ranks.rank, ranks.broadcast_bytes)
+            if not comm_ready:
+                init_communicator(ctx, ranks.world, ranks.rank, ranks.broadcast_bytes)
             gathered = ctx.empty((ranks.world, m, local_n), np.float32)
             g0, g1 = ctx.event(), ctx.event()
             ctx.all_gather(dc, gathered)
@@ -723,6 +750,12 @@ def run_gpu_arm(args, ranks: Ranks) -> None:
             ctx.comm_destroy()
         except Exception as exc:
             gather = {"error": f"{type(exc).__name__}: {exc}"}
+
+    if comm_ready and (args.no_gather or (gather is not None and "error" in gather)):
+        try:
+            ctx.comm_destroy()
+        except Exception:
+            pass
 
     # ---- the same product with the gather fused into the epilogue (N > 1) ------------------
     fused = None

@@ -251,6 +251,16 @@ HC_CUDA_CAPI_EXPORTED int hcCudaGemm(HcCudaContext *ctx, const HcCudaGemmArgs *a
  * asynchronous and about twice as fast. */
 HC_CUDA_CAPI_EXPORTED int hcCudaGemmHost(HcCudaContext *ctx, const HcCudaGemmArgs *args);
 
+/* Synchronous. hcCudaGemmHost for a caller whose A already lives on the device: `a` is a device
+ * pointer (16-byte aligned, lda a multiple of 8 elements), b and c are host pointers. B travels
+ * in column panels, each panel's columns of C are multiplied as it arrives and leave while the
+ * next panel arrives. This is the per-rank call of the N-sharded product from host arrays: every
+ * rank uploads only its share of A's rows, the ranks exchange the shares over NVLink
+ * (hcCudaCommAllGather), and each multiplies the gathered A with its own column slab of B.
+ * float16 / bfloat16 operands, k > 0, no accumulate. No counterpart in the reference (its only
+ * launch is the single-process hc.simulator.launch, hc/simulator.py:165-186). */
+HC_CUDA_CAPI_EXPORTED int hcCudaGemmHostDeviceA(HcCudaContext *ctx, const HcCudaGemmArgs *args);
+
 /* ---- the masked element-wise map ---------------------------------------------------------- */
 
 /* Operations of hcCudaMap, applied in order to every element: with a float32 constant, or with the

@@ -109,6 +109,55 @@ def _rank_main(rank: int, world: int, port: int, out_dir: str) -> None:
         a, b_slab = workloads.make_sharded_inputs(slab.begin, slab.end, m=m, k=k)
         c_slab = cpu_ref.matmul_k_ascending(a, b_slab, threads=1)
         np.save(os.path.join(out_dir, f"c_{rank}.npy"), c_slab)
+
+        # host_product's plumbing on stand-in device memory: the rank uploads only its rows of A,
+        # the in-place all-gather (here over gloo) completes A, the slab product follows.
+        import torch
+
+        from hc.distributed import ShardedMatmul, row_shard
+
+        class Buffer:
+            def __init__(self, array, row0=0):
+                self.array, self.row0 = array, row0
+                self.shape, self.dtype = array.shape, array.dtype
+
+            def window(self, r0, r1, c0, c1):
+                return Buffer(self.array[r0:r1, c0:c1], r0)
+
+            def copy_from_host(self, host):
+                self.array[...] = host
+
+            def free(self):
+                pass
+
+        class Device(_FakeContext):
+            uploads = 0
+
+            def empty(self, shape, dtype):
+                return Buffer(np.full(shape, 7, dtype))
+
+            def all_gather(self, send, recv):
+                assert send.array.base is not None and np.shares_memory(send.array, recv.array)  # in place
+                Device.uploads += send.array.shape[0]
+                parts = [torch.zeros(send.shape, dtype=torch.float16) for _ in range(world)]
+                dist.all_gather(parts, torch.from_numpy(np.ascontiguousarray(send.array)))
+                recv.array[...] = np.concatenate([p.numpy() for p in parts])
+
+            def gemm_host_device_a(self, da, b, c):
+                c[...] = cpu_ref.matmul_k_ascending(da.array, b, threads=1)
+
+            def synchronize(self):
+                pass
+
+        device = Device()
+        sharded = ShardedMatmul(None, device, n, world, rank, align=2048)
+        out = np.zeros((m, slab.width), np.float32)
+        scrambled = a.copy()
+        share = row_shard(m, world, rank)
+        scrambled[: share.begin] = 0  # rows of other ranks must come from them, not from this host copy
+        scrambled[share.end :] = 0
+        sharded.host_product(scrambled, b_slab, out)
+        assert Device.uploads == m // world and np.array_equal(out, c_slab)
         dist.barrier()
     finally:
         dist.destroy_process_group()
@@ -132,6 +181,8 @@ def test_sharded_matmul_checks_its_inputs() -> None:
     assert (sharded.slab.begin, sharded.slab.end) == (2048, 4096)
     with pytest.raises(ValueError, match="columns"):
         sharded.upload(np.zeros((4, 4), np.float16), np.zeros((4, 100), np.float16))
+    with pytest.raises(ValueError, match="do not match this rank's column slab"):
+        sharded.host_product(np.zeros((4, 8), np.float16), np.zeros((8, 100), np.float16), np.zeros((4, 100), np.float32))
     uneven = ShardedMatmul(handle=None, ctx=None, n=3073, world_size=2, rank=0, align=256)
     with pytest.raises(ValueError, match="equal slabs"):
         uneven.all_gather(None, None)

@@ -59,6 +59,22 @@ def _rank_main(rank: int, world: int, out_dir: str) -> None:
     sharded.all_gather(dc, gathered)
     ctx.synchronize()
     np.save(Path(out_dir) / f"gathered_{rank}.npy", gathered.to_numpy())
+    # The same slab from host arrays: each rank uploads half of A's rows, the halves are exchanged
+    # over NVLink, B travels in column panels. A larger problem so that the panel pipeline runs.
+    big_m, big_k = 2048, 1024
+    big_a, big_b = workloads.make_sharded_inputs(sharded.slab.begin, sharded.slab.end, m=big_m, k=big_k)
+    pa, pb = cuda.pinned_empty(big_a.shape, big_a.dtype), cuda.pinned_empty(big_b.shape, big_b.dtype)
+    pa[...], pb[...] = big_a, big_b
+    pc = cuda.pinned_empty((big_m, sharded.slab.width), np.float32)
+    pc[...] = np.nan
+    for _ in range(2):  # the gathered A is kept between calls
+        sharded.host_product(pa, pb, pc)
+    np.save(Path(out_dir) / f"host_slab_{rank}.npy", np.array(pc))
+    dbig_a, dbig_b = ctx.to_device(big_a), ctx.to_device(big_b)
+    dbig_c = ctx.empty((big_m, sharded.slab.width), np.float32)
+    sharded.run(dbig_a, dbig_b, dbig_c)
+    ctx.synchronize()
+    np.save(Path(out_dir) / f"device_slab_{rank}.npy", dbig_c.to_numpy())
     ctx.comm_destroy()
 
     # The same product with the gather fused into the epilogue: tiles are pushed into every
@@ -129,3 +145,7 @@ def test_two_gpus_shard_and_gather(tmp_path) -> None:
         assert np.array_equal(full, first)  # every rank holds the same gathered C
         pushed = np.load(tmp_path / f"pushed_{r}.npy")
         assert np.array_equal(pushed, first)  # the fused push yields the same C, row-major, on every rank
+        # The host-array path (rows of A shared out, gathered over NVLink) gives the bits of the
+        # device-buffer product of the same slab.
+        host_slab, device_slab = np.load(tmp_path / f"host_slab_{r}.npy"), np.load(tmp_path / f"device_slab_{r}.npy")
+        assert np.isfinite(host_slab).all() and np.array_equal(host_slab, device_slab)
