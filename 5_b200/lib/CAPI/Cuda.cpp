@@ -121,6 +121,7 @@ struct HcCudaContext {
   cudaEvent_t panel_in[kMaxSteps] = {};
   cudaEvent_t panel_done[kMaxSteps] = {};
   bool planning_host_panels = false;  // plan_gemm then never splits k: see hcCudaGemmHost
+  bool planning_push = false;         // plan_gemm then keeps to the kernels that can push tiles to peers
   cudaEvent_t fence_event = nullptr;
   EncodeTiledFn encode = nullptr;
   int group_n = 8;
@@ -291,7 +292,28 @@ int plan_gemm(const HcCudaContext *ctx, const HcCudaGemmArgs *args, int sm_count
   if (variant == HC_CUDA_GEMM_DENSE) {
     const hc::sm100::DenseTileShape t = hc::sm100::dense_tile_shape();
     const bool pairs = hc::sm100::dense_uses_pairs(m, n, k, sm_count);
-    const int64_t tile_m = pairs ? 2 * t.block_m : t.block_m;
+    // 512x256 tiles for products that fill the GPU with them, when the epilogue never has to read C
+    // with ordinary loads (an accumulation must be one the TMA stores can perform) and the tiles go
+    // nowhere but C. Decided again below if tiles turn out to be split over k.
+    const bool c_tma_ok = (static_cast<size_t>(args->ldc) * c_elem) % 16 == 0 &&
+                          (reinterpret_cast<uintptr_t>(args->c) & 15) == 0 && (ctx == nullptr || ctx->c_tma_store);
+    bool wide = pairs && hc::sm100::dense_uses_wide(m, n, k, sm_count) &&
+                (args->accumulate == 0 || (c_tma_ok && args->epilogue_count == 0)) &&
+                !(ctx != nullptr && ctx->planning_push);
+    int64_t tile_m = wide ? hc::sm100::kDenseWideTileM : (pairs ? 2 * t.block_m : t.block_m);
+    if (wide) {
+      const int64_t wide_tiles = ((m + tile_m - 1) / tile_m) * ((n + t.block_n - 1) / t.block_n);
+      const int wide_kb = static_cast<int>((k + 64 * (2 / es) - 1) / (64 * (2 / es)));
+      long long ignored = 0;
+      const bool forced_split = std::getenv("HC_CUDA_DENSE_SPLITS") != nullptr;
+      const char *forced_wide = std::getenv("HC_CUDA_DENSE_WIDE");  // "1": the tuning aid also rules out splits
+      const bool keep_wide = forced_wide != nullptr && std::strcmp(forced_wide, "1") == 0;
+      if (forced_split || (!keep_wide && !(ctx != nullptr && ctx->planning_host_panels) &&
+                           hc::sm100::dense_choose_splits(wide_tiles, sm_count / 2, wide_kb, &ignored) > 1)) {
+        wide = false;
+        tile_m = 2 * t.block_m;
+      }
+    }
     plan->tiles_m = static_cast<int32_t>((m + tile_m - 1) / tile_m);
     plan->tiles_n = static_cast<int32_t>((n + t.block_n - 1) / t.block_n);
     const int64_t tiles = static_cast<int64_t>(plan->tiles_m) * plan->tiles_n;
@@ -299,7 +321,7 @@ int plan_gemm(const HcCudaContext *ctx, const HcCudaGemmArgs *args, int sm_count
       return fail(ctx, HC_CUDA_ERR_UNSUPPORTED, "too many tiles");
     // Tiles that do not fill a round of the persistent CTAs (all of them, or the last round's) are
     // split over k when k is long enough.
-    const int block_k = hc::sm100::dense_block_k(pairs) * static_cast<int>(2 / es);  // a stage holds the same bytes
+    const int block_k = (wide ? 64 : hc::sm100::dense_block_k(pairs)) * static_cast<int>(2 / es);  // same bytes per stage
     const int num_kb = static_cast<int>((k + block_k - 1) / block_k);
     const int slots = pairs ? sm_count / 2 : sm_count;
     long long first_split_tile = 0;
@@ -560,7 +582,14 @@ int enqueue_gemm(HcCudaContext *ctx, const HcCudaGemmArgs *args, const HcCudaGem
                               static_cast<uint64_t>(t.block_n) * 4, 32, 32))
         return rc;
     }
-    if (pairs) {
+    // (plan_gemm chose 512x256 tiles iff it counted the rows of C in tiles of 512.)
+    const bool wide = pairs && m >= 2 * hc::sm100::kDenseWideTileM && plan.splits == 1 &&
+                      plan.tiles_m == (m + hc::sm100::kDenseWideTileM - 1) / hc::sm100::kDenseWideTileM;
+    if (wide) {
+      HC_TRY_CUDA(ctx, hc::sm100::launch_gemm_dense_wide(tmap_a, tmap_b, args->c, m, n, k, args->ldc, args->dtype,
+                                                         ctx->group_n, plan.grid, b_layout, ep, c_map,
+                                                         ctx->status_dev, ctx->stream));
+    } else if (pairs) {
       HC_TRY_CUDA(ctx, hc::sm100::launch_gemm_dense_pair(tmap_a, tmap_b, args->c, m, n, k, args->ldc,
                                                          args->dtype, ctx->group_n, plan.grid, b_layout, ep,
                                                          c_map, split, &tmap_p, ctx->status_dev, ctx->stream));
@@ -936,8 +965,11 @@ int hcCudaGemmPush(HcCudaContext *ctx, const HcCudaGemmArgs *args, float *const 
   if (dense.c_dtype != HC_CUDA_C_F32 && n_targets > 0)
     return fail(ctx, HC_CUDA_ERR_UNSUPPORTED, "pushing C to other buffers needs a float32 C");
   HcCudaGemmPlanInfo plan;
-  if (int rc = plan_gemm(ctx, &dense, ctx->prop.multiProcessorCount, false, &plan))
-    return rc;
+  ctx->planning_push = n_targets > 0;
+  const int plan_rc = plan_gemm(ctx, &dense, ctx->prop.multiProcessorCount, false, &plan);
+  ctx->planning_push = false;
+  if (plan_rc)
+    return plan_rc;
   hc::sm100::Epilogue push{};
   if (plan.variant == HC_CUDA_GEMM_DENSE && n_targets > 0) {
     if ((dense.ldc & 3) != 0 || (reinterpret_cast<uintptr_t>(dense.c) & 15) != 0)  // (float32 C here)

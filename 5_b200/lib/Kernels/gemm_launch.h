@@ -123,6 +123,17 @@ cudaError_t launch_gemm_dense_pair(const CUtensorMap &tmap_a, const CUtensorMap 
                                    const SplitK &split, const CUtensorMap *tmap_partials, int *status,
                                    cudaStream_t stream);
 
+// The pair kernel's big brother: 512x256 tiles per pair (a 256x256 accumulator per CTA, all of its
+// tensor memory), a quarter fewer operand bytes per flop, no overlap of epilogue and next k-loop.
+// For launches whose epilogue never reads C with ordinary loads (stores, element-wise work, 16-bit
+// C, accumulation by TMA additions), without split-k and without push targets.
+cudaError_t launch_gemm_dense_wide(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, void *c, int m, int n,
+                                   int k, long long ldc, int dtype, int group_n, int max_ctas, int b_layout,
+                                   const Epilogue &ep, const CUtensorMap *tmap_c, int *status, cudaStream_t stream);
+// Whether a product of this shape is large enough for the 512x256 tiles to pay.
+bool dense_uses_wide(long long m, long long n, long long k, int sm_count);
+constexpr int kDenseWideTileM = 512;
+
 // Whether the dense variant runs on CTA pairs for this problem.
 bool dense_uses_pairs(long long m, long long n, long long k, int sm_count);
 

@@ -507,6 +507,8 @@ class DeviceRun:
     def kernel_name(self) -> str:
         if self.plan.variant == "skinny":
             return "gemm_skinny_kernel"
+        if self.m >= 1024 and self.plan.tiles_m == -(-self.m // 512):
+            return "gemm_dense_wide_kernel"
         pairs = self.m > 128 and self.plan.tiles_m == -(-self.m // 256)
         return "gemm_dense_pair_kernel" if pairs else "gemm_dense_kernel"
 

@@ -57,7 +57,15 @@ def test_missing_device_is_reported_not_papered_over() -> None:
 
 def test_plan_chooses_variants() -> None:
     dense = cuda.plan_gemm(8192, 8192, 8192, "float16")
-    assert (dense.variant, dense.tiles_m, dense.tiles_n, dense.grid, dense.splits) == ("dense", 32, 32, 148, 1)  # 256x256 pair tiles
+    assert (dense.variant, dense.tiles_m, dense.tiles_n, dense.grid, dense.splits) == ("dense", 16, 32, 148, 1)  # 512x256 tiles
+    # The 512x256 tiles need a long k-loop, several rounds of tiles, and an epilogue that never reads C
+    # with ordinary loads; otherwise the 256x256 pair tiles (or 128x256 single-CTA tiles) run.
+    assert cuda.plan_gemm(8192, 8192, 512, "float16").tiles_m == 32
+    assert cuda.plan_gemm(4096, 4096, 4096, "float16").tiles_m == 16
+    assert cuda.plan_gemm(8192, 8192, 8192, "float16", accumulate=True).tiles_m == 16
+    assert cuda.plan_gemm(8192, 8192, 8192, "float16", accumulate=True, epilogue=(("scale", 2.0),)).tiles_m == 32
+    assert cuda.plan_gemm(8192, 8192, 8192, "float16", accumulate=True, ldc=8193).tiles_m == 32
+    assert cuda.plan_gemm(8192, 8192, 8192, "float16", ldc=8193).tiles_m == 16
     assert dense.kernel_launches == 1 and dense.scratch_bytes == 0 and not dense.repack_a
     small = cuda.plan_gemm(100, 300, 64, "bfloat16")
     assert (small.variant, small.tiles_m, small.tiles_n, small.grid) == ("dense", 1, 2, 2)

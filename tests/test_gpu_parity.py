@@ -117,6 +117,63 @@ def test_b_stored_transposed(shape: tuple[int, int, int], dtype: str) -> None:
     assert_close_to_oracle(c, a, b)
 
 
+WIDE_SHAPES = [(512, 256, 64), (513, 257, 130), (1100, 700, 300), (1024, 1024, 2048), (2500, 3000, 520), (300, 5000, 1000)]
+
+
+@pytest.mark.parametrize("shape", WIDE_SHAPES)
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16", "float8_e4m3fn"])
+def test_dense_wide_tiles(shape, dtype: str, gpu_ctx, monkeypatch) -> None:
+    """The 512x256-tile kernel, forced onto shapes far smaller than it is chosen for so that edge
+    tiles on every axis, a second accumulator half that lies wholly outside C, both layouts of B,
+    fused operations, a 16-bit C and accumulation by TMA additions all run through it."""
+    monkeypatch.setenv("HC_CUDA_DENSE_WIDE", "1")
+    m, n, k = shape
+    assert gpu_ctx.plan(m, n, k, dtype).tiles_m == -(-m // 512)
+    a, b = float8_inputs(m, n, k, dtype) if dtype.startswith("float8") else random_inputs(m, n, k, dtype, scale=0.25)
+    expect = cpu_ref.matmul_k_ascending(a, b)
+    da, db, dbt = gpu_ctx.to_device(a), gpu_ctx.to_device(b), gpu_ctx.to_device(np.ascontiguousarray(b.T))
+    guard = 3
+    raw = cuda.DeviceBuffer(gpu_ctx, (m + 2 * guard, n + 8), np.float32)
+    raw.fill_bytes(0xFF)
+    dc = raw.window(guard, guard + m, 4, 4 + n)  # 16-byte aligned rows: the TMA-store path
+    gpu_ctx.gemm(da, db, dc)
+    gpu_ctx.synchronize()
+    whole = raw.to_numpy()
+    c = whole[guard : guard + m, 4 : 4 + n]
+    assert_close_to_oracle(np.ascontiguousarray(c), a, b, expect=expect)
+    whole[guard : guard + m, 4 : 4 + n] = np.nan
+    assert np.isnan(whole).all()  # nothing written outside C
+    dct = gpu_ctx.empty((m, n), np.float32)
+    gpu_ctx.gemm(da, dbt, dct, b_transposed=True)
+    gpu_ctx.synchronize()
+    assert np.array_equal(dct.to_numpy(), c)
+    odd = cuda.DeviceBuffer(gpu_ctx, (m, n), np.float32, ld=n + 1)  # ordinary stores
+    gpu_ctx.gemm(da, db, odd)
+    gpu_ctx.synchronize()
+    assert np.array_equal(odd.to_numpy(), c)
+    bias = np.random.default_rng(4).standard_normal(n).astype(np.float32)
+    dbias = gpu_ctx.to_device(bias)
+    ops = (("scale", 0.5), ("bias",), ("max", 0.0))
+    gpu_ctx.gemm(da, db, dct, epilogue=ops, bias=dbias)
+    gpu_ctx.synchronize()
+    assert_fused_close(dct.to_numpy(), a, b, epilogue=ops, bias=bias)
+    c0 = np.random.default_rng(5).standard_normal((m, n)).astype(np.float32)
+    dct.copy_from_host(c0)
+    gpu_ctx.gemm(da, db, dct, accumulate=True)  # performed by the TMA stores
+    gpu_ctx.synchronize()
+    assert_fused_close(dct.to_numpy(), a, b, c0=c0)
+    half = gpu_ctx.empty((m, n), np.float16)
+    gpu_ctx.gemm(da, db, half)
+    gpu_ctx.synchronize()
+    assert np.array_equal(half.to_numpy(), c.astype(np.float16))
+    monkeypatch.setenv("HC_CUDA_DENSE_WIDE", "0")
+    gpu_ctx.gemm(da, db, dct)
+    gpu_ctx.synchronize()
+    assert_close_to_oracle(dct.to_numpy(), a, b, expect=expect)  # the 256x256 tiles, for comparison
+    for buf in (da, db, dbt, raw, dct, odd, dbias, half):
+        buf.free()
+
+
 FLOAT8_SHAPES = [
     # dense on single CTAs and CTA pairs, skinny with and without split-k; k below, at and across the
     # 128-element stage of the 8-bit kernels; odd pitches (repack) and aligned ones

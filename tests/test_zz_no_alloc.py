@@ -23,12 +23,12 @@ from hc import cuda
 pytestmark = pytest.mark.gpu
 
 
-def _static_gemm(a_dev, b_dev, c_dev, m: int, n: int, k: int, dtype) -> None:
+def _static_gemm(a_dev, b_dev, c_dev, m: int, n: int, k: int, dtype, stream=None, synchronize: int = 1) -> None:
     lib = cuda.library()
     args = cuda._GemmArgs(m, n, k, cuda.dtype_code(dtype), cuda.VARIANT_AUTO,
                           a_dev.ptr, a_dev.ld, b_dev.ptr, b_dev.ld, c_dev.ptr, c_dev.ld)
     text = ctypes.create_string_buffer(512)
-    status = lib.hcCudaGemmSkinnyStatic(ctypes.byref(args), None, 1, text, len(text))
+    status = lib.hcCudaGemmSkinnyStatic(ctypes.byref(args), stream, synchronize, text, len(text))
     assert status == 0, (lib.hcCudaStatusString(status), text.value)
 
 
@@ -67,6 +67,42 @@ def test_static_scratch_entry_point_matches_the_allocating_one(gpu_ctx) -> None:
             buf.free()
 
 
+def test_static_scratch_entry_point_unsplit_shape_and_a_callers_stream(gpu_ctx) -> None:
+    """The benchmark's skinny shape (no split over k, so only the status word of the array is used)
+    and a split one, enqueued without waiting on a stream the caller owns; a synchronising call on
+    the same stream then finishes the batch, which is also how a device-side timeout would surface.
+    A k == 0 call only clears C and reads no status."""
+    torch = pytest.importorskip("torch")
+    stream = torch.cuda.Stream(device=0)
+    shapes = [(8, 16384, 8192), (8, 4096, 8192)]
+    assert gpu_ctx.plan(*shapes[0], "float16").splits == 1 and gpu_ctx.plan(*shapes[1], "float16").splits > 1
+    results = []
+    for seed, (m, n, k) in enumerate(shapes):
+        a, b = _inputs(m, n, k, 10 + seed)
+        da, db = gpu_ctx.to_device(a), gpu_ctx.to_device(b)
+        expected_dev, got_dev = gpu_ctx.empty((m, n), np.float32), gpu_ctx.empty((m, n), np.float32)
+        gpu_ctx.gemm(da, db, expected_dev)
+        got_dev.fill_bytes(0xFF)
+        gpu_ctx.synchronize()
+        results.append((da, db, expected_dev, got_dev, m, n, k))
+    handle = ctypes.c_void_p(stream.cuda_stream)
+    for da, db, _, got_dev, m, n, k in results:  # same stream: the launches cannot overlap
+        _static_gemm(da, db, got_dev, m, n, k, np.float16, stream=handle, synchronize=0)
+    da, db, _, got_dev, m, n, k = results[-1]
+    _static_gemm(da, db, got_dev, m, n, k, np.float16, stream=handle, synchronize=1)
+    stream.synchronize()
+    for da, db, expected_dev, got_dev, *_ in results:
+        assert np.array_equal(got_dev.to_numpy(), expected_dev.to_numpy())
+    # k == 0: C is cleared, nothing is launched, and a waiting call has no status to report.
+    da, db, _, got_dev, m, n, _ = results[0]
+    for _ in range(2):
+        _static_gemm(da, db, got_dev, m, n, 0, np.float16, stream=handle, synchronize=1)
+    assert not got_dev.to_numpy().any()
+    for da, db, expected_dev, got_dev, *_ in results:
+        for buf in (da, db, expected_dev, got_dev):
+            buf.free()
+
+
 def test_static_scratch_entry_point_rejects_what_does_not_fit(gpu_ctx, monkeypatch) -> None:
     """Rejections happen during validation, before anything is launched, so placeholder
     addresses are safe here."""
@@ -89,4 +125,8 @@ def test_static_scratch_entry_point_rejects_what_does_not_fit(gpu_ctx, monkeypat
                           0x7F8000000000, 256)
     status = lib.hcCudaGemmSkinnyStatic(ctypes.byref(args), None, 1, text, len(text))
     assert status == 2 and b"m <= 64" in text.value
+    args = cuda._GemmArgs(8, 256, 512, cuda.F8E4M3, 0, 0x7F0000000000, 512, 0x7F1000000000, 256,
+                          0x7F8000000000, 256)
+    status = lib.hcCudaGemmSkinnyStatic(ctypes.byref(args), None, 1, text, len(text))
+    assert status == 2 and b"float16 or bfloat16" in text.value
     assert lib.hcCudaGemmSkinnyStatic(None, None, 1, text, len(text)) == 1
