@@ -326,8 +326,9 @@ int plan_gemm(const HcCudaContext *ctx, const HcCudaGemmArgs *args, int sm_count
     const int slots = pairs ? sm_count / 2 : sm_count;
     long long first_split_tile = 0;
     plan->splits = hc::sm100::dense_choose_splits(tiles, slots, num_kb, &first_split_tile);
-    if (ctx != nullptr && ctx->planning_host_panels) {
-      // The panels of one host-buffer product must give the bits of the unsplit product.
+    if (wide || (ctx != nullptr && ctx->planning_host_panels)) {
+      // The 512x256 tiles are never split (they are only kept when no split is wanted), and the
+      // panels of one host-buffer product must give the bits of the unsplit product.
       plan->splits = 1;
       first_split_tile = 0;
     } else if (const char *forced = std::getenv("HC_CUDA_DENSE_SPLITS")) {  // tuning aid: split every tile
