@@ -48,9 +48,9 @@ class MapContract:
     out_param: str               # the buffer that is stored to (may be an input: in place)
     extent: Any                  # symbol name (str) or fixed int extent of all buffers
     group_size: int              # G of the kernel as written (not observable on the GPU)
-    ops: tuple[tuple, ...]       # ("scale", c) ("add", c) ("max", c) ("min", c) ("rsub", c)
-    #                              ("add_other",) ("sub_other",) ("rsub_other",) ("mul_other",)
-    #                              ("max_other",) ("min_other",), applied in order
+    ops: tuple[tuple, ...]       # ("scale", c) ("add", c) ("max", c) ("min", c) ("rsub", c) ("rmax", c)
+    #                              ("rmin", c) ("add_other",) ("sub_other",) ("rsub_other",) ("mul_other",)
+    #                              ("max_other",) ("min_other",) ("rmax_other",) ("rmin_other",), in order
     dtype: str = "float32"
 
 
@@ -91,7 +91,9 @@ def _const(node: ast.AST, consts: dict[str, Any]) -> float | None:
 _BINARY = {ast.Mult: ("scale", "scale", "mul_other", "mul_other"),
            ast.Add: ("add", "add", "add_other", "add_other"),
            ast.Sub: ("add", "rsub", "sub_other", "rsub_other")}  # (v op c, c op v, v op w, w op v)
-_CALLS = {"maximum": ("max", "max_other"), "minimum": ("min", "min_other")}
+# np.maximum / np.minimum return their second operand when neither is greater (zeros of opposite
+# sign), so the operand order is kept: "r..." has the chain as the second operand.
+_CALLS = {"maximum": ("max", "rmax", "max_other", "rmax_other"), "minimum": ("min", "rmin", "min_other", "rmin_other")}
 
 
 class _Expressions:
@@ -119,9 +121,7 @@ class _Expressions:
             func = node.func
             name = func.attr if isinstance(func, ast.Attribute) else (func.id if isinstance(func, ast.Name) else None)
             if name in _CALLS and len(node.args) == 2:
-                with_const, with_other = _CALLS[name]
-                return self._combine(node, node.args[0], node.args[1],
-                                     (with_const, with_const, with_other, with_other), negate_const=False)
+                return self._combine(node, node.args[0], node.args[1], _CALLS[name], negate_const=False)
             if (name == "astype" and isinstance(func, ast.Attribute) and len(node.args) == 1
                     and ast.unparse(node.args[0]).split(".")[-1] == "float32"):
                 return self.chain(func.value)

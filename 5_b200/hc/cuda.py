@@ -77,7 +77,8 @@ class _GemmArgs(ctypes.Structure):
 # Operations of the element-wise map (HcCudaMapOp): with a float32 constant, or with the element of
 # the second input ("..._other").
 MAP_KINDS = {"scale": 1, "add": 2, "max": 3, "min": 4, "rsub": 5, "add_other": 6, "sub_other": 7,
-             "rsub_other": 8, "mul_other": 9, "max_other": 10, "min_other": 11}
+             "rsub_other": 8, "mul_other": 9, "max_other": 10, "min_other": 11, "rmax": 12, "rmin": 13,
+             "rmax_other": 14, "rmin_other": 15}
 MAX_MAP_OPS = 8
 
 

@@ -1395,9 +1395,9 @@ int check_map_args(const HcCudaContext *ctx, const HcCudaMapArgs *args, hc::sm10
   ops->count = args->op_count;
   for (int i = 0; i < args->op_count; ++i) {
     const int kind = args->op_kind[i];
-    if (kind < HC_CUDA_MAP_SCALE || kind > HC_CUDA_MAP_MIN_OTHER)
+    if (kind < HC_CUDA_MAP_SCALE || kind > HC_CUDA_MAP_REVERSE_MIN_OTHER)
       return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "op_kind[%d] is not an HcCudaMapOp (got %d)", i, kind);
-    uses_other = uses_other || kind >= HC_CUDA_MAP_ADD_OTHER;
+    uses_other = uses_other || hc::sm100::map_op_uses_other(kind);
     ops->kind[i] = kind;
     ops->value[i] = args->op_value[i];
   }
@@ -1449,7 +1449,7 @@ int hcCudaMapHost(HcCudaContext *ctx, const HcCudaMapArgs *args) {
   HC_TRY_CUDA(ctx, cudaSetDevice(ctx->device));
   bool two = false;
   for (int i = 0; i < ops.count; ++i)
-    two = two || ops.kind[i] >= HC_CUDA_MAP_ADD_OTHER;
+    two = two || hc::sm100::map_op_uses_other(ops.kind[i]);
   const size_t n = static_cast<size_t>(args->n);
   // Chunks of 4 Mi elements (16 MiB per array): a ring of kMaxSteps device chunks per array, so
   // that chunk i + 1 arrives and chunk i - 1 leaves while chunk i is computed.

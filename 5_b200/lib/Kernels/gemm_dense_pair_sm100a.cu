@@ -33,6 +33,7 @@
 
 #include <cstdlib>
 #include <cstring>
+#include <type_traits>
 
 namespace hc {
 namespace sm100 {
@@ -214,53 +215,62 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (CTA 0) -
     if (lane == 0 && cta_rank == 0) {
-      uint32_t stage = 0, phase = 0;
-      uint32_t iter = 0;
-      bool ok = true;
-      for (int unit = cluster_id; ok && unit < num_units; unit += num_clusters, ++iter) {
-        const DenseUnit u = decode_unit(unit, split);
-        const uint32_t acc = iter & 1u;
-        const uint32_t acc_phase = (iter >> 1) & 1u;
-        if (!mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, abort_flag))
-          break;
-        tcgen05_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + acc * kTileN;
-        const int kb_begin = first_kb(u.part, u.parts), kb_end = first_kb(u.part + 1, u.parts);
-        for (int kb = kb_begin; kb < kb_end; ++kb) {
-          if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
-            ok = false;
+      // The instruction kind (16-bit or 8-bit operands) is a template argument of the whole role
+      // loop, chosen by one branch here.
+      auto mma_role = [&](auto f8) {
+        constexpr bool kF8 = decltype(f8)::value;
+        uint32_t stage = 0, phase = 0;
+        uint32_t iter = 0;
+        bool ok = true;
+        for (int unit = cluster_id; ok && unit < num_units; unit += num_clusters, ++iter) {
+          const DenseUnit u = decode_unit(unit, split);
+          const uint32_t acc = iter & 1u;
+          const uint32_t acc_phase = (iter >> 1) & 1u;
+          if (!mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, abort_flag))
             break;
-          }
           tcgen05_fence_after_sync();
-          const uint32_t a_addr = smem_base + stage * kStageBytes;
-          const uint32_t b_addr = a_addr + kATileBytes;
-          const bool b_kn = b_layout == kBLayoutKN;
+          const uint32_t d_tmem = tmem_base + acc * kTileN;
+          const int kb_begin = first_kb(u.part, u.parts), kb_end = first_kb(u.part + 1, u.parts);
+          for (int kb = kb_begin; kb < kb_end; ++kb) {
+            if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
+              ok = false;
+              break;
+            }
+            tcgen05_fence_after_sync();
+            const uint32_t a_addr = smem_base + stage * kStageBytes;
+            const uint32_t b_addr = a_addr + kATileBytes;
+            const bool b_kn = b_layout == kBLayoutKN;
 #pragma unroll
-          for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
-            // A: one 16 KiB sub-block per 64 k, +32 bytes per 16-wide k-step inside its swizzle
-            // row. B stored [K, N]: k-rows are contiguous across the stage, +2 KiB per k-step;
-            // B stored [N, K]: laid out and advanced exactly like A.
-            const uint64_t a_desc = make_smem_desc_sw128(a_addr + (kk / 4) * kASubBytes, 16, 1024) +
-                                    static_cast<uint64_t>((kk % 4) * 2);
-            const uint64_t b_desc =
-                b_kn ? make_smem_desc_sw128(b_addr, kBChunkBytes, 1024) + static_cast<uint64_t>(kk * 128)
-                     : make_smem_desc_sw128(b_addr + (kk / 4) * kASubBytes, 16, 1024) +
-                           static_cast<uint64_t>((kk % 4) * 2);
-            umma_ss_pair(d_tmem, a_desc, b_desc, idesc, (kb != kb_begin || kk != 0) ? 1u : 0u, static_cast<uint32_t>(elem8));
+            for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
+              // A: one 16 KiB sub-block per 64 k, +32 bytes per 16-wide k-step inside its swizzle
+              // row. B stored [K, N]: k-rows are contiguous across the stage, +2 KiB per k-step;
+              // B stored [N, K]: laid out and advanced exactly like A.
+              const uint64_t a_desc = make_smem_desc_sw128(a_addr + (kk / 4) * kASubBytes, 16, 1024) +
+                                      static_cast<uint64_t>((kk % 4) * 2);
+              const uint64_t b_desc =
+                  b_kn ? make_smem_desc_sw128(b_addr, kBChunkBytes, 1024) + static_cast<uint64_t>(kk * 128)
+                       : make_smem_desc_sw128(b_addr + (kk / 4) * kASubBytes, 16, 1024) +
+                             static_cast<uint64_t>((kk % 4) * 2);
+              umma_ss_pair<kF8>(d_tmem, a_desc, b_desc, idesc, (kb != kb_begin || kk != 0) ? 1u : 0u);
+            }
+            // Hand ring slot `stage` back to both producers.
+            umma_commit_pair(map_to_cta(empty_bar(stage), 0));
+            umma_commit_pair(map_to_cta(empty_bar(stage), 1));
+            if (++stage == kStages) {
+              stage = 0;
+              phase ^= 1u;
+            }
           }
-          // Hand ring slot `stage` back to both producers.
-          umma_commit_pair(map_to_cta(empty_bar(stage), 0));
-          umma_commit_pair(map_to_cta(empty_bar(stage), 1));
-          if (++stage == kStages) {
-            stage = 0;
-            phase ^= 1u;
+          if (ok) {
+            umma_commit_pair(map_to_cta(tmem_full_bar(acc), 0));
+            umma_commit_pair(map_to_cta(tmem_full_bar(acc), 1));
           }
         }
-        if (ok) {
-          umma_commit_pair(map_to_cta(tmem_full_bar(acc), 0));
-          umma_commit_pair(map_to_cta(tmem_full_bar(acc), 1));
-        }
-      }
+      };
+      if (elem8)
+        mma_role(std::true_type{});
+      else
+        mma_role(std::false_type{});
     }
   } else {
     // ------------------------------------------------------------ epilogue ----------

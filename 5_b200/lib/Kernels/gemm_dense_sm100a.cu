@@ -25,6 +25,8 @@
 #include "gemm_launch.h"
 #include "sm100_ptx.cuh"
 
+#include <type_traits>
+
 namespace hc {
 namespace sm100 {
 
@@ -174,51 +176,59 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tmap_a,
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer --------
     if (lane == 0) {
-      uint32_t stage = 0, phase = 0;
-      uint32_t iter = 0;
-      bool ok = true;
-      for (int unit = blockIdx.x; ok && unit < num_units; unit += gridDim.x, ++iter) {
-        const DenseUnit u = decode_unit(unit, split);
-        const uint32_t acc = iter & 1u;
-        const uint32_t acc_phase = (iter >> 1) & 1u;
-        if (!mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, abort_flag))
-          break;
-        tcgen05_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + acc * kBlockN;
-        const int kb_begin = first_kb(u.part, u.parts), kb_end = first_kb(u.part + 1, u.parts);
-        for (int kb = kb_begin; kb < kb_end; ++kb) {
-          if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
-            ok = false;
+      // The instruction kind (16-bit or 8-bit operands) is a template argument of the whole role
+      // loop, chosen by one branch here.
+      auto mma_role = [&](auto f8) {
+        constexpr bool kF8 = decltype(f8)::value;
+        uint32_t stage = 0, phase = 0;
+        uint32_t iter = 0;
+        bool ok = true;
+        for (int unit = blockIdx.x; ok && unit < num_units; unit += gridDim.x, ++iter) {
+          const DenseUnit u = decode_unit(unit, split);
+          const uint32_t acc = iter & 1u;
+          const uint32_t acc_phase = (iter >> 1) & 1u;
+          if (!mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, abort_flag))
             break;
-          }
           tcgen05_fence_after_sync();
-          const uint32_t a_addr = smem_base + stage * kStageBytes;
-          const uint32_t b_addr = a_addr + kATileBytes;
-          // A: K-major, groups of 8 rows are 1024 bytes apart.
-          const uint64_t a_desc = make_smem_desc_sw128(a_addr, 16, 1024);
-          // B stored [K, N]: N-major, 64-column chunks are kBChunkBytes apart, groups of 8 k-rows
-          // 1024. B stored [N, K]: K-major exactly like A.
-          const bool b_kn = b_layout == kBLayoutKN;
-          const uint64_t b_desc = b_kn ? make_smem_desc_sw128(b_addr, kBChunkBytes, 1024)
-                                       : make_smem_desc_sw128(b_addr, 16, 1024);
-          const uint64_t b_step = b_kn ? 128 : 2;  // descriptor units (16 bytes) per 16-wide k-step
+          const uint32_t d_tmem = tmem_base + acc * kBlockN;
+          const int kb_begin = first_kb(u.part, u.parts), kb_end = first_kb(u.part + 1, u.parts);
+          for (int kb = kb_begin; kb < kb_end; ++kb) {
+            if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
+              ok = false;
+              break;
+            }
+            tcgen05_fence_after_sync();
+            const uint32_t a_addr = smem_base + stage * kStageBytes;
+            const uint32_t b_addr = a_addr + kATileBytes;
+            // A: K-major, groups of 8 rows are 1024 bytes apart.
+            const uint64_t a_desc = make_smem_desc_sw128(a_addr, 16, 1024);
+            // B stored [K, N]: N-major, 64-column chunks are kBChunkBytes apart, groups of 8 k-rows
+            // 1024. B stored [N, K]: K-major exactly like A.
+            const bool b_kn = b_layout == kBLayoutKN;
+            const uint64_t b_desc = b_kn ? make_smem_desc_sw128(b_addr, kBChunkBytes, 1024)
+                                         : make_smem_desc_sw128(b_addr, 16, 1024);
+            const uint64_t b_step = b_kn ? 128 : 2;  // descriptor units (16 bytes) per 16-wide k-step
 #pragma unroll
-          for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
-            // Per 16-wide k-step: A advances 32 bytes inside the swizzle row, B advances
-            // two groups of 8 k-rows (2048 bytes); both in 16-byte descriptor units.
-            umma_ss(d_tmem, a_desc + static_cast<uint64_t>(kk * 2),
-                        b_desc + static_cast<uint64_t>(kk) * b_step, idesc,
-                        (kb != kb_begin || kk != 0) ? 1u : 0u, static_cast<uint32_t>(elem8));
+            for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
+              // Per 16-wide k-step: A advances 32 bytes inside the swizzle row, B advances
+              // two groups of 8 k-rows (2048 bytes); both in 16-byte descriptor units.
+              umma_ss<kF8>(d_tmem, a_desc + static_cast<uint64_t>(kk * 2), b_desc + static_cast<uint64_t>(kk) * b_step,
+                           idesc, (kb != kb_begin || kk != 0) ? 1u : 0u);
+            }
+            umma_commit(empty_bar(stage));
+            if (++stage == kStages) {
+              stage = 0;
+              phase ^= 1u;
+            }
           }
-          umma_commit(empty_bar(stage));
-          if (++stage == kStages) {
-            stage = 0;
-            phase ^= 1u;
-          }
+          if (ok)
+            umma_commit(tmem_full_bar(acc));
         }
-        if (ok)
-          umma_commit(tmem_full_bar(acc));
-      }
+      };
+      if (elem8)
+        mma_role(std::true_type{});
+      else
+        mma_role(std::false_type{});
     }
   } else {
     // ------------------------------------------------------------ epilogue ----------

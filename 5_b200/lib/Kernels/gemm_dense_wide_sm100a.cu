@@ -30,6 +30,7 @@
 
 #include <cstdlib>
 #include <cstring>
+#include <type_traits>
 
 namespace hc {
 namespace sm100 {
@@ -175,57 +176,65 @@ gemm_dense_wide_kernel(const __grid_constant__ CUtensorMap tmap_a,
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (CTA 0) -
     if (lane == 0 && cta_rank == 0) {
-      uint32_t stage = 0, phase = 0;
-      uint32_t iter = 0;
-      bool ok = true;
-      const bool b_kn = b_layout == kBLayoutKN;
-      for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters, ++iter) {
-        const uint32_t acc_phase = iter & 1u;  // each tile uses each half once
-        for (int kb = 0; ok && kb < num_kb; ++kb) {
-          if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
-            ok = false;
-            break;
-          }
-          tcgen05_fence_after_sync();
-          const uint32_t a_addr = smem_base + stage * kStageBytes;
-          const uint32_t b_addr = a_addr + kATileBytes;
+      // The instruction kind (16-bit or 8-bit operands) is a template argument of the whole role
+      // loop, chosen by one branch here.
+      auto mma_role = [&](auto f8) {
+        constexpr bool kF8 = decltype(f8)::value;
+        uint32_t stage = 0, phase = 0;
+        uint32_t iter = 0;
+        bool ok = true;
+        const bool b_kn = b_layout == kBLayoutKN;
+        for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters, ++iter) {
+          const uint32_t acc_phase = iter & 1u;  // each tile uses each half once
+          for (int kb = 0; ok && kb < num_kb; ++kb) {
+            if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
+              ok = false;
+              break;
+            }
+            tcgen05_fence_after_sync();
+            const uint32_t a_addr = smem_base + stage * kStageBytes;
+            const uint32_t b_addr = a_addr + kATileBytes;
 #pragma unroll
-          for (uint32_t h = 0; h < 2; ++h) {
-            if (kb == 0) {
-              // The half must have been drained by the previous tile's epilogue.
-              if (!mbar_wait(tmem_empty_bar(h), acc_phase ^ 1u, abort_flag)) {
-                ok = false;
-                break;
+            for (uint32_t h = 0; h < 2; ++h) {
+              if (kb == 0) {
+                // The half must have been drained by the previous tile's epilogue.
+                if (!mbar_wait(tmem_empty_bar(h), acc_phase ^ 1u, abort_flag)) {
+                  ok = false;
+                  break;
+                }
+                tcgen05_fence_after_sync();
               }
-              tcgen05_fence_after_sync();
-            }
 #pragma unroll
-            for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
-              // A: +32 bytes per k-step inside the swizzle row. B stored [K, N]: 64-column chunks
-              // 8 KiB apart, +2 KiB per k-step; stored [N, K]: laid out and advanced like A.
-              const uint64_t a_desc =
-                  make_smem_desc_sw128(a_addr + h * kABoxBytes, 16, 1024) + static_cast<uint64_t>(kk * 2);
-              const uint64_t b_desc = b_kn ? make_smem_desc_sw128(b_addr, kBBoxBytes, 1024) + static_cast<uint64_t>(kk * 128)
-                                           : make_smem_desc_sw128(b_addr, 16, 1024) + static_cast<uint64_t>(kk * 2);
-              umma_ss_pair(tmem_base + h * kTileN, a_desc, b_desc, idesc, (kb != 0 || kk != 0) ? 1u : 0u,
-                           static_cast<uint32_t>(elem8));
+              for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
+                // A: +32 bytes per k-step inside the swizzle row. B stored [K, N]: 64-column chunks
+                // 8 KiB apart, +2 KiB per k-step; stored [N, K]: laid out and advanced like A.
+                const uint64_t a_desc =
+                    make_smem_desc_sw128(a_addr + h * kABoxBytes, 16, 1024) + static_cast<uint64_t>(kk * 2);
+                const uint64_t b_desc = b_kn ? make_smem_desc_sw128(b_addr, kBBoxBytes, 1024) + static_cast<uint64_t>(kk * 128)
+                                             : make_smem_desc_sw128(b_addr, 16, 1024) + static_cast<uint64_t>(kk * 2);
+                umma_ss_pair<kF8>(tmem_base + h * kTileN, a_desc, b_desc, idesc, (kb != 0 || kk != 0) ? 1u : 0u);
+              }
+              if (kb == num_kb - 1) {
+                umma_commit_pair(map_to_cta(tmem_full_bar(h), 0));
+                umma_commit_pair(map_to_cta(tmem_full_bar(h), 1));
+              }
             }
-            if (kb == num_kb - 1) {
-              umma_commit_pair(map_to_cta(tmem_full_bar(h), 0));
-              umma_commit_pair(map_to_cta(tmem_full_bar(h), 1));
+            if (!ok)
+              break;
+            // Hand ring slot `stage` back to both producers.
+            umma_commit_pair(map_to_cta(empty_bar(stage), 0));
+            umma_commit_pair(map_to_cta(empty_bar(stage), 1));
+            if (++stage == kStages) {
+              stage = 0;
+              phase ^= 1u;
             }
-          }
-          if (!ok)
-            break;
-          // Hand ring slot `stage` back to both producers.
-          umma_commit_pair(map_to_cta(empty_bar(stage), 0));
-          umma_commit_pair(map_to_cta(empty_bar(stage), 1));
-          if (++stage == kStages) {
-            stage = 0;
-            phase ^= 1u;
           }
         }
-      }
+      };
+      if (elem8)
+        mma_role(std::true_type{});
+      else
+        mma_role(std::false_type{});
     }
   } else {
     // ------------------------------------------------------------ epilogue ----------

@@ -196,7 +196,7 @@ cudaError_t launch_repack_pitch_two(const void *src0, long long src0_ld, void *d
 constexpr int kMaxMapOps = 8;
 constexpr int kMapScale = 1;            // v = v * value
 constexpr int kMapAdd = 2;              // v = v + value
-constexpr int kMapMax = 3;              // v = maximum(v, value)   (NaN propagates, as in NumPy)
+constexpr int kMapMax = 3;              // v = maximum(v, value)   (NumPy's: NaN propagates; ties give the second operand)
 constexpr int kMapMin = 4;              // v = minimum(v, value)
 constexpr int kMapReverseSub = 5;       // v = value - v
 constexpr int kMapAddOther = 6;         // v = v + y[i]
@@ -205,6 +205,15 @@ constexpr int kMapReverseSubOther = 8;  // v = y[i] - v
 constexpr int kMapMulOther = 9;         // v = v * y[i]
 constexpr int kMapMaxOther = 10;        // v = maximum(v, y[i])
 constexpr int kMapMinOther = 11;        // v = minimum(v, y[i])
+// maximum / minimum with the operands the other way round. NumPy returns the second operand when
+// neither is greater (two zeros of opposite sign), so the order is observable.
+constexpr int kMapReverseMax = 12;       // v = maximum(value, v)
+constexpr int kMapReverseMin = 13;       // v = minimum(value, v)
+constexpr int kMapReverseMaxOther = 14;  // v = maximum(y[i], v)
+constexpr int kMapReverseMinOther = 15;  // v = minimum(y[i], v)
+inline bool map_op_uses_other(int kind) {
+  return (kind >= kMapAddOther && kind <= kMapMinOther) || kind == kMapReverseMaxOther || kind == kMapReverseMinOther;
+}
 struct MapOps {
   int count;
   int kind[kMaxMapOps];

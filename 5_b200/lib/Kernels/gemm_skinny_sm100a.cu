@@ -24,6 +24,7 @@
 
 #include <cstdlib>
 #include <cstring>
+#include <type_traits>
 
 namespace hc {
 namespace sm100 {
@@ -152,50 +153,58 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a,
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer --------
     if (lane == 0) {
-      uint32_t stage = 0, phase = 0;
-      uint32_t iter = 0;
-      bool ok = true;
-      for (int unit = blockIdx.x; ok && unit < num_units; unit += gridDim.x, ++iter) {
-        const int split = unit / n_tiles;
-        const int kb_begin = static_cast<int>(static_cast<long long>(split) * kb_total / splits);
-        const int kb_end = static_cast<int>(static_cast<long long>(split + 1) * kb_total / splits);
-        const uint32_t acc = iter & 1u;
-        const uint32_t acc_phase = (iter >> 1) & 1u;
-        if (!mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, abort_flag))
-          break;
-        tcgen05_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + acc * kMp;
-        for (int kb = kb_begin; kb < kb_end; ++kb) {
-          if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
-            ok = false;
+      // The instruction kind (16-bit or 8-bit operands) is a template argument of the whole role
+      // loop, chosen by one branch here.
+      auto mma_role = [&](auto f8) {
+        constexpr bool kF8 = decltype(f8)::value;
+        uint32_t stage = 0, phase = 0;
+        uint32_t iter = 0;
+        bool ok = true;
+        for (int unit = blockIdx.x; ok && unit < num_units; unit += gridDim.x, ++iter) {
+          const int split = unit / n_tiles;
+          const int kb_begin = static_cast<int>(static_cast<long long>(split) * kb_total / splits);
+          const int kb_end = static_cast<int>(static_cast<long long>(split + 1) * kb_total / splits);
+          const uint32_t acc = iter & 1u;
+          const uint32_t acc_phase = (iter >> 1) & 1u;
+          if (!mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, abort_flag))
             break;
-          }
           tcgen05_fence_after_sync();
-          const uint32_t bt_addr = smem_base + stage * Cfg::kStageBytes;
-          const uint32_t a_addr = bt_addr + kBTileBytes;
-          // UMMA "A" operand = B^T tile (128 n x 64 k): MN-major when B is stored [K, N] (n
-          // contiguous), K-major when it is stored [N, K].
-          const bool b_kn = b_layout == kBLayoutKN;
-          const uint64_t bt_desc = b_kn ? make_smem_desc_sw128(bt_addr, kBChunkBytes, 1024)
-                                        : make_smem_desc_sw128(bt_addr, 16, 1024);
-          const uint64_t bt_step = b_kn ? 128 : 2;
-          // UMMA "B" operand = A tile (kMp rows x 64 k), k contiguous: K-major.
-          const uint64_t a_desc = make_smem_desc_sw128(a_addr, 16, 1024);
+          const uint32_t d_tmem = tmem_base + acc * kMp;
+          for (int kb = kb_begin; kb < kb_end; ++kb) {
+            if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
+              ok = false;
+              break;
+            }
+            tcgen05_fence_after_sync();
+            const uint32_t bt_addr = smem_base + stage * Cfg::kStageBytes;
+            const uint32_t a_addr = bt_addr + kBTileBytes;
+            // UMMA "A" operand = B^T tile (128 n x 64 k): MN-major when B is stored [K, N] (n
+            // contiguous), K-major when it is stored [N, K].
+            const bool b_kn = b_layout == kBLayoutKN;
+            const uint64_t bt_desc = b_kn ? make_smem_desc_sw128(bt_addr, kBChunkBytes, 1024)
+                                          : make_smem_desc_sw128(bt_addr, 16, 1024);
+            const uint64_t bt_step = b_kn ? 128 : 2;
+            // UMMA "B" operand = A tile (kMp rows x 64 k), k contiguous: K-major.
+            const uint64_t a_desc = make_smem_desc_sw128(a_addr, 16, 1024);
 #pragma unroll
-          for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
-            umma_ss(d_tmem, bt_desc + static_cast<uint64_t>(kk) * bt_step,
-                    a_desc + static_cast<uint64_t>(kk * 2), idesc,
-                    (kb != kb_begin || kk != 0) ? 1u : 0u, static_cast<uint32_t>(elem8));
+            for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
+              umma_ss<kF8>(d_tmem, bt_desc + static_cast<uint64_t>(kk) * bt_step, a_desc + static_cast<uint64_t>(kk * 2),
+                           idesc, (kb != kb_begin || kk != 0) ? 1u : 0u);
+            }
+            umma_commit(empty_bar(stage));
+            if (++stage == kStages) {
+              stage = 0;
+              phase ^= 1u;
+            }
           }
-          umma_commit(empty_bar(stage));
-          if (++stage == kStages) {
-            stage = 0;
-            phase ^= 1u;
-          }
+          if (ok)
+            umma_commit(tmem_full_bar(acc));
         }
-        if (ok)
-          umma_commit(tmem_full_bar(acc));
-      }
+      };
+      if (elem8)
+        mma_role(std::true_type{});
+      else
+        mma_role(std::false_type{});
     }
   } else {
     // ------------------------------------------------------------ epilogue ----------

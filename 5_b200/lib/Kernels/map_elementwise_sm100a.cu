@@ -21,59 +21,100 @@
 // the reference simulator's.
 #include "gemm_launch.h"
 
+#include <cstdlib>
+
 namespace hc {
 namespace sm100 {
 
 namespace {
 
-__device__ __forceinline__ float map_max_nan(float a, float b) {
-  float d;
-  asm("max.NaN.f32 %0, %1, %2;" : "=f"(d) : "f"(a), "f"(b));
-  return d;
+// maximum / minimum as NumPy computes them on float32 arrays (x86: the SIMD max/min select, plus
+// NaN propagation): the first operand if it is greater (smaller) or a NaN, otherwise the second. A
+// NaN in either operand therefore gives NaN, and two zeros of opposite sign give the second one.
+__device__ __forceinline__ float numpy_max(float first, float second) {
+  return (first > second || first != first) ? first : second;
 }
-__device__ __forceinline__ float map_min_nan(float a, float b) {
-  float d;
-  asm("min.NaN.f32 %0, %1, %2;" : "=f"(d) : "f"(a), "f"(b));
-  return d;
-}
-
-__device__ __forceinline__ float apply_map_ops(float v, float w, const MapOps &ops) {
-#pragma unroll
-  for (int i = 0; i < kMaxMapOps; ++i) {
-    if (i < ops.count) {
-      const int kind = ops.kind[i];
-      const float x = kind >= kMapAddOther ? w : ops.value[i];
-      switch (kind) {
-      case kMapScale:
-      case kMapMulOther:
-        v = __fmul_rn(v, x);
-        break;
-      case kMapAdd:
-      case kMapAddOther:
-        v = __fadd_rn(v, x);
-        break;
-      case kMapSubOther:
-        v = __fsub_rn(v, x);
-        break;
-      case kMapReverseSub:
-      case kMapReverseSubOther:
-        v = __fsub_rn(x, v);
-        break;
-      case kMapMax:
-      case kMapMaxOther:
-        v = map_max_nan(v, x);
-        break;
-      default:  // kMapMin, kMapMinOther
-        v = map_min_nan(v, x);
-        break;
-      }
-    }
-  }
-  return v;
+__device__ __forceinline__ float numpy_min(float first, float second) {
+  return (first < second || first != first) ? first : second;
 }
 
 constexpr int kThreads = 256;
 constexpr int kVectorsPerThread = 4;  // independent 16-byte loads in flight per thread and input
+constexpr int kValues = 4 * kVectorsPerThread;
+
+// The operations on the N values a thread holds. The kind of each operation is the same for the
+// whole grid, so it is branched on once per operation and batch of values, not per element; every
+// operation is one correctly rounded float32 instruction per value.
+template <int N>
+__device__ __forceinline__ void apply_map_ops(float (&v)[N], const float (&w)[N], const MapOps &ops) {
+#pragma unroll 1
+  for (int i = 0; i < ops.count; ++i) {
+    const int kind = ops.kind[i];
+    const float c = ops.value[i];
+    switch (kind) {
+    case kMapScale:
+#pragma unroll
+      for (int j = 0; j < N; ++j) v[j] = __fmul_rn(v[j], c);
+      break;
+    case kMapAdd:
+#pragma unroll
+      for (int j = 0; j < N; ++j) v[j] = __fadd_rn(v[j], c);
+      break;
+    case kMapMax:
+#pragma unroll
+      for (int j = 0; j < N; ++j) v[j] = numpy_max(v[j], c);
+      break;
+    case kMapMin:
+#pragma unroll
+      for (int j = 0; j < N; ++j) v[j] = numpy_min(v[j], c);
+      break;
+    case kMapReverseSub:
+#pragma unroll
+      for (int j = 0; j < N; ++j) v[j] = __fsub_rn(c, v[j]);
+      break;
+    case kMapReverseMax:
+#pragma unroll
+      for (int j = 0; j < N; ++j) v[j] = numpy_max(c, v[j]);
+      break;
+    case kMapReverseMin:
+#pragma unroll
+      for (int j = 0; j < N; ++j) v[j] = numpy_min(c, v[j]);
+      break;
+    case kMapAddOther:
+#pragma unroll
+      for (int j = 0; j < N; ++j) v[j] = __fadd_rn(v[j], w[j]);
+      break;
+    case kMapSubOther:
+#pragma unroll
+      for (int j = 0; j < N; ++j) v[j] = __fsub_rn(v[j], w[j]);
+      break;
+    case kMapReverseSubOther:
+#pragma unroll
+      for (int j = 0; j < N; ++j) v[j] = __fsub_rn(w[j], v[j]);
+      break;
+    case kMapMulOther:
+#pragma unroll
+      for (int j = 0; j < N; ++j) v[j] = __fmul_rn(v[j], w[j]);
+      break;
+    case kMapMaxOther:
+#pragma unroll
+      for (int j = 0; j < N; ++j) v[j] = numpy_max(v[j], w[j]);
+      break;
+    case kMapMinOther:
+#pragma unroll
+      for (int j = 0; j < N; ++j) v[j] = numpy_min(v[j], w[j]);
+      break;
+    case kMapReverseMaxOther:
+#pragma unroll
+      for (int j = 0; j < N; ++j) v[j] = numpy_max(w[j], v[j]);
+      break;
+    default:  // kMapReverseMinOther
+#pragma unroll
+      for (int j = 0; j < N; ++j) v[j] = numpy_min(w[j], v[j]);
+      break;
+    }
+  }
+}
 
 // kVec: all pointers are 16-byte aligned, so the body runs on float4; the tail (n % 4) and the
 // unaligned case use 4-byte accesses (still coalesced).
@@ -89,49 +130,48 @@ map_f32_kernel(const float *__restrict__ x, const float *__restrict__ y, float *
     const float4 *y4 = reinterpret_cast<const float4 *>(y);
     float4 *o4 = reinterpret_cast<float4 *>(out);
     for (long long base = tid; base < vectors; base += threads * kVectorsPerThread) {
-      float4 xv[kVectorsPerThread], yv[kVectorsPerThread];
+      float v[kValues], w[kValues];
 #pragma unroll
       for (int j = 0; j < kVectorsPerThread; ++j) {
         const long long i = base + j * threads;
+        float4 xv = make_float4(0.f, 0.f, 0.f, 0.f), yv = xv;
         if (i < vectors) {
-          xv[j] = __ldcs(x4 + i);
+          xv = __ldcs(x4 + i);
           if (kTwoInputs)
-            yv[j] = __ldcs(y4 + i);
+            yv = __ldcs(y4 + i);
         }
+        v[4 * j] = xv.x, v[4 * j + 1] = xv.y, v[4 * j + 2] = xv.z, v[4 * j + 3] = xv.w;
+        w[4 * j] = yv.x, w[4 * j + 1] = yv.y, w[4 * j + 2] = yv.z, w[4 * j + 3] = yv.w;
       }
+      apply_map_ops(v, w, ops);
 #pragma unroll
       for (int j = 0; j < kVectorsPerThread; ++j) {
         const long long i = base + j * threads;
-        if (i < vectors) {
-          float4 r;
-          r.x = apply_map_ops(xv[j].x, kTwoInputs ? yv[j].x : 0.0f, ops);
-          r.y = apply_map_ops(xv[j].y, kTwoInputs ? yv[j].y : 0.0f, ops);
-          r.z = apply_map_ops(xv[j].z, kTwoInputs ? yv[j].z : 0.0f, ops);
-          r.w = apply_map_ops(xv[j].w, kTwoInputs ? yv[j].w : 0.0f, ops);
-          __stcs(o4 + i, r);
-        }
+        if (i < vectors)
+          __stcs(o4 + i, make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]));
       }
     }
     const long long tail = vectors << 2;
-    if (tid < n - tail)
-      out[tail + tid] = apply_map_ops(x[tail + tid], kTwoInputs ? y[tail + tid] : 0.0f, ops);
+    if (tid < n - tail) {
+      float v[1] = {x[tail + tid]}, w[1] = {kTwoInputs ? y[tail + tid] : 0.0f};
+      apply_map_ops(v, w, ops);
+      out[tail + tid] = v[0];
+    }
   } else {
-    for (long long base = tid; base < n; base += threads * kVectorsPerThread) {
-      float xv[kVectorsPerThread], yv[kVectorsPerThread];
+    for (long long base = tid; base < n; base += threads * kValues) {
+      float v[kValues], w[kValues];
 #pragma unroll
-      for (int j = 0; j < kVectorsPerThread; ++j) {
+      for (int j = 0; j < kValues; ++j) {
         const long long i = base + j * threads;
-        if (i < n) {
-          xv[j] = __ldcs(x + i);
-          if (kTwoInputs)
-            yv[j] = __ldcs(y + i);
-        }
+        v[j] = i < n ? __ldcs(x + i) : 0.0f;
+        w[j] = (kTwoInputs && i < n) ? __ldcs(y + i) : 0.0f;
       }
+      apply_map_ops(v, w, ops);
 #pragma unroll
-      for (int j = 0; j < kVectorsPerThread; ++j) {
+      for (int j = 0; j < kValues; ++j) {
         const long long i = base + j * threads;
         if (i < n)
-          __stcs(out + i, apply_map_ops(xv[j], kTwoInputs ? yv[j] : 0.0f, ops));
+          __stcs(out + i, v[j]);
       }
     }
   }
@@ -143,7 +183,13 @@ int map_grid(long long n, int sm_count) {
   // Persistent grid: eight CTAs of 256 threads per SM (all 2048 thread slots), fewer when the
   // array is too short to give every thread a vector.
   const long long wanted = (n / 4 + kThreads - 1) / kThreads;
-  const long long most = static_cast<long long>(sm_count > 0 ? sm_count : 148) * 8;
+  long long per_sm = 8;
+  if (const char *forced = std::getenv("HC_CUDA_MAP_CTAS_PER_SM")) {  // tuning aid
+    const long long v = std::atoll(forced);
+    if (v >= 1 && v <= 64)
+      per_sm = v;
+  }
+  const long long most = static_cast<long long>(sm_count > 0 ? sm_count : 148) * per_sm;
   const long long grid = wanted < 1 ? 1 : (wanted < most ? wanted : most);
   return static_cast<int>(grid);
 }
@@ -158,7 +204,7 @@ cudaError_t launch_map_f32(const float *x, const float *y, float *out, long long
   const uintptr_t bits = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out) |
                          (two ? reinterpret_cast<uintptr_t>(y) : 0);
   const bool vec = (bits & 15) == 0;
-  const int grid = map_grid(vec ? n : n * 4, sm_count);
+  const int grid = map_grid(n, sm_count);
   if (vec && two)
     map_f32_kernel<true, true><<<grid, kThreads, 0, stream>>>(x, y, out, n, ops);
   else if (vec)

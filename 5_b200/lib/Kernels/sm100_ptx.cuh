@@ -204,22 +204,30 @@ __device__ __forceinline__ void umma_f16_ss(uint32_t tmem_d, uint64_t desc_a, ui
       : "memory");
 }
 
-// The same with the element width chosen at run time: `elem8` != 0 issues kind::f8f6f4 (8-bit
-// floats, 32 of k per instruction), otherwise kind::f16 (16 of k). Both read 32 bytes of k per
-// operand row, so descriptors and their per-step advance are the same in bytes.
-__device__ __forceinline__ void umma_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                        uint32_t accumulate, uint32_t elem8) {
+// The same for 8-bit floats: kind::f8f6f4, 32 of k per instruction. Both kinds read 32 bytes of k per
+// operand row, so descriptors and their per-step advance are the same in bytes. (The kind is a
+// template argument of the issue loops, chosen by one branch per ring stage: a pair of oppositely
+// predicated instructions per step, one of each kind, measured 10-30 % slower kernels.)
+__device__ __forceinline__ void umma_f8_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                           uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n"
-      ".reg .pred p, q;\n"
+      ".reg .pred p;\n"
       "setp.ne.b32 p, %4, 0;\n"
-      "setp.ne.b32 q, %5, 0;\n"
-      "@q tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n"
-      "@!q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n"
       "}\n"
       :
-      : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(elem8)
+      : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
+}
+
+template <bool kF8>
+__device__ __forceinline__ void umma_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                        uint32_t accumulate) {
+  if constexpr (kF8)
+    umma_f8_ss(tmem_d, desc_a, desc_b, idesc, accumulate);
+  else
+    umma_f16_ss(tmem_d, desc_a, desc_b, idesc, accumulate);
 }
 
 // Makes `bar` receive one arrival once every tcgen05.mma issued so far by this thread has
@@ -361,19 +369,26 @@ __device__ __forceinline__ void umma_f16_ss_pair(uint32_t tmem_d, uint64_t desc_
       : "memory");
 }
 
-__device__ __forceinline__ void umma_ss_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                             uint32_t accumulate, uint32_t elem8) {
+__device__ __forceinline__ void umma_f8_ss_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                                uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n"
-      ".reg .pred p, q;\n"
+      ".reg .pred p;\n"
       "setp.ne.b32 p, %4, 0;\n"
-      "setp.ne.b32 q, %5, 0;\n"
-      "@q tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n"
-      "@!q tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n"
       "}\n"
       :
-      : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(elem8)
+      : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
+}
+
+template <bool kF8>
+__device__ __forceinline__ void umma_ss_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                             uint32_t accumulate) {
+  if constexpr (kF8)
+    umma_f8_ss_pair(tmem_d, desc_a, desc_b, idesc, accumulate);
+  else
+    umma_f16_ss_pair(tmem_d, desc_a, desc_b, idesc, accumulate);
 }
 
 // One arrival on `cluster_bar` (either CTA's) once all pair MMAs issued so far have finished.

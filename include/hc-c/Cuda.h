@@ -269,7 +269,8 @@ HC_CUDA_CAPI_EXPORTED int hcCudaGemmHostDeviceA(HcCudaContext *ctx, const HcCuda
 typedef enum HcCudaMapOp {
   HC_CUDA_MAP_SCALE = 1,             /* v = v * value */
   HC_CUDA_MAP_ADD = 2,               /* v = v + value */
-  HC_CUDA_MAP_MAX = 3,               /* v = maximum(v, value); NaN propagates, as in NumPy */
+  HC_CUDA_MAP_MAX = 3,               /* v = maximum(v, value) as NumPy computes it: a NaN operand gives NaN, and
+                                        when neither operand is greater the second one is returned */
   HC_CUDA_MAP_MIN = 4,               /* v = minimum(v, value) */
   HC_CUDA_MAP_REVERSE_SUB = 5,       /* v = value - v */
   HC_CUDA_MAP_ADD_OTHER = 6,         /* v = v + y[i] */
@@ -277,7 +278,13 @@ typedef enum HcCudaMapOp {
   HC_CUDA_MAP_REVERSE_SUB_OTHER = 8, /* v = y[i] - v */
   HC_CUDA_MAP_MUL_OTHER = 9,         /* v = v * y[i] */
   HC_CUDA_MAP_MAX_OTHER = 10,        /* v = maximum(v, y[i]) */
-  HC_CUDA_MAP_MIN_OTHER = 11         /* v = minimum(v, y[i]) */
+  HC_CUDA_MAP_MIN_OTHER = 11,        /* v = minimum(v, y[i]) */
+  /* maximum / minimum with the operands the other way round: NumPy returns the second operand when
+   * neither is greater (two zeros of opposite sign), so the order is observable. */
+  HC_CUDA_MAP_REVERSE_MAX = 12,      /* v = maximum(value, v) */
+  HC_CUDA_MAP_REVERSE_MIN = 13,      /* v = minimum(value, v) */
+  HC_CUDA_MAP_REVERSE_MAX_OTHER = 14, /* v = maximum(y[i], v) */
+  HC_CUDA_MAP_REVERSE_MIN_OTHER = 15  /* v = minimum(y[i], v) */
 } HcCudaMapOp;
 #define HC_CUDA_MAX_MAP_OPS 8
 

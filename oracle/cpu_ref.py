@@ -165,7 +165,8 @@ def map_elementwise(x: np.ndarray, ops, other: np.ndarray | None = None) -> np.n
     element below the buffers' extent goes through the statements once, each statement one
     float32 NumPy operation. `ops` as the recogniser lists them: ("scale", c), ("add", c),
     ("max", c), ("min", c), ("rsub", c), ("add_other",), ("sub_other",), ("rsub_other",),
-    ("mul_other",), ("max_other",), ("min_other",)."""
+    ("mul_other",), ("max_other",), ("min_other",), and "rmax" / "rmin" (with a constant or
+    "_other") for maximum / minimum with the chain as the second operand."""
     v = np.array(x, dtype=np.float32, copy=True)
     w = None if other is None else np.asarray(other, dtype=np.float32)
     with np.errstate(invalid="ignore", over="ignore"):
@@ -185,6 +186,10 @@ def map_elementwise(x: np.ndarray, ops, other: np.ndarray | None = None) -> np.n
                 v = np.maximum(v, operand)
             elif base == "min":
                 v = np.minimum(v, operand)
+            elif base == "rmax":  # operand order matters when neither is greater (signed zeros)
+                v = np.maximum(operand, v)
+            elif base == "rmin":
+                v = np.minimum(operand, v)
             else:
                 raise ValueError(f"unknown operation {kind!r}")
     return v.astype(np.float32, copy=False)

@@ -78,8 +78,13 @@ def test_every_operation_matches_numpy(gpu_ctx) -> None:
     x[:4] = np.nan, np.inf, -np.inf, -0.0
     y[:8] = 1.0, 2.0, 3.0, 0.0, np.nan, np.inf, -np.inf, -0.0
     dx, dy, dout = gpu_ctx.to_device(x), gpu_ctx.to_device(y), gpu_ctx.empty((n,), np.float32)
-    for op in (("scale", 0.1), ("add", 0.1), ("max", 0.5), ("min", -0.5), ("rsub", 7.25), ("add_other",),
-               ("sub_other",), ("rsub_other",), ("mul_other",), ("max_other",), ("min_other",)):
+    # (x[3] is -0.0 where y[3] is 0.0, and x[7] is a number where y[7] is -0.0: maximum / minimum of two
+    # zeros of opposite sign return the second operand in NumPy, in either order.)
+    x[7] = 0.0
+    dx.copy_from_host(x)
+    for op in (("scale", 0.1), ("add", 0.1), ("max", 0.5), ("min", -0.5), ("rsub", 7.25), ("max", 0.0), ("rmax", 0.0),
+               ("min", 0.0), ("rmin", 0.0), ("max", -0.0), ("rmin", -0.0), ("add_other",), ("sub_other",),
+               ("rsub_other",), ("mul_other",), ("max_other",), ("min_other",), ("rmax_other",), ("rmin_other",)):
         gpu_ctx.map(dx, dout, (op,), other=dy)
         gpu_ctx.synchronize()
         assert same_bits(dout.to_numpy(), cpu_ref.map_elementwise(x, (op,), other=y)), op

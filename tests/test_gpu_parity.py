@@ -139,8 +139,8 @@ def test_dense_wide_tiles(shape, dtype: str, gpu_ctx, monkeypatch) -> None:
     gpu_ctx.gemm(da, db, dc)
     gpu_ctx.synchronize()
     whole = raw.to_numpy()
-    c = whole[guard : guard + m, 4 : 4 + n]
-    assert_close_to_oracle(np.ascontiguousarray(c), a, b, expect=expect)
+    c = np.ascontiguousarray(whole[guard : guard + m, 4 : 4 + n])
+    assert_close_to_oracle(c, a, b, expect=expect)
     whole[guard : guard + m, 4 : 4 + n] = np.nan
     assert np.isnan(whole).all()  # nothing written outside C
     dct = gpu_ctx.empty((m, n), np.float32)

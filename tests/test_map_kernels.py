@@ -57,6 +57,17 @@ def test_spellings() -> None:
     assert plan is not None, why
     assert (plan.x_param, plan.out_param, plan.ops) == ("x", "x", (("rsub", 3.0), ("min", 1.5)))
 
+    @kernel(work_shape=(W,), group_shape=(8,))
+    def relu(group, x: Buffer[W, np.float32], y: Buffer[W, np.float32]) -> None:
+        start = group.work_offset[0]
+        v = group.load(x[start:], shape=(8,))
+        group.store(y[start:], np.maximum(0.0, v))
+
+    # np.maximum returns its second operand when neither is greater, so maximum(0.0, -0.0) is -0.0 but
+    # maximum(-0.0, 0.0) is 0.0: the operand order is part of the operation.
+    plan, why = recognise_elementwise_map(relu)
+    assert plan is not None and plan.ops == (("rmax", 0.0),), why
+
     @kernel(work_shape=(16,), group_shape=(16,))
     def fixed(group, a: Buffer[16], b: Buffer[16], c: Buffer[16]) -> None:
         g = group.work_offset[0]
@@ -162,4 +173,4 @@ def test_c_abi_rejects_bad_map_arguments_without_a_device() -> None:
         cuda._map_args(4, 0x1000, None, 0x2000, (("add", 1.0),) * 9)
     with pytest.raises(ValueError, match="unknown element-wise operation"):
         cuda._map_args(4, 0x1000, None, 0x2000, (("divide", 1.0),))
-    assert cuda.MAP_KINDS["min_other"] == 11 and cuda.MAX_MAP_OPS == 8
+    assert cuda.MAP_KINDS["min_other"] == 11 and cuda.MAP_KINDS["rmin_other"] == 15 and cuda.MAX_MAP_OPS == 8
