@@ -124,7 +124,8 @@ struct HcCudaContext {
   bool planning_push = false;         // plan_gemm then keeps to the kernels that can push tiles to peers
   cudaEvent_t fence_event = nullptr;
   EncodeTiledFn encode = nullptr;
-  int group_n = 8;
+  int group_n = 8;        // tile columns per group of the tile walk (256-column tiles)
+  int group_n_wide = 16;  // the same for the 512x256-tile kernel (measured best of 4/8/12/16)
   bool c_tma_store = true;  // HC_CUDA_C_TMA_STORE=0 keeps ordinary stores (tuning aid)
   MapCacheEntry map_cache[kMapCacheEntries];  // recently encoded tensor maps, see encode_map
   unsigned map_cache_next = 0;
@@ -588,7 +589,7 @@ int enqueue_gemm(HcCudaContext *ctx, const HcCudaGemmArgs *args, const HcCudaGem
                       plan.tiles_m == (m + hc::sm100::kDenseWideTileM - 1) / hc::sm100::kDenseWideTileM;
     if (wide) {
       HC_TRY_CUDA(ctx, hc::sm100::launch_gemm_dense_wide(tmap_a, tmap_b, args->c, m, n, k, args->ldc, args->dtype,
-                                                         ctx->group_n, plan.grid, b_layout, ep, c_map,
+                                                         ctx->group_n_wide, plan.grid, b_layout, ep, c_map,
                                                          ctx->status_dev, ctx->stream));
     } else if (pairs) {
       HC_TRY_CUDA(ctx, hc::sm100::launch_gemm_dense_pair(tmap_a, tmap_b, args->c, m, n, k, args->ldc,
@@ -740,7 +741,7 @@ int hcCudaContextCreate(int device, HcCudaContext **out) {
   if (const char *g = std::getenv("HC_CUDA_GROUP_N")) {
     const int v = std::atoi(g);
     if (v >= 1)
-      ctx->group_n = v;
+      ctx->group_n = ctx->group_n_wide = v;
   }
   if (const char *t = std::getenv("HC_CUDA_C_TMA_STORE"))
     ctx->c_tma_store = std::atoi(t) != 0;

@@ -54,6 +54,17 @@ def register_custom(m: int, n: int, k: int, dtype: str = "float16") -> str:
     return "custom"
 
 
+def with_input_dtype(name: str, dtype: str) -> str:
+    """Registers workload `name` again with another element type of A and B (same shape, seed and
+    distribution, values rounded to `dtype`), e.g. "float8_e4m3fn"; returns the new workload's name."""
+    w = CONFIGS[name]
+    if dtype == w.dtype:
+        return name
+    alias = f"{name}:{dtype}"
+    CONFIGS[alias] = Workload(alias, w.m, w.n, w.k, dtype, w.seed)
+    return alias
+
+
 def flops(m: int, n: int, k: int) -> float:
     return 2.0 * m * n * k
 
@@ -63,10 +74,10 @@ def algorithmic_bytes(m: int, n: int, k: int) -> float:
 
 
 def _np_dtype(name: str):
-    if name == "bfloat16":
+    if name in ("bfloat16", "float8_e4m3fn", "float8_e5m2"):
         import ml_dtypes
 
-        return ml_dtypes.bfloat16
+        return getattr(ml_dtypes, name)
     return np.dtype(name).type
 
 
@@ -81,6 +92,7 @@ def make_inputs(name: str) -> tuple[np.ndarray, np.ndarray]:
     """A and B of configurations 1-4 (and of 5, in full; prefer make_sharded_inputs there)."""
     w = CONFIGS[name]
     dtype = _np_dtype(w.dtype)
+    name = name.split(":", 1)[0]  # "<workload>:<dtype>" (with_input_dtype) draws like <workload>
     if name == "sharded":
         a, b = make_sharded_inputs(0, w.n)
         return a, b

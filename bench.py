@@ -521,7 +521,8 @@ class DeviceRun:
         out: dict = {}
         if self.plan.variant == "skinny":
             algo = workloads.algorithmic_bytes(self.m, self.local_n, self.k) \
-                - (4 - self.c_type.itemsize) * self.m * self.local_n
+                - (4 - self.c_type.itemsize) * self.m * self.local_n \
+                - (2 - self.a.dtype.itemsize) * (self.m * self.k + self.k * self.local_n)
             algo += (4 * self.m * self.local_n if self.contract.accumulate else 0) \
                 + (0 if self.bias is None else self.bias.nbytes)
             achieved, peak = algo / seconds / 1e9, float(peaks["hbm_gbs"])
@@ -538,6 +539,7 @@ class DeviceRun:
             # too); a longer one is compared with the figure cuBLAS sustains under the power cap.
             is_burst = self.region_ms < 1000.0
             peak = burst if is_burst else long_run
+            eight_bit = self.w.dtype.startswith("float8")
             out = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                    "frac": achieved / peak, "flops_per_launch": self.local_flops,
                    "peak_source": f"{peaks_source} cuBLAS bf16 8192^3 (16-bit output), "
@@ -545,7 +547,11 @@ class DeviceRun:
                                      else "sustained: the timed region lasted over a second"),
                    "timed_region_ms": self.region_ms,
                    "frac_of_burst_peak": achieved / burst, "frac_of_sustained_peak": achieved / long_run,
-                   "frac_of_nominal": achieved / NOMINAL_PEAK_TFLOPS}
+                   "frac_of_nominal": achieved / (NOMINAL_PEAK_TFLOPS * (2 if eight_bit else 1))}
+            if eight_bit:
+                out["note"] = ("8-bit operands: no peak was measured for them on this pool, so `peak` is still the "
+                               "16-bit cuBLAS figure (a fraction above 1 is expected); frac_of_nominal is against "
+                               "the nominal dense fp8 rate, 4500 TFLOP/s")
             if self.sustained:
                 rate = self.local_flops / (self.sustained["ms_per_step"] * 1e-3) / 1e12
                 out["sustained"] = {**self.sustained, "achieved": rate, "peak": long_run, "frac": rate / long_run,
@@ -868,9 +874,12 @@ def main() -> int:
     parser.add_argument("--steps", type=int, default=200)
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", choices=("b200", "reference"), default="b200")
-    parser.add_argument("--workload", choices=sorted(workloads.CONFIGS), default=None)
+    parser.add_argument("--workload", choices=sorted(workloads.CONFIGS), default=None)  # (aliases are added below)
     parser.add_argument("--shape", default=None, metavar="MxNxK",
                         help="an arbitrary float16 shape instead of a named workload (single GPU), e.g. 8192x8192x512")
+    parser.add_argument("--input-dtype", default=None, choices=("float16", "bfloat16", "float8_e4m3fn", "float8_e5m2"),
+                        help="single GPU: run the workload with A and B of this element type (same shape, seed and "
+                             "distribution, values rounded to it) instead of the type the configuration names")
     parser.add_argument("--e2e-steps", type=int, default=5)
     parser.add_argument("--sustained-seconds", type=float, default=2.0,
                         help="after the timed steps, repeat the same launches for at least this long and report "
@@ -900,6 +909,10 @@ def main() -> int:
         if args.gpus > 1 or args.workload is not None:
             parser.error("--shape is a single-GPU measurement and excludes --workload")
         args.workload = workloads.register_custom(*dims)
+    if args.input_dtype is not None:
+        if args.gpus > 1:
+            parser.error("--input-dtype is a single-GPU measurement")
+        args.workload = workloads.with_input_dtype(args.workload or "gemm_8192", args.input_dtype)
     if (args.b_transposed or args.member != "plain") and args.gpus > 1:
         parser.error("--b-transposed and --member are single-GPU measurements")
     if args.b_transposed and args.member != "plain":
