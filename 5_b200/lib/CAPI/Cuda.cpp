@@ -308,7 +308,10 @@ int plan_gemm(const HcCudaContext *ctx, const HcCudaGemmArgs *args, int sm_count
       long long ignored = 0;
       const bool forced_split = std::getenv("HC_CUDA_DENSE_SPLITS") != nullptr;
       const char *forced_wide = std::getenv("HC_CUDA_DENSE_WIDE");  // "1": the tuning aid also rules out splits
-      const bool keep_wide = forced_wide != nullptr && std::strcmp(forced_wide, "1") == 0;
+      // With many rounds of tiles an underfilled last round is a per cent or two and not worth leaving
+      // the wide tiles for; with few rounds the pair tiles split it over k instead.
+      const bool many_rounds = wide_tiles >= 8LL * (sm_count / 2);
+      const bool keep_wide = many_rounds || (forced_wide != nullptr && std::strcmp(forced_wide, "1") == 0);
       if (forced_split || (!keep_wide && !(ctx != nullptr && ctx->planning_host_panels) &&
                            hc::sm100::dense_choose_splits(wide_tiles, sm_count / 2, wide_kb, &ignored) > 1)) {
         wide = false;

@@ -11,8 +11,9 @@
 // stored once, nothing past the end is touched (hc/simulator.py:1338-1357, 1441-1458). The group
 // size is not observable, so the launch is re-tiled: a persistent grid of a multiple of the SM
 // count walks the array in 128-bit vectors. The kernel is HBM-bound (4 bytes read per input and 4
-// written per element), so that is all there is to it: coalesced 16-byte accesses, enough of them
-// in flight per thread, streaming cache hints (each byte is used once).
+// written per element): coalesced 16-byte accesses, eight of them in flight per thread and input,
+// streaming cache hints (each byte is used once), and an operation loop whose dispatch is paid once
+// per 32 values.
 //
 // The arithmetic is what NumPy does on float32 arrays with float32 (or weak Python) constants: one
 // correctly rounded float32 operation per statement. __fmul_rn / __fadd_rn keep the compiler from
@@ -32,15 +33,13 @@ namespace {
 // NaN propagation): the first operand if it is greater (smaller) or a NaN, otherwise the second. A
 // NaN in either operand therefore gives NaN, and two zeros of opposite sign give the second one.
 __device__ __forceinline__ float numpy_max(float first, float second) {
-  return (first > second || first != first) ? first : second;
+  return ((first > second) | (first != first)) ? first : second;  // (no short-circuit: branch-free)
 }
 __device__ __forceinline__ float numpy_min(float first, float second) {
-  return (first < second || first != first) ? first : second;
+  return ((first < second) | (first != first)) ? first : second;
 }
 
 constexpr int kThreads = 256;
-constexpr int kVectorsPerThread = 4;  // independent 16-byte loads in flight per thread and input
-constexpr int kValues = 4 * kVectorsPerThread;
 
 // The operations on the N values a thread holds. The kind of each operation is the same for the
 // whole grid, so it is branched on once per operation and batch of values, not per element; every
@@ -52,76 +51,94 @@ __device__ __forceinline__ void apply_map_ops(float (&v)[N], const float (&w)[N]
     const int kind = ops.kind[i];
     const float c = ops.value[i];
     switch (kind) {
-    case kMapScale:
+    case kMapScale: {
 #pragma unroll
       for (int j = 0; j < N; ++j) v[j] = __fmul_rn(v[j], c);
       break;
-    case kMapAdd:
+    }
+    case kMapAdd: {
 #pragma unroll
       for (int j = 0; j < N; ++j) v[j] = __fadd_rn(v[j], c);
       break;
-    case kMapMax:
+    }
+    case kMapMax: {
 #pragma unroll
       for (int j = 0; j < N; ++j) v[j] = numpy_max(v[j], c);
       break;
-    case kMapMin:
+    }
+    case kMapMin: {
 #pragma unroll
       for (int j = 0; j < N; ++j) v[j] = numpy_min(v[j], c);
       break;
-    case kMapReverseSub:
+    }
+    case kMapReverseSub: {
 #pragma unroll
       for (int j = 0; j < N; ++j) v[j] = __fsub_rn(c, v[j]);
       break;
-    case kMapReverseMax:
+    }
+    case kMapReverseMax: {
 #pragma unroll
       for (int j = 0; j < N; ++j) v[j] = numpy_max(c, v[j]);
       break;
-    case kMapReverseMin:
+    }
+    case kMapReverseMin: {
 #pragma unroll
       for (int j = 0; j < N; ++j) v[j] = numpy_min(c, v[j]);
       break;
-    case kMapAddOther:
+    }
+    case kMapAddOther: {
 #pragma unroll
       for (int j = 0; j < N; ++j) v[j] = __fadd_rn(v[j], w[j]);
       break;
-    case kMapSubOther:
+    }
+    case kMapSubOther: {
 #pragma unroll
       for (int j = 0; j < N; ++j) v[j] = __fsub_rn(v[j], w[j]);
       break;
-    case kMapReverseSubOther:
+    }
+    case kMapReverseSubOther: {
 #pragma unroll
       for (int j = 0; j < N; ++j) v[j] = __fsub_rn(w[j], v[j]);
       break;
-    case kMapMulOther:
+    }
+    case kMapMulOther: {
 #pragma unroll
       for (int j = 0; j < N; ++j) v[j] = __fmul_rn(v[j], w[j]);
       break;
-    case kMapMaxOther:
+    }
+    case kMapMaxOther: {
 #pragma unroll
       for (int j = 0; j < N; ++j) v[j] = numpy_max(v[j], w[j]);
       break;
-    case kMapMinOther:
+    }
+    case kMapMinOther: {
 #pragma unroll
       for (int j = 0; j < N; ++j) v[j] = numpy_min(v[j], w[j]);
       break;
-    case kMapReverseMaxOther:
+    }
+    case kMapReverseMaxOther: {
 #pragma unroll
       for (int j = 0; j < N; ++j) v[j] = numpy_max(w[j], v[j]);
       break;
-    default:  // kMapReverseMinOther
+    }
+    default: {  // kMapReverseMinOther
 #pragma unroll
       for (int j = 0; j < N; ++j) v[j] = numpy_min(w[j], v[j]);
       break;
+    }
     }
   }
 }
 
 // kVec: all pointers are 16-byte aligned, so the body runs on float4; the tail (n % 4) and the
 // unaligned case use 4-byte accesses (still coalesced).
-template <bool kVec, bool kTwoInputs>
+// kVectorsPerThread: independent 16-byte loads in flight per thread and input, and the number of
+// values (4 x that) one pass of the operation loop works on.
+template <bool kVec, bool kTwoInputs, int kVectorsPerThread>
 __global__ void __launch_bounds__(kThreads)
 map_f32_kernel(const float *__restrict__ x, const float *__restrict__ y, float *__restrict__ out,
                long long n, MapOps ops) {
+  constexpr int kValues = 4 * kVectorsPerThread;
   const long long tid = static_cast<long long>(blockIdx.x) * kThreads + threadIdx.x;
   const long long threads = static_cast<long long>(gridDim.x) * kThreads;
   if (kVec) {
@@ -205,14 +222,30 @@ cudaError_t launch_map_f32(const float *x, const float *y, float *out, long long
                          (two ? reinterpret_cast<uintptr_t>(y) : 0);
   const bool vec = (bits & 15) == 0;
   const int grid = map_grid(n, sm_count);
-  if (vec && two)
-    map_f32_kernel<true, true><<<grid, kThreads, 0, stream>>>(x, y, out, n, ops);
-  else if (vec)
-    map_f32_kernel<true, false><<<grid, kThreads, 0, stream>>>(x, y, out, n, ops);
-  else if (two)
-    map_f32_kernel<false, true><<<grid, kThreads, 0, stream>>>(x, y, out, n, ops);
+  // Eight vectors (32 values) per pass of the operation loop: the dispatch of an operation costs a
+  // fixed hundred or so issue slots, so a chain of seven operations ran at 1.7 / 3.3 / 5.7 TB/s with
+  // 2 / 4 / 8 vectors per pass (a single operation: 6.0 / 6.4 / 6.5 TB/s).
+  int vectors = 8;
+  if (const char *forced = std::getenv("HC_CUDA_MAP_VECTORS"))  // tuning aid: 2, 4 or 8
+    vectors = std::atoi(forced);
+#define HC_LAUNCH_MAP(V)                                                                          \
+  do {                                                                                            \
+    if (vec && two)                                                                               \
+      map_f32_kernel<true, true, V><<<grid, kThreads, 0, stream>>>(x, y, out, n, ops);            \
+    else if (vec)                                                                                 \
+      map_f32_kernel<true, false, V><<<grid, kThreads, 0, stream>>>(x, y, out, n, ops);           \
+    else if (two)                                                                                 \
+      map_f32_kernel<false, true, V><<<grid, kThreads, 0, stream>>>(x, y, out, n, ops);           \
+    else                                                                                          \
+      map_f32_kernel<false, false, V><<<grid, kThreads, 0, stream>>>(x, y, out, n, ops);          \
+  } while (0)
+  if (vectors == 4)
+    HC_LAUNCH_MAP(4);
+  else if (vectors == 2)
+    HC_LAUNCH_MAP(2);
   else
-    map_f32_kernel<false, false><<<grid, kThreads, 0, stream>>>(x, y, out, n, ops);
+    HC_LAUNCH_MAP(8);
+#undef HC_LAUNCH_MAP
   return cudaGetLastError();
 }
 
