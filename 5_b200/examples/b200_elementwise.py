@@ -2,12 +2,13 @@
 
     python 5_b200/examples/b200_elementwise.py [--n 1000003]
 
-Two kernels of the one-dimensional load / compute / store class:
+Kernels of the masked load / element-wise / store class:
 
   add_two       the reference simulator's own masked vector test
                 (tests/test_simulator.py:210-224): y = x + 2, four elements per workgroup;
   scaled_clamp  out = maximum(y - (0.5 * x - 1), 0.25) * -3 + y on float32 buffers, 64 elements
-                per workgroup: a chain of element-wise statements with a second input.
+                per workgroup: a chain of element-wise statements with a second input;
+  affine_relu_2d  out = maximum(0, 2 * x + shift) on matrices, one 8 x 32 tile per workgroup.
 
 The file only uses the public `hc` surface, so it means the same thing under either `hc` package:
 with the reference's, `hc.simulator.launch(add_two, x, y)` interprets the body on the host; with
@@ -52,6 +53,18 @@ def scaled_clamp(group, x: Buffer[W, np.float32], y: Buffer[W, np.float32], out:
     group.store(out[gid:], -t * 3 + yv)
 
 
+M, N = sym.M, sym.N
+
+
+@kernel(work_shape=(M, N), group_shape=(8, 32))
+def affine_relu_2d(group, x: Buffer[M, N, np.float32], shift: Buffer[M, N, np.float32], out: Buffer[M, N, np.float32]) -> None:
+    """out = maximum(0, 2 * x + shift) on matrices, one 8 x 32 tile per workgroup."""
+    r0, c0 = group.work_offset
+    tile = group.load(x[r0 : r0 + 8, c0 : c0 + 32], shape=(8, 32))
+    other = group.load(shift[r0:, c0:], shape=(8, 32))
+    group.store(out[r0:, c0:], np.maximum(0.0, tile * 2 + other))
+
+
 def scaled_clamp_numpy(x, y):
     """The same statements on whole float32 arrays (what the kernel computes element by element)."""
     t = np.float32(HALF) * x - np.float32(1)
@@ -61,7 +74,8 @@ def scaled_clamp_numpy(x, y):
 
 @functools.lru_cache(maxsize=None)
 def compiled(name, device=None):
-    return hc.compile({"add_two": add_two, "scaled_clamp": scaled_clamp}[name], target=NVIDIA_TARGET, device=device)
+    kernels = {"add_two": add_two, "scaled_clamp": scaled_clamp, "affine_relu_2d": affine_relu_2d}
+    return hc.compile(kernels[name], target=NVIDIA_TARGET, device=device)
 
 
 def main(argv=None):

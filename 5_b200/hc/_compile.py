@@ -132,6 +132,15 @@ class CompiledKernel:
             ctx = x.ctx
             if any(buf.ctx is not ctx for buf in buffers):
                 raise LaunchError("device buffers must belong to one context")
+            if plan.rank == 2:
+                # The function is element-wise, so a matrix is its elements in row-major order.
+                for name, buf in zip(names, buffers):
+                    if buf.ld != buf.shape[1]:
+                        raise LaunchError(f"{name}: a two-dimensional element-wise kernel needs device matrices "
+                                          f"without row padding (pitch {buf.ld} for {buf.shape[1]} columns)")
+                flat = [type(buf).wrap(ctx, buf.ptr, (buf.shape[0] * buf.shape[1],), buf.dtype) for buf in buffers]
+                x, out = flat[0], flat[-1]
+                other = flat[1] if plan.other_param else None
             ctx.map(x, out, plan.ops, other=other)
             ctx.synchronize()
             return
@@ -147,10 +156,10 @@ class CompiledKernel:
             if arr is out:
                 if not direct:
                     staged[...] = out
-                return staged
-            return np.ascontiguousarray(arr)
+                return staged.reshape(-1)
+            return np.ascontiguousarray(arr).reshape(-1)  # (a matrix goes as its elements in row-major order)
 
-        ctx.map_host(host(x), staged, plan.ops, other=None if other is None else host(other))
+        ctx.map_host(host(x), staged.reshape(-1), plan.ops, other=None if other is None else host(other))
         if not direct:
             out[...] = staged
 

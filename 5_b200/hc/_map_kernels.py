@@ -15,6 +15,10 @@ the active elements that fall inside the output (hc/simulator.py:1441-1458). Wit
 work_shape=(W,), group_shape=(G,) and a load of exactly G elements the groups tile [0, W) once,
 so the kernel computes out[i] = f(x[i] [, y[i]]) for i < W and touches nothing else. The group
 size is not observable (doc/langref.md:694-697); the GPU kernel re-tiles to 128-bit vectors.
+The two-dimensional form is the same with one offset, one slice and one group extent per axis
+(`r0, c0 = group.work_offset`, `group.load(x[r0:, c0:], shape=(GM, GN))`, work_shape=(M, N)):
+the (GM, GN) workgroups tile the matrix once (hc/simulator.py:914-920), the function is
+element-wise, so the launch runs over the M * N elements in row-major order.
 
 As for the matmul family the body is matched statement by statement and anything else is refused
 with a diagnostic. `f` must be a chain of at most eight float32 operations, each with a constant
@@ -46,12 +50,13 @@ class MapContract:
     x_param: str                 # the input the chain starts from
     other_param: str | None      # the second input, if any operation uses it
     out_param: str               # the buffer that is stored to (may be an input: in place)
-    extent: Any                  # symbol name (str) or fixed int extent of all buffers
-    group_size: int              # G of the kernel as written (not observable on the GPU)
+    extent: Any                  # symbol name (str) or fixed int extent of all buffers; a pair for rank 2
+    group_size: Any              # G of the kernel as written (not observable on the GPU); a pair for rank 2
     ops: tuple[tuple, ...]       # ("scale", c) ("add", c) ("max", c) ("min", c) ("rsub", c) ("rmax", c)
     #                              ("rmin", c) ("add_other",) ("sub_other",) ("rsub_other",) ("mul_other",)
     #                              ("max_other",) ("min_other",) ("rmax_other",) ("rmin_other",), in order
     dtype: str = "float32"
+    rank: int = 1                # 1: vectors; 2: matrices tiled by (GM, GN) workgroups, elements in row-major order
 
 
 @dataclass(frozen=True)
@@ -197,33 +202,36 @@ def recognise_elementwise_map(kernel_fn: Any) -> tuple[MapContract | None, list[
                       f"found {len(params)} parameters")
     group = params[0]
     annotations = resolved_annotations(kernel_fn)
-    extent = None
+    extents: tuple | None = None
     for param in params[1:]:
         spec = annotations.get(param)
-        if type(spec).__name__ != "BufferSpec" or len(spec.dimensions) != 1:
-            return refuse(f"parameter `{param}` must be annotated as a rank-1 Buffer")
-        key = _dim_key(spec.dimensions[0])
-        if key is None or (extent is not None and key != extent):
-            return refuse("all buffers of an element-wise map must have one extent (the same symbol or integer)")
-        extent = key
+        if type(spec).__name__ != "BufferSpec" or len(spec.dimensions) not in (1, 2):
+            return refuse(f"parameter `{param}` must be annotated as a rank-1 or rank-2 Buffer")
+        keys = tuple(_dim_key(d) for d in spec.dimensions)
+        if None in keys or (extents is not None and keys != extents):
+            return refuse("all buffers of an element-wise map must have the same extents (the same symbols or integers)")
+        extents = keys
         if spec.dtype not in (None, "float32"):
             return refuse(f"`{param}` is Buffer[..., {spec.dtype}]; this target runs element-wise kernels on float32")
+    assert extents is not None
+    rank = len(extents)
 
-    # Geometry: work_shape == (extent,), group_shape == (G,) with a constant G.
+    # Geometry: work_shape == the buffers' extents, group_shape constant, one axis per buffer axis.
     work, group_shape = meta.work_shape, meta.group_shape
     work = work if isinstance(work, tuple) else (work,)
     group_shape = group_shape if isinstance(group_shape, tuple) else (group_shape,)
-    if len(work) != 1 or len(group_shape) != 1:
-        return refuse("work_shape and group_shape of an element-wise map must be one-dimensional")
-    group_size = _evaluate(group_shape[0], {})
-    if group_size is None or group_size <= 0:
+    if len(work) != rank or len(group_shape) != rank:
+        return refuse("work_shape and group_shape of an element-wise map must have one axis per buffer axis")
+    group_sizes = tuple(_evaluate(g, {}) for g in group_shape)
+    if any(g is None or g <= 0 for g in group_sizes):
         return refuse("group_shape must be a positive constant")
-    for probe in (1, 5, 4096, 1000003):
-        names = {extent: probe} if isinstance(extent, str) else {}
-        want = probe if isinstance(extent, str) else extent
-        if _evaluate(work[0], names) != want:
-            return refuse(f"work_shape must be the buffers' extent, one workitem per element (it evaluates to "
-                          f"{_evaluate(work[0], names)} for an extent of {want})")
+    for probe in ((1, 3), (5, 1), (4096, 17), (1000003, 2)):
+        names = {key: probe[axis] for axis, key in enumerate(extents) if isinstance(key, str)}
+        for axis, key in enumerate(extents):
+            want = names[key] if isinstance(key, str) else key
+            if _evaluate(work[axis], names) != want:
+                return refuse(f"work_shape must be the buffers' extent, one workitem per element (axis {axis} evaluates "
+                              f"to {_evaluate(work[axis], names)} for an extent of {want})")
 
     fn_node = _function_node(kernel_fn)
     if fn_node is None:
@@ -234,25 +242,41 @@ def recognise_elementwise_map(kernel_fn: Any) -> tuple[MapContract | None, list[
             isinstance(body[-1].value, ast.Constant) and body[-1].value.value is None)):
         body = body[:-1]
 
-    offset_names: set[str] = set()
+    offset_names: dict[str, int] = {}  # name -> axis of group.work_offset it holds
     exprs = _Expressions(consts)
     out_param: str | None = None
     result: _Chain | None = None
+    shape_text = "(" + ", ".join(str(g) for g in group_sizes) + ("," if rank == 1 else "") + ")"
+    window_text = "buf[" + ", ".join(f"o{axis}:" for axis in range(rank)) + "]" if rank > 1 else "buf[gid:]"
 
     def window_of(node: ast.AST) -> str | None:
-        """`buf[gid:]` or `buf[gid:gid + G]` -> buf."""
-        if not (isinstance(node, ast.Subscript) and isinstance(node.value, ast.Name) and node.value.id in params[1:]
-                and isinstance(node.slice, ast.Slice) and node.slice.step is None
-                and isinstance(node.slice.lower, ast.Name) and node.slice.lower.id in offset_names):
+        """`buf[gid:]` / `buf[gid:gid + G]` (one slice per axis, each from that axis' work offset) -> buf."""
+        if not (isinstance(node, ast.Subscript) and isinstance(node.value, ast.Name) and node.value.id in params[1:]):
             return None
-        upper = node.slice.upper
-        if upper is not None:
-            ok = (isinstance(upper, ast.BinOp) and isinstance(upper.op, ast.Add)
-                  and isinstance(upper.left, ast.Name) and upper.left.id == node.slice.lower.id
-                  and _const(upper.right, consts) == group_size)
-            if not ok:
+        parts = list(node.slice.elts) if isinstance(node.slice, ast.Tuple) else [node.slice]
+        if len(parts) != rank:
+            return None
+        for axis, part in enumerate(parts):
+            if not (isinstance(part, ast.Slice) and part.step is None and isinstance(part.lower, ast.Name)
+                    and offset_names.get(part.lower.id) == axis):
                 return None
+            upper = part.upper
+            if upper is not None:
+                ok = (isinstance(upper, ast.BinOp) and isinstance(upper.op, ast.Add)
+                      and isinstance(upper.left, ast.Name) and upper.left.id == part.lower.id
+                      and _const(upper.right, consts) == group_sizes[axis])
+                if not ok:
+                    return None
         return node.value.id
+
+    def work_offset_axis(value: ast.AST | None) -> int | None:
+        """`group.work_offset[axis]` -> axis."""
+        if (isinstance(value, ast.Subscript) and isinstance(value.value, ast.Attribute)
+                and value.value.attr == "work_offset" and isinstance(value.value.value, ast.Name)
+                and value.value.value.id == group and isinstance(value.slice, ast.Constant)
+                and isinstance(value.slice.value, int) and 0 <= value.slice.value < rank):
+            return value.slice.value
+        return None
 
     for stmt in body:
         text = ast.unparse(stmt)
@@ -261,12 +285,16 @@ def recognise_elementwise_map(kernel_fn: Any) -> tuple[MapContract | None, list[
         target = (stmt.targets[0].id if isinstance(stmt, ast.Assign) and len(stmt.targets) == 1
                   and isinstance(stmt.targets[0], ast.Name) else None)
         value = stmt.value if isinstance(stmt, (ast.Assign, ast.Expr)) else None
-        # gid = group.work_offset[0]
-        if (target and isinstance(value, ast.Subscript) and isinstance(value.value, ast.Attribute)
-                and value.value.attr == "work_offset" and isinstance(value.value.value, ast.Name)
-                and value.value.value.id == group and isinstance(value.slice, ast.Constant)
-                and value.slice.value == 0):
-            offset_names.add(target)
+        # gid = group.work_offset[axis]   (or `r0, c0 = group.work_offset` for two axes)
+        if target and work_offset_axis(value) is not None:
+            offset_names[target] = work_offset_axis(value)
+            continue
+        if (isinstance(stmt, ast.Assign) and len(stmt.targets) == 1 and isinstance(stmt.targets[0], ast.Tuple)
+                and len(stmt.targets[0].elts) == rank and all(isinstance(e, ast.Name) for e in stmt.targets[0].elts)
+                and isinstance(value, ast.Attribute) and value.attr == "work_offset"
+                and isinstance(value.value, ast.Name) and value.value.id == group):
+            for axis, elt in enumerate(stmt.targets[0].elts):
+                offset_names[elt.id] = axis
             continue
         call = value if isinstance(value, ast.Call) else None
         func = call.func if call is not None else None
@@ -276,18 +304,18 @@ def recognise_elementwise_map(kernel_fn: Any) -> tuple[MapContract | None, list[
             source = window_of(call.args[0]) if len(call.args) == 1 else None
             keywords = {kw.arg: kw.value for kw in call.keywords}
             shape = keywords.get("shape")
-            shape_ok = (set(keywords) == {"shape"} and isinstance(shape, ast.Tuple) and len(shape.elts) == 1
-                        and _const(shape.elts[0], consts) == group_size)
+            shape_ok = (set(keywords) == {"shape"} and isinstance(shape, ast.Tuple) and len(shape.elts) == rank
+                        and tuple(_const(elt, consts) for elt in shape.elts) == group_sizes)
             if source is None or not shape_ok:
-                return refuse(f"`{text}` must load the group's own window, `{group}.vload(buf[gid:], shape=({group_size},))` "
-                              f"with gid = {group}.work_offset[0] and the group size as shape")
+                return refuse(f"`{text}` must load the group's own window, `{group}.vload({window_text}, shape={shape_text})` "
+                              f"with the offsets taken from {group}.work_offset and the group shape as shape")
             exprs.env[target] = _Chain(source, (), None)
             continue
         # group.store(out[gid:], <expression>)
         if isinstance(stmt, ast.Expr) and on_group and func.attr == "store" and len(call.args) == 2 and not call.keywords:
             out_param = window_of(call.args[0])
             if out_param is None:
-                return refuse(f"`{text}` must store to the group's own window, `{group}.store(out[gid:], vec)`")
+                return refuse(f"`{text}` must store to the group's own window, `{group}.store(out{window_text[3:]}, vec)`")
             result = exprs.chain(call.args[1])
             if result is None:
                 return refuse(exprs.why or "unsupported expression")
@@ -302,8 +330,9 @@ def recognise_elementwise_map(kernel_fn: Any) -> tuple[MapContract | None, list[
         return refuse(f"`{text}` is not part of the load / element-wise / store form")
 
     if out_param is None or result is None:
-        return refuse(f"the kernel must end with `{group}.store(out[gid:], vec)`")
+        return refuse(f"the kernel must end with `{group}.store(out{window_text[3:]}, vec)`")
     if len(result.ops) > MAX_MAP_OPS:
         return refuse(f"at most {MAX_MAP_OPS} element-wise operations are supported, found {len(result.ops)}")
     return MapContract(kernel_name=name, x_param=result.base, other_param=result.other, out_param=out_param,
-                       extent=extent, group_size=group_size, ops=result.ops), []
+                       extent=extents[0] if rank == 1 else extents, group_size=group_sizes[0] if rank == 1 else group_sizes,
+                       ops=result.ops, rank=rank), []

@@ -37,7 +37,8 @@ Fixtures (all produced by `hc.simulator.launch` on the example kernel):
   simmap_f32_seed15
       the masked element-wise kernels of 5_b200/examples/b200_elementwise.py: `add_two_x/_y` the
       reference's own vector test (tests/test_simulator.py:210-224), `x`, `y`, `out` the
-      scaled_clamp kernel on 1003 elements with NaN and infinities
+      scaled_clamp kernel on 1003 elements with NaN and infinities, `x_2d`, `shift_2d`, `out_2d` the
+      two-dimensional affine_relu_2d kernel on a 37 x 70 matrix
 The file blocked_reference.npz holds `reference_blocked_matmul` of the first four (the
 reference test's own comparison value, atol 2e-6).
 """
@@ -214,8 +215,18 @@ def main() -> int:
     out2 = np.full((1003,), np.float32(-7.0))
     with np.errstate(invalid="ignore"):
         ew.hc.simulator.launch(ew.scaled_clamp, x2, y2, out2)
-    np.savez_compressed(HERE / "simmap_f32_seed15.npz", add_two_x=x, add_two_y=y, x=x2, y=y2, out=out2)
-    print(f"simmap_f32_seed15: add_two{ x.shape } scaled_clamp{ x2.shape }", flush=True)
+    # The two-dimensional member: 8 x 32 tiles over a 37 x 70 matrix (ragged on both axes), with zeros of
+    # both signs where the maximum's tie rule shows.
+    x3 = rng.standard_normal((37, 70)).astype(np.float32)
+    s3 = rng.standard_normal((37, 70)).astype(np.float32)
+    x3[0, :4] = 0.0, -0.0, np.nan, np.inf
+    s3[0, :4] = -0.0, -0.0, 1.0, -np.inf
+    out3 = np.full((37, 70), np.float32(-7.0))
+    with np.errstate(invalid="ignore"):
+        ew.hc.simulator.launch(ew.affine_relu_2d, x3, s3, out3)
+    np.savez_compressed(HERE / "simmap_f32_seed15.npz", add_two_x=x, add_two_y=y, x=x2, y=y2, out=out2,
+                        x_2d=x3, shift_2d=s3, out_2d=out3)
+    print(f"simmap_f32_seed15: add_two{ x.shape } scaled_clamp{ x2.shape } affine_relu_2d{ x3.shape }", flush=True)
     return 0
 
 

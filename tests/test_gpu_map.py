@@ -40,6 +40,27 @@ def test_simulator_fixture_through_the_handles() -> None:
     assert np.array_equal(x, fixture["add_two_y"])
 
 
+def test_two_dimensional_kernel_matches_the_simulator(gpu_ctx) -> None:
+    with np.load(GOLDEN / "simmap_f32_seed15.npz") as data:
+        x, shift, want = data["x_2d"], data["shift_2d"], data["out_2d"]
+    out = np.full(want.shape, np.float32(-7.0))
+    compiled("affine_relu_2d")(x, shift, out)
+    assert same_bits(out.reshape(-1), want.reshape(-1))
+    # Views that are not contiguous are staged; the rest of the parent array stays as it was.
+    parent = np.full((37, 80), np.float32(-7.0))
+    compiled("affine_relu_2d")(np.asfortranarray(x), shift, parent[:, 5:75])
+    assert same_bits(np.ascontiguousarray(parent[:, 5:75]).reshape(-1), want.reshape(-1))
+    assert (parent[:, :5] == -7.0).all() and (parent[:, 75:] == -7.0).all()
+    dx, ds, dout = gpu_ctx.to_device(x), gpu_ctx.to_device(shift), gpu_ctx.empty(want.shape, np.float32)
+    compiled("affine_relu_2d")(dx, ds, dout)
+    assert same_bits(dout.to_numpy().reshape(-1), want.reshape(-1))
+    padded = cuda.DeviceBuffer(gpu_ctx, want.shape, np.float32, ld=72)
+    with pytest.raises(Exception, match="without row padding"):
+        compiled("affine_relu_2d")(dx, ds, padded)
+    for buf in (dx, ds, dout, padded):
+        buf.free()
+
+
 @pytest.mark.parametrize("n", [1, 3, 4, 5, 1023, 4096, 65537, 1 << 20, (1 << 22) + 3, 20_000_003])
 def test_against_the_oracle_on_device_buffers(n: int, gpu_ctx) -> None:
     rng = np.random.default_rng([n, 41])

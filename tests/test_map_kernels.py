@@ -16,6 +16,7 @@ from hc._pipeline import NVIDIA_SM100A
 from examples.b200_elementwise import add_two, compiled, scaled_clamp
 
 W, V = sym.W, sym.V
+M_, N_ = sym.M, sym.N
 THREE = 3
 WIDE = np.float64(0.1)
 
@@ -90,6 +91,49 @@ def test_spellings() -> None:
     assert (plan.x_param, plan.other_param, plan.ops) == ("a", "b", (("max_other",), ("sub_other",)))
 
 
+def test_two_dimensional_kernels() -> None:
+    from examples.b200_elementwise import affine_relu_2d
+
+    plan = hc.compile(affine_relu_2d, target=NVIDIA_SM100A).plan
+    assert isinstance(plan, MapContract) and plan.rank == 2
+    assert (plan.x_param, plan.other_param, plan.out_param) == ("x", "shift", "out")
+    assert plan.extent == ("M", "N") and plan.group_size == (8, 32)
+    assert plan.ops == (("scale", 2.0), ("add_other",), ("rmax", 0.0))
+
+    @kernel(work_shape=(M_, N_), group_shape=(8, 32))
+    def swapped(group, x: Buffer[M_, N_], out: Buffer[M_, N_]) -> None:
+        r0, c0 = group.work_offset
+        tile = group.load(x[c0:, r0:], shape=(8, 32))
+        group.store(out[r0:, c0:], tile + 1)
+
+    plan, why = recognise_elementwise_map(swapped)
+    assert plan is None and "must load the group's own window" in why[0]
+
+    @kernel(work_shape=(M_, N_), group_shape=(8, 32))
+    def wrong_shape(group, x: Buffer[M_, N_], out: Buffer[M_, N_]) -> None:
+        r0 = group.work_offset[0]
+        c0 = group.work_offset[1]
+        tile = group.load(x[r0 : r0 + 8, c0 : c0 + 32], shape=(32, 8))
+        group.store(out[r0:, c0:], tile + 1)
+
+    plan, why = recognise_elementwise_map(wrong_shape)
+    assert plan is None and "shape=(8, 32)" in why[0]
+
+    @kernel(work_shape=(M_,), group_shape=(8,))
+    def rank_mismatch(group, x: Buffer[M_, N_], out: Buffer[M_, N_]) -> None:
+        r0 = group.work_offset[0]
+        tile = group.load(x[r0:, r0:], shape=(8, 8))
+        group.store(out[r0:, r0:], tile + 1)
+
+    plan, why = recognise_elementwise_map(rank_mismatch)
+    assert plan is None and "one axis per buffer axis" in why[0]
+    handle = hc.compile(affine_relu_2d, target=NVIDIA_SM100A)
+    launch = handle.prepare(np.zeros((5, 7), np.float32), np.zeros((5, 7), np.float32), np.zeros((5, 7), np.float32))
+    assert launch.symbols == {"M": 5, "N": 7} and launch.group_counts == (1, 1)
+    with pytest.raises(hc.LaunchError, match="conflicting binding for N"):
+        handle(np.zeros((5, 7), np.float32), np.zeros((5, 8), np.float32), np.zeros((5, 7), np.float32))
+
+
 def _kernel(body: str, *, params="x: Buffer[W], y: Buffer[W]", work="(W,)", group_shape="(4,)", tmp_path=None, name="k"):
     import importlib.util
 
@@ -129,10 +173,11 @@ GOOD = "    gid = group.work_offset[0]\n    vec = group.vload(x[gid:], shape=(4,
         ("tail", {"body": GOOD + "\n    group.store(y[gid:], vec)"}, "follows the store"),
         ("no_store", {"body": GOOD.rsplit("\n", 1)[0]}, "must end with"),
         ("loop", {"body": GOOD + "\n    for i in range(2):\n        pass"}, "follows the store"),
-        ("extents", {"body": GOOD, "params": "x: Buffer[W], y: Buffer[V]"}, "must have one extent"),
+        ("extents", {"body": GOOD, "params": "x: Buffer[W], y: Buffer[V]"}, "must have the same extents"),
         ("dtype", {"body": GOOD, "params": "x: Buffer[W, np.float16], y: Buffer[W, np.float16]"},
          "runs element-wise kernels on float32"),
-        ("rank", {"body": GOOD, "params": "x: Buffer[W, V], y: Buffer[W]"}, "rank-1 Buffer"),
+        ("rank", {"body": GOOD, "params": "x: Buffer[W, V], y: Buffer[W]"}, "must have the same extents"),
+        ("rank3", {"body": GOOD, "params": "x: Buffer[W, V, 4], y: Buffer[W, V, 4]"}, "rank-1 or rank-2 Buffer"),
         ("work", {"body": GOOD, "work": "(W * 2,)"}, "work_shape must be the buffers' extent"),
         ("group", {"body": GOOD, "group_shape": "(W,)"}, "group_shape must be a positive constant"),
         ("many", {"body": GOOD.replace("vec + 2", "vec" + " + 1" * 9)}, "at most 8 element-wise operations"),

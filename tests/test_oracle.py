@@ -209,6 +209,15 @@ def test_elementwise_map_fixture() -> None:
     assert np.array_equal(np.isnan(out), np.isnan(want))
     keep = ~np.isnan(want)
     assert np.array_equal(out[keep].view(np.uint32), want[keep].view(np.uint32))
+    # The two-dimensional kernel (8 x 32 tiles over 37 x 70): element-wise, so the same restatement on the
+    # flattened matrices; np.maximum(0.0, v) returns v when neither is greater, so -0.0 survives.
+    ops2 = (("scale", 2.0), ("add_other",), ("rmax", 0.0))
+    out2 = cpu_ref.map_elementwise(fixture["x_2d"].reshape(-1), ops2, other=fixture["shift_2d"].reshape(-1))
+    want2 = fixture["out_2d"].reshape(-1)
+    assert np.signbit(want2[1]) and want2[1] == 0 and not np.signbit(want2[0]) and not (want2 == -7.0).any()
+    keep2 = ~np.isnan(want2)
+    assert np.array_equal(np.isnan(out2), ~keep2)
+    assert np.array_equal(out2[keep2].view(np.uint32), want2[keep2].view(np.uint32))
 
 
 def test_float8_kernel_fixtures() -> None:
