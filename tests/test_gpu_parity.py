@@ -1029,6 +1029,37 @@ def test_full_size_configs(name: str, gpu_ctx) -> None:
         buf.free()
 
 
+def test_config5_slab_at_full_size(gpu_ctx, monkeypatch) -> None:
+    """Config 5's per-rank problem at 8 GPUs, at full size on one GPU (16384 x 4096 x 16384, the last
+    rank's column slab, on the 512x256 tiles): sampled rows against float64 and the oracle, run-to-run
+    reproducibility, and the same bits from the 256x256 tiles."""
+    w = workloads.CONFIGS["sharded"]
+    lo, hi = w.n - w.n // 8, w.n
+    a, b = workloads.make_sharded_inputs(lo, hi)
+    assert gpu_ctx.plan(w.m, hi - lo, w.k, "float16").tiles_m == w.m // 512
+    da, db = gpu_ctx.to_device(a), gpu_ctx.to_device(b)
+    dc = gpu_ctx.empty((w.m, hi - lo), np.float32)
+    dc.fill_bytes(0xFF)
+    gpu_ctx.gemm(da, db, dc)
+    gpu_ctx.synchronize()
+    c = dc.to_numpy()
+    assert np.isfinite(c).all()
+    rows = _sample_rows(w.m)
+    assert workloads.check_against_float64(c, a, b, rows=rows)["ok"]
+    sample = np.ascontiguousarray(a[rows])
+    assert_close_to_oracle(np.ascontiguousarray(c[rows]), sample, b, expect=cpu_ref.matmul_k_ascending(sample, b))
+    gpu_ctx.gemm(da, db, dc)
+    gpu_ctx.synchronize()
+    assert np.array_equal(dc.to_numpy(), c)
+    monkeypatch.setenv("HC_CUDA_DENSE_WIDE", "0")
+    assert gpu_ctx.plan(w.m, hi - lo, w.k, "float16").tiles_m == w.m // 256
+    gpu_ctx.gemm(da, db, dc)
+    gpu_ctx.synchronize()
+    assert np.array_equal(dc.to_numpy(), c)
+    for buf in (da, db, dc):
+        buf.free()
+
+
 def test_config1_through_the_example_entry_point() -> None:
     a, b = workloads.make_inputs("sim_64")
     golden_a, golden_b, c_sim = load_golden("sim_f16_m64_n64_k64_normal_seed0")
