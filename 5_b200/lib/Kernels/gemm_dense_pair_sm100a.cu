@@ -102,7 +102,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Roles<kReadsC>::kThr
 gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                        const __grid_constant__ CUtensorMap tmap_b,
                        const __grid_constant__ CUtensorMap tmap_c, int c_tma,
-                       const __grid_constant__ CUtensorMap tmap_partials, void *c, int m, int n,
+                       const __grid_constant__ CUtensorMap tmap_partials,
+                       const __grid_constant__ PushMaps push_maps, void *c, int m, int n,
                        int k, long long ldc, uint32_t idesc, int tiles_m, int tiles_n, int group_n,
                        int l2_hints, int b_layout, int elem8, Epilogue ep, SplitK split, int *status) {
   extern __shared__ uint8_t smem_raw[];
@@ -301,7 +302,8 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
         drain_accumulator_rows<kColumnsPerWarp, kReadsC>(taddr, stage_gen, c, ldc, m, n, row_base, col_base, vec_ok,
                                                         lane, map_to_cta(tmem_empty_bar(acc), 0),
                                                         /*release_remote=*/true, ep, c_tma ? &tmap_c : nullptr,
-                                                        c_load_bar, &c_load_phase, abort_flag);
+                                                        c_load_bar, &c_load_phase, abort_flag,
+                                                        (c_tma && push_maps.count > 0) ? &push_maps : nullptr);
         continue;
       }
       // Split-k: the partial rows go to this unit's tile of the partials buffer (TMA stores, like
@@ -354,7 +356,7 @@ cudaError_t launch_gemm_dense_pair(const CUtensorMap &tmap_a, const CUtensorMap 
                                    int m, int n, int k, long long ldc, int dtype, int group_n,
                                    int max_ctas, int b_layout, const Epilogue &ep, const CUtensorMap *tmap_c,
                                    const SplitK &split, const CUtensorMap *tmap_partials, int *status,
-                                   cudaStream_t stream) {
+                                   cudaStream_t stream, const PushMaps *push_maps) {
   using namespace dense_pair;
   static thread_local int configured_device = -1;
   int device = 0;
@@ -403,7 +405,13 @@ cudaError_t launch_gemm_dense_pair(const CUtensorMap &tmap_a, const CUtensorMap 
   if (ep.c_dtype != kCTypeF32 && (ep.accumulate != 0 || ep.push_count != 0))
     return cudaErrorInvalidValue;  // rejected with a message by the caller's validation
   Epilogue launch_ep = ep;
-  const bool tma_possible = tmap_c != nullptr && ep.push_count == 0;
+  // With push targets the tiles leave through TMA stores too when the caller supplies the targets'
+  // tensor maps and the launch is the plain or element-wise product on whole tiles (an accumulating
+  // or split launch keeps the ordinary peer stores: the value the peers need exists in registers
+  // only there).
+  const bool tma_push = tmap_c != nullptr && push_maps != nullptr && push_maps->count == ep.push_count &&
+                        ep.push_count > 0 && ep.accumulate == 0 && split.splits == 1 && ep.c_dtype == kCTypeF32;
+  const bool tma_possible = tmap_c != nullptr && (ep.push_count == 0 || tma_push);
   launch_ep.accumulate_by_tma = (tma_possible && ep.accumulate != 0 && ep.op_count == 0) ? 1 : 0;
   launch_ep.accumulate_by_tma_load =
       (tma_possible && ep.accumulate != 0 && ep.op_count != 0 && split.splits == 1) ? 1 : 0;
@@ -412,16 +420,19 @@ cudaError_t launch_gemm_dense_pair(const CUtensorMap &tmap_a, const CUtensorMap 
   const int c_tma = (tma_possible && !reads_c) ? 1 : 0;
   const CUtensorMap c_map = c_tma ? *tmap_c : tmap_a;  // unused unless c_tma
   const CUtensorMap p_map = split.splits > 1 ? *tmap_partials : tmap_a;  // unused unless split
+  PushMaps no_push;
+  no_push.count = 0;
+  const PushMaps &push_arg = tma_push ? *push_maps : no_push;
   int l2_hints = 3;
   if (const char *h = std::getenv("HC_CUDA_L2_HINTS"))  // tuning aid
     l2_hints = std::atoi(h);
   const unsigned grid = static_cast<unsigned>(clusters * 2);
   if (reads_c)
     gemm_dense_pair_kernel<true><<<grid, Roles<true>::kThreads, kSmemBytes, stream>>>(
-        tmap_a, tmap_b, c_map, c_tma, p_map, c, m, n, k, ldc, idesc, tiles_m, tiles_n, group_n, l2_hints, b_layout, elem8, launch_ep, split, status);
+        tmap_a, tmap_b, c_map, c_tma, p_map, push_arg, c, m, n, k, ldc, idesc, tiles_m, tiles_n, group_n, l2_hints, b_layout, elem8, launch_ep, split, status);
   else
     gemm_dense_pair_kernel<false><<<grid, Roles<false>::kThreads, kSmemBytes, stream>>>(
-        tmap_a, tmap_b, c_map, c_tma, p_map, c, m, n, k, ldc, idesc, tiles_m, tiles_n, group_n, l2_hints, b_layout, elem8, launch_ep, split, status);
+        tmap_a, tmap_b, c_map, c_tma, p_map, push_arg, c, m, n, k, ldc, idesc, tiles_m, tiles_n, group_n, l2_hints, b_layout, elem8, launch_ep, split, status);
   return cudaGetLastError();
 }
 

@@ -466,9 +466,12 @@ __device__ __forceinline__ void write_chunk(const uint32_t (&r)[32], int chunk, 
 // elected lane issues a 32x32 box store. Rows >= m and columns >= n are clipped by the tensor map.
 // Needs C's base and pitch 16-byte aligned; `buf` is 1024-byte aligned.
 // `add`: the box is added to C (TMA reduction) instead of replacing it.
+// `push`: the same box also goes to every push target (the peers' copies of C), one more TMA store
+// per target from the same staged block.
 __device__ __forceinline__ void store_chunk_tma(const uint32_t (&r)[32], int chunk, float *buf,
                                                 const CUtensorMap *tmap_c, int m, int n, int row_base,
-                                                int col_base, int lane, bool add = false) {
+                                                int col_base, int lane, bool add = false,
+                                                const PushMaps *push = nullptr) {
   const int col0 = col_base + chunk * 32;
   if (col0 >= n || row_base >= m)
     return;  // warp-uniform
@@ -483,6 +486,9 @@ __device__ __forceinline__ void store_chunk_tma(const uint32_t (&r)[32], int chu
       tma_reduce_add_2d(tmap_c, smem_u32(buf), col0, row_base);
     else
       tma_store_2d(tmap_c, smem_u32(buf), col0, row_base);
+    if (push != nullptr)
+      for (int t = 0; t < push->count; ++t)
+        tma_store_2d(&push->map[t], smem_u32(buf), col0, row_base);
     tma_store_commit();
   }
 }
@@ -631,7 +637,8 @@ __device__ __forceinline__ void drain_accumulator_rows(uint32_t taddr, float *st
                                                        uint32_t release_bar, bool release_remote,
                                                        const Epilogue &ep, const CUtensorMap *tmap_c,
                                                        uint32_t c_load_bar = 0, uint32_t *c_load_phase = nullptr,
-                                                       volatile uint32_t *abort_flag = nullptr) {
+                                                       volatile uint32_t *abort_flag = nullptr,
+                                                       const PushMaps *push_maps = nullptr) {
   constexpr int kChunks = kColumns / 32;
   static_assert(kChunks % 2 == 0, "chunks are processed in pairs");
   if constexpr (!kReadsC) {
@@ -660,7 +667,7 @@ __device__ __forceinline__ void drain_accumulator_rows(uint32_t taddr, float *st
       accumulate_chunk_tma(ra, chunk, stage, tmap_c, m, n, row_base, col_base, lane, c_load_bar, *c_load_phase,
                            abort_flag, ep);
     else if (tma)
-      store_chunk_tma(ra, chunk, stage, tmap_c, m, n, row_base, col_base, lane, tma_add);
+      store_chunk_tma(ra, chunk, stage, tmap_c, m, n, row_base, col_base, lane, tma_add, push_maps);
     else
       write_chunk<kReadsC>(ra, chunk, false, stage, c, ldc, m, n, row_base, col_base, vec_ok, lane, carry, ep);
     tmem_load_wait_for(rb);
@@ -683,7 +690,7 @@ __device__ __forceinline__ void drain_accumulator_rows(uint32_t taddr, float *st
       accumulate_chunk_tma(rb, chunk + 1, stage, tmap_c, m, n, row_base, col_base, lane, c_load_bar, *c_load_phase,
                            abort_flag, ep);
     else if (tma)
-      store_chunk_tma(rb, chunk + 1, stage, tmap_c, m, n, row_base, col_base, lane, tma_add);
+      store_chunk_tma(rb, chunk + 1, stage, tmap_c, m, n, row_base, col_base, lane, tma_add, push_maps);
     else
       write_chunk<kReadsC>(rb, chunk + 1, chunk + 2 >= kChunks, stage, c, ldc, m, n, row_base, col_base, vec_ok, lane,
                           carry, ep);

@@ -39,6 +39,15 @@ constexpr int kStatusDeviceWaitTimeout = 5;
 // computed (plain peer stores; nothing is ever loaded from a peer).
 constexpr int kMaxPushTargets = 7;
 
+// The push targets as tensor maps (same extents, pitch and 32 x 32 float32 box as C's own map): with
+// them the epilogue hands every staged chunk of a tile to the TMA store engine once per
+// destination -- C and each peer's copy -- instead of writing the peers' copies with 16-byte stores
+// from the warp. Stores only: nothing is loaded from a peer, and no multicast is involved.
+struct PushMaps {
+  CUtensorMap map[kMaxPushTargets];
+  int count;
+};
+
 // Element-wise work fused into the store of C. With `accumulate` the previous contents of C are
 // the starting value of the sum (the hc kernel that loads its accumulators from `c` before the
 // k-loop); `ops` then run in order on every element, mirroring the element-wise statements an
@@ -121,7 +130,7 @@ cudaError_t launch_gemm_dense_pair(const CUtensorMap &tmap_a, const CUtensorMap 
                                    int m, int n, int k, long long ldc, int dtype, int group_n,
                                    int max_ctas, int b_layout, const Epilogue &ep, const CUtensorMap *tmap_c,
                                    const SplitK &split, const CUtensorMap *tmap_partials, int *status,
-                                   cudaStream_t stream);
+                                   cudaStream_t stream, const PushMaps *push_maps = nullptr);
 
 // The pair kernel's big brother: 512x256 tiles per pair (a 256x256 accumulator per CTA, all of its
 // tensor memory), a quarter fewer operand bytes per flop, no overlap of epilogue and next k-loop.

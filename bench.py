@@ -52,7 +52,8 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # (bytes, where the figure comes from): ncu captures summarised under profiles/, NOT measured by
 # the run that prints them. Workloads without a capture carry no figure.
 NCU_DRAM_TRAFFIC = {
-    "gemm_8192": (1.317e9, "ncu capture, profiles/gemm_dense_pair_kernel__gemm_8192.md"),
+    "gemm_8192": (1.105e9, "ncu capture, profiles/gemm_dense_wide_kernel__gemm_8192.md"),
+    "gemm_8192:float8_e4m3fn": (0.618e9, "ncu capture, profiles/gemm_dense_wide_kernel__gemm_8192_float8.md (B stored [N, K])"),
     "skinny": (272.4e6, "ncu capture, profiles/gemm_skinny_kernel__skinny_8x16384x8192.md"),
     "ragged": (21.1e6, "ncu capture, profiles/ragged_4095x3073x1031__launches.md (GEMM kernel only)"),
 }
