@@ -107,6 +107,17 @@ def _rank_main(rank: int, world: int, out_dir: str) -> None:
     exchange("done", b"1")           # every rank's pushes have landed
     np.save(Path(out_dir) / f"pushed_{rank}.npy", full_c.to_numpy())
     exchange("saved", b"1")
+    # The same push with the tiles handed to the TMA store engine once per destination.
+    os.environ["HC_CUDA_PUSH_TMA"] = "1"
+    full_c.fill_bytes(0xFF)
+    ctx.synchronize()
+    exchange("ready_tma", b"1")
+    pushed.run(da, db)
+    ctx.synchronize()
+    exchange("done_tma", b"1")
+    np.save(Path(out_dir) / f"pushed_tma_{rank}.npy", full_c.to_numpy())
+    exchange("saved_tma", b"1")
+    del os.environ["HC_CUDA_PUSH_TMA"]
     pushed.close()
     exchange("closed", b"1")         # no rank frees its C while a peer still maps it
     ctx.close()
@@ -145,6 +156,7 @@ def test_two_gpus_shard_and_gather(tmp_path) -> None:
         assert np.array_equal(full, first)  # every rank holds the same gathered C
         pushed = np.load(tmp_path / f"pushed_{r}.npy")
         assert np.array_equal(pushed, first)  # the fused push yields the same C, row-major, on every rank
+        assert np.array_equal(np.load(tmp_path / f"pushed_tma_{r}.npy"), first)  # and so do TMA stores to the peers
         # The host-array path (rows of A shared out, gathered over NVLink) gives the bits of the
         # device-buffer product of the same slab.
         host_slab, device_slab = np.load(tmp_path / f"host_slab_{r}.npy"), np.load(tmp_path / f"device_slab_{r}.npy")
