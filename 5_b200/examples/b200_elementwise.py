@@ -81,12 +81,25 @@ def compiled(name, device=None):
 def main(argv=None):
     parser = argparse.ArgumentParser(description="hc element-wise kernels on a B200")
     parser.add_argument("--n", type=int, default=1000003)
+    parser.add_argument("--device", action="store_true",
+                        help="keep the buffers on the GPU: one launch over all n elements per kernel (for profiling)")
     args = parser.parse_args(argv)
     rng = np.random.default_rng(0)
     x = rng.standard_normal(args.n).astype(np.float32)
     y = rng.standard_normal(args.n).astype(np.float32)
     out = np.zeros_like(x)
-    compiled("scaled_clamp")(x, y, out)
+    if args.device:
+        from hc import cuda
+
+        ctx = cuda.default_context()
+        dx, dy, dout = ctx.to_device(x), ctx.to_device(y), ctx.empty((args.n,), np.float32)
+        compiled("add_two")(dx, dout)
+        if not np.array_equal(dout.to_numpy(), x + np.float32(2)):
+            raise SystemExit("add_two differs")
+        compiled("scaled_clamp")(dx, dy, dout)
+        out = dout.to_numpy()
+    else:
+        compiled("scaled_clamp")(x, y, out)
     print(f"{compiled('scaled_clamp')!r}")
     same = np.array_equal(out, scaled_clamp_numpy(x, y))
     print(f"n={args.n}: bit-identical to NumPy: {same}")
