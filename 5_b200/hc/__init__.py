@@ -3,8 +3,10 @@
 The public names are those of the reference package (hc/__init__.py:11-63). `hc.compile`
 gains `target="nvidia-sm100a"`, which makes the returned handle launch hand-written sm_100a
 kernels through the C ABI of include/hc-c/Cuda.h; `hc.cuda` exposes that ABI (contexts,
-device buffers, pinned arrays) and `hc.distributed` the N-sharding helpers. `hc.symbols`
-and `hc.cuda` load lazily, as `symbols` does in the reference.
+device buffers, pinned arrays) and `hc.distributed` the N-sharding helpers;
+`hc.simulator.launch(fn, *args)`, the reference's launch entry point, runs the kernel on the GPU
+through the same handle. `hc.symbols`, `hc.cuda` and the others load lazily, as `symbols` does in
+the reference.
 """
 
 from __future__ import annotations
@@ -26,11 +28,11 @@ __all__ = [
     "Buffer", "BufferSpec", "CompiledKernel", "CurrentGroup", "DeviceError", "IdxTypeSpec",
     "IndexMap", "LaunchError", "Result", "Scope", "SimulatorError", "SubGroup", "Symbol",
     "TensorTypeSpec", "UndefTypeSpec", "VectorTypeSpec", "WorkGroup", "WorkItem", "as_layout",
-    "compile", "cuda", "distributed", "idx_type", "index_map", "kernel", "sym", "symbols",
+    "compile", "cuda", "distributed", "idx_type", "index_map", "kernel", "simulator", "sym", "symbols",
     "tensor_type", "undef_type", "vector_type",
 ]
 
-_LAZY_MODULES = {"symbols", "cuda", "distributed"}
+_LAZY_MODULES = {"symbols", "cuda", "distributed", "simulator"}
 
 
 def __getattr__(name: str) -> Any:

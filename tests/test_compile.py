@@ -643,3 +643,48 @@ print("ok")
                             capture_output=True, text=True, timeout=120, cwd=str(REPO / "tests"))
     assert result.returncode == 0, result.stderr
     assert result.stdout.strip() == "ok"
+
+
+def test_simulator_launch_entry_point_runs_the_target() -> None:
+    """`hc.simulator.launch(fn, *args)`, the reference's launch call, compiles for the NVIDIA target and
+    launches: same binding errors, zero-sized work is a no-op, an unrecognised kernel is refused (there
+    is no simulator to fall back to)."""
+    import hc.simulator as sim
+
+    kern = tiled_wmma_matmul_for("float16")
+    handle = sim.compiled(kern)
+    assert handle.plan is not None and handle.target == NVIDIA_SM100A and sim.compiled(kern) is handle
+    assert sim.run is sim.launch
+    a, b, c = _buffers(0, 8, 16)
+    assert sim.launch(kern, a, b, c) is None  # zero-sized work: no CUDA library is touched
+    with pytest.raises(sim.LaunchError, match="conflicting binding for K"):
+        sim.launch(kern, np.zeros((4, 4), np.float16), np.zeros((5, 4), np.float16), np.zeros((4, 4), np.float32))
+    with pytest.raises(sim.LaunchError, match="expects a function decorated with @kernel"):
+        sim.launch(lambda group: None)
+    with pytest.raises(sim.LaunchError, match="takes no simulator target"):
+        sim.launch(kern, a, b, c, target=object())
+    with pytest.raises(NotImplementedError, match="cannot launch"):
+        sim.launch(_family(windows="constant"), *_buffers(16, 16, 16))
+
+
+@pytest.mark.skipif(not REFERENCE.exists(), reason="the reference checkout is not on this machine")
+def test_the_reference_example_module_runs_against_this_package() -> None:
+    """The reference's example file, imported as it is with this package as `hc`: its own entry point
+    `simulate_gfx11_wmma_matmul` reaches the GPU launch through `hc.simulator.launch` (checked here as
+    far as a machine without a GPU goes: compilation, binding, the zero-sized launch)."""
+    import importlib.util
+
+    import hc.simulator as sim
+
+    spec = importlib.util.spec_from_file_location("reference_example_under_b200",
+                                                  REFERENCE / "examples" / "amdgpu_gfx11_wmma_matmul.py")
+    example = importlib.util.module_from_spec(spec)
+    sys.modules[spec.name] = example
+    spec.loader.exec_module(example)
+    assert example.sim is sim
+    handle = sim.compiled(example.tiled_gfx11_wmma_matmul)
+    assert handle.plan is not None and handle.plan.intrinsic_name == "wmma_gfx11", handle.pipeline_diagnostics
+    out = example.simulate_gfx11_wmma_matmul(np.zeros((0, 16), np.float16), np.zeros((16, 8), np.float16))
+    assert out.shape == (0, 8)
+    with pytest.raises(ValueError, match="must match"):
+        example.simulate_gfx11_wmma_matmul(np.zeros((4, 4), np.float16), np.zeros((5, 4), np.float16))

@@ -58,6 +58,17 @@ def test_handle_matches_reference_simulator_output(name: str) -> None:
     assert_close_to_oracle(c, a, b, expect=c_sim)
 
 
+def test_simulator_launch_entry_point(gpu_ctx) -> None:
+    """`hc.simulator.launch(kernel, a, b, c)`, the call the reference's example makes, on the GPU."""
+    import hc.simulator as sim
+    from examples.b200_wmma_matmul import tiled_wmma_matmul_for
+
+    a, b, c_sim = load_golden("sim_f16_m17_n19_k18_seed7")
+    c = np.full(c_sim.shape, np.nan, np.float32)
+    assert sim.launch(tiled_wmma_matmul_for("float16"), a, b, c) is None
+    assert_close_to_oracle(c, a, b, expect=c_sim)
+
+
 def test_reference_tests_own_tolerance_on_its_shapes() -> None:
     # tests/test_examples.py:22-33 of the reference uses atol=2e-6 against its blocked product;
     # the tensor-core result stays inside 1e-5 of it at these sizes (K <= 32, |values| <= 1).
