@@ -43,7 +43,7 @@ constexpr int kStages = 4;
 constexpr int kMaxEpilogueWarps = 8;
 template <bool kReadsC>
 struct Roles {
-  static constexpr int kEpilogueWarps = kReadsC ? 4 : 8;
+  static constexpr int kEpilogueWarps = 8;
   static constexpr int kThreads = 64 + 32 * kEpilogueWarps;
 };
 constexpr int kTmemColumns = 512;  // two fp32 accumulators of kBlockN columns

@@ -75,38 +75,6 @@ __device__ __forceinline__ float finish_value(float v, const float *dst, int col
   return v;
 }
 
-// Four consecutive values of one row, all inside C, `dst` 16-byte aligned.
-__device__ __forceinline__ float4 finish_group(float4 v, const float *dst, int col, const Epilogue &ep) {
-  if (ep.accumulate) {
-    const float4 old = __ldcs(reinterpret_cast<const float4 *>(dst));
-    v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
-  }
-#pragma unroll
-  for (int i = 0; i < kMaxEpilogueOps; ++i) {
-    if (i < ep.op_count) {
-      const int kind = ep.op_kind[i];
-      float4 x;
-      if (kind == kEpilogueBiasColumn) {
-        x = make_float4(__ldg(ep.bias + col), __ldg(ep.bias + col + 1), __ldg(ep.bias + col + 2),
-                        __ldg(ep.bias + col + 3));
-      } else {
-        const float s = ep.op_value[i];
-        x = make_float4(s, s, s, s);
-      }
-      if (kind == kEpilogueScale) {
-        v.x *= x.x; v.y *= x.y; v.z *= x.z; v.w *= x.w;
-      } else if (kind == kEpilogueMax) {
-        v.x = max_nan(v.x, x.x); v.y = max_nan(v.y, x.y); v.z = max_nan(v.z, x.z); v.w = max_nan(v.w, x.w);
-      } else if (kind == kEpilogueMin) {
-        v.x = min_nan(v.x, x.x); v.y = min_nan(v.y, x.y); v.z = min_nan(v.z, x.z); v.w = min_nan(v.w, x.w);
-      } else {
-        v.x += x.x; v.y += x.y; v.z += x.z; v.w += x.w;
-      }
-    }
-  }
-  return v;
-}
-
 // The operations on the eight groups a lane stores per chunk. The kind of each operation is the
 // same for the whole grid, so it is branched on once per chunk and the work inside is one
 // instruction per value. `bias_of(i)` gives the four bias values of group i.
@@ -146,19 +114,6 @@ __device__ __forceinline__ void apply_ops_to_groups(float4 (&v)[8], const Epilog
       }
     }
   }
-}
-
-// Previous contents of four consecutive elements of C starting at column `col` (zeros past n).
-// `aligned`: dst is 16-byte aligned, so a full group is one 128-bit load.
-__device__ __forceinline__ float4 load_previous(const float *dst, int col, int n, bool aligned) {
-  if (aligned && col + 3 < n)
-    return __ldcs(reinterpret_cast<const float4 *>(dst));
-  float4 old = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-  if (col < n) old.x = __ldcs(dst);
-  if (col + 1 < n) old.y = __ldcs(dst + 1);
-  if (col + 2 < n) old.z = __ldcs(dst + 2);
-  if (col + 3 < n) old.w = __ldcs(dst + 3);
-  return old;
 }
 
 // With an accumulating kernel the epilogue reads C before it writes it. Each lane asks for the
@@ -254,48 +209,258 @@ __device__ __forceinline__ void stage_row_shifted(const uint32_t (&r)[32], float
   }
 }
 
-// Writes one 32-column chunk (already in registers, lane = row) of this warp's 32 rows to C.
-// `carry` holds the last three values of this lane's row from the previous chunk (odd-pitch
-// path only); `last_chunk` says that no further chunk of the tile follows.
-// kReadsC: the launch adds to C's previous contents and has to read them here (an accumulating
-// kernel whose stores cannot do the addition); the operations then run here too, after that
-// addition. Otherwise the operations have already been applied to `r` and this is a plain store.
-template <bool kReadsC>
-__device__ __forceinline__ void write_chunk(const uint32_t (&r)[32], int chunk, bool last_chunk, float *buf,
-                                            float *__restrict__ c, long long ldc, int m, int n,
-                                            int row_base, int col_base, bool vec_ok, int lane,
-                                            float (&carry)[3], const Epilogue &ep) {
+// v + previous (the element's old value, when accumulating), then the operations; `bias`: of the element's column.
+__device__ __forceinline__ float finish_loaded(float v, float previous, float bias, const Epilogue &ep) {
+  v += previous;
+#pragma unroll
+  for (int i = 0; i < kMaxEpilogueOps; ++i) {
+    if (i < ep.op_count) {
+      const int kind = ep.op_kind[i];
+      const float x = kind == kEpilogueBiasColumn ? bias : ep.op_value[i];
+      v = kind == kEpilogueScale ? v * x
+        : kind == kEpilogueMax   ? max_nan(v, x)
+        : kind == kEpilogueMin   ? min_nan(v, x)
+                                 : v + x;
+    }
+  }
+  return v;
+}
+
+// Previous contents of four consecutive elements of C starting at column `col` (zeros past n);
+// `src` is 16-byte aligned, so a group that lies inside C is one 128-bit load.
+__device__ __forceinline__ float4 load_previous(const float *src, int col, int n) {
+  if (col + 3 < n)
+    return __ldcs(reinterpret_cast<const float4 *>(src));
+  float4 old = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  if (col < n) old.x = __ldcs(src);
+  if (col + 1 < n) old.y = __ldcs(src + 1);
+  if (col + 2 < n) old.z = __ldcs(src + 2);
+  return old;
+}
+
+// One 32-column chunk of an accumulating launch whose stores cannot do the addition (C's base or
+// pitch rules out TMA, push targets, or operations after the sum in a launch split over k): C's
+// previous contents are read here and the operations run here, after that addition.
+// The accesses are those of the plain writer below -- 8 lanes x 128 bits per row segment, each
+// row rotated to its own 16-byte phase when C's rows are not aligned -- and every read of the
+// chunk (the staged groups, the group that straddles the previous chunk, the single elements at
+// the ends of a tile row) is issued before its first store: a load cannot move above a store that
+// might alias it, so reads placed between the stores would each cost a full memory latency. The
+// tile's rows were prefetched into L2 during the k-loop.
+__device__ __forceinline__ void write_chunk_reading_c(const uint32_t (&r)[32], int chunk, bool last_chunk,
+                                                      float *buf, float *__restrict__ c, long long ldc, int m,
+                                                      int n, int row_base, int col_base, bool vec_ok, int lane,
+                                                      float (&carry)[6], const Epilogue &ep) {
   const int col0 = col_base + chunk * 32;
   if (col0 >= n)
     return;  // warp-uniform
   const int piece = lane & 7;
-  constexpr bool fused = kReadsC;
+  const bool acc = ep.accumulate != 0;
   // One bias value per lane (column col0 + lane); groups fetch theirs by shuffle.
   float bias_lane = 0.0f;
-  if (fused && ep.bias != nullptr && col0 + lane < n)
+  if (ep.bias != nullptr && col0 + lane < n)
     bias_lane = __ldg(ep.bias + col0 + lane);
+  float4 previous[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    previous[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
   if (vec_ok) {
     const int col = col0 + piece * 4;
-    // Everything that has to be read comes first, so that the reads of all eight row groups are
-    // in flight together instead of one after each store.
-    float4 previous[8];
-    float4 bias = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    if (fused) {
-      bias = make_float4(__shfl_sync(0xffffffffu, bias_lane, piece * 4), __shfl_sync(0xffffffffu, bias_lane, piece * 4 + 1),
-                         __shfl_sync(0xffffffffu, bias_lane, piece * 4 + 2), __shfl_sync(0xffffffffu, bias_lane, piece * 4 + 3));
-      if (ep.accumulate) {
+    if (acc) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int row = row_base + i * 4 + (lane >> 3);
-          previous[i] = row < m ? load_previous(c + static_cast<long long>(row) * ldc + col, col, n, true)
-                                : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      for (int i = 0; i < 8; ++i) {
+        const int row = row_base + i * 4 + (lane >> 3);
+        if (row < m)
+          previous[i] = load_previous(c + static_cast<long long>(row) * ldc + col, col, n);
+      }
+    }
+    const float4 bias =
+        make_float4(__shfl_sync(0xffffffffu, bias_lane, piece * 4), __shfl_sync(0xffffffffu, bias_lane, piece * 4 + 1),
+                    __shfl_sync(0xffffffffu, bias_lane, piece * 4 + 2), __shfl_sync(0xffffffffu, bias_lane, piece * 4 + 3));
+    stage_row_shifted<0>(r, buf, lane);
+    __syncwarp();
+    float4 v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int rr = i * 4 + (lane >> 3);
+      v[i] = *reinterpret_cast<const float4 *>(buf + rr * 32 + ((piece ^ (rr & 7)) << 2));
+      v[i].x += previous[i].x; v[i].y += previous[i].y; v[i].z += previous[i].z; v[i].w += previous[i].w;
+    }
+    apply_ops_to_groups(v, ep, [&](int) { return bias; });
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int row = row_base + i * 4 + (lane >> 3);
+      if (row < m) {
+        const long long offset = static_cast<long long>(row) * ldc + col;
+        float *dst = c + offset;
+        if (col + 3 < n) {
+          __stcs(reinterpret_cast<float4 *>(dst), v[i]);
+          for (int t = 0; t < ep.push_count; ++t)  // the peers' copies of C
+            __stcs(reinterpret_cast<float4 *>(ep.push[t] + offset), v[i]);
+        } else {
+          for (int t = -1; t < ep.push_count; ++t) {
+            float *edge = t < 0 ? dst : ep.push[t] + offset;
+            if (col < n) __stcs(edge, v[i].x);
+            if (col + 1 < n) __stcs(edge + 1, v[i].y);
+            if (col + 2 < n) __stcs(edge + 2, v[i].z);
+          }
         }
       }
     }
+    __syncwarp();
+    return;
+  }
+  // Rows that do not start on 16-byte boundaries: see write_chunk for the layout.
+  const unsigned phase0 = (static_cast<unsigned>(reinterpret_cast<uintptr_t>(c) >> 2) +
+                           static_cast<unsigned>(row_base) * static_cast<unsigned>(ldc & 3) +
+                           static_cast<unsigned>(col0)) & 3u;
+  const unsigned phase_step = static_cast<unsigned>(ldc & 3);
+  auto shift_of = [&](int rr) {
+    return static_cast<int>((4u - ((phase0 + static_cast<unsigned>(rr) * phase_step) & 3u)) & 3u);
+  };
+  float *tile_dst = c + static_cast<long long>(row_base) * ldc + col0;
+  // -- every read of the chunk --
+  // Row rr = 4 i + (lane >> 3) of the staged groups: its phase does not depend on i (four pitches are
+  // a multiple of 16 bytes), so a lane's groups start at the same element e0 of every row it serves.
+  const int e0 = shift_of(lane >> 3) + piece * 4;
+  if (acc && e0 + 3 < 32) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int rr = i * 4 + (lane >> 3);
+      if (row_base + rr < m)
+        previous[i] = load_previous(tile_dst + static_cast<long long>(rr) * ldc + e0, col0 + e0, n);
+    }
+  }
+  const int shift = shift_of(lane);
+  float *dst = tile_dst + static_cast<long long>(lane) * ldc;
+  const bool own = shift != 0 && row_base + lane < m;  // this lane writes the ragged ends of its row itself
+  const bool tail_now = last_chunk || col0 + 32 >= n;
+  // lead: old values of the group that straddles the previous chunk (chunk > 0) or of the elements
+  // before the first aligned group (chunk 0); tail: of the elements after the last aligned group.
+  float4 lead = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  float tail[3] = {0.0f, 0.0f, 0.0f};
+  if (acc && own) {
+    if (chunk == 0) {
+      if (col0 < n) lead.x = __ldcs(dst);
+      if (shift >= 2 && col0 + 1 < n) lead.y = __ldcs(dst + 1);
+      if (shift == 3 && col0 + 2 < n) lead.z = __ldcs(dst + 2);
+    } else {
+      lead = load_previous(dst + shift - 4, col0 + shift - 4, n);
+    }
+    if (tail_now) {
+#pragma unroll
+      for (int e = 29; e < 32; ++e)
+        if (e >= 28 + shift && col0 + e < n)
+          tail[e - 29] = __ldcs(dst + e);
+    }
+  }
+  // Bias values of the columns at the two ends of the chunk, for the elements a lane finishes itself
+  // (those of the previous chunk's last three columns travel in `carry`).
+  const float b0 = __shfl_sync(0xffffffffu, bias_lane, 0), b1 = __shfl_sync(0xffffffffu, bias_lane, 1),
+              b2 = __shfl_sync(0xffffffffu, bias_lane, 2);
+  const float b29 = __shfl_sync(0xffffffffu, bias_lane, 29), b30 = __shfl_sync(0xffffffffu, bias_lane, 30),
+              b31 = __shfl_sync(0xffffffffu, bias_lane, 31);
+  // -- stage, then the stores --
+  if (shift == 0)
+    stage_row_shifted<0>(r, buf, lane);
+  else if (shift == 1)
+    stage_row_shifted<1>(r, buf, lane);
+  else if (shift == 2)
+    stage_row_shifted<2>(r, buf, lane);
+  else
+    stage_row_shifted<3>(r, buf, lane);
+  if (own) {
+    const float f0 = __uint_as_float(r[0]), f1 = __uint_as_float(r[1]), f2 = __uint_as_float(r[2]);
+    if (chunk == 0) {
+      if (col0 < n) __stcs(dst, finish_loaded(f0, lead.x, b0, ep));
+      if (shift >= 2 && col0 + 1 < n) __stcs(dst + 1, finish_loaded(f1, lead.y, b1, ep));
+      if (shift == 3 && col0 + 2 < n) __stcs(dst + 2, finish_loaded(f2, lead.z, b2, ep));
+    } else {
+      // The straddling group: its first 4 - shift elements were kept from the previous chunk.
+      const float4 v = shift == 1 ? make_float4(carry[0], carry[1], carry[2], f0)
+                     : shift == 2 ? make_float4(carry[1], carry[2], f0, f1)
+                                  : make_float4(carry[2], f0, f1, f2);
+      const float4 vb = shift == 1 ? make_float4(carry[3], carry[4], carry[5], b0)
+                      : shift == 2 ? make_float4(carry[4], carry[5], b0, b1)
+                                   : make_float4(carry[5], b0, b1, b2);
+      float *group = dst + shift - 4;
+      const int group_col = col0 + shift - 4;
+      float4 out;  // (elements at or past column n are computed from zeros and not stored)
+      out.x = finish_loaded(v.x, lead.x, vb.x, ep);
+      out.y = finish_loaded(v.y, lead.y, vb.y, ep);
+      out.z = finish_loaded(v.z, lead.z, vb.z, ep);
+      out.w = finish_loaded(v.w, lead.w, vb.w, ep);
+      if (group_col + 3 < n) {
+        __stcs(reinterpret_cast<float4 *>(group), out);
+      } else {
+        __stcs(group, out.x);
+        if (group_col + 1 < n) __stcs(group + 1, out.y);
+        if (group_col + 2 < n) __stcs(group + 2, out.z);
+      }
+    }
+    if (tail_now) {
+#pragma unroll
+      for (int e = 29; e < 32; ++e)
+        if (e >= 28 + shift && col0 + e < n)
+          __stcs(dst + e, finish_loaded(__uint_as_float(r[e]), tail[e - 29], e == 29 ? b29 : (e == 30 ? b30 : b31), ep));
+    }
+  }
+  carry[0] = __uint_as_float(r[29]);
+  carry[1] = __uint_as_float(r[30]);
+  carry[2] = __uint_as_float(r[31]);
+  carry[3] = b29;
+  carry[4] = b30;
+  carry[5] = b31;
+  __syncwarp();
+  float4 v[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int rr = i * 4 + (lane >> 3);
+    v[i] = *reinterpret_cast<const float4 *>(buf + rr * 32 + ((piece ^ (rr & 7)) << 2));
+    v[i].x += previous[i].x; v[i].y += previous[i].y; v[i].z += previous[i].z; v[i].w += previous[i].w;
+  }
+  // (e0 + j) & 31: lanes whose groups are skipped below still take part in the shuffles.
+  const float4 bias =
+      make_float4(__shfl_sync(0xffffffffu, bias_lane, e0 & 31), __shfl_sync(0xffffffffu, bias_lane, (e0 + 1) & 31),
+                  __shfl_sync(0xffffffffu, bias_lane, (e0 + 2) & 31), __shfl_sync(0xffffffffu, bias_lane, (e0 + 3) & 31));
+  apply_ops_to_groups(v, ep, [&](int) { return bias; });
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int rr = i * 4 + (lane >> 3);
+    if (row_base + rr < m && e0 + 3 < 32) {
+      float *group = tile_dst + static_cast<long long>(rr) * ldc + e0;
+      if (col0 + e0 + 3 < n) {
+        __stcs(reinterpret_cast<float4 *>(group), v[i]);
+      } else {
+        if (col0 + e0 < n) __stcs(group, v[i].x);
+        if (col0 + e0 + 1 < n) __stcs(group + 1, v[i].y);
+        if (col0 + e0 + 2 < n) __stcs(group + 2, v[i].z);
+      }
+    }
+  }
+  __syncwarp();
+}
+
+// Writes one 32-column chunk (already in registers, lane = row, operations applied) of this warp's
+// 32 rows to C. `carry` holds the last three values of this lane's row from the previous chunk
+// (odd-pitch path only); `last_chunk` says that no further chunk of the tile follows.
+__device__ __forceinline__ void write_chunk(const uint32_t (&r)[32], int chunk, bool last_chunk, float *buf,
+                                            float *__restrict__ c, long long ldc, int m, int n,
+                                            int row_base, int col_base, bool vec_ok, int lane,
+                                            float (&carry)[6], const Epilogue &ep) {
+  const int col0 = col_base + chunk * 32;
+  if (col0 >= n)
+    return;  // warp-uniform
+  const int piece = lane & 7;
+  if (vec_ok) {
+    const int col = col0 + piece * 4;
     stage_row_shifted<0>(r, buf, lane);
     __syncwarp();
-    auto store_group_of_row = [&](int i, const float4 &value) {
-      const int row = row_base + i * 4 + (lane >> 3);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int rr = i * 4 + (lane >> 3);
+      const float4 value = *reinterpret_cast<const float4 *>(buf + rr * 32 + ((piece ^ (rr & 7)) << 2));
+      const int row = row_base + rr;
       if (row < m) {
         const long long offset = static_cast<long long>(row) * ldc + col;
         float *dst = c + offset;
@@ -313,27 +478,6 @@ __device__ __forceinline__ void write_chunk(const uint32_t (&r)[32], int chunk, 
           }
         }
       }
-    };
-    if constexpr (!kReadsC) {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int rr = i * 4 + (lane >> 3);
-        store_group_of_row(i, *reinterpret_cast<const float4 *>(buf + rr * 32 + ((piece ^ (rr & 7)) << 2)));
-      }
-    } else {
-      float4 v[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int rr = i * 4 + (lane >> 3);
-        v[i] = *reinterpret_cast<const float4 *>(buf + rr * 32 + ((piece ^ (rr & 7)) << 2));
-        if (ep.accumulate) {
-          v[i].x += previous[i].x; v[i].y += previous[i].y; v[i].z += previous[i].z; v[i].w += previous[i].w;
-        }
-      }
-      apply_ops_to_groups(v, ep, [&](int) { return bias; });
-#pragma unroll
-      for (int i = 0; i < 8; ++i)
-        store_group_of_row(i, v[i]);
     }
   } else {
     // C's rows do not start on 16-byte boundaries (odd pitch or base). For row r, `shift(r)`
@@ -351,12 +495,6 @@ __device__ __forceinline__ void write_chunk(const uint32_t (&r)[32], int chunk, 
       return static_cast<int>((4u - ((phase0 + static_cast<unsigned>(rr) * phase_step) & 3u)) & 3u);
     };
     float *tile_dst = c + static_cast<long long>(row_base) * ldc + col0;
-    auto store_value = [&](float *dst, float v, int col) {
-      __stcs(dst, fused ? finish_value(v, dst, col, ep) : v);
-    };
-    auto store_group = [&](float *dst, float4 v, int col) {
-      __stcs(reinterpret_cast<float4 *>(dst), fused ? finish_group(v, dst, col, ep) : v);
-    };
     {
       const int shift = shift_of(lane);
       float *dst = tile_dst + static_cast<long long>(lane) * ldc;
@@ -373,9 +511,9 @@ __device__ __forceinline__ void write_chunk(const uint32_t (&r)[32], int chunk, 
         const float f0 = __uint_as_float(r[0]), f1 = __uint_as_float(r[1]), f2 = __uint_as_float(r[2]);
         if (chunk == 0) {
           // Elements before the first aligned group of the tile row.
-          if (col0 < n) store_value(dst, f0, col0);
-          if (shift >= 2 && col0 + 1 < n) store_value(dst + 1, f1, col0 + 1);
-          if (shift == 3 && col0 + 2 < n) store_value(dst + 2, f2, col0 + 2);
+          if (col0 < n) __stcs(dst, f0);
+          if (shift >= 2 && col0 + 1 < n) __stcs(dst + 1, f1);
+          if (shift == 3 && col0 + 2 < n) __stcs(dst + 2, f2);
         } else {
           // The group that straddles the previous chunk and this one: its first 4 - shift
           // elements were kept from the previous chunk in `carry`.
@@ -385,19 +523,19 @@ __device__ __forceinline__ void write_chunk(const uint32_t (&r)[32], int chunk, 
           float *group = dst + shift - 4;
           const int group_col = col0 + shift - 4;
           if (group_col + 3 < n) {
-            store_group(group, v, group_col);
+            __stcs(reinterpret_cast<float4 *>(group), v);
           } else {
             // Only the elements left of column n exist (the previous chunk's are always inside).
-            store_value(group, v.x, group_col);
-            if (group_col + 1 < n) store_value(group + 1, v.y, group_col + 1);
-            if (group_col + 2 < n) store_value(group + 2, v.z, group_col + 2);
+            __stcs(group, v.x);
+            if (group_col + 1 < n) __stcs(group + 1, v.y);
+            if (group_col + 2 < n) __stcs(group + 2, v.z);
           }
         }
         if (last_chunk || col0 + 32 >= n) {
           // No next chunk will complete the trailing group: write its elements singly.
           for (int e = 28 + shift; e < 32; ++e)
             if (col0 + e < n)
-              store_value(dst + e, __uint_as_float(e == 29 ? r[29] : (e == 30 ? r[30] : r[31])), col0 + e);
+              __stcs(dst + e, __uint_as_float(e == 29 ? r[29] : (e == 30 ? r[30] : r[31])));
         }
       }
       carry[0] = __uint_as_float(r[29]);
@@ -405,21 +543,13 @@ __device__ __forceinline__ void write_chunk(const uint32_t (&r)[32], int chunk, 
       carry[2] = __uint_as_float(r[31]);
     }
     __syncwarp();
-    // The staged groups: reads of all eight row groups first, then the stores.
-    float4 previous[8];
-    if (fused && ep.accumulate) {
+    // Row rr = 4 i + (lane >> 3): its phase does not depend on i (four pitches are a multiple of 16
+    // bytes), so a lane's groups start at the same element e0 of every row it serves.
+    const int e0 = shift_of(lane >> 3) + piece * 4;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int rr = i * 4 + (lane >> 3);
-        const int e0 = shift_of(rr) + piece * 4;
-        previous[i] = (row_base + rr < m && e0 + 3 < 32)
-                          ? load_previous(tile_dst + static_cast<long long>(rr) * ldc + e0, col0 + e0, n, true)
-                          : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-      }
-    }
-    auto store_staged_group = [&](int i, const float4 &value) {
+    for (int i = 0; i < 8; ++i) {
       const int rr = i * 4 + (lane >> 3);
-      const int e0 = shift_of(rr) + piece * 4;
+      const float4 value = *reinterpret_cast<const float4 *>(buf + rr * 32 + ((piece ^ (rr & 7)) << 2));
       if (row_base + rr < m && e0 + 3 < 32) {
         float *dst = tile_dst + static_cast<long long>(rr) * ldc + e0;
         if (col0 + e0 + 3 < n) {
@@ -430,32 +560,6 @@ __device__ __forceinline__ void write_chunk(const uint32_t (&r)[32], int chunk, 
           if (col0 + e0 + 2 < n) __stcs(dst + 2, value.z);
         }
       }
-    };
-    if constexpr (!kReadsC) {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int rr = i * 4 + (lane >> 3);
-        store_staged_group(i, *reinterpret_cast<const float4 *>(buf + rr * 32 + ((piece ^ (rr & 7)) << 2)));
-      }
-    } else {
-      float4 v[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int rr = i * 4 + (lane >> 3);
-        v[i] = *reinterpret_cast<const float4 *>(buf + rr * 32 + ((piece ^ (rr & 7)) << 2));
-        if (ep.accumulate) {
-          v[i].x += previous[i].x; v[i].y += previous[i].y; v[i].z += previous[i].z; v[i].w += previous[i].w;
-        }
-      }
-      apply_ops_to_groups(v, ep, [&](int i) {
-        // (e0 + j) & 31: lanes whose group is skipped below still take part in the shuffles.
-        const int e0 = shift_of(i * 4 + (lane >> 3)) + piece * 4;
-        return make_float4(__shfl_sync(0xffffffffu, bias_lane, e0 & 31), __shfl_sync(0xffffffffu, bias_lane, (e0 + 1) & 31),
-                           __shfl_sync(0xffffffffu, bias_lane, (e0 + 2) & 31), __shfl_sync(0xffffffffu, bias_lane, (e0 + 3) & 31));
-      });
-#pragma unroll
-      for (int i = 0; i < 8; ++i)
-        store_staged_group(i, v[i]);
     }
   }
   __syncwarp();
@@ -650,7 +754,7 @@ __device__ __forceinline__ void drain_accumulator_rows(uint32_t taddr, float *st
   }
   float *__restrict__ c = static_cast<float *>(c_any);
   uint32_t ra[32], rb[32];
-  float carry[3] = {0.0f, 0.0f, 0.0f};
+  float carry[6] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
   // Stores of an aligned C go through TMA (`tmap_c` is null otherwise).
   const bool tma = !kReadsC && tmap_c != nullptr;
   const bool tma_add = ep.accumulate_by_tma != 0;
@@ -668,8 +772,10 @@ __device__ __forceinline__ void drain_accumulator_rows(uint32_t taddr, float *st
                            abort_flag, ep);
     else if (tma)
       store_chunk_tma(ra, chunk, stage, tmap_c, m, n, row_base, col_base, lane, tma_add, push_maps);
+    else if constexpr (kReadsC)
+      write_chunk_reading_c(ra, chunk, false, stage, c, ldc, m, n, row_base, col_base, vec_ok, lane, carry, ep);
     else
-      write_chunk<kReadsC>(ra, chunk, false, stage, c, ldc, m, n, row_base, col_base, vec_ok, lane, carry, ep);
+      write_chunk(ra, chunk, false, stage, c, ldc, m, n, row_base, col_base, vec_ok, lane, carry, ep);
     tmem_load_wait_for(rb);
     if (chunk + 2 < kChunks) {
       tmem_load_32x32b_x32(taddr + (chunk + 2) * 32, ra);
@@ -691,9 +797,12 @@ __device__ __forceinline__ void drain_accumulator_rows(uint32_t taddr, float *st
                            abort_flag, ep);
     else if (tma)
       store_chunk_tma(rb, chunk + 1, stage, tmap_c, m, n, row_base, col_base, lane, tma_add, push_maps);
+    else if constexpr (kReadsC)
+      write_chunk_reading_c(rb, chunk + 1, chunk + 2 >= kChunks, stage, c, ldc, m, n, row_base, col_base, vec_ok, lane,
+                            carry, ep);
     else
-      write_chunk<kReadsC>(rb, chunk + 1, chunk + 2 >= kChunks, stage, c, ldc, m, n, row_base, col_base, vec_ok, lane,
-                          carry, ep);
+      write_chunk(rb, chunk + 1, chunk + 2 >= kChunks, stage, c, ldc, m, n, row_base, col_base, vec_ok, lane, carry,
+                  ep);
   }
 }
 
@@ -717,7 +826,7 @@ __device__ __noinline__ void reduce_partials_rows(const float *partial_rows, int
                                                   int m, int n, int row_base, int col_base, bool vec_ok, int lane,
                                                   const Epilogue &ep, const CUtensorMap *tmap_c) {
   constexpr int kChunks = kColumns / 32;
-  float carry[3] = {0.0f, 0.0f, 0.0f};
+  float carry[6] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
   float *__restrict__ c = static_cast<float *>(c_any);
   const bool half_out = !kReadsC && ep.c_dtype != kCTypeF32;  // then `tmap_c` (64-column boxes) is not used here
   const bool tma = !kReadsC && tmap_c != nullptr && !half_out;
@@ -805,8 +914,11 @@ __device__ __noinline__ void reduce_partials_rows(const float *partial_rows, int
                           lane);
       continue;
     }
-    write_chunk<kReadsC>(r, chunk, chunk == kChunks - 1, stage, c, ldc, m, n, row_base, col_base, vec_ok, lane,
-                        carry, ep);
+    if constexpr (kReadsC)
+      write_chunk_reading_c(r, chunk, chunk == kChunks - 1, stage, c, ldc, m, n, row_base, col_base, vec_ok, lane, carry,
+                            ep);
+    else
+      write_chunk(r, chunk, chunk == kChunks - 1, stage, c, ldc, m, n, row_base, col_base, vec_ok, lane, carry, ep);
   }
 }
 
