@@ -27,6 +27,7 @@ SOURCES = [
     LIB_DIR / "Kernels" / "gemm_dense_sm100a.cu",
     LIB_DIR / "Kernels" / "gemm_dense_pair_sm100a.cu",
     LIB_DIR / "Kernels" / "gemm_dense_wide_sm100a.cu",
+    LIB_DIR / "Kernels" / "gemm_dense_cluster_sm100a.cu",
     LIB_DIR / "Kernels" / "gemm_skinny_sm100a.cu",
     LIB_DIR / "Kernels" / "repack_sm100a.cu",
     LIB_DIR / "Kernels" / "repack_bytes_sm100a.cu",

@@ -342,6 +342,29 @@ int plan_gemm(const HcCudaContext *ctx, const HcCudaGemmArgs *args, int sm_count
         first_split_tile = 0;
       }
     }
+    // When every tile would be split (fewer tiles than CTAs), a float32 C that TMA can address gets the
+    // cluster form instead: the CTAs that share a tile are one thread-block cluster and add their partial
+    // tiles through distributed shared memory, not through global memory and counters.
+    const char *cluster_env = std::getenv("HC_CUDA_DENSE_CLUSTER");  // tuning aid: a size forces the form
+    const bool cluster_forced = cluster_env != nullptr && std::atoi(cluster_env) >= 2;
+    if (((plan->splits > 1 && first_split_tile == 0 && std::getenv("HC_CUDA_DENSE_SPLITS") == nullptr) ||
+         cluster_forced) &&
+        c_tma_ok && args->c_dtype == HC_CUDA_C_F32 && !(ctx != nullptr && ctx->planning_push) &&
+        !(ctx != nullptr && ctx->planning_host_panels)) {
+      const hc::sm100::ClusterPlan cp = hc::sm100::dense_cluster_choose(m, n, k, static_cast<int>(es), sm_count);
+      if (cp.cluster_size >= 2) {
+        plan->cluster_size = cp.cluster_size;
+        plan->tiles_m = static_cast<int32_t>((m + t.block_m - 1) / t.block_m);
+        plan->tiles_n = static_cast<int32_t>((n + t.block_n - 1) / t.block_n);
+        plan->splits = cp.cluster_size * cp.groups;
+        plan->first_split_tile = 0;
+        plan->grid = plan->tiles_m * plan->tiles_n * plan->splits;
+        scratch += static_cast<int64_t>(hc::sm100::dense_cluster_partials_bytes(
+            static_cast<long long>(plan->tiles_m) * plan->tiles_n, cp.groups));
+        plan->scratch_bytes = scratch;
+        return HC_CUDA_OK;
+      }
+    }
     const int64_t split_tiles = plan->splits > 1 ? tiles - first_split_tile : 0;
     const int64_t units = tiles + split_tiles * (plan->splits - 1);
     plan->grid = static_cast<int32_t>((pairs ? 2 : 1) * (units < slots ? units : slots));
@@ -554,7 +577,8 @@ int enqueue_gemm(HcCudaContext *ctx, const HcCudaGemmArgs *args, const HcCudaGem
     // B stored [K, N]: 64 (n) x 64 (k) boxes. Stored [N, K]: one box of 64 (k) x the CTA's rows
     // of n (256 on single CTAs, 128 per CTA of a pair).
     if (int rc = b_nk_now ? encode_map(ctx, &tmap_b, args->dtype, b, k, n, static_cast<uint64_t>(ldb) * es,
-                                       t.block_k * k_scale, pairs ? t.block_n / 2 : t.block_n)
+                                       t.block_k * k_scale,
+                                       (pairs && plan.cluster_size == 0) ? t.block_n / 2 : t.block_n)
                           : encode_map(ctx, &tmap_b, args->dtype, b, n, k, static_cast<uint64_t>(ldb) * 2, 64,
                                        t.block_k))
       return rc;
@@ -572,6 +596,35 @@ int enqueue_gemm(HcCudaContext *ctx, const HcCudaGemmArgs *args, const HcCudaGem
                               args->c_dtype == HC_CUDA_C_F32 ? 32 : 64, 32))
         return rc;
       c_map = &tmap_c;
+    }
+    if (plan.cluster_size > 1) {
+      if (c_map == nullptr || args->c_dtype != HC_CUDA_C_F32 || ep.push_count != 0)
+        return fail(ctx, HC_CUDA_ERR_UNSUPPORTED, "the cluster form needs a float32 C that TMA can address");
+      // A planned size that this device does not offer is halved (with twice the clusters per tile, so
+      // the k ranges stay the same).
+      int size = plan.cluster_size, groups = plan.splits / plan.cluster_size;
+      while (size > 2 && hc::sm100::dense_cluster_capacity(size) <= 0) {
+        size >>= 1;
+        groups <<= 1;
+      }
+      const long long cluster_tiles = static_cast<long long>(plan.tiles_m) * plan.tiles_n;
+      float *partials = nullptr;
+      if (groups > 1) {
+        if (hc::sm100::dense_cluster_partials_bytes(cluster_tiles, groups) + (cursor - static_cast<char *>(ctx->scratch)) >
+            ctx->scratch_bytes)
+          return fail(ctx, HC_CUDA_ERR_UNSUPPORTED, "no cluster size of the plan is available on this device");
+        if (int rc = ensure_counters(ctx, hc::sm100::dense_cluster_counters_bytes(cluster_tiles)))
+          return rc;
+        partials = reinterpret_cast<float *>(cursor);
+      }
+      CUtensorMap tmap_rows;  // C in boxes of as many rows as one warp finishes at a time
+      if (int rc = encode_map(ctx, &tmap_rows, kMapFloat32, args->c, n, m, static_cast<uint64_t>(args->ldc) * 4, 32,
+                              hc::sm100::dense_cluster_store_rows(size)))
+        return rc;
+      HC_TRY_CUDA(ctx, hc::sm100::launch_gemm_dense_cluster(tmap_a, tmap_b, tmap_rows, m, n, k, args->dtype, size,
+                                                            groups, partials, ctx->counters, b_layout, ep,
+                                                            ctx->status_dev, ctx->stream));
+      return HC_CUDA_OK;
     }
     hc::sm100::SplitK split{plan.splits, plan.first_split_tile, nullptr, nullptr};
     CUtensorMap tmap_p;

@@ -123,6 +123,31 @@ cudaError_t launch_gemm_dense(const CUtensorMap &tmap_a, const CUtensorMap &tmap
                               const SplitK &split, const CUtensorMap *tmap_partials, int *status,
                                    cudaStream_t stream);
 
+// Few tiles, long k: every 128x256 tile is shared by `groups` thread-block clusters of `cluster_size`
+// CTAs (2, 4, 8 or 16), each CTA a range of the k-blocks; the partial tiles are summed through
+// distributed shared memory inside a cluster and, with groups > 1, through `partials`
+// (dense_cluster_partials_bytes) and `counters` (dense_cluster_counters_bytes, zeroed once; the
+// kernel leaves them zero) between clusters -- always in ascending-k order. Takes launch_gemm_dense's
+// tensor maps for A and B and a float32 C that TMA can address; `tmap_c` has boxes of 32 columns x
+// dense_cluster_store_rows(cluster_size) rows. No push targets.
+cudaError_t launch_gemm_dense_cluster(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, const CUtensorMap &tmap_c,
+                                      int m, int n, int k, int dtype, int cluster_size, int groups, float *partials,
+                                      unsigned *counters, int b_layout, const Epilogue &ep, int *status,
+                                      cudaStream_t stream);
+int dense_cluster_store_rows(int cluster_size);
+size_t dense_cluster_partials_bytes(long long tiles, int groups);
+size_t dense_cluster_counters_bytes(long long tiles);
+// Clusters of that size that the current device runs at once (0: the size is not available).
+int dense_cluster_capacity(int cluster_size);
+// The form planned for a product on a device with `sm_count` SMs, from a model of how many clusters
+// of each size such a device runs at once (needs no device); cluster_size 0: do not use clusters.
+// `elem_bytes`: 2 or 1.
+struct ClusterPlan {
+  int cluster_size;
+  int groups;
+};
+ClusterPlan dense_cluster_choose(long long m, long long n, long long k, int elem_bytes, int sm_count);
+
 // Same product on CTA pairs: clusters of two CTAs own 256x256 tiles and issue
 // tcgen05.mma.cta_group::2. Takes the same tensor maps as launch_gemm_dense. `max_ctas` is
 // rounded down to an even number of CTAs.

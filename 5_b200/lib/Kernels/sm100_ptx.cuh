@@ -306,6 +306,28 @@ __device__ __forceinline__ void cluster_sync_all() {
                "barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ uint32_t cluster_cta_count() {
+  uint32_t count;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(count));
+  return count;
+}
+
+__device__ __forceinline__ uint32_t cluster_id_x() {
+  uint32_t id;
+  asm volatile("mov.u32 %0, %%clusterid.x;" : "=r"(id));
+  return id;
+}
+
+// 16 bytes from the shared memory of any CTA of the cluster (`cluster_addr` from map_to_cta).
+__device__ __forceinline__ float4 ld_shared_cluster_f4(uint32_t cluster_addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(cluster_addr)
+               : "memory");
+  return v;
+}
+
 // Arrive on an mbarrier that may live in the other CTA of the cluster.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar)

@@ -39,7 +39,7 @@
 extern "C" {
 #endif
 
-#define HC_CUDA_API_VERSION 5
+#define HC_CUDA_API_VERSION 6
 
 typedef enum HcCudaStatus {
   HC_CUDA_OK = 0,
@@ -156,6 +156,9 @@ typedef struct HcCudaGemmPlanInfo {
   int32_t ring_stages;      /* skinny: stages of the CTA's shared-memory ring for this grid on
                                `sm_count` SMs -- the deep ring (all of an SM's shared memory) when
                                no two CTAs share an SM, else the shallow one; 0 for other variants */
+  int32_t cluster_size;     /* dense, few tiles and a long k: CTAs per thread-block cluster that share
+                               one 128x256 tile (each a range of k, `splits` == cluster_size, partial
+                               tiles added through distributed shared memory); 0 otherwise */
 } HcCudaGemmPlanInfo;
 
 typedef struct HcCudaDeviceInfo {

@@ -171,11 +171,11 @@ def test_plan_with_accumulate_and_fused_operations() -> None:
 def test_plan_splits_dense_tiles_that_do_not_fill_a_round() -> None:
     """Few tiles and a long k: every tile is split. More tiles than CTAs with a small remainder and
     k >= 8192: only the last round's tiles. Otherwise nothing is split."""
-    few = cuda.plan_gemm(128, 8192, 8192, "float16")
+    few = cuda.plan_gemm(128, 8192, 8192, "float16", ldc=8192 + 1)  # (a C that TMA cannot address)
     assert (few.variant, few.tiles_m, few.tiles_n, few.splits, few.first_split_tile, few.grid) == ("dense", 1, 32, 4, 0, 128)
-    assert few.scratch_bytes == 32 * 4 * 128 * 256 * 4 and few.kernel_launches == 1
-    one_tile = cuda.plan_gemm(256, 256, 32768, "bfloat16")
-    assert one_tile.splits == 32 and one_tile.grid == 64  # 32 CTA pairs
+    assert few.scratch_bytes == 32 * 4 * 128 * 256 * 4 and few.kernel_launches == 1 and few.cluster_size == 0
+    one_tile = cuda.plan_gemm(256, 256, 32768, "bfloat16", c_dtype="bfloat16")
+    assert one_tile.splits == 32 and one_tile.grid == 64 and one_tile.cluster_size == 0  # 32 CTA pairs
     tail = cuda.plan_gemm(4864, 1024, 8192, "float16")  # 19 x 4 pair tiles = one round of 74 + 2
     assert (tail.splits, tail.first_split_tile, tail.grid) == (8, 74, 148)
     assert tail.scratch_bytes == 2 * 8 * 256 * 256 * 4
@@ -186,6 +186,26 @@ def test_plan_splits_dense_tiles_that_do_not_fill_a_round() -> None:
     assert cuda.plan_gemm(128, 8192, 512, "float16").splits == 1
     # Fewer SMs, more rounds.
     assert cuda.plan_gemm(128, 8192, 8192, "float16", sm_count=32).splits == 1
+
+
+def test_plan_shares_few_tiles_among_clusters() -> None:
+    """Few tiles, a long k and a float32 C that TMA can address: each 128x256 tile goes to one or several
+    thread-block clusters, every CTA a range of k; partial tiles in global memory only between clusters."""
+    few = cuda.plan_gemm(128, 8192, 8192, "float16")  # 32 tiles: clusters of four fill 128 SMs
+    assert (few.cluster_size, few.splits, few.tiles_m, few.tiles_n, few.grid) == (4, 4, 1, 32, 128)
+    assert few.scratch_bytes == 0 and few.first_split_tile == 0 and few.kernel_launches == 1
+    one = cuda.plan_gemm(256, 256, 32768, "bfloat16")  # 2 tiles: seven clusters of eight each
+    assert (one.cluster_size, one.splits, one.tiles_m, one.tiles_n, one.grid) == (8, 56, 2, 1, 112)
+    assert one.scratch_bytes == 2 * 7 * 128 * 256 * 4
+    mid = cuda.plan_gemm(512, 512, 16384, "float16", accumulate=True, epilogue=(("scale", 0.5),))
+    assert (mid.cluster_size, mid.splits, mid.grid) == (4, 16, 128)
+    # Products that fill the GPU with whole tiles, a short k, and the last round of a larger product
+    # are not shared.
+    for shape in ((8192, 8192, 8192), (2048, 2048, 2048), (128, 8192, 512), (4864, 1024, 8192)):
+        assert cuda.plan_gemm(*shape, "float16").cluster_size == 0, shape
+    # A smaller device: fewer clusters at once.
+    small = cuda.plan_gemm(256, 256, 32768, "float16", sm_count=64)
+    assert small.cluster_size >= 2 and small.grid <= 64
 
 
 def test_library_calls_from_threads() -> None:

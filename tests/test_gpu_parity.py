@@ -477,6 +477,88 @@ def test_dense_split_k(shape, dtype: str, gpu_ctx) -> None:
         buf.free()
 
 
+CLUSTER_CASES = [
+    # (m, n, k, cluster size, clusters per tile)
+    (256, 256, 32768, 8, 7), (256, 256, 32768, 16, 3), (512, 512, 16384, 4, 4), (300, 500, 4100, 16, 1),
+    (300, 500, 4100, 2, 6), (128, 256, 1024, 2, 1), (130, 264, 2048, 8, 2), (384, 768, 12288, 4, 3),
+    (129, 520, 704, 4, 2),  # eleven k-blocks over eight CTAs: ranges of one and two blocks
+]
+
+
+@pytest.mark.parametrize("case", CLUSTER_CASES)
+def test_dense_cluster_form(case, gpu_ctx, monkeypatch) -> None:
+    """Few tiles, long k, a float32 C that TMA can address: the CTAs that share a tile are one or several
+    thread-block clusters and add their partial tiles through distributed shared memory (and, between
+    clusters, through partial sums in global memory). Every cluster size and number of clusters per tile
+    gives the oracle's product, bit-identical from launch to launch, with the fused members and float8."""
+    m, n, k, size, groups = case
+    monkeypatch.setenv("HC_CUDA_DENSE_CLUSTER", str(size))
+    monkeypatch.setenv("HC_CUDA_DENSE_CLUSTER_GROUPS", str(groups))
+    plan = gpu_ctx.plan(m, n, k, "float16")
+    assert (plan.variant, plan.cluster_size, plan.splits) == ("dense", size, size * groups), plan
+    assert plan.grid == plan.tiles_m * plan.tiles_n * size * groups and plan.tiles_m == -(-m // 128)
+    a, b = random_inputs(m, n, k, "float16", scale=0.25)
+    da, db = gpu_ctx.to_device(a), gpu_ctx.to_device(b)
+    dc = gpu_ctx.empty((m, n), np.float32)
+    dc.fill_bytes(0xFF)
+    gpu_ctx.gemm(da, db, dc)
+    gpu_ctx.synchronize()
+    first = dc.to_numpy()
+    assert_close_to_oracle(first, a, b)
+    for _ in range(3):  # the order of arrival does not matter and the counters are back at zero
+        dc.fill_bytes(0xFF)
+        gpu_ctx.gemm(da, db, dc)
+        gpu_ctx.synchronize()
+        assert np.array_equal(dc.to_numpy(), first)
+    rng = np.random.default_rng([m, n, k, 9])
+    c0 = rng.standard_normal((m, n)).astype(np.float32)
+    bias = rng.standard_normal((n,)).astype(np.float32)
+    dbias = gpu_ctx.to_device(bias)
+    ops = (("scale", 0.5), ("bias",), ("max", -0.5), ("min", 2.0))
+    for accumulate, epilogue in ((True, ()), (True, ops), (False, ops)):
+        dc.copy_from_host(c0)
+        gpu_ctx.gemm(da, db, dc, accumulate=accumulate, epilogue=epilogue, bias=dbias if epilogue else None)
+        gpu_ctx.synchronize()
+        assert_fused_close(dc.to_numpy(), a, b, c0=c0 if accumulate else None, epilogue=epilogue, bias=bias,
+                           use_oracle=m * n * k <= 1 << 28)
+    bt = gpu_ctx.to_device(np.ascontiguousarray(b.T))
+    dc.fill_bytes(0xFF)
+    gpu_ctx.gemm(da, bt, dc, b_transposed=True)
+    gpu_ctx.synchronize()
+    assert np.array_equal(dc.to_numpy(), first)
+    # The same product without clusters: equal up to the order of the partial sums.
+    monkeypatch.setenv("HC_CUDA_DENSE_CLUSTER", "0")
+    assert gpu_ctx.plan(m, n, k, "float16").cluster_size == 0
+    gpu_ctx.gemm(da, db, dc)
+    gpu_ctx.synchronize()
+    np.testing.assert_allclose(dc.to_numpy(), first, rtol=0, atol=2e-3)
+    # float8 operands (twice the k per stage) and bfloat16.
+    monkeypatch.setenv("HC_CUDA_DENSE_CLUSTER", str(size))
+    for dtype in ("float8_e4m3fn", "bfloat16"):
+        if dtype.startswith("float8"):
+            a8, b8 = float8_inputs(m, n, k, dtype)
+            b8 = np.ascontiguousarray(b8.T)  # [N, K]: no transposition launch
+        else:
+            a8, b8 = random_inputs(m, n, k, dtype, scale=0.25)
+        if gpu_ctx.plan(m, n, k, dtype, b_transposed=dtype.startswith("float8")).cluster_size != size:
+            continue  # too few k-blocks of 128 for this many CTAs
+        d8a, d8b = gpu_ctx.to_device(a8), gpu_ctx.to_device(b8)
+        dc.fill_bytes(0xFF)
+        gpu_ctx.gemm(d8a, d8b, dc, b_transposed=dtype.startswith("float8"))
+        gpu_ctx.synchronize()
+        assert_close_to_oracle(dc.to_numpy(), a8, b8.T if dtype.startswith("float8") else b8)
+        d8a.free(), d8b.free()
+    for buf in (da, db, dc, dbias, bt):
+        buf.free()
+
+
+def test_dense_cluster_form_is_not_chosen_where_it_cannot_store(gpu_ctx) -> None:
+    """A 16-bit C, a pitch that TMA cannot address and push targets keep the counter-based split."""
+    assert gpu_ctx.plan(256, 256, 32768, "float16").cluster_size > 0
+    assert gpu_ctx.plan(256, 256, 32768, "float16", ldc=259).cluster_size == 0
+    assert gpu_ctx.plan(256, 256, 32768, "float16", c_dtype="bfloat16").cluster_size == 0
+
+
 def test_dense_split_k_forced(gpu_ctx, monkeypatch) -> None:
     """Split counts the plan would not choose, on a shape with many tiles per CTA (units of one tile
     land on different CTAs in different rounds)."""
@@ -579,8 +661,14 @@ def test_16_bit_c(shape, dtype: str, gpu_ctx) -> None:
     out = dc.to_numpy()
     assert out.dtype == np.dtype(out_type)
     assert_narrow_close(out, a, b)
-    # Exactly the float32 result rounded to nearest even (same plan, so the same float32 bits).
-    assert np.array_equal(out.view(np.uint16), d32.to_numpy().astype(out_type).view(np.uint16))
+    # Exactly the float32 result rounded to nearest even where both take the same plan (so the same
+    # float32 bits); a split float32 product may instead share its tiles among clusters, which adds
+    # the partial sums in another order.
+    same_plan = gpu_ctx.plan(m, n, k, dtype).cluster_size == gpu_ctx.plan(m, n, k, dtype, ldc=n + pad, c_dtype=dtype).cluster_size
+    if same_plan:
+        assert np.array_equal(out.view(np.uint16), d32.to_numpy().astype(out_type).view(np.uint16))
+    else:
+        np.testing.assert_allclose(out.astype(np.float32), d32.to_numpy(), rtol=2.0 ** -7, atol=1e-3)
     bias = np.linspace(-1, 1, n).astype(np.float32)
     dbias = gpu_ctx.to_device(bias)
     ops = (("scale", 0.5), ("bias",), ("max", 0.0))
