@@ -44,6 +44,9 @@ CONFIGS = {
     "ragged": Workload("ragged", 4095, 3073, 1031, "bfloat16", 2),
     "skinny": Workload("skinny", 8, 16384, 8192, "float16", 3),
     "sharded": Workload("sharded", 16384, 32768, 16384, "float16", 4),
+    # Not one of the five benchmark configurations: a product with few tiles and a long k-loop (eight
+    # 128x256 tiles), the shape class whose tiles are shared among thread-block clusters.
+    "long_k": Workload("long_k", 512, 512, 16384, "float16", 6),
 }
 
 
@@ -100,7 +103,7 @@ def make_inputs(name: str) -> tuple[np.ndarray, np.ndarray]:
     if name == "sim_64":
         a = rng.standard_normal((w.m, w.k)).astype(dtype)
         b = rng.standard_normal((w.k, w.n)).astype(dtype)
-    elif name in ("gemm_8192", "custom"):
+    elif name in ("gemm_8192", "custom", "long_k"):
         scale = 1.0 / np.sqrt(w.k)
         a = _normal(rng, (w.m, w.k), scale, dtype)
         b = _normal(rng, (w.k, w.n), scale, dtype)

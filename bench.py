@@ -818,6 +818,7 @@ def run_gpu_arm(args, ranks: Ranks) -> None:
         side["skinny"] = side_record(ctx, ranks, sampler, "skinny", 400, peaks, peaks_source)
         side["ragged"] = side_record(ctx, ranks, sampler, "ragged", 400, peaks, peaks_source)
         side["sim_64"] = side_record(ctx, ranks, sampler, "sim_64", 1000, peaks, peaks_source)
+        side["long_k"] = side_record(ctx, ranks, sampler, "long_k", 1000, peaks, peaks_source)
         side["elementwise_map"] = map_record(ctx, ranks, sampler, 50, peaks, peaks_source)
         side["sharded_1gpu"] = side_record(ctx, ranks, sampler, "sharded", 10, peaks, peaks_source,
                                            sustained_seconds=args.sustained_seconds)

@@ -59,6 +59,7 @@ def test_workload_definitions() -> None:
         "ragged": (4095, 3073, 1031, "bfloat16"),
         "skinny": (8, 16384, 8192, "float16"),
         "sharded": (16384, 32768, 16384, "float16"),
+        "long_k": (512, 512, 16384, "float16"),  # (an extra shape class, not one of the five configurations)
     }
     assert workloads.flops(8192, 8192, 8192) == 2.0 * 8192**3
     assert workloads.algorithmic_bytes(8, 16384, 8192) == 2 * 8 * 8192 + 2 * 8192 * 16384 + 4 * 8 * 16384

@@ -203,6 +203,15 @@ def test_plan_shares_few_tiles_among_clusters() -> None:
     # are not shared.
     for shape in ((8192, 8192, 8192), (2048, 2048, 2048), (128, 8192, 512), (4864, 1024, 8192)):
         assert cuda.plan_gemm(*shape, "float16").cluster_size == 0, shape
+    # 8 < m <= 64 with few column blocks: the shared dense tiles instead of the skinny kernel's split;
+    # not for m <= 8, not when there are column blocks enough, not when C rules the clusters out.
+    assert (cuda.plan_gemm(64, 8192, 8192, "float16").variant, cuda.plan_gemm(64, 8192, 8192, "float16").cluster_size) == ("dense", 4)
+    assert cuda.plan_gemm(33, 4096, 8192, "bfloat16").cluster_size == 4
+    for kwargs in (dict(m=8, n=8192), dict(m=64, n=16384), dict(m=64, n=8192, ldc=8193), dict(m=64, n=8192, c_dtype="float16")):
+        shape = dict(m=64, n=8192, k=8192) | {k_: v for k_, v in kwargs.items() if k_ in ("m", "n")}
+        extra = {k_: v for k_, v in kwargs.items() if k_ not in ("m", "n")}
+        plan = cuda.plan_gemm(shape["m"], shape["n"], shape["k"], "float16", **extra)
+        assert (plan.variant, plan.cluster_size) == ("skinny", 0), (kwargs, plan)
     # A smaller device: fewer clusters at once.
     small = cuda.plan_gemm(256, 256, 32768, "float16", sm_count=64)
     assert small.cluster_size >= 2 and small.grid <= 64
