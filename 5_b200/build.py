@@ -33,6 +33,7 @@ SOURCES = [
     LIB_DIR / "Kernels" / "repack_bytes_sm100a.cu",
     LIB_DIR / "Kernels" / "epilogue_only_sm100a.cu",
     LIB_DIR / "Kernels" / "map_elementwise_sm100a.cu",
+    LIB_DIR / "Kernels" / "pairwise_distance_sm100a.cu",
     LIB_DIR / "Kernels" / "gemm_skinny_static_sm100a.cu",
     LIB_DIR / "Kernels" / "selftest_sm100a.cu",
     LIB_DIR / "CAPI" / "Cuda.cpp",

@@ -25,6 +25,7 @@ import numpy as np
 
 from ._launch import PreparedLaunch, prepare_launch
 from ._map_kernels import MapContract
+from ._pairwise_kernels import PairwiseContract
 from ._pipeline import GemmContract, ScheduleSource, lower_for_target
 from .errors import LaunchError
 
@@ -48,7 +49,7 @@ class CompiledKernel:
     pipeline_diagnostics: tuple[str, ...] = field(default=())
     # Extensions of the NVIDIA path.
     target: str | None = field(default=None)
-    plan: GemmContract | MapContract | None = field(default=None)
+    plan: GemmContract | MapContract | PairwiseContract | None = field(default=None)
     schedule: ScheduleSource = field(default=None)
     device: int | None = field(default=None)
 
@@ -67,6 +68,8 @@ class CompiledKernel:
             return None
         if isinstance(self.plan, MapContract):
             self._launch_map(launch)
+        elif isinstance(self.plan, PairwiseContract):
+            self._launch_pairwise(launch)
         else:
             self._launch_gemm(launch)
         return None
@@ -160,6 +163,38 @@ class CompiledKernel:
             return np.ascontiguousarray(arr).reshape(-1)  # (a matrix goes as its elements in row-major order)
 
         ctx.map_host(host(x), staged.reshape(-1), plan.ops, other=None if other is None else host(other))
+        if not direct:
+            out[...] = staged
+
+    def _launch_pairwise(self, launch: PreparedLaunch) -> None:
+        """out[i, j] = [sqrt] sum_h (x1[i, h] - x2[j, h])^2 for a recognised pairwise kernel."""
+        from . import cuda
+
+        plan = self.plan
+        assert isinstance(plan, PairwiseContract)
+        names = [plan.lhs_param, plan.rhs_param, plan.out_param]
+        x1, x2, out = (launch.arguments[name] for name in names)
+        for name, buf in zip(names, (x1, x2, out)):
+            if buf.dtype != np.float32:
+                raise LaunchError(f"{name} dtype expected float32, got {buf.dtype.name}: target {self.target!r} runs "
+                                  f"pairwise kernels on float32 buffers")
+        on_device = [type(buf).__name__ == "DeviceBuffer" for buf in (x1, x2, out)]
+        if any(on_device) and not all(on_device):
+            raise LaunchError("buffers must be all numpy.ndarray or all DeviceBuffer")
+        if all(on_device):
+            ctx = x1.ctx
+            if x2.ctx is not ctx or out.ctx is not ctx:
+                raise LaunchError("device buffers must belong to one context")
+            ctx.pairwise(x1, x2, out, take_sqrt=plan.take_sqrt)
+            ctx.synchronize()
+            return
+        if not out.flags.writeable:
+            raise LaunchError(f"{plan.out_param} must be writeable")
+        ctx = cuda.default_context(self.device)
+        direct = _is_row_major(out)
+        # (Only the w1 x w2 results are written, so a staged copy starts from out's contents when h == 0.)
+        staged = out if direct else np.array(out, order="C")
+        ctx.pairwise_host(_row_major(x1), _row_major(x2), staged, take_sqrt=plan.take_sqrt)
         if not direct:
             out[...] = staged
 

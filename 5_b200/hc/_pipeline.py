@@ -93,7 +93,7 @@ class GemmContract:
 @dataclass(frozen=True)
 class TargetResult:
     target: str
-    plan: Any  # GemmContract, hc._map_kernels.MapContract, or None
+    plan: Any  # GemmContract, hc._map_kernels.MapContract, hc._pairwise_kernels.PairwiseContract, or None
     diagnostics: tuple[str, ...]
 
 
@@ -108,15 +108,32 @@ def lower_for_target(kernel_fn: Any, target: str) -> TargetResult:
     if target != NVIDIA_SM100A:
         raise ValueError(f"unknown hc.compile target {target!r}; known targets: {list(known_targets())}")
     from ._map_kernels import recognise_elementwise_map
+    from ._pairwise_kernels import recognise_pairwise
 
     plan, diagnostics = recognise_tiled_matmul(kernel_fn)
     if plan is None:
         map_plan, map_diagnostics = recognise_elementwise_map(kernel_fn)
         if map_plan is not None:
             return TargetResult(target, map_plan, ())
+        pair_plan, pair_diagnostics = recognise_pairwise(kernel_fn)
+        if pair_plan is not None:
+            return TargetResult(target, pair_plan, ())
         if _looks_one_dimensional(kernel_fn):
             diagnostics = map_diagnostics
+        elif _looks_like_pairwise(kernel_fn):
+            diagnostics = pair_diagnostics
     return TargetResult(target, plan, tuple(diagnostics))
+
+
+def _looks_like_pairwise(kernel_fn: Any) -> bool:
+    """Two-dimensional work over three rank-2 buffers and no k-loop: not a member of the matmul family."""
+    source = _function_node(kernel_fn)
+    has_loop = source is not None and any(isinstance(node, (ast.For, ast.While)) for node in ast.walk(source))
+    try:
+        count = len(inspect.signature(kernel_fn).parameters)
+    except (TypeError, ValueError):
+        return False
+    return count == 4 and not has_loop
 
 
 def _looks_one_dimensional(kernel_fn: Any) -> bool:

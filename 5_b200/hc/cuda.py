@@ -56,7 +56,7 @@ EXPORTS = (
     "hcCudaEventDestroy", "hcCudaEventRecord", "hcCudaEventElapsedMs", "hcCudaCommGetUniqueId",
     "hcCudaCommInitRank", "hcCudaCommAllGather", "hcCudaCommDestroy", "hcCudaGemmSkinnyStatic", "hcCudaSelfTestDeviceTimeout", "hcCudaGemmPush", "hcCudaIpcExport",
     "hcCudaIpcOpen", "hcCudaIpcClose", "hcCudaMap", "hcCudaMapHost",
-    "hcCudaGemmHostDeviceA",
+    "hcCudaGemmHostDeviceA", "hcCudaPairwise", "hcCudaPairwiseHost",
 )
 
 
@@ -110,6 +110,17 @@ class _PlanInfo(ctypes.Structure):
         ("scratch_bytes", ctypes.c_int64), ("first_split_tile", ctypes.c_int32), ("ring_stages", ctypes.c_int32),
         ("cluster_size", ctypes.c_int32),
     ]
+
+
+class _PairwiseArgs(ctypes.Structure):
+    _fields_ = [
+        ("w1", ctypes.c_int64), ("w2", ctypes.c_int64), ("h", ctypes.c_int64),
+        ("x1", ctypes.c_void_p), ("ld1", ctypes.c_int64), ("x2", ctypes.c_void_p), ("ld2", ctypes.c_int64),
+        ("out", ctypes.c_void_p), ("ldo", ctypes.c_int64), ("op", ctypes.c_int32),
+    ]
+
+
+PAIRWISE_EUCLIDEAN, PAIRWISE_SQUARED = 0, 1
 
 
 class _DeviceInfo(ctypes.Structure):
@@ -188,6 +199,8 @@ def library() -> ctypes.CDLL:
         lib.hcCudaGemmSkinnyStatic.argtypes = [ctypes.POINTER(_GemmArgs), vp, i, ctypes.c_char_p, sz]
         lib.hcCudaMap.argtypes = [vp, ctypes.POINTER(_MapArgs)]
         lib.hcCudaMapHost.argtypes = [vp, ctypes.POINTER(_MapArgs)]
+        lib.hcCudaPairwise.argtypes = [vp, ctypes.POINTER(_PairwiseArgs)]
+        lib.hcCudaPairwiseHost.argtypes = [vp, ctypes.POINTER(_PairwiseArgs)]
         for name in EXPORTS:
             getattr(lib, name)  # AttributeError here means a stale or foreign library
         _LIB = lib
@@ -457,6 +470,37 @@ class Context:
         args = _map_args(x.shape[0], x.ctypes.data, None if other is None else other.ctypes.data,
                          out.ctypes.data, ops)
         self._check(self._lib.hcCudaMapHost(self._handle, ctypes.byref(args)))
+
+    def pairwise(self, x1: "DeviceBuffer", x2: "DeviceBuffer", out: "DeviceBuffer", *, take_sqrt: bool = True) -> None:
+        """Enqueues out[i, j] = sqrt(sum_h (x1[i, h] - x2[j, h])**2) (the sum itself with `take_sqrt`
+        off) on float32 device matrices x1 (w1, h), x2 (w2, h), out (w1, w2): the pairwise kernel
+        class, bit-identical to the reference simulator (asynchronous; see `synchronize`)."""
+        for buf in (x1, x2, out):
+            if buf.dtype != np.float32 or len(buf.shape) != 2:
+                raise ValueError("pairwise() takes two-dimensional float32 device buffers")
+        (w1, h), (w2, h2) = x1.shape, x2.shape
+        if h != h2 or out.shape != (w1, w2):
+            raise ValueError(f"pairwise(): shapes {x1.shape}, {x2.shape} -> {out.shape} do not fit")
+        args = _PairwiseArgs(w1, w2, h, x1.ptr, x1.ld, x2.ptr, x2.ld, out.ptr, out.ld,
+                             PAIRWISE_EUCLIDEAN if take_sqrt else PAIRWISE_SQUARED)
+        self._check(self._lib.hcCudaPairwise(self._handle, ctypes.byref(args)))
+
+    def pairwise_host(self, x1: np.ndarray, x2: np.ndarray, out: np.ndarray, *, take_sqrt: bool = True) -> None:
+        """The same on row-major float32 host matrices (rows may be padded): copies in, runs, copies
+        `out` back in place; returns when `out` is complete."""
+        for arr in (x1, x2, out):
+            if arr.dtype != np.float32 or arr.ndim != 2 or (arr.shape[1] > 1 and arr.strides[1] != 4):
+                raise ValueError("pairwise_host() takes row-major two-dimensional float32 arrays")
+        (w1, h), (w2, h2) = x1.shape, x2.shape
+        if h != h2 or out.shape != (w1, w2):
+            raise ValueError(f"pairwise_host(): shapes {x1.shape}, {x2.shape} -> {out.shape} do not fit")
+
+        def pitch(arr: np.ndarray) -> int:
+            return arr.strides[0] // 4 if arr.shape[0] > 1 else max(arr.shape[1], 1)
+
+        args = _PairwiseArgs(w1, w2, h, x1.ctypes.data, pitch(x1), x2.ctypes.data, pitch(x2), out.ctypes.data,
+                             pitch(out), PAIRWISE_EUCLIDEAN if take_sqrt else PAIRWISE_SQUARED)
+        self._check(self._lib.hcCudaPairwiseHost(self._handle, ctypes.byref(args)))
 
     def gemm_host(self, a: np.ndarray, b: np.ndarray, c: np.ndarray, *,
                   variant: int = VARIANT_AUTO, b_transposed: bool = False, accumulate: bool = False,

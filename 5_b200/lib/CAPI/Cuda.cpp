@@ -20,6 +20,7 @@
 #include <cstring>
 #include <initializer_list>
 #include <mutex>
+#include <vector>
 #include <new>
 #include <string>
 
@@ -110,6 +111,8 @@ struct HcCudaContext {
   size_t scratch_bytes = 0;
   unsigned *counters = nullptr;
   size_t counters_bytes = 0;
+  int4 *pairwise_leaves = nullptr;  // summation schedule of the pairwise kernel for `pairwise_h`
+  int pairwise_h = -1, pairwise_leaf_count = 0;
   void *stage[3] = {nullptr, nullptr, nullptr};  // device staging for host-buffer calls
   size_t stage_bytes[3] = {0, 0, 0};
   // Host-buffer calls on large dense problems overlap copies with compute: A arrives in row
@@ -869,6 +872,8 @@ int hcCudaContextDestroy(HcCudaContext *ctx) {
       cudaFree(ctx->scratch);
     if (ctx->counters != nullptr)
       cudaFree(ctx->counters);
+    if (ctx->pairwise_leaves != nullptr)
+      cudaFree(ctx->pairwise_leaves);
     if (ctx->status_dev != nullptr)
       cudaFree(ctx->status_dev);
     if (ctx->status_host != nullptr)
@@ -1599,6 +1604,124 @@ int hcCudaMapHost(HcCudaContext *ctx, const HcCudaMapArgs *args) {
   }
   HC_TRY_CUDA(ctx, cudaEventRecord(ctx->fence_event, ctx->copy_out));
   HC_TRY_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->fence_event, 0));
+  return synchronize_locked(ctx);
+}
+
+namespace {
+
+int check_pairwise_args(const HcCudaContext *ctx, const HcCudaPairwiseArgs *args) {
+  if (args == nullptr)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "args must not be null");
+  if (args->w1 < 0 || args->w2 < 0 || args->h < 0)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "w1, w2 and h must be non-negative (got %lld, %lld, %lld)",
+                (long long)args->w1, (long long)args->w2, (long long)args->h);
+  if (args->w1 > 0x7fffffffLL || args->w2 > 0x7fffffffLL)
+    return fail(ctx, HC_CUDA_ERR_UNSUPPORTED, "w1 and w2 must be below 2^31");
+  if (args->h > hc::sm100::pairwise_max_h())
+    return fail(ctx, HC_CUDA_ERR_UNSUPPORTED, "h must be at most %d (got %lld)", hc::sm100::pairwise_max_h(),
+                (long long)args->h);
+  if (args->op != HC_CUDA_PAIRWISE_EUCLIDEAN && args->op != HC_CUDA_PAIRWISE_SQUARED)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "op is not an HcCudaPairwiseOp (got %d)", args->op);
+  if (args->w1 == 0 || args->w2 == 0 || args->h == 0)
+    return HC_CUDA_OK;
+  if (args->x1 == nullptr || args->x2 == nullptr || args->out == nullptr)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "x1, x2 and out must not be null");
+  if (((reinterpret_cast<uintptr_t>(args->x1) | reinterpret_cast<uintptr_t>(args->x2) |
+        reinterpret_cast<uintptr_t>(args->out)) & 3) != 0)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "x1, x2 and out must be 4-byte aligned");
+  if (args->ld1 < args->h || args->ld2 < args->h || args->ldo < args->w2 || args->ld1 > kMaxPitch ||
+      args->ld2 > kMaxPitch || args->ldo > kMaxPitch)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "ld1 and ld2 must be at least h (%lld) and ldo at least w2 (%lld)",
+                (long long)args->h, (long long)args->w2);
+  const size_t bytes1 = (static_cast<size_t>(args->w1 - 1) * args->ld1 + args->h) * 4;
+  const size_t bytes2 = (static_cast<size_t>(args->w2 - 1) * args->ld2 + args->h) * 4;
+  const size_t bytes_out = (static_cast<size_t>(args->w1 - 1) * args->ldo + args->w2) * 4;
+  if (ranges_overlap(args->out, bytes_out, args->x1, bytes1) || ranges_overlap(args->out, bytes_out, args->x2, bytes2))
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "out must not overlap x1 or x2");
+  return HC_CUDA_OK;
+}
+
+// The summation schedule for h on the device (kept until another h is asked for).
+int ensure_pairwise_schedule(HcCudaContext *ctx, int h) {
+  if (ctx->pairwise_h == h)
+    return HC_CUDA_OK;
+  const int count = hc::sm100::pairwise_schedule(h, nullptr, 0);
+  std::vector<int4> leaves(static_cast<size_t>(count));
+  hc::sm100::pairwise_schedule(h, leaves.data(), count);
+  HC_TRY_CUDA(ctx, cudaStreamSynchronize(ctx->stream));  // no launch may still read the old schedule
+  if (ctx->pairwise_leaves != nullptr) {
+    HC_TRY_CUDA(ctx, cudaFree(ctx->pairwise_leaves));
+    ctx->pairwise_leaves = nullptr;
+    ctx->pairwise_h = -1;
+  }
+  HC_TRY_CUDA(ctx, cudaMalloc(reinterpret_cast<void **>(&ctx->pairwise_leaves), sizeof(int4) * static_cast<size_t>(count)));
+  HC_TRY_CUDA(ctx, cudaMemcpy(ctx->pairwise_leaves, leaves.data(), sizeof(int4) * static_cast<size_t>(count),
+                              cudaMemcpyHostToDevice));
+  ctx->pairwise_h = h;
+  ctx->pairwise_leaf_count = count;
+  return HC_CUDA_OK;
+}
+
+} // namespace
+
+int hcCudaPairwise(HcCudaContext *ctx, const HcCudaPairwiseArgs *args) {
+  if (ctx == nullptr)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "ctx must not be null");
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  if (int rc = check_pairwise_args(ctx, args))
+    return rc;
+  if (args->w1 == 0 || args->w2 == 0 || args->h == 0)
+    return HC_CUDA_OK;
+  HC_TRY_CUDA(ctx, cudaSetDevice(ctx->device));
+  if (int rc = ensure_pairwise_schedule(ctx, static_cast<int>(args->h)))
+    return rc;
+  HC_TRY_CUDA(ctx, hc::sm100::launch_pairwise_f32(args->x1, args->ld1, args->x2, args->ld2, args->out, args->ldo,
+                                                  static_cast<int>(args->w1), static_cast<int>(args->w2),
+                                                  static_cast<int>(args->h), args->op == HC_CUDA_PAIRWISE_EUCLIDEAN,
+                                                  ctx->pairwise_leaves, ctx->pairwise_leaf_count, ctx->stream));
+  return HC_CUDA_OK;
+}
+
+int hcCudaPairwiseHost(HcCudaContext *ctx, const HcCudaPairwiseArgs *args) {
+  if (ctx == nullptr)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "ctx must not be null");
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  if (int rc = check_pairwise_args(ctx, args))
+    return rc;
+  if (args->w1 == 0 || args->w2 == 0 || args->h == 0)
+    return HC_CUDA_OK;
+  HC_TRY_CUDA(ctx, cudaSetDevice(ctx->device));
+  if (int rc = ensure_pairwise_schedule(ctx, static_cast<int>(args->h)))
+    return rc;
+  // Compact device copies with pitches that allow 16-byte accesses.
+  const size_t w1 = static_cast<size_t>(args->w1), w2 = static_cast<size_t>(args->w2), h = static_cast<size_t>(args->h);
+  const size_t ld_in = static_cast<size_t>(round_up(static_cast<int64_t>(h), 4));
+  const size_t ld_out = static_cast<size_t>(round_up(static_cast<int64_t>(w2), 4));
+  if (int rc = ensure_stage(ctx, 0, w1 * ld_in * 4))
+    return rc;
+  if (int rc = ensure_stage(ctx, 1, w2 * ld_in * 4))
+    return rc;
+  if (int rc = ensure_stage(ctx, 2, w1 * ld_out * 4))
+    return rc;
+  struct Drain {  // no copy may still touch the caller's arrays when the call returns
+    HcCudaContext *ctx;
+    ~Drain() {
+      if (cudaStreamSynchronize(ctx->stream) != cudaSuccess)
+        cudaGetLastError();
+    }
+  } drain{ctx};
+  HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(ctx->stage[0], ld_in * 4, args->x1, static_cast<size_t>(args->ld1) * 4, h * 4, w1,
+                                     cudaMemcpyHostToDevice, ctx->stream));
+  HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(ctx->stage[1], ld_in * 4, args->x2, static_cast<size_t>(args->ld2) * 4, h * 4, w2,
+                                     cudaMemcpyHostToDevice, ctx->stream));
+  HC_TRY_CUDA(ctx, hc::sm100::launch_pairwise_f32(static_cast<const float *>(ctx->stage[0]), static_cast<long long>(ld_in),
+                                                  static_cast<const float *>(ctx->stage[1]), static_cast<long long>(ld_in),
+                                                  static_cast<float *>(ctx->stage[2]), static_cast<long long>(ld_out),
+                                                  static_cast<int>(w1), static_cast<int>(w2), static_cast<int>(h),
+                                                  args->op == HC_CUDA_PAIRWISE_EUCLIDEAN, ctx->pairwise_leaves,
+                                                  ctx->pairwise_leaf_count, ctx->stream));
+  HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(args->out, static_cast<size_t>(args->ldo) * 4, ctx->stage[2], ld_out * 4, w2 * 4, w1,
+                                     cudaMemcpyDeviceToHost, ctx->stream));
   return synchronize_locked(ctx);
 }
 

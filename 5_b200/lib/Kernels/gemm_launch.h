@@ -202,6 +202,17 @@ cudaError_t launch_gemm_skinny(const CUtensorMap &tmap_a, const CUtensorMap &tma
                                float *partials, unsigned *counters, int max_ctas, int sm_count,
                                int b_layout, const Epilogue &ep, int *status, cudaStream_t stream);
 
+// Pairwise distances out[i, j] = [sqrt] sum_h (x1[i, h] - x2[j, h])^2 in float32, the sum in the order
+// of NumPy's float32 sum. `leaves_dev`: pairwise_schedule(h, ...) copied to the device.
+cudaError_t launch_pairwise_f32(const float *x1, long long ld1, const float *x2, long long ld2, float *out,
+                                long long ldo, int w1, int w2, int h, int take_sqrt, const int4 *leaves_dev,
+                                int num_leaves, cudaStream_t stream);
+// The leaves of NumPy's pairwise summation of h values: {first, length, additions of pending partial
+// sums once the leaf is done, 0}. Returns their number (which may exceed `capacity`; nothing is
+// written past it).
+int pairwise_schedule(int h, int4 *leaves, int capacity);
+int pairwise_max_h();
+
 // k == 0 with fused element-wise work: C = ops(accumulate ? C : 0), no product to add.
 cudaError_t launch_epilogue_only(void *c, int m, int n, long long ldc, const Epilogue &ep,
                                  cudaStream_t stream);

@@ -319,6 +319,47 @@ HC_CUDA_CAPI_EXPORTED int hcCudaMap(HcCudaContext *ctx, const HcCudaMapArgs *arg
  * (hc/simulator.py:165-186). */
 HC_CUDA_CAPI_EXPORTED int hcCudaMapHost(HcCudaContext *ctx, const HcCudaMapArgs *args);
 
+/* ---- pairwise distances: the two-dimensional workgroup kernel of the simulator tests ---- */
+
+typedef enum HcCudaPairwiseOp {
+  HC_CUDA_PAIRWISE_EUCLIDEAN = 0, /* out[i, j] = sqrt(sum_h (x1[i, h] - x2[j, h])^2) */
+  HC_CUDA_PAIRWISE_SQUARED = 1    /* the same without the square root */
+} HcCudaPairwiseOp;
+
+/* out[i, j] for i < w1, j < w2 from x1 (w1 x h) and x2 (w2 x h), all float32, row-major with
+ * pitches ld1, ld2, ldo in elements: what the reference simulator computes for
+ *
+ *     gid = group.work_offset
+ *     lhs = group.load(x1[gid[0]:], shape=(group.shape[0], x1.shape[1]))
+ *     rhs = group.load(x2[gid[1]:], shape=(group.shape[1], x2.shape[1]))
+ *     group.store(out[gid[0]:, gid[1]:], np.sqrt(((lhs[:, None, :] - rhs[None, :, :]) ** 2).sum(axis=2)))
+ *
+ * launched over work_shape=(w1, w2) (tests/test_simulator.py:142-167): loads and stores are masked
+ * at the ends of the buffers, so exactly the w1 x w2 elements of out are written. Every operation
+ * rounds once and the sum over h runs in the order of NumPy's float32 sum (hc/_sim_types.py:1100-1102),
+ * so the result is bit-identical to the simulator's. h == 0 writes nothing (a reduction over no
+ * active element is inactive, hc/_sim_types.py:1057-1063). h at most 2^20; out must not overlap
+ * x1 or x2. */
+typedef struct HcCudaPairwiseArgs {
+  int64_t w1, w2, h;
+  const float *x1;
+  int64_t ld1;
+  const float *x2;
+  int64_t ld2;
+  float *out;
+  int64_t ldo;
+  int32_t op; /* HcCudaPairwiseOp */
+} HcCudaPairwiseArgs;
+
+/* Asynchronous; x1, x2, out are device pointers on the context's device. What
+ * `CompiledKernel.__call__` (hc/_compile.py:57-62) resolves to for a recognised pairwise kernel on
+ * device buffers. */
+HC_CUDA_CAPI_EXPORTED int hcCudaPairwise(HcCudaContext *ctx, const HcCudaPairwiseArgs *args);
+
+/* Synchronous; x1, x2, out are host pointers (NumPy buffers): the in-place, synchronous behaviour
+ * of `hc.simulator.launch` (hc/simulator.py:165-186). */
+HC_CUDA_CAPI_EXPORTED int hcCudaPairwiseHost(HcCudaContext *ctx, const HcCudaPairwiseArgs *args);
+
 /* ---- the product fused with its gather (N-sharded GEMM, one process per GPU) ------------- */
 
 #define HC_CUDA_MAX_PUSH_TARGETS 7

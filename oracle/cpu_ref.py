@@ -193,3 +193,56 @@ def map_elementwise(x: np.ndarray, ops, other: np.ndarray | None = None) -> np.n
             else:
                 raise ValueError(f"unknown operation {kind!r}")
     return v.astype(np.float32, copy=False)
+
+
+def pairwise_distance(x1: np.ndarray, x2: np.ndarray, *, take_sqrt: bool = True, rows_per_block: int = 64) -> np.ndarray:
+    """The pairwise kernel class as the reference simulator executes it (tests/test_simulator.py:142-167):
+    out[i, j] = sqrt(sum_h (x1[i, h] - x2[j, h]) ** 2) in float32, one NumPy operation per step -- the
+    difference, the power (np.power with exponent 2, hc/_sim_types.py:403-404), the sum. The simulator
+    reduces every (i, j) with `np.sum(payload[active])` over a contiguous float32 vector of h values
+    (hc/_sim_types.py:1050-1066, 1100-1102), NumPy's pairwise summation; reducing the last axis of a
+    contiguous block is the same inner loop, so the rows are evaluated a block at a time here
+    (`pairwise_sum_in_numpy_order` restates that order explicitly and the tests hold both against
+    np.sum)."""
+    x1 = np.ascontiguousarray(x1, dtype=np.float32)
+    x2 = np.ascontiguousarray(x2, dtype=np.float32)
+    w1, w2 = x1.shape[0], x2.shape[0]
+    out = np.empty((w1, w2), np.float32)
+    with np.errstate(invalid="ignore", over="ignore"):
+        for r0 in range(0, w1, rows_per_block):
+            block = np.power(x1[r0 : r0 + rows_per_block, None, :] - x2[None, :, :], 2)
+            total = np.ascontiguousarray(block).sum(axis=2)
+            out[r0 : r0 + rows_per_block] = np.sqrt(total) if take_sqrt else total
+    return out
+
+
+def pairwise_sum_in_numpy_order(values: np.ndarray) -> np.float32:
+    """NumPy's float32 sum of a contiguous vector, written out: fewer than 8 values are added in
+    order; up to 128 go into eight interleaved accumulators r[i % 8] that are combined as
+    ((r0 + r1) + (r2 + r3)) + ((r4 + r5) + (r6 + r7)) before the n % 8 tail is added in order; longer
+    vectors are split at n / 2 rounded down to a multiple of 8 and the two sums are added. This is
+    the order the CUDA pairwise kernel follows."""
+    a = np.asarray(values, dtype=np.float32)
+    n = a.shape[0]
+    f = np.float32
+    with np.errstate(invalid="ignore", over="ignore"):
+        if n < 8:
+            total = f(0.0)
+            for v in a:
+                total = f(total + v)
+            return total
+        if n <= 128:
+            r = [f(v) for v in a[:8]]
+            i = 8
+            while i < n - n % 8:
+                for j in range(8):
+                    r[j] = f(r[j] + a[i + j])
+                i += 8
+            total = f(f(f(r[0] + r[1]) + f(r[2] + r[3])) + f(f(r[4] + r[5]) + f(r[6] + r[7])))
+            while i < n:
+                total = f(total + a[i])
+                i += 1
+            return total
+        left = n // 2
+        left -= left % 8
+        return f(pairwise_sum_in_numpy_order(a[:left]) + pairwise_sum_in_numpy_order(a[left:]))

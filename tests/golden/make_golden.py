@@ -39,6 +39,11 @@ Fixtures (all produced by `hc.simulator.launch` on the example kernel):
       reference's own vector test (tests/test_simulator.py:210-224), `x`, `y`, `out` the
       scaled_clamp kernel on 1003 elements with NaN and infinities, `x_2d`, `shift_2d`, `out_2d` the
       two-dimensional affine_relu_2d kernel on a 37 x 70 matrix
+  simpair_f32_seed18
+      the pairwise-distance kernels of 5_b200/examples/b200_pairwise.py: `test_x1/_x2/_out` the
+      reference's own test (tests/test_simulator.py:142-167), `x1`, `x2`, `out` the same kernel on
+      37 x 29 outputs over 150 values, `sq_x1`, `sq_x2`, `sq_out` the squared-distance kernel on
+      19 x 35 outputs over 333 values with an infinity and a NaN
 The file blocked_reference.npz holds `reference_blocked_matmul` of the first four (the
 reference test's own comparison value, atol 2e-6).
 """
@@ -227,6 +232,35 @@ def main() -> int:
     np.savez_compressed(HERE / "simmap_f32_seed15.npz", add_two_x=x, add_two_y=y, x=x2, y=y2, out=out2,
                         x_2d=x3, shift_2d=s3, out_2d=out3)
     print(f"simmap_f32_seed15: add_two{ x.shape } scaled_clamp{ x2.shape } affine_relu_2d{ x3.shape }", flush=True)
+
+    # The pairwise kernels of 5_b200/examples/b200_pairwise.py under the reference simulator: the
+    # reference's own test (tests/test_simulator.py:142-167, 5 x 6 outputs over 3 values), and shapes
+    # that no group shape divides with 150 values per row (NumPy's sum splits at 72, the tail has
+    # 6 values) and with 333 (three levels of splitting), with an infinity and a NaN among them.
+    path = REPO / "5_b200" / "examples" / "b200_pairwise.py"
+    spec = importlib.util.spec_from_file_location("b200_pairwise_under_reference", path)
+    pw = importlib.util.module_from_spec(spec)
+    pw.__package__ = "loaded_by_make_golden"
+    sys.modules[spec.name] = pw
+    spec.loader.exec_module(pw)
+    t1 = np.arange(15, dtype=np.float32).reshape(5, 3)
+    t2 = np.arange(18, dtype=np.float32).reshape(6, 3) / 3.0
+    t_out = np.zeros((5, 6), dtype=np.float32)
+    pw.hc.simulator.launch(pw.pairwise, t1, t2, t_out)
+    rng = np.random.default_rng(18)
+    p1 = (rng.standard_normal((37, 150)) * rng.choice([1e-3, 1.0, 300.0], size=(37, 150))).astype(np.float32)
+    p2 = (rng.standard_normal((29, 150)) * rng.choice([1e-3, 1.0, 300.0], size=(29, 150))).astype(np.float32)
+    p_out = np.full((37, 29), np.float32(-7.0))
+    pw.hc.simulator.launch(pw.pairwise, p1, p2, p_out)
+    q1 = rng.standard_normal((19, 333)).astype(np.float32)
+    q2 = rng.standard_normal((35, 333)).astype(np.float32)
+    q1[3, 200], q2[7, 5] = np.inf, np.nan
+    q_out = np.full((19, 35), np.float32(-7.0))
+    with np.errstate(invalid="ignore"):
+        pw.hc.simulator.launch(pw.pairwise_squared, q1, q2, q_out)
+    np.savez_compressed(HERE / "simpair_f32_seed18.npz", test_x1=t1, test_x2=t2, test_out=t_out, x1=p1, x2=p2, out=p_out,
+                        sq_x1=q1, sq_x2=q2, sq_out=q_out)
+    print(f"simpair_f32_seed18: pairwise{t_out.shape} pairwise{p_out.shape} pairwise_squared{q_out.shape}", flush=True)
     return 0
 
 
