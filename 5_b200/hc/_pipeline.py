@@ -126,14 +126,18 @@ def lower_for_target(kernel_fn: Any, target: str) -> TargetResult:
 
 
 def _looks_like_pairwise(kernel_fn: Any) -> bool:
-    """Two-dimensional work over three rank-2 buffers and no k-loop: not a member of the matmul family."""
+    """Three buffers, no k-loop and a reduction of a value (`.sum(...)`): not a member of the matmul family."""
     source = _function_node(kernel_fn)
-    has_loop = source is not None and any(isinstance(node, (ast.For, ast.While)) for node in ast.walk(source))
+    if source is None:
+        return False
+    nodes = list(ast.walk(source))
+    has_loop = any(isinstance(node, (ast.For, ast.While)) for node in nodes)
+    reduces = any(isinstance(node, ast.Attribute) and node.attr == "sum" for node in nodes)
     try:
         count = len(inspect.signature(kernel_fn).parameters)
     except (TypeError, ValueError):
         return False
-    return count == 4 and not has_loop
+    return count == 4 and reduces and not has_loop
 
 
 def _looks_one_dimensional(kernel_fn: Any) -> bool:

@@ -43,39 +43,62 @@ constexpr int kRowsPitch = kTileRows + 2;  // floats; keeps the 8-byte reads ali
 constexpr int kColsPitch = kTileCols + 4;  // floats; keeps the 16-byte reads aligned
 constexpr int kStackDepth = 24;   // pending partial sums: the recursion halves n down to 128
 
-// Stages `rows` rows x kChunk values of `x` (row-major, pitch ld) starting at (row0, h0), transposed:
-// dst[h][row]. Rows at or past `limit` and h at or past `h_end` are staged as zeros (never used
-// for an output that is stored, or added as an exact 0 difference).
-template <int kRows, int kPitch>
-__device__ __forceinline__ void stage_rows(float *dst, const float *__restrict__ x, long long ld, int row0, int limit,
-                                           int h0, int h_end, bool vector_ok) {
-  constexpr int kVectors = kRows * (kChunk / 4);
-  for (int v = threadIdx.x; v < kVectors; v += kThreads) {
+// The part of a chunk one thread brings in: `kVectors` groups of four consecutive h of one row each
+// (vector v of the chunk is row v / 8, h 4 (v % 8) .. + 3). Rows at or past `limit` and h at or past
+// `h_end` read as zeros (they are never used for an output that is stored, nor added to a sum).
+template <int kVectors>
+struct Fetched {
+  float4 value[kVectors];
+};
+
+template <int kVectors>
+__device__ __forceinline__ Fetched<kVectors> fetch_rows(const float *__restrict__ x, long long ld, int row0, int limit,
+                                                        int h0, int h_end, bool vector_ok) {
+  Fetched<kVectors> f;
+#pragma unroll
+  for (int i = 0; i < kVectors; ++i) {
+    const int v = static_cast<int>(threadIdx.x) + i * kThreads;
     const int row = v / (kChunk / 4), h = (v % (kChunk / 4)) * 4;
     float4 value = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    if (row0 + row < limit) {
+    if (row0 + row < limit && h0 + h < h_end) {
       const float *src = x + static_cast<long long>(row0 + row) * ld + h0 + h;
       if (vector_ok && h0 + h + 3 < h_end) {
         value = __ldg(reinterpret_cast<const float4 *>(src));
       } else {
-        if (h0 + h < h_end) value.x = __ldg(src);
+        value.x = __ldg(src);
         if (h0 + h + 1 < h_end) value.y = __ldg(src + 1);
         if (h0 + h + 2 < h_end) value.z = __ldg(src + 2);
         if (h0 + h + 3 < h_end) value.w = __ldg(src + 3);
       }
     }
-    dst[(h + 0) * kPitch + row] = value.x;
-    dst[(h + 1) * kPitch + row] = value.y;
-    dst[(h + 2) * kPitch + row] = value.z;
-    dst[(h + 3) * kPitch + row] = value.w;
+    f.value[i] = value;
+  }
+  return f;
+}
+
+// ... and puts into shared memory transposed: dst[h][row].
+template <int kVectors, int kPitch>
+__device__ __forceinline__ void stage_rows(float *dst, const Fetched<kVectors> &f) {
+#pragma unroll
+  for (int i = 0; i < kVectors; ++i) {
+    const int v = static_cast<int>(threadIdx.x) + i * kThreads;
+    const int row = v / (kChunk / 4), h = (v % (kChunk / 4)) * 4;
+    dst[(h + 0) * kPitch + row] = f.value[i].x;
+    dst[(h + 1) * kPitch + row] = f.value[i].y;
+    dst[(h + 2) * kPitch + row] = f.value[i].z;
+    dst[(h + 3) * kPitch + row] = f.value[i].w;
   }
 }
 
 template <bool kSqrt>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 2)
 pairwise_f32_kernel(const float *__restrict__ x1, long long ld1, const float *__restrict__ x2, long long ld2,
                     float *__restrict__ out, long long ldo, int w1, int w2, int h, const int4 *__restrict__ leaves,
                     int num_leaves, int tiles_j) {
+  constexpr int kRowVectors = kTileRows * (kChunk / 4) / kThreads;  // 1
+  constexpr int kColVectors = kTileCols * (kChunk / 4) / kThreads;  // 2
+  static_assert(kRowVectors * kThreads == kTileRows * (kChunk / 4) && kColVectors * kThreads == kTileCols * (kChunk / 4),
+                "every thread brings in the same number of vectors");
   __shared__ __align__(16) float rows_s[kChunk * kRowsPitch];
   __shared__ __align__(16) float cols_s[kChunk * kColsPitch];
   const int tile_i = blockIdx.x / tiles_j, tile_j = blockIdx.x - tile_i * tiles_j;
@@ -86,77 +109,102 @@ pairwise_f32_kernel(const float *__restrict__ x1, long long ld1, const float *__
 
   float pending[8][kStackDepth];  // per output: partial sums waiting for their right-hand neighbour
   int depth = 0;
+  float acc[8][8];
+  float sum[8];
+  // The chunks of all leaves in order; the next chunk's values are fetched into registers while the
+  // current one is being used.
+  int leaf = 0;
+  int4 entry = num_leaves > 0 ? leaves[0] : make_int4(0, 0, 0, 0);  // x: first h, y: length, z: additions once done
+  int c0 = entry.x;
+  Fetched<kRowVectors> next_rows;
+  Fetched<kColVectors> next_cols;
+  if (num_leaves > 0) {
+    next_rows = fetch_rows<kRowVectors>(x1, ld1, i0, w1, c0, entry.x + entry.y, vec1);
+    next_cols = fetch_rows<kColVectors>(x2, ld2, j0, w2, c0, entry.x + entry.y, vec2);
+  }
 #pragma unroll 1
-  for (int leaf = 0; leaf < num_leaves; ++leaf) {
-    const int4 entry = leaves[leaf];  // x: first h, y: length, z: additions once it is done
+  while (leaf < num_leaves) {
     const int begin = entry.x, full = entry.y & ~7, end = entry.x + entry.y;
-    float acc[8][8];
-#pragma unroll
-    for (int o = 0; o < 8; ++o)
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-        acc[o][j] = 0.0f;  // (0 + s == s exactly: a square is never -0)
-    float sum[8];
-#pragma unroll 1
-    for (int c0 = begin; c0 < end; c0 += kChunk) {
-      __syncthreads();  // the previous chunk has been read
-      stage_rows<kTileRows, kRowsPitch>(rows_s, x1, ld1, i0, w1, c0, end, vec1);
-      stage_rows<kTileCols, kColsPitch>(cols_s, x2, ld2, j0, w2, c0, end, vec2);
-      __syncthreads();
-      const int groups = min(kChunk, begin + full - c0) / 8;  // whole groups of eight in this chunk (may be <= 0)
-#pragma unroll 1
-      for (int g = 0; g < groups; ++g) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int hh = g * 8 + j;
-          const float2 a = *reinterpret_cast<const float2 *>(rows_s + hh * kRowsPitch + ty * 2);
-          const float4 b = *reinterpret_cast<const float4 *>(cols_s + hh * kColsPitch + tx * 4);
-          const float av[2] = {a.x, a.y};
-          const float bv[4] = {b.x, b.y, b.z, b.w};
-#pragma unroll
-          for (int r = 0; r < 2; ++r)
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-              const float d = __fsub_rn(av[r], bv[c]);
-              acc[r * 4 + c][j] = __fadd_rn(acc[r * 4 + c][j], __fmul_rn(d, d));
-            }
-        }
+    __syncthreads();  // the previous chunk has been read
+    stage_rows<kRowVectors, kRowsPitch>(rows_s, next_rows);
+    stage_rows<kColVectors, kColsPitch>(cols_s, next_cols);
+    __syncthreads();
+    int following_leaf = leaf, following_c0 = c0 + kChunk;
+    int4 following = entry;
+    if (following_c0 >= end) {
+      following_leaf = leaf + 1;
+      if (following_leaf < num_leaves) {
+        following = leaves[following_leaf];
+        following_c0 = following.x;
       }
-      if (c0 + kChunk >= end) {
-        // The leaf is complete: combine the accumulators, then the tail of fewer than eight values
-        // (it lies in this chunk) in order.
+    }
+    if (following_leaf < num_leaves) {
+      next_rows = fetch_rows<kRowVectors>(x1, ld1, i0, w1, following_c0, following.x + following.y, vec1);
+      next_cols = fetch_rows<kColVectors>(x2, ld2, j0, w2, following_c0, following.x + following.y, vec2);
+    }
+    if (c0 == begin) {
+#pragma unroll
+      for (int o = 0; o < 8; ++o)
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          acc[o][j] = 0.0f;  // (0 + s == s exactly: a square is never -0)
+    }
+    const int groups = min(kChunk, begin + full - c0) / 8;  // whole groups of eight in this chunk (may be <= 0)
+#pragma unroll 1
+    for (int g = 0; g < groups; ++g) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int hh = g * 8 + j;
+        const float2 a = *reinterpret_cast<const float2 *>(rows_s + hh * kRowsPitch + ty * 2);
+        const float4 b = *reinterpret_cast<const float4 *>(cols_s + hh * kColsPitch + tx * 4);
+        const float av[2] = {a.x, a.y};
+        const float bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int r = 0; r < 2; ++r)
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const float d = __fsub_rn(av[r], bv[c]);
+            acc[r * 4 + c][j] = __fadd_rn(acc[r * 4 + c][j], __fmul_rn(d, d));
+          }
+      }
+    }
+    if (c0 + kChunk >= end) {
+      // The leaf is complete: combine the accumulators, then the tail of fewer than eight values
+      // (it lies in this chunk) in order.
+#pragma unroll
+      for (int o = 0; o < 8; ++o)
+        sum[o] = __fadd_rn(__fadd_rn(__fadd_rn(acc[o][0], acc[o][1]), __fadd_rn(acc[o][2], acc[o][3])),
+                           __fadd_rn(__fadd_rn(acc[o][4], acc[o][5]), __fadd_rn(acc[o][6], acc[o][7])));
+      for (int hh = begin + full - c0; hh < end - c0; ++hh) {
+        const float2 a = *reinterpret_cast<const float2 *>(rows_s + hh * kRowsPitch + ty * 2);
+        const float4 b = *reinterpret_cast<const float4 *>(cols_s + hh * kColsPitch + tx * 4);
+        const float av[2] = {a.x, a.y};
+        const float bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int r = 0; r < 2; ++r)
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const float d = __fsub_rn(av[r], bv[c]);
+            sum[r * 4 + c] = __fadd_rn(sum[r * 4 + c], __fmul_rn(d, d));
+          }
+      }
+      // Push, then add the pairs the recursion closes here (left + right).
+      if (depth < kStackDepth) {
 #pragma unroll
         for (int o = 0; o < 8; ++o)
-          sum[o] = __fadd_rn(__fadd_rn(__fadd_rn(acc[o][0], acc[o][1]), __fadd_rn(acc[o][2], acc[o][3])),
-                             __fadd_rn(__fadd_rn(acc[o][4], acc[o][5]), __fadd_rn(acc[o][6], acc[o][7])));
-        for (int hh = begin + full - c0; hh < end - c0; ++hh) {
-          const float2 a = *reinterpret_cast<const float2 *>(rows_s + hh * kRowsPitch + ty * 2);
-          const float4 b = *reinterpret_cast<const float4 *>(cols_s + hh * kColsPitch + tx * 4);
-          const float av[2] = {a.x, a.y};
-          const float bv[4] = {b.x, b.y, b.z, b.w};
+          pending[o][depth] = sum[o];
+        ++depth;
+      }
+      for (int a = 0; a < entry.z && depth >= 2; ++a) {
+        --depth;
 #pragma unroll
-          for (int r = 0; r < 2; ++r)
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-              const float d = __fsub_rn(av[r], bv[c]);
-              sum[r * 4 + c] = __fadd_rn(sum[r * 4 + c], __fmul_rn(d, d));
-            }
-        }
+        for (int o = 0; o < 8; ++o)
+          pending[o][depth - 1] = __fadd_rn(pending[o][depth - 1], pending[o][depth]);
       }
     }
-    // Push, then add the pairs the recursion closes here (left + right).
-    if (depth < kStackDepth) {
-#pragma unroll
-      for (int o = 0; o < 8; ++o)
-        pending[o][depth] = sum[o];
-      ++depth;
-    }
-    for (int a = 0; a < entry.z && depth >= 2; ++a) {
-      --depth;
-#pragma unroll
-      for (int o = 0; o < 8; ++o)
-        pending[o][depth - 1] = __fadd_rn(pending[o][depth - 1], pending[o][depth]);
-    }
+    leaf = following_leaf;
+    entry = following;
+    c0 = following_c0;
   }
 
 #pragma unroll

@@ -104,7 +104,7 @@ def test_other_signatures_and_geometries_are_refused(kwargs, why: str) -> None:
 
 
 def test_unrecognised_pairwise_kernels_report_why_through_compile() -> None:
-    handle = hc.compile(_variant(GOOD.replace("** 2", "** 4")), target=TARGET)
+    handle = hc.compile(_variant(GOOD.replace("** 2", "** 4")), target=TARGET)  # (still a `.sum(...)` of something)
     assert handle.plan is None and any("is not `np.sqrt" in text for text in handle.pipeline_diagnostics)
     with pytest.raises(NotImplementedError, match="cannot launch"):
         handle(np.zeros((2, 2), np.float32), np.zeros((2, 2), np.float32), np.zeros((2, 2), np.float32))
