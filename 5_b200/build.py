@@ -22,6 +22,7 @@ REPO_ROOT = PACKAGE_DIR.parent
 LIB_DIR = PACKAGE_DIR / "lib"
 BUILD_DIR = LIB_DIR / "build"
 OUTPUT = LIB_DIR / "libhc_cuda.so"
+CHECKED_OUTPUT = LIB_DIR / "libhc_cuda_checked.so"
 
 SOURCES = [
     LIB_DIR / "Kernels" / "gemm_dense_sm100a.cu",
@@ -42,6 +43,7 @@ HEADERS = [
     LIB_DIR / "Kernels" / "gemm_launch.h",
     LIB_DIR / "Kernels" / "sm100_ptx.cuh",
     LIB_DIR / "Kernels" / "gemm_epilogue.cuh",
+    LIB_DIR / "Kernels" / "device_checks.cuh",
     REPO_ROOT / "include" / "hc-c" / "Cuda.h",
 ]
 
@@ -71,34 +73,45 @@ def _stale(target: Path, deps: list[Path]) -> bool:
     return any(dep.stat().st_mtime > stamp for dep in deps)
 
 
-def build(*, force: bool = False, verbose: bool = False) -> Path:
-    """Compiles what is out of date and returns the path of the shared library."""
+def build(*, force: bool = False, verbose: bool = False, checked: bool = False) -> Path:
+    """Compiles what is out of date and returns the path of the shared library. `checked`: the
+    variant with index checks inside the kernels (-DHC_CUDA_CHECKED, lib/libhc_cuda_checked.so)."""
+    from concurrent.futures import ThreadPoolExecutor
+
     nvcc = find_nvcc()
-    BUILD_DIR.mkdir(parents=True, exist_ok=True)
-    objects = []
+    build_dir = BUILD_DIR.with_name(BUILD_DIR.name + "_checked") if checked else BUILD_DIR
+    output = CHECKED_OUTPUT if checked else OUTPUT
+    flags = [*NVCC_FLAGS, "-DHC_CUDA_CHECKED=1"] if checked else NVCC_FLAGS
+    build_dir.mkdir(parents=True, exist_ok=True)
+    objects, commands = [], []
     for src in SOURCES:
-        obj = BUILD_DIR / (src.stem + ".o")
+        obj = build_dir / (src.stem + ".o")
         objects.append(obj)
         if force or _stale(obj, [src, *HEADERS, Path(__file__)]):
-            cmd = [nvcc, *NVCC_FLAGS, "-x", "cu", "-c", str(src), "-o", str(obj)]
+            cmd = [nvcc, *flags, "-x", "cu", "-c", str(src), "-o", str(obj)]
             if verbose:
                 cmd.insert(1, "-Xptxas=-v")
                 print(" ".join(cmd), flush=True)
-            subprocess.run(cmd, check=True)
-    if force or _stale(OUTPUT, objects):
-        cmd = [nvcc, "-shared", "-Wno-deprecated-gpu-targets", "-o", str(OUTPUT), *map(str, objects), "-ldl"]
+            commands.append(cmd)
+    with ThreadPoolExecutor(max_workers=max(1, min(8, os.cpu_count() or 1))) as pool:
+        for done in pool.map(lambda cmd: subprocess.run(cmd, check=True), commands):
+            del done
+    if force or _stale(output, objects):
+        cmd = [nvcc, "-shared", "-Wno-deprecated-gpu-targets", "-o", str(output), *map(str, objects), "-ldl"]
         if verbose:
             print(" ".join(cmd), flush=True)
         subprocess.run(cmd, check=True)
-    return OUTPUT
+    return output
 
 
 def main(argv: list[str] | None = None) -> int:
     parser = argparse.ArgumentParser(description=__doc__.splitlines()[0])
     parser.add_argument("--force", action="store_true", help="rebuild everything")
     parser.add_argument("--verbose", action="store_true", help="print commands and ptxas resource use")
+    parser.add_argument("--checked", action="store_true",
+                        help="build libhc_cuda_checked.so (index checks inside the kernels) instead")
     args = parser.parse_args(argv)
-    print(build(force=args.force, verbose=args.verbose))
+    print(build(force=args.force, verbose=args.verbose, checked=args.checked))
     return 0
 
 

@@ -56,7 +56,7 @@ EXPORTS = (
     "hcCudaEventDestroy", "hcCudaEventRecord", "hcCudaEventElapsedMs", "hcCudaCommGetUniqueId",
     "hcCudaCommInitRank", "hcCudaCommAllGather", "hcCudaCommDestroy", "hcCudaGemmSkinnyStatic", "hcCudaSelfTestDeviceTimeout", "hcCudaGemmPush", "hcCudaIpcExport",
     "hcCudaIpcOpen", "hcCudaIpcClose", "hcCudaMap", "hcCudaMapHost",
-    "hcCudaGemmHostDeviceA", "hcCudaPairwise", "hcCudaPairwiseHost",
+    "hcCudaGemmHostDeviceA", "hcCudaPairwise", "hcCudaPairwiseHost", "hcCudaBuildFlags", "hcCudaSelfTestDeviceCheck",
 )
 
 
@@ -199,12 +199,18 @@ def library() -> ctypes.CDLL:
         lib.hcCudaGemmSkinnyStatic.argtypes = [ctypes.POINTER(_GemmArgs), vp, i, ctypes.c_char_p, sz]
         lib.hcCudaMap.argtypes = [vp, ctypes.POINTER(_MapArgs)]
         lib.hcCudaMapHost.argtypes = [vp, ctypes.POINTER(_MapArgs)]
+        lib.hcCudaSelfTestDeviceCheck.argtypes = [vp]
         lib.hcCudaPairwise.argtypes = [vp, ctypes.POINTER(_PairwiseArgs)]
         lib.hcCudaPairwiseHost.argtypes = [vp, ctypes.POINTER(_PairwiseArgs)]
         for name in EXPORTS:
             getattr(lib, name)  # AttributeError here means a stale or foreign library
         _LIB = lib
     return _LIB
+
+
+def library_is_checked() -> bool:
+    """Whether the loaded library is the checked build (in-kernel index checks; `HC_CUDA_LIB` selects it)."""
+    return bool(library().hcCudaBuildFlags() & 1)
 
 
 def _raise(status: int, ctx_handle: Any = None) -> None:
@@ -518,6 +524,11 @@ class Context:
         if bias is not None and (bias.dtype != np.float32 or bias.shape != (n,) or not bias.flags.c_contiguous):
             raise ValueError("bias must be a contiguous float32 vector of n values")
         self._check(self._lib.hcCudaGemmHost(self._handle, ctypes.byref(args)))
+
+    def selftest_device_check(self) -> None:
+        """Checked build only: enqueues a kernel whose index check fails (the access is skipped); the
+        next `synchronize` raises DeviceError (HC_CUDA_ERR_DEVICE_CHECK) and the context stays usable."""
+        self._check(self._lib.hcCudaSelfTestDeviceCheck(self._handle))
 
     def selftest_device_timeout(self, budget_cycles: int = 2_000_000) -> None:
         """Enqueues a kernel whose bounded wait runs out; the next `synchronize` raises

@@ -746,6 +746,11 @@ int synchronize_locked(HcCudaContext *ctx) {
     if (ctx->counters != nullptr)
       HC_TRY_CUDA(ctx, cudaMemsetAsync(ctx->counters, 0, ctx->counters_bytes, ctx->stream));
     HC_TRY_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if ((device_status & 0xff) == hc::sm100::kStatusCheckFailed)
+      return fail(ctx, HC_CUDA_ERR_DEVICE_CHECK,
+                  "index check %d of a kernel failed (checked build): the access was not made; the output of that "
+                  "launch is invalid",
+                  device_status >> 8);
     return fail(ctx, HC_CUDA_ERR_DEVICE_TIMEOUT,
                 "a kernel reported status %d: a bounded device-side wait ran out; the output of "
                 "that launch is invalid",
@@ -760,6 +765,8 @@ extern "C" {
 
 int hcCudaApiVersion(void) { return HC_CUDA_API_VERSION; }
 
+int hcCudaBuildFlags(void) { return hc::sm100::library_is_checked() ? 1 : 0; }
+
 const char *hcCudaStatusString(int status) {
   switch (status) {
   case HC_CUDA_OK: return "HC_CUDA_OK";
@@ -770,6 +777,7 @@ const char *hcCudaStatusString(int status) {
   case HC_CUDA_ERR_DEVICE_TIMEOUT: return "HC_CUDA_ERR_DEVICE_TIMEOUT";
   case HC_CUDA_ERR_COMM: return "HC_CUDA_ERR_COMM";
   case HC_CUDA_ERR_OUT_OF_MEMORY: return "HC_CUDA_ERR_OUT_OF_MEMORY";
+  case HC_CUDA_ERR_DEVICE_CHECK: return "HC_CUDA_ERR_DEVICE_CHECK";
   default: return "HC_CUDA_ERR_UNKNOWN";
   }
 }
@@ -1731,6 +1739,17 @@ int hcCudaSelfTestDeviceTimeout(HcCudaContext *ctx, int64_t budget_cycles) {
   std::lock_guard<std::mutex> lock(ctx->mu);
   HC_TRY_CUDA(ctx, cudaSetDevice(ctx->device));
   HC_TRY_CUDA(ctx, hc::sm100::launch_wait_selftest(budget_cycles, ctx->status_dev, ctx->stream));
+  return HC_CUDA_OK;
+}
+
+int hcCudaSelfTestDeviceCheck(HcCudaContext *ctx) {
+  if (ctx == nullptr)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "ctx must not be null");
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  if (!hc::sm100::library_is_checked())
+    return fail(ctx, HC_CUDA_ERR_UNSUPPORTED, "this library is not the checked build");
+  HC_TRY_CUDA(ctx, cudaSetDevice(ctx->device));
+  HC_TRY_CUDA(ctx, hc::sm100::launch_check_selftest(ctx->status_dev, ctx->stream));
   return HC_CUDA_OK;
 }
 

@@ -28,6 +28,7 @@
 // Needs a float32 C that TMA can address (16-byte aligned base and pitch) and no push targets; the
 // caller keeps the counter-based split of the persistent kernels otherwise.
 #include "gemm_epilogue.cuh"
+#include "device_checks.cuh"
 #include "gemm_launch.h"
 #include "sm100_ptx.cuh"
 
@@ -264,8 +265,18 @@ gemm_dense_cluster_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
     // ------------------------------------------------------------ TMA producer ------
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
-      for (int kb = kb_begin; kb < kb_end; ++kb) {
+      const bool placed =
+          HC_CHECK(status, abort_flag, HC_CHECK_TILE_COORDINATES,
+                   tile >= 0 && group >= 0 && group < groups && m0 < m + kBlockM && n0 / kBlockN < tiles_n && rank < ranks) &&
+          HC_CHECK(status, abort_flag, HC_CHECK_K_BLOCKS, kb_begin >= 0 && kb_begin <= kb_end && kb_end <= num_kb);
+      for (int kb = kb_begin; placed && kb < kb_end; ++kb) {
         if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag))
+          break;
+        if (!HC_CHECK(status, abort_flag, HC_CHECK_RING_STAGE,
+                      stage < kStages && smem_base + (stage + 1) * kStageBytes <= epi_base) ||
+            !HC_CHECK(status, abort_flag, HC_CHECK_TMA_COORDINATES,
+                      m0 >= 0 && n0 >= 0 && ((n0 * 2) & 15) == 0 &&
+                          ((((kb * kBlockK) << elem8) * (elem8 ? 1 : 2)) & 15) == 0))
           break;
         const uint32_t a_dst = smem_base + stage * kStageBytes;
         const uint32_t b_dst = a_dst + kATileBytes;
@@ -388,6 +399,11 @@ gemm_dense_cluster_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
       const int first_row = part * (32 / parts);
       const int row_base = m0 + (block >> 3) * 32 + first_row;
       const int col_base = n0 + (block & 7) * 32;
+      if (!HC_CHECK(status, abort_flag, HC_CHECK_PARTIAL_SLOT,
+                    block >= 0 && block < kBlocks && first_row >= 0 && first_row + 32 / parts <= 32 &&
+                        static_cast<uint32_t>(block) * kBlockBytes + static_cast<uint32_t>(first_row) * 128u +
+                                (32u / static_cast<uint32_t>(parts)) * 128u <= kPartialBytes))
+        break;
       if (row_base >= m || col_base >= n)
         continue;  // warp-uniform, and the same in every cluster of the tile: the rows lie outside C
       if (parts == 1)
@@ -407,7 +423,7 @@ gemm_dense_cluster_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
   __syncthreads();
   if (*abort_flag != 0) {
     if (threadIdx.x == 0)
-      atomicExch(status, kStatusDeviceWaitTimeout);
+      atomicCAS(status, 0, kStatusDeviceWaitTimeout);  // (a failed check recorded earlier stays)
     const long long start = clock64();
     while (clock64() - start < 2000000LL) {
     }

@@ -28,6 +28,7 @@
 // element-wise operations, writes a float32 or 16-bit C, and, when tiles are split over k, parks
 // partial tiles and lets the last unit of a tile add them up.
 #include "gemm_epilogue.cuh"
+#include "device_checks.cuh"
 #include "gemm_launch.h"
 #include "sm100_ptx.cuh"
 
@@ -182,8 +183,21 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const int m0 = tc.m_blk * kTileM + static_cast<int>(cta_rank) * kCtaM;
         const int n0 = tc.n_blk * kTileN + static_cast<int>(cta_rank) * kCtaN;
         const int kb_end = first_kb(u.part + 1, u.parts);
+        if (!HC_CHECK(status, abort_flag, HC_CHECK_TILE_COORDINATES,
+                      tc.m_blk >= 0 && tc.m_blk < tiles_m && tc.n_blk >= 0 && tc.n_blk < tiles_n) ||
+            !HC_CHECK(status, abort_flag, HC_CHECK_K_BLOCKS,
+                      u.part >= 0 && u.part < u.parts && first_kb(u.part, u.parts) >= 0 && kb_end <= num_kb))
+          break;
         for (int kb = first_kb(u.part, u.parts); kb < kb_end; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
+            ok = false;
+            break;
+          }
+          if (!HC_CHECK(status, abort_flag, HC_CHECK_RING_STAGE,
+                        stage < kStages && smem_base + (stage + 1) * kStageBytes <= epi_base) ||
+              !HC_CHECK(status, abort_flag, HC_CHECK_TMA_COORDINATES,
+                        m0 >= 0 && n0 >= 0 && kb >= 0 && ((n0 * 2) & 15) == 0 &&
+                            ((((kb * kBlockK) << elem8) * (elem8 ? 1 : 2)) & 15) == 0)) {
             ok = false;
             break;
           }
@@ -298,6 +312,13 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       tcgen05_fence_after_sync();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kTileN +
                              column_part * kColumnsPerWarp;
+      if (!HC_CHECK(status, abort_flag, HC_CHECK_TMEM_COLUMNS,
+                    acc * kTileN + column_part * kColumnsPerWarp + kColumnsPerWarp <= kTmemColumns) ||
+          !HC_CHECK(status, abort_flag, HC_CHECK_OUTPUT_RANGE,
+                    row_base >= 0 && row_base < tiles_m * kTileM && col_base >= 0 && col_base < tiles_n * kTileN) ||
+          !HC_CHECK(status, abort_flag, HC_CHECK_PARTIAL_SLOT,
+                    u.parts == 1 || (u.split_index >= 0 && u.split_tile >= 0 && u.split_index < num_units)))
+        break;
       if (u.parts == 1) {
         drain_accumulator_rows<kColumnsPerWarp, kReadsC>(taddr, stage_gen, c, ldc, m, n, row_base, col_base, vec_ok,
                                                         lane, map_to_cta(tmem_empty_bar(acc), 0),
@@ -339,7 +360,7 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
   __syncthreads();
   if (*abort_flag != 0) {
     if (threadIdx.x == 0)
-      atomicExch(status, kStatusDeviceWaitTimeout);
+      atomicCAS(status, 0, kStatusDeviceWaitTimeout);  // (a failed check recorded earlier stays)
     const long long start = clock64();
     while (clock64() - start < 2000000LL) {
     }

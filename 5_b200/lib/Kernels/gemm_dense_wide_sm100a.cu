@@ -25,6 +25,7 @@
 // ordinary loads and that are neither split over k nor pushed to peers; everything else runs
 // gemm_dense_pair_kernel.
 #include "gemm_epilogue.cuh"
+#include "device_checks.cuh"
 #include "gemm_launch.h"
 #include "sm100_ptx.cuh"
 
@@ -145,8 +146,19 @@ gemm_dense_wide_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const TileCoord tc = tile_coord(tile, tiles_m, tiles_n, group_n);
         const int m0 = tc.m_blk * kTileM + static_cast<int>(cta_rank) * kCtaM;
         const int n0 = tc.n_blk * kTileN + static_cast<int>(cta_rank) * kCtaN;
+        if (!HC_CHECK(status, abort_flag, HC_CHECK_TILE_COORDINATES,
+                      tc.m_blk >= 0 && tc.m_blk < tiles_m && tc.n_blk >= 0 && tc.n_blk < tiles_n))
+          break;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
+            ok = false;
+            break;
+          }
+          if (!HC_CHECK(status, abort_flag, HC_CHECK_RING_STAGE,
+                        stage < kStages && smem_base + (stage + 1) * kStageBytes <= epi_base) ||
+              !HC_CHECK(status, abort_flag, HC_CHECK_TMA_COORDINATES,
+                        m0 >= 0 && n0 >= 0 && ((n0 * 2) & 15) == 0 &&
+                            ((((kb * kBlockK) << elem8) * (elem8 ? 1 : 2)) & 15) == 0)) {
             ok = false;
             break;
           }
@@ -260,6 +272,13 @@ gemm_dense_wide_kernel(const __grid_constant__ CUtensorMap tmap_a,
                              quarter * 32;
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + h * kTileN +
                                column_part * kColumnsPerWarp;
+        if (!HC_CHECK(status, abort_flag, HC_CHECK_TMEM_COLUMNS,
+                      h * kTileN + column_part * kColumnsPerWarp + kColumnsPerWarp <= kTmemColumns) ||
+            !HC_CHECK(status, abort_flag, HC_CHECK_OUTPUT_RANGE,
+                      row_base >= 0 && row_base < tiles_m * kTileM && col_base >= 0 && col_base < tiles_n * kTileN)) {
+          ok = false;
+          break;
+        }
         drain_accumulator_rows<kColumnsPerWarp, false>(taddr, stage_gen, c, ldc, m, n, row_base, col_base, vec_ok, lane,
                                                        map_to_cta(tmem_empty_bar(h), 0), /*release_remote=*/true, ep,
                                                        c_tma ? &tmap_c : nullptr);
@@ -275,7 +294,7 @@ gemm_dense_wide_kernel(const __grid_constant__ CUtensorMap tmap_a,
   __syncthreads();
   if (*abort_flag != 0) {
     if (threadIdx.x == 0)
-      atomicExch(status, kStatusDeviceWaitTimeout);
+      atomicCAS(status, 0, kStatusDeviceWaitTimeout);  // (a failed check recorded earlier stays)
     const long long start = clock64();
     while (clock64() - start < 2000000LL) {
     }

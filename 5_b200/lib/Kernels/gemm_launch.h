@@ -32,6 +32,7 @@ constexpr int kCTypeBF16 = 2;
 
 // Value a kernel writes to the status word when one of its bounded waits ran out.
 constexpr int kStatusDeviceWaitTimeout = 5;
+constexpr int kStatusCheckFailed = 6;  // checked build: low byte; the number of the check above it
 
 // Additional destinations of a dense GEMM's output: every tile of C is also stored, at the same
 // row/column offsets and with the same pitch, to each of these matrices. Used to push a rank's
@@ -221,6 +222,10 @@ cudaError_t launch_epilogue_only(void *c, int m, int n, long long ldc, const Epi
 // signals and then reports kStatusDeviceWaitTimeout through `status`, like a GEMM kernel whose
 // wait ran out.
 cudaError_t launch_wait_selftest(long long budget_cycles, int *status, cudaStream_t stream);
+// Checked build only: one thread checks an index that is made up to be out of range, does not make
+// the access and reports the failed check through `status`. cudaErrorNotSupported otherwise.
+cudaError_t launch_check_selftest(int *status, cudaStream_t stream);
+bool library_is_checked();
 
 // 8-bit operands: copies a rows x cols matrix of bytes (pitch src_ld) to dst with pitch dst_ld
 // (a multiple of 16), transposed when `transpose` is set (dst is then cols x rows). This is how a

@@ -19,6 +19,7 @@
 // Warp roles: warp 0 TMA producer, warp 1 TMEM owner + tcgen05.mma issuer, warps 2-5
 // epilogue (TMEM -> registers -> partials / C).
 #include "gemm_epilogue.cuh"
+#include "device_checks.cuh"
 #include "gemm_launch.h"
 #include "sm100_ptx.cuh"
 
@@ -125,8 +126,19 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const int kb_begin = static_cast<int>(static_cast<long long>(split) * kb_total / splits);
         const int kb_end = static_cast<int>(static_cast<long long>(split + 1) * kb_total / splits);
         const int n0 = n_tile * kBlockN;
+        if (!HC_CHECK(status, abort_flag, HC_CHECK_TILE_COORDINATES, n_tile >= 0 && n_tile < n_tiles) ||
+            !HC_CHECK(status, abort_flag, HC_CHECK_K_BLOCKS,
+                      split >= 0 && split < splits && kb_begin >= 0 && kb_begin <= kb_end && kb_end <= kb_total))
+          break;
         for (int kb = kb_begin; kb < kb_end; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
+            ok = false;
+            break;
+          }
+          if (!HC_CHECK(status, abort_flag, HC_CHECK_RING_STAGE,
+                        stage < kStages && smem_base + (stage + 1) * Cfg::kStageBytes <= bar_base) ||
+              !HC_CHECK(status, abort_flag, HC_CHECK_TMA_COORDINATES,
+                        ((n0 * 2) & 15) == 0 && ((((kb * kBlockK) << elem8) * (elem8 ? 1 : 2)) & 15) == 0)) {
             ok = false;
             break;
           }
@@ -231,6 +243,10 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a,
       // TMEM columns are the rows of C.
       uint32_t r[kMp];
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kMp;
+      if (!HC_CHECK(status, abort_flag, HC_CHECK_TMEM_COLUMNS, acc * kMp + kMp <= Cfg::kTmemColumns) ||
+          !HC_CHECK(status, abort_flag, HC_CHECK_OUTPUT_RANGE, n_tile >= 0 && n_tile < n_tiles) ||
+          !HC_CHECK(status, abort_flag, HC_CHECK_PARTIAL_SLOT, split >= 0 && split < splits))
+        break;
 #pragma unroll
       for (int g = 0; g < kMp / 16; ++g) {
         uint32_t part[16];
@@ -331,7 +347,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a,
   tcgen05_fence_after_sync();
   if (*abort_flag != 0) {
     if (threadIdx.x == 0)
-      atomicExch(status, kStatusDeviceWaitTimeout);
+      atomicCAS(status, 0, kStatusDeviceWaitTimeout);  // (a failed check recorded earlier stays)
     const long long start = clock64();
     while (clock64() - start < 2000000LL) {
     }

@@ -6,6 +6,7 @@
 // faulting or hanging anything: one thread waits, with a budget of about a millisecond, on an
 // mbarrier that nothing ever signals, and then follows the same give-up path as the GEMM
 // kernels (abort flag -> status word -> return).
+#include "device_checks.cuh"
 #include "gemm_launch.h"
 #include "sm100_ptx.cuh"
 
@@ -27,7 +28,33 @@ __global__ void __launch_bounds__(32) wait_that_runs_out_kernel(long long budget
   }
 }
 
+// The checked build's self-test: an index past the end of a small array is checked, found out of
+// range, recorded, and the access is skipped.
+__global__ void __launch_bounds__(32) check_that_fails_kernel(int *status, int index, int *sink) {
+  __shared__ int values[8];
+  if (threadIdx.x < 8)
+    values[threadIdx.x] = static_cast<int>(threadIdx.x);
+  __syncthreads();
+  if (threadIdx.x == 0 && HC_CHECK(status, nullptr, HC_CHECK_SELFTEST, index >= 0 && index < 8))
+    *sink = values[index];  // (not reached with the index the host passes)
+}
+
 } // namespace
+
+bool library_is_checked() {
+#ifdef HC_CUDA_CHECKED
+  return true;
+#else
+  return false;
+#endif
+}
+
+cudaError_t launch_check_selftest(int *status, cudaStream_t stream) {
+  if (!library_is_checked())
+    return cudaErrorNotSupported;
+  check_that_fails_kernel<<<1, 32, 0, stream>>>(status, 8, status);
+  return cudaGetLastError();
+}
 
 cudaError_t launch_wait_selftest(long long budget_cycles, int *status, cudaStream_t stream) {
   if (budget_cycles < 1000)

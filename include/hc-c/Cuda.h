@@ -49,7 +49,9 @@ typedef enum HcCudaStatus {
   HC_CUDA_ERR_NO_DEVICE = 4,        /* no such device, or not an sm_100 device */
   HC_CUDA_ERR_DEVICE_TIMEOUT = 5,   /* a bounded wait inside a kernel ran out */
   HC_CUDA_ERR_COMM = 6,             /* NCCL missing, not initialised, or a collective failed */
-  HC_CUDA_ERR_OUT_OF_MEMORY = 7
+  HC_CUDA_ERR_OUT_OF_MEMORY = 7,
+  HC_CUDA_ERR_DEVICE_CHECK = 8      /* checked build: an index check inside a kernel failed (the access
+                                       was not made); the message names the check */
 } HcCudaStatus;
 
 /* Element type of A and B. Accumulation is always float32 and C is float32 unless c_dtype says
@@ -175,6 +177,12 @@ typedef struct HcCudaContext HcCudaContext;
 typedef struct HcCudaEvent HcCudaEvent;
 
 /* ---- library ------------------------------------------------------------------------ */
+
+/* Bit 0: the library is the checked build (libhc_cuda_checked.so, compiled with -DHC_CUDA_CHECKED):
+ * its GEMM kernels verify tile coordinates, k-block ranges, ring stages, TMA coordinates,
+ * tensor-memory columns, output ranges and partial-tile slots before using them, and a failure is
+ * reported as HC_CUDA_ERR_DEVICE_CHECK at the next synchronise instead of becoming a wild access. */
+HC_CUDA_CAPI_EXPORTED int hcCudaBuildFlags(void);
 
 /* Returns HC_CUDA_API_VERSION of the built library. */
 HC_CUDA_CAPI_EXPORTED int hcCudaApiVersion(void);
@@ -427,6 +435,13 @@ HC_CUDA_CAPI_EXPORTED int hcCudaGemmSkinnyStatic(const HcCudaGemmArgs *args, voi
  * hcCudaContextSynchronize therefore returns HC_CUDA_ERR_DEVICE_TIMEOUT, clears the status and
  * leaves the context usable. Nothing faults or hangs. No counterpart in the reference. */
 HC_CUDA_CAPI_EXPORTED int hcCudaSelfTestDeviceTimeout(HcCudaContext *ctx, int64_t budget_cycles);
+
+/* Checked build only (HC_CUDA_ERR_UNSUPPORTED otherwise): enqueues a one-thread kernel that checks
+ * an index made up to be out of range, skips the access and records the failed check; the next
+ * hcCudaContextSynchronize returns HC_CUDA_ERR_DEVICE_CHECK and the context stays usable. Makes
+ * the checked build's reporting path observable without faulting anything. No counterpart in the
+ * reference. */
+HC_CUDA_CAPI_EXPORTED int hcCudaSelfTestDeviceCheck(HcCudaContext *ctx);
 
 /* ---- timing ------------------------------------------------------------------------- */
 

@@ -295,3 +295,19 @@ def test_comm_entry_points_validate_before_touching_nccl() -> None:
     assert lib.hcCudaCommGetUniqueId(buf, 16) == 1
     assert lib.hcCudaCommAllGather(None, None, None, 0) == 1
     assert lib.hcCudaCommInitRank(None, buf, 16, 2, 0) == 1
+
+
+def test_checked_build_exports_the_same_symbols() -> None:
+    """`python 5_b200/build.py --checked` gives libhc_cuda_checked.so: the same C ABI, with index checks
+    compiled into the kernels (a flag says which build a library is)."""
+    import importlib
+
+    checked = importlib.import_module("build").build(checked=True)  # (5_b200/ is on the path: conftest)
+    assert checked.name == "libhc_cuda_checked.so" and checked.exists()
+    lib = ctypes.CDLL(str(checked))
+    for name in cuda.EXPORTS:
+        assert hasattr(lib, name), name
+    assert lib.hcCudaBuildFlags() & 1 and not cuda.library_is_checked()
+    assert lib.hcCudaApiVersion() == cuda.API_VERSION
+    lib.hcCudaStatusString.restype = ctypes.c_char_p
+    assert lib.hcCudaStatusString(8) == b"HC_CUDA_ERR_DEVICE_CHECK"
