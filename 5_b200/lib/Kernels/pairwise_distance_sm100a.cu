@@ -29,18 +29,21 @@
 #include "gemm_launch.h"
 
 #include <cstdint>
+#include <cstdlib>
 
 namespace hc {
 namespace sm100 {
 
 namespace {
 
-constexpr int kTileRows = 32;     // of x1 per CTA (outputs i)
 constexpr int kTileCols = 64;     // rows of x2 per CTA (outputs j)
-constexpr int kThreads = 256;     // 16 x 16: a thread owns 2 rows x 4 columns
+constexpr int kThreads = 256;     // 16 x 16: a thread owns kRowsPerThread rows x 4 columns
 constexpr int kChunk = 32;        // h staged per step
-constexpr int kRowsPitch = kTileRows + 2;  // floats; keeps the 8-byte reads aligned
 constexpr int kColsPitch = kTileCols + 4;  // floats; keeps the 16-byte reads aligned
+// Rows of x1 per CTA (outputs i) and the pitch of their staging, for 2 or 4 rows per thread: the
+// pitch keeps the 8-byte (16-byte) reads of a thread's rows aligned.
+__host__ __device__ constexpr int tile_rows(int rows_per_thread) { return 16 * rows_per_thread; }
+__host__ __device__ constexpr int rows_pitch(int rows_per_thread) { return tile_rows(rows_per_thread) + rows_per_thread; }
 constexpr int kStackDepth = 24;   // pending partial sums: the recursion halves n down to 128
 
 // The part of a chunk one thread brings in: `kVectors` groups of four consecutive h of one row each
@@ -90,12 +93,30 @@ __device__ __forceinline__ void stage_rows(float *dst, const Fetched<kVectors> &
   }
 }
 
-template <bool kSqrt>
-__global__ void __launch_bounds__(kThreads, 2)
+// The values of a thread's rows (kR of them, consecutive) and columns (4) at one h.
+template <int kR>
+__device__ __forceinline__ void load_operands(const float *rows_s, const float *cols_s, int hh, int ty, int tx,
+                                              float (&av)[kR], float (&bv)[4]) {
+  if constexpr (kR == 2) {
+    const float2 a = *reinterpret_cast<const float2 *>(rows_s + hh * rows_pitch(2) + ty * 2);
+    av[0] = a.x, av[1] = a.y;
+  } else {
+    const float4 a = *reinterpret_cast<const float4 *>(rows_s + hh * rows_pitch(4) + ty * 4);
+    av[0] = a.x, av[1] = a.y, av[2] = a.z, av[3] = a.w;
+  }
+  const float4 b = *reinterpret_cast<const float4 *>(cols_s + hh * kColsPitch + tx * 4);
+  bv[0] = b.x, bv[1] = b.y, bv[2] = b.z, bv[3] = b.w;
+}
+
+// kR: rows per thread (2: 32 x 64 outputs per CTA, two CTAs per SM; 4: 64 x 64, one CTA per SM, half
+// the shared-memory loads per arithmetic instruction).
+template <int kR, bool kSqrt>
+__global__ void __launch_bounds__(kThreads, kR == 2 ? 2 : 1)
 pairwise_f32_kernel(const float *__restrict__ x1, long long ld1, const float *__restrict__ x2, long long ld2,
                     float *__restrict__ out, long long ldo, int w1, int w2, int h, const int4 *__restrict__ leaves,
                     int num_leaves, int tiles_j) {
-  constexpr int kRowVectors = kTileRows * (kChunk / 4) / kThreads;  // 1
+  constexpr int kTileRows = tile_rows(kR), kRowsPitch = rows_pitch(kR), kOutputs = kR * 4;
+  constexpr int kRowVectors = kTileRows * (kChunk / 4) / kThreads;  // 1 or 2
   constexpr int kColVectors = kTileCols * (kChunk / 4) / kThreads;  // 2
   static_assert(kRowVectors * kThreads == kTileRows * (kChunk / 4) && kColVectors * kThreads == kTileCols * (kChunk / 4),
                 "every thread brings in the same number of vectors");
@@ -107,10 +128,10 @@ pairwise_f32_kernel(const float *__restrict__ x1, long long ld1, const float *__
   const bool vec1 = (ld1 & 3) == 0 && (reinterpret_cast<uintptr_t>(x1) & 15) == 0;
   const bool vec2 = (ld2 & 3) == 0 && (reinterpret_cast<uintptr_t>(x2) & 15) == 0;
 
-  float pending[8][kStackDepth];  // per output: partial sums waiting for their right-hand neighbour
+  float pending[kOutputs][kStackDepth];  // per output: partial sums waiting for their right-hand neighbour
   int depth = 0;
-  float acc[8][8];
-  float sum[8];
+  float acc[kOutputs][8];
+  float sum[kOutputs];
   // The chunks of all leaves in order; the next chunk's values are fetched into registers while the
   // current one is being used.
   int leaf = 0;
@@ -144,7 +165,7 @@ pairwise_f32_kernel(const float *__restrict__ x1, long long ld1, const float *__
     }
     if (c0 == begin) {
 #pragma unroll
-      for (int o = 0; o < 8; ++o)
+      for (int o = 0; o < kOutputs; ++o)
 #pragma unroll
         for (int j = 0; j < 8; ++j)
           acc[o][j] = 0.0f;  // (0 + s == s exactly: a square is never -0)
@@ -154,13 +175,10 @@ pairwise_f32_kernel(const float *__restrict__ x1, long long ld1, const float *__
     for (int g = 0; g < groups; ++g) {
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        const int hh = g * 8 + j;
-        const float2 a = *reinterpret_cast<const float2 *>(rows_s + hh * kRowsPitch + ty * 2);
-        const float4 b = *reinterpret_cast<const float4 *>(cols_s + hh * kColsPitch + tx * 4);
-        const float av[2] = {a.x, a.y};
-        const float bv[4] = {b.x, b.y, b.z, b.w};
+        float av[kR], bv[4];
+        load_operands<kR>(rows_s, cols_s, g * 8 + j, ty, tx, av, bv);
 #pragma unroll
-        for (int r = 0; r < 2; ++r)
+        for (int r = 0; r < kR; ++r)
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
             const float d = __fsub_rn(av[r], bv[c]);
@@ -172,16 +190,14 @@ pairwise_f32_kernel(const float *__restrict__ x1, long long ld1, const float *__
       // The leaf is complete: combine the accumulators, then the tail of fewer than eight values
       // (it lies in this chunk) in order.
 #pragma unroll
-      for (int o = 0; o < 8; ++o)
+      for (int o = 0; o < kOutputs; ++o)
         sum[o] = __fadd_rn(__fadd_rn(__fadd_rn(acc[o][0], acc[o][1]), __fadd_rn(acc[o][2], acc[o][3])),
                            __fadd_rn(__fadd_rn(acc[o][4], acc[o][5]), __fadd_rn(acc[o][6], acc[o][7])));
       for (int hh = begin + full - c0; hh < end - c0; ++hh) {
-        const float2 a = *reinterpret_cast<const float2 *>(rows_s + hh * kRowsPitch + ty * 2);
-        const float4 b = *reinterpret_cast<const float4 *>(cols_s + hh * kColsPitch + tx * 4);
-        const float av[2] = {a.x, a.y};
-        const float bv[4] = {b.x, b.y, b.z, b.w};
+        float av[kR], bv[4];
+        load_operands<kR>(rows_s, cols_s, hh, ty, tx, av, bv);
 #pragma unroll
-        for (int r = 0; r < 2; ++r)
+        for (int r = 0; r < kR; ++r)
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
             const float d = __fsub_rn(av[r], bv[c]);
@@ -191,14 +207,14 @@ pairwise_f32_kernel(const float *__restrict__ x1, long long ld1, const float *__
       // Push, then add the pairs the recursion closes here (left + right).
       if (depth < kStackDepth) {
 #pragma unroll
-        for (int o = 0; o < 8; ++o)
+        for (int o = 0; o < kOutputs; ++o)
           pending[o][depth] = sum[o];
         ++depth;
       }
       for (int a = 0; a < entry.z && depth >= 2; ++a) {
         --depth;
 #pragma unroll
-        for (int o = 0; o < 8; ++o)
+        for (int o = 0; o < kOutputs; ++o)
           pending[o][depth - 1] = __fadd_rn(pending[o][depth - 1], pending[o][depth]);
       }
     }
@@ -208,8 +224,8 @@ pairwise_f32_kernel(const float *__restrict__ x1, long long ld1, const float *__
   }
 
 #pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    const int i = i0 + ty * 2 + r;
+  for (int r = 0; r < kR; ++r) {
+    const int i = i0 + ty * kR + r;
     if (i >= w1)
       continue;
     float v[4];
@@ -261,6 +277,23 @@ int pairwise_max_h() {
   return 1 << 20;
 }
 
+template <int kR>
+cudaError_t launch_pairwise_tiles(const float *x1, long long ld1, const float *x2, long long ld2, float *out,
+                                  long long ldo, int w1, int w2, int h, int take_sqrt, const int4 *leaves_dev,
+                                  int num_leaves, cudaStream_t stream) {
+  const long long tiles_i = (w1 + tile_rows(kR) - 1) / tile_rows(kR), tiles_j = (w2 + kTileCols - 1) / kTileCols;
+  if (tiles_i * tiles_j > 0x7fffffffLL)
+    return cudaErrorInvalidValue;
+  const unsigned grid = static_cast<unsigned>(tiles_i * tiles_j);
+  if (take_sqrt)
+    pairwise_f32_kernel<kR, true><<<grid, kThreads, 0, stream>>>(x1, ld1, x2, ld2, out, ldo, w1, w2, h, leaves_dev,
+                                                                 num_leaves, static_cast<int>(tiles_j));
+  else
+    pairwise_f32_kernel<kR, false><<<grid, kThreads, 0, stream>>>(x1, ld1, x2, ld2, out, ldo, w1, w2, h, leaves_dev,
+                                                                  num_leaves, static_cast<int>(tiles_j));
+  return cudaGetLastError();
+}
+
 cudaError_t launch_pairwise_f32(const float *x1, long long ld1, const float *x2, long long ld2, float *out,
                                 long long ldo, int w1, int w2, int h, int take_sqrt, const int4 *leaves_dev,
                                 int num_leaves, cudaStream_t stream) {
@@ -268,17 +301,12 @@ cudaError_t launch_pairwise_f32(const float *x1, long long ld1, const float *x2,
     return cudaSuccess;
   if (h < 0 || h > pairwise_max_h() || (h > 0 && (leaves_dev == nullptr || num_leaves < 1)))
     return cudaErrorInvalidValue;
-  const long long tiles_i = (w1 + kTileRows - 1) / kTileRows, tiles_j = (w2 + kTileCols - 1) / kTileCols;
-  if (tiles_i * tiles_j > 0x7fffffffLL)
-    return cudaErrorInvalidValue;
-  const unsigned grid = static_cast<unsigned>(tiles_i * tiles_j);
-  if (take_sqrt)
-    pairwise_f32_kernel<true><<<grid, kThreads, 0, stream>>>(x1, ld1, x2, ld2, out, ldo, w1, w2, h, leaves_dev,
-                                                             num_leaves, static_cast<int>(tiles_j));
-  else
-    pairwise_f32_kernel<false><<<grid, kThreads, 0, stream>>>(x1, ld1, x2, ld2, out, ldo, w1, w2, h, leaves_dev,
-                                                              num_leaves, static_cast<int>(tiles_j));
-  return cudaGetLastError();
+  int rows_per_thread = 2;
+  if (const char *forced = std::getenv("HC_CUDA_PAIRWISE_ROWS"))  // tuning aid: 2 or 4 rows per thread
+    rows_per_thread = std::atoi(forced);
+  if (rows_per_thread == 4)
+    return launch_pairwise_tiles<4>(x1, ld1, x2, ld2, out, ldo, w1, w2, h, take_sqrt, leaves_dev, num_leaves, stream);
+  return launch_pairwise_tiles<2>(x1, ld1, x2, ld2, out, ldo, w1, w2, h, take_sqrt, leaves_dev, num_leaves, stream);
 }
 
 } // namespace sm100
