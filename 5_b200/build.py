@@ -59,6 +59,12 @@ NVCC_FLAGS = [
 ]
 
 
+# The pairwise kernel reproduces NumPy's float32 results bit for bit: no multiply may be contracted
+# with an addition anywhere in that file. (The flag alone does not stop ptxas from fusing a packed
+# float32x2 multiply with the add it feeds; the kernel writes its squares in a form that cannot be.)
+EXTRA_FLAGS = {"pairwise_distance_sm100a.cu": ["-fmad=false"]}
+
+
 def find_nvcc() -> str:
     nvcc = os.environ.get("NVCC") or shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     if not Path(nvcc).exists():
@@ -88,7 +94,7 @@ def build(*, force: bool = False, verbose: bool = False, checked: bool = False) 
         obj = build_dir / (src.stem + ".o")
         objects.append(obj)
         if force or _stale(obj, [src, *HEADERS, Path(__file__)]):
-            cmd = [nvcc, *flags, "-x", "cu", "-c", str(src), "-o", str(obj)]
+            cmd = [nvcc, *flags, *EXTRA_FLAGS.get(src.name, []), "-x", "cu", "-c", str(src), "-o", str(obj)]
             if verbose:
                 cmd.insert(1, "-Xptxas=-v")
                 print(" ".join(cmd), flush=True)

@@ -11,7 +11,8 @@
 //
 // with work_shape=(W1, W2): every (i, j) below (W1, W2) is computed once and nothing else is
 // written. The group shape is not observable, so the launch is re-tiled: a CTA of 256 threads
-// computes 32 x 64 outputs, a thread 2 x 4 of them, from rows staged (transposed) in shared memory.
+// computes 32 x 64 outputs, a thread 2 x 4 of them (as four pairs of neighbouring columns), from rows
+// staged (transposed) in shared memory.
 //
 // The result is bit-identical to the reference simulator's, which computes in float32 with NumPy:
 // one rounding per operation -- the difference, its square (np.power with exponent 2 multiplies), the
@@ -24,27 +25,30 @@
 // recursively and added. The host lists the leaves of that recursion (start, length, and how many
 // pending partial sums to add once the leaf is done); every thread walks the list with the eight
 // accumulators per output in registers and the pending partial sums on a small stack.
-// Arithmetic: 3 float32 instructions per (i, j, h), none of them fusable; the kernel is bound by the
-// float32 issue rate, not by memory (the rows of a tile are re-read from L2 by the tiles beside it).
+// Arithmetic: 3 float32 operations per (i, j, h), none of them fusable; the kernel is bound by the
+// float32 rate, not by memory (the rows of a tile are re-read from L2 by the tiles beside it). The
+// operations are issued two outputs at a time as packed float32x2 instructions (add.rn.f32x2 and,
+// for the square, fma.rn.f32x2 with a zero addend: two independent, individually rounded IEEE
+// operations per lane), which halves the issue
+// slots the arithmetic takes. x1 is staged negated and duplicated, so that d = x2 + (-x1) needs no
+// operand shuffling: (b - a)^2 and (a - b)^2 are the same float32 number.
 #include "gemm_launch.h"
 
 #include <cstdint>
-#include <cstdlib>
 
 namespace hc {
 namespace sm100 {
 
 namespace {
 
+constexpr int kTileRows = 32;     // of x1 per CTA (outputs i)
 constexpr int kTileCols = 64;     // rows of x2 per CTA (outputs j)
-constexpr int kThreads = 256;     // 16 x 16: a thread owns kRowsPerThread rows x 4 columns
+constexpr int kThreads = 256;     // 16 x 16: a thread owns 2 rows x 4 columns
 constexpr int kChunk = 32;        // h staged per step
-constexpr int kColsPitch = kTileCols + 4;  // floats; keeps the 16-byte reads aligned
-// Rows of x1 per CTA (outputs i) and the pitch of their staging, for 2 or 4 rows per thread: the
-// pitch keeps the 8-byte (16-byte) reads of a thread's rows aligned.
-__host__ __device__ constexpr int tile_rows(int rows_per_thread) { return 16 * rows_per_thread; }
-__host__ __device__ constexpr int rows_pitch(int rows_per_thread) { return tile_rows(rows_per_thread) + rows_per_thread; }
+constexpr int kRowsPitch = 2 * kTileRows + 4;  // floats: every value of x1 twice; 16-byte reads stay aligned
+constexpr int kColsPitch = kTileCols + 4;      // floats; 16-byte reads stay aligned
 constexpr int kStackDepth = 24;   // pending partial sums: the recursion halves n down to 128
+constexpr int kPairs = 4;         // a thread's outputs as pairs of neighbouring columns: pair 2 r + p
 
 // The part of a chunk one thread brings in: `kVectors` groups of four consecutive h of one row each
 // (vector v of the chunk is row v / 8, h 4 (v % 8) .. + 3). Rows at or past `limit` and h at or past
@@ -79,44 +83,75 @@ __device__ __forceinline__ Fetched<kVectors> fetch_rows(const float *__restrict_
   return f;
 }
 
-// ... and puts into shared memory transposed: dst[h][row].
-template <int kVectors, int kPitch>
+// ... and puts into shared memory transposed, dst[h][row]; the rows of x1 negated and twice each,
+// dst[h][2 row], dst[h][2 row + 1] = -x1[row][h] (the two lanes of a packed operation).
+template <int kVectors, int kPitch, bool kNegatedTwice>
 __device__ __forceinline__ void stage_rows(float *dst, const Fetched<kVectors> &f) {
 #pragma unroll
   for (int i = 0; i < kVectors; ++i) {
     const int v = static_cast<int>(threadIdx.x) + i * kThreads;
     const int row = v / (kChunk / 4), h = (v % (kChunk / 4)) * 4;
-    dst[(h + 0) * kPitch + row] = f.value[i].x;
-    dst[(h + 1) * kPitch + row] = f.value[i].y;
-    dst[(h + 2) * kPitch + row] = f.value[i].z;
-    dst[(h + 3) * kPitch + row] = f.value[i].w;
+    const float value[4] = {f.value[i].x, f.value[i].y, f.value[i].z, f.value[i].w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      if constexpr (kNegatedTwice)
+        *reinterpret_cast<float2 *>(dst + (h + q) * kPitch + 2 * row) = make_float2(-value[q], -value[q]);
+      else
+        dst[(h + q) * kPitch + row] = value[q];
+    }
   }
 }
 
-// The values of a thread's rows (kR of them, consecutive) and columns (4) at one h.
-template <int kR>
-__device__ __forceinline__ void load_operands(const float *rows_s, const float *cols_s, int hh, int ty, int tx,
-                                              float (&av)[kR], float (&bv)[4]) {
-  if constexpr (kR == 2) {
-    const float2 a = *reinterpret_cast<const float2 *>(rows_s + hh * rows_pitch(2) + ty * 2);
-    av[0] = a.x, av[1] = a.y;
-  } else {
-    const float4 a = *reinterpret_cast<const float4 *>(rows_s + hh * rows_pitch(4) + ty * 4);
-    av[0] = a.x, av[1] = a.y, av[2] = a.z, av[3] = a.w;
-  }
+// Packed float32x2 addition and multiplication, each lane rounded to nearest on its own. Written as
+// PTX with the rounding mode spelled out: an operation with an explicit rounding modifier is never
+// contracted with a neighbour into a fused multiply-add (the add2(acc, mul2(d, d)) of the
+// CUDA headers was, and came out one unit in the last place away from NumPy on a third of the sums).
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+  unsigned long long d;
+  asm("add.rn.f32x2 %0, %1, %2;"
+      : "=l"(d)
+      : "l"(*reinterpret_cast<const unsigned long long *>(&a)), "l"(*reinterpret_cast<const unsigned long long *>(&b)));
+  return *reinterpret_cast<float2 *>(&d);
+}
+
+// d * d for a packed pair, written as the fused form d * d + (+0): exactly the rounded product (a
+// square is never -0, and x + (+0) == x for every other x). ptxas contracts a packed multiply that
+// feeds a packed add into one fused multiply-add -- with the rounding modes spelled out, with
+// -fmad=false, and when the add is itself written as square * 1 + acc (measured each time: a third
+// of the sums one unit in the last place away from NumPy, and equal to the fused model) -- but a
+// fused multiply-add with a +0 addend is not a multiply (they differ when the product is -0), so it
+// has to stay, and nothing contracts a fused multiply-add with the add that follows.
+__device__ __forceinline__ float2 square2(float2 d) {
+  const float2 zero = make_float2(0.0f, 0.0f);
+  unsigned long long r;
+  asm("fma.rn.f32x2 %0, %1, %1, %2;"
+      : "=l"(r)
+      : "l"(*reinterpret_cast<const unsigned long long *>(&d)), "l"(*reinterpret_cast<const unsigned long long *>(&zero)));
+  return *reinterpret_cast<float2 *>(&r);
+}
+
+// One h of a thread's 2 x 4 outputs: pair 2 r + p holds columns 2 p, 2 p + 1 of row r.
+__device__ __forceinline__ void squared_differences(const float *rows_s, const float *cols_s, int hh, int ty, int tx,
+                                                    float2 (&square)[kPairs]) {
+  const float4 a = *reinterpret_cast<const float4 *>(rows_s + hh * kRowsPitch + ty * 4);  // -a0, -a0, -a1, -a1
   const float4 b = *reinterpret_cast<const float4 *>(cols_s + hh * kColsPitch + tx * 4);
-  bv[0] = b.x, bv[1] = b.y, bv[2] = b.z, bv[3] = b.w;
+  const float2 minus_a[2] = {make_float2(a.x, a.y), make_float2(a.z, a.w)};
+  const float2 b_pair[2] = {make_float2(b.x, b.y), make_float2(b.z, b.w)};
+#pragma unroll
+  for (int r = 0; r < 2; ++r)
+#pragma unroll
+    for (int p = 0; p < 2; ++p) {
+      const float2 d = add2(b_pair[p], minus_a[r]);  // b - a, each lane rounded on its own
+      square[2 * r + p] = square2(d);
+    }
 }
 
-// kR: rows per thread (2: 32 x 64 outputs per CTA, two CTAs per SM; 4: 64 x 64, one CTA per SM, half
-// the shared-memory loads per arithmetic instruction).
-template <int kR, bool kSqrt>
-__global__ void __launch_bounds__(kThreads, kR == 2 ? 2 : 1)
+template <bool kSqrt>
+__global__ void __launch_bounds__(kThreads, 2)
 pairwise_f32_kernel(const float *__restrict__ x1, long long ld1, const float *__restrict__ x2, long long ld2,
                     float *__restrict__ out, long long ldo, int w1, int w2, int h, const int4 *__restrict__ leaves,
                     int num_leaves, int tiles_j) {
-  constexpr int kTileRows = tile_rows(kR), kRowsPitch = rows_pitch(kR), kOutputs = kR * 4;
-  constexpr int kRowVectors = kTileRows * (kChunk / 4) / kThreads;  // 1 or 2
+  constexpr int kRowVectors = kTileRows * (kChunk / 4) / kThreads;  // 1
   constexpr int kColVectors = kTileCols * (kChunk / 4) / kThreads;  // 2
   static_assert(kRowVectors * kThreads == kTileRows * (kChunk / 4) && kColVectors * kThreads == kTileCols * (kChunk / 4),
                 "every thread brings in the same number of vectors");
@@ -128,10 +163,10 @@ pairwise_f32_kernel(const float *__restrict__ x1, long long ld1, const float *__
   const bool vec1 = (ld1 & 3) == 0 && (reinterpret_cast<uintptr_t>(x1) & 15) == 0;
   const bool vec2 = (ld2 & 3) == 0 && (reinterpret_cast<uintptr_t>(x2) & 15) == 0;
 
-  float pending[kOutputs][kStackDepth];  // per output: partial sums waiting for their right-hand neighbour
+  float2 pending[kPairs][kStackDepth];  // per pair of outputs: partial sums waiting for their right-hand neighbour
   int depth = 0;
-  float acc[kOutputs][8];
-  float sum[kOutputs];
+  float2 acc[kPairs][8];
+  float2 sum[kPairs];
   // The chunks of all leaves in order; the next chunk's values are fetched into registers while the
   // current one is being used.
   int leaf = 0;
@@ -147,8 +182,8 @@ pairwise_f32_kernel(const float *__restrict__ x1, long long ld1, const float *__
   while (leaf < num_leaves) {
     const int begin = entry.x, full = entry.y & ~7, end = entry.x + entry.y;
     __syncthreads();  // the previous chunk has been read
-    stage_rows<kRowVectors, kRowsPitch>(rows_s, next_rows);
-    stage_rows<kColVectors, kColsPitch>(cols_s, next_cols);
+    stage_rows<kRowVectors, kRowsPitch, true>(rows_s, next_rows);
+    stage_rows<kColVectors, kColsPitch, false>(cols_s, next_cols);
     __syncthreads();
     int following_leaf = leaf, following_c0 = c0 + kChunk;
     int4 following = entry;
@@ -165,57 +200,49 @@ pairwise_f32_kernel(const float *__restrict__ x1, long long ld1, const float *__
     }
     if (c0 == begin) {
 #pragma unroll
-      for (int o = 0; o < kOutputs; ++o)
+      for (int o = 0; o < kPairs; ++o)
 #pragma unroll
         for (int j = 0; j < 8; ++j)
-          acc[o][j] = 0.0f;  // (0 + s == s exactly: a square is never -0)
+          acc[o][j] = make_float2(0.0f, 0.0f);  // (0 + s == s exactly: a square is never -0)
     }
     const int groups = min(kChunk, begin + full - c0) / 8;  // whole groups of eight in this chunk (may be <= 0)
 #pragma unroll 1
     for (int g = 0; g < groups; ++g) {
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        float av[kR], bv[4];
-        load_operands<kR>(rows_s, cols_s, g * 8 + j, ty, tx, av, bv);
+        float2 square[kPairs];
+        squared_differences(rows_s, cols_s, g * 8 + j, ty, tx, square);
 #pragma unroll
-        for (int r = 0; r < kR; ++r)
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            const float d = __fsub_rn(av[r], bv[c]);
-            acc[r * 4 + c][j] = __fadd_rn(acc[r * 4 + c][j], __fmul_rn(d, d));
-          }
+        for (int o = 0; o < kPairs; ++o)
+          acc[o][j] = add2(acc[o][j], square[o]);
       }
     }
     if (c0 + kChunk >= end) {
       // The leaf is complete: combine the accumulators, then the tail of fewer than eight values
       // (it lies in this chunk) in order.
 #pragma unroll
-      for (int o = 0; o < kOutputs; ++o)
-        sum[o] = __fadd_rn(__fadd_rn(__fadd_rn(acc[o][0], acc[o][1]), __fadd_rn(acc[o][2], acc[o][3])),
-                           __fadd_rn(__fadd_rn(acc[o][4], acc[o][5]), __fadd_rn(acc[o][6], acc[o][7])));
+      for (int o = 0; o < kPairs; ++o)
+        sum[o] = add2(add2(add2(acc[o][0], acc[o][1]), add2(acc[o][2], acc[o][3])),
+                            add2(add2(acc[o][4], acc[o][5]), add2(acc[o][6], acc[o][7])));
       for (int hh = begin + full - c0; hh < end - c0; ++hh) {
-        float av[kR], bv[4];
-        load_operands<kR>(rows_s, cols_s, hh, ty, tx, av, bv);
+        float2 square[kPairs];
+        squared_differences(rows_s, cols_s, hh, ty, tx, square);
 #pragma unroll
-        for (int r = 0; r < kR; ++r)
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            const float d = __fsub_rn(av[r], bv[c]);
-            sum[r * 4 + c] = __fadd_rn(sum[r * 4 + c], __fmul_rn(d, d));
-          }
+        for (int o = 0; o < kPairs; ++o)
+          sum[o] = add2(sum[o], square[o]);
       }
       // Push, then add the pairs the recursion closes here (left + right).
       if (depth < kStackDepth) {
 #pragma unroll
-        for (int o = 0; o < kOutputs; ++o)
+        for (int o = 0; o < kPairs; ++o)
           pending[o][depth] = sum[o];
         ++depth;
       }
       for (int a = 0; a < entry.z && depth >= 2; ++a) {
         --depth;
 #pragma unroll
-        for (int o = 0; o < kOutputs; ++o)
-          pending[o][depth - 1] = __fadd_rn(pending[o][depth - 1], pending[o][depth]);
+        for (int o = 0; o < kPairs; ++o)
+          pending[o][depth - 1] = add2(pending[o][depth - 1], pending[o][depth]);
       }
     }
     leaf = following_leaf;
@@ -224,15 +251,17 @@ pairwise_f32_kernel(const float *__restrict__ x1, long long ld1, const float *__
   }
 
 #pragma unroll
-  for (int r = 0; r < kR; ++r) {
-    const int i = i0 + ty * kR + r;
+  for (int r = 0; r < 2; ++r) {
+    const int i = i0 + ty * 2 + r;
     if (i >= w1)
       continue;
-    float v[4];
+    const float2 zero = make_float2(0.0f, 0.0f);  // an empty sum is 0
+    const float2 left = num_leaves > 0 ? pending[2 * r][0] : zero, right = num_leaves > 0 ? pending[2 * r + 1][0] : zero;
+    float v[4] = {left.x, left.y, right.x, right.y};
+    if (kSqrt) {
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      const float total = num_leaves > 0 ? pending[r * 4 + c][0] : 0.0f;  // an empty sum is 0
-      v[c] = kSqrt ? __fsqrt_rn(total) : total;
+      for (int c = 0; c < 4; ++c)
+        v[c] = __fsqrt_rn(v[c]);
     }
     const int j = j0 + tx * 4;
     float *dst = out + static_cast<long long>(i) * ldo + j;
@@ -277,23 +306,6 @@ int pairwise_max_h() {
   return 1 << 20;
 }
 
-template <int kR>
-cudaError_t launch_pairwise_tiles(const float *x1, long long ld1, const float *x2, long long ld2, float *out,
-                                  long long ldo, int w1, int w2, int h, int take_sqrt, const int4 *leaves_dev,
-                                  int num_leaves, cudaStream_t stream) {
-  const long long tiles_i = (w1 + tile_rows(kR) - 1) / tile_rows(kR), tiles_j = (w2 + kTileCols - 1) / kTileCols;
-  if (tiles_i * tiles_j > 0x7fffffffLL)
-    return cudaErrorInvalidValue;
-  const unsigned grid = static_cast<unsigned>(tiles_i * tiles_j);
-  if (take_sqrt)
-    pairwise_f32_kernel<kR, true><<<grid, kThreads, 0, stream>>>(x1, ld1, x2, ld2, out, ldo, w1, w2, h, leaves_dev,
-                                                                 num_leaves, static_cast<int>(tiles_j));
-  else
-    pairwise_f32_kernel<kR, false><<<grid, kThreads, 0, stream>>>(x1, ld1, x2, ld2, out, ldo, w1, w2, h, leaves_dev,
-                                                                  num_leaves, static_cast<int>(tiles_j));
-  return cudaGetLastError();
-}
-
 cudaError_t launch_pairwise_f32(const float *x1, long long ld1, const float *x2, long long ld2, float *out,
                                 long long ldo, int w1, int w2, int h, int take_sqrt, const int4 *leaves_dev,
                                 int num_leaves, cudaStream_t stream) {
@@ -301,12 +313,17 @@ cudaError_t launch_pairwise_f32(const float *x1, long long ld1, const float *x2,
     return cudaSuccess;
   if (h < 0 || h > pairwise_max_h() || (h > 0 && (leaves_dev == nullptr || num_leaves < 1)))
     return cudaErrorInvalidValue;
-  int rows_per_thread = 2;
-  if (const char *forced = std::getenv("HC_CUDA_PAIRWISE_ROWS"))  // tuning aid: 2 or 4 rows per thread
-    rows_per_thread = std::atoi(forced);
-  if (rows_per_thread == 4)
-    return launch_pairwise_tiles<4>(x1, ld1, x2, ld2, out, ldo, w1, w2, h, take_sqrt, leaves_dev, num_leaves, stream);
-  return launch_pairwise_tiles<2>(x1, ld1, x2, ld2, out, ldo, w1, w2, h, take_sqrt, leaves_dev, num_leaves, stream);
+  const long long tiles_i = (w1 + kTileRows - 1) / kTileRows, tiles_j = (w2 + kTileCols - 1) / kTileCols;
+  if (tiles_i * tiles_j > 0x7fffffffLL)
+    return cudaErrorInvalidValue;
+  const unsigned grid = static_cast<unsigned>(tiles_i * tiles_j);
+  if (take_sqrt)
+    pairwise_f32_kernel<true><<<grid, kThreads, 0, stream>>>(x1, ld1, x2, ld2, out, ldo, w1, w2, h, leaves_dev,
+                                                             num_leaves, static_cast<int>(tiles_j));
+  else
+    pairwise_f32_kernel<false><<<grid, kThreads, 0, stream>>>(x1, ld1, x2, ld2, out, ldo, w1, w2, h, leaves_dev,
+                                                              num_leaves, static_cast<int>(tiles_j));
+  return cudaGetLastError();
 }
 
 } // namespace sm100
