@@ -57,6 +57,7 @@ NCU_DRAM_TRAFFIC = {
     "gemm_8192:float8_e4m3fn": (0.618e9, "ncu capture, profiles/gemm_dense_wide_kernel__gemm_8192_float8.md (B stored [N, K])"),
     "skinny": (272.4e6, "ncu capture, profiles/gemm_skinny_kernel__skinny_8x16384x8192.md"),
     "ragged": (21.1e6, "ncu capture, profiles/ragged_4095x3073x1031__launches.md (GEMM kernel only)"),
+    "long_k": (33.6e6, "ncu capture, profiles/gemm_dense_cluster_kernel__512x512x16384.md"),
 }
 
 
