@@ -30,6 +30,7 @@ SOURCES = [
     LIB_DIR / "Kernels" / "gemm_dense_wide_sm100a.cu",
     LIB_DIR / "Kernels" / "gemm_dense_cluster_sm100a.cu",
     LIB_DIR / "Kernels" / "gemm_skinny_sm100a.cu",
+    LIB_DIR / "Kernels" / "gemm_tiny_sm100a.cu",
     LIB_DIR / "Kernels" / "repack_sm100a.cu",
     LIB_DIR / "Kernels" / "repack_bytes_sm100a.cu",
     LIB_DIR / "Kernels" / "epilogue_only_sm100a.cu",

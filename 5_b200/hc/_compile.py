@@ -84,7 +84,8 @@ class CompiledKernel:
         plan = self.plan
         assert plan is not None
         a, b, c = (launch.arguments[p] for p in (plan.a_param, plan.b_param, plan.c_param))
-        variant = {"auto": cuda.VARIANT_AUTO, "dense": cuda.VARIANT_DENSE, "skinny": cuda.VARIANT_SKINNY}[
+        variant = {"auto": cuda.VARIANT_AUTO, "dense": cuda.VARIANT_DENSE, "skinny": cuda.VARIANT_SKINNY,
+                   "tiny": cuda.VARIANT_TINY}[
             (plan.lowering or {}).get("variant", "auto")]
         bias = launch.arguments[plan.bias_param] if plan.bias_param is not None else None
         buffers = (a, b, c) if bias is None else (a, b, c, bias)

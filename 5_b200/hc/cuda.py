@@ -37,7 +37,8 @@ __all__ = [
 
 F16, BF16, F8E4M3, F8E5M2 = 0, 1, 2, 3  # HcCudaDType
 VARIANT_AUTO, VARIANT_DENSE, VARIANT_SKINNY, VARIANT_NOOP, VARIANT_ZERO_FILL, VARIANT_ELEMENTWISE = 0, 1, 2, 3, 4, 5
-VARIANT_NAMES = {0: "auto", 1: "dense", 2: "skinny", 3: "noop", 4: "zero_fill", 5: "elementwise"}
+VARIANT_TINY = 6  # float32 pipes, bit-identical to the reference simulator; AUTO picks it for m, n <= 64, k <= 128
+VARIANT_NAMES = {0: "auto", 1: "dense", 2: "skinny", 3: "noop", 4: "zero_fill", 5: "elementwise", 6: "tiny"}
 API_VERSION = 6
 # Element-wise operations fused into the store of C: ("scale", x), ("add", x), ("max", x),
 # ("min", x) and ("bias",) -- the last adds bias[column].

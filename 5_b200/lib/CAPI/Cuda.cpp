@@ -193,8 +193,8 @@ int plan_gemm(const HcCudaContext *ctx, const HcCudaGemmArgs *args, int sm_count
   const bool f8 = hc::sm100::dtype_is_8bit(args->dtype);
   const int64_t es = f8 ? 1 : 2;  // bytes per element of A and B
   if (args->variant != HC_CUDA_GEMM_AUTO && args->variant != HC_CUDA_GEMM_DENSE &&
-      args->variant != HC_CUDA_GEMM_SKINNY)
-    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "variant must be AUTO, DENSE or SKINNY (got %d)",
+      args->variant != HC_CUDA_GEMM_SKINNY && args->variant != HC_CUDA_GEMM_TINY)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "variant must be AUTO, DENSE, SKINNY or TINY (got %d)",
                 args->variant);
   if (args->accumulate != 0 && args->accumulate != 1)
     return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "accumulate must be 0 or 1 (got %d)", args->accumulate);
@@ -272,6 +272,24 @@ int plan_gemm(const HcCudaContext *ctx, const HcCudaGemmArgs *args, int sm_count
   if (variant == HC_CUDA_GEMM_SKINNY && m > skinny_max_m)
     return fail(ctx, HC_CUDA_ERR_UNSUPPORTED, "the skinny variant needs m <= %d (got %lld)",
                 skinny_max_m, (long long)m);
+  if (variant == HC_CUDA_GEMM_TINY && (f8 || (ctx != nullptr && ctx->planning_push)))
+    return fail(ctx, HC_CUDA_ERR_UNSUPPORTED, "the tiny variant takes 16-bit operands and no push targets");
+  if (variant == HC_CUDA_GEMM_AUTO && !(ctx != nullptr && (ctx->planning_push || ctx->planning_host_panels)) &&
+      hc::sm100::tiny_takes(m, n, k, args->dtype, sm_count))
+    variant = HC_CUDA_GEMM_TINY;
+  if (variant == HC_CUDA_GEMM_TINY) {
+    const int tile = hc::sm100::tiny_tile();
+    plan->variant = variant;
+    plan->tiles_m = static_cast<int32_t>((m + tile - 1) / tile);
+    plan->tiles_n = static_cast<int32_t>((n + tile - 1) / tile);
+    if (plan->tiles_m > 65535)
+      return fail(ctx, HC_CUDA_ERR_UNSUPPORTED, "the tiny variant takes at most 65535 tile rows");
+    plan->splits = 1;
+    plan->grid = plan->tiles_m * plan->tiles_n;
+    plan->kernel_launches = 1;
+    plan->scratch_bytes = 0;
+    return HC_CUDA_OK;
+  }
   if (variant == HC_CUDA_GEMM_AUTO) {
     variant = m <= skinny_max_m ? HC_CUDA_GEMM_SKINNY : HC_CUDA_GEMM_DENSE;
     // 8 < m <= 64 with so few column blocks that the skinny kernel would split k: the dense tiles
@@ -525,6 +543,16 @@ int enqueue_gemm(HcCudaContext *ctx, const HcCudaGemmArgs *args, const HcCudaGem
   if (plan.variant == HC_CUDA_GEMM_ZERO_FILL) {
     HC_TRY_CUDA(ctx, cudaMemset2DAsync(args->c, static_cast<size_t>(args->ldc) * c_elem, 0,
                                        static_cast<size_t>(n) * c_elem, static_cast<size_t>(m), ctx->stream));
+    return HC_CUDA_OK;
+  }
+  if (plan.variant == HC_CUDA_GEMM_TINY) {
+    if (ep.push_count != 0)
+      return fail(ctx, HC_CUDA_ERR_UNSUPPORTED, "the tiny variant has no push targets");
+    HC_TRY_CUDA(ctx, hc::sm100::launch_gemm_tiny(args->a, args->lda, args->b, args->ldb, args->c, args->ldc, m, n, k,
+                                                 args->dtype,
+                                                 args->b_layout == HC_CUDA_B_NK ? hc::sm100::kBLayoutNK
+                                                                                : hc::sm100::kBLayoutKN,
+                                                 ep, ctx->stream));
     return HC_CUDA_OK;
   }
   if (int rc = ensure_scratch(ctx, static_cast<size_t>(plan.scratch_bytes)))

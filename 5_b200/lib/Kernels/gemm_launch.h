@@ -214,6 +214,15 @@ cudaError_t launch_pairwise_f32(const float *x1, long long ld1, const float *x2,
 int pairwise_schedule(int h, int4 *leaves, int capacity);
 int pairwise_max_h();
 
+// Small products on the float32 pipes, one small CTA per 16x16 tile, bit-identical to the reference
+// simulator (products and sums rounded one by one, k ascending): any pitch and alignment, 16-bit
+// operands, every member of the family except push targets. `tiny_takes`: whether the AUTO variant
+// hands a product to it (m, n <= 64 and a k-loop staged in one go).
+cudaError_t launch_gemm_tiny(const void *a, long long lda, const void *b, long long ldb, void *c, long long ldc, int m,
+                             int n, int k, int dtype, int b_layout, const Epilogue &ep, cudaStream_t stream);
+bool tiny_takes(long long m, long long n, long long k, int dtype, int sm_count);
+int tiny_tile();
+
 // k == 0 with fused element-wise work: C = ops(accumulate ? C : 0), no product to add.
 cudaError_t launch_epilogue_only(void *c, int m, int n, long long ldc, const Epilogue &ep,
                                  cudaStream_t stream);

@@ -70,11 +70,17 @@ typedef enum HcCudaDType {
 } HcCudaDType;
 
 typedef enum HcCudaGemmVariant {
-  HC_CUDA_GEMM_AUTO = 0,   /* skinny when m <= 64, dense otherwise */
+  HC_CUDA_GEMM_AUTO = 0,   /* tiny for m, n <= 64 with a short k, else skinny when m <= 64 (dense tiles
+                              shared among clusters when that kernel would split k), dense otherwise */
   HC_CUDA_GEMM_DENSE = 1,  /* TMA ring + tcgen05.mma, persistent; 256x256 tiles on CTA pairs
                               (cta_group::2) or 128x256 on single CTAs, chosen per shape */
   HC_CUDA_GEMM_SKINNY = 2, /* m <= 64: B streamed once; split over k (ordered reduction) only
                               when there are too few column blocks to fill the GPU */
+  HC_CUDA_GEMM_TINY = 6,   /* float32 pipes, one small CTA per 16x16 tile: products and sums rounded
+                              one by one with k ascending, i.e. bit-identical to the reference
+                              simulator; any pitch and alignment (no repack), 16-bit operands, no push
+                              targets. AUTO picks it for m, n <= 64 and k <= 128 (benchmark
+                              configuration 1), where the tensor-core kernels would be all set-up */
   /* Reported by hcCudaGemmPlan only: */
   HC_CUDA_GEMM_NOOP = 3,     /* m == 0 or n == 0: nothing to write */
   HC_CUDA_GEMM_ZERO_FILL = 4,    /* k == 0: C is set to zero, no kernel */
@@ -119,7 +125,7 @@ typedef enum HcCudaEpilogueOp {
 typedef struct HcCudaGemmArgs {
   int64_t m, n, k;
   int32_t dtype;   /* HcCudaDType */
-  int32_t variant; /* HcCudaGemmVariant: AUTO, DENSE or SKINNY */
+  int32_t variant; /* HcCudaGemmVariant: AUTO, DENSE, SKINNY or TINY */
   const void *a;
   int64_t lda;
   const void *b;

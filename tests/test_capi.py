@@ -311,3 +311,22 @@ def test_checked_build_exports_the_same_symbols() -> None:
     assert lib.hcCudaApiVersion() == cuda.API_VERSION
     lib.hcCudaStatusString.restype = ctypes.c_char_p
     assert lib.hcCudaStatusString(8) == b"HC_CUDA_ERR_DEVICE_CHECK"
+
+
+def test_plan_sends_one_small_tile_with_a_short_k_to_the_tiny_variant() -> None:
+    """m, n <= 64 and k <= 128 (benchmark configuration 1 and every matmul fixture): the float32 kernel
+    that is bit-identical to the reference simulator; it needs no repack and no scratch whatever the
+    pitches, takes no float8, and can be asked for on any shape."""
+    plan = cuda.plan_gemm(64, 64, 64, "float16")
+    assert (plan.variant, plan.tiles_m, plan.tiles_n, plan.grid, plan.splits, plan.kernel_launches) == ("tiny", 4, 4, 16, 1, 1)
+    odd = cuda.plan_gemm(33, 17, 40, "bfloat16", lda=41, ldb=19, ldc=23, a=0x1002)
+    assert (odd.variant, odd.repack_a, odd.repack_b, odd.scratch_bytes) == ("tiny", False, False, 0)
+    for shape in ((65, 64, 64), (64, 65, 64), (64, 64, 129)):
+        assert cuda.plan_gemm(*shape, "float16").variant != "tiny", shape
+    assert cuda.plan_gemm(64, 64, 64, "float8_e5m2", b_transposed=True).variant == "skinny"
+    forced = cuda.plan_gemm(300, 500, 700, "float16", variant=cuda.VARIANT_TINY)
+    assert (forced.variant, forced.tiles_m, forced.tiles_n, forced.grid) == ("tiny", 19, 32, 19 * 32)
+    with pytest.raises(DeviceError, match="16-bit operands"):
+        cuda.plan_gemm(64, 64, 64, "float8_e5m2", b_transposed=True, variant=cuda.VARIANT_TINY)
+    with pytest.raises(DeviceError, match="variant must be AUTO, DENSE, SKINNY or TINY"):
+        cuda.plan_gemm(64, 64, 64, "float16", variant=7)

@@ -55,7 +55,7 @@ LADDER = textwrap.dedent("""
     os.environ["HC_CUDA_DENSE_WIDE"] = "1"
     assert product(2048, 1024, 4096).tiles_m == 4  # 512-row tiles
     del os.environ["HC_CUDA_DENSE_WIDE"]
-    for shape in [(8, 1024, 512), (8, 256, 4096), (33, 512, 2048), (64, 3000, 520), (1, 1, 1)]:
+    for shape in [(8, 1024, 512), (8, 256, 4096), (33, 512, 2048), (64, 3000, 520), (8, 16384, 256), (1, 1, 1)]:
         plan = product(*shape)
         seen.add((plan.variant, plan.cluster_size > 0, plan.splits > 1))
     assert {("dense", False, False), ("dense", True, True), ("dense", False, True), ("skinny", False, False),

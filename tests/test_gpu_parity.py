@@ -109,7 +109,7 @@ def test_skinny_ladder(shape: tuple[int, int, int], dtype: str) -> None:
     # (NumPy buffers take the skinny kernel for every m <= 64; on device buffers 8 < m <= 64 with few
     # column blocks may go to the dense tiles shared among clusters instead.)
     assert cuda.plan_gemm(m, n, k, dtype, variant=cuda.VARIANT_SKINNY).variant == "skinny"
-    assert cuda.plan_gemm(m, n, k, dtype).variant in ("skinny", "dense")
+    assert cuda.plan_gemm(m, n, k, dtype).variant in ("skinny", "dense", "tiny")
     assert_close_to_oracle(gpu_wmma_matmul(a, b), a, b)
 
 
