@@ -6,6 +6,8 @@ Kernels of the masked load / element-wise / store class:
 
   add_two       the reference simulator's own masked vector test
                 (tests/test_simulator.py:210-224): y = x + 2, four elements per workgroup;
+  add_two_per_workitem  the same written one element per work-item inside `@group.workitems`
+                (tests/test_simulator.py:901-917);
   scaled_clamp  out = maximum(y - (0.5 * x - 1), 0.25) * -3 + y on float32 buffers, 64 elements
                 per workgroup: a chain of element-wise statements with a second input;
   affine_relu_2d  out = maximum(0, 2 * x + shift) on matrices, one 8 x 32 tile per workgroup.
@@ -51,6 +53,17 @@ def scaled_clamp(group, x: Buffer[W, np.float32], y: Buffer[W, np.float32], out:
     t = HALF * xv - 1
     t = np.maximum(yv - t, FLOOR)
     group.store(out[gid:], -t * 3 + yv)
+
+
+@kernel(work_shape=(W,), group_shape=(4,))
+def add_two_per_workitem(group, src: Buffer[W], dst: Buffer[W]) -> None:
+    @group.workitems
+    def inner(wi) -> None:
+        gid = wi.global_id()[0]
+        vec = group.vload(src[gid:], shape=(1,))
+        group.store(dst[gid:], vec + 2)
+
+    inner()
 
 
 M, N = sym.M, sym.N

@@ -242,6 +242,33 @@ def recognise_elementwise_map(kernel_fn: Any) -> tuple[MapContract | None, list[
             isinstance(body[-1].value, ast.Constant) and body[-1].value.value is None)):
         body = body[:-1]
 
+    # The same kernel written one element per work-item (tests/test_simulator.py:901-917):
+    #
+    #     @group.workitems
+    #     def inner(wi) -> None:
+    #         gid = wi.global_id()[0]
+    #         vec = group.vload(src[gid:], shape=(1,))
+    #         group.store(dst[gid:], vec + 2)
+    #     inner()
+    #
+    # Every work-item of every group runs the body once with its own global id (ids past the end of
+    # the buffers load nothing and store nothing), so it is the map with windows of one element.
+    workitem: str | None = None
+    if (len(body) == 2 and isinstance(body[0], ast.FunctionDef) and isinstance(body[1], ast.Expr)
+            and isinstance(body[1].value, ast.Call) and isinstance(body[1].value.func, ast.Name)
+            and body[1].value.func.id == body[0].name and not body[1].value.args and not body[1].value.keywords):
+        inner = body[0]
+        decorators = [ast.unparse(d) for d in inner.decorator_list]
+        inner_args = inner.args
+        if (decorators == [f"{group}.workitems"] and len(inner_args.args) == 1 and not inner_args.vararg
+                and not inner_args.kwarg and not inner_args.kwonlyargs and not inner_args.posonlyargs):
+            workitem = inner_args.args[0].arg
+            body = _without_docstring(list(inner.body))
+            if body and isinstance(body[-1], ast.Return) and (body[-1].value is None or (
+                    isinstance(body[-1].value, ast.Constant) and body[-1].value.value is None)):
+                body = body[:-1]
+            group_sizes = (1,) * rank  # the window a work-item loads and stores
+
     offset_names: dict[str, int] = {}  # name -> axis of group.work_offset it holds
     exprs = _Expressions(consts)
     out_param: str | None = None
@@ -270,7 +297,13 @@ def recognise_elementwise_map(kernel_fn: Any) -> tuple[MapContract | None, list[
         return node.value.id
 
     def work_offset_axis(value: ast.AST | None) -> int | None:
-        """`group.work_offset[axis]` -> axis."""
+        """`group.work_offset[axis]` (or, in a work-item body, `wi.global_id()[axis]`) -> axis."""
+        if workitem is not None:
+            if (isinstance(value, ast.Subscript) and isinstance(value.slice, ast.Constant)
+                    and isinstance(value.slice.value, int) and not isinstance(value.slice.value, bool)
+                    and 0 <= value.slice.value < rank and ast.unparse(value.value) == f"{workitem}.global_id()"):
+                return value.slice.value
+            return None
         if (isinstance(value, ast.Subscript) and isinstance(value.value, ast.Attribute)
                 and value.value.attr == "work_offset" and isinstance(value.value.value, ast.Name)
                 and value.value.value.id == group and isinstance(value.slice, ast.Constant)
@@ -291,8 +324,9 @@ def recognise_elementwise_map(kernel_fn: Any) -> tuple[MapContract | None, list[
             continue
         if (isinstance(stmt, ast.Assign) and len(stmt.targets) == 1 and isinstance(stmt.targets[0], ast.Tuple)
                 and len(stmt.targets[0].elts) == rank and all(isinstance(e, ast.Name) for e in stmt.targets[0].elts)
-                and isinstance(value, ast.Attribute) and value.attr == "work_offset"
-                and isinstance(value.value, ast.Name) and value.value.id == group):
+                and ((workitem is None and isinstance(value, ast.Attribute) and value.attr == "work_offset"
+                      and isinstance(value.value, ast.Name) and value.value.id == group)
+                     or (workitem is not None and value is not None and ast.unparse(value) == f"{workitem}.global_id()"))):
             for axis, elt in enumerate(stmt.targets[0].elts):
                 offset_names[elt.id] = axis
             continue

@@ -38,7 +38,8 @@ Fixtures (all produced by `hc.simulator.launch` on the example kernel):
       the masked element-wise kernels of 5_b200/examples/b200_elementwise.py: `add_two_x/_y` the
       reference's own vector test (tests/test_simulator.py:210-224), `x`, `y`, `out` the
       scaled_clamp kernel on 1003 elements with NaN and infinities, `x_2d`, `shift_2d`, `out_2d` the
-      two-dimensional affine_relu_2d kernel on a 37 x 70 matrix
+      two-dimensional affine_relu_2d kernel on a 37 x 70 matrix, `workitem_x/_y` the one-element-per-work-item
+      form (tests/test_simulator.py:901-917) on 11 elements
   simpair_f32_seed18
       the pairwise-distance kernels of 5_b200/examples/b200_pairwise.py: `test_x1/_x2/_out` the
       reference's own test (tests/test_simulator.py:142-167), `x1`, `x2`, `out` the same kernel on
@@ -229,8 +230,12 @@ def main() -> int:
     out3 = np.full((37, 70), np.float32(-7.0))
     with np.errstate(invalid="ignore"):
         ew.hc.simulator.launch(ew.affine_relu_2d, x3, s3, out3)
+    # The work-item form (tests/test_simulator.py:901-917) on a length the group size does not divide.
+    wi_x = rng.standard_normal(11).astype(np.float32)
+    wi_y = np.full((11,), np.float32(-7.0))
+    ew.hc.simulator.launch(ew.add_two_per_workitem, wi_x, wi_y)
     np.savez_compressed(HERE / "simmap_f32_seed15.npz", add_two_x=x, add_two_y=y, x=x2, y=y2, out=out2,
-                        x_2d=x3, shift_2d=s3, out_2d=out3)
+                        x_2d=x3, shift_2d=s3, out_2d=out3, workitem_x=wi_x, workitem_y=wi_y)
     print(f"simmap_f32_seed15: add_two{ x.shape } scaled_clamp{ x2.shape } affine_relu_2d{ x3.shape }", flush=True)
 
     # The pairwise kernels of 5_b200/examples/b200_pairwise.py under the reference simulator: the

@@ -38,6 +38,10 @@ def test_simulator_fixture_through_the_handles() -> None:
     x = fixture["add_two_x"].copy()
     compiled("add_two")(x, x)
     assert np.array_equal(x, fixture["add_two_y"])
+    # The one-element-per-work-item form of the same kernel.
+    y = np.full(11, np.float32(-7.0))
+    compiled("add_two_per_workitem")(fixture["workitem_x"], y)
+    assert same_bits(y, fixture["workitem_y"])
 
 
 def test_two_dimensional_kernel_matches_the_simulator(gpu_ctx) -> None:

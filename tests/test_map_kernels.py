@@ -192,6 +192,32 @@ def test_other_kernels_are_refused_with_a_reason(tmp_path, name, kwargs, message
         handle(np.zeros(4, np.float32), np.zeros(4, np.float32))
 
 
+WORKITEM = ("    @group.workitems\n    def inner(wi) -> None:\n        gid = wi.global_id()[0]\n"
+            "        vec = group.vload(x[gid:], shape=(1,))\n        group.store(y[gid:], vec + 2)\n\n    inner()")
+
+
+def test_one_element_per_workitem_is_the_same_map(tmp_path) -> None:
+    """The kernel written inside `@group.workitems` (tests/test_simulator.py:901-917 in the reference):
+    every work-item loads, transforms and stores the element at its global id."""
+    from examples.b200_elementwise import add_two_per_workitem
+
+    plan, diagnostics = recognise_elementwise_map(add_two_per_workitem)
+    assert diagnostics == [] and (plan.x_param, plan.out_param, plan.ops, plan.extent) == ("src", "dst", (("add", 2.0),), "W")
+    plan, diagnostics = recognise_elementwise_map(_kernel(WORKITEM, tmp_path=tmp_path, name="wi_good"))
+    assert plan is not None and diagnostics == []
+    for name, change, message in [
+        ("wi_local", ("wi.global_id()[0]", "wi.local_id()[0]"), "is not element-wise arithmetic"),
+        ("wi_wide", ("shape=(1,)", "shape=(4,)"), "must load the group's own window"),
+        ("wi_group_offset", ("wi.global_id()[0]", "group.work_offset[0]"), "is not element-wise arithmetic"),
+        ("wi_not_called", ("\n\n    inner()", ""), "not part of the load / element-wise / store form"),
+        ("wi_subgroups", ("@group.workitems", "@group.subgroups"), "not part of the load / element-wise / store form"),
+        ("wi_twice", ("    inner()", "    inner()\n    inner()"), "not part of the load / element-wise / store form"),
+    ]:
+        assert change[0] in WORKITEM
+        plan, diagnostics = recognise_elementwise_map(_kernel(WORKITEM.replace(*change), tmp_path=tmp_path, name=name))
+        assert plan is None and message in diagnostics[0], (name, diagnostics)
+
+
 def test_launch_binding_uses_the_simulator_messages() -> None:
     handle = compiled("add_two")
     launch = handle.prepare(np.zeros(6, np.float32), np.zeros(6, np.float32))

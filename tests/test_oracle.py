@@ -218,6 +218,8 @@ def test_elementwise_map_fixture() -> None:
     keep2 = ~np.isnan(want2)
     assert np.array_equal(np.isnan(out2), ~keep2)
     assert np.array_equal(out2[keep2].view(np.uint32), want2[keep2].view(np.uint32))
+    # The one-element-per-work-item form (11 elements, groups of 4): every element written, once.
+    assert np.array_equal(cpu_ref.map_elementwise(fixture["workitem_x"], (("add", 2.0),)), fixture["workitem_y"])
 
 
 def test_float8_kernel_fixtures() -> None:
