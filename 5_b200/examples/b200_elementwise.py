@@ -87,7 +87,12 @@ def scaled_clamp_numpy(x, y):
 
 @functools.lru_cache(maxsize=None)
 def compiled(name, device=None):
-    kernels = {"add_two": add_two, "scaled_clamp": scaled_clamp, "affine_relu_2d": affine_relu_2d}
+    kernels = {
+        "add_two": add_two,
+        "scaled_clamp": scaled_clamp,
+        "add_two_per_workitem": add_two_per_workitem,
+        "affine_relu_2d": affine_relu_2d,
+    }
     return hc.compile(kernels[name], target=NVIDIA_TARGET, device=device)
 
 

@@ -206,7 +206,7 @@ pairwise_f32_kernel(const float *__restrict__ x1, long long ld1, const float *__
           acc[o][j] = make_float2(0.0f, 0.0f);  // (0 + s == s exactly: a square is never -0)
     }
     const int groups = min(kChunk, begin + full - c0) / 8;  // whole groups of eight in this chunk (may be <= 0)
-#pragma unroll 1
+#pragma unroll 4
     for (int g = 0; g < groups; ++g) {
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
