@@ -36,6 +36,7 @@ SOURCES = [
     LIB_DIR / "Kernels" / "epilogue_only_sm100a.cu",
     LIB_DIR / "Kernels" / "map_elementwise_sm100a.cu",
     LIB_DIR / "Kernels" / "pairwise_distance_sm100a.cu",
+    LIB_DIR / "Kernels" / "row_reduce_sm100a.cu",
     LIB_DIR / "Kernels" / "gemm_skinny_static_sm100a.cu",
     LIB_DIR / "Kernels" / "selftest_sm100a.cu",
     LIB_DIR / "CAPI" / "Cuda.cpp",

@@ -26,6 +26,7 @@ import numpy as np
 from ._launch import PreparedLaunch, prepare_launch
 from ._map_kernels import MapContract
 from ._pairwise_kernels import PairwiseContract
+from ._reduce_kernels import RowSumContract
 from ._pipeline import GemmContract, ScheduleSource, lower_for_target
 from .errors import LaunchError
 
@@ -70,6 +71,8 @@ class CompiledKernel:
             self._launch_map(launch)
         elif isinstance(self.plan, PairwiseContract):
             self._launch_pairwise(launch)
+        elif isinstance(self.plan, RowSumContract):
+            self._launch_row_sum(launch)
         else:
             self._launch_gemm(launch)
         return None
@@ -196,6 +199,38 @@ class CompiledKernel:
         # (Only the w1 x w2 results are written, so a staged copy starts from out's contents when h == 0.)
         staged = out if direct else np.array(out, order="C")
         ctx.pairwise_host(_row_major(x1), _row_major(x2), staged, take_sqrt=plan.take_sqrt)
+        if not direct:
+            out[...] = staged
+
+    def _launch_row_sum(self, launch: PreparedLaunch) -> None:
+        """out[i] = [sqrt] sum_h x[i, h] [squared] for a recognised row-sum kernel."""
+        from . import cuda
+
+        plan = self.plan
+        assert isinstance(plan, RowSumContract)
+        names = [plan.in_param, plan.out_param]
+        x, out = (launch.arguments[name] for name in names)
+        for name, buf in zip(names, (x, out)):
+            if buf.dtype != np.float32:
+                raise LaunchError(f"{name} dtype expected float32, got {buf.dtype.name}: target {self.target!r} runs "
+                                  f"row sums on float32 buffers")
+        on_device = [type(buf).__name__ == "DeviceBuffer" for buf in (x, out)]
+        if any(on_device) and not all(on_device):
+            raise LaunchError("buffers must be all numpy.ndarray or all DeviceBuffer")
+        if all(on_device):
+            ctx = x.ctx
+            if out.ctx is not ctx:
+                raise LaunchError("device buffers must belong to one context")
+            ctx.row_sum(x, out, square=plan.square, take_sqrt=plan.take_sqrt)
+            ctx.synchronize()
+            return
+        if not out.flags.writeable:
+            raise LaunchError(f"{plan.out_param} must be writeable")
+        ctx = cuda.default_context(self.device)
+        direct = out.ndim == 1 and (out.shape[0] <= 1 or out.strides[0] == out.itemsize)
+        # (Only the w results are written, so a staged copy starts from out's contents when h == 0.)
+        staged = out if direct else np.array(out, order="C")
+        ctx.row_sum_host(_row_major(x), staged, square=plan.square, take_sqrt=plan.take_sqrt)
         if not direct:
             out[...] = staged
 

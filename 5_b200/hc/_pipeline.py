@@ -93,7 +93,9 @@ class GemmContract:
 @dataclass(frozen=True)
 class TargetResult:
     target: str
-    plan: Any  # GemmContract, hc._map_kernels.MapContract, hc._pairwise_kernels.PairwiseContract, or None
+    # GemmContract, hc._map_kernels.MapContract, hc._pairwise_kernels.PairwiseContract,
+    # hc._reduce_kernels.RowSumContract, or None
+    plan: Any
     diagnostics: tuple[str, ...]
 
 
@@ -103,12 +105,14 @@ def known_targets() -> tuple[str, ...]:
 
 def lower_for_target(kernel_fn: Any, target: str) -> TargetResult:
     """Tries the kernel classes the target runs: the tiled matmul family, then the masked
-    element-wise map (`hc._map_kernels`). The diagnostics of the class the kernel's signature
-    points at are reported when neither matches."""
+    element-wise map (`hc._map_kernels`), pairwise distances (`hc._pairwise_kernels`) and row sums
+    (`hc._reduce_kernels`). The diagnostics of the class the kernel's signature points at are
+    reported when none matches."""
     if target != NVIDIA_SM100A:
         raise ValueError(f"unknown hc.compile target {target!r}; known targets: {list(known_targets())}")
     from ._map_kernels import recognise_elementwise_map
     from ._pairwise_kernels import recognise_pairwise
+    from ._reduce_kernels import recognise_row_sum
 
     plan, diagnostics = recognise_tiled_matmul(kernel_fn)
     if plan is None:
@@ -118,8 +122,11 @@ def lower_for_target(kernel_fn: Any, target: str) -> TargetResult:
         pair_plan, pair_diagnostics = recognise_pairwise(kernel_fn)
         if pair_plan is not None:
             return TargetResult(target, pair_plan, ())
+        row_plan, row_diagnostics = recognise_row_sum(kernel_fn)
+        if row_plan is not None:
+            return TargetResult(target, row_plan, ())
         if _looks_one_dimensional(kernel_fn):
-            diagnostics = map_diagnostics
+            diagnostics = row_diagnostics if _reduces_without_loop(kernel_fn, 3) else map_diagnostics
         elif _looks_like_pairwise(kernel_fn):
             diagnostics = pair_diagnostics
     return TargetResult(target, plan, tuple(diagnostics))
@@ -127,17 +134,23 @@ def lower_for_target(kernel_fn: Any, target: str) -> TargetResult:
 
 def _looks_like_pairwise(kernel_fn: Any) -> bool:
     """Three buffers, no k-loop and a reduction of a value (`.sum(...)`): not a member of the matmul family."""
+    return _reduces_without_loop(kernel_fn, 4)
+
+
+def _reduces_without_loop(kernel_fn: Any, parameter_count: int) -> bool:
+    """`parameter_count` parameters (the group included), no loop and a reduction of a value
+    (`.sum(...)`, `.max(...)`, `.min(...)`)."""
     source = _function_node(kernel_fn)
     if source is None:
         return False
     nodes = list(ast.walk(source))
     has_loop = any(isinstance(node, (ast.For, ast.While)) for node in nodes)
-    reduces = any(isinstance(node, ast.Attribute) and node.attr == "sum" for node in nodes)
+    reduces = any(isinstance(node, ast.Attribute) and node.attr in ("sum", "max", "min") for node in nodes)
     try:
         count = len(inspect.signature(kernel_fn).parameters)
     except (TypeError, ValueError):
         return False
-    return count == 4 and reduces and not has_loop
+    return count == parameter_count and reduces and not has_loop
 
 
 def _looks_one_dimensional(kernel_fn: Any) -> bool:

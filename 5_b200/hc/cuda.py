@@ -39,7 +39,7 @@ F16, BF16, F8E4M3, F8E5M2 = 0, 1, 2, 3  # HcCudaDType
 VARIANT_AUTO, VARIANT_DENSE, VARIANT_SKINNY, VARIANT_NOOP, VARIANT_ZERO_FILL, VARIANT_ELEMENTWISE = 0, 1, 2, 3, 4, 5
 VARIANT_TINY = 6  # float32 pipes, bit-identical to the reference simulator; AUTO picks it for m, n <= 64, k <= 128
 VARIANT_NAMES = {0: "auto", 1: "dense", 2: "skinny", 3: "noop", 4: "zero_fill", 5: "elementwise", 6: "tiny"}
-API_VERSION = 6
+API_VERSION = 7
 # Element-wise operations fused into the store of C: ("scale", x), ("add", x), ("max", x),
 # ("min", x) and ("bias",) -- the last adds bias[column].
 EPILOGUE_KINDS = {"scale": 1, "add": 2, "max": 3, "min": 4, "bias": 5}
@@ -57,7 +57,7 @@ EXPORTS = (
     "hcCudaEventDestroy", "hcCudaEventRecord", "hcCudaEventElapsedMs", "hcCudaCommGetUniqueId",
     "hcCudaCommInitRank", "hcCudaCommAllGather", "hcCudaCommDestroy", "hcCudaGemmSkinnyStatic", "hcCudaSelfTestDeviceTimeout", "hcCudaGemmPush", "hcCudaIpcExport",
     "hcCudaIpcOpen", "hcCudaIpcClose", "hcCudaMap", "hcCudaMapHost",
-    "hcCudaGemmHostDeviceA", "hcCudaPairwise", "hcCudaPairwiseHost", "hcCudaBuildFlags", "hcCudaSelfTestDeviceCheck",
+    "hcCudaGemmHostDeviceA", "hcCudaPairwise", "hcCudaPairwiseHost", "hcCudaRowSum", "hcCudaRowSumHost", "hcCudaBuildFlags", "hcCudaSelfTestDeviceCheck",
 )
 
 
@@ -122,6 +122,14 @@ class _PairwiseArgs(ctypes.Structure):
 
 
 PAIRWISE_EUCLIDEAN, PAIRWISE_SQUARED = 0, 1
+
+
+class _RowSumArgs(ctypes.Structure):
+    _fields_ = [("w", ctypes.c_int64), ("h", ctypes.c_int64), ("x", ctypes.c_void_p), ("ldx", ctypes.c_int64),
+                ("out", ctypes.c_void_p), ("flags", ctypes.c_int32)]
+
+
+ROW_SUM_SQUARE, ROW_SUM_SQRT = 1, 2
 
 
 class _DeviceInfo(ctypes.Structure):
@@ -203,6 +211,8 @@ def library() -> ctypes.CDLL:
         lib.hcCudaSelfTestDeviceCheck.argtypes = [vp]
         lib.hcCudaPairwise.argtypes = [vp, ctypes.POINTER(_PairwiseArgs)]
         lib.hcCudaPairwiseHost.argtypes = [vp, ctypes.POINTER(_PairwiseArgs)]
+        lib.hcCudaRowSum.argtypes = [vp, ctypes.POINTER(_RowSumArgs)]
+        lib.hcCudaRowSumHost.argtypes = [vp, ctypes.POINTER(_RowSumArgs)]
         for name in EXPORTS:
             getattr(lib, name)  # AttributeError here means a stale or foreign library
         _LIB = lib
@@ -508,6 +518,34 @@ class Context:
         args = _PairwiseArgs(w1, w2, h, x1.ctypes.data, pitch(x1), x2.ctypes.data, pitch(x2), out.ctypes.data,
                              pitch(out), PAIRWISE_EUCLIDEAN if take_sqrt else PAIRWISE_SQUARED)
         self._check(self._lib.hcCudaPairwiseHost(self._handle, ctypes.byref(args)))
+
+    def row_sum(self, x: "DeviceBuffer", out: "DeviceBuffer", *, square: bool = False, take_sqrt: bool = False) -> None:
+        """Enqueues out[i] = sum_h x[i, h] on a float32 device matrix x (w, h) and vector out (w,),
+        with every value squared first (`square`) and the square root of the sum stored (`take_sqrt`)
+        if asked: the row-sum kernel class, bit-identical to the reference simulator (asynchronous;
+        see `synchronize`)."""
+        if x.dtype != np.float32 or out.dtype != np.float32 or len(x.shape) != 2 or len(out.shape) != 1:
+            raise ValueError("row_sum() takes a two-dimensional and a one-dimensional float32 device buffer")
+        w, h = x.shape
+        if out.shape != (w,):
+            raise ValueError(f"row_sum(): shapes {x.shape} -> {out.shape} do not fit")
+        flags = (ROW_SUM_SQUARE if square else 0) | (ROW_SUM_SQRT if take_sqrt else 0)
+        args = _RowSumArgs(w, h, x.ptr, x.ld, out.ptr, flags)
+        self._check(self._lib.hcCudaRowSum(self._handle, ctypes.byref(args)))
+
+    def row_sum_host(self, x: np.ndarray, out: np.ndarray, *, square: bool = False, take_sqrt: bool = False) -> None:
+        """The same on a row-major float32 host matrix (rows may be padded) and a contiguous float32
+        host vector: copies in, runs, copies `out` back in place; returns when `out` is complete."""
+        if (x.dtype != np.float32 or x.ndim != 2 or (x.shape[1] > 1 and x.strides[1] != 4) or out.dtype != np.float32
+                or out.ndim != 1 or (out.shape[0] > 1 and out.strides[0] != 4)):
+            raise ValueError("row_sum_host() takes a row-major float32 matrix and a contiguous float32 vector")
+        w, h = x.shape
+        if out.shape != (w,):
+            raise ValueError(f"row_sum_host(): shapes {x.shape} -> {out.shape} do not fit")
+        pitch = x.strides[0] // 4 if w > 1 else max(h, 1)
+        flags = (ROW_SUM_SQUARE if square else 0) | (ROW_SUM_SQRT if take_sqrt else 0)
+        args = _RowSumArgs(w, h, x.ctypes.data, pitch, out.ctypes.data, flags)
+        self._check(self._lib.hcCudaRowSumHost(self._handle, ctypes.byref(args)))
 
     def gemm_host(self, a: np.ndarray, b: np.ndarray, c: np.ndarray, *,
                   variant: int = VARIANT_AUTO, b_transposed: bool = False, accumulate: bool = False,

@@ -1761,6 +1761,91 @@ int hcCudaPairwiseHost(HcCudaContext *ctx, const HcCudaPairwiseArgs *args) {
   return synchronize_locked(ctx);
 }
 
+namespace {
+
+int check_row_sum_args(const HcCudaContext *ctx, const HcCudaRowSumArgs *args) {
+  if (args == nullptr)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "args must not be null");
+  if (args->w < 0 || args->h < 0)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "w and h must be non-negative (got %lld, %lld)",
+                (long long)args->w, (long long)args->h);
+  if (args->w > 0x7fffffffLL)
+    return fail(ctx, HC_CUDA_ERR_UNSUPPORTED, "w must be below 2^31");
+  if (args->h > hc::sm100::pairwise_max_h())
+    return fail(ctx, HC_CUDA_ERR_UNSUPPORTED, "h must be at most %d (got %lld)", hc::sm100::pairwise_max_h(),
+                (long long)args->h);
+  if ((args->flags & ~(HC_CUDA_ROW_SUM_SQUARE | HC_CUDA_ROW_SUM_SQRT)) != 0)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "flags has bits that are no HcCudaRowSumFlags (got %d)", args->flags);
+  if (args->w == 0 || args->h == 0)
+    return HC_CUDA_OK;
+  if (args->x == nullptr || args->out == nullptr)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "x and out must not be null");
+  if (((reinterpret_cast<uintptr_t>(args->x) | reinterpret_cast<uintptr_t>(args->out)) & 3) != 0)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "x and out must be 4-byte aligned");
+  if (args->ldx < args->h || args->ldx > kMaxPitch)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "ldx must be at least h (%lld)", (long long)args->h);
+  const size_t bytes_x = (static_cast<size_t>(args->w - 1) * args->ldx + args->h) * 4;
+  if (ranges_overlap(args->out, static_cast<size_t>(args->w) * 4, args->x, bytes_x))
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "out must not overlap x");
+  return HC_CUDA_OK;
+}
+
+} // namespace
+
+int hcCudaRowSum(HcCudaContext *ctx, const HcCudaRowSumArgs *args) {
+  if (ctx == nullptr)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "ctx must not be null");
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  if (int rc = check_row_sum_args(ctx, args))
+    return rc;
+  if (args->w == 0 || args->h == 0)
+    return HC_CUDA_OK;
+  HC_TRY_CUDA(ctx, cudaSetDevice(ctx->device));
+  if (int rc = ensure_pairwise_schedule(ctx, static_cast<int>(args->h)))
+    return rc;
+  HC_TRY_CUDA(ctx, hc::sm100::launch_row_sum_f32(args->x, args->ldx, args->out, static_cast<int>(args->w),
+                                                 static_cast<int>(args->h), args->flags & HC_CUDA_ROW_SUM_SQUARE,
+                                                 args->flags & HC_CUDA_ROW_SUM_SQRT, ctx->pairwise_leaves,
+                                                 ctx->pairwise_leaf_count, ctx->prop.multiProcessorCount, ctx->stream));
+  return HC_CUDA_OK;
+}
+
+int hcCudaRowSumHost(HcCudaContext *ctx, const HcCudaRowSumArgs *args) {
+  if (ctx == nullptr)
+    return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "ctx must not be null");
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  if (int rc = check_row_sum_args(ctx, args))
+    return rc;
+  if (args->w == 0 || args->h == 0)
+    return HC_CUDA_OK;
+  HC_TRY_CUDA(ctx, cudaSetDevice(ctx->device));
+  if (int rc = ensure_pairwise_schedule(ctx, static_cast<int>(args->h)))
+    return rc;
+  // A compact device copy with a pitch that allows 16-byte loads.
+  const size_t w = static_cast<size_t>(args->w), h = static_cast<size_t>(args->h);
+  const size_t ld = static_cast<size_t>(round_up(static_cast<int64_t>(h), 4));
+  if (int rc = ensure_stage(ctx, 0, w * ld * 4))
+    return rc;
+  if (int rc = ensure_stage(ctx, 2, w * 4))
+    return rc;
+  struct Drain {  // no copy may still touch the caller's arrays when the call returns
+    HcCudaContext *ctx;
+    ~Drain() {
+      if (cudaStreamSynchronize(ctx->stream) != cudaSuccess)
+        cudaGetLastError();
+    }
+  } drain{ctx};
+  HC_TRY_CUDA(ctx, cudaMemcpy2DAsync(ctx->stage[0], ld * 4, args->x, static_cast<size_t>(args->ldx) * 4, h * 4, w,
+                                     cudaMemcpyHostToDevice, ctx->stream));
+  HC_TRY_CUDA(ctx, hc::sm100::launch_row_sum_f32(static_cast<const float *>(ctx->stage[0]), static_cast<long long>(ld),
+                                                 static_cast<float *>(ctx->stage[2]), static_cast<int>(w),
+                                                 static_cast<int>(h), args->flags & HC_CUDA_ROW_SUM_SQUARE,
+                                                 args->flags & HC_CUDA_ROW_SUM_SQRT, ctx->pairwise_leaves,
+                                                 ctx->pairwise_leaf_count, ctx->prop.multiProcessorCount, ctx->stream));
+  HC_TRY_CUDA(ctx, cudaMemcpyAsync(args->out, ctx->stage[2], w * 4, cudaMemcpyDeviceToHost, ctx->stream));
+  return synchronize_locked(ctx);
+}
+
 int hcCudaSelfTestDeviceTimeout(HcCudaContext *ctx, int64_t budget_cycles) {
   if (ctx == nullptr)
     return fail(ctx, HC_CUDA_ERR_INVALID_ARGUMENT, "ctx must not be null");

@@ -685,6 +685,46 @@ def pairwise_record(ctx, ranks: Ranks, sampler: ClockSampler, steps: int) -> dic
         return {"error": f"{type(exc).__name__}: {exc}"}
 
 
+def row_sum_record(ctx, ranks: Ranks, sampler: ClockSampler, steps: int, peaks: dict, peaks_source: str) -> dict:
+    """The row-sum kernel class (examples/b200_rowsum.py: row_norms, the square root of the sum of the
+    squared values of each row) on 2^19 rows of 512 values: HBM-bound, 4 bytes read per value and 4
+    written per row, checked bit for bit against the NumPy oracle (the additions follow the order of
+    NumPy's sum)."""
+    try:
+        from oracle import cpu_ref
+
+        w, h = 1 << 19, 512
+        rng = np.random.default_rng(19)
+        x = rng.standard_normal((w, h), dtype=np.float32)
+        dx, dout = ctx.to_device(x), ctx.empty((w,), np.float32)
+        launch = lambda i: ctx.row_sum(dx, dout, square=True, take_sqrt=True)  # noqa: E731
+        for i in range(5):
+            launch(i)
+        ctx.synchronize()
+        elapsed_ms, clocks = timed_region(ctx, ranks, sampler, launch, steps)
+        ms = elapsed_ms / steps
+        rows = np.r_[0:8192, w - 8192 : w]
+        got = dout.to_numpy()[rows]
+        want = cpu_ref.row_sums(x[rows], square=True, take_sqrt=True)
+        ok = bool(np.array_equal(got.view(np.uint32), want.view(np.uint32)))
+        algo = 4.0 * w * h + 4.0 * w
+        achieved, peak = algo / (ms * 1e-3) / 1e9, float(peaks["hbm_gbs"])
+        for buf in (dx, dout):
+            buf.free()
+        return {"kernel_class": "row sums (row_norms: sqrt of the sum of the squared values of a row)",
+                "w": w, "h": h, "steps": steps, "ms_per_step": ms, "gbs": achieved,
+                "l2": "input larger than L2 (1 GiB per launch)",
+                "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                             "frac": achieved / peak, "algorithmic_bytes_per_launch": algo,
+                             "peak_source": f"{peaks_source} HBM copy bandwidth", "kernel": "row_sum_f32_kernel",
+                             "frac_of_nominal": achieved / NOMINAL_HBM_GBS, "traffic": None,
+                             "traffic_source": "not captured for this workload"},
+                "parity": {"rule": "bit-identical to the NumPy oracle (first and last 8192 rows)", "ok": ok},
+                "clocks": clocks}
+    except Exception as exc:
+        return {"error": f"{type(exc).__name__}: {exc}"}
+
+
 def run_gpu_arm(args, ranks: Ranks) -> None:
     from hc import cuda
     from hc.distributed import column_slab, init_communicator
@@ -869,6 +909,7 @@ def run_gpu_arm(args, ranks: Ranks) -> None:
         side["long_k"] = side_record(ctx, ranks, sampler, "long_k", 1000, peaks, peaks_source)
         side["elementwise_map"] = map_record(ctx, ranks, sampler, 50, peaks, peaks_source)
         side["pairwise"] = pairwise_record(ctx, ranks, sampler, 20)
+        side["row_sum"] = row_sum_record(ctx, ranks, sampler, 50, peaks, peaks_source)
         side["sharded_1gpu"] = side_record(ctx, ranks, sampler, "sharded", 10, peaks, peaks_source,
                                            sustained_seconds=args.sustained_seconds)
     sampler.stop()

@@ -39,7 +39,7 @@
 extern "C" {
 #endif
 
-#define HC_CUDA_API_VERSION 6
+#define HC_CUDA_API_VERSION 7
 
 typedef enum HcCudaStatus {
   HC_CUDA_OK = 0,
@@ -373,6 +373,44 @@ HC_CUDA_CAPI_EXPORTED int hcCudaPairwise(HcCudaContext *ctx, const HcCudaPairwis
 /* Synchronous; x1, x2, out are host pointers (NumPy buffers): the in-place, synchronous behaviour
  * of `hc.simulator.launch` (hc/simulator.py:165-186). */
 HC_CUDA_CAPI_EXPORTED int hcCudaPairwiseHost(HcCudaContext *ctx, const HcCudaPairwiseArgs *args);
+
+/* ---- row sums: the one-dimensional workgroup kernel that reduces the rows it loads ------- */
+
+typedef enum HcCudaRowSumFlags {
+  HC_CUDA_ROW_SUM_SQUARE = 1, /* every value is multiplied by itself (one rounding) before it is added */
+  HC_CUDA_ROW_SUM_SQRT = 2    /* the square root of the sum is stored */
+} HcCudaRowSumFlags;
+
+/* out[i] for i < w from x (w x h), float32, row-major with pitch ldx in elements: what the reference
+ * simulator computes for
+ *
+ *     r0 = group.work_offset[0]
+ *     rows = group.load(x[r0:], shape=(group.shape[0], x.shape[1]))
+ *     group.store(out[r0:], rows.sum(axis=1))
+ *
+ * launched over work_shape=(w,) -- optionally `(rows * rows).sum(axis=1)` (HC_CUDA_ROW_SUM_SQUARE)
+ * and `np.sqrt(...)` of the sum (HC_CUDA_ROW_SUM_SQRT). The load is masked at the end of the buffer
+ * (hc/simulator.py:1338-1357) and a reduction keeps the active values only
+ * (hc/_sim_types.py:1050-1102), so exactly the w elements of out are written, each the np.sum of its
+ * row: float32 additions in the order of NumPy's sum of a contiguous vector, which the kernel
+ * follows, so the result is bit-identical to the simulator's. h == 0 writes nothing (a reduction
+ * over no active element is inactive). h at most 2^20; out must not overlap x. */
+typedef struct HcCudaRowSumArgs {
+  int64_t w, h;
+  const float *x;
+  int64_t ldx;
+  float *out;
+  int32_t flags; /* HcCudaRowSumFlags, or'ed */
+} HcCudaRowSumArgs;
+
+/* Asynchronous; x and out are device pointers on the context's device. What
+ * `CompiledKernel.__call__` (hc/_compile.py:57-62) resolves to for a recognised row-sum kernel on
+ * device buffers. */
+HC_CUDA_CAPI_EXPORTED int hcCudaRowSum(HcCudaContext *ctx, const HcCudaRowSumArgs *args);
+
+/* Synchronous; x and out are host pointers (NumPy buffers): the in-place, synchronous behaviour of
+ * `hc.simulator.launch` (hc/simulator.py:165-186). */
+HC_CUDA_CAPI_EXPORTED int hcCudaRowSumHost(HcCudaContext *ctx, const HcCudaRowSumArgs *args);
 
 /* ---- the product fused with its gather (N-sharded GEMM, one process per GPU) ------------- */
 

@@ -216,6 +216,27 @@ def pairwise_distance(x1: np.ndarray, x2: np.ndarray, *, take_sqrt: bool = True,
     return out
 
 
+def row_sums(x: np.ndarray, *, square: bool = False, take_sqrt: bool = False, restated: bool = False) -> np.ndarray:
+    """The row-sum kernel class as the reference simulator executes it: out[i] = np.sum of row i in
+    float32 (`_reduce_active` hands the active values of a row, a contiguous vector, to np.sum,
+    hc/_sim_types.py:1050-1066, 1100-1102), with every value multiplied by itself first (`square`:
+    `rows * rows` and `rows ** 2` are the same float32 product) and np.sqrt of the sum (`take_sqrt`) if
+    asked. Reducing the last axis of a contiguous matrix runs the same inner loop per row, so the
+    fast form is one NumPy call; `restated` computes every row with `pairwise_sum_in_numpy_order`
+    plus the reduction's initial value +0 instead (the tests hold the two against each other).
+    A matrix without columns gives no output at all in the simulator (a reduction over no active
+    value is inactive and is not stored); callers handle that case, this function returns zeros."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    with np.errstate(invalid="ignore", over="ignore"):
+        values = x * x if square else x
+        if restated:
+            total = np.array([np.float32(np.float32(0.0) + pairwise_sum_in_numpy_order(row)) for row in values],
+                             np.float32).reshape(x.shape[0])
+        else:
+            total = np.ascontiguousarray(values).sum(axis=1, dtype=np.float32)
+        return np.sqrt(total) if take_sqrt else total
+
+
 def pairwise_sum_in_numpy_order(values: np.ndarray) -> np.float32:
     """NumPy's float32 sum of a contiguous vector, written out: fewer than 8 values are added in
     order; up to 128 go into eight interleaved accumulators r[i % 8] that are combined as

@@ -45,6 +45,11 @@ Fixtures (all produced by `hc.simulator.launch` on the example kernel):
       reference's own test (tests/test_simulator.py:142-167), `x1`, `x2`, `out` the same kernel on
       37 x 29 outputs over 150 values, `sq_x1`, `sq_x2`, `sq_out` the squared-distance kernel on
       19 x 35 outputs over 333 values with an infinity and a NaN
+  simrow_f32_seed19
+      the row-sum kernels of 5_b200/examples/b200_rowsum.py: `x`, `sums` row_sums on 37 rows of 150
+      values (scales from 1e-3 to 300, some -0.0), `few_x`, `few_sums` on 9 rows of 5 values (one row
+      all -0.0), `norm_x`, `norms` row_norms on 21 rows of 333 values with an infinity and a NaN,
+      `energy_x`, `energy` row_energy on 13 rows of 1000 values
 The file blocked_reference.npz holds `reference_blocked_matmul` of the first four (the
 reference test's own comparison value, atol 2e-6).
 """
@@ -266,6 +271,36 @@ def main() -> int:
     np.savez_compressed(HERE / "simpair_f32_seed18.npz", test_x1=t1, test_x2=t2, test_out=t_out, x1=p1, x2=p2, out=p_out,
                         sq_x1=q1, sq_x2=q2, sq_out=q_out)
     print(f"simpair_f32_seed18: pairwise{t_out.shape} pairwise{p_out.shape} pairwise_squared{q_out.shape}", flush=True)
+
+    # The row-sum kernels of 5_b200/examples/b200_rowsum.py under the reference simulator: row lengths
+    # below eight (added in order), 150 (NumPy's sum splits at 72, the tail has 6 values), 333 and 1000
+    # (three levels of splitting); no group size divides the row counts.
+    path = REPO / "5_b200" / "examples" / "b200_rowsum.py"
+    spec = importlib.util.spec_from_file_location("b200_rowsum_under_reference", path)
+    rs = importlib.util.module_from_spec(spec)
+    rs.__package__ = "loaded_by_make_golden"
+    sys.modules[spec.name] = rs
+    spec.loader.exec_module(rs)
+    rng = np.random.default_rng(19)
+    r1 = (rng.standard_normal((37, 150)) * rng.choice([1e-3, 1.0, 300.0], size=(37, 150))).astype(np.float32)
+    r1[rng.integers(0, 37, 40), rng.integers(0, 150, 40)] = -0.0
+    r1_out = np.full((37,), np.float32(-7.0))
+    rs.hc.simulator.launch(rs.row_sums, r1, r1_out)
+    r2 = rng.standard_normal((9, 5)).astype(np.float32)
+    r2[4, :] = -0.0
+    r2_out = np.full((9,), np.float32(-7.0))
+    rs.hc.simulator.launch(rs.row_sums, r2, r2_out)
+    r3 = rng.standard_normal((21, 333)).astype(np.float32)
+    r3[3, 200], r3[7, 5] = np.inf, np.nan
+    r3_out = np.full((21,), np.float32(-7.0))
+    with np.errstate(invalid="ignore"):
+        rs.hc.simulator.launch(rs.row_norms, r3, r3_out)
+    r4 = (rng.standard_normal((13, 1000)) * 30.0).astype(np.float32)
+    r4_out = np.full((13,), np.float32(-7.0))
+    rs.hc.simulator.launch(rs.row_energy, r4, r4_out)
+    np.savez_compressed(HERE / "simrow_f32_seed19.npz", x=r1, sums=r1_out, few_x=r2, few_sums=r2_out, norm_x=r3,
+                        norms=r3_out, energy_x=r4, energy=r4_out)
+    print(f"simrow_f32_seed19: row_sums{r1.shape} row_sums{r2.shape} row_norms{r3.shape} row_energy{r4.shape}", flush=True)
     return 0
 
 
