@@ -1806,7 +1806,7 @@ int hcCudaRowSum(HcCudaContext *ctx, const HcCudaRowSumArgs *args) {
   HC_TRY_CUDA(ctx, hc::sm100::launch_row_sum_f32(args->x, args->ldx, args->out, static_cast<int>(args->w),
                                                  static_cast<int>(args->h), args->flags & HC_CUDA_ROW_SUM_SQUARE,
                                                  args->flags & HC_CUDA_ROW_SUM_SQRT, ctx->pairwise_leaves,
-                                                 ctx->pairwise_leaf_count, ctx->prop.multiProcessorCount, ctx->stream));
+                                                 ctx->pairwise_leaf_count, ctx->stream));
   return HC_CUDA_OK;
 }
 
@@ -1841,7 +1841,7 @@ int hcCudaRowSumHost(HcCudaContext *ctx, const HcCudaRowSumArgs *args) {
                                                  static_cast<float *>(ctx->stage[2]), static_cast<int>(w),
                                                  static_cast<int>(h), args->flags & HC_CUDA_ROW_SUM_SQUARE,
                                                  args->flags & HC_CUDA_ROW_SUM_SQRT, ctx->pairwise_leaves,
-                                                 ctx->pairwise_leaf_count, ctx->prop.multiProcessorCount, ctx->stream));
+                                                 ctx->pairwise_leaf_count, ctx->stream));
   HC_TRY_CUDA(ctx, cudaMemcpyAsync(args->out, ctx->stage[2], w * 4, cudaMemcpyDeviceToHost, ctx->stream));
   return synchronize_locked(ctx);
 }

@@ -210,11 +210,10 @@ cudaError_t launch_pairwise_f32(const float *x1, long long ld1, const float *x2,
                                 int num_leaves, cudaStream_t stream);
 // Row sums out[i] = [sqrt] sum_h x[i, h] [squared] in float32, the sum in the order of NumPy's float32
 // sum (np.sum of the row, starting from +0). `leaves_dev`: pairwise_schedule(h, ...) on the device.
-// A row is shared among row_sum_parts(w, h, sm_count) lane pairs (1 to 16) when there are too few rows to
-// fill `sm_count` SMs.
+// A row of more than 128 values is shared among row_sum_parts(h) lane pairs (2 to 16) of one warp.
 cudaError_t launch_row_sum_f32(const float *x, long long ldx, float *out, int w, int h, int square, int take_sqrt,
-                               const int4 *leaves_dev, int num_leaves, int sm_count, cudaStream_t stream);
-int row_sum_parts(int w, int h, int sm_count);
+                               const int4 *leaves_dev, int num_leaves, cudaStream_t stream);
+int row_sum_parts(int h);
 // The leaves of NumPy's pairwise summation of h values: {first, length, additions of pending partial
 // sums once the leaf is done, 0}. Returns their number (which may exceed `capacity`; nothing is
 // written past it).

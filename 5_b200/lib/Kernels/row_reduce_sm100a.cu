@@ -29,11 +29,13 @@
 // one accumulator never leave their lane, so their order is NumPy's; the two lanes meet in one
 // shuffle per leaf. The partial sums that wait for their right-hand neighbour in the recursion sit
 // on a small per-thread stack.
-// With few rows (fewer lanes than the GPU holds) a row is shared by P = 2, 4, 8 or 16 pairs of one
-// warp: the first log2(P) levels of the recursion cut the row into P consecutive ranges of leaves,
-// each pair sums one range exactly as above, and the P results are added in the recursion's own
-// order (neighbours first) with shuffles. All lanes of a warp then walk the same number of steps
-// with their loads and additions predicated, since ranges and leaves differ in length.
+// A row of more than 128 values is shared by P = 2, 4, 8 or 16 pairs of one warp: the first log2(P)
+// levels of the recursion cut the row into P consecutive ranges of leaves (P as large as the
+// recursion allows), each pair sums one range exactly as above, and the P results are added in the
+// recursion's own order (neighbours first) with shuffles. All lanes of a warp then walk the same
+// number of steps with their loads and additions predicated, since ranges and leaves differ in
+// length. Up to 16 leaves a pair has one leaf, so a warp's loads fall into consecutive leaves; beyond
+// that the ranges also keep many lanes busy when the rows are few.
 // Bytes per launch: 4 W H read once + 4 W written; there is no reuse, the kernel is HBM bound.
 #include "gemm_launch.h"
 
@@ -186,12 +188,14 @@ bool list_parts(int n, int depth, int first_leaf, RowParts *parts, int *index) {
 
 } // namespace
 
-int row_sum_parts(int w, int h, int sm_count) {
-  // Two lanes per row and part; a row is shared among more pairs while the lanes would not fill the
-  // SMs (2048 per SM) and the recursion still has a level to cut at.
-  const long long lanes_wanted = static_cast<long long>(sm_count > 0 ? sm_count : 1) * 2048;
+int row_sum_parts(int h) {
+  // As many ranges as the recursion has levels to cut at, up to 16. With as many ranges as leaves a
+  // warp reads 16 consecutive leaves (8 KB) at a time whatever the row length, and the results meet
+  // in shuffles instead of on the stack; with more leaves than that the ranges are what keeps many
+  // lanes busy when the rows are few. Measured on 2^19 rows of 512 values: 5.66 TB/s with one pair per
+  // row, 6.68 with four; 8192 rows of 32768: 1.98 against 5.19 TB/s with sixteen.
   int parts = 1, depth = 0;
-  while (parts < 16 && 2LL * w * parts < lanes_wanted) {
+  while (parts < 16) {
     RowParts probe;
     int index = 0;
     if (!list_parts(h, depth + 1, 0, &probe, &index))
@@ -203,13 +207,20 @@ int row_sum_parts(int w, int h, int sm_count) {
 }
 
 cudaError_t launch_row_sum_f32(const float *x, long long ldx, float *out, int w, int h, int square, int take_sqrt,
-                               const int4 *leaves_dev, int num_leaves, int sm_count, cudaStream_t stream) {
+                               const int4 *leaves_dev, int num_leaves, cudaStream_t stream) {
   if (w <= 0 || h <= 0)
     return cudaSuccess;  // a row without values is not stored
   if (h > pairwise_max_h() || leaves_dev == nullptr || num_leaves < 1)
     return cudaErrorInvalidValue;
   RowParts parts;
-  parts.parts = row_sum_parts(w, h, sm_count);
+  parts.parts = row_sum_parts(h);
+  // Rows that only allow 4-byte loads (a pitch or base off the 16-byte grid) keep one pair each when
+  // there are enough of them to fill the GPU: with four times the load instructions the predicated
+  // steps of shared rows cost more than the consecutive leaves give (300000 rows of 1031 values:
+  // 3.7 TB/s against 2.2).
+  const bool vector_ok = (ldx & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+  if (!vector_ok && w >= 65536)
+    parts.parts = 1;
   int depth = 0, index = 0;
   while ((1 << depth) < parts.parts)
     ++depth;

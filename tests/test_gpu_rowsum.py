@@ -39,7 +39,8 @@ def test_handle_matches_the_reference_simulator_bit_for_bit() -> None:
 @pytest.mark.parametrize("h", [1, 5, 7, 8, 9, 15, 16, 31, 33, 127, 128, 129, 150, 256, 257, 300, 1031, 4100, 70000])
 def test_every_summation_shape_matches_numpy(h: int, gpu_ctx) -> None:
     """The order of NumPy's float32 sum changes with the number of values (fewer than 8, up to 128,
-    recursive halves): each regime, with a row count no CTA size divides, against the oracle."""
+    recursive halves, which the kernel cuts into 2 to 16 ranges per row): each regime, with a row
+    count no CTA size divides, against the oracle."""
     rng = np.random.default_rng([h, 31])
     w = 301 if h < 10000 else 37
     x = (rng.standard_normal((w, h)) * rng.choice([1e-3, 1.0, 50.0], size=(w, h))).astype(np.float32)
@@ -133,9 +134,9 @@ def test_a_larger_problem_on_device_buffers_through_the_handle(gpu_ctx) -> None:
     dout.free()
 
 
-def test_many_rows_one_pair_of_lanes_per_row(gpu_ctx) -> None:
-    """Enough rows to fill the GPU, so no row is shared among lane pairs, with rows long enough for
-    NumPy's recursion (the smaller shapes above run with shared rows)."""
+def test_many_rows_of_several_leaves(gpu_ctx) -> None:
+    """More rows than the GPU holds at once, each of four leaves of NumPy's recursion (four pairs of
+    lanes per row), and the row count not a multiple of the rows of a CTA."""
     rng = np.random.default_rng(36)
     w, h = 330001, 300
     x = rng.standard_normal((w, h)).astype(np.float32)
