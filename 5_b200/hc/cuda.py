@@ -39,7 +39,7 @@ F16, BF16, F8E4M3, F8E5M2 = 0, 1, 2, 3  # HcCudaDType
 VARIANT_AUTO, VARIANT_DENSE, VARIANT_SKINNY, VARIANT_NOOP, VARIANT_ZERO_FILL, VARIANT_ELEMENTWISE = 0, 1, 2, 3, 4, 5
 VARIANT_TINY = 6  # float32 pipes, bit-identical to the reference simulator; AUTO picks it for m, n <= 64, k <= 128
 VARIANT_NAMES = {0: "auto", 1: "dense", 2: "skinny", 3: "noop", 4: "zero_fill", 5: "elementwise", 6: "tiny"}
-API_VERSION = 7
+API_VERSION = 8
 # Element-wise operations fused into the store of C: ("scale", x), ("add", x), ("max", x),
 # ("min", x) and ("bias",) -- the last adds bias[column].
 EPILOGUE_KINDS = {"scale": 1, "add": 2, "max": 3, "min": 4, "bias": 5}
@@ -109,7 +109,7 @@ class _PlanInfo(ctypes.Structure):
         ("splits", ctypes.c_int32), ("grid", ctypes.c_int32), ("repack_a", ctypes.c_int32),
         ("repack_b", ctypes.c_int32), ("kernel_launches", ctypes.c_int32),
         ("scratch_bytes", ctypes.c_int64), ("first_split_tile", ctypes.c_int32), ("ring_stages", ctypes.c_int32),
-        ("cluster_size", ctypes.c_int32),
+        ("cluster_size", ctypes.c_int32), ("tile_n", ctypes.c_int32),
     ]
 
 
@@ -274,6 +274,7 @@ class GemmPlan:
         self.first_split_tile = info.first_split_tile
         self.ring_stages = info.ring_stages  # skinny: shared-memory ring depth of this grid; else 0
         self.cluster_size = info.cluster_size  # dense, few tiles: CTAs per cluster sharing a tile; else 0
+        self.tile_n = info.tile_n  # dense: columns of a tile (256, or 128 for small products); else 0
 
     def __repr__(self) -> str:
         splits = f"{self.splits}" + (f" from tile {self.first_split_tile}" if self.first_split_tile else "")

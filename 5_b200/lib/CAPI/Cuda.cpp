@@ -360,6 +360,7 @@ int plan_gemm(const HcCudaContext *ctx, const HcCudaGemmArgs *args, int sm_count
     }
     plan->tiles_m = static_cast<int32_t>((m + tile_m - 1) / tile_m);
     plan->tiles_n = static_cast<int32_t>((n + t.block_n - 1) / t.block_n);
+    plan->tile_n = static_cast<int32_t>(t.block_n);
     const int64_t tiles = static_cast<int64_t>(plan->tiles_m) * plan->tiles_n;
     if (tiles > 0x3fffffffLL)
       return fail(ctx, HC_CUDA_ERR_UNSUPPORTED, "too many tiles");
@@ -404,6 +405,20 @@ int plan_gemm(const HcCudaContext *ctx, const HcCudaGemmArgs *args, int sm_count
         plan->scratch_bytes = scratch;
         return HC_CUDA_OK;
       }
+    }
+    // A small unsplit product whose 256-wide tiles would leave most SMs idle runs on 128 x 128 tiles
+    // (single CTAs): twice the tiles, each a little over half the time.
+    if (plan->splits == 1 && !wide && !(ctx != nullptr && (ctx->planning_push || ctx->planning_host_panels)) &&
+        hc::sm100::dense_uses_narrow(m, n, sm_count, pairs)) {
+      const int64_t narrow_n = hc::sm100::dense_narrow_block_n();
+      plan->tile_n = static_cast<int32_t>(narrow_n);
+      plan->tiles_m = static_cast<int32_t>((m + t.block_m - 1) / t.block_m);
+      plan->tiles_n = static_cast<int32_t>((n + narrow_n - 1) / narrow_n);
+      const int64_t narrow_tiles = static_cast<int64_t>(plan->tiles_m) * plan->tiles_n;
+      plan->grid = static_cast<int32_t>(narrow_tiles < sm_count ? narrow_tiles : sm_count);
+      plan->first_split_tile = 0;
+      plan->scratch_bytes = scratch;
+      return HC_CUDA_OK;
     }
     const int64_t split_tiles = plan->splits > 1 ? tiles - first_split_tile : 0;
     const int64_t units = tiles + split_tiles * (plan->splits - 1);
@@ -620,7 +635,8 @@ int enqueue_gemm(HcCudaContext *ctx, const HcCudaGemmArgs *args, const HcCudaGem
   const uint32_t k_scale = static_cast<uint32_t>(2 / es);  // elements of k per 2 bytes: boxes are 128 bytes of k
   if (plan.variant == HC_CUDA_GEMM_DENSE) {
     const hc::sm100::DenseTileShape t = hc::sm100::dense_tile_shape();
-    const bool pairs = hc::sm100::dense_uses_pairs(m, n, k, ctx->prop.multiProcessorCount);
+    const bool narrow = plan.tile_n == hc::sm100::dense_narrow_block_n();  // 128 x 128 tiles on single CTAs
+    const bool pairs = !narrow && hc::sm100::dense_uses_pairs(m, n, k, ctx->prop.multiProcessorCount);
     if (int rc = encode_map(ctx, &tmap_a, args->dtype, a, k, m, static_cast<uint64_t>(lda) * es,
                             t.block_k * k_scale, t.block_m))
       return rc;
@@ -628,7 +644,7 @@ int enqueue_gemm(HcCudaContext *ctx, const HcCudaGemmArgs *args, const HcCudaGem
     // of n (256 on single CTAs, 128 per CTA of a pair).
     if (int rc = b_nk_now ? encode_map(ctx, &tmap_b, args->dtype, b, k, n, static_cast<uint64_t>(ldb) * es,
                                        t.block_k * k_scale,
-                                       (pairs && plan.cluster_size == 0) ? t.block_n / 2 : t.block_n)
+                                       (narrow || (pairs && plan.cluster_size == 0)) ? t.block_n / 2 : t.block_n)
                           : encode_map(ctx, &tmap_b, args->dtype, b, n, k, static_cast<uint64_t>(ldb) * 2, 64,
                                        t.block_k))
       return rc;
@@ -722,7 +738,8 @@ int enqueue_gemm(HcCudaContext *ctx, const HcCudaGemmArgs *args, const HcCudaGem
     } else {
       HC_TRY_CUDA(ctx, hc::sm100::launch_gemm_dense(tmap_a, tmap_b, args->c, m, n, k, args->ldc,
                                                     args->dtype, ctx->group_n, plan.grid, b_layout, ep,
-                                                    c_map, split, &tmap_p, ctx->status_dev, ctx->stream));
+                                                    c_map, split, &tmap_p, ctx->status_dev, ctx->stream,
+                                                    narrow ? hc::sm100::dense_narrow_block_n() : t.block_n));
     }
     return HC_CUDA_OK;
   }

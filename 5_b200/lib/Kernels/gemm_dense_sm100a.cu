@@ -26,6 +26,7 @@
 #include "gemm_launch.h"
 #include "sm100_ptx.cuh"
 
+#include <cstdlib>
 #include <type_traits>
 
 namespace hc {
@@ -34,10 +35,11 @@ namespace sm100 {
 namespace dense {
 
 constexpr int kBlockM = 128;
-constexpr int kBlockN = 256;
+constexpr int kWideBlockN = 256;    // the tile width the planner counts with
+constexpr int kNarrowBlockN = 128;  // for products whose 256-wide tiles would leave most SMs idle
 constexpr int kBlockK = 64;  // 64 x 2 bytes = one 128-byte swizzle row
 constexpr int kUmmaK = 16;
-constexpr int kStages = 4;
+constexpr int kStages = 4;  // of the 256-wide tiles; the 128-wide ones have five (see Tile)
 // Warp 0 loads, warp 1 issues the MMAs, the rest drain accumulators: eight warps in the plain
 // kernel (two per quarter of tensor-memory lanes, each half of the tile's columns), four in the
 // one that reads C in its epilogue, which needs more registers per thread.
@@ -47,16 +49,25 @@ struct Roles {
   static constexpr int kEpilogueWarps = 8;
   static constexpr int kThreads = 64 + 32 * kEpilogueWarps;
 };
-constexpr int kTmemColumns = 512;  // two fp32 accumulators of kBlockN columns
-
 constexpr uint32_t kATileBytes = kBlockM * kBlockK * 2;            // 16 KiB
 constexpr uint32_t kBChunkBytes = 64 * kBlockK * 2;                // 64 columns x 64 k-rows
-constexpr uint32_t kBTileBytes = kBChunkBytes * (kBlockN / 64);    // 32 KiB
-constexpr uint32_t kStageBytes = kATileBytes + kBTileBytes;        // 48 KiB
 constexpr uint32_t kEpilogueWarpBytes = 32 * 32 * 4;               // one 32x32 fp32 block
 constexpr uint32_t kBarrierBytes = 256;
-constexpr uint32_t kSmemBytes = kStages * kStageBytes + kMaxEpilogueWarps * kEpilogueWarpBytes +
-                                kBarrierBytes + 1024 /* alignment slack */;
+
+// What follows from the tile width: 256 columns -- 48 KiB per stage, four stages, all 512 columns of
+// tensor memory for the two accumulators; 128 columns -- 32 KiB per stage, five stages (the
+// barriers of a sixth would not fit below the per-warp ones), 256 columns of tensor memory.
+template <int kBlockN>
+struct Tile {
+  static constexpr int kStages = kBlockN == kWideBlockN ? dense::kStages : 5;
+  static constexpr int kTmemColumns = 2 * kBlockN;  // two fp32 accumulators
+  static constexpr uint32_t kBTileBytes = kBChunkBytes * (kBlockN / 64);
+  static constexpr uint32_t kStageBytes = kATileBytes + kBTileBytes;
+  static constexpr uint32_t kSmemBytes = kStages * kStageBytes + kMaxEpilogueWarps * kEpilogueWarpBytes +
+                                         kBarrierBytes + 1024 /* alignment slack */;
+  static_assert(8 * (2 * kStages + 4) + 8 <= 128, "ring and accumulator barriers end below the per-warp barriers");
+};
+constexpr uint32_t kSmemBytes = Tile<kWideBlockN>::kSmemBytes;
 
 struct TileCoord {
   int m_blk;
@@ -78,7 +89,7 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int tiles_m, int tiles
 }
 
 // kReadsC: the epilogue has to read C's previous contents (see gemm_dense_pair_kernel).
-template <bool kReadsC>
+template <bool kReadsC, int kBlockN>
 __global__ void __launch_bounds__(Roles<kReadsC>::kThreads, 1)
 gemm_dense_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   const __grid_constant__ CUtensorMap tmap_b,
@@ -90,6 +101,9 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t smem_base = (raw_addr + 1023u) & ~1023u;  // swizzled tiles need 1 KiB alignment
   uint8_t *smem_gen = smem_raw + (smem_base - raw_addr);
+  constexpr int kStages = Tile<kBlockN>::kStages;
+  constexpr int kTmemColumns = Tile<kBlockN>::kTmemColumns;
+  constexpr uint32_t kStageBytes = Tile<kBlockN>::kStageBytes;
 
   const uint32_t epi_base = smem_base + kStages * kStageBytes;
   constexpr int kEpilogueWarps = Roles<kReadsC>::kEpilogueWarps;
@@ -177,7 +191,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tmap_a,
             for (int j = 0; j < kBlockN / 64; ++j)
               tma_load_2d(b_dst + j * kBChunkBytes, &tmap_b, full_bar(stage), n0 + j * 64, kb * kBlockK);
           } else {
-            // B stored [N, K]: one box of 256 rows (n) x 64 k, K-major like A.
+            // B stored [N, K]: one box of kBlockN rows (n) x 64 k, K-major like A.
             tma_load_2d(b_dst, &tmap_b, full_bar(stage), (kb * kBlockK) << elem8, n0);
           }
           if (++stage == kStages) {
@@ -332,25 +346,36 @@ cudaError_t launch_gemm_dense(const CUtensorMap &tmap_a, const CUtensorMap &tmap
                               int m, int n, int k, long long ldc, int dtype, int group_n,
                               int max_ctas, int b_layout, const Epilogue &ep, const CUtensorMap *tmap_c,
                               const SplitK &split, const CUtensorMap *tmap_partials, int *status,
-                                   cudaStream_t stream) {
+                                   cudaStream_t stream, int block_n) {
   using namespace dense;
+  if (block_n != kWideBlockN && block_n != kNarrowBlockN)
+    return cudaErrorInvalidValue;
+  const bool narrow = block_n == kNarrowBlockN;
+  if (narrow && split.splits != 1)
+    return cudaErrorInvalidValue;  // the partial tiles are laid out for 256-wide tiles
   static thread_local int configured_device = -1;
   int device = 0;
   cudaError_t err = cudaGetDevice(&device);
   if (err != cudaSuccess)
     return err;
   if (configured_device != device) {
-    err = cudaFuncSetAttribute(gemm_dense_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               static_cast<int>(kSmemBytes));
+    err = cudaFuncSetAttribute(gemm_dense_kernel<false, kWideBlockN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(Tile<kWideBlockN>::kSmemBytes));
     if (err == cudaSuccess)
-      err = cudaFuncSetAttribute(gemm_dense_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 static_cast<int>(kSmemBytes));
+      err = cudaFuncSetAttribute(gemm_dense_kernel<true, kWideBlockN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(Tile<kWideBlockN>::kSmemBytes));
+    if (err == cudaSuccess)
+      err = cudaFuncSetAttribute(gemm_dense_kernel<false, kNarrowBlockN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(Tile<kNarrowBlockN>::kSmemBytes));
+    if (err == cudaSuccess)
+      err = cudaFuncSetAttribute(gemm_dense_kernel<true, kNarrowBlockN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(Tile<kNarrowBlockN>::kSmemBytes));
     if (err != cudaSuccess)
       return err;
     configured_device = device;
   }
   const int tiles_m = (m + kBlockM - 1) / kBlockM;
-  const int tiles_n = (n + kBlockN - 1) / kBlockN;
+  const int tiles_n = (n + block_n - 1) / block_n;
   const long long num_tiles = static_cast<long long>(tiles_m) * tiles_n;
   if (num_tiles <= 0 || num_tiles > 0x7fffffffLL)
     return cudaErrorInvalidValue;
@@ -366,7 +391,7 @@ cudaError_t launch_gemm_dense(const CUtensorMap &tmap_a, const CUtensorMap &tmap
   if (elem8 && b_layout != kBLayoutNK)
     return cudaErrorInvalidValue;  // 8-bit operands are K-major: the caller transposes a [K, N] B first
   const uint32_t idesc = make_idesc_f16(dtype_format(dtype), /*a_mn_major=*/false,
-                                        /*b_mn_major=*/b_layout == kBLayoutKN, kBlockM, kBlockN);
+                                        /*b_mn_major=*/b_layout == kBLayoutKN, kBlockM, block_n);
   if (group_n < 1)
     group_n = 1;
   // C leaves through TMA stores when it is aligned (tmap_c) and goes nowhere else. Element-wise work
@@ -386,14 +411,19 @@ cudaError_t launch_gemm_dense(const CUtensorMap &tmap_a, const CUtensorMap &tmap
   const int c_tma = (tma_possible && !reads_c) ? 1 : 0;
   const CUtensorMap c_map = c_tma ? *tmap_c : tmap_a;  // unused unless c_tma
   const CUtensorMap p_map = split.splits > 1 ? *tmap_partials : tmap_a;  // unused unless split
-  if (reads_c)
-    gemm_dense_kernel<true><<<grid, Roles<true>::kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, c_map, c_tma, p_map, c, m, n, k, ldc, idesc,
-                                                                       tiles_m, tiles_n, group_n, b_layout, elem8, launch_ep,
-                                                                       split, status);
+#define HC_DENSE_LAUNCH(READS_C, BLOCK_N)                                                                       \
+  gemm_dense_kernel<READS_C, BLOCK_N><<<grid, Roles<READS_C>::kThreads, Tile<BLOCK_N>::kSmemBytes, stream>>>(      \
+      tmap_a, tmap_b, c_map, c_tma, p_map, c, m, n, k, ldc, idesc, tiles_m, tiles_n, group_n, b_layout, elem8,  \
+      launch_ep, split, status)
+  if (reads_c && narrow)
+    HC_DENSE_LAUNCH(true, kNarrowBlockN);
+  else if (reads_c)
+    HC_DENSE_LAUNCH(true, kWideBlockN);
+  else if (narrow)
+    HC_DENSE_LAUNCH(false, kNarrowBlockN);
   else
-    gemm_dense_kernel<false><<<grid, Roles<false>::kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, c_map, c_tma, p_map, c, m, n, k, ldc, idesc,
-                                                                        tiles_m, tiles_n, group_n, b_layout, elem8, launch_ep,
-                                                                        split, status);
+    HC_DENSE_LAUNCH(false, kWideBlockN);
+#undef HC_DENSE_LAUNCH
   return cudaGetLastError();
 }
 
@@ -427,7 +457,7 @@ int dense_choose_splits(long long tiles, int slots, int num_kb, long long *first
 size_t dense_partials_bytes(long long split_tiles, int splits, bool pairs) {
   if (splits <= 1)
     return 0;
-  const size_t tile_floats = static_cast<size_t>(pairs ? 2 * dense::kBlockM : dense::kBlockM) * dense::kBlockN;
+  const size_t tile_floats = static_cast<size_t>(pairs ? 2 * dense::kBlockM : dense::kBlockM) * dense::kWideBlockN;
   return static_cast<size_t>(split_tiles) * splits * tile_floats * sizeof(float);
 }
 
@@ -435,10 +465,30 @@ size_t dense_counters_bytes(long long split_tiles) {
   return static_cast<size_t>(split_tiles) * 2 * dense::kMaxEpilogueWarps * sizeof(unsigned);
 }
 
+int dense_narrow_block_n() { return dense::kNarrowBlockN; }
+
+bool dense_uses_narrow(long long m, long long n, int sm_count, bool pairs) {
+  if (const char *forced = std::getenv("HC_CUDA_DENSE_NARROW"))  // tuning aid: "1" always, "0" never
+    return std::atoi(forced) != 0;
+  if (sm_count < 1)
+    return false;
+  // Only when the 256-wide tiles (on CTA pairs: their 256 x 256) would keep at most half of the SMs
+  // busy and the 128 x 128 tiles fit one round: twice the CTAs then work for a little over half as
+  // long each. A 128 x 128 tile needs half as many flops per operand byte again as a 128 x 256 one,
+  // and with every SM pulling its own operands the L2 is the bound (measured: 1536^3, 144 tiles, 17.2
+  // us = 6.6 TB/s out of L2, against 20.2 us on 72 CTAs; 1024^3 12.3 against 16.4 us), so products of
+  // more than one round lose (2560^3: 45 against 37 us) and stay on the wide tiles.
+  const long long rows = (m + dense::kBlockM - 1) / dense::kBlockM;
+  const long long wide_ctas = pairs ? 2 * ((m + 2 * dense::kBlockM - 1) / (2 * dense::kBlockM)) * ((n + 255) / 256)
+                                    : rows * ((n + 255) / 256);
+  const long long narrow_tiles = rows * ((n + 127) / 128);
+  return 2 * wide_ctas <= sm_count && narrow_tiles <= sm_count && narrow_tiles > wide_ctas;
+}
+
 DenseTileShape dense_tile_shape() {
   DenseTileShape s;
   s.block_m = dense::kBlockM;
-  s.block_n = dense::kBlockN;
+  s.block_n = dense::kWideBlockN;
   s.block_k = dense::kBlockK;
   s.stages = dense::kStages;
   s.smem_bytes = dense::kSmemBytes;

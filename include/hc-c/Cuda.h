@@ -39,7 +39,7 @@
 extern "C" {
 #endif
 
-#define HC_CUDA_API_VERSION 7
+#define HC_CUDA_API_VERSION 8
 
 typedef enum HcCudaStatus {
   HC_CUDA_OK = 0,
@@ -167,6 +167,9 @@ typedef struct HcCudaGemmPlanInfo {
   int32_t cluster_size;     /* dense, few tiles and a long k: CTAs per thread-block cluster that share
                                one 128x256 tile (each a range of k, `splits` == cluster_size, partial
                                tiles added through distributed shared memory); 0 otherwise */
+  int32_t tile_n;           /* dense: columns of a tile of C -- 256, or 128 for small products whose
+                               256-wide tiles would leave most SMs idle (single CTAs, never split
+                               over k); 0 for other variants */
 } HcCudaGemmPlanInfo;
 
 typedef struct HcCudaDeviceInfo {

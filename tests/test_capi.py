@@ -55,6 +55,10 @@ def test_missing_device_is_reported_not_papered_over() -> None:
     assert lib.hcCudaGemm(None, None) == 1
 
 
+def skinny_tile_n_is_zero() -> bool:
+    return cuda.plan_gemm(8, 16384, 8192, "float16").tile_n == 0
+
+
 def test_plan_chooses_variants() -> None:
     dense = cuda.plan_gemm(8192, 8192, 8192, "float16")
     assert (dense.variant, dense.tiles_m, dense.tiles_n, dense.grid, dense.splits) == ("dense", 16, 32, 148, 1)  # 512x256 tiles
@@ -68,7 +72,16 @@ def test_plan_chooses_variants() -> None:
     assert cuda.plan_gemm(8192, 8192, 8192, "float16", ldc=8193).tiles_m == 16
     assert dense.kernel_launches == 1 and dense.scratch_bytes == 0 and not dense.repack_a
     small = cuda.plan_gemm(100, 300, 64, "bfloat16")
-    assert (small.variant, small.tiles_m, small.tiles_n, small.grid) == ("dense", 1, 2, 2)
+    assert (small.variant, small.tiles_m, small.tiles_n, small.grid, small.tile_n) == ("dense", 1, 3, 3, 128)
+    # 128-wide tiles for small unsplit products that would otherwise leave most SMs idle.
+    mid = cuda.plan_gemm(1536, 1536, 1536, "float16")
+    assert (mid.tile_n, mid.tiles_m, mid.tiles_n, mid.grid, mid.splits) == (128, 12, 12, 144, 1)
+    assert cuda.plan_gemm(1024, 1024, 1024, "float16").tile_n == 128
+    assert cuda.plan_gemm(2048, 2048, 2048, "float16").tile_n == 256  # 128 CTAs busy already
+    assert cuda.plan_gemm(2560, 2560, 2560, "float16").tile_n == 256  # more than a round of narrow tiles
+    assert dense.tile_n == 256 and cuda.plan_gemm(4096, 4096, 1024, "float16").tile_n == 256
+    assert cuda.plan_gemm(512, 512, 16384, "float16").tile_n == 256  # shared among clusters instead
+    assert skinny_tile_n_is_zero()
     skinny = cuda.plan_gemm(8, 16384, 8192, "float16")
     assert (skinny.variant, skinny.tiles_n, skinny.splits, skinny.grid) == ("skinny", 128, 1, 128)
     assert skinny.scratch_bytes == 0  # enough column blocks to fill the GPU: no split over k

@@ -188,6 +188,76 @@ def test_dense_wide_tiles(shape, dtype: str, gpu_ctx, monkeypatch) -> None:
         buf.free()
 
 
+NARROW_SHAPES = [
+    # one tile; ragged on every axis; more tiles than SMs (several rounds through both accumulators);
+    # k below, at and across a ring stage; n below one tile
+    (100, 300, 64), (128, 128, 128), (129, 130, 70), (1000, 1100, 520), (1536, 1536, 1536), (2100, 2300, 200), (333, 40, 500),
+]
+
+
+@pytest.mark.parametrize("shape", NARROW_SHAPES)
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16", "float8_e4m3fn"])
+def test_dense_narrow_tiles(shape, dtype: str, gpu_ctx, monkeypatch) -> None:
+    """The 128x128 tiles of the single-CTA dense kernel, forced onto every shape so that edge tiles on
+    every axis, several rounds of tiles, both layouts of B, ordinary stores, fused operations, both
+    kinds of accumulation and a 16-bit C run through them; same bits as the 256-wide tiles."""
+    monkeypatch.setenv("HC_CUDA_DENSE_NARROW", "1")
+    m, n, k = shape
+    plan = gpu_ctx.plan(m, n, k, dtype, variant=cuda.VARIANT_DENSE)
+    assert (plan.tile_n, plan.tiles_m, plan.tiles_n, plan.splits) == (128, -(-m // 128), -(-n // 128), 1)
+    a, b = float8_inputs(m, n, k, dtype) if dtype.startswith("float8") else random_inputs(m, n, k, dtype, scale=0.25)
+    expect = cpu_ref.matmul_k_ascending(a, b)
+    da, db, dbt = gpu_ctx.to_device(a), gpu_ctx.to_device(b), gpu_ctx.to_device(np.ascontiguousarray(b.T))
+    guard = 3
+    raw = cuda.DeviceBuffer(gpu_ctx, (m + 2 * guard, n + 8), np.float32)
+    raw.fill_bytes(0xFF)
+    dc = raw.window(guard, guard + m, 4, 4 + n)  # 16-byte aligned rows: the TMA-store path
+    gpu_ctx.gemm(da, db, dc, variant=cuda.VARIANT_DENSE)
+    gpu_ctx.synchronize()
+    whole = raw.to_numpy()
+    c = np.ascontiguousarray(whole[guard : guard + m, 4 : 4 + n])
+    assert_close_to_oracle(c, a, b, expect=expect)
+    whole[guard : guard + m, 4 : 4 + n] = np.nan
+    assert np.isnan(whole).all()  # nothing written outside C
+    dct = gpu_ctx.empty((m, n), np.float32)
+    gpu_ctx.gemm(da, dbt, dct, b_transposed=True, variant=cuda.VARIANT_DENSE)
+    gpu_ctx.synchronize()
+    assert np.array_equal(dct.to_numpy(), c)
+    odd = cuda.DeviceBuffer(gpu_ctx, (m, n), np.float32, ld=n + 1)  # ordinary stores
+    gpu_ctx.gemm(da, db, odd, variant=cuda.VARIANT_DENSE)
+    gpu_ctx.synchronize()
+    assert np.array_equal(odd.to_numpy(), c)
+    bias = np.random.default_rng(4).standard_normal(n).astype(np.float32)
+    dbias = gpu_ctx.to_device(bias)
+    ops = (("scale", 0.5), ("bias",), ("max", 0.0))
+    gpu_ctx.gemm(da, db, dct, epilogue=ops, bias=dbias, variant=cuda.VARIANT_DENSE)
+    gpu_ctx.synchronize()
+    assert_fused_close(dct.to_numpy(), a, b, epilogue=ops, bias=bias)
+    c0 = np.random.default_rng(5).standard_normal((m, n)).astype(np.float32)
+    dct.copy_from_host(c0)
+    gpu_ctx.gemm(da, db, dct, accumulate=True, variant=cuda.VARIANT_DENSE)  # performed by the TMA stores
+    gpu_ctx.synchronize()
+    assert_fused_close(dct.to_numpy(), a, b, c0=c0)
+    odd.copy_from_host(c0)
+    gpu_ctx.gemm(da, db, odd, accumulate=True, epilogue=(("scale", 2.0),), variant=cuda.VARIANT_DENSE)  # reads C
+    gpu_ctx.synchronize()
+    assert_fused_close(odd.to_numpy(), a, b, c0=c0, epilogue=(("scale", 2.0),))
+    half = gpu_ctx.empty((m, n), np.float16)
+    gpu_ctx.gemm(da, db, half, variant=cuda.VARIANT_DENSE)
+    gpu_ctx.synchronize()
+    assert np.array_equal(half.to_numpy(), c.astype(np.float16))
+    monkeypatch.setenv("HC_CUDA_DENSE_NARROW", "0")
+    assert gpu_ctx.plan(m, n, k, dtype, variant=cuda.VARIANT_DENSE).tile_n == 256
+    gpu_ctx.gemm(da, db, dct, variant=cuda.VARIANT_DENSE)
+    gpu_ctx.synchronize()
+    if gpu_ctx.plan(m, n, k, dtype, variant=cuda.VARIANT_DENSE).splits == 1:
+        assert np.array_equal(dct.to_numpy(), c)  # the 256-wide tiles: the same sums in the same order
+    else:
+        assert_close_to_oracle(dct.to_numpy(), a, b, expect=expect)
+    for buf in (da, db, dbt, raw, dct, odd, dbias, half):
+        buf.free()
+
+
 FLOAT8_SHAPES = [
     # dense on single CTAs and CTA pairs, skinny with and without split-k; k below, at and across the
     # 128-element stage of the 8-bit kernels; odd pitches (repack) and aligned ones
