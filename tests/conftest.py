@@ -12,8 +12,9 @@ import pytest
 REPO = Path(__file__).resolve().parent.parent
 PACKAGE = REPO / "5_b200"
 GOLDEN = REPO / "tests" / "golden"
-# Checkout of the reference project, for the few tests that run its own code (skipped without it).
-REFERENCE = Path(os.environ.get("HC_REFERENCE_DIR", "/root/reference"))
+# Checkout of the reference project, for the few tests that run its own code (skipped without it)
+# and for tests/golden/make_golden.py: $HC_REFERENCE_DIR, else this location.
+REFERENCE = Path(os.environ.get("HC_REFERENCE_DIR") or "/root/reference")
 
 for entry in (str(REPO), str(PACKAGE)):
     if entry not in sys.path:

@@ -104,9 +104,15 @@ def _save(name: str, a: np.ndarray, b: np.ndarray, c: np.ndarray, **extra: np.nd
 
 def main() -> int:
     parser = argparse.ArgumentParser()
-    parser.add_argument("--reference", default=os.environ.get("HC_REFERENCE_DIR", "/root/reference"),
-                        help="checkout of the reference project (default: $HC_REFERENCE_DIR)")
+    parser.add_argument("--reference", default=os.environ.get("HC_REFERENCE_DIR"),
+                        help="checkout of the reference project (default: $HC_REFERENCE_DIR, else the location "
+                             "tests/conftest.py names)")
     args = parser.parse_args()
+    if args.reference is None:
+        sys.path.insert(0, str(HERE.parent))
+        from conftest import REFERENCE  # the one place that names a default location
+
+        args.reference = str(REFERENCE)
     ex = _import_reference(Path(args.reference))
 
     blocked = {}
