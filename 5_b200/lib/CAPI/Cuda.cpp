@@ -370,7 +370,14 @@ int plan_gemm(const HcCudaContext *ctx, const HcCudaGemmArgs *args, int sm_count
     const int num_kb = static_cast<int>((k + block_k - 1) / block_k);
     const int slots = pairs ? sm_count / 2 : sm_count;
     long long first_split_tile = 0;
-    plan->splits = hc::sm100::dense_choose_splits(tiles, slots, num_kb, &first_split_tile);
+    // A small product with a short k whose 256-wide tiles would leave most SMs idle runs on 128 x 128
+    // tiles (single CTAs, decided first: it is then not split over k).
+    const bool narrow = !wide && !(ctx != nullptr && (ctx->planning_push || ctx->planning_host_panels)) &&
+                        std::getenv("HC_CUDA_DENSE_SPLITS") == nullptr &&
+                        hc::sm100::dense_uses_narrow(m, n, k, sm_count, pairs);
+    plan->splits = narrow ? 1 : hc::sm100::dense_choose_splits(tiles, slots, num_kb, &first_split_tile);
+    if (narrow)
+      first_split_tile = 0;
     if (wide || (ctx != nullptr && ctx->planning_host_panels)) {
       // The 512x256 tiles are never split (they are only kept when no split is wanted), and the
       // panels of one host-buffer product must give the bits of the unsplit product.
@@ -406,10 +413,7 @@ int plan_gemm(const HcCudaContext *ctx, const HcCudaGemmArgs *args, int sm_count
         return HC_CUDA_OK;
       }
     }
-    // A small unsplit product whose 256-wide tiles would leave most SMs idle runs on 128 x 128 tiles
-    // (single CTAs): twice the tiles, each a little over half the time.
-    if (plan->splits == 1 && !wide && !(ctx != nullptr && (ctx->planning_push || ctx->planning_host_panels)) &&
-        hc::sm100::dense_uses_narrow(m, n, sm_count, pairs)) {
+    if (narrow && plan->splits == 1 && plan->cluster_size == 0) {
       const int64_t narrow_n = hc::sm100::dense_narrow_block_n();
       plan->tile_n = static_cast<int32_t>(narrow_n);
       plan->tiles_m = static_cast<int32_t>((m + t.block_m - 1) / t.block_m);

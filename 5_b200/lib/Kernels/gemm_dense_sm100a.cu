@@ -467,22 +467,23 @@ size_t dense_counters_bytes(long long split_tiles) {
 
 int dense_narrow_block_n() { return dense::kNarrowBlockN; }
 
-bool dense_uses_narrow(long long m, long long n, int sm_count, bool pairs) {
+bool dense_uses_narrow(long long m, long long n, long long k, int sm_count, bool pairs) {
   if (const char *forced = std::getenv("HC_CUDA_DENSE_NARROW"))  // tuning aid: "1" always, "0" never
     return std::atoi(forced) != 0;
   if (sm_count < 1)
     return false;
-  // Only when the 256-wide tiles (on CTA pairs: their 256 x 256) would keep at most half of the SMs
-  // busy and the 128 x 128 tiles fit one round: twice the CTAs then work for a little over half as
-  // long each. A 128 x 128 tile needs half as many flops per operand byte again as a 128 x 256 one,
-  // and with every SM pulling its own operands the L2 is the bound (measured: 1536^3, 144 tiles, 17.2
-  // us = 6.6 TB/s out of L2, against 20.2 us on 72 CTAs; 1024^3 12.3 against 16.4 us), so products of
-  // more than one round lose (2560^3: 45 against 37 us) and stay on the wide tiles.
+  // Only when the 256-wide tiles (on CTA pairs: their 256 x 256) would keep at most a quarter of the
+  // SMs busy, the 128 x 128 tiles fit one round and k is short: twice the CTAs then work for a little
+  // over half as long each, and no partial tiles have to be added up (1024^3: 12.3 us against 14.4 on
+  // 32 CTAs or split over k; 768^3: 10.8 against 12.3). A 128 x 128 tile needs half as many flops per
+  // operand byte again as a 128 x 256 one, and with every SM pulling its own operands the L2 becomes
+  // the bound (1536^3, 144 tiles: 16.3 us = 6.6 TB/s out of L2, against 14.6 us for 72 tiles split in
+  // two over k), so larger products stay on the wide tiles (2560^3: 45 against 37 us).
   const long long rows = (m + dense::kBlockM - 1) / dense::kBlockM;
   const long long wide_ctas = pairs ? 2 * ((m + 2 * dense::kBlockM - 1) / (2 * dense::kBlockM)) * ((n + 255) / 256)
                                     : rows * ((n + 255) / 256);
   const long long narrow_tiles = rows * ((n + 127) / 128);
-  return 2 * wide_ctas <= sm_count && narrow_tiles <= sm_count && narrow_tiles > wide_ctas;
+  return 4 * wide_ctas <= sm_count && narrow_tiles <= sm_count && narrow_tiles > wide_ctas && k <= 2048;
 }
 
 DenseTileShape dense_tile_shape() {

@@ -125,9 +125,10 @@ cudaError_t launch_gemm_dense(const CUtensorMap &tmap_a, const CUtensorMap &tmap
                                    cudaStream_t stream, int block_n = 256);
 // `block_n`: 256, or 128 (dense_narrow_block_n) for tiles of 128 x 128 -- never split over k; tmap_b of a
 // B stored [N, K] then has boxes of 128 rows. dense_uses_narrow: whether the 256-wide tiles (or CTA pairs)
-// of an unsplit m x n product would keep at most half of the SMs busy while 128-wide tiles fit one round.
+// of an m x n product with a short k would keep at most a quarter of the SMs busy while 128-wide tiles fit
+// one round; such a product is not split over k.
 int dense_narrow_block_n();
-bool dense_uses_narrow(long long m, long long n, int sm_count, bool pairs);
+bool dense_uses_narrow(long long m, long long n, long long k, int sm_count, bool pairs);
 
 // Few tiles, long k: every 128x256 tile is shared by `groups` thread-block clusters of `cluster_size`
 // CTAs (2, 4, 8 or 16), each CTA a range of the k-blocks; the partial tiles are summed through

@@ -74,10 +74,16 @@ def test_plan_chooses_variants() -> None:
     small = cuda.plan_gemm(100, 300, 64, "bfloat16")
     assert (small.variant, small.tiles_m, small.tiles_n, small.grid, small.tile_n) == ("dense", 1, 3, 3, 128)
     # 128-wide tiles for small unsplit products that would otherwise leave most SMs idle.
+    little = cuda.plan_gemm(1024, 1024, 1024, "float16")
+    assert (little.tile_n, little.tiles_m, little.tiles_n, little.grid, little.splits) == (128, 8, 8, 64, 1)
+    assert cuda.plan_gemm(1024, 1024, 4096, "float16").tile_n == 256  # a long k: shared among clusters instead
+    # One round of 128 x 256 tiles and a moderate k: single CTAs, not pairs (a cluster launch costs more);
+    # 72 tiles are split in two over k and the halves meet in a cluster of two.
     mid = cuda.plan_gemm(1536, 1536, 1536, "float16")
-    assert (mid.tile_n, mid.tiles_m, mid.tiles_n, mid.grid, mid.splits) == (128, 12, 12, 144, 1)
-    assert cuda.plan_gemm(1024, 1024, 1024, "float16").tile_n == 128
-    assert cuda.plan_gemm(2048, 2048, 2048, "float16").tile_n == 256  # 128 CTAs busy already
+    assert (mid.tile_n, mid.tiles_m, mid.tiles_n, mid.grid, mid.splits, mid.cluster_size) == (256, 12, 6, 144, 2, 2)
+    square = cuda.plan_gemm(2048, 2048, 2048, "float16")
+    assert (square.tile_n, square.tiles_m, square.tiles_n, square.grid, square.splits) == (256, 16, 8, 128, 1)
+    assert cuda.plan_gemm(512, 8192, 8192, "float16").tiles_m == 2  # a long k: CTA pairs
     assert cuda.plan_gemm(2560, 2560, 2560, "float16").tile_n == 256  # more than a round of narrow tiles
     assert dense.tile_n == 256 and cuda.plan_gemm(4096, 4096, 1024, "float16").tile_n == 256
     assert cuda.plan_gemm(512, 512, 16384, "float16").tile_n == 256  # shared among clusters instead
