@@ -7,7 +7,9 @@
 // examples/amdgpu_gfx11_wmma_matmul.py:316-323).
 //
 // One thread produces 8 consecutive destination elements (one 128-bit store). The source
-// row may start at any 2-byte boundary, so it is read with 16-bit loads; neighbouring
+// row may start at any 2-byte boundary: where its 8 elements start on a 4-byte boundary they
+// are read with four 32-bit loads, otherwise with a 16-bit load, three 32-bit loads and a
+// 16-bit load (the last piece of a row, which may be shorter, with 16-bit loads); neighbouring
 // threads read neighbouring addresses, so the loads of a warp still coalesce.
 #include "gemm_launch.h"
 
@@ -36,18 +38,35 @@ repack_pitch_kernel(RepackJob job0, RepackJob job1, int blocks0) {
   const int pieces_per_row = (job.cols + 7) >> 3;
   const long long total = static_cast<long long>(job.rows) * pieces_per_row;
   for (long long idx = block * blockDim.x + threadIdx.x; idx < total; idx += blocks * blockDim.x) {
-    const int row = static_cast<int>(idx / pieces_per_row);
+    // (A 32-bit division when the number of pieces allows: the 64-bit one costs a hundred cycles.)
+    const int row = total <= 0x7fffffffLL ? static_cast<int>(static_cast<unsigned>(idx) / static_cast<unsigned>(pieces_per_row))
+                                          : static_cast<int>(idx / pieces_per_row);
     const int col0 = static_cast<int>(idx - static_cast<long long>(row) * pieces_per_row) << 3;
     const uint16_t *s = job.src + row * job.src_ld + col0;
-    uint16_t v[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i)
-      v[i] = (col0 + i < job.cols) ? __ldg(s + i) : static_cast<uint16_t>(0);
     uint4 packed;
-    packed.x = v[0] | (static_cast<uint32_t>(v[1]) << 16);
-    packed.y = v[2] | (static_cast<uint32_t>(v[3]) << 16);
-    packed.z = v[4] | (static_cast<uint32_t>(v[5]) << 16);
-    packed.w = v[6] | (static_cast<uint32_t>(v[7]) << 16);
+    if (col0 + 8 <= job.cols) {
+      if ((reinterpret_cast<uintptr_t>(s) & 3) == 0) {
+        const uint32_t *w = reinterpret_cast<const uint32_t *>(s);
+        packed = make_uint4(__ldg(w), __ldg(w + 1), __ldg(w + 2), __ldg(w + 3));
+      } else {
+        // s + 1 is 4-byte aligned: elements 1..6 come as three words, 0 and 7 on their own.
+        const uint32_t *w = reinterpret_cast<const uint32_t *>(s + 1);
+        const uint32_t first = __ldg(s), w0 = __ldg(w), w1 = __ldg(w + 1), w2 = __ldg(w + 2), last = __ldg(s + 7);
+        packed.x = first | (w0 << 16);
+        packed.y = (w0 >> 16) | (w1 << 16);
+        packed.z = (w1 >> 16) | (w2 << 16);
+        packed.w = (w2 >> 16) | (last << 16);
+      }
+    } else {
+      uint16_t v[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        v[i] = (col0 + i < job.cols) ? __ldg(s + i) : static_cast<uint16_t>(0);
+      packed.x = v[0] | (static_cast<uint32_t>(v[1]) << 16);
+      packed.y = v[2] | (static_cast<uint32_t>(v[3]) << 16);
+      packed.z = v[4] | (static_cast<uint32_t>(v[5]) << 16);
+      packed.w = v[6] | (static_cast<uint32_t>(v[7]) << 16);
+    }
     *reinterpret_cast<uint4 *>(job.dst + row * job.dst_ld + col0) = packed;
   }
 }
