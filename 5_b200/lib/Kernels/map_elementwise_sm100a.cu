@@ -146,11 +146,15 @@ map_f32_kernel(const float *__restrict__ x, const float *__restrict__ y, float *
     const float4 *x4 = reinterpret_cast<const float4 *>(x);
     const float4 *y4 = reinterpret_cast<const float4 *>(y);
     float4 *o4 = reinterpret_cast<float4 *>(out);
-    for (long long base = tid; base < vectors; base += threads * kVectorsPerThread) {
+    // A CTA's pass covers kVectorsPerThread x 4 KB in a row (vector j of a thread lies 4 KB behind
+    // vector j - 1), and the passes of the grid follow one another through the array.
+    constexpr long long kStride = kThreads;
+    for (long long base = static_cast<long long>(blockIdx.x) * (kThreads * kVectorsPerThread) + threadIdx.x;
+         base < vectors; base += threads * kVectorsPerThread) {
       float v[kValues], w[kValues];
 #pragma unroll
       for (int j = 0; j < kVectorsPerThread; ++j) {
-        const long long i = base + j * threads;
+        const long long i = base + j * kStride;
         float4 xv = make_float4(0.f, 0.f, 0.f, 0.f), yv = xv;
         if (i < vectors) {
           xv = __ldcs(x4 + i);
@@ -163,7 +167,7 @@ map_f32_kernel(const float *__restrict__ x, const float *__restrict__ y, float *
       apply_map_ops(v, w, ops);
 #pragma unroll
       for (int j = 0; j < kVectorsPerThread; ++j) {
-        const long long i = base + j * threads;
+        const long long i = base + j * kStride;
         if (i < vectors)
           __stcs(o4 + i, make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]));
       }
@@ -175,18 +179,19 @@ map_f32_kernel(const float *__restrict__ x, const float *__restrict__ y, float *
       out[tail + tid] = v[0];
     }
   } else {
-    for (long long base = tid; base < n; base += threads * kValues) {
+    for (long long base = static_cast<long long>(blockIdx.x) * (kThreads * kValues) + threadIdx.x; base < n;
+         base += threads * kValues) {
       float v[kValues], w[kValues];
 #pragma unroll
       for (int j = 0; j < kValues; ++j) {
-        const long long i = base + j * threads;
+        const long long i = base + j * kThreads;
         v[j] = i < n ? __ldcs(x + i) : 0.0f;
         w[j] = (kTwoInputs && i < n) ? __ldcs(y + i) : 0.0f;
       }
       apply_map_ops(v, w, ops);
 #pragma unroll
       for (int j = 0; j < kValues; ++j) {
-        const long long i = base + j * threads;
+        const long long i = base + j * kThreads;
         if (i < n)
           __stcs(out + i, v[j]);
       }
