@@ -332,7 +332,7 @@ int plan_gemm(const HcCudaContext *ctx, const HcCudaGemmArgs *args, int sm_count
 
   if (variant == HC_CUDA_GEMM_DENSE) {
     const hc::sm100::DenseTileShape t = hc::sm100::dense_tile_shape();
-    const bool pairs = hc::sm100::dense_uses_pairs(m, n, k, sm_count);
+    const bool pairs = hc::sm100::dense_uses_pairs(m, n, k, sm_count, ctx != nullptr && ctx->planning_push);
     // 512x256 tiles for products that fill the GPU with them, when the epilogue never has to read C
     // with ordinary loads (an accumulation must be one the TMA stores can perform) and the tiles go
     // nowhere but C. Decided again below if tiles turn out to be split over k.
@@ -640,7 +640,7 @@ int enqueue_gemm(HcCudaContext *ctx, const HcCudaGemmArgs *args, const HcCudaGem
   if (plan.variant == HC_CUDA_GEMM_DENSE) {
     const hc::sm100::DenseTileShape t = hc::sm100::dense_tile_shape();
     const bool narrow = plan.tile_n == hc::sm100::dense_narrow_block_n();  // 128 x 128 tiles on single CTAs
-    const bool pairs = !narrow && hc::sm100::dense_uses_pairs(m, n, k, ctx->prop.multiProcessorCount);
+    const bool pairs = !narrow && hc::sm100::dense_uses_pairs(m, n, k, ctx->prop.multiProcessorCount, ep.push_count > 0);
     if (int rc = encode_map(ctx, &tmap_a, args->dtype, a, k, m, static_cast<uint64_t>(lda) * es,
                             t.block_k * k_scale, t.block_m))
       return rc;

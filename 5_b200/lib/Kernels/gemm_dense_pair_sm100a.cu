@@ -459,7 +459,7 @@ cudaError_t launch_gemm_dense_pair(const CUtensorMap &tmap_a, const CUtensorMap 
 
 int dense_block_k(bool pairs) { return pairs ? dense_pair::kBlockK : dense_tile_shape().block_k; }
 
-bool dense_uses_pairs(long long m, long long n, long long k, int sm_count) {
+bool dense_uses_pairs(long long m, long long n, long long k, int sm_count, bool pushes) {
   // HC_CUDA_DENSE_MODE=single|pair forces a mode (tuning aid).
   if (const char *mode = std::getenv("HC_CUDA_DENSE_MODE")) {
     if (std::strcmp(mode, "single") == 0)
@@ -478,7 +478,8 @@ bool dense_uses_pairs(long long m, long long n, long long k, int sm_count) {
   // back over a long k (2048^3: 20.5 us on single CTAs against 22.5 on pairs; 2048 x 2048 x 256: 10.3
   // against 13.3; 512 x 8192 x 8192: 64 against 61).
   const char *forced_wide = std::getenv("HC_CUDA_DENSE_WIDE");  // tuning aid: "1" forces the 512x256 pair tiles
-  if (single_tiles <= sm_count && k <= 4096 && !(forced_wide != nullptr && std::strcmp(forced_wide, "1") == 0))
+  if (single_tiles <= sm_count && k <= 4096 && !pushes &&
+      !(forced_wide != nullptr && std::strcmp(forced_wide, "1") == 0))
     return false;
   const long long single_rounds = (single_tiles + sm_count - 1) / sm_count;
   const long long pair_rounds = (pair_tiles + sm_count / 2 - 1) / (sm_count / 2);

@@ -176,7 +176,10 @@ bool dense_uses_wide(long long m, long long n, long long k, int sm_count);
 constexpr int kDenseWideTileM = 512;
 
 // Whether the dense variant runs on CTA pairs for this problem.
-bool dense_uses_pairs(long long m, long long n, long long k, int sm_count);
+bool dense_uses_pairs(long long m, long long n, long long k, int sm_count, bool pushes = false);
+// (`pushes`: the launch also stores its tiles to peers. Such a product keeps the pairs' tile shape when
+// it fits one round of single CTAs too: its split decision, and with it the bits of C, then stay those
+// of the product without peers.)
 
 struct SkinnyShape {
   int block_n;     // columns of C per work unit
