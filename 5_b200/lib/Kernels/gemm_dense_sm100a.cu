@@ -476,9 +476,9 @@ bool dense_uses_narrow(long long m, long long n, long long k, int sm_count, bool
   // SMs busy, the 128 x 128 tiles fit one round and k is short: twice the CTAs then work for a little
   // over half as long each, and no partial tiles have to be added up (1024^3: 12.3 us against 14.4 on
   // 32 CTAs or split over k; 768^3: 10.8 against 12.3). A 128 x 128 tile needs half as many flops per
-  // operand byte again as a 128 x 256 one, and with every SM pulling its own operands the L2 becomes
-  // the bound (1536^3, 144 tiles: 16.3 us = 6.6 TB/s out of L2, against 14.6 us for 72 tiles split in
-  // two over k), so larger products stay on the wide tiles (2560^3: 45 against 37 us).
+  // operand byte again as a 128 x 256 one, and what an SM receives of its operands is bounded (1536^3,
+  // 144 tiles: a 32 KiB ring stage per CTA every 0.8 us, 16.3 us in all, against 14.6 us for 72 tiles
+  // split in two over k), so larger products stay on the wide tiles (2560^3: 45 against 37 us).
   const long long rows = (m + dense::kBlockM - 1) / dense::kBlockM;
   const long long wide_ctas = pairs ? 2 * ((m + 2 * dense::kBlockM - 1) / (2 * dense::kBlockM)) * ((n + 255) / 256)
                                     : rows * ((n + 255) / 256);
