@@ -149,6 +149,39 @@ def test_many_rows_of_several_leaves(gpu_ctx) -> None:
     dout.free()
 
 
+def test_random_shapes_pitches_and_forms_match_numpy(gpu_ctx) -> None:
+    """Eighty random problems (rows from 1 to 20000, values from 1 to 30000, padded and odd pitches,
+    rows of -0.0, all three forms), each against NumPy's own sum row by row."""
+    rng = np.random.default_rng(37)
+    for case in range(80):
+        kind = case % 4
+        if kind == 0:
+            w, h = int(rng.integers(1, 3000)), int(rng.integers(1, 300))
+        elif kind == 1:
+            w, h = int(rng.integers(1, 100)), int(rng.integers(1, 30000))
+        elif kind == 2:
+            w, h = int(rng.integers(1, 20000)), int(rng.integers(1, 140))
+        else:
+            w, h = int(rng.integers(1, 1000)), 8 * int(rng.integers(1, 400))
+        pad = int(rng.choice([0, 0, 1, 3, 4, 8]))
+        x = (rng.standard_normal((w, h)) * rng.choice([1e-3, 1.0, 1e3], size=(w, h))).astype(np.float32)
+        if case % 3 == 0:
+            x[int(rng.integers(0, w)), :] = -0.0
+        dx = cuda.DeviceBuffer(gpu_ctx, (w, h), np.float32, ld=h + pad)
+        dx.copy_from_host(x)
+        dout = gpu_ctx.empty((w,), np.float32)
+        square, take_sqrt = bool(case & 1), bool(case & 1) and bool(case & 2)
+        gpu_ctx.row_sum(dx, dout, square=square, take_sqrt=take_sqrt)
+        gpu_ctx.synchronize()
+        values = x * x if square else x
+        want = np.array([np.sum(row) for row in values], np.float32)
+        if take_sqrt:
+            want = np.sqrt(want)
+        assert same_bits(dout.to_numpy(), want), (w, h, pad, square, take_sqrt)
+        dx.free()
+        dout.free()
+
+
 def test_bad_arguments_are_rejected(gpu_ctx) -> None:
     dx, dout = gpu_ctx.empty((4, 8), np.float32), gpu_ctx.empty((4,), np.float32)
     with pytest.raises(ValueError, match="do not fit"):
